@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized linear-layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode GEMV of BASELINE config 2 (Q4_K, M=1, K=5120,
+N=25600) through the kernel-pack C ABI.  Prints ONE JSON line:
+
+  value     weight GB/s = algorithmic bytes per step / device time per step,
+            planes resident in HBM, cold L2 (the plane is cloned so that
+            consecutive steps never touch the same bytes);
+  e2e       the same metric with the step's activations coming from pinned
+            host memory and its outputs read back, copies inside the timed
+            region;
+  roofline  achieved GB/s of the GEMV kernel (per-launch CUDA events) against
+            the measured HBM copy bandwidth;
+  cpu_baseline  the reference's CPU path (dequant + scalar f32 matvec), ported
+            in oracle/, timed on this host's cores.
+
+With --gpus N > 1 (launched under torchrun) the N rows are sharded across the
+ranks and the outputs are all-gathered with NCCL (strong scaling).
+`--impl reference` times only the CPU path and prints the same line shape.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+K_DIM = 5120
+N_DIM = 25600
+FALLBACK_HBM_GBS = 6650.0
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(m, n=N_DIM, k=K_DIM):
+    """Q4_K GEMV bytes per step: raw weights 144 B per 256 + bf16 x + f32 y."""
+    return n * k // 256 * 144 + m * k * 2 + m * n * 4
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Polls NVML for SM clock and throttle reasons while a region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = get_reasons(self._h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self._nv:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "samples": len(self.samples), "reasons": sorted(self.reasons)}
+
+
+def cpu_baseline(steps, warmup, rows=N_DIM // 4):
+    """Reference CPU path for one step: dequant_q4_k of the plane + scalar f32
+    ascending-k matvec, on all host threads.  Returns (GB/s, cores, sample, ms)."""
+    import numpy as np
+    import oracle
+    w = oracle.fill_normal(rows * K_DIM, 0x5EED0200, 0.02)
+    raw = oracle.quantize_q4_k(w)
+    del w
+    x = oracle.bf16_round(oracle.fill_normal(K_DIM, 0x5EED0201, 1.0))
+    out = np.empty(rows * K_DIM, np.float32)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        oracle.dequant_q4_k(raw, out)
+        oracle.matvec_f32(out, x, K_DIM, rows)
+        t1 = time.perf_counter()
+        if i >= warmup:
+            times.append(t1 - t0)
+    sec = sum(times) / len(times)
+    gbs = algorithmic_bytes(1, rows) / sec / 1e9
+    sample = f"{rows} of {N_DIM} rows x K={K_DIM}, dequant_q4_k + scalar f32 matvec, {len(times)} passes"
+    return gbs, oracle.num_threads(), sample, sec * 1e3
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    steps = min(args.steps, 20)
+    warm = min(args.warmup, 2)
+    gbs, cores, sample, ms = cpu_baseline(steps, max(warm, 1))
+    line = {
+        "impl": "reference", "metric": "q4k_gemv_weight_gbs", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": max(warm, 1), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "Q4_K decode GEMV M=1 K=5120 N=25600 (BASELINE config 2), f32 activations holding bf16 values",
+            "sharding": "none" if n_gpus == 1 else f"N rows / {n_gpus} ranks + NCCL all-gather of y",
+            "l2": "cold: steps rotate over weight-plane clones totalling > 2x the 126 MB L2"}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from paddock_b200 import synth
+    from paddock_b200.planes import GpuExecutor
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ex = GpuExecutor()
+    rows = N_DIM // world
+    assert rows * world == N_DIM
+
+    # ---- synthetic plane: this rank's row band, quantized to raw Q4_K, repacked
+    w = synth.normal(rows * K_DIM, 0x5EED0200 + rank, 0.02, dev)
+    raw = synth.quantize_q4_k(w)
+    del w
+    plane_bytes = rows * K_DIM // 256 * 152
+    n_clones = max(2, -(-2 * L2_BYTES // plane_bytes) + 1)
+    planes = [ex.repack_kquant_raw(raw, K_DIM, rows) for _ in range(n_clones)]
+    del raw
+    x_host = synth.bf16_round(synth.normal(K_DIM, 0x5EED0201, 1.0, "cpu")).pin_memory()
+    x = x_host.to(dev)
+    y = torch.zeros(rows, dtype=torch.float32, device=dev)
+    y_all = torch.zeros(N_DIM, dtype=torch.float32, device=dev) if world > 1 else y
+    y_host = torch.zeros(N_DIM, dtype=torch.float32).pin_memory()
+    torch.cuda.synchronize()
+
+    def step(i):
+        ex.kquant_gemv(planes[i % n_clones], x, y)
+        if world > 1:
+            dist.all_gather_into_tensor(y_all, y)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+
+    # ---- timed region: exactly K steps, device time, max over ranks
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    # keep the same load running until the clock sampler has a few dozen samples
+    t_end = time.time() + 0.4
+    i = 0
+    while time.time() < t_end:
+        step(i)
+        i += 1
+        if i % 64 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    sampler.stop()
+
+    # ---- per-launch duration of the GEMV kernel alone (roofline)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for i, (a, b) in enumerate(evs):
+        a.record()
+        ex.kquant_gemv(planes[i % n_clones], x, y)
+        b.record()
+    torch.cuda.synchronize()
+    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+
+    # ---- end to end: pinned host activations in, outputs back, every step
+    for i in range(3):
+        x.copy_(x_host, non_blocking=True)
+        step(i)
+        y_host[:y_all.numel()].copy_(y_all, non_blocking=True)
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(args.steps):
+        x.copy_(x_host, non_blocking=True)
+        step(i)
+        y_host[:y_all.numel()].copy_(y_all, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    t1.record()
+    barrier()
+    e2e_ms = t0.elapsed_time(t1)
+
+    times = torch.tensor([total_ms, e2e_ms, kern_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, kern_ms = times.tolist()
+
+    if rank == 0:
+        ms_step = total_ms / args.steps
+        bytes_step = algorithmic_bytes(1)
+        peak, peak_kind = measured_peak()
+        kern_bytes = algorithmic_bytes(1, rows)
+        # one step is one GEMV launch at N=1, so the timed region's average is the
+        # kernel's back-to-back launch duration; with a collective in the step the
+        # separately event-bracketed launches are used instead
+        event_us = kern_ms * 1e3
+        if world == 1:
+            kern_ms = ms_step
+        achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
+        line = {
+            "metric": "q4k_gemv_weight_gbs", "value": bytes_step / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": bytes_step / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": K_DIM * 4, "d2h_bytes_per_step": N_DIM * 4,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "q4k_gemv_kernel", "us_per_launch": kern_ms * 1e3,
+                         "us_per_launch_event_bracketed": event_us,
+                         "algorithmic_bytes_per_launch": kern_bytes},
+            "clocks": sampler.summary(),
+        }
+        if world == 1:
+            gbs, cores, sample, _ = cpu_baseline(3, 1)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus != 1 or world != 1:
+            raise SystemExit(f"--gpus {args.gpus} needs a torchrun launch with WORLD_SIZE={args.gpus} (got {world})")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

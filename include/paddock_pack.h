@@ -1,0 +1,135 @@
+/*
+ * paddock_pack.h - C ABI of libpaddock_b200.so, a B200 (sm_100a) kernel pack
+ * for Paddock's quantized linear-layer path.
+ *
+ * The library is a drop-in "kernel pack": it exports the two symbols the
+ * reference's loader resolves (crates/paddock-kernels/src/abi.rs:42-46,
+ * loader.rs:140-288) and fills the slots of KernelTableV1 that belong to this
+ * path; every other slot is NULL, which the engine reports as a missing op at
+ * the point of use (crates/paddock-engine/src/gpu/error.rs:36-40).
+ *
+ * Conventions shared by every launcher (abi.rs:48-54, packs/cuda/src/abi.cuh:11-16):
+ *   - all pointers are raw device pointers owned by the caller;
+ *   - the last argument is the caller's CUstream; launches are asynchronous;
+ *   - the return value is 0 or a raw cudaError_t; shapes the kernel cannot
+ *     take are refused up front with cudaErrorInvalidValue (1) or
+ *     cudaErrorNotSupported (801), never assumed;
+ *   - the pack never allocates, synchronizes or creates streams.
+ *
+ * The launchers are also exported by name (pd_*), with the signatures the
+ * reference gives the same names in packs/cuda/src/abi.cuh, so a host that
+ * links instead of walking the table binds the same entry points.
+ */
+#ifndef PADDOCK_PACK_H
+#define PADDOCK_PACK_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PDK_PACK_MAGIC 0x504b4450u      /* "PDKP", abi.rs:13 */
+#define PDK_PACK_ABI_VERSION 2u         /* abi.rs:10 */
+#define PDK_TABLE_SLOTS 953u            /* abi.rs:1186-12800 */
+#define PDK_TABLE_BYTES (8u + 8u * PDK_TABLE_SLOTS) /* 7632, abi.rs:12805-12812 */
+
+/* ggml type ids used as the k-quant `dtype` tag (packs/cuda/src/quant/kquant.cuh:64-68) */
+#define PDK_KQ_Q4_0 2u
+#define PDK_KQ_Q4K 12u
+#define PDK_KQ_Q5K 13u
+#define PDK_KQ_Q6K 14u
+#define PDK_KQ_IQ4XS 23u
+
+#define PDK_MOE_PAD 0xFFFFFFFFu         /* packs/cuda/src/attn/decode.cuh: PD_MOE_PAD */
+
+/* abi.rs:20-28, packs/cuda/src/abi.cuh:361-366 */
+typedef struct PdkPackInfo {
+    uint32_t magic;
+    uint32_t abi_version;
+    uint8_t arch[16];
+    uint32_t pack_version[3];
+} PdkPackInfo;
+
+/* abi.rs:1186-1189: {u32 size; u32 reserved; 953 nullable fn pointers} */
+typedef struct PdkKernelTableV1 {
+    uint32_t size;
+    uint32_t reserved;
+    void* slot[PDK_TABLE_SLOTS];
+} PdkKernelTableV1;
+
+/* 0-based member index of each implemented slot inside KernelTableV1 (byte
+ * offset 8 + 8*idx), in the member order of packs/cuda/src/abi.cuh:368-... */
+enum PdkSlot {
+    PDK_SLOT_mxfp4_dequant_f32 = 0,
+    PDK_SLOT_q8_0_dequant_f32 = 1,
+    PDK_SLOT_add_inplace_f32 = 6,
+    PDK_SLOT_mxfp4_repack = 37,
+    PDK_SLOT_q8_0_repack = 51,
+    PDK_SLOT_q8_0_gemv_repacked = 52,
+    PDK_SLOT_q8_0_gemm_repacked = 57,
+    PDK_SLOT_kquant_dequant = 202,
+    PDK_SLOT_kquant_repack = 203,
+    PDK_SLOT_kquant_gemv = 204
+};
+
+/* ---- the drop-in boundary ------------------------------------------------ */
+
+/* abi.rs:42, packs/cuda/src/exports.cuh:757.  Static storage. */
+const PdkPackInfo* paddock_pack_info(void);
+/* abi.rs:46, packs/cuda/src/exports.cuh:2114-2118.  Static storage; slots this
+ * pack does not implement, or that the current device cannot run, are NULL. */
+const PdkKernelTableV1* paddock_pack_kernels_v1(void);
+
+/* ---- Q8_0 (packs/cuda/src/deltanet/core.cuh:2552-3090) -------------------- */
+
+/* slot 1, packs/cuda/src/gemm/f32_qkv.cuh:138-147 + elementwise.cuh:65-79:
+ * n_blocks 34-byte blocks {f16 d, int8 q[32]} -> f32[n_blocks*32], y = q*d. */
+int pd_q8_0_dequant_f32(const void* in, void* out, uint64_t n_blocks, void* stream);
+/* slot 51, core.cuh:2567-2576: 34-byte blocks -> int8 plane [n_blocks*32] +
+ * f16 scale plane [n_blocks]. */
+int pd_q8_0_repack(const void* src, void* dst_data, void* dst_scale, uint64_t n_blocks, void* stream);
+/* slot 52, core.cuh:2698-2730: y[o] = bias[o] + sum_b d[o,b] * sum_i q*x over
+ * repacked planes; x f32[in_dim], y f32[out_dim], bias f32 or NULL, f32 math. */
+int pd_q8_0_gemv_repacked(const void* data, const void* scale, const void* bias, const void* x,
+                          void* y, uint32_t in_dim, uint32_t out_dim, void* stream);
+/* slot 57, core.cuh:3076-3090: x f32[batch][in_dim], y f32[batch][out_dim]. */
+int pd_q8_0_gemm_repacked(const void* data, const void* scale, const void* bias, const void* x,
+                          void* y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* stream);
+
+/* ---- k-quants (packs/cuda/src/quant/kquant.cuh) --------------------------- */
+
+/* slot 202, kquant.cuh:144-250: n_super raw GGUF super-blocks -> f32[n_super*256].
+ * Q4_K: y = (d*sc_j)*q - (dmin*m_j).  dtype = PDK_KQ_*. */
+int pd_kquant_dequant(const void* src, void* dst, uint64_t n_super, uint32_t dtype, void* stream);
+/* slot 203, kquant.cuh:255-345 (layout kquant.cuh:37-54): Q4_K -> data 128 B/sb
+ * (nibbles verbatim) + 24 B/sb record {f16 d, f16 dmin, u8 sc[8], u8 m[8], pad4}. */
+int pd_kquant_repack(const void* src, void* dst_data, void* dst_scales, uint64_t n_super,
+                     uint32_t dtype, void* stream);
+/* slot 204, kquant.cuh:372-653: exact-f32 decode GEMV over repacked planes. */
+int pd_kquant_gemv(const void* data, const void* scales, const void* x, void* y, uint32_t in_dim,
+                   uint32_t out_dim, uint32_t dtype, void* stream);
+/* No slot: small-batch sibling of pd_kquant_gemv with f32 activations,
+ * x f32[batch][in_dim], y f32[batch][out_dim], batch <= 64.  The reference's
+ * small-batch route quantizes activations to int8 first (kquant_w4a8_sb.cuh);
+ * this keeps them f32, the numeric class of slot 204. */
+int pdk_kquant_gemm_f32(const void* data, const void* scales, const void* x, void* y,
+                        uint32_t in_dim, uint32_t out_dim, uint32_t batch, uint32_t dtype,
+                        void* stream);
+
+/* ---- MXFP4 ----------------------------------------------------------------- */
+
+/* slot 0, packs/cuda/src/elementwise.cuh:47-62: 17-byte blocks {e8m0, 16 nibble
+ * bytes} -> f32[n_blocks*32]; element j = low nibble of byte j, j+16 = high. */
+int pd_mxfp4_dequant_f32(const void* in, void* out, uint64_t n_blocks, void* stream);
+/* slot 37, packs/cuda/src/attn/decode.cuh:2294-2304 (launcher gemm/f32_qkv.cuh:1465). */
+int pd_mxfp4_repack(const void* src, void* dst_data, void* dst_scale, uint64_t n_blocks, void* stream);
+
+/* ---- glue the engine's preflight needs ------------------------------------- */
+
+/* slot 6 (crates/paddock-engine/src/gpu/mod.rs:507-528 launches it at start-up): y += x */
+int pd_add_inplace_f32(void* y, const void* x, uint32_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

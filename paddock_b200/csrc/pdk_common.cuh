@@ -1,0 +1,39 @@
+// pdk_common.cuh - helpers shared by every translation unit of the pack.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/paddock_pack.h"
+
+#define PDK_EXPORT extern "C" __attribute__((visibility("default")))
+
+// 0 or the raw cudaError_t of the launch just issued (the reference's
+// launchers return the same, packs/cuda/src/gemm/f32_qkv.cuh:7).
+static inline int pdk_launch_status() { return (int)cudaGetLastError(); }
+
+static inline bool pdk_aligned(const void* p, uintptr_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
+
+// Number of SMs of the current device, read once per process per device.
+int pdk_sm_count();
+
+__device__ __forceinline__ float pdk_warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// 16-byte streaming load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 pdk_ldg_stream16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint32_t pdk_ldg_stream4(const void* p) {
+    uint32_t r;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}

@@ -1,0 +1,133 @@
+"""Decode GEMV / small-batch GEMM parity against the CPU oracle: outputs within
+1e-2 (the stated tolerance) of an f64 matmul of the dequantized weights, both
+as max |err| / sum|w x| and as rel-L2; the exact-f32 kernels are additionally
+held to 1e-5."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_util import TOL, bf16_activations, cond_err, dev, dev_f32, rel_l2, seed_for
+
+pytestmark = pytest.mark.gpu
+
+
+def q8_planes(pack, w, n, k):
+    raw = oracle.quantize_q8_0(w)
+    nb = n * k // 32
+    d_data = torch.zeros(nb * 32, dtype=torch.int8, device="cuda")
+    d_scale = torch.zeros(nb, dtype=torch.float16, device="cuda")
+    pack.call("q8_0_repack", dev(raw), d_data, d_scale, nb)
+    return raw, d_data, d_scale
+
+
+@pytest.mark.parametrize("k,n", [(32, 1), (512, 37), (2880, 100), (5120, 1024), (8192, 64)])
+def test_q8_0_gemv_shapes(pack, k, n):
+    w = oracle.fill_normal(n * k, seed_for(0, k + n), 0.02)
+    x = bf16_activations(k, seed_for(0, 1))
+    raw, d_data, d_scale = q8_planes(pack, w, n, k)
+    bias = oracle.fill_normal(n, 9, 0.1)
+    d_y = torch.zeros(n, dtype=torch.float32, device="cuda")
+    pack.call("q8_0_gemv_repacked", d_data, d_scale, dev_f32(bias), dev_f32(x), d_y, k, n)
+    torch.cuda.synchronize()
+    wd = oracle.dequant_q8_0(raw)
+    ref, ab = oracle.matmul_f64(wd, x, k, n, 1, with_abs=True)
+    y = d_y.cpu().numpy() - bias
+    assert cond_err(y, ref[0], ab[0]) < 1e-5
+    assert rel_l2(y, ref[0]) < 1e-5 < TOL
+    # the reference CPU path (scalar f32, ascending k) agrees to f32 rounding
+    y_cpu = oracle.matvec_f32(wd, x, k, n)
+    assert rel_l2(y, y_cpu.astype(np.float64)) < 1e-5
+
+
+def test_q8_0_gemv_config1_rows(pack):
+    """BASELINE config 1 at full K with a 2048-row band of the 17408 rows."""
+    k, n = 5120, 2048
+    w = oracle.fill_normal(n * k, seed_for(1, 0), 0.02)
+    x = bf16_activations(k, seed_for(1, 1))
+    raw, d_data, d_scale = q8_planes(pack, w, n, k)
+    d_y = torch.zeros(n, dtype=torch.float32, device="cuda")
+    pack.call("q8_0_gemv_repacked", d_data, d_scale, None, dev_f32(x), d_y, k, n)
+    torch.cuda.synchronize()
+    ref, ab = oracle.matmul_f64(oracle.dequant_q8_0(raw), x, k, n, 1, with_abs=True)
+    assert cond_err(d_y.cpu().numpy(), ref[0], ab[0]) < 1e-5
+
+
+@pytest.mark.parametrize("batch", [1, 2, 3, 4, 7, 16])
+def test_q8_0_gemm_small_batch(pack, batch):
+    k, n = 1024, 96
+    w = oracle.fill_normal(n * k, 31, 0.02)
+    x = bf16_activations(batch * k, 32)
+    raw, d_data, d_scale = q8_planes(pack, w, n, k)
+    d_y = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+    pack.call("q8_0_gemm_repacked", d_data, d_scale, None, dev_f32(x), d_y, k, n, batch)
+    torch.cuda.synchronize()
+    ref, ab = oracle.matmul_f64(oracle.dequant_q8_0(raw), x, k, n, batch, with_abs=True)
+    assert cond_err(d_y.cpu().numpy().reshape(batch, n), ref, ab) < 1e-5
+
+
+def test_q8_0_gemv_refuses_bad_shapes(pack):
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    assert pack.status("q8_0_gemv_repacked", buf, buf, None, buf, buf, 48, 4) == 1
+    assert pack.status("q8_0_gemv_repacked", buf, buf, None, buf.data_ptr() + 4, buf, 64, 4) == 1
+    assert pack.status("q8_0_gemv_repacked", buf, buf, None, buf, buf, 64, 0) == 0
+
+
+def q4k_planes(pack, w, n, k):
+    raw = oracle.quantize_q4_k(w)
+    ns = n * k // 256
+    d_data = torch.zeros(ns * 128, dtype=torch.uint8, device="cuda")
+    d_sc = torch.zeros(ns * 24, dtype=torch.uint8, device="cuda")
+    pack.call("kquant_repack", dev(raw), d_data, d_sc, ns, 12)
+    return raw, d_data, d_sc
+
+
+@pytest.mark.parametrize("k,n", [(256, 1), (512, 33), (2560, 100), (5120, 1000), (14336, 16)])
+def test_q4_k_gemv_shapes(pack, k, n):
+    w = oracle.fill_normal(n * k, seed_for(2, k + n), 0.02)
+    x = bf16_activations(k, seed_for(2, 1))
+    raw, d_data, d_sc = q4k_planes(pack, w, n, k)
+    d_y = torch.zeros(n, dtype=torch.float32, device="cuda")
+    pack.call("kquant_gemv", d_data, d_sc, dev_f32(x), d_y, k, n, 12)
+    torch.cuda.synchronize()
+    ref, ab = oracle.matmul_f64(oracle.dequant_q4_k(raw), x, k, n, 1, with_abs=True)
+    y = d_y.cpu().numpy()
+    assert cond_err(y, ref[0], ab[0]) < 1e-5
+    assert rel_l2(y, ref[0]) < 1e-4 < TOL
+
+
+@pytest.mark.parametrize("batch", [1, 4, 16])
+def test_q4_k_small_batch_config2_band(pack, batch):
+    """BASELINE config 2 (K=5120, M in {1,4,16}) on a 1536-row band of N=25600."""
+    k, n = 5120, 1536
+    w = oracle.fill_normal(n * k, seed_for(2, 0), 0.02)
+    x = bf16_activations(batch * k, seed_for(2, 100 + batch))
+    raw, d_data, d_sc = q4k_planes(pack, w, n, k)
+    d_y = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+    pack.call("pdk_kquant_gemm_f32", d_data, d_sc, dev_f32(x), d_y, k, n, batch, 12)
+    torch.cuda.synchronize()
+    ref, ab = oracle.matmul_f64(oracle.dequant_q4_k(raw), x, k, n, batch, with_abs=True)
+    y = d_y.cpu().numpy().reshape(batch, n)
+    assert cond_err(y, ref, ab) < 1e-5
+    assert rel_l2(y, ref) < 1e-4 < TOL
+
+
+def test_q4_k_gemv_general_f32_activations(pack):
+    """Activations that are not bf16-representable keep f32 precision."""
+    k, n = 2048, 64
+    w = oracle.fill_normal(n * k, 55, 0.02)
+    x = oracle.fill_normal(k, 56, 1.0)
+    raw, d_data, d_sc = q4k_planes(pack, w, n, k)
+    d_y = torch.zeros(n, dtype=torch.float32, device="cuda")
+    pack.call("kquant_gemv", d_data, d_sc, dev_f32(x), d_y, k, n, 12)
+    torch.cuda.synchronize()
+    ref, ab = oracle.matmul_f64(oracle.dequant_q4_k(raw), x, k, n, 1, with_abs=True)
+    assert cond_err(d_y.cpu().numpy(), ref[0], ab[0]) < 1e-5
+
+
+def test_q4_k_gemv_refuses_bad_shapes(pack):
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    assert pack.status("kquant_gemv", buf, buf, buf, buf, 128, 4, 12) == 1     # K not a multiple of 256
+    assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 99) == 1     # unknown dtype
+    assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 13) == 801   # Q5_K not built
+    assert pack.status("pdk_kquant_gemm_f32", buf, buf, buf, buf, 256, 4, 65, 12) == 1
