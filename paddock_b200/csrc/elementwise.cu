@@ -78,7 +78,7 @@ __device__ __forceinline__ float pdk_fp4_doubled(uint32_t nib) {
     // magnitudes 0,1,2,3,4,6,8,12 packed one per byte; sign in bit 3
     const uint64_t mags = 0x0C08060403020100ull;
     float m = (float)(uint32_t)((mags >> ((nib & 7u) * 8u)) & 0xffu);
-    return (nib & 8u) ? -m : m;
+    return (nib & 8u) ? 0.0f - m : m;  // code 8 is +0.0 in the ggml table
 }
 
 // One thread per element: i -> block b, element j; byte 1 + (j & 15), low
