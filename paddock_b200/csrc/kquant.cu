@@ -1,13 +1,27 @@
-// kquant.cu - Q4_K: dequant, repack and the exact-f32 decode GEMV / small-batch
-// GEMM over the repacked planes.
+// kquant.cu - Q4_K: dequant, repack and the decode GEMV / small-batch GEMM over
+// the repacked planes.
 //
 // Repacked layout (the byte budget the engine allocates: 128 B + 24 B per
-// 256-weight super-block):
-//   data   : the 128 nibble bytes verbatim - group g (32 bytes) byte l holds
-//            element g*64 + l in its low nibble and g*64 + 32 + l in its high;
+// 256-weight super-block; every super-block is self-contained because the
+// repack call is only told a super-block count):
+//   data   : the 128 nibble bytes, permuted so that the 16 bytes one tensor-core
+//            lane needs are contiguous.  ggml stores group G (32 bytes) byte l =
+//            element G*64 + l (low nibble) | element G*64 + 32 + l (high
+//            nibble).  Here byte P*64 + t*16 + h*8 + i holds ggml byte
+//            (2P + h)*32 + 8t + i   (P, h in 0..1, t in 0..3, i in 0..7).
 //   scales : 24-byte record {f16 d, f16 dmin, u8 sc[8], u8 m[8], 4 pad bytes}
 //            with the 6-bit (scale, min) pairs unpacked to bytes.
 // Dequant value of element l of sub-block j: (d*sc_j)*q - (dmin*m_j).
+//
+// The GEMV is HBM-bound (4.5 bits per weight streamed once).  Per-weight f32
+// FMAs would make it issue-bound on B200, so the inner product runs on the
+// tensor cores without leaving the f32 numeric class: nibbles become the exact
+// bf16 integers 128+q (one logic op per pair), activations are split into
+// bf16 hi + bf16 lo parts that ride in two columns of the same mma, and the
+// per-sub-block scale, the min term and the 128 offset are applied in f32 to
+// the 32-element partial sums.
+#include <cstdlib>
+
 #include "pdk_common.cuh"
 
 namespace {
@@ -44,16 +58,19 @@ __global__ void q4k_dequant_kernel(const uint8_t* __restrict__ src, float* __res
     }
 }
 
-// One warp per super-block: lanes copy the 128 nibble bytes as 32 words (the
-// source payload at 144*b + 16 is 4-byte aligned when the plane is); lane 0..7
-// unpack one (sc, m) pair each into the 24-byte record.
+// One warp per super-block: lane l moves one 4-byte word of the nibble payload
+// to its permuted place (the source payload at 144*b + 16 is 4-byte aligned
+// when the plane is); lanes 0..7 unpack one (sc, m) pair each into the record.
 __global__ void q4k_repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst_data,
                                   uint8_t* __restrict__ dst_scales, uint64_t n_super) {
     const uint64_t b = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (b >= n_super) return;
     const uint32_t lane = threadIdx.x & 31u;
     const uint8_t* s = src + b * 144u;
-    reinterpret_cast<uint32_t*>(dst_data + b * 128u)[lane] = reinterpret_cast<const uint32_t*>(s + 16)[lane];
+    // destination word `lane` = (P, t, h, iw): source word (2P+h)*8 + 2t + iw
+    const uint32_t P = lane >> 4, t = (lane >> 2) & 3u, h = (lane >> 1) & 1u, iw = lane & 1u;
+    reinterpret_cast<uint32_t*>(dst_data + b * 128u)[lane] =
+        reinterpret_cast<const uint32_t*>(s + 16)[(2u * P + h) * 8u + 2u * t + iw];
     uint8_t* rec = dst_scales + b * 24u;
     if (lane < 8u) {
         uint32_t sc, m;
@@ -67,34 +84,299 @@ __global__ void q4k_repack_kernel(const uint8_t* __restrict__ src, uint8_t* __re
     }
 }
 
+// ===========================================================================
+// Tensor-core streaming GEMV / small-batch GEMM
+// ===========================================================================
+
+constexpr uint32_t kTileSlots = 4;                    // 16-row tiles a CTA works on at once
+constexpr uint32_t kSlices = 4;                       // K slices per tile (one warp each)
+constexpr uint32_t kThreads = kTileSlots * kSlices * 32;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void bar_sync(uint32_t id, uint32_t count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+struct SbData {   // one super-block of two rows (g and g+8) in registers
+    uint4 lo[2];  // row g: halves P = 0, 1
+    uint4 hi[2];  // row g + 8
+};
+struct SbScale {  // the two rows' 24-byte records (first 20 bytes used)
+    uint2 lo[3];
+    uint2 hi[3];
+};
+
+// Shared-memory plan (dynamic):
+//   xs   : bf16 [NCOLS][pitch/2]  activations, permuted per 8 elements as
+//          [0,2,1,3,4,6,5,7] so a lane's B fragments for one sub-block are one
+//          16-byte read; pitch = 2*K + 64 bytes keeps the 8 columns of an
+//          n-tile on distinct banks.
+//   xsum : f32 [K/32][NCOLS]      per-sub-block sums of the staged values
+//   red  : f32 [2][kTileSlots][kSlices][16][NCOLS]  K-slice partials
+//
+// NT = number of 8-column n-tiles; SPLIT = columns (2m, 2m+1) carry the bf16
+// hi and lo parts of token m (f32-exact activations), else column m = token m
+// rounded to bf16.
+template <uint32_t NT, bool SPLIT>
+__global__ void __launch_bounds__(kThreads, 1)
+q4k_mma_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ scales,
+               const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim, uint32_t out_dim,
+               uint32_t batch) {
+    constexpr uint32_t NCOLS = NT * 8u;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t n_sub = in_dim >> 5, n_super = in_dim >> 8;
+    const uint32_t pitch = in_dim * 2u + 64u;
+    uint8_t* xs = smem;
+    float* xsum = reinterpret_cast<float*>(smem + (size_t)NCOLS * pitch);
+    float* red = xsum + (size_t)n_sub * NCOLS;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t slot = warp / kSlices, slice = warp % kSlices;
+    const uint32_t n_tiles = (out_dim + 15u) >> 4;
+    const uint32_t per = (n_super + kSlices - 1u) / kSlices;
+    const uint32_t sb_lo = min(slice * per, n_super), sb_hi = min(sb_lo + per, n_super);
+
+    const size_t row_data = (size_t)n_super * 128u, row_rec = (size_t)n_super * 24u;
+
+    auto load_data = [&](SbData& s, const uint8_t* p0, const uint8_t* p1, uint32_t sb) {
+        const uint8_t* a = p0 + (size_t)sb * 128u + t * 16u;
+        const uint8_t* b = p1 + (size_t)sb * 128u + t * 16u;
+        s.lo[0] = pdk_ldg_stream16(a);
+        s.lo[1] = pdk_ldg_stream16(a + 64);
+        s.hi[0] = pdk_ldg_stream16(b);
+        s.hi[1] = pdk_ldg_stream16(b + 64);
+    };
+    auto load_scale = [&](SbScale& s, const uint8_t* r0, const uint8_t* r1, uint32_t sb) {
+        const uint2* a = reinterpret_cast<const uint2*>(r0 + (size_t)sb * 24u);
+        const uint2* b = reinterpret_cast<const uint2*>(r1 + (size_t)sb * 24u);
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            s.lo[i] = __ldg(a + i);
+            s.hi[i] = __ldg(b + i);
+        }
+    };
+
+    // ---- first tile's weights go in flight before the activations are staged
+    uint32_t tile = blockIdx.x * kTileSlots + slot;
+    const uint32_t tile_stride = gridDim.x * kTileSlots;
+    SbData d0, d1;
+    SbScale s0, s1;
+    const uint8_t *p0 = data, *p1 = data, *r0 = scales, *r1 = scales;
+    auto set_rows = [&](uint32_t tl) {
+        const uint32_t ra = min(tl * 16u + g, out_dim - 1u), rb = min(tl * 16u + g + 8u, out_dim - 1u);
+        p0 = data + ra * row_data;
+        p1 = data + rb * row_data;
+        r0 = scales + ra * row_rec;
+        r1 = scales + rb * row_rec;
+    };
+    if (tile < n_tiles) {
+        set_rows(tile);
+        if (sb_lo < sb_hi) { load_data(d0, p0, p1, sb_lo); load_scale(s0, r0, r1, sb_lo); }
+        if (sb_lo + 1u < sb_hi) load_data(d1, p0, p1, sb_lo + 1u);
+    }
+
+    // ---- stage activations: one thread per (column, 8 elements)
+    {
+        const uint32_t groups = in_dim >> 3;  // 8-element groups per column
+        const uint32_t used_cols = SPLIT ? 2u * batch : batch;
+        for (uint32_t idx = tid; idx < NCOLS * groups; idx += kThreads) {
+            const uint32_t col = idx / groups, grp = idx % groups;  // grp = j*4 + t
+            float v[8];
+            if (col < used_cols) {
+                const uint32_t tok = SPLIT ? (col >> 1) : col;
+                const float4 a = *reinterpret_cast<const float4*>(x + (size_t)tok * in_dim + grp * 8u);
+                const float4 b = *reinterpret_cast<const float4*>(x + (size_t)tok * in_dim + grp * 8u + 4u);
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+                v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float hi = __bfloat162float(__float2bfloat16_rn(v[i]));
+                    if (SPLIT && (col & 1u)) v[i] = __bfloat162float(__float2bfloat16_rn(v[i] - hi));
+                    else v[i] = hi;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+            }
+            uint4 w;
+            w.x = pack_bf16(v[0], v[2]);
+            w.y = pack_bf16(v[1], v[3]);
+            w.z = pack_bf16(v[4], v[6]);
+            w.w = pack_bf16(v[5], v[7]);
+            *reinterpret_cast<uint4*>(xs + (size_t)col * pitch + grp * 16u) = w;
+            // the four groups of a sub-block sit in four adjacent lanes
+            float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if ((grp & 3u) == 0u) xsum[(size_t)(grp >> 2) * NCOLS + col] = sum;
+        }
+    }
+    __syncthreads();
+
+    const uint8_t* xs_lane = xs + (size_t)g * pitch + t * 16u;  // column g of each n-tile
+    uint32_t iter = 0;
+    for (; tile < n_tiles; tile += tile_stride, ++iter) {
+        float acc[NT][4];
+#pragma unroll
+        for (uint32_t n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+
+        // one super-block: 8 sub-blocks x (2 mma per n-tile), then the f32 fold
+        auto compute = [&](const SbData& dd, const SbScale& ss, uint32_t sb) {
+            const __half2 dl = *reinterpret_cast<const __half2*>(&ss.lo[0].x);
+            const __half2 dh = *reinterpret_cast<const __half2*>(&ss.hi[0].x);
+            const float d_lo = __low2float(dl), m_lo = __high2float(dl);
+            const float d_hi = __low2float(dh), m_hi = __high2float(dh);
+            // sc[8] = bytes 4..11, m[8] = bytes 12..19 of the record
+            const uint32_t sc_lo[2] = {ss.lo[0].y, ss.lo[1].x}, mn_lo[2] = {ss.lo[1].y, ss.lo[2].x};
+            const uint32_t sc_hi[2] = {ss.hi[0].y, ss.hi[1].x}, mn_hi[2] = {ss.hi[1].y, ss.hi[2].x};
+#pragma unroll
+            for (uint32_t G = 0; G < 4u; ++G) {
+                // words of rows g / g+8 for group G: (W0, W1) of the 8 bytes
+                const uint4& ql = dd.lo[G >> 1];
+                const uint4& qh = dd.hi[G >> 1];
+                const uint32_t wl0 = (G & 1u) ? ql.z : ql.x, wl1 = (G & 1u) ? ql.w : ql.y;
+                const uint32_t wh0 = (G & 1u) ? qh.z : qh.x, wh1 = (G & 1u) ? qh.w : qh.y;
+#pragma unroll
+                for (uint32_t h = 0; h < 2u; ++h) {  // h = 0: low nibbles (sub-block 2G), 1: high
+                    const uint32_t j = 2u * G + h;
+                    const uint32_t sh = h * 4u;
+                    const uint32_t M = 0x000F000Fu, O = 0x43004300u;
+                    const uint32_t a0 = ((wl0 >> sh) & M) | O, a2 = ((wl0 >> (sh + 8u)) & M) | O;
+                    const uint32_t a1 = ((wh0 >> sh) & M) | O, a3 = ((wh0 >> (sh + 8u)) & M) | O;
+                    const uint32_t e0 = ((wl1 >> sh) & M) | O, e2 = ((wl1 >> (sh + 8u)) & M) | O;
+                    const uint32_t e1 = ((wh1 >> sh) & M) | O, e3 = ((wh1 >> (sh + 8u)) & M) | O;
+                    const uint32_t bsh = (j & 3u) * 8u;
+                    const float sl = (float)((sc_lo[j >> 2] >> bsh) & 0xffu), ml = (float)((mn_lo[j >> 2] >> bsh) & 0xffu);
+                    const float su = (float)((sc_hi[j >> 2] >> bsh) & 0xffu), mu = (float)((mn_hi[j >> 2] >> bsh) & 0xffu);
+                    const float dsl = d_lo * sl, dsu = d_hi * su;
+                    const float ofl = fmaf(128.0f, dsl, m_lo * ml), ofu = fmaf(128.0f, dsu, m_hi * mu);
+                    const uint32_t sub = sb * 8u + j;
+#pragma unroll
+                    for (uint32_t n = 0; n < NT; ++n) {
+                        const uint4 b = *reinterpret_cast<const uint4*>(xs_lane + (size_t)n * 8u * pitch + (size_t)sub * 64u);
+                        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        mma_bf16(c, a0, a1, a2, a3, b.x, b.y);
+                        mma_bf16(c, e0, e1, e2, e3, b.z, b.w);
+                        const float2 xsv = *reinterpret_cast<const float2*>(xsum + (size_t)sub * NCOLS + n * 8u + 2u * t);
+                        acc[n][0] += dsl * c[0] - ofl * xsv.x;
+                        acc[n][1] += dsl * c[1] - ofl * xsv.y;
+                        acc[n][2] += dsu * c[2] - ofu * xsv.x;
+                        acc[n][3] += dsu * c[3] - ofu * xsv.y;
+                    }
+                }
+            }
+        };
+
+        // software pipeline over the slice: data two super-blocks ahead, records one
+        SbData d2;
+        for (uint32_t sb = sb_lo; sb < sb_hi; sb += 3u) {
+            if (sb + 2u < sb_hi) load_data(d2, p0, p1, sb + 2u);
+            if (sb + 1u < sb_hi) load_scale(s1, r0, r1, sb + 1u);
+            compute(d0, s0, sb);
+            if (sb + 1u >= sb_hi) break;
+            if (sb + 3u < sb_hi) load_data(d0, p0, p1, sb + 3u);
+            if (sb + 2u < sb_hi) load_scale(s0, r0, r1, sb + 2u);
+            compute(d1, s1, sb + 1u);
+            if (sb + 2u >= sb_hi) break;
+            if (sb + 4u < sb_hi) load_data(d1, p0, p1, sb + 4u);
+            if (sb + 3u < sb_hi) load_scale(s1, r0, r1, sb + 3u);
+            compute(d2, s0, sb + 2u);
+            if (sb + 3u < sb_hi) s0 = s1;
+        }
+
+        // next tile's first loads go out before the reduction
+        const uint32_t next = tile + tile_stride;
+        const uint32_t cur_rows = tile * 16u;
+        if (next < n_tiles) {
+            set_rows(next);
+            if (sb_lo < sb_hi) { load_data(d0, p0, p1, sb_lo); load_scale(s0, r0, r1, sb_lo); }
+            if (sb_lo + 1u < sb_hi) load_data(d1, p0, p1, sb_lo + 1u);
+        }
+
+        // ---- fold the K slices: [slice][16 rows][NCOLS] per tile slot, two buffers
+        float* rbuf = red + ((size_t)(iter & 1u) * kTileSlots + slot) * (kSlices * 16u * NCOLS);
+        float* mine = rbuf + (size_t)slice * 16u * NCOLS;
+#pragma unroll
+        for (uint32_t n = 0; n < NT; ++n) {
+            *reinterpret_cast<float2*>(mine + (size_t)g * NCOLS + n * 8u + 2u * t) = make_float2(acc[n][0], acc[n][1]);
+            *reinterpret_cast<float2*>(mine + (size_t)(g + 8u) * NCOLS + n * 8u + 2u * t) = make_float2(acc[n][2], acc[n][3]);
+        }
+        bar_sync(1u + slot, kSlices * 32u);
+        const uint32_t sub_tid = slice * 32u + lane;  // 0..127 within the tile slot
+        const uint32_t outs = 16u * batch;
+        for (uint32_t o = sub_tid; o < outs; o += kSlices * 32u) {
+            const uint32_t r = o % 16u, tok = o / 16u;
+            float v = 0.0f;
+#pragma unroll
+            for (uint32_t s = 0; s < kSlices; ++s) {
+                const float* pr = rbuf + ((size_t)s * 16u + r) * NCOLS;
+                v += SPLIT ? (pr[2u * tok] + pr[2u * tok + 1u]) : pr[tok];
+            }
+            if (cur_rows + r < out_dim) y[(size_t)tok * out_dim + cur_rows + r] = v;
+        }
+    }
+}
+
+template <uint32_t NT, bool SPLIT>
+int launch_mma(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+               uint32_t batch, cudaStream_t st) {
+    constexpr uint32_t NCOLS = NT * 8u;
+    const size_t smem = (size_t)NCOLS * (in_dim * 2u + 64u) + (size_t)(in_dim >> 5) * NCOLS * 4u +
+                        (size_t)2u * kTileSlots * kSlices * 16u * NCOLS * 4u;
+    if (smem > 227u * 1024u) return -1;  // caller falls back
+    auto kern = q4k_mma_kernel<NT, SPLIT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const uint32_t n_tiles = (out_dim + 15u) / 16u;
+    uint32_t grid = (uint32_t)pdk_sm_count();
+    const uint32_t need = (n_tiles + kTileSlots - 1u) / kTileSlots;
+    if (grid > need) grid = need;
+    kern<<<grid, kThreads, smem, st>>>((const uint8_t*)data, (const uint8_t*)scales, x, y, in_dim, out_dim, batch);
+    return pdk_launch_status();
+}
+
+// ===========================================================================
+// Plain-load f32 kernel: the route for shapes the tensor-core kernel's shared
+// memory plan cannot hold.  A warp owns one output row at a time; lane l reads
+// word l of each super-block (a coalesced 128-byte line).
+// ===========================================================================
 constexpr uint32_t kWarps = 8;
 
-// Exact-f32 GEMV / small-batch GEMM.  A warp owns one output row at a time and
-// reads each super-block's 128 nibble bytes as one coalesced 128-byte line:
-// lane l = (group g = l/8, word w = l%8) holds four low nibbles (sub-block 2g,
-// elements 4w..4w+3) and four high nibbles (sub-block 2g+1).  Per sub-block
-// the partial is (d*sc)*sum(q*x) - (dmin*m)*sum(x), all f32.
 template <uint32_t TOK, uint32_t UNROLL>
 __global__ void __launch_bounds__(kWarps * 32)
 q4k_gemv_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ scales,
                 const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim, uint32_t out_dim,
                 uint32_t batch0) {
-    extern __shared__ __align__(16) float xs[];  // [TOK][in_dim]
+    extern __shared__ __align__(16) float xsf[];  // [TOK][in_dim]
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const float* xg = x + (size_t)batch0 * in_dim;
     for (uint32_t i = tid * 4u; i < TOK * in_dim; i += blockDim.x * 4u)
-        *reinterpret_cast<float4*>(xs + i) = *reinterpret_cast<const float4*>(xg + i);
+        *reinterpret_cast<float4*>(xsf + i) = *reinterpret_cast<const float4*>(xg + i);
     __syncthreads();
 
     const uint32_t n_super = in_dim >> 8;
-    const uint32_t g = lane >> 3, w = lane & 7u;
-    const uint32_t koff = g * 64u + w * 4u;  // first low-nibble element inside the super-block
+    // word `lane` of the permuted payload = ggml group G, word w of that group
+    const uint32_t G = 2u * (lane >> 4) + ((lane >> 1) & 1u), w = 2u * ((lane >> 2) & 3u) + (lane & 1u);
+    const uint32_t koff = G * 64u + w * 4u;  // first low-nibble element inside the super-block
     for (uint32_t row = blockIdx.x * kWarps + warp; row < out_dim; row += gridDim.x * kWarps) {
         const uint8_t* drow = data + (size_t)row * n_super * 128u;
         const uint8_t* srow = scales + (size_t)row * n_super * 24u;
         float acc[TOK];
 #pragma unroll
-        for (uint32_t t = 0; t < TOK; ++t) acc[t] = 0.0f;
+        for (uint32_t tk = 0; tk < TOK; ++tk) acc[tk] = 0.0f;
         for (uint32_t sb0 = 0; sb0 < n_super; sb0 += UNROLL) {
             uint32_t q[UNROLL];
             uint32_t dd[UNROLL];
@@ -106,8 +388,8 @@ q4k_gemv_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sc
                     q[u] = pdk_ldg_stream4(drow + sb * 128u + lane * 4u);
                     const uint8_t* rec = srow + sb * 24u;
                     dd[u] = *reinterpret_cast<const uint32_t*>(rec);
-                    const uint32_t s2 = *reinterpret_cast<const uint16_t*>(rec + 4u + 2u * g);
-                    const uint32_t m2 = *reinterpret_cast<const uint16_t*>(rec + 12u + 2u * g);
+                    const uint32_t s2 = *reinterpret_cast<const uint16_t*>(rec + 4u + 2u * G);
+                    const uint32_t m2 = *reinterpret_cast<const uint16_t*>(rec + 12u + 2u * G);
                     scm[u] = s2 | (m2 << 16);
                 } else {
                     q[u] = 0u; dd[u] = 0u; scm[u] = 0u;
@@ -123,9 +405,9 @@ q4k_gemv_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sc
                 const float m_lo = dmin * (float)((scm[u] >> 16) & 0xffu), m_hi = dmin * (float)(scm[u] >> 24);
                 const uint32_t k = sb * 256u + koff;
 #pragma unroll
-                for (uint32_t t = 0; t < TOK; ++t) {
-                    const float4 xl = *reinterpret_cast<const float4*>(xs + t * in_dim + k);
-                    const float4 xh = *reinterpret_cast<const float4*>(xs + t * in_dim + k + 32u);
+                for (uint32_t tk = 0; tk < TOK; ++tk) {
+                    const float4 xl = *reinterpret_cast<const float4*>(xsf + tk * in_dim + k);
+                    const float4 xh = *reinterpret_cast<const float4*>(xsf + tk * in_dim + k + 32u);
                     float sl = (float)(q[u] & 0xFu) * xl.x;
                     sl = fmaf((float)((q[u] >> 8) & 0xFu), xl.y, sl);
                     sl = fmaf((float)((q[u] >> 16) & 0xFu), xl.z, sl);
@@ -136,21 +418,21 @@ q4k_gemv_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sc
                     sh = fmaf((float)(q[u] >> 28), xh.w, sh);
                     const float xsl = (xl.x + xl.y) + (xl.z + xl.w);
                     const float xsh = (xh.x + xh.y) + (xh.z + xh.w);
-                    acc[t] += (d_lo * sl - m_lo * xsl) + (d_hi * sh - m_hi * xsh);
+                    acc[tk] += (d_lo * sl - m_lo * xsl) + (d_hi * sh - m_hi * xsh);
                 }
             }
         }
 #pragma unroll
-        for (uint32_t t = 0; t < TOK; ++t) {
-            const float v = pdk_warp_sum(acc[t]);
-            if (lane == 0) y[(size_t)(batch0 + t) * out_dim + row] = v;
+        for (uint32_t tk = 0; tk < TOK; ++tk) {
+            const float v = pdk_warp_sum(acc[tk]);
+            if (lane == 0) y[(size_t)(batch0 + tk) * out_dim + row] = v;
         }
     }
 }
 
 template <uint32_t TOK>
-int launch(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
-           uint32_t batch0, cudaStream_t st) {
+int launch_plain(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                 uint32_t batch0, cudaStream_t st) {
     const size_t smem = (size_t)TOK * in_dim * sizeof(float);
     auto kern = q4k_gemv_kernel<TOK, 10>;
     if (smem > 48u * 1024u) {
@@ -167,6 +449,50 @@ int launch(const void* data, const void* scales, const float* x, float* y, uint3
     if (grid > need) grid = need;
     kern<<<grid, kWarps * 32u, smem, st>>>((const uint8_t*)data, (const uint8_t*)scales, x, y, in_dim, out_dim, batch0);
     return pdk_launch_status();
+}
+
+int plain_batch(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                uint32_t batch, cudaStream_t st) {
+    uint32_t b = 0;
+    for (; b + 4u <= batch; b += 4u)
+        if (int rc = launch_plain<4>(data, scales, x, y, in_dim, out_dim, b, st)) return rc;
+    for (; b + 2u <= batch; b += 2u)
+        if (int rc = launch_plain<2>(data, scales, x, y, in_dim, out_dim, b, st)) return rc;
+    for (; b < batch; ++b)
+        if (int rc = launch_plain<1>(data, scales, x, y, in_dim, out_dim, b, st)) return rc;
+    return 0;
+}
+
+// PDK_Q4K_PLAIN=1 forces the plain-load kernel (A/B switch, read once).
+bool force_plain() {
+    static const bool v = [] {
+        const char* e = getenv("PDK_Q4K_PLAIN");
+        return e && e[0] == '1';
+    }();
+    return v;
+}
+
+int gemm_any(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+             uint32_t batch, cudaStream_t st) {
+    if (!force_plain()) {
+        uint32_t b = 0;
+        int rc = 0;
+        while (b < batch && rc == 0) {
+            const uint32_t left = batch - b;
+            const float* xb = x + (size_t)b * in_dim;
+            float* yb = y + (size_t)b * out_dim;
+            uint32_t take;
+            if (left <= 4u) { take = left; rc = launch_mma<1, true>(data, scales, xb, yb, in_dim, out_dim, take, st); }
+            else if (left <= 8u) { take = left; rc = launch_mma<1, false>(data, scales, xb, yb, in_dim, out_dim, take, st); }
+            else { take = left < 16u ? left : 16u; rc = launch_mma<2, false>(data, scales, xb, yb, in_dim, out_dim, take, st); }
+            if (rc == -1) break;  // shared-memory plan does not fit: plain route for the rest
+            b += take;
+        }
+        if (rc > 0) return rc;
+        if (b == batch) return 0;
+        return plain_batch(data, scales, x + (size_t)b * in_dim, y + (size_t)b * out_dim, in_dim, out_dim, batch - b, st);
+    }
+    return plain_batch(data, scales, x, y, in_dim, out_dim, batch, st);
 }
 
 int check_gemv(const void* data, const void* scales, const void* x, const void* y, uint32_t in_dim, uint32_t dtype) {
@@ -213,7 +539,7 @@ PDK_EXPORT int pd_kquant_gemv(const void* data, const void* scales, const void* 
                               uint32_t out_dim, uint32_t dtype, void* stream) {
     if (out_dim == 0) return 0;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
-    return launch<1>(data, scales, (const float*)x, (float*)y, in_dim, out_dim, 0u, (cudaStream_t)stream);
+    return gemm_any(data, scales, (const float*)x, (float*)y, in_dim, out_dim, 1u, (cudaStream_t)stream);
 }
 
 PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const void* x, void* y, uint32_t in_dim,
@@ -221,15 +547,5 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
     if (out_dim == 0 || batch == 0) return 0;
     if (batch > 64u) return cudaErrorInvalidValue;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
-    const float* xf = (const float*)x;
-    float* yf = (float*)y;
-    auto st = (cudaStream_t)stream;
-    uint32_t b = 0;
-    for (; b + 4u <= batch; b += 4u)
-        if (int rc = launch<4>(data, scales, xf, yf, in_dim, out_dim, b, st)) return rc;
-    for (; b + 2u <= batch; b += 2u)
-        if (int rc = launch<2>(data, scales, xf, yf, in_dim, out_dim, b, st)) return rc;
-    for (; b < batch; ++b)
-        if (int rc = launch<1>(data, scales, xf, yf, in_dim, out_dim, b, st)) return rc;
-    return 0;
+    return gemm_any(data, scales, (const float*)x, (float*)y, in_dim, out_dim, batch, (cudaStream_t)stream);
 }
