@@ -4,11 +4,8 @@
 // Repacked layout (the byte budget the engine allocates: 128 B + 24 B per
 // 256-weight super-block; every super-block is self-contained because the
 // repack call is only told a super-block count):
-//   data   : the 128 nibble bytes, permuted so that the 16 bytes one tensor-core
-//            lane needs are contiguous.  ggml stores group G (32 bytes) byte l =
-//            element G*64 + l (low nibble) | element G*64 + 32 + l (high
-//            nibble).  Here byte P*64 + t*16 + h*8 + i holds ggml byte
-//            (2P + h)*32 + 8t + i   (P, h in 0..1, t in 0..3, i in 0..7).
+//   data   : the 128 nibble bytes verbatim: group G (32 bytes) byte l holds
+//            element G*64 + l (low nibble) and element G*64 + 32 + l (high nibble);
 //   scales : 24-byte record {f16 d, f16 dmin, u8 sc[8], u8 m[8], 4 pad bytes}
 //            with the 6-bit (scale, min) pairs unpacked to bytes.
 // Dequant value of element l of sub-block j: (d*sc_j)*q - (dmin*m_j).
@@ -23,6 +20,9 @@
 #include <cstdlib>
 
 #include "pdk_common.cuh"
+
+int pdk_q4k_gemv_diag(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                      uint32_t out_dim, cudaStream_t st);
 
 namespace {
 
@@ -59,18 +59,15 @@ __global__ void q4k_dequant_kernel(const uint8_t* __restrict__ src, float* __res
 }
 
 // One warp per super-block: lane l moves one 4-byte word of the nibble payload
-// to its permuted place (the source payload at 144*b + 16 is 4-byte aligned
-// when the plane is); lanes 0..7 unpack one (sc, m) pair each into the record.
+// (the source payload at 144*b + 16 is 4-byte aligned when the plane is);
+// lanes 0..7 unpack one (sc, m) pair each into the record.
 __global__ void q4k_repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst_data,
                                   uint8_t* __restrict__ dst_scales, uint64_t n_super) {
     const uint64_t b = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (b >= n_super) return;
     const uint32_t lane = threadIdx.x & 31u;
     const uint8_t* s = src + b * 144u;
-    // destination word `lane` = (P, t, h, iw): source word (2P+h)*8 + 2t + iw
-    const uint32_t P = lane >> 4, t = (lane >> 2) & 3u, h = (lane >> 1) & 1u, iw = lane & 1u;
-    reinterpret_cast<uint32_t*>(dst_data + b * 128u)[lane] =
-        reinterpret_cast<const uint32_t*>(s + 16)[(2u * P + h) * 8u + 2u * t + iw];
+    reinterpret_cast<uint32_t*>(dst_data + b * 128u)[lane] = reinterpret_cast<const uint32_t*>(s + 16)[lane];
     uint8_t* rec = dst_scales + b * 24u;
     if (lane < 8u) {
         uint32_t sc, m;
@@ -110,8 +107,8 @@ __device__ __forceinline__ void bar_sync(uint32_t id, uint32_t count) {
 }
 
 struct SbData {   // one super-block of two rows (g and g+8) in registers
-    uint4 lo[2];  // row g: halves P = 0, 1
-    uint4 hi[2];  // row g + 8
+    uint2 lo[4];  // row g: bytes 8t..8t+7 of groups 0..3
+    uint2 hi[4];  // row g + 8
 };
 struct SbScale {  // the two rows' 24-byte records (first 20 bytes used)
     uint2 lo[3];
@@ -146,18 +143,18 @@ q4k_mma_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sca
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t slot = warp / kSlices, slice = warp % kSlices;
     const uint32_t n_tiles = (out_dim + 15u) >> 4;
-    const uint32_t per = (n_super + kSlices - 1u) / kSlices;
-    const uint32_t sb_lo = min(slice * per, n_super), sb_hi = min(sb_lo + per, n_super);
+    const uint32_t sb_lo = slice * n_super / kSlices, sb_hi = (slice + 1u) * n_super / kSlices;
 
     const size_t row_data = (size_t)n_super * 128u, row_rec = (size_t)n_super * 24u;
 
     auto load_data = [&](SbData& s, const uint8_t* p0, const uint8_t* p1, uint32_t sb) {
-        const uint8_t* a = p0 + (size_t)sb * 128u + t * 16u;
-        const uint8_t* b = p1 + (size_t)sb * 128u + t * 16u;
-        s.lo[0] = pdk_ldg_stream16(a);
-        s.lo[1] = pdk_ldg_stream16(a + 64);
-        s.hi[0] = pdk_ldg_stream16(b);
-        s.hi[1] = pdk_ldg_stream16(b + 64);
+        const uint8_t* a = p0 + (size_t)sb * 128u + t * 8u;
+        const uint8_t* b = p1 + (size_t)sb * 128u + t * 8u;
+#pragma unroll
+        for (uint32_t G = 0; G < 4u; ++G) {
+            s.lo[G] = pdk_ldg_stream8(a + G * 32u);
+            s.hi[G] = pdk_ldg_stream8(b + G * 32u);
+        }
     };
     auto load_scale = [&](SbScale& s, const uint8_t* r0, const uint8_t* r1, uint32_t sb) {
         const uint2* a = reinterpret_cast<const uint2*>(r0 + (size_t)sb * 24u);
@@ -245,10 +242,8 @@ q4k_mma_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sca
 #pragma unroll
             for (uint32_t G = 0; G < 4u; ++G) {
                 // words of rows g / g+8 for group G: (W0, W1) of the 8 bytes
-                const uint4& ql = dd.lo[G >> 1];
-                const uint4& qh = dd.hi[G >> 1];
-                const uint32_t wl0 = (G & 1u) ? ql.z : ql.x, wl1 = (G & 1u) ? ql.w : ql.y;
-                const uint32_t wh0 = (G & 1u) ? qh.z : qh.x, wh1 = (G & 1u) ? qh.w : qh.y;
+                const uint32_t wl0 = dd.lo[G].x, wl1 = dd.lo[G].y;
+                const uint32_t wh0 = dd.hi[G].x, wh1 = dd.hi[G].y;
 #pragma unroll
                 for (uint32_t h = 0; h < 2u; ++h) {  // h = 0: low nibbles (sub-block 2G), 1: high
                     const uint32_t j = 2u * G + h;
@@ -368,8 +363,8 @@ q4k_gemv_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sc
     __syncthreads();
 
     const uint32_t n_super = in_dim >> 8;
-    // word `lane` of the permuted payload = ggml group G, word w of that group
-    const uint32_t G = 2u * (lane >> 4) + ((lane >> 1) & 1u), w = 2u * ((lane >> 2) & 3u) + (lane & 1u);
+    // word `lane` of the payload = ggml group G, word w of that group
+    const uint32_t G = lane >> 3, w = lane & 7u;
     const uint32_t koff = G * 64u + w * 4u;  // first low-nibble element inside the super-block
     for (uint32_t row = blockIdx.x * kWarps + warp; row < out_dim; row += gridDim.x * kWarps) {
         const uint8_t* drow = data + (size_t)row * n_super * 128u;
@@ -474,6 +469,10 @@ bool force_plain() {
 
 int gemm_any(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
              uint32_t batch, cudaStream_t st) {
+    if (!force_plain() && batch == 1u) {
+        const int rc = pdk_q4k_gemv_diag(data, scales, x, y, in_dim, out_dim, st);
+        if (rc != -1) return rc;
+    }
     if (!force_plain()) {
         uint32_t b = 0;
         int rc = 0;

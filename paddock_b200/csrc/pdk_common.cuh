@@ -32,6 +32,11 @@ __device__ __forceinline__ uint4 pdk_ldg_stream16(const void* p) {
                  : "l"(p));
     return r;
 }
+__device__ __forceinline__ uint2 pdk_ldg_stream8(const void* p) {
+    uint2 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+    return r;
+}
 __device__ __forceinline__ uint32_t pdk_ldg_stream4(const void* p) {
     uint32_t r;
     asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));

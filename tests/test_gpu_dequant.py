@@ -92,9 +92,7 @@ def test_q4_k_dequant_random_bytes_bit_exact(pack):
 
 
 def test_q4_k_repack_layout(pack):
-    """128 nibble bytes permuted per super-block (byte P*64 + t*16 + h*8 + i holds
-    ggml byte (2P+h)*32 + 8t + i) + the 24-byte scale record of
-    packs/cuda/src/quant/kquant.cuh:37-54."""
+    """packs/cuda/src/quant/kquant.cuh:37-54: nibbles verbatim + 24-byte record."""
     n_super = 40
     raw = oracle.quantize_q4_k(oracle.fill_normal(n_super * 256, 77, 0.02))
     d_data = torch.zeros(n_super * 128, dtype=torch.uint8, device="cuda")
@@ -103,14 +101,7 @@ def test_q4_k_repack_layout(pack):
     torch.cuda.synchronize()
     data, rec = host(d_data, np.uint8).reshape(n_super, 128), host(d_sc, np.uint8).reshape(n_super, 24)
     src = raw.reshape(n_super, 144)
-    perm = np.empty(128, np.int64)
-    for P in range(2):
-        for t in range(4):
-            for h in range(2):
-                for i in range(8):
-                    perm[P * 64 + t * 16 + h * 8 + i] = (2 * P + h) * 32 + 8 * t + i
-    assert sorted(perm.tolist()) == list(range(128))
-    assert np.array_equal(data, src[:, 16:][:, perm])
+    assert np.array_equal(data, src[:, 16:])
     assert np.array_equal(rec[:, 0:4], src[:, 0:4])
     assert not rec[:, 20:24].any()
     for b in range(n_super):
