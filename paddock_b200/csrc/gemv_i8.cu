@@ -1,0 +1,357 @@
+// gemv_i8.cu - single-token decode GEMV for Q4_K and Q8_0 planes.
+//
+// Both formats are integer codes with one f32-class scale per 32 weights, and
+// the GEMV is HBM-bound (4.5 / 8.5 bits per weight, each read once), so the
+// kernel's job is to stay far below one instruction per weight:
+//
+//   * The 32-element inner sums run on the tensor cores as exact integer dot
+//     products (mma m16n8k32, s8 x s8 -> s32).  Q8_0 bytes are the A operand
+//     as loaded; a Q4_K word of eight nibbles becomes two A registers with two
+//     logic ops.
+//   * The activation vector is turned into block floating point once per CTA:
+//     per 32-element block a power-of-two step s and a 15-bit integer
+//     v = rint(x/s), |v| <= 2^14, kept as two int8 limbs v = 256*hi + lo.  For
+//     bf16-valued activations this is exact unless a block spans more than 7
+//     binades; in general the error is below 2^-15 of the block's largest
+//     element.  The limbs are two n-tiles of the same mma, so the weights are
+//     unpacked once.
+//   * One token would use one of an mma's eight columns.  Instead the B operand
+//     is block diagonal: the 32 k-slots of each mma are spread over the eight
+//     32-weight blocks of a 256-weight unit (4 slots each) and column c is
+//     non-zero only in block c's slots.  After the 8 mmas of a unit the
+//     accumulator tile holds C[row][c] = sum_i q x over block c for 16 rows and
+//     all eight blocks, and lane (g,t) owns exactly blocks (2t, 2t+1) of rows g
+//     and g+8, whose scales it applies in f32.
+//
+// A CTA (one per SM, persistent) runs 4 tiles of 16 rows at a time, each tile's
+// K range split over 4 warps; a warp walks all of its (tile, unit) pairs as one
+// software pipeline with its loads issued DEPTH-1 units ahead.  Lane t of a
+// row reads a contiguous quarter of the row's unit, so the four lanes of a row
+// read one contiguous 128-byte (Q4_K) or 256-byte (Q8_0) run.
+#include "pdk_common.cuh"
+
+namespace {
+
+constexpr uint32_t kSlots = 4;    // 16-row tiles in flight per CTA
+constexpr uint32_t kSlices = 4;   // K slices per tile, one warp each
+constexpr uint32_t kThreads = kSlots * kSlices * 32;
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void bar_sync(uint32_t id, uint32_t count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Format traits.  A "unit" is 256 weights of one row (a Q4_K super-block, or
+// eight Q8_0 blocks).  Lane t owns blocks 2t and 2t+1 of the unit.
+// ---------------------------------------------------------------------------
+struct Q4K {
+    static constexpr uint32_t kDepth = 3;
+    static constexpr uint32_t kDataBytes = 128;  // per row per unit
+    static constexpr uint32_t kRecBytes = 24;
+    struct Stage {
+        uint4 q[4];      // row g: bytes 0..15 / 16..31 of ggml group t; row g+8 likewise
+        uint32_t dd[2];  // {f16 d, f16 dmin} of the two rows
+        uint32_t sm[2];  // sc[2t] | sc[2t+1]<<8 | m[2t]<<16 | m[2t+1]<<24
+    };
+    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
+                                                const uint8_t* r1, uint32_t t) {
+        s.q[0] = pdk_ldg_stream16(d0 + t * 32u);
+        s.q[1] = pdk_ldg_stream16(d0 + t * 32u + 16u);
+        s.q[2] = pdk_ldg_stream16(d1 + t * 32u);
+        s.q[3] = pdk_ldg_stream16(d1 + t * 32u + 16u);
+        s.dd[0] = __ldg(reinterpret_cast<const uint32_t*>(r0));
+        s.dd[1] = __ldg(reinterpret_cast<const uint32_t*>(r1));
+        s.sm[0] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r0 + 4u + 2u * t)) |
+                  ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r0 + 12u + 2u * t)) << 16);
+        s.sm[1] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r1 + 4u + 2u * t)) |
+                  ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r1 + 12u + 2u * t)) << 16);
+    }
+    // A registers of mma i (i = 0..7): word i of the lane's 32 bytes, low nibbles
+    // (block 2t) in k-slots 4t..4t+3, high nibbles (block 2t+1) in slots 16+4t..
+    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint4& lo = s.q[i >> 2];
+        const uint4& hi = s.q[2u + (i >> 2)];
+        const uint32_t wl = (i & 3u) == 0u ? lo.x : (i & 3u) == 1u ? lo.y : (i & 3u) == 2u ? lo.z : lo.w;
+        const uint32_t wh = (i & 3u) == 0u ? hi.x : (i & 3u) == 1u ? hi.y : (i & 3u) == 2u ? hi.z : hi.w;
+        a0 = wl & 0x0F0F0F0Fu;
+        a1 = wh & 0x0F0F0F0Fu;
+        a2 = (wl >> 4) & 0x0F0F0F0Fu;
+        a3 = (wh >> 4) & 0x0F0F0F0Fu;
+    }
+    // f[0..1]: row g blocks 2t, 2t+1 (already times the activation step); f[2..3]: row g+8.
+    // X0, X1: the blocks' activation sums.
+    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float X0, float X1,
+                                                float& acc_g, float& acc_g8) {
+        {
+            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[0]);
+            const float s0 = (float)(s.sm[0] & 0xffu), s1 = (float)((s.sm[0] >> 8) & 0xffu);
+            const float m0 = (float)((s.sm[0] >> 16) & 0xffu), m1 = (float)(s.sm[0] >> 24);
+            acc_g += __low2float(dh) * (s0 * f[0] + s1 * f[1]) - __high2float(dh) * (m0 * X0 + m1 * X1);
+        }
+        {
+            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[1]);
+            const float s0 = (float)(s.sm[1] & 0xffu), s1 = (float)((s.sm[1] >> 8) & 0xffu);
+            const float m0 = (float)((s.sm[1] >> 16) & 0xffu), m1 = (float)(s.sm[1] >> 24);
+            acc_g8 += __low2float(dh) * (s0 * f[2] + s1 * f[3]) - __high2float(dh) * (m0 * X0 + m1 * X1);
+        }
+    }
+};
+
+struct Q80 {
+    static constexpr uint32_t kDepth = 2;
+    static constexpr uint32_t kDataBytes = 256;  // 8 blocks of 32 int8
+    static constexpr uint32_t kRecBytes = 16;    // 8 f16 scales
+    struct Stage {
+        uint4 q[8];      // row g: blocks 2t, 2t+1 (64 bytes); row g+8 likewise
+        uint32_t dd[2];  // {f16 d[2t], f16 d[2t+1]} of the two rows
+    };
+    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
+                                                const uint8_t* r1, uint32_t t) {
+#pragma unroll
+        for (uint32_t i = 0; i < 4u; ++i) {
+            s.q[i] = pdk_ldg_stream16(d0 + t * 64u + i * 16u);
+            s.q[4u + i] = pdk_ldg_stream16(d1 + t * 64u + i * 16u);
+        }
+        s.dd[0] = __ldg(reinterpret_cast<const uint32_t*>(r0 + 4u * t));
+        s.dd[1] = __ldg(reinterpret_cast<const uint32_t*>(r1 + 4u * t));
+    }
+    __device__ static __forceinline__ uint32_t word(const uint4& v, uint32_t i) {
+        return i == 0u ? v.x : i == 1u ? v.y : i == 2u ? v.z : v.w;
+    }
+    // mma i: word i of block 2t in slots 4t..4t+3, word i of block 2t+1 in slots 16+4t..
+    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        a0 = word(s.q[i >> 2], i & 3u);
+        a2 = word(s.q[2u + (i >> 2)], i & 3u);
+        a1 = word(s.q[4u + (i >> 2)], i & 3u);
+        a3 = word(s.q[6u + (i >> 2)], i & 3u);
+    }
+    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float, float, float& acc_g,
+                                                float& acc_g8) {
+        const __half2 d0 = *reinterpret_cast<const __half2*>(&s.dd[0]);
+        const __half2 d1 = *reinterpret_cast<const __half2*>(&s.dd[1]);
+        acc_g += __low2float(d0) * f[0] + __high2float(d0) * f[1];
+        acc_g8 += __low2float(d1) * f[2] + __high2float(d1) * f[3];
+    }
+};
+
+// Shared memory: limb planes int8 [2][K] (hi, lo), 32 zero bytes,
+// xmeta float2 [K/32] = {step s_j, s_j * sum_i v_ji}, red f32 [2][kSlots][kSlices][16].
+template <class F>
+__global__ void __launch_bounds__(kThreads, 1)
+gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ recs, const float* __restrict__ bias,
+               const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim, uint32_t out_dim) {
+    using Stage = typename F::Stage;
+    constexpr uint32_t DEPTH = F::kDepth;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t n_blk = in_dim >> 5, n_unit = in_dim >> 8;
+    uint8_t* xs_hi = smem;
+    uint8_t* xs_lo = smem + in_dim;
+    uint8_t* zeros = smem + 2u * (size_t)in_dim;
+    float2* xmeta = reinterpret_cast<float2*>(zeros + 32u);
+    float* red = reinterpret_cast<float*>(xmeta + n_blk);
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t slot = warp / kSlices, slice = warp % kSlices;
+    const uint32_t n_tiles = (out_dim + 15u) >> 4;
+    const uint32_t u_lo = slice * n_unit / kSlices, u_hi = (slice + 1u) * n_unit / kSlices;
+    const uint32_t len = u_hi - u_lo;
+    const size_t row_data = (size_t)n_unit * F::kDataBytes, row_rec = (size_t)n_unit * F::kRecBytes;
+
+    const uint32_t tile0 = blockIdx.x * kSlots + slot, tile_stride = gridDim.x * kSlots;
+    const uint32_t my_tiles = tile0 < n_tiles ? (n_tiles - tile0 + tile_stride - 1u) / tile_stride : 0u;
+    const uint32_t total = my_tiles * len;
+
+    // ---- load cursor over this warp's (tile, unit) sequence
+    uint32_t l_tile = tile0, l_u = u_lo;
+    const uint8_t *p0 = data, *p1 = data, *r0 = recs, *r1 = recs;
+    auto set_rows = [&](uint32_t tl) {
+        const uint32_t ra = min(tl * 16u + g, out_dim - 1u), rb = min(tl * 16u + g + 8u, out_dim - 1u);
+        p0 = data + ra * row_data;
+        p1 = data + rb * row_data;
+        r0 = recs + ra * row_rec;
+        r1 = recs + rb * row_rec;
+    };
+    auto issue = [&](Stage& s) {
+        F::load(s, p0 + (size_t)l_u * F::kDataBytes, p1 + (size_t)l_u * F::kDataBytes,
+                r0 + (size_t)l_u * F::kRecBytes, r1 + (size_t)l_u * F::kRecBytes, t);
+        if (++l_u == u_hi) {
+            l_u = u_lo;
+            l_tile += tile_stride;
+            if (l_tile < n_tiles) set_rows(l_tile);
+        }
+    };
+
+    Stage st[DEPTH];
+    if (total > 0u) {
+        set_rows(tile0);
+#pragma unroll
+        for (uint32_t d = 0; d + 1u < DEPTH; ++d)
+            if (d < total) issue(st[d]);
+    }
+
+    // ---- activations -> block floating point limbs (8 elements per thread,
+    //      the 4 lanes of a block agree on the step through two shuffles)
+    {
+        const uint32_t groups = in_dim >> 3;
+        for (uint32_t grp = tid; grp < groups; grp += kThreads) {
+            const float4 a = *reinterpret_cast<const float4*>(x + grp * 8u);
+            const float4 b = *reinterpret_cast<const float4*>(x + grp * 8u + 4u);
+            const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            // amax < 2^ex  ->  step 2^(ex-14) keeps |v| <= 2^14
+            int ex = 0;
+            float step = 1.0f, inv = 0.0f;
+            if (amax > 0.0f && amax < 3.0e38f) {
+                (void)frexpf(amax, &ex);
+                ex = max(ex, -110);
+                step = ldexpf(1.0f, ex - 14);
+                inv = ldexpf(1.0f, 14 - ex);
+            }
+            uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+            int isum = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                int q = __float2int_rn(v[i] * inv);
+                q = max(-16384, min(16384, q));
+                const int h = (q + 128) >> 8, l = q - (h << 8);
+                hi[i >> 2] |= ((uint32_t)h & 0xffu) << (8 * (i & 3));
+                lo[i >> 2] |= ((uint32_t)l & 0xffu) << (8 * (i & 3));
+                isum += q;
+            }
+            *reinterpret_cast<uint2*>(xs_hi + (size_t)grp * 8u) = make_uint2(hi[0], hi[1]);
+            *reinterpret_cast<uint2*>(xs_lo + (size_t)grp * 8u) = make_uint2(lo[0], lo[1]);
+            isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+            isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+            if ((grp & 3u) == 0u) xmeta[grp >> 2] = make_float2(step, step * (float)isum);
+        }
+        if (tid < 8u) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
+    }
+    __syncthreads();
+
+    // B operand source of this lane: block 2t feeds k-slots 4t..4t+3 of column
+    // 2t, block 2t+1 feeds slots 16+4t.. of column 2t+1; every other
+    // (lane, slot) pair reads the zero line.
+    const bool role_a = (g == 2u * t), role_b = (g == 2u * t + 1u);
+
+    float acc_g = 0.0f, acc_g8 = 0.0f;
+    uint32_t c_u = u_lo, c_tile = tile0, iter = 0;
+
+    auto compute = [&](const Stage& s) {
+        int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+        const uint32_t xoff = c_u * 256u;
+        const uint8_t* ha = role_a ? xs_hi + xoff + 2u * t * 32u : zeros;
+        const uint8_t* hb = role_b ? xs_hi + xoff + (2u * t + 1u) * 32u : zeros;
+        const uint8_t* la = role_a ? xs_lo + xoff + 2u * t * 32u : zeros;
+        const uint8_t* lb = role_b ? xs_lo + xoff + (2u * t + 1u) * 32u : zeros;
+#pragma unroll
+        for (uint32_t half = 0; half < 2u; ++half) {
+            const uint4 bha = *reinterpret_cast<const uint4*>(ha + half * 16u);
+            const uint4 bhb = *reinterpret_cast<const uint4*>(hb + half * 16u);
+            const uint4 bla = *reinterpret_cast<const uint4*>(la + half * 16u);
+            const uint4 blb = *reinterpret_cast<const uint4*>(lb + half * 16u);
+            const uint32_t vha[4] = {bha.x, bha.y, bha.z, bha.w}, vhb[4] = {bhb.x, bhb.y, bhb.z, bhb.w};
+            const uint32_t vla[4] = {bla.x, bla.y, bla.z, bla.w}, vlb[4] = {blb.x, blb.y, blb.z, blb.w};
+#pragma unroll
+            for (uint32_t k = 0; k < 4u; ++k) {
+                uint32_t a0, a1, a2, a3;
+                F::a_regs(s, half * 4u + k, a0, a1, a2, a3);
+                mma_s8(ch, a0, a1, a2, a3, vha[k], vhb[k]);
+                mma_s8(cl, a0, a1, a2, a3, vla[k], vlb[k]);
+            }
+        }
+        // this lane's two blocks (2t, 2t+1) for rows g and g+8
+        const float4 xm = *reinterpret_cast<const float4*>(xmeta + c_u * 8u + 2u * t);  // {s0, X0, s1, X1}
+        float f[4];
+        f[0] = (float)(ch[0] * 256 + cl[0]) * xm.x;
+        f[1] = (float)(ch[1] * 256 + cl[1]) * xm.z;
+        f[2] = (float)(ch[2] * 256 + cl[2]) * xm.x;
+        f[3] = (float)(ch[3] * 256 + cl[3]) * xm.z;
+        F::fold(s, f, xm.y, xm.w, acc_g, acc_g8);
+
+        // ---- end of this warp's K slice for the tile: fold lanes, then slices
+        if (++c_u == u_hi) {
+            c_u = u_lo;
+            float a = acc_g, b = acc_g8;
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            b += __shfl_xor_sync(0xffffffffu, b, 1);
+            b += __shfl_xor_sync(0xffffffffu, b, 2);
+            float* rbuf = red + ((size_t)(iter & 1u) * kSlots + slot) * (kSlices * 16u);
+            if (t == 0u) {
+                rbuf[slice * 16u + g] = a;
+                rbuf[slice * 16u + g + 8u] = b;
+            }
+            bar_sync(1u + slot, kSlices * 32u);
+            const uint32_t r = slice * 32u + lane;
+            if (r < 16u) {
+                float v = (rbuf[r] + rbuf[16u + r]) + (rbuf[32u + r] + rbuf[48u + r]);
+                const uint32_t row = c_tile * 16u + r;
+                if (row < out_dim) {
+                    if (bias) v += bias[row];
+                    y[row] = v;
+                }
+            }
+            acc_g = acc_g8 = 0.0f;
+            c_tile += tile_stride;
+            ++iter;
+        }
+    };
+
+    // ---- one pipeline over every (tile, unit) of this warp, loads DEPTH-1 ahead
+    for (uint32_t q = 0; q < total; q += DEPTH) {
+#pragma unroll
+        for (uint32_t d = 0; d < DEPTH; ++d) {
+            if (q + d >= total) break;
+            if (q + d + DEPTH - 1u < total) issue(st[(d + DEPTH - 1u) % DEPTH]);
+            compute(st[d]);
+        }
+    }
+}
+
+template <class F>
+int launch(const void* data, const void* recs, const float* bias, const float* x, float* y, uint32_t in_dim,
+           uint32_t out_dim, cudaStream_t st) {
+    const uint32_t n_unit = in_dim >> 8;
+    if ((in_dim & 255u) != 0u || n_unit < kSlices) return -1;
+    const size_t smem = (size_t)in_dim * 2u + 32u + (size_t)(in_dim >> 5) * 8u + 2u * kSlots * kSlices * 16u * 4u;
+    if (smem > 200u * 1024u) return -1;
+    auto kern = gemv_i8_kernel<F>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const uint32_t n_tiles = (out_dim + 15u) / 16u;
+    uint32_t grid = (uint32_t)pdk_sm_count();
+    const uint32_t need = (n_tiles + kSlots - 1u) / kSlots;
+    if (grid > need) grid = need;
+    kern<<<grid, kThreads, smem, st>>>((const uint8_t*)data, (const uint8_t*)recs, bias, x, y, in_dim, out_dim);
+    return pdk_launch_status();
+}
+
+}  // namespace
+
+// Both return 0 / a cudaError_t, or -1 when the shape is outside the kernel's
+// plan (K not a multiple of 256, fewer than four units per row, or activations
+// too long for shared memory) and the caller should take another route.
+int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                    uint32_t out_dim, cudaStream_t st) {
+    return launch<Q4K>(data, scales, nullptr, x, y, in_dim, out_dim, st);
+}
+
+int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, const float* x, float* y,
+                     uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
+    return launch<Q80>(data, scale, bias, x, y, in_dim, out_dim, st);
+}

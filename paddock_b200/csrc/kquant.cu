@@ -21,8 +21,8 @@
 
 #include "pdk_common.cuh"
 
-int pdk_q4k_gemv_diag(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
-                      uint32_t out_dim, cudaStream_t st);
+int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                    uint32_t out_dim, cudaStream_t st);
 
 namespace {
 
@@ -130,7 +130,7 @@ template <uint32_t NT, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 q4k_mma_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ scales,
                const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim, uint32_t out_dim,
-               uint32_t batch) {
+               uint32_t batch, uint32_t magic) {
     constexpr uint32_t NCOLS = NT * 8u;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t n_sub = in_dim >> 5, n_super = in_dim >> 8;
@@ -248,11 +248,11 @@ q4k_mma_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ sca
                 for (uint32_t h = 0; h < 2u; ++h) {  // h = 0: low nibbles (sub-block 2G), 1: high
                     const uint32_t j = 2u * G + h;
                     const uint32_t sh = h * 4u;
-                    const uint32_t M = 0x000F000Fu, O = 0x43004300u;
-                    const uint32_t a0 = ((wl0 >> sh) & M) | O, a2 = ((wl0 >> (sh + 8u)) & M) | O;
-                    const uint32_t a1 = ((wh0 >> sh) & M) | O, a3 = ((wh0 >> (sh + 8u)) & M) | O;
-                    const uint32_t e0 = ((wl1 >> sh) & M) | O, e2 = ((wl1 >> (sh + 8u)) & M) | O;
-                    const uint32_t e1 = ((wh1 >> sh) & M) | O, e3 = ((wh1 >> (sh + 8u)) & M) | O;
+                    const uint32_t M = 0x000F000Fu, O = magic;  // 0x43004300: bf16 128.0 twice
+                    const uint32_t a0 = pdk_and_or(wl0 >> sh, M, O), a2 = pdk_and_or(wl0 >> (sh + 8u), M, O);
+                    const uint32_t a1 = pdk_and_or(wh0 >> sh, M, O), a3 = pdk_and_or(wh0 >> (sh + 8u), M, O);
+                    const uint32_t e0 = pdk_and_or(wl1 >> sh, M, O), e2 = pdk_and_or(wl1 >> (sh + 8u), M, O);
+                    const uint32_t e1 = pdk_and_or(wh1 >> sh, M, O), e3 = pdk_and_or(wh1 >> (sh + 8u), M, O);
                     const uint32_t bsh = (j & 3u) * 8u;
                     const float sl = (float)((sc_lo[j >> 2] >> bsh) & 0xffu), ml = (float)((mn_lo[j >> 2] >> bsh) & 0xffu);
                     const float su = (float)((sc_hi[j >> 2] >> bsh) & 0xffu), mu = (float)((mn_hi[j >> 2] >> bsh) & 0xffu);
@@ -339,7 +339,8 @@ int launch_mma(const void* data, const void* scales, const float* x, float* y, u
     uint32_t grid = (uint32_t)pdk_sm_count();
     const uint32_t need = (n_tiles + kTileSlots - 1u) / kTileSlots;
     if (grid > need) grid = need;
-    kern<<<grid, kThreads, smem, st>>>((const uint8_t*)data, (const uint8_t*)scales, x, y, in_dim, out_dim, batch);
+    kern<<<grid, kThreads, smem, st>>>((const uint8_t*)data, (const uint8_t*)scales, x, y, in_dim, out_dim, batch,
+                                       0x43004300u);
     return pdk_launch_status();
 }
 
@@ -470,7 +471,7 @@ bool force_plain() {
 int gemm_any(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
              uint32_t batch, cudaStream_t st) {
     if (!force_plain() && batch == 1u) {
-        const int rc = pdk_q4k_gemv_diag(data, scales, x, y, in_dim, out_dim, st);
+        const int rc = pdk_q4k_gemv_i8(data, scales, x, y, in_dim, out_dim, st);
         if (rc != -1) return rc;
     }
     if (!force_plain()) {

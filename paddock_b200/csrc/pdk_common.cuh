@@ -32,6 +32,14 @@ __device__ __forceinline__ uint4 pdk_ldg_stream16(const void* p) {
                  : "l"(p));
     return r;
 }
+// (a & m) | o in one LOP3.  `o` must live in a register: callers pass a value
+// that comes in as a kernel argument so it is not folded into a second immediate.
+__device__ __forceinline__ uint32_t pdk_and_or(uint32_t a, uint32_t m, uint32_t o) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(m), "r"(o));
+    return d;
+}
+
 __device__ __forceinline__ uint2 pdk_ldg_stream8(const void* p) {
     uint2 r;
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));

@@ -1,4 +1,4 @@
-// q8_0.cu - Q8_0 decode GEMV / small-batch GEMM over the repacked planes
+// q8_0.cu - Q8_0 launchers and the plain-load f32 GEMV / small-batch GEMM over the repacked planes
 // (int8 data [out][in] + f16 scale [out][in/32]).
 //
 // HBM-bound: 8.5 bits per weight are streamed once.  A warp owns one output
@@ -7,9 +7,23 @@
 // in flight.  Activations sit in shared memory as f32; the 16-term inner
 // products and the scale application are exact f32 (reduction order differs
 // from a scalar walk, nothing else).
+#include <cstdlib>
+
 #include "pdk_common.cuh"
 
+int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, const float* x, float* y,
+                     uint32_t in_dim, uint32_t out_dim, cudaStream_t st);
+
 namespace {
+
+// PDK_Q8_PLAIN=1 forces the plain-load f32 kernel (A/B switch, read once).
+bool force_plain() {
+    static const bool v = [] {
+        const char* e = getenv("PDK_Q8_PLAIN");
+        return e && e[0] == '1';
+    }();
+    return v;
+}
 
 constexpr uint32_t kWarps = 8;         // warps per CTA
 constexpr uint32_t kMaxChunks = 16;    // 16 * 512 = 8192 elements per register pass
@@ -134,6 +148,11 @@ PDK_EXPORT int pd_q8_0_gemv_repacked(const void* data, const void* scale, const 
                                      uint32_t in_dim, uint32_t out_dim, void* stream) {
     if (out_dim == 0) return 0;
     if (int rc = check(data, scale, x, y, in_dim)) return rc;
+    if (!force_plain()) {
+        const int rc = pdk_q8_0_gemv_i8(data, scale, (const float*)bias, (const float*)x, (float*)y, in_dim, out_dim,
+                                        (cudaStream_t)stream);
+        if (rc != -1) return rc;
+    }
     return dispatch<1>(data, scale, bias, (const float*)x, (float*)y, in_dim, out_dim, 0u, (cudaStream_t)stream);
 }
 

@@ -1,7 +1,10 @@
 """Decode GEMV / small-batch GEMM parity against the CPU oracle: outputs within
 1e-2 (the stated tolerance) of an f64 matmul of the dequantized weights, both
-as max |err| / sum|w x| and as rel-L2; the exact-f32 kernels are additionally
-held to 1e-5."""
+as max |err| / sum|w x| and as rel-L2.  The kernels are held much tighter than
+that: the weights' integer dot products are exact and the activations are
+carried as 15-bit block floating point (error below 2^-15 of each 32-element
+block's largest value), so rel-L2 stays under 1e-4 and the condition-aware
+error under 1e-5."""
 import numpy as np
 import pytest
 import torch
@@ -34,10 +37,10 @@ def test_q8_0_gemv_shapes(pack, k, n):
     ref, ab = oracle.matmul_f64(wd, x, k, n, 1, with_abs=True)
     y = d_y.cpu().numpy() - bias
     assert cond_err(y, ref[0], ab[0]) < 1e-5
-    assert rel_l2(y, ref[0]) < 1e-5 < TOL
-    # the reference CPU path (scalar f32, ascending k) agrees to f32 rounding
+    assert rel_l2(y, ref[0]) < 1e-4 < TOL
+    # the reference CPU path (scalar f32, ascending k) agrees to the same bound
     y_cpu = oracle.matvec_f32(wd, x, k, n)
-    assert rel_l2(y, y_cpu.astype(np.float64)) < 1e-5
+    assert rel_l2(y, y_cpu.astype(np.float64)) < 1e-4
 
 
 def test_q8_0_gemv_config1_rows(pack):
