@@ -251,7 +251,7 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
     float acc_g = 0.0f, acc_g8 = 0.0f;
     uint32_t c_u = u_lo, c_tile = tile0, iter = 0;
 
-    auto compute = [&](const Stage& s) {
+    auto compute = [&](const Stage& s, auto&& prefetch) {
         int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
         const uint32_t xoff = c_u * 256u;
         const uint8_t* ha = role_a ? xs_hi + xoff + 2u * t * 32u : zeros;
@@ -274,6 +274,10 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
                 mma_s8(cl, a0, a1, a2, a3, vla[k], vlb[k]);
             }
         }
+        // The next loads are issued only now, after every register of this unit
+        // has been consumed: a wait on this unit's data can then never be a wait
+        // on loads that were issued a moment ago.
+        prefetch();
         // this lane's two blocks (2t, 2t+1) for rows g and g+8
         const float4 xm = *reinterpret_cast<const float4*>(xmeta + c_u * 8u + 2u * t);  // {s0, X0, s1, X1}
         float f[4];
@@ -317,8 +321,9 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
 #pragma unroll
         for (uint32_t d = 0; d < DEPTH; ++d) {
             if (q + d >= total) break;
-            if (q + d + DEPTH - 1u < total) issue(st[(d + DEPTH - 1u) % DEPTH]);
-            compute(st[d]);
+            compute(st[d], [&] {
+                if (q + d + DEPTH - 1u < total) issue(st[(d + DEPTH - 1u) % DEPTH]);
+            });
         }
     }
 }
