@@ -69,7 +69,11 @@ enum PdkSlot {
     PDK_SLOT_q8_0_gemm_repacked = 57,
     PDK_SLOT_kquant_dequant = 202,
     PDK_SLOT_kquant_repack = 203,
-    PDK_SLOT_kquant_gemv = 204
+    PDK_SLOT_kquant_gemv = 204,
+    PDK_SLOT_quantize_e4m3_row = 183,
+    PDK_SLOT_f8row_gemm = 184,
+    PDK_SLOT_bf16_to_f8row = 375,
+    PDK_SLOT_f8row_gemm_tc5x = 855
 };
 
 /* ---- the drop-in boundary ------------------------------------------------ */
@@ -115,6 +119,31 @@ int pd_kquant_gemv(const void* data, const void* scales, const void* x, void* y,
 int pdk_kquant_gemm_f32(const void* data, const void* scales, const void* x, void* y,
                         uint32_t in_dim, uint32_t out_dim, uint32_t batch, uint32_t dtype,
                         void* stream);
+
+/* ---- FP8 E4M3, one f32 scale per row ----------------------------------------- */
+
+/* slot 375, packs/cuda/src/gemm/dense_fp4_w8.cuh:627-677: bf16 weights [out][in] ->
+ * e4m3 [out][in] + f32 row scale 2^e, e = ex - 9 + (fr > 0.875) for amax = fr*2^ex. */
+int pd_bf16_to_f8row(const void* bf16, void* f8_data, void* row_scale, uint32_t in_dim, uint32_t out_dim,
+                     void* stream);
+/* slot 183, packs/cuda/src/gemm/dense_f8_decode.cuh:3179-3235: f32 activations
+ * [batch][n_dim] -> e4m3 + f32 scale per token row, same power-of-two rule. */
+int pd_quantize_e4m3_row(const void* x, void* q, void* rscale, uint32_t n_dim, uint32_t batch, void* stream);
+/* slot 184, packs/cuda/src/gemm/dense_f8_decode.cuh:4638-4722 (kernel gemm/dense_tc5.cuh:46-215):
+ * y f32 [batch][out] = (sum_k W[o][k] Xq[t][k]) * w_rowscale[o] * x_rowscale[t], tcgen05 + TMA.
+ * in_dim must be a multiple of 16; data and xq 16-byte aligned. */
+int pd_f8row_gemm(const void* data, const void* w_rowscale, const void* xq, const void* x_rowscale, void* y,
+                  uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* stream);
+/* slot 855, packs/cuda/src/gemm/dense_nvf4_tc5.cuh:1480-1515: same contract as slot 184. */
+int pd_f8row_gemm_tc5x(const void* data, const void* w_rowscale, const void* xq, const void* x_rowscale, void* y,
+                       uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* stream);
+/* No slot: slot 184 with bf16 output (the reference writes f32). */
+int pdk_f8row_gemm_bf16(const void* data, const void* w_rowscale, const void* xq, const void* x_rowscale, void* y,
+                        uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* stream);
+/* No slot: reads and clears the device error word the tcgen05 kernels report a
+ * timed-out wait in (0 = none; code << 8 | detail otherwise).  Synchronizes the
+ * device, so it is a test / diagnostics call, never part of a launch path. */
+unsigned int pdk_device_error(void);
 
 /* ---- MXFP4 ----------------------------------------------------------------- */
 

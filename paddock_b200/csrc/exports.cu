@@ -36,6 +36,10 @@ static void fill_table() {
     PDK_SET(kquant_dequant);
     PDK_SET(kquant_repack);
     PDK_SET(kquant_gemv);
+    PDK_SET(quantize_e4m3_row);
+    PDK_SET(f8row_gemm);
+    PDK_SET(bf16_to_f8row);
+    PDK_SET(f8row_gemm_tc5x);
 #undef PDK_SET
 }
 

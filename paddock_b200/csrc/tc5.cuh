@@ -1,0 +1,187 @@
+// tc5.cuh - sm_100a building blocks shared by the tcgen05 GEMMs: mbarriers with
+// bounded waits, TMA tensor maps and loads, tensor-memory allocation, UMMA
+// descriptors, MMA issue / commit and TMEM loads.
+//
+// Every wait in here is bounded: a wait that has not succeeded after
+// kWaitBudgetNs records a code in the device error word and returns false, and
+// the kernels built on it then leave their loops, free their tensor memory and
+// exit.  Nothing spins forever and nothing traps.
+#pragma once
+#include <cuda.h>
+
+#include "pdk_common.cuh"
+
+// Device error word: 0 = no error.  Kernels OR in (code << 8 | detail); the host
+// reads it through pdk_device_error().  Launchers pass its device address
+// (pdk_error_word(), resolved once per device) to the kernels.
+unsigned int* pdk_error_word();
+
+namespace tc5 {
+
+constexpr unsigned long long kWaitBudgetNs = 1000000000ull;  // 1 s per wait
+
+enum ErrCode : unsigned int {
+    kErrFullWait = 1,      // MMA warp: TMA data never arrived
+    kErrEmptyWait = 2,     // producer: smem stage never released
+    kErrTmemFullWait = 3,  // epilogue: accumulator never completed
+    kErrTmemEmptyWait = 4, // MMA warp: accumulator never drained
+    kErrTestWait = 5       // self-test: a barrier nothing arrives on
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+struct WaitCtx {
+    volatile int* abort_flag;  // shared-memory flag: one role gave up, the others leave too
+    unsigned int* err;         // device error word
+};
+
+__device__ __forceinline__ void report(unsigned int* err, unsigned int code, unsigned int detail) {
+    atomicOr(err, (code << 8) | (detail & 0xffu));
+}
+
+// ---- mbarrier --------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: true when the phase completed; false after the budget (the
+// caller must then abandon its loop).  `abort_flag` lets the other roles of the
+// CTA leave early once one of them has given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, unsigned int code,
+                                          unsigned int detail) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0u) {
+            if (*ctx.abort_flag) return false;
+            if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+                *ctx.abort_flag = 1;
+                report(ctx.err, code, detail);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// ---- TMA -------------------------------------------------------------------
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
+}
+// 2-D tiled load: x = innermost (byte) coordinate, y = row.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int32_t x,
+                                            int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// ---- tensor memory -----------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols) {  // one full warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {  // one full warp
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ---- descriptors ---------------------------------------------------------------
+// Shared-memory operand descriptor, K-major tile with 128-byte rows written by
+// a SWIZZLE_128B tensor map: start address and offsets in 16-byte units,
+// stride between 8-row groups 1024 bytes, descriptor version 1, layout 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)1u << 16) | ((uint64_t)64u << 32) | ((uint64_t)1u << 46) |
+           ((uint64_t)2u << 61);
+}
+// Instruction descriptor for kind::f8f6f4 / kind::f16: D = f32, both operands
+// K-major.  fmt: f8f6f4 0 = e4m3, 1 = e5m2, 5 = e2m1; f16 kind 0 = f16, 1 = bf16.
+__host__ __device__ constexpr uint32_t idesc_f32acc(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n) {
+    return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// ---- MMA issue (one thread) ------------------------------------------------------
+__device__ __forceinline__ void mma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on `bar` once every MMA this thread has issued so far has completed.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// ---- TMEM -> registers: 32 lanes x 32 columns of 32 bits per warp ------------------
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+}  // namespace tc5
+
+// Host: 2-D byte/element tensor map with 128-byte-swizzled boxes.
+//   inner  = innermost extent in elements, rows = outer extent,
+//   pitch  = bytes between rows (multiple of 16), box = {inner elements, rows}.
+// Returns 0 or a cudaError_t.
+int pdk_make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
+                     uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_inner, uint32_t box_rows);

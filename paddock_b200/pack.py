@@ -97,10 +97,13 @@ _SIGS = {
     "mxfp4_dequant_f32": "ppU", "q8_0_dequant_f32": "ppU", "add_inplace_f32": "ppu",
     "mxfp4_repack": "pppU", "q8_0_repack": "pppU",
     "q8_0_gemv_repacked": "pppppuu", "q8_0_gemm_repacked": "pppppuuu",
+    "quantize_e4m3_row": "pppuu", "bf16_to_f8row": "pppuu",
+    "f8row_gemm": "pppppuuu", "f8row_gemm_tc5x": "pppppuuu",
     "kquant_dequant": "ppUu", "kquant_repack": "pppUu", "kquant_gemv": "ppppuuu",
 }
 _EXTRA_SIGS = {
     "pdk_kquant_gemm_f32": "ppppuuuu",
+    "pdk_f8row_gemm_bf16": "pppppuuu",
 }
 _KIND = {"p": C.c_void_p, "u": C.c_uint32, "U": C.c_uint64, "f": C.c_float}
 
@@ -178,6 +181,12 @@ class KernelPack:
             f.argtypes = [_KIND[c] for c in _EXTRA_SIGS[symbol]] + [C.c_void_p]
             self._fns[symbol] = f
         return self._fns[symbol]
+
+    def device_error(self):
+        """Read and clear the device error word (0 = no timed-out wait)."""
+        f = self._lib.pdk_device_error
+        f.restype = C.c_uint
+        return f()
 
     def call(self, name, *args, stream=0):
         """Launch slot `name` (or a named extra) and raise LaunchError on a
