@@ -73,7 +73,12 @@ enum PdkSlot {
     PDK_SLOT_quantize_e4m3_row = 183,
     PDK_SLOT_f8row_gemm = 184,
     PDK_SLOT_bf16_to_f8row = 375,
-    PDK_SLOT_f8row_gemm_tc5x = 855
+    PDK_SLOT_f8row_gemm_tc5x = 855,
+    PDK_SLOT_quantize_nvf4 = 119,
+    PDK_SLOT_nvf4_dequant = 393,
+    PDK_SLOT_nvf4_gemv = 394,
+    PDK_SLOT_nvf4_gemm_tc5w = 852,
+    PDK_SLOT_nvf4_tc5_tile_scales = 853
 };
 
 /* ---- the drop-in boundary ------------------------------------------------ */
@@ -144,6 +149,33 @@ int pdk_f8row_gemm_bf16(const void* data, const void* w_rowscale, const void* xq
  * timed-out wait in (0 = none; code << 8 | detail otherwise).  Synchronizes the
  * device, so it is a test / diagnostics call, never part of a launch path. */
 unsigned int pdk_device_error(void);
+
+/* ---- NVFP4: e2m1 nibbles (low nibble = even k), e4m3 scale per 16, f32 scale2 per tensor --- */
+
+/* slot 119, packs/cuda/src/quant/nvf4.cuh:405-421 (rules quant/e2m1.cuh:12-41): f32 x[n] ->
+ * q u8[n/2] + scale u8[n/16]; scale = RN_e4m3(amax/6), at least the smallest subnormal when
+ * amax > 0; element = RN-even e2m1 of v/scale.  n % 32 == 0. */
+int pd_quantize_nvf4(const void* x, void* q, void* scale, uint32_t n, void* stream);
+/* slot 393, packs/cuda/src/quant/nvf4.cuh:4365-4403: y f32[out][in] = (e2m1 * e4m3) * scale2. */
+int pd_nvf4_dequant(const void* data, const void* scale, float scale2, void* y, uint32_t in_dim,
+                    uint32_t out_dim, void* stream);
+/* slot 394, packs/cuda/src/quant/nvf4.cuh:4436-4779: W4A16 decode GEMV, f32 x,
+ * y[o] = scale2 * sum + bias[o] (bias may be NULL). */
+int pd_nvf4_gemv(const void* data, const void* scale, const void* bias, const void* x, void* y, float scale2,
+                 uint32_t in_dim, uint32_t out_dim, void* stream);
+/* slot 853, packs/cuda/src/gemm/dense_nvf4_tc5.cuh:845-861,981-994: weight scales [out][in/16]
+ * -> ceil(out/128) * (in/256) records of 2048 bytes in the tensor core's scale-cell order.
+ * in_dim % 256 == 0. */
+int pd_nvf4_tc5_tile_scales(const void* scale, void* tiled, uint32_t in_dim, uint32_t out_dim, void* stream);
+/* slot 852, packs/cuda/src/gemm/dense_nvf4_tc5.cuh:1216-1263: W4A4 GEMM, tcgen05 kind::mxf4nvf4 with
+ * hardware block scaling.  xq u8[batch][in/2] + xs e4m3[batch][in/16] as pd_quantize_nvf4 writes
+ * them; y f32[batch][out] = scale2 * acc + bias.  part / part_floats are accepted and unused. */
+int pd_nvf4_gemm_tc5w(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs,
+                      void* y, float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* part,
+                      uint64_t part_floats, void* stream);
+/* No slot: slot 852 with bf16 output and without the unused scratch arguments. */
+int pdk_nvf4_gemm_bf16(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs,
+                       void* y, float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* stream);
 
 /* ---- MXFP4 ----------------------------------------------------------------- */
 

@@ -40,6 +40,11 @@ static void fill_table() {
     PDK_SET(f8row_gemm);
     PDK_SET(bf16_to_f8row);
     PDK_SET(f8row_gemm_tc5x);
+    PDK_SET(quantize_nvf4);
+    PDK_SET(nvf4_dequant);
+    PDK_SET(nvf4_gemv);
+    PDK_SET(nvf4_gemm_tc5w);
+    PDK_SET(nvf4_tc5_tile_scales);
 #undef PDK_SET
 }
 

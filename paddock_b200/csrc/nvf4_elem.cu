@@ -1,0 +1,191 @@
+// nvf4_elem.cu - NVFP4 element kernels: activation quantizer, dequant, the
+// weight-scale tiler for the tcgen05 GEMM, and the W4A16 decode GEMV.
+//
+// NVFP4 plane (ModelOpt / llm-compressor checkpoints):
+//   data   u8  [out][in/2]   e2m1 nibbles, low nibble = even element
+//   scale  u8  [out][in/16]  e4m3 per 16 elements
+//   scale2 f32               per tensor;  w = (e2m1 * e4m3) * scale2
+#include <cuda_fp8.h>
+
+#include "pdk_common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
+    const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+    return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+__device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
+    // magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 stored doubled, one per byte
+    const uint64_t mags2 = 0x0C08060403020100ull;
+    const float m = 0.5f * (float)(uint32_t)((mags2 >> ((code & 7u) * 8u)) & 0xffu);
+    return (code & 8u) ? -m : m;
+}
+
+// RN-even onto {0, .5, 1, 1.5, 2, 3, 4, 6}; ties go to the even mantissa.
+__device__ __forceinline__ uint32_t e2m1_rn(float v) {
+    const uint32_t s = v < 0.0f ? 8u : 0u;
+    const float a = fabsf(v);
+    uint32_t m;
+    if (a <= 0.25f) m = 0u;
+    else if (a < 0.75f) m = 1u;
+    else if (a <= 1.25f) m = 2u;
+    else if (a < 1.75f) m = 3u;
+    else if (a <= 2.5f) m = 4u;
+    else if (a < 3.5f) m = 5u;
+    else if (a <= 5.0f) m = 6u;
+    else m = 7u;
+    return s | m;
+}
+
+// One thread per 8 elements (half a block); the lane pair closes the 16-element
+// amax.  scale byte = RN_e4m3(amax / 6), floored at the smallest subnormal when
+// amax > 0; elements = e2m1_rn(v / scale).
+__global__ void quantize_nvf4_kernel(const float* __restrict__ x, uint8_t* __restrict__ q,
+                                     uint8_t* __restrict__ scale, uint32_t n) {
+    const uint32_t i = (blockIdx.x * 256u + threadIdx.x) * 8u;
+    if (i >= n) return;  // n % 32 == 0: lane pairs leave together
+    const float4 a = *reinterpret_cast<const float4*>(x + i);
+    const float4 b = *reinterpret_cast<const float4*>(x + i + 4u);
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+    const uint32_t lane = threadIdx.x & 31u;
+    amax = fmaxf(amax, __shfl_xor_sync(0x3u << (lane & 30u), amax, 1));
+    uint32_t sb = 0u;
+    float inv = 0.0f;
+    if (amax > 0.0f) {
+        sb = (uint32_t)__nv_cvt_float_to_fp8(amax * (1.0f / 6.0f), __NV_SATFINITE, __NV_E4M3);
+        if (sb == 0u) sb = 1u;
+        inv = 1.0f / e4m3_to_f32((uint8_t)sb);
+    }
+    uint32_t p = 0u;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) p |= e2m1_rn(v[k] * inv) << (4 * k);
+    *reinterpret_cast<uint32_t*>(q + (i >> 1)) = p;
+    if ((lane & 1u) == 0u) scale[i >> 4] = (uint8_t)sb;
+}
+
+// One CTA per output row; (e2m1 * e4m3) * scale2 with two separate roundings.
+__global__ void nvf4_dequant_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ scale, float scale2,
+                                    float* __restrict__ y, uint32_t in_dim) {
+    const uint32_t o = blockIdx.x, kh = in_dim >> 1;
+    const uint8_t* row = data + (size_t)o * kh;
+    const uint8_t* srow = scale + (size_t)o * (in_dim >> 4);
+    float* yrow = y + (size_t)o * in_dim;
+    for (uint32_t j = threadIdx.x; j < kh; j += blockDim.x) {
+        const uint32_t b = row[j];
+        const float s = e4m3_to_f32(srow[j >> 3]);
+        float2 out;
+        out.x = __fmul_rn(__fmul_rn(e2m1_to_f32(b & 15u), s), scale2);
+        out.y = __fmul_rn(__fmul_rn(e2m1_to_f32(b >> 4), s), scale2);
+        *reinterpret_cast<float2*>(yrow + 2u * j) = out;
+    }
+}
+
+// Weight scales [out][in/16] -> the tensor core's scale-cell order.  For row
+// tile rt (128 rows) and K slab kb (256 elements) a 2048-byte record of four
+// 512-byte cells, one per 64-element MMA step j:
+//   byte l*16 + c*4 + b  of cell j  =  scale[rt*128 + c*32 + l][kb*16 + j*4 + b]
+// (rows past out_dim read as 0).  One thread per 4-byte word of the output.
+__global__ void nvf4_tile_scales_kernel(const uint8_t* __restrict__ scale, uint32_t* __restrict__ tiled,
+                                        uint32_t in_dim, uint32_t out_dim, uint64_t n_words) {
+    const uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= n_words) return;
+    const uint32_t n_slab = in_dim >> 8, kb16 = in_dim >> 4;
+    const uint32_t c = (uint32_t)(w & 3u), l = (uint32_t)((w >> 2) & 31u), j = (uint32_t)((w >> 7) & 3u);
+    const uint64_t rec = w >> 9;
+    const uint32_t kb = (uint32_t)(rec % n_slab), rt = (uint32_t)(rec / n_slab);
+    const uint32_t row = rt * 128u + c * 32u + l;
+    uint32_t v = 0u;
+    if (row < out_dim) v = *reinterpret_cast<const uint32_t*>(scale + (size_t)row * kb16 + kb * 16u + j * 4u);
+    tiled[w] = v;
+}
+
+// W4A16 decode GEMV, f32 activations: a warp per output row, 8 rows per CTA.
+// Lane l owns elements 32l'.. in steps of 1024: 16 packed bytes (32 elements,
+// two scale blocks) per step.
+__global__ void __launch_bounds__(256)
+nvf4_gemv_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ scale, const float* __restrict__ bias,
+                 const float* __restrict__ x, float* __restrict__ y, float scale2, uint32_t in_dim, uint32_t out_dim) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t row = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (row >= out_dim) return;
+    const uint8_t* drow = data + (size_t)row * (in_dim >> 1);
+    const uint8_t* srow = scale + (size_t)row * (in_dim >> 4);
+    float acc = 0.0f;
+    for (uint32_t e = lane * 32u; e < in_dim; e += 1024u) {
+        const uint4 q = pdk_ldg_stream16(drow + (e >> 1));
+        const uint32_t ss = *reinterpret_cast<const uint16_t*>(srow + (e >> 4));
+        const float s0 = e4m3_to_f32((uint8_t)(ss & 0xffu)), s1 = e4m3_to_f32((uint8_t)(ss >> 8));
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        float part[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 xa = *reinterpret_cast<const float4*>(x + e + 8 * i);
+            const float4 xb = *reinterpret_cast<const float4*>(x + e + 8 * i + 4);
+            float t = e2m1_to_f32(w[i] & 15u) * xa.x;
+            t = fmaf(e2m1_to_f32((w[i] >> 4) & 15u), xa.y, t);
+            t = fmaf(e2m1_to_f32((w[i] >> 8) & 15u), xa.z, t);
+            t = fmaf(e2m1_to_f32((w[i] >> 12) & 15u), xa.w, t);
+            t = fmaf(e2m1_to_f32((w[i] >> 16) & 15u), xb.x, t);
+            t = fmaf(e2m1_to_f32((w[i] >> 20) & 15u), xb.y, t);
+            t = fmaf(e2m1_to_f32((w[i] >> 24) & 15u), xb.z, t);
+            t = fmaf(e2m1_to_f32(w[i] >> 28), xb.w, t);
+            part[i >> 1] += t;
+        }
+        acc = fmaf(s0, part[0], acc);
+        acc = fmaf(s1, part[1], acc);
+    }
+    acc = pdk_warp_sum(acc);
+    if (lane == 0) y[row] = fmaf(acc, scale2, bias ? bias[row] : 0.0f);
+}
+
+}  // namespace
+
+// slot 119, packs/cuda/src/quant/nvf4.cuh:405-421
+PDK_EXPORT int pd_quantize_nvf4(const void* x, void* q, void* scale, uint32_t n, void* stream) {
+    if (n == 0) return 0;
+    if ((n & 31u) != 0u || !pdk_aligned(x, 16) || !pdk_aligned(q, 4)) return cudaErrorInvalidValue;
+    quantize_nvf4_kernel<<<(n / 8u + 255u) / 256u, 256, 0, (cudaStream_t)stream>>>((const float*)x, (uint8_t*)q,
+                                                                                    (uint8_t*)scale, n);
+    return pdk_launch_status();
+}
+
+// slot 393, packs/cuda/src/quant/nvf4.cuh:4365-4403
+PDK_EXPORT int pd_nvf4_dequant(const void* data, const void* scale, float scale2, void* y, uint32_t in_dim,
+                               uint32_t out_dim, void* stream) {
+    if (out_dim == 0) return 0;
+    if ((in_dim & 31u) != 0u || !pdk_aligned(y, 8)) return cudaErrorInvalidValue;
+    nvf4_dequant_kernel<<<out_dim, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)data, (const uint8_t*)scale, scale2,
+                                                                   (float*)y, in_dim);
+    return pdk_launch_status();
+}
+
+// slot 853, packs/cuda/src/gemm/dense_nvf4_tc5.cuh:845-861,981-994
+PDK_EXPORT int pd_nvf4_tc5_tile_scales(const void* scale, void* tiled, uint32_t in_dim, uint32_t out_dim,
+                                       void* stream) {
+    if (out_dim == 0 || in_dim == 0) return 0;
+    if ((in_dim & 255u) != 0u || !pdk_aligned(scale, 4) || !pdk_aligned(tiled, 16)) return cudaErrorInvalidValue;
+    const uint64_t n_words = (uint64_t)((out_dim + 127u) / 128u) * (in_dim >> 8) * 512u;
+    const uint64_t blocks = (n_words + 255u) / 256u;
+    if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
+    nvf4_tile_scales_kernel<<<(uint32_t)blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)scale,
+                                                                                (uint32_t*)tiled, in_dim, out_dim,
+                                                                                n_words);
+    return pdk_launch_status();
+}
+
+// slot 394, packs/cuda/src/quant/nvf4.cuh:4436-4779
+PDK_EXPORT int pd_nvf4_gemv(const void* data, const void* scale, const void* bias, const void* x, void* y,
+                            float scale2, uint32_t in_dim, uint32_t out_dim, void* stream) {
+    if (out_dim == 0) return 0;
+    if ((in_dim & 31u) != 0u || in_dim == 0u) return cudaErrorInvalidValue;
+    if (!pdk_aligned(data, 16) || !pdk_aligned(scale, 2) || !pdk_aligned(x, 16)) return cudaErrorInvalidValue;
+    nvf4_gemv_kernel<<<(out_dim + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>(
+        (const uint8_t*)data, (const uint8_t*)scale, (const float*)bias, (const float*)x, (float*)y, scale2, in_dim,
+        out_dim);
+    return pdk_launch_status();
+}

@@ -1,0 +1,279 @@
+// nvf4_gemm.cu - NVFP4 x NVFP4 GEMM on tcgen05 with hardware block scaling.
+//
+//   y[t][n] = scale2 * sum over 16-element blocks b of
+//             e4m3(ws[n][b]) * e4m3(xs[t][b]) * sum_{k in b} e2m1(W[n][k]) * e2m1(X[t][k])   (+ bias[n])
+//
+// tcgen05.mma kind::mxf4nvf4 reads packed e2m1 operands straight from shared
+// memory (K = 64 per instruction) and applies both operands' per-16 UE4M3
+// scales from tensor memory, so no weight ever passes through a register: at
+// decode widths the kernel is a pure HBM stream (4.5 bits per weight), at
+// prefill widths it is tensor-bound.
+//
+// Tile: 128 weight rows (the MMA's M, one TMEM lane each) x 128 tokens (N) x
+// 256 K per pipeline stage.  Weights are the A operand so that a decode batch
+// is a single token tile and the epilogue writes, per token, 128 consecutive
+// channels.  One persistent CTA per SM:
+//   warp 0      producer: TMA boxes of W and X (128 rows x 128 bytes, 128-byte
+//               swizzle), one 2 KB bulk copy of the pre-tiled weight scale cells,
+//               and a 32-lane gather of the activation scale cells into the same
+//               cell order
+//   warp 1      MMA issuer: per stage 8 tcgen05.cp (scale cells -> TMEM) + 4 MMAs
+//   warps 2..5  epilogue: TMEM -> registers -> y (f32 or bf16), * scale2 + bias
+// Accumulators are double buffered (2 x 128 TMEM columns); scale cells take
+// 32 columns per stage.
+#include "tc5.cuh"
+
+namespace {
+
+constexpr uint32_t BM = 128;            // weight rows per tile
+constexpr uint32_t BN = 128;            // tokens per tile
+constexpr uint32_t BKB = 128;           // bytes of K per stage = 256 e2m1
+constexpr uint32_t kStages = 5;
+constexpr uint32_t kABytes = BM * BKB, kBBytes = BN * BKB, kSfBytes = 2048;
+constexpr uint32_t kStageBytes = kABytes + kBBytes + 2u * kSfBytes;  // 36 KB
+constexpr uint32_t kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSfCol0 = 2u * BN;   // scale cells start after the two accumulators
+
+struct Shared {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     tc5::smem_u32(smem_dst)),
+                 "l"(gmem), "r"(bytes), "r"(tc5::smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// 512-byte scale cell (32 rows x 16 bytes, no swizzle) -> 4 TMEM columns, broadcast to the 4 lane quarters
+__device__ __forceinline__ void sf_copy(uint32_t taddr, uint32_t saddr) {
+    const uint64_t desc = (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)1u << 16) | ((uint64_t)8u << 32);
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+// e2m1 x e2m1 (format code 1 in the mxf4 encoding), UE4M3 scales, scale ids 0
+constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+
+template <typename TO>
+__device__ __forceinline__ void store_one(TO* p, float v);
+template <>
+__device__ __forceinline__ void store_one<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <typename TO>
+__global__ void __launch_bounds__(kThreads, 1)
+nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                 const uint8_t* __restrict__ w_sf_tiled, const uint8_t* __restrict__ x_sf,
+                 const float* __restrict__ bias, TO* __restrict__ y, float scale2, uint32_t in_dim, uint32_t out_dim,
+                 uint32_t batch, unsigned int* err_word) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * kStageBytes);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t tiles_w = (out_dim + BM - 1u) / BM, tiles_t = (batch + BN - 1u) / BN;
+    const uint32_t n_tiles = tiles_w * tiles_t;
+    const uint32_t num_kb = in_dim >> 8;       // 256-element slabs (in_dim % 256 == 0)
+    const uint32_t sf_row = in_dim >> 4;       // activation scale bytes per token
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            tc5::mbar_init(&sh->full[s], 33);  // producer lane 0 (expect_tx) + 32 gather lanes
+            tc5::mbar_init(&sh->empty[s], 1);
+        }
+        for (uint32_t b = 0; b < 2; ++b) {
+            tc5::mbar_init(&sh->tmem_full[b], 1);
+            tc5::mbar_init(&sh->tmem_empty[b], 4);
+        }
+        sh->abort_flag = 0;
+        tc5::mbar_fence_init();
+        tc5::tma_prefetch_desc(&tmap_w);
+        tc5::tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == 1) {
+        tc5::tmem_alloc(&sh->tmem_base, kTmemCols);
+        tc5::tmem_relinquish();
+    }
+    tc5::fence_before_sync();
+    __syncthreads();
+    tc5::fence_after_sync();
+    const uint32_t tmem_base = sh->tmem_base;
+    const tc5::WaitCtx ctx{&sh->abort_flag, err_word};
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (whole warp)
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        // tiles are walked weight-tile fastest: a wave of CTAs shares one token tile
+        for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const uint32_t w0 = (tile % tiles_w) * BM, t0 = (tile / tiles_w) * BN;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                uint8_t* a = tiles + stage * kStageBytes;
+                uint8_t* sfa = a + kABytes + kBBytes;
+                uint8_t* sfb = sfa + kSfBytes;
+                if (lane == 0) {
+                    tc5::mbar_arrive_expect_tx(&sh->full[stage], kABytes + kBBytes + kSfBytes);
+                    tc5::tma_load_2d(a, &tmap_w, &sh->full[stage], (int32_t)(kb * BKB), (int32_t)w0);
+                    tc5::tma_load_2d(a + kABytes, &tmap_x, &sh->full[stage], (int32_t)(kb * BKB), (int32_t)t0);
+                    bulk_copy_g2s(sfa, w_sf_tiled + ((size_t)(tile % tiles_w) * num_kb + kb) * kSfBytes, kSfBytes,
+                                  &sh->full[stage]);
+                }
+                // activation scale cells: word (j, l, c) = xs[t0 + c*32 + l][kb*16 + 4j .. 4j+3]
+#pragma unroll
+                for (uint32_t i = 0; i < 16u; ++i) {
+                    const uint32_t w = i * 32u + lane;  // word index inside the 2 KB record
+                    const uint32_t c = w & 3u, l = (w >> 2) & 31u, j = w >> 7;
+                    const uint32_t t = t0 + c * 32u + l;
+                    uint32_t v = 0u;
+                    if (t < batch) v = __ldg(reinterpret_cast<const uint32_t*>(x_sf + (size_t)t * sf_row + kb * 16u + j * 4u));
+                    reinterpret_cast<uint32_t*>(sfb)[w] = v;
+                }
+                fence_proxy_async_smem();
+                tc5::mbar_arrive(&sh->full[stage]);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok && lane == 0) {
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
+                const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
+                ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
+                if (!ok) break;
+                tc5::fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    ok = tc5::mbar_wait(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
+                    if (!ok) break;
+                    tc5::fence_after_sync();
+                    const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
+                    const uint32_t sfa_addr = a_addr + kABytes + kBBytes, sfb_addr = sfa_addr + kSfBytes;
+                    const uint32_t sfa_t = tmem_base + kSfCol0 + stage * 32u, sfb_t = sfa_t + 16u;
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j) {
+                        sf_copy(sfa_t + j * 4u, sfa_addr + j * 512u);
+                        sf_copy(sfb_t + j * 4u, sfb_addr + j * 512u);
+                    }
+                    const uint64_t a_desc = tc5::smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j)  // 64 e2m1 = 32 bytes of K per instruction
+                        mma_nvf4(d_tmem, a_desc + 2u * j, b_desc + 2u * j, kIdesc, sfa_t + j * 4u, sfb_t + j * 4u,
+                                 (kb | j) != 0u);
+                    tc5::mma_commit(&sh->empty[stage]);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc5::mma_commit(&sh->tmem_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t quarter = warp & 3u;
+        uint32_t iter = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
+            const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
+            const uint32_t w0 = (tile % tiles_w) * BM, t0 = (tile / tiles_w) * BN;
+            ok = tc5::mbar_wait(&sh->tmem_full[buf], aphase, ctx, tc5::kErrTmemFullWait, buf);
+            if (!ok) break;
+            tc5::fence_after_sync();
+            const uint32_t n = w0 + quarter * 32u + lane;
+            const float b = (bias != nullptr && n < out_dim) ? bias[n] : 0.0f;
+            const uint32_t n_tok = min(BN, batch - t0);
+#pragma unroll 1
+            for (uint32_t c = 0; c * 32u < n_tok; ++c) {
+                uint32_t r[32];
+                tc5::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + buf * BN + c * 32u, r);
+                tc5::tmem_ld_wait();
+                if (n < out_dim) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 32u; ++i) {
+                        const uint32_t t = c * 32u + i;
+                        if (t < n_tok) store_one<TO>(y + (size_t)(t0 + t) * out_dim + n, fmaf(__uint_as_float(r[i]), scale2, b));
+                    }
+                }
+            }
+            tc5::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive(&sh->tmem_empty[buf]);
+        }
+    }
+
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc5::fence_after_sync();
+        tc5::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <typename TO>
+int launch(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs, void* y,
+           float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
+    if (out_dim == 0 || batch == 0) return 0;
+    if (in_dim == 0 || (in_dim & 255u) != 0u) return cudaErrorInvalidValue;
+    if (!pdk_aligned(data, 16) || !pdk_aligned(xq, 16) || !pdk_aligned(scale_tiled, 16) || !pdk_aligned(xs, 4) ||
+        !pdk_aligned(y, sizeof(TO)))
+        return cudaErrorInvalidValue;
+    CUtensorMap tw, tx;
+    const uint32_t kbytes = in_dim >> 1;
+    if (int rc = pdk_make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, data, kbytes, out_dim, kbytes, BKB, BM))
+        return rc;
+    if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, kbytes, batch, kbytes, BKB, BN)) return rc;
+    const size_t smem = (size_t)kStages * kStageBytes + sizeof(Shared) + 1024u;
+    auto kern = nvf4_gemm_kernel<TO>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const uint32_t n_tiles = ((out_dim + BM - 1u) / BM) * ((batch + BN - 1u) / BN);
+    uint32_t grid = (uint32_t)pdk_sm_count();
+    if (grid > n_tiles) grid = n_tiles;
+    kern<<<grid, kThreads, smem, st>>>(tw, tx, (const uint8_t*)scale_tiled, (const uint8_t*)xs, (const float*)bias,
+                                       (TO*)y, scale2, in_dim, out_dim, batch, pdk_error_word());
+    return pdk_launch_status();
+}
+
+}  // namespace
+
+// slot 852, packs/cuda/src/gemm/dense_nvf4_tc5.cuh:1216-1263.  `part` / `part_floats`
+// (the reference's K-split partial planes) are accepted and unused: this kernel
+// never splits K.
+PDK_EXPORT int pd_nvf4_gemm_tc5w(const void* data, const void* scale_tiled, const void* bias, const void* xq,
+                                 const void* xs, void* y, float scale2, uint32_t in_dim, uint32_t out_dim,
+                                 uint32_t batch, void* part, uint64_t part_floats, void* stream) {
+    (void)part;
+    (void)part_floats;
+    return launch<float>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, (cudaStream_t)stream);
+}
+
+// No slot: slot 852 with bf16 output.
+PDK_EXPORT int pdk_nvf4_gemm_bf16(const void* data, const void* scale_tiled, const void* bias, const void* xq,
+                                  const void* xs, void* y, float scale2, uint32_t in_dim, uint32_t out_dim,
+                                  uint32_t batch, void* stream) {
+    return launch<__nv_bfloat16>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch,
+                                 (cudaStream_t)stream);
+}

@@ -1,0 +1,115 @@
+"""Per-kernel micro-benchmarks for the pack's launchers (the counterpart of the
+reference's examples/*_kbench.rs): CUDA-event timing after warm-up, cold L2 for
+the memory-bound operators (operand clones rotated so consecutive launches
+never touch the same bytes), one JSON line per case.
+
+    python -m paddock_b200.kbench --op f8row_gemm --m 4096 --n 17408 --k 5120
+    python -m paddock_b200.kbench --op q4k_gemv --m 1
+    python -m paddock_b200.kbench --op q8_gemv
+"""
+import argparse
+import json
+import os
+
+import torch
+
+from . import synth
+from .planes import GpuExecutor
+
+L2_BYTES = 126 << 20
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def time_launches(fn, iters, warmup=5):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+def clones_for(nbytes):
+    return max(2, -(-2 * L2_BYTES // max(nbytes, 1)) + 1)
+
+
+def bench_q4k(ex, a):
+    k, n, m = a.k, a.n, a.m
+    raw = synth.quantize_q4_k(synth.normal(n * k, 1, 0.02, "cuda"))
+    planes = [ex.repack_kquant_raw(raw, k, n) for _ in range(clones_for(n * k // 256 * 152))]
+    x = synth.bf16_round(synth.normal(m * k, 2, 1.0, "cuda"))
+    y = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+    if m == 1:
+        sec = time_launches(lambda i: ex.kquant_gemv(planes[i % len(planes)], x, y), a.iters)
+    else:
+        sec = time_launches(lambda i: ex.kquant_gemm_f32(planes[i % len(planes)], x, y, m), a.iters)
+    nbytes = n * k // 256 * 144 + m * k * 2 + m * n * 4
+    return sec, {"bound": "hbm", "bytes": nbytes}
+
+
+def bench_q8(ex, a):
+    k, n = a.k, a.n
+    raw = synth.quantize_q8_0(synth.normal(n * k, 3, 0.02, "cuda"))
+    planes = [ex.repack_q8_blocks(raw, k, n) for _ in range(clones_for(n * k // 32 * 34))]
+    x = synth.bf16_round(synth.normal(k, 4, 1.0, "cuda"))
+    y = torch.zeros(n, dtype=torch.float32, device="cuda")
+    sec = time_launches(lambda i: ex.q8_0_gemv_repacked(planes[i % len(planes)], None, x, y), a.iters)
+    return sec, {"bound": "hbm", "bytes": n * k // 32 * 34 + k * 2 + n * 4}
+
+
+def bench_f8(ex, a):
+    m, n, k = a.m, a.n, a.k
+    w = torch.randint(0, 0x7E, (n * k,), dtype=torch.uint8, device="cuda")
+    xq = torch.randint(0, 0x7E, (m * k,), dtype=torch.uint8, device="cuda")
+    ws = torch.rand(n, device="cuda") + 0.5
+    xs = torch.rand(m, device="cuda") + 0.5
+    y = torch.zeros(m * n, dtype=torch.bfloat16 if a.out == "bf16" else torch.float32, device="cuda")
+    name = "pdk_f8row_gemm_bf16" if a.out == "bf16" else "f8row_gemm"
+    st = torch.cuda.current_stream().cuda_stream
+    sec = time_launches(lambda i: ex.pack.call(name, w, ws, xq, xs, y, k, n, m, stream=st), a.iters)
+    return sec, {"bound": "tensor", "flops": 2.0 * m * n * k}
+
+
+OPS = {"q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True, choices=sorted(OPS))
+    ap.add_argument("--m", type=int)
+    ap.add_argument("--n", type=int)
+    ap.add_argument("--k", type=int)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--out", default="bf16", choices=["bf16", "f32"])
+    a = ap.parse_args()
+    dm, dn, dk = DEFAULTS[a.op]
+    a.m, a.n, a.k = a.m or dm, a.n or dn, a.k or dk
+    ex = GpuExecutor()
+    sec, info = OPS[a.op](ex, a)
+    err = ex.pack.device_error()
+    hbm, bf16, kind = peaks()
+    line = {"op": a.op, "m": a.m, "n": a.n, "k": a.k, "us": sec * 1e6, "device_error": err, "peak_kind": kind}
+    if info["bound"] == "hbm":
+        line.update(gbs=info["bytes"] / sec / 1e9, frac_of_hbm=info["bytes"] / sec / 1e9 / hbm)
+    else:
+        tf = info["flops"] / sec / 1e12
+        line.update(tflops=tf, frac_of_2x_bf16=tf / (2 * bf16), frac_of_4x_bf16=tf / (4 * bf16))
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -99,11 +99,14 @@ _SIGS = {
     "q8_0_gemv_repacked": "pppppuu", "q8_0_gemm_repacked": "pppppuuu",
     "quantize_e4m3_row": "pppuu", "bf16_to_f8row": "pppuu",
     "f8row_gemm": "pppppuuu", "f8row_gemm_tc5x": "pppppuuu",
+    "quantize_nvf4": "pppu", "nvf4_dequant": "ppfpuu", "nvf4_gemv": "pppppfuu",
+    "nvf4_tc5_tile_scales": "ppuu", "nvf4_gemm_tc5w": "ppppppfuuupU",
     "kquant_dequant": "ppUu", "kquant_repack": "pppUu", "kquant_gemv": "ppppuuu",
 }
 _EXTRA_SIGS = {
     "pdk_kquant_gemm_f32": "ppppuuuu",
     "pdk_f8row_gemm_bf16": "pppppuuu",
+    "pdk_nvf4_gemm_bf16": "ppppppfuuu",
 }
 _KIND = {"p": C.c_void_p, "u": C.c_uint32, "U": C.c_uint64, "f": C.c_float}
 
