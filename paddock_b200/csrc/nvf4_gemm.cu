@@ -26,18 +26,27 @@
 namespace {
 
 constexpr uint32_t BM = 128;            // weight rows per tile
-constexpr uint32_t BN = 128;            // tokens per tile
 constexpr uint32_t BKB = 128;           // bytes of K per stage = 256 e2m1
-constexpr uint32_t kStages = 5;
-constexpr uint32_t kABytes = BM * BKB, kBBytes = BN * BKB, kSfBytes = 2048;
-constexpr uint32_t kStageBytes = kABytes + kBBytes + 2u * kSfBytes;  // 36 KB
+constexpr uint32_t kABytes = BM * BKB, kSfBytes = 2048;
 constexpr uint32_t kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSfCol0 = 2u * BN;   // scale cells start after the two accumulators
+constexpr uint32_t kMaxStages = 9;
+
+// Token tile BN: 128 for prefill widths; 32 for decode widths, where the smaller
+// activation box leaves room for 9 stages (162 KB of weights in flight per SM).
+template <uint32_t BN>
+struct Cfg {
+    static constexpr uint32_t kStages = BN == 32u ? 9u : 5u;
+    static constexpr uint32_t kBBytes = BN * BKB;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes + 2u * kSfBytes;
+    static constexpr uint32_t kSfCol0 = 2u * BN;  // scale cells start after the two accumulators
+    // e2m1 x e2m1 (format code 1 in the mxf4 encoding), UE4M3 scales, scale ids 0
+    static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+};
 
 struct Shared {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
@@ -67,9 +76,6 @@ __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint6
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
         : "memory");
 }
-// e2m1 x e2m1 (format code 1 in the mxf4 encoding), UE4M3 scales, scale ids 0
-constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
-
 template <typename TO>
 __device__ __forceinline__ void store_one(TO* p, float v);
 template <>
@@ -77,12 +83,14 @@ __device__ __forceinline__ void store_one<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-template <typename TO>
+template <uint32_t BN, typename TO>
 __global__ void __launch_bounds__(kThreads, 1)
 nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  const uint8_t* __restrict__ w_sf_tiled, const uint8_t* __restrict__ x_sf,
                  const float* __restrict__ bias, TO* __restrict__ y, float scale2, uint32_t in_dim, uint32_t out_dim,
                  uint32_t batch, unsigned int* err_word) {
+    constexpr uint32_t kStages = Cfg<BN>::kStages, kBBytes = Cfg<BN>::kBBytes, kStageBytes = Cfg<BN>::kStageBytes;
+    constexpr uint32_t kSfCol0 = Cfg<BN>::kSfCol0, kIdesc = Cfg<BN>::kIdesc;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * kStageBytes);
@@ -121,6 +129,21 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // ------------------------------------------------------------ producer (whole warp)
         uint32_t stage = 0, phase = 0;
         bool ok = true;
+        // Activation scale cells of one stage, 16 words per lane:
+        // word (j, l, c) = xs[t0 + c*32 + l][kb*16 + 4j .. 4j+3].  They are fetched one
+        // stage ahead so their latency hides behind the wait for a free stage.
+        uint32_t sfw[16];
+        auto fetch_sf = [&](uint32_t t0, uint32_t kb) {
+#pragma unroll
+            for (uint32_t i = 0; i < 16u; ++i) {
+                const uint32_t w = i * 32u + lane;  // word index inside the 2 KB record
+                const uint32_t c = w & 3u, l = (w >> 2) & 31u, j = w >> 7;
+                const uint32_t t = t0 + c * 32u + l;
+                sfw[i] = t < batch ? __ldg(reinterpret_cast<const uint32_t*>(x_sf + (size_t)t * sf_row + kb * 16u + j * 4u))
+                                   : 0u;
+            }
+        };
+        if (blockIdx.x < n_tiles && num_kb > 0u) fetch_sf((blockIdx.x / tiles_w) * BN, 0u);
         // tiles are walked weight-tile fastest: a wave of CTAs shares one token tile
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const uint32_t w0 = (tile % tiles_w) * BM, t0 = (tile / tiles_w) * BN;
@@ -138,18 +161,13 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     bulk_copy_g2s(sfa, w_sf_tiled + ((size_t)(tile % tiles_w) * num_kb + kb) * kSfBytes, kSfBytes,
                                   &sh->full[stage]);
                 }
-                // activation scale cells: word (j, l, c) = xs[t0 + c*32 + l][kb*16 + 4j .. 4j+3]
 #pragma unroll
-                for (uint32_t i = 0; i < 16u; ++i) {
-                    const uint32_t w = i * 32u + lane;  // word index inside the 2 KB record
-                    const uint32_t c = w & 3u, l = (w >> 2) & 31u, j = w >> 7;
-                    const uint32_t t = t0 + c * 32u + l;
-                    uint32_t v = 0u;
-                    if (t < batch) v = __ldg(reinterpret_cast<const uint32_t*>(x_sf + (size_t)t * sf_row + kb * 16u + j * 4u));
-                    reinterpret_cast<uint32_t*>(sfb)[w] = v;
-                }
+                for (uint32_t i = 0; i < 16u; ++i) reinterpret_cast<uint32_t*>(sfb)[i * 32u + lane] = sfw[i];
                 fence_proxy_async_smem();
                 tc5::mbar_arrive(&sh->full[stage]);
+                // next stage's cells
+                if (kb + 1u < num_kb) fetch_sf(t0, kb + 1u);
+                else if (tile + gridDim.x < n_tiles) fetch_sf(((tile + gridDim.x) / tiles_w) * BN, 0u);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -232,21 +250,16 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     }
 }
 
-template <typename TO>
-int launch(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs, void* y,
-           float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
-    if (out_dim == 0 || batch == 0) return 0;
-    if (in_dim == 0 || (in_dim & 255u) != 0u) return cudaErrorInvalidValue;
-    if (!pdk_aligned(data, 16) || !pdk_aligned(xq, 16) || !pdk_aligned(scale_tiled, 16) || !pdk_aligned(xs, 4) ||
-        !pdk_aligned(y, sizeof(TO)))
-        return cudaErrorInvalidValue;
+template <uint32_t BN, typename TO>
+int launch_bn(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs, void* y,
+              float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
     CUtensorMap tw, tx;
     const uint32_t kbytes = in_dim >> 1;
     if (int rc = pdk_make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, data, kbytes, out_dim, kbytes, BKB, BM))
         return rc;
     if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, kbytes, batch, kbytes, BKB, BN)) return rc;
-    const size_t smem = (size_t)kStages * kStageBytes + sizeof(Shared) + 1024u;
-    auto kern = nvf4_gemm_kernel<TO>;
+    const size_t smem = (size_t)Cfg<BN>::kStages * Cfg<BN>::kStageBytes + sizeof(Shared) + 1024u;
+    auto kern = nvf4_gemm_kernel<BN, TO>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const uint32_t n_tiles = ((out_dim + BM - 1u) / BM) * ((batch + BN - 1u) / BN);
@@ -255,6 +268,18 @@ int launch(const void* data, const void* scale_tiled, const void* bias, const vo
     kern<<<grid, kThreads, smem, st>>>(tw, tx, (const uint8_t*)scale_tiled, (const uint8_t*)xs, (const float*)bias,
                                        (TO*)y, scale2, in_dim, out_dim, batch, pdk_error_word());
     return pdk_launch_status();
+}
+
+template <typename TO>
+int launch(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs, void* y,
+           float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
+    if (out_dim == 0 || batch == 0) return 0;
+    if (in_dim == 0 || (in_dim & 255u) != 0u) return cudaErrorInvalidValue;
+    if (!pdk_aligned(data, 16) || !pdk_aligned(xq, 16) || !pdk_aligned(scale_tiled, 16) || !pdk_aligned(xs, 4) ||
+        !pdk_aligned(y, sizeof(TO)))
+        return cudaErrorInvalidValue;
+    if (batch <= 32u) return launch_bn<32, TO>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
+    return launch_bn<128, TO>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
 }
 
 }  // namespace

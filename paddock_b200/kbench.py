@@ -83,8 +83,26 @@ def bench_f8(ex, a):
     return sec, {"bound": "tensor", "flops": 2.0 * m * n * k}
 
 
-OPS = {"q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
-DEFAULTS = {"q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+def bench_nvf4(ex, a):
+    m, n, k = a.m, a.n, a.k
+    st = torch.cuda.current_stream().cuda_stream
+    nbytes_w = n * k // 2 + n * k // 16
+    nc = clones_for(nbytes_w) if m <= 512 else 1
+    ws = [(torch.randint(0, 256, (n * k // 2,), dtype=torch.uint8, device="cuda"),
+           torch.randint(0x20, 0x48, (((n + 127) // 128) * (k // 256) * 2048,), dtype=torch.uint8, device="cuda"))
+          for _ in range(nc)]
+    x = synth.bf16_round(synth.normal(m * k, 5, 1.0, "cuda"))
+    xq = torch.zeros(m * k // 2, dtype=torch.uint8, device="cuda")
+    xs = torch.zeros(m * k // 16, dtype=torch.uint8, device="cuda")
+    ex.pack.call("quantize_nvf4", x, xq, xs, m * k, stream=st)
+    y = torch.zeros(m * n, dtype=torch.bfloat16, device="cuda")
+    sec = time_launches(lambda i: ex.pack.call("pdk_nvf4_gemm_bf16", ws[i % nc][0], ws[i % nc][1], None, xq, xs, y,
+                                               1.0, k, n, m, stream=st), a.iters)
+    return sec, {"bound": "both", "flops": 2.0 * m * n * k, "bytes": nbytes_w + 4 + m * (k // 2 + k // 16) + m * n * 2}
+
+
+OPS = {"nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
 def main():
@@ -103,9 +121,9 @@ def main():
     err = ex.pack.device_error()
     hbm, bf16, kind = peaks()
     line = {"op": a.op, "m": a.m, "n": a.n, "k": a.k, "us": sec * 1e6, "device_error": err, "peak_kind": kind}
-    if info["bound"] == "hbm":
+    if info["bound"] in ("hbm", "both"):
         line.update(gbs=info["bytes"] / sec / 1e9, frac_of_hbm=info["bytes"] / sec / 1e9 / hbm)
-    else:
+    if info["bound"] in ("tensor", "both"):
         tf = info["flops"] / sec / 1e12
         line.update(tflops=tf, frac_of_2x_bf16=tf / (2 * bf16), frac_of_4x_bf16=tf / (4 * bf16))
     print(json.dumps(line), flush=True)
