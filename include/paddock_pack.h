@@ -78,7 +78,11 @@ enum PdkSlot {
     PDK_SLOT_nvf4_dequant = 393,
     PDK_SLOT_nvf4_gemv = 394,
     PDK_SLOT_nvf4_gemm_tc5w = 852,
-    PDK_SLOT_nvf4_tc5_tile_scales = 853
+    PDK_SLOT_nvf4_tc5_tile_scales = 853,
+    PDK_SLOT_moe_topk_batch = 29,
+    PDK_SLOT_moe_align = 34,
+    PDK_SLOT_moe_slot_combine = 91,
+    PDK_SLOT_moe_align_bm = 146
 };
 
 /* ---- the drop-in boundary ------------------------------------------------ */
@@ -184,6 +188,47 @@ int pdk_nvf4_gemm_bf16(const void* data, const void* scale_tiled, const void* bi
 int pd_mxfp4_dequant_f32(const void* in, void* out, uint64_t n_blocks, void* stream);
 /* slot 37, packs/cuda/src/attn/decode.cuh:2294-2304 (launcher gemm/f32_qkv.cuh:1465). */
 int pd_mxfp4_repack(const void* src, void* dst_data, void* dst_scale, uint64_t n_blocks, void* stream);
+
+/* ---- MoE routing and MXFP4 expert GEMMs (caller: crates/paddock-engine/src/gpu_model/gpt_oss.rs:2279-2521) --- */
+
+/* slot 29, packs/cuda/src/attn/decode.cuh:1392-1500: per token, k rounds of argmax over
+ * logits + bias (ties to the lowest index); out_w = softmax over the k selected logits.
+ * logits f32[batch][n_expert], out_idx u32[batch][k], out_w f32[batch][k]; n_expert <= 512, k <= 16. */
+int pd_moe_topk_batch(const void* logits, const void* bias, uint32_t n_expert, uint32_t k, void* out_idx,
+                      void* out_w, uint32_t batch, void* stream);
+/* slot 34, packs/cuda/src/attn/decode.cuh:2316-2396: group the (token, slot) pairs by expert into
+ * blocks of 32, padding each expert's tail.  sorted_row / sorted_slot u32[max_blocks*32]
+ * (PDK_MOE_PAD = padding), block_expert u32[max_blocks] (PDK_MOE_PAD = unused block).
+ * Entries of an expert are in ascending pair order (the reference's order is unspecified). */
+int pd_moe_align(const void* idx, void* sorted_row, void* sorted_slot, void* block_expert, uint32_t rows,
+                 uint32_t n_active, uint32_t n_expert, uint32_t max_blocks, void* stream);
+/* slot 146, packs/cuda/src/gemm/f32_qkv.cuh:1269-1279: same with block size bm (a power of two). */
+int pd_moe_align_bm(const void* idx, void* sorted_row, void* sorted_slot, void* block_expert, uint32_t rows,
+                    uint32_t n_active, uint32_t n_expert, uint32_t bm, uint32_t max_blocks, void* stream);
+/* slot 91, packs/cuda/src/moe/mmq.cuh:447-483: residual[t] += sum over slots (ascending) of
+ * part[t*n_active + slot]; f32, embd % 4 == 0. */
+int pd_moe_slot_combine(const void* part, void* residual, uint32_t embd, uint32_t n_active, uint32_t rows,
+                        void* stream);
+/* No slot.  Activation step in front of the expert GEMMs; the reference quantizes to int8 at this
+ * point (pd_quantize_q8, packs/cuda/src/attn/decode.cuh:2981-3004).  x f32[rows][dim] ->
+ * xq u8[rows][2*dim] (exact e4m3 hi + lo pairs in mma fragment order) + xscale f32[rows]
+ * (power-of-two step per row).  dim % 32 == 0. */
+int pdk_moe_prep_act(const void* x, void* xq, void* xscale, uint32_t dim, uint32_t rows, void* stream);
+/* No slot; counterpart of slot 88 (pd_mxfp4_moe_gate_up_mmq, packs/cuda/src/moe/mmq.cuh:550-590)
+ * with the activation operands of pdk_moe_prep_act.  gate/up planes as pd_mxfp4_repack writes
+ * them: data [expert][ff][in/32*16], scale [expert][ff][in/32]; bias f32[expert][ff] or NULL.
+ * h f32[max_blocks*bm][ff] = swiglu_oai(gate, up) in block order; bm = 8 or 32 as given to
+ * pd_moe_align_bm. */
+int pdk_mxfp4_moe_gate_up(const void* gate_data, const void* gate_scale, const void* gate_bias, const void* up_data,
+                          const void* up_scale, const void* up_bias, const void* sorted_row, const void* block_expert,
+                          const void* xq, const void* xscale, void* h, uint32_t in_dim, uint32_t ff, uint32_t bm,
+                          uint32_t max_blocks, float alpha, float limit, void* stream);
+/* No slot; counterpart of slot 89 (pd_mxfp4_moe_down_mmq, packs/cuda/src/moe/mmq.cuh:592-626).
+ * hq / hscale = pdk_moe_prep_act of h.  part f32[rows*n_active][embd] = topk_w * (W_down h + bias). */
+int pdk_mxfp4_moe_down(const void* down_data, const void* down_scale, const void* down_bias, const void* sorted_row,
+                       const void* sorted_slot, const void* block_expert, const void* topk_w, const void* hq,
+                       const void* hscale, void* part, uint32_t ff, uint32_t embd, uint32_t n_active, uint32_t bm,
+                       uint32_t max_blocks, void* stream);
 
 /* ---- glue the engine's preflight needs ------------------------------------- */
 

@@ -45,6 +45,10 @@ static void fill_table() {
     PDK_SET(nvf4_gemv);
     PDK_SET(nvf4_gemm_tc5w);
     PDK_SET(nvf4_tc5_tile_scales);
+    PDK_SET(moe_topk_batch);
+    PDK_SET(moe_align);
+    PDK_SET(moe_align_bm);
+    PDK_SET(moe_slot_combine);
 #undef PDK_SET
 }
 

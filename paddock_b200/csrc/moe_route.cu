@@ -1,0 +1,241 @@
+// moe_route.cu - MoE routing around the grouped expert GEMMs: top-k router,
+// expert alignment (token permutation into expert-contiguous blocks),
+// activation preparation for the FP8 tensor-core path, and the fixed-order
+// slot combine.
+#include <cuda_fp8.h>
+
+#include "pdk_common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------- top-k router
+// One warp per token.  k rounds of argmax over logits + bias with strict ">",
+// ties to the lowest expert index; weights = softmax over the k selected
+// logits.  Up to 512 experts (16 register slots per lane), k <= 16.
+__global__ void moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, uint32_t n_expert,
+                                uint32_t k, uint32_t* __restrict__ out_idx, float* __restrict__ out_w,
+                                uint32_t batch) {
+    const uint32_t token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (token >= batch) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const float* row = logits + (size_t)token * n_expert;
+    float v[16];
+#pragma unroll
+    for (uint32_t j = 0; j < 16u; ++j) {
+        const uint32_t i = lane + 32u * j;
+        v[j] = i < n_expert ? row[i] + (bias ? bias[i] : 0.0f) : -1e30f;
+    }
+    float sel = 0.0f;  // lane s keeps the s-th selected logit
+    for (uint32_t s = 0; s < k; ++s) {
+        float best = -1e30f;
+        uint32_t bi = 0;
+#pragma unroll
+        for (uint32_t j = 0; j < 16u; ++j) {
+            const uint32_t i = lane + 32u * j;
+            if (v[j] > best) { best = v[j]; bi = i; }
+        }
+#pragma unroll
+        for (uint32_t off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == s) sel = best;
+        if (lane == 0) out_idx[(size_t)token * k + s] = bi;
+#pragma unroll
+        for (uint32_t j = 0; j < 16u; ++j)
+            if (lane + 32u * j == bi) v[j] = -1e30f;
+    }
+    float mm = lane < k ? sel : -1e30f;
+#pragma unroll
+    for (uint32_t off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+    // sum in ascending slot order, as a scalar walk would
+    const float e = lane < k ? __expf(sel - mm) : 0.0f;
+    float sum = 0.0f;
+    for (uint32_t s = 0; s < k; ++s) sum += __shfl_sync(0xffffffffu, e, s);
+    if (lane < k) out_w[(size_t)token * k + lane] = e / sum;
+}
+
+// ---------------------------------------------------------------- expert alignment
+// Groups the (token, slot) pairs by expert into blocks of `bm` entries, padding
+// each expert's last block.  One CTA; a warp owns experts warp, warp+nwarps, ...
+// and walks the pair list in order with ballots, so entries inside an expert
+// keep ascending pair order (the layout is a pure function of the routing).
+//   sorted_row[b*bm + i]  source token row, or PDK_MOE_PAD
+//   sorted_slot[b*bm + i] which of the token's k picks
+//   block_expert[b]       expert of block b, PDK_MOE_PAD past the used blocks
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const uint32_t* __restrict__ idx, uint32_t* __restrict__ sorted_row,
+                 uint32_t* __restrict__ sorted_slot, uint32_t* __restrict__ block_expert, uint32_t rows,
+                 uint32_t n_active, uint32_t n_expert, uint32_t bm, uint32_t max_blocks) {
+    extern __shared__ uint32_t ash[];
+    uint32_t* count = ash;               // [n_expert]
+    uint32_t* boff = ash + n_expert;     // [n_expert + 1] first block of each expert
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    const uint32_t npairs = rows * n_active;
+    for (uint32_t e = tid; e < n_expert; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (uint32_t p = tid; p < npairs; p += blockDim.x) {
+        const uint32_t e = idx[p];
+        if (e < n_expert) atomicAdd(&count[e], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t b = 0;
+        for (uint32_t e = 0; e < n_expert; ++e) {
+            boff[e] = b;
+            b += (count[e] + bm - 1u) / bm;
+        }
+        boff[n_expert] = b;
+    }
+    __syncthreads();
+    const uint32_t used = min(boff[n_expert], max_blocks);
+    for (uint32_t b = used + tid; b < max_blocks; b += blockDim.x) block_expert[b] = PDK_MOE_PAD;
+    for (uint32_t e = warp; e < n_expert; e += nwarp) {
+        const uint32_t b0 = boff[e], nb = boff[e + 1] - b0;
+        for (uint32_t b = lane; b < nb; b += 32u)
+            if (b0 + b < max_blocks) block_expert[b0 + b] = e;
+        uint32_t pos = b0 * bm;
+        for (uint32_t base = 0; base < npairs; base += 32u) {
+            const uint32_t p = base + lane;
+            const bool mine = p < npairs && idx[p] == e;
+            const uint32_t m = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const uint32_t at = pos + __popc(m & ((1u << lane) - 1u));
+                if (at < max_blocks * bm) {
+                    sorted_row[at] = p / n_active;
+                    sorted_slot[at] = p % n_active;
+                }
+            }
+            pos += __popc(m);
+        }
+        const uint32_t end = (b0 + nb) * bm;
+        for (uint32_t at = pos + lane; at < end; at += 32u)
+            if (at < max_blocks * bm) {
+                sorted_row[at] = PDK_MOE_PAD;
+                sorted_slot[at] = 0;
+            }
+    }
+}
+
+// ---------------------------------------------------------------- activation prep
+// f32 rows -> the B operand of the expert GEMMs.  Per row a power-of-two step
+// 2^e with amax / 2^e in [128, 256); x' = x / 2^e is split into hi = e4m3(x')
+// and lo = e4m3(x' - hi), both exact roundings on the e4m3 grid, so hi + lo
+// carries 8 significant bits of every element within 2^-10 of the row maximum
+// (bf16 activations are reproduced exactly there).
+// Layout per row and 32-element block, 64 bytes: for t = 0..3 the 16 bytes
+//   [hi k=4t..4t+3 | hi k=16+4t..16+4t+3 | lo k=4t.. | lo k=16+4t..]
+// which is one lane's two B registers for the hi mma followed by the lo mma.
+__global__ void __launch_bounds__(256)
+moe_prep_act_kernel(const float* __restrict__ x, uint8_t* __restrict__ xq, float* __restrict__ xscale, uint32_t dim) {
+    __shared__ float wmax[8];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const float* xr = x + (size_t)row * dim;
+    float a = 0.0f;
+    for (uint32_t i = tid; i < dim; i += 256u) a = fmaxf(a, fabsf(xr[i]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
+    if ((tid & 31u) == 0u) wmax[tid >> 5] = a;
+    __syncthreads();
+    float amax = 0.0f;
+    for (int w = 0; w < 8; ++w) amax = fmaxf(amax, wmax[w]);
+    int e = 0;
+    if (amax > 0.0f && amax < 3.0e38f) {
+        (void)frexpf(amax, &e);   // amax in [2^(e-1), 2^e)
+        e -= 8;                   // amax / 2^e in [128, 256)
+        e = max(e, -100);
+    }
+    const float inv = ldexpf(1.0f, -e);
+    if (tid == 0) xscale[row] = ldexpf(1.0f, e);
+    uint8_t* out = xq + (size_t)row * dim * 2u;
+    // one thread per (block, t): 8 elements -> 16 bytes
+    for (uint32_t u = tid; u < (dim >> 3); u += 256u) {
+        const uint32_t blk = u >> 2, t = u & 3u;
+        const float4 p = *reinterpret_cast<const float4*>(xr + blk * 32u + 4u * t);
+        const float4 q = *reinterpret_cast<const float4*>(xr + blk * 32u + 16u + 4u * t);
+        const float v[8] = {p.x, p.y, p.z, p.w, q.x, q.y, q.z, q.w};
+        uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float s = v[i] * inv;
+            const __nv_fp8_storage_t h = __nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
+            const __half_raw hr = __nv_cvt_fp8_to_halfraw(h, __NV_E4M3);
+            const float hf = __half2float(*reinterpret_cast<const __half*>(&hr));
+            const __nv_fp8_storage_t l = __nv_cvt_float_to_fp8(s - hf, __NV_SATFINITE, __NV_E4M3);
+            hi[i >> 2] |= (uint32_t)h << (8 * (i & 3));
+            lo[i >> 2] |= (uint32_t)l << (8 * (i & 3));
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)blk * 64u + t * 16u) = make_uint4(hi[0], hi[1], lo[0], lo[1]);
+    }
+}
+
+// ---------------------------------------------------------------- slot combine
+__global__ void moe_slot_combine_kernel(const float4* __restrict__ part, float4* __restrict__ residual,
+                                        uint32_t embd4, uint32_t n_active, uint32_t rows) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * embd4) return;
+    const size_t t = i / embd4, r = i % embd4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t k = 0; k < n_active; ++k) {  // fixed slot order: bit-reproducible
+        const float4 p = part[(t * n_active + k) * embd4 + r];
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    float4 d = residual[i];
+    d.x += acc.x; d.y += acc.y; d.z += acc.z; d.w += acc.w;
+    residual[i] = d;
+}
+
+}  // namespace
+
+// slot 29, packs/cuda/src/attn/decode.cuh:1392-1500 (launcher gemm/f32_qkv.cuh:1137-1150)
+PDK_EXPORT int pd_moe_topk_batch(const void* logits, const void* bias, uint32_t n_expert, uint32_t k, void* out_idx,
+                                 void* out_w, uint32_t batch, void* stream) {
+    if (batch == 0) return 0;
+    if (n_expert == 0 || n_expert > 512u || k == 0 || k > 16u || k > n_expert) return cudaErrorInvalidValue;
+    moe_topk_kernel<<<(batch + 3u) / 4u, 128, 0, (cudaStream_t)stream>>>((const float*)logits, (const float*)bias,
+                                                                        n_expert, k, (uint32_t*)out_idx,
+                                                                        (float*)out_w, batch);
+    return pdk_launch_status();
+}
+
+// slot 146, packs/cuda/src/gemm/f32_qkv.cuh:1269-1279 (kernel attn/decode.cuh:2316-2396)
+PDK_EXPORT int pd_moe_align_bm(const void* idx, void* sorted_row, void* sorted_slot, void* block_expert,
+                               uint32_t rows, uint32_t n_active, uint32_t n_expert, uint32_t bm, uint32_t max_blocks,
+                               void* stream) {
+    if (rows == 0 || n_expert == 0) return 0;
+    if (bm == 0 || (bm & (bm - 1u)) || n_expert > 4096u) return cudaErrorInvalidValue;
+    const size_t shmem = (size_t)(2u * n_expert + 1u) * sizeof(uint32_t);
+    moe_align_kernel<<<1, 1024, shmem, (cudaStream_t)stream>>>((const uint32_t*)idx, (uint32_t*)sorted_row,
+                                                               (uint32_t*)sorted_slot, (uint32_t*)block_expert, rows,
+                                                               n_active, n_expert, bm, max_blocks);
+    return pdk_launch_status();
+}
+
+// slot 34, packs/cuda/src/attn/decode.cuh:2316-2396: blocks of 32 entries
+PDK_EXPORT int pd_moe_align(const void* idx, void* sorted_row, void* sorted_slot, void* block_expert, uint32_t rows,
+                            uint32_t n_active, uint32_t n_expert, uint32_t max_blocks, void* stream) {
+    return pd_moe_align_bm(idx, sorted_row, sorted_slot, block_expert, rows, n_active, n_expert, 32u, max_blocks,
+                           stream);
+}
+
+// No slot: the activation step in front of the expert GEMMs (the reference's
+// chain quantizes to int8 here, packs/cuda/src/attn/decode.cuh:2981-3004).
+// x f32[rows][dim] -> xq u8[rows][2*dim] + xscale f32[rows]; dim % 32 == 0.
+PDK_EXPORT int pdk_moe_prep_act(const void* x, void* xq, void* xscale, uint32_t dim, uint32_t rows, void* stream) {
+    if (rows == 0 || dim == 0) return 0;
+    if ((dim & 31u) != 0u || !pdk_aligned(x, 16) || !pdk_aligned(xq, 16)) return cudaErrorInvalidValue;
+    moe_prep_act_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((const float*)x, (uint8_t*)xq, (float*)xscale, dim);
+    return pdk_launch_status();
+}
+
+// slot 91, packs/cuda/src/moe/mmq.cuh:447-483
+PDK_EXPORT int pd_moe_slot_combine(const void* part, void* residual, uint32_t embd, uint32_t n_active, uint32_t rows,
+                                   void* stream) {
+    if (rows == 0 || embd == 0) return 0;
+    if ((embd & 3u) != 0u || !pdk_aligned(part, 16) || !pdk_aligned(residual, 16)) return cudaErrorInvalidValue;
+    const size_t total = (size_t)rows * (embd >> 2);
+    moe_slot_combine_kernel<<<(uint32_t)((total + 255u) / 256u), 256, 0, (cudaStream_t)stream>>>(
+        (const float4*)part, (float4*)residual, embd >> 2, n_active, rows);
+    return pdk_launch_status();
+}

@@ -101,12 +101,16 @@ _SIGS = {
     "f8row_gemm": "pppppuuu", "f8row_gemm_tc5x": "pppppuuu",
     "quantize_nvf4": "pppu", "nvf4_dequant": "ppfpuu", "nvf4_gemv": "pppppfuu",
     "nvf4_tc5_tile_scales": "ppuu", "nvf4_gemm_tc5w": "ppppppfuuupU",
+    "moe_topk_batch": "ppuuppu", "moe_align": "ppppuuuu", "moe_align_bm": "ppppuuuuu", "moe_slot_combine": "ppuuu",
     "kquant_dequant": "ppUu", "kquant_repack": "pppUu", "kquant_gemv": "ppppuuu",
 }
 _EXTRA_SIGS = {
     "pdk_kquant_gemm_f32": "ppppuuuu",
     "pdk_f8row_gemm_bf16": "pppppuuu",
     "pdk_nvf4_gemm_bf16": "ppppppfuuu",
+    "pdk_moe_prep_act": "pppuu",
+    "pdk_mxfp4_moe_gate_up": "pppppppppppuuuuff",
+    "pdk_mxfp4_moe_down": "ppppppppppuuuuu",
 }
 _KIND = {"p": C.c_void_p, "u": C.c_uint32, "U": C.c_uint64, "f": C.c_float}
 

@@ -79,3 +79,77 @@ class GpuExecutor:
     def kquant_gemm_f32(self, w, x, y, batch):
         self.pack.call("pdk_kquant_gemm_f32", w.data, w.scales, x, y, w.dims[0], w.dims[1], batch, w.ty,
                        stream=_stream())
+
+
+@dataclass
+class RepackedMxfp4:
+    """types.rs:111-127: 16-byte nibble blocks + 1-byte E8M0 scales."""
+    data: torch.Tensor
+    scale: torch.Tensor
+
+
+@dataclass
+class MoeMxfp4Planes:
+    """One MoE layer's expert planes (gate / up: [expert][ff][embd], down: [expert][embd][ff])
+    and optional f32 biases ([expert][ff] / [expert][embd])."""
+    gate: RepackedMxfp4
+    up: RepackedMxfp4
+    down: RepackedMxfp4
+    n_expert: int
+    embd: int
+    ff: int
+    gate_bias: torch.Tensor = None
+    up_bias: torch.Tensor = None
+    down_bias: torch.Tensor = None
+
+
+def repack_mxfp4(ex, raw_dev):
+    """gpu/moe_mxfp4.rs:908-936: raw 17-byte blocks -> data + scale planes."""
+    n_blocks = raw_dev.numel() // 17
+    data = torch.empty(n_blocks * 16, dtype=torch.uint8, device=ex.device)
+    scale = torch.empty(n_blocks, dtype=torch.uint8, device=ex.device)
+    ex.pack.call("mxfp4_repack", raw_dev, data, scale, n_blocks, stream=_stream())
+    return RepackedMxfp4(data, scale)
+
+
+class MoeWorkspace:
+    """Buffers of one MoE block call, sized for `tokens` tokens (allocated once, reused)."""
+
+    def __init__(self, ex, planes, tokens, n_active, bm):
+        dev, f32, u32 = ex.device, torch.float32, torch.int32
+        pairs = tokens * n_active
+        self.bm, self.tokens, self.n_active = bm, tokens, n_active
+        self.max_blocks = min(pairs, pairs // bm + planes.n_expert)
+        nb = self.max_blocks * bm
+        self.idx = torch.empty(pairs, dtype=u32, device=dev)
+        self.w = torch.empty(pairs, dtype=f32, device=dev)
+        self.sorted_row = torch.empty(nb, dtype=u32, device=dev)
+        self.sorted_slot = torch.empty(nb, dtype=u32, device=dev)
+        self.block_expert = torch.empty(self.max_blocks, dtype=u32, device=dev)
+        self.xq = torch.empty(tokens * planes.embd * 2, dtype=torch.uint8, device=dev)
+        self.xscale = torch.empty(tokens, dtype=f32, device=dev)
+        self.h = torch.zeros(nb * planes.ff, dtype=f32, device=dev)
+        self.hq = torch.empty(nb * planes.ff * 2, dtype=torch.uint8, device=dev)
+        self.hscale = torch.empty(nb, dtype=f32, device=dev)
+        self.part = torch.empty(pairs * planes.embd, dtype=f32, device=dev)
+
+
+def moe_mxfp4_forward(ex, planes, ws, x, router_logits, out, alpha=1.702, limit=7.0, router_bias=None):
+    """The MoE block the way crates/paddock-engine/src/gpu_model/gpt_oss.rs:2279-2521 walks it:
+    top-k -> align -> activation step -> gate|up + SwiGLU -> activation step -> down -> combine.
+    x f32[tokens][embd], router_logits f32[tokens][n_expert], out f32[tokens][embd] (accumulated into)."""
+    st = _stream()
+    c = ex.pack.call
+    T, k, bm = ws.tokens, ws.n_active, ws.bm
+    c("moe_topk_batch", router_logits, router_bias, planes.n_expert, k, ws.idx, ws.w, T, stream=st)
+    c("moe_align_bm", ws.idx, ws.sorted_row, ws.sorted_slot, ws.block_expert, T, k, planes.n_expert, bm,
+      ws.max_blocks, stream=st)
+    c("pdk_moe_prep_act", x, ws.xq, ws.xscale, planes.embd, T, stream=st)
+    c("pdk_mxfp4_moe_gate_up", planes.gate.data, planes.gate.scale, planes.gate_bias, planes.up.data,
+      planes.up.scale, planes.up_bias, ws.sorted_row, ws.block_expert, ws.xq, ws.xscale, ws.h, planes.embd,
+      planes.ff, bm, ws.max_blocks, alpha, limit, stream=st)
+    c("pdk_moe_prep_act", ws.h, ws.hq, ws.hscale, planes.ff, ws.max_blocks * bm, stream=st)
+    c("pdk_mxfp4_moe_down", planes.down.data, planes.down.scale, planes.down_bias, ws.sorted_row, ws.sorted_slot,
+      ws.block_expert, ws.w, ws.hq, ws.hscale, ws.part, planes.ff, planes.embd, k, bm, ws.max_blocks, stream=st)
+    c("moe_slot_combine", ws.part, out, planes.embd, k, T, stream=st)
+    return 7  # launches
