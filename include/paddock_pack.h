@@ -230,6 +230,22 @@ int pdk_mxfp4_moe_down(const void* down_data, const void* down_scale, const void
                        const void* hscale, void* part, uint32_t ff, uint32_t embd, uint32_t n_active, uint32_t bm,
                        uint32_t max_blocks, void* stream);
 
+/* No counterpart in the reference.  pdk_mxfp4_moe_down + pd_moe_slot_combine for callers that may
+ * not allocate device memory (a serving loop that must stay off the allocator, a plug-in handed
+ * pointers by its host, a process with a memory budget fixed at start-up): the per-(token, slot)
+ * partial buffer is a 1 MiB static device array inside the library, held by every GPU that loads
+ * it.  rows*n_active*embd <= pdk_static_part_capacity() (262144), otherwise refused with
+ * cudaErrorInvalidValue (reason in pdk_static_last_refusal()).  The first call on a device resolves
+ * the array's address and should come before any stream capture; calls share the array, so calls
+ * that overlap on the GPU race. */
+int pdk_mxfp4_moe_down_combine_static(const void* down_data, const void* down_scale, const void* down_bias,
+                                      const void* sorted_row, const void* sorted_slot, const void* block_expert,
+                                      const void* topk_w, const void* hq, const void* hscale, void* residual,
+                                      uint32_t ff, uint32_t embd, uint32_t n_active, uint32_t rows, uint32_t bm,
+                                      uint32_t max_blocks, void* stream);
+uint64_t pdk_static_part_capacity(void);
+const char* pdk_static_last_refusal(void);
+
 /* ---- glue the engine's preflight needs ------------------------------------- */
 
 /* slot 6 (crates/paddock-engine/src/gpu/mod.rs:507-528 launches it at start-up): y += x */

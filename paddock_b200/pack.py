@@ -111,6 +111,7 @@ _EXTRA_SIGS = {
     "pdk_moe_prep_act": "pppuu",
     "pdk_mxfp4_moe_gate_up": "pppppppppppuuuuff",
     "pdk_mxfp4_moe_down": "ppppppppppuuuuu",
+    "pdk_mxfp4_moe_down_combine_static": "ppppppppppuuuuuu",
 }
 _KIND = {"p": C.c_void_p, "u": C.c_uint32, "U": C.c_uint64, "f": C.c_float}
 
