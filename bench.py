@@ -36,6 +36,9 @@ K_DIM = 5120
 N_DIM = 25600
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the GEMV kernel, from
+# the ncu capture summarized in profiles/q4k_gemv_i8_config2_m1.md (scaled by rows when sharded)
+NCU_TRAFFIC_BYTES = 79_500_000
 
 
 def algorithmic_bytes(m, n=N_DIM, k=K_DIM):
@@ -273,8 +276,8 @@ def run_ours(args, rank, world, local_rank):
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "q4k_gemv_kernel", "us_per_launch": kern_ms * 1e3,
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES * rows // N_DIM, "peak_kind": peak_kind,
+                         "kernel": "gemv_i8_kernel<Q4K>", "us_per_launch": kern_ms * 1e3,
                          "us_per_launch_event_bracketed": event_us,
                          "algorithmic_bytes_per_launch": kern_bytes},
             "clocks": sampler.summary(),
