@@ -167,9 +167,9 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    from paddock_b200 import shard
     ex = GpuExecutor()
-    rows = N_DIM // world
-    assert rows * world == N_DIM
+    _, rows = shard.row_band(N_DIM, world, rank, align=16)
 
     # ---- synthetic plane: this rank's row band, quantized to raw Q4_K, repacked
     w = synth.normal(rows * K_DIM, 0x5EED0200 + rank, 0.02, dev)

@@ -1,0 +1,56 @@
+"""World-size-2 check (gloo, CPU) of the output-row sharding convention the
+multi-GPU benchmark uses: each rank computes its band of y from its band of
+the raw quantized tensor, the bands are all-gathered, and the result must equal
+the unsharded product.  The per-rank compute here is the CPU oracle; on GPUs it
+is the kernel pack."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from paddock_b200 import shard
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def worker(rank, world, port, n, k, batch, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    w = oracle.fill_normal(n * k, 5, 0.02)
+    raw = oracle.quantize_q4_k(w)                      # every rank derives the same full tensor
+    x = oracle.bf16_round(oracle.fill_normal(batch * k, 6, 1.0))
+    off, nbytes = shard.raw_band_bytes(n, k, world, rank, 256, 144)
+    first, rows = shard.row_band(n, world, rank)
+    band = oracle.dequant_q4_k(raw[off:off + nbytes])
+    y_band = oracle.matmul_f64(band, x, k, rows, batch)          # [batch][rows]
+    gathered = torch.empty(world * batch * rows, dtype=torch.float32)
+    dist.all_gather_into_tensor(gathered, torch.from_numpy(np.ascontiguousarray(y_band)).reshape(-1))
+    y = shard.gathered_to_token_major(gathered, world, batch, rows)
+    if rank == 0:
+        full = oracle.matmul_f64(oracle.dequant_q4_k(raw), x, k, n, batch)
+        np.save(out_path, np.stack([y.numpy(), full]))
+    dist.destroy_process_group()
+
+
+def test_row_sharded_gemm_matches_unsharded(tmp_path):
+    n, k, batch, world = 64, 512, 3, 2
+    out = str(tmp_path / "y.npy")
+    mp.spawn(worker, args=(world, free_port(), n, k, batch, out), nprocs=world, join=True)
+    y, full = np.load(out)
+    assert np.array_equal(y, full)
+
+
+def test_band_helpers():
+    assert shard.row_band(25600, 8, 3) == (9600, 3200)
+    assert shard.raw_band_bytes(25600, 5120, 8, 1, 256, 144) == (3200 * 20 * 144, 3200 * 20 * 144)
+    import pytest
+    with pytest.raises(ValueError):
+        shard.row_band(100, 8, 0)
