@@ -28,6 +28,8 @@
 // software pipeline with its loads issued DEPTH-1 units ahead.  Lane t of a
 // row reads a contiguous quarter of the row's unit, so the four lanes of a row
 // read one contiguous 128-byte (Q4_K) or 256-byte (Q8_0) run.
+#include <cstdlib>
+
 #include "pdk_common.cuh"
 
 namespace {
@@ -192,6 +194,12 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
         }
     };
 
+    // Programmatic dependent launch: let the next kernel in the stream start its
+    // own prologue as soon as every CTA of this one is running, and put this
+    // kernel's first weight loads (weights never depend on the previous kernel) in
+    // flight before waiting for the previous kernel's results (x, and y's old
+    // contents).  Both instructions are no-ops under an ordinary launch.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     Stage st[DEPTH];
     if (total > 0u) {
         set_rows(tile0);
@@ -199,6 +207,7 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
         for (uint32_t d = 0; d + 1u < DEPTH; ++d)
             if (d < total) issue(st[d]);
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- activations -> block floating point limbs (8 elements per thread,
     //      the 4 lanes of a block agree on the step through two shuffles)
@@ -328,6 +337,15 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
     }
 }
 
+// PDK_NO_PDL=1 launches without programmatic stream serialization (A/B switch, read once).
+bool pdl_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("PDK_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return v;
+}
+
 template <class F>
 int launch(const void* data, const void* recs, const float* bias, const float* x, float* y, uint32_t in_dim,
            uint32_t out_dim, cudaStream_t st) {
@@ -342,8 +360,18 @@ int launch(const void* data, const void* recs, const float* bias, const float* x
     uint32_t grid = (uint32_t)pdk_sm_count();
     const uint32_t need = (n_tiles + kSlots - 1u) / kSlots;
     if (grid > need) grid = need;
-    kern<<<grid, kThreads, smem, st>>>((const uint8_t*)data, (const uint8_t*)recs, bias, x, y, in_dim, out_dim);
-    return pdk_launch_status();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, (const uint8_t*)data, (const uint8_t*)recs, bias, x, y, in_dim, out_dim);
+    return e == cudaSuccess ? pdk_launch_status() : (int)e;
 }
 
 }  // namespace

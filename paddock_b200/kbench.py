@@ -101,8 +101,37 @@ def bench_nvf4(ex, a):
     return sec, {"bound": "both", "flops": 2.0 * m * n * k, "bytes": nbytes_w + 4 + m * (k // 2 + k // 16) + m * n * 2}
 
 
-OPS = {"nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
-DEFAULTS = {"nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+def bench_moe(ex, a):
+    """BASELINE config 5: 128 experts, top-4, hidden = ff = 2880, T = --m tokens."""
+    from . import planes as P
+    n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
+    bm = 8 if T * k <= 1024 else 32
+    blocks_per_plane = n_expert * embd * ff // 32
+
+    def plane(seed):
+        g = torch.Generator(device="cuda")
+        g.manual_seed(seed)
+        data = torch.randint(0, 256, (blocks_per_plane * 16,), dtype=torch.uint8, device="cuda", generator=g)
+        scale = torch.randint(118, 124, (blocks_per_plane,), dtype=torch.uint8, device="cuda", generator=g)
+        return P.RepackedMxfp4(data, scale)
+
+    planes = P.MoeMxfp4Planes(plane(1), plane(2), plane(3), n_expert, embd, ff)
+    x = synth.bf16_round(synth.normal(T * embd, 7, 1.0, "cuda"))
+    ws = P.MoeWorkspace(ex, planes, T, k, bm)
+    out = torch.zeros(T * embd, dtype=torch.float32, device="cuda")
+    n_sets = 6 if T <= 64 else 1          # different routings so consecutive steps touch different experts
+    logits = [synth.normal(T * n_expert, 100 + i, 1.0, "cuda") for i in range(n_sets)]
+    sec = time_launches(lambda i: P.moe_mxfp4_forward(ex, planes, ws, x, logits[i % n_sets], out), a.iters)
+    distinct = 0
+    for lg in logits:
+        distinct += torch.unique(torch.topk(lg.view(T, n_expert), k, dim=1).indices).numel()
+    distinct /= n_sets
+    per_expert = 3 * embd * ff // 32 * 17
+    return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
+
+
+OPS = {"moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
 def main():
@@ -120,7 +149,8 @@ def main():
     sec, info = OPS[a.op](ex, a)
     err = ex.pack.device_error()
     hbm, bf16, kind = peaks()
-    line = {"op": a.op, "m": a.m, "n": a.n, "k": a.k, "us": sec * 1e6, "device_error": err, "peak_kind": kind}
+    extra = {k: v for k, v in info.items() if k not in ("bound", "bytes", "flops")}
+    line = {**extra, "op": a.op, "m": a.m, "n": a.n, "k": a.k, "us": sec * 1e6, "device_error": err, "peak_kind": kind}
     if info["bound"] in ("hbm", "both"):
         line.update(gbs=info["bytes"] / sec / 1e9, frac_of_hbm=info["bytes"] / sec / 1e9 / hbm)
     if info["bound"] in ("tensor", "both"):
