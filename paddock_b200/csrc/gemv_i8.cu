@@ -170,7 +170,9 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
     const uint32_t len = u_hi - u_lo;
     const size_t row_data = (size_t)n_unit * F::kDataBytes, row_rec = (size_t)n_unit * F::kRecBytes;
 
-    const uint32_t tile0 = blockIdx.x * kSlots + slot, tile_stride = gridDim.x * kSlots;
+    // slot-major tile numbering: the tiles of the last, partial round land on different
+    // CTAs instead of filling the first CTAs' four slots
+    const uint32_t tile0 = slot * gridDim.x + blockIdx.x, tile_stride = gridDim.x * kSlots;
     const uint32_t my_tiles = tile0 < n_tiles ? (n_tiles - tile0 + tile_stride - 1u) / tile_stride : 0u;
     const uint32_t total = my_tiles * len;
 
