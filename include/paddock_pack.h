@@ -211,8 +211,8 @@ int pd_moe_slot_combine(const void* part, void* residual, uint32_t embd, uint32_
                         void* stream);
 /* No slot.  Activation step in front of the expert GEMMs; the reference quantizes to int8 at this
  * point (pd_quantize_q8, packs/cuda/src/attn/decode.cuh:2981-3004).  x f32[rows][dim] ->
- * xq u8[rows][2*dim] (exact e4m3 hi + lo pairs in mma fragment order) + xscale f32[rows]
- * (power-of-two step per row).  dim % 32 == 0. */
+ * xq f16[rows][dim] (2*dim bytes per row, mma fragment order) + xscale f32[rows] (power-of-two
+ * step per row): bf16 activations exactly, f32 ones to 11 significant bits.  dim % 32 == 0. */
 int pdk_moe_prep_act(const void* x, void* xq, void* xscale, uint32_t dim, uint32_t rows, void* stream);
 /* No slot; counterpart of slot 88 (pd_mxfp4_moe_gate_up_mmq, packs/cuda/src/moe/mmq.cuh:550-590)
  * with the activation operands of pdk_moe_prep_act.  gate/up planes as pd_mxfp4_repack writes

@@ -1,21 +1,23 @@
 // moe_mxfp4.cu - MXFP4 expert GEMMs over expert-aligned token blocks
 // (gate + up + SwiGLU, then down), the MoE half of the quantized linear path.
 //
-// HBM-bound at every batch size: a routed expert's 13 MB of 4.25-bit weights
-// are read once for a handful of tokens.  Weights stay packed until they are in
-// registers.  An e2m1 nibble (s e1 e0 m) becomes the e4m3 byte (s 00e1e0 m00)
-// with two shifts and two logic ops per four weights; that byte's value is
-// exactly e2m1 * 2^-6 (the e4m3 subnormal range continues the e2m1 grid), so
-// the FP8 tensor cores (mma m16n8k32 e4m3 x e4m3 -> f32) compute exact block
-// dot products with no lookup.  A ggml MXFP4 block keeps element j in the low
-// nibble of byte j and element j+16 in the high nibble, which is precisely the
-// mma's A fragment (k-slots 4t..4t+3 and 16+4t..16+4t+3 from word t of the
-// block), so lane t reads word t of each 16-byte block.
-// Activations arrive as exact e4m3 hi + e4m3 lo pairs with one power-of-two
-// step per row (pdk_moe_prep_act): both mmas accumulate into the same tile.
-// After each 32-element block the tile is folded in f32 with the block's E8M0
-// weight scale; the row step, bias, SwiGLU and the routing weight are applied
-// in the epilogue.
+// HBM-bound at decode widths: a routed expert's 13 MB of 4.25-bit weights are read
+// once for a handful of tokens.  Weights stay packed until they are in registers.
+// An e2m1 nibble (s e1 e0 m) placed at bits (15 | 11 10 | 9) of an f16 is exactly
+// e2m1 * 2^-14 - the f16 subnormal range continues the e2m1 grid, so codes 0 and 1
+// need no special case - which costs two shifts and two logic ops per nibble pair
+// and no lookup.  The products run on the tensor cores (mma m16n8k16 f16 -> f32).
+// A ggml MXFP4 block keeps element j in the low nibble of byte j and element j+16
+// in the high nibble; lane t takes word t of each 16-byte block (elements 4t..4t+3
+// and 16+4t..16+4t+3) and the activation operand is stored in the matching order,
+// so the k permutation costs nothing.
+// Activations arrive as f16 with one power-of-two step per row (pdk_moe_prep_act):
+// bf16 activations are carried exactly, general f32 ones to 11 significant bits.
+// Lane t of a row loads whole 16-byte blocks (block 4*group + t), so the four
+// lanes of a row read 64 contiguous bytes per step.  Each block is multiplied in
+// f16 by 2^(its E8M0 exponent - the largest of the warp's K slice) - exact - so
+// every mma of the slice accumulates into one tile; the common scale, the row
+// step, bias, SwiGLU and the routing weight are applied in the epilogue.
 //
 // A CTA works on one aligned block of BM = 8*NT tokens.  NT = 1 (BM = 8) is the
 // decode shape: 4 row tiles x 4 K slices per CTA, several CTAs per SM.  NT = 4
@@ -25,28 +27,29 @@
 
 namespace {
 
-__device__ __forceinline__ void mma_e4m3(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1, const float (&c)[4]) {
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1, const float (&)[4]) {
     asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%11,%12,%13};"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ void bar_sync(uint32_t id, uint32_t count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-// word of 8 nibbles -> e4m3 bytes of the 4 low nibbles / the 4 high nibbles
-__device__ __forceinline__ uint32_t nib_lo_e4m3(uint32_t w) {
-    return ((w << 2) & 0x1C1C1C1Cu) | ((w << 4) & 0x80808080u);
+// Word of 8 nibbles n0..n7 -> four f16x2 registers holding (n0,n4), (n2,n6), (n1,n5), (n3,n7)
+// as e2m1 * 2^-14: magnitude bits to f16 bits 9..11, sign bit to bit 15.
+__device__ __forceinline__ void nib_to_f16x2(uint32_t w, uint32_t& p04, uint32_t& p26, uint32_t& p15, uint32_t& p37) {
+    constexpr uint32_t M = 0x0E000E00u, S = 0x80008000u;
+    p04 = ((w << 9) & M) | ((w << 12) & S);
+    p15 = ((w << 5) & M) | ((w << 8) & S);
+    p26 = ((w << 1) & M) | ((w << 4) & S);
+    p37 = ((w >> 3) & M) | (w & S);
 }
-__device__ __forceinline__ uint32_t nib_hi_e4m3(uint32_t w) {
-    return ((w >> 2) & 0x1C1C1C1Cu) | (w & 0x80808080u);
-}
-// E8M0 byte s -> 2^(s - 127) * 2^6 (the e4m3 bytes carry e2m1 * 2^-6)
-__device__ __forceinline__ float e8m0_x64(uint32_t s) { return __uint_as_float(min(s + 6u, 254u) << 23); }
+// E8M0 byte s -> 2^(s - 127) * 2^14 (the f16 values carry e2m1 * 2^-14)
+__device__ __forceinline__ float e8m0_x2p14(uint32_t s) { return __uint_as_float(min(s + 14u, 254u) << 23); }
 
 struct Args {
     const uint8_t* w0_data;   // gate (or down) nibbles  [expert][rows][nblk*16]
@@ -59,7 +62,7 @@ struct Args {
     const uint32_t* sorted_slot;
     const uint32_t* block_expert;
     const float* topk_w;      // down only
-    const uint8_t* xq;        // [src rows][2*in_dim]
+    const uint8_t* xq;        // f16 [src rows][in_dim] in fragment order
     const float* xscale;      // [src rows]
     float* out;               // GATED: h [max_blocks*BM][out_dim];  else part [rows*n_active][out_dim]
     uint32_t in_dim, out_dim, n_active;
@@ -110,9 +113,11 @@ moe_mxfp4_kernel(const Args a) {
     }
     __syncthreads();
 
-    const uint32_t kb_lo = slice * nblk / KS, kb_hi = (slice + 1u) * nblk / KS;
+    // K is walked in groups of four 32-element blocks; lane t owns block 4*grp + t of its rows
+    const uint32_t n_grp = (nblk + 3u) >> 2;
+    const uint32_t grp_lo = slice * n_grp / KS, grp_hi = (slice + 1u) * n_grp / KS;
     const size_t plane_rows = (size_t)expert * out_dim;
-    const uint8_t* xs_lane = xs + (size_t)g * pitch + t * 16u;
+    const uint8_t* xs_lane = xs + (size_t)g * pitch;
     const uint32_t n_tiles = (out_dim + 15u) >> 4;
     uint32_t iter = 0;
 
@@ -120,13 +125,13 @@ moe_mxfp4_kernel(const Args a) {
         const uint32_t r0 = min(tile * 16u + g, out_dim - 1u), r1 = min(tile * 16u + g + 8u, out_dim - 1u);
         const uint8_t* d[NP][2];
         const uint8_t* s[NP][2];
-        d[0][0] = a.w0_data + (plane_rows + r0) * nblk * 16u + t * 4u;
-        d[0][1] = a.w0_data + (plane_rows + r1) * nblk * 16u + t * 4u;
+        d[0][0] = a.w0_data + (plane_rows + r0) * nblk * 16u;
+        d[0][1] = a.w0_data + (plane_rows + r1) * nblk * 16u;
         s[0][0] = a.w0_scale + (plane_rows + r0) * nblk;
         s[0][1] = a.w0_scale + (plane_rows + r1) * nblk;
         if (GATED) {
-            d[NP - 1][0] = a.w1_data + (plane_rows + r0) * nblk * 16u + t * 4u;
-            d[NP - 1][1] = a.w1_data + (plane_rows + r1) * nblk * 16u + t * 4u;
+            d[NP - 1][0] = a.w1_data + (plane_rows + r0) * nblk * 16u;
+            d[NP - 1][1] = a.w1_data + (plane_rows + r1) * nblk * 16u;
             s[NP - 1][0] = a.w1_scale + (plane_rows + r0) * nblk;
             s[NP - 1][1] = a.w1_scale + (plane_rows + r1) * nblk;
         }
@@ -136,53 +141,107 @@ moe_mxfp4_kernel(const Args a) {
 #pragma unroll
             for (uint32_t n = 0; n < NT; ++n) acc[p][n][0] = acc[p][n][1] = acc[p][n][2] = acc[p][n][3] = 0.0f;
 
-        // register prefetch, DEPTH blocks ahead
-        constexpr uint32_t DEPTH = 4;
-        uint32_t wq[DEPTH][NP][2], sq[DEPTH][NP][2];
-        auto fetch = [&](uint32_t slot_i, uint32_t kb) {
+        // Common power of two of this warp's K slice, per plane and row: the largest E8M0
+        // byte among the slice's blocks.  Every block is brought to it in f16 (a
+        // power-of-two multiply, exact for blocks within 24 binades of the largest; what
+        // smaller blocks lose is below 2^-28 of the largest block, under f32 resolution), so all mmas of the slice
+        // accumulate into one tile and the scale is applied once, in the epilogue.
+        uint32_t smax[NP][2];
+#pragma unroll
+        for (uint32_t p = 0; p < NP; ++p)
+#pragma unroll
+            for (uint32_t r = 0; r < 2u; ++r) {
+                uint32_t m = 0u;
+                for (uint32_t kb = grp_lo * 4u + t; kb < min(grp_hi * 4u, nblk); kb += 4u)
+                    m = max(m, (uint32_t)__ldg(s[p][r] + kb));
+                m = max(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = max(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                smax[p][r] = m;
+            }
+
+        // Register prefetch, DEPTH groups ahead: one 16-byte block per lane, row and plane;
+        // the four lanes of a row bring four consecutive blocks.
+        constexpr uint32_t DEPTH = (GATED && NT == 4) ? 2 : 3;  // what fits in 128 registers
+        uint4 wq[DEPTH][NP][2];
+        uint32_t sq[DEPTH][NP][2];
+        auto fetch = [&](uint32_t slot_i, uint32_t grp) {
+            const uint32_t kb = grp * 4u + t;
+            const bool have = kb < nblk;
 #pragma unroll
             for (uint32_t p = 0; p < NP; ++p)
 #pragma unroll
                 for (uint32_t r = 0; r < 2u; ++r) {
-                    wq[slot_i][p][r] = __ldg(reinterpret_cast<const uint32_t*>(d[p][r] + (size_t)kb * 16u));
-                    sq[slot_i][p][r] = __ldg(s[p][r] + kb);
+                    wq[slot_i][p][r] = have ? pdk_ldg_stream16(d[p][r] + (size_t)kb * 16u) : make_uint4(0u, 0u, 0u, 0u);
+                    sq[slot_i][p][r] = have ? (uint32_t)__ldg(s[p][r] + kb) : 0u;
                 }
         };
 #pragma unroll
         for (uint32_t i = 0; i < DEPTH; ++i)
-            if (kb_lo + i < kb_hi) fetch(i, kb_lo + i);
+            if (grp_lo + i < grp_hi) fetch(i, grp_lo + i);
 
-        for (uint32_t kb0 = kb_lo; kb0 < kb_hi; kb0 += DEPTH) {
+        for (uint32_t g0 = grp_lo; g0 < grp_hi; g0 += DEPTH) {
 #pragma unroll
             for (uint32_t i = 0; i < DEPTH; ++i) {
-                const uint32_t kb = kb0 + i;
-                if (kb >= kb_hi) break;
-                uint32_t al[NP][2], ah[NP][2];
-                float f[NP][2];
+                const uint32_t grp = g0 + i;
+                if (grp >= grp_hi) break;
+                // block value in f16 = e2m1 * 2^-14 * 2^(sb - smax + 15) (the largest multiplier f16 holds):
+                // at most 12, exact for blocks within 24 binades of the largest, rounded to 2^-24 below
+                __half2 h2[NP][2];
+                uint32_t w[NP][2][4];
 #pragma unroll
                 for (uint32_t p = 0; p < NP; ++p)
 #pragma unroll
                     for (uint32_t r = 0; r < 2u; ++r) {
-                        al[p][r] = nib_lo_e4m3(wq[i][p][r]);
-                        ah[p][r] = nib_hi_e4m3(wq[i][p][r]);
-                        f[p][r] = e8m0_x64(sq[i][p][r]);
+                        const int e = (int)sq[i][p][r] - (int)smax[p][r] + 15;
+                        h2[p][r] = __half2half2(
+                            __float2half_rn(e >= -24 ? __uint_as_float((uint32_t)(e + 127) << 23) : 0.0f));
+                        // lane t walks its block's words in the order k ^ t, so that the four lanes'
+                        // activation reads of one step fall on different shared-memory banks
+                        uint32_t* ww = w[p][r];
+                        ww[0] = wq[i][p][r].x; ww[1] = wq[i][p][r].y; ww[2] = wq[i][p][r].z; ww[3] = wq[i][p][r].w;
+                        if (t & 1u) { const uint32_t a0 = ww[0], a2 = ww[2]; ww[0] = ww[1]; ww[1] = a0; ww[2] = ww[3]; ww[3] = a2; }
+                        if (t & 2u) { const uint32_t a0 = ww[0], a1 = ww[1]; ww[0] = ww[2]; ww[2] = a0; ww[1] = ww[3]; ww[3] = a1; }
                     }
-                if (kb + DEPTH < kb_hi) fetch(i, kb + DEPTH);
-                const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (grp + DEPTH < grp_hi) fetch(i, grp + DEPTH);
+                const uint32_t kb = min(grp * 4u + t, nblk - 1u);  // lanes past the end hold zero weights
 #pragma unroll
-                for (uint32_t n = 0; n < NT; ++n) {
-                    const uint4 b = *reinterpret_cast<const uint4*>(xs_lane + (size_t)n * 8u * pitch + (size_t)kb * 64u);
+                for (uint32_t k = 0; k < 4u; ++k) {
+                    // word k of both rows and planes -> scaled f16x2 pairs (e0,e2) (e1,e3) (e16,e18) (e17,e19)
+                    uint32_t qa[NP][2][4];
 #pragma unroll
-                    for (uint32_t p = 0; p < NP; ++p) {
-                        float c[4], c2[4];
-                        mma_e4m3(c, al[p][0], al[p][1], ah[p][0], ah[p][1], b.x, b.y, zero);
-                        mma_e4m3(c2, al[p][0], al[p][1], ah[p][0], ah[p][1], b.z, b.w, c);
-                        acc[p][n][0] = fmaf(f[p][0], c2[0], acc[p][n][0]);
-                        acc[p][n][1] = fmaf(f[p][0], c2[1], acc[p][n][1]);
-                        acc[p][n][2] = fmaf(f[p][1], c2[2], acc[p][n][2]);
-                        acc[p][n][3] = fmaf(f[p][1], c2[3], acc[p][n][3]);
+                    for (uint32_t p = 0; p < NP; ++p)
+#pragma unroll
+                        for (uint32_t r = 0; r < 2u; ++r) {
+                            uint32_t c[4];
+                            nib_to_f16x2(w[p][r][k], c[0], c[1], c[2], c[3]);
+#pragma unroll
+                            for (uint32_t u = 0; u < 4u; ++u) {
+                                const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&c[u]), h2[p][r]);
+                                qa[p][r][u] = *reinterpret_cast<const uint32_t*>(&v);
+                            }
+                        }
+#pragma unroll
+                    for (uint32_t n = 0; n < NT; ++n) {
+                        const uint4 b = *reinterpret_cast<const uint4*>(xs_lane + (size_t)n * 8u * pitch +
+                                                                        (size_t)kb * 64u + ((k ^ t) * 16u));
+#pragma unroll
+                        for (uint32_t p = 0; p < NP; ++p) {
+                            mma_f16(acc[p][n], qa[p][0][0], qa[p][1][0], qa[p][0][1], qa[p][1][1], b.x, b.y, acc[p][n]);
+                            mma_f16(acc[p][n], qa[p][0][2], qa[p][1][2], qa[p][0][3], qa[p][1][3], b.z, b.w, acc[p][n]);
+                        }
                     }
                 }
+            }
+        }
+        // true weight = stored * 2^(smax - 128)
+#pragma unroll
+        for (uint32_t p = 0; p < NP; ++p) {
+            const float f0 = smax[p][0] >= 2u ? __uint_as_float((smax[p][0] - 1u) << 23) : 0.0f;
+            const float f1 = smax[p][1] >= 2u ? __uint_as_float((smax[p][1] - 1u) << 23) : 0.0f;
+#pragma unroll
+            for (uint32_t n = 0; n < NT; ++n) {
+                acc[p][n][0] *= f0; acc[p][n][1] *= f0;
+                acc[p][n][2] *= f1; acc[p][n][3] *= f1;
             }
         }
 
