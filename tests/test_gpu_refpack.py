@@ -1,0 +1,246 @@
+"""Cross-check against the reference's own CUDA pack, slot by slot.
+
+`oracle/build_ref.sh` compiles the reference's `packs/cuda/pack.cu` into
+`oracle/_ref/pd-cuda-ref.so` (test infrastructure, never shipped).  Both
+libraries are opened through the same loader and the same table offsets
+(crates/paddock-kernels/src/loader.rs:140-283) and given identical device
+operands: dequant / repack / quantizer outputs must be byte-identical, GEMV and
+GEMM outputs agree within the stated tolerance.  A slot the reference build
+leaves NULL or answers "not supported" for on this device is skipped with that
+reason.  The whole module is skipped when the reference library was not built.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from gpu_util import TOL, dev, dev_f32, rel_l2
+from paddock_b200 import KernelPack
+from paddock_b200.pack import LaunchError, MissingOp
+
+pytestmark = pytest.mark.gpu
+
+REF_SO = os.path.join(os.path.dirname(os.path.abspath(oracle.__file__)), "_ref", "pd-cuda-ref.so")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not os.path.exists(REF_SO):
+        pytest.skip("reference pack not built (oracle/build_ref.sh)")
+    return KernelPack.load(REF_SO)
+
+
+def run_both(pack, ref, name, make_args, n_out):
+    """Call slot `name` of both packs on operands from make_args(); returns the
+    last n_out tensors each call wrote, as numpy byte arrays."""
+    outs = []
+    for p in (pack, ref):
+        args, written = make_args()
+        try:
+            p.call(name, *args)
+        except MissingOp:
+            assert p is ref
+            pytest.skip(f"reference pack has no {name} on this build")
+        except LaunchError as e:
+            assert p is ref, e
+            pytest.skip(f"reference {name} declined: {e}")
+        torch.cuda.synchronize()
+        outs.append([w.cpu().numpy().view(np.uint8).copy() for w in written[:n_out]])
+    return outs
+
+
+def assert_bytes_equal(outs):
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+
+
+def test_reference_pack_descriptor(ref):
+    assert ref.info.magic == 0x504B4450 and ref.info.abi_version == 2
+    assert ref.table_size() == 7632
+
+
+def test_mxfp4_and_q8_0_dequant(pack, ref):
+    rng = np.random.default_rng(11)
+    raw = rng.integers(0, 256, 4096 * 17, dtype=np.uint8)
+    raw[::17] = rng.integers(0, 255, 4096, dtype=np.uint8)
+
+    def mk():
+        out = torch.zeros(4096 * 32, dtype=torch.float32, device="cuda")
+        return (dev(raw), out, 4096), [out]
+    assert_bytes_equal(run_both(pack, ref, "mxfp4_dequant_f32", mk, 1))
+    q8 = oracle.quantize_q8_0(oracle.fill_normal(4096 * 32, 12, 0.02))
+
+    def mk8():
+        out = torch.zeros(4096 * 32, dtype=torch.float32, device="cuda")
+        return (dev(q8), out, 4096), [out]
+    assert_bytes_equal(run_both(pack, ref, "q8_0_dequant_f32", mk8, 1))
+
+
+def test_q8_0_and_mxfp4_repack(pack, ref):
+    nb = 5120 // 32 * 64
+    q8 = oracle.quantize_q8_0(oracle.fill_normal(nb * 32, 13, 0.02))
+
+    def mk():
+        d = torch.zeros(nb * 32, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(nb * 2, dtype=torch.uint8, device="cuda")
+        return (dev(q8), d, s, nb), [d, s]
+    assert_bytes_equal(run_both(pack, ref, "q8_0_repack", mk, 2))
+    mx = oracle.quantize_mxfp4(oracle.fill_normal(nb * 32, 14, 0.02))
+
+    def mkm():
+        d = torch.zeros(nb * 16, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+        return (dev(mx), d, s, nb), [d, s]
+    assert_bytes_equal(run_both(pack, ref, "mxfp4_repack", mkm, 2))
+
+
+def q4k_planes(pack, n, k, seed):
+    from paddock_b200 import synth
+    raw = synth.quantize_q4_k(torch.from_numpy(oracle.fill_normal(n * k, seed, 0.02))).numpy()
+    return raw, n * k // 256
+
+
+def test_q4k_dequant_repack_gemv(pack, ref):
+    k, n = 5120, 512
+    raw, ns = q4k_planes(pack, n, k, 15)
+
+    def mkd():
+        out = torch.zeros(n * k, dtype=torch.float32, device="cuda")
+        return (dev(raw), out, ns, 12), [out]
+    assert_bytes_equal(run_both(pack, ref, "kquant_dequant", mkd, 1))
+
+    def mkr():
+        d = torch.zeros(ns * 128, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(ns * 24, dtype=torch.uint8, device="cuda")
+        return (dev(raw), d, s, ns, 12), [d, s]
+    planes = run_both(pack, ref, "kquant_repack", mkr, 2)
+    assert_bytes_equal(planes)
+    x = oracle.bf16_round(oracle.fill_normal(k, 16, 1.0))
+
+    def mkg():
+        y = torch.zeros(n, dtype=torch.float32, device="cuda")
+        return (dev(planes[0][0]), dev(planes[0][1]), dev_f32(x), y, k, n, 12), [y]
+    ours, theirs = (o[0].view(np.float32) for o in run_both(pack, ref, "kquant_gemv", mkg, 1))
+    assert rel_l2(ours, theirs.astype(np.float64)) < 1e-4 < TOL
+
+
+def test_q8_0_gemv_and_gemm(pack, ref):
+    k, n = 5120, 768
+    q8 = oracle.quantize_q8_0(oracle.fill_normal(n * k, 17, 0.02))
+    nb = n * k // 32
+    d = torch.zeros(nb * 32, dtype=torch.uint8, device="cuda")
+    s = torch.zeros(nb * 2, dtype=torch.uint8, device="cuda")
+    pack.call("q8_0_repack", dev(q8), d, s, nb)
+    x = oracle.bf16_round(oracle.fill_normal(4 * k, 18, 1.0))
+    bias = oracle.fill_normal(n, 19, 0.1)
+
+    def mkv():
+        y = torch.zeros(n, dtype=torch.float32, device="cuda")
+        return (d, s, dev_f32(bias), dev_f32(x[:k]), y, k, n), [y]
+    ours, theirs = (o[0].view(np.float32) for o in run_both(pack, ref, "q8_0_gemv_repacked", mkv, 1))
+    assert rel_l2(ours, theirs.astype(np.float64)) < 1e-4 < TOL
+
+    def mkm():
+        y = torch.zeros(4 * n, dtype=torch.float32, device="cuda")
+        return (d, s, None, dev_f32(x), y, k, n, 4), [y]
+    ours, theirs = (o[0].view(np.float32) for o in run_both(pack, ref, "q8_0_gemm_repacked", mkm, 1))
+    assert rel_l2(ours, theirs.astype(np.float64)) < 1e-4 < TOL
+
+
+def test_moe_routing_and_combine(pack, ref):
+    tokens, n_expert, k, bm = 70, 128, 4, 32
+    logits = oracle.fill_normal(tokens * n_expert, 20, 1.0)
+    logits[5] = logits[9]                       # a tie: lowest index wins
+
+    def mkt():
+        i = torch.zeros(tokens * k, dtype=torch.int32, device="cuda")
+        w = torch.zeros(tokens * k, dtype=torch.float32, device="cuda")
+        return (dev_f32(logits), None, n_expert, k, i, w, tokens), [i, w]
+    ours, theirs = run_both(pack, ref, "moe_topk_batch", mkt, 2)
+    assert np.array_equal(ours[0], theirs[0])
+    assert np.allclose(ours[1].view(np.float32), theirs[1].view(np.float32), rtol=2e-6, atol=0)
+    idx = ours[0].view(np.uint32)
+    max_blocks = (tokens * k + n_expert * (bm - 1)) // bm + 1
+
+    def mka():
+        r = torch.full((max_blocks * bm,), 0x7FFFFFFF, dtype=torch.int32, device="cuda")
+        sl = torch.full((max_blocks * bm,), 0x7FFFFFFF, dtype=torch.int32, device="cuda")
+        be = torch.full((max_blocks,), 0x7FFFFFFF, dtype=torch.int32, device="cuda")
+        return (dev(idx), r, sl, be, tokens, k, n_expert, max_blocks), [be, r, sl]
+    ours, theirs = run_both(pack, ref, "moe_align", mka, 3)
+    be_o, be_t = ours[0].view(np.uint32), theirs[0].view(np.uint32)
+    assert np.array_equal(be_o, be_t)
+    # the same (row, slot) pairs in every block; order inside a block is the implementation's
+    ro, so = ours[1].view(np.uint32).reshape(-1, bm), ours[2].view(np.uint32).reshape(-1, bm)
+    rt, st = theirs[1].view(np.uint32).reshape(-1, bm), theirs[2].view(np.uint32).reshape(-1, bm)
+    for b in range(max_blocks):
+        a = sorted(zip(ro[b].tolist(), so[b].tolist()))
+        c = sorted(zip(rt[b].tolist(), st[b].tolist()))
+        live_a = [p for p in a if p[0] < tokens]
+        live_c = [p for p in c if p[0] < tokens]
+        assert live_a == live_c, b
+
+    part = oracle.fill_normal(tokens * k * 64, 21, 1.0)
+    res = oracle.fill_normal(tokens * 64, 22, 1.0)
+
+    def mkc():
+        r = dev_f32(res)
+        return (dev_f32(part), r, 64, k, tokens), [r]
+    assert_bytes_equal(run_both(pack, ref, "moe_slot_combine", mkc, 1))
+
+
+def test_nvf4_quantize_dequant_tile_gemv(pack, ref):
+    n_el = 64 * 5120
+    x = oracle.fill_normal(n_el, 23, 1.0)
+    x[:16] = 0.0
+
+    def mkq():
+        q = torch.zeros(n_el // 2, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(n_el // 16, dtype=torch.uint8, device="cuda")
+        return (dev_f32(x), q, s, n_el), [q, s]
+    assert_bytes_equal(run_both(pack, ref, "quantize_nvf4", mkq, 2))
+
+    n, k = 300, 1024
+    rng = np.random.default_rng(24)
+    q = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    s = rng.integers(0, 0x7F, (n, k // 16), dtype=np.uint8)
+
+    def mkd():
+        y = torch.zeros(n * k, dtype=torch.float32, device="cuda")
+        return (dev(q), dev(s), 0.0173, y, k, n), [y]
+    assert_bytes_equal(run_both(pack, ref, "nvf4_dequant", mkd, 1))
+
+    def mkt():
+        t = torch.zeros(((n + 127) // 128) * (k // 256) * 2048, dtype=torch.uint8, device="cuda")
+        return (dev(s), t, k, n), [t]
+    assert_bytes_equal(run_both(pack, ref, "nvf4_tc5_tile_scales", mkt, 1))
+
+    s_small = rng.integers(0x28, 0x48, (n, k // 16), dtype=np.uint8)
+    xv = oracle.bf16_round(oracle.fill_normal(k, 25, 1.0))
+
+    def mkg():
+        y = torch.zeros(n, dtype=torch.float32, device="cuda")
+        return (dev(q), dev(s_small), None, dev_f32(xv), y, 0.0173, k, n), [y]
+    ours, theirs = (o[0].view(np.float32) for o in run_both(pack, ref, "nvf4_gemv", mkg, 1))
+    assert rel_l2(ours, theirs.astype(np.float64)) < 1e-4 < TOL
+
+
+def test_fp8_row_quantizers(pack, ref):
+    k, rows = 5120, 96
+    x = oracle.fill_normal(rows * k, 26, 1.0)
+    x[:k] = 0.0
+
+    def mkq():
+        q = torch.zeros(rows * k, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(rows, dtype=torch.float32, device="cuda")
+        return (dev_f32(x), q, s, k, rows), [q, s]
+    assert_bytes_equal(run_both(pack, ref, "quantize_e4m3_row", mkq, 2))
+    w = torch.from_numpy(oracle.fill_normal(rows * k, 27, 0.02)).to(torch.bfloat16)
+
+    def mkw():
+        q = torch.zeros(rows * k, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(rows, dtype=torch.float32, device="cuda")
+        return (w.cuda(), q, s, k, rows), [q, s]
+    assert_bytes_equal(run_both(pack, ref, "bf16_to_f8row", mkw, 2))
