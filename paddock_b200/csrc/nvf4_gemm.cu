@@ -15,9 +15,9 @@
 // channels.  One persistent CTA per SM:
 //   warp 0      producer: TMA boxes of W and X (128 rows x 128 bytes, 128-byte
 //               swizzle), one 2 KB bulk copy of the pre-tiled weight scale cells,
-//               and a 32-lane gather of the activation scale cells into the same
-//               cell order
-//   warp 1      MMA issuer: per stage 8 tcgen05.cp (scale cells -> TMEM) + 4 MMAs
+//               and a 32-lane cp.async gather of the activation scale cells into
+//               the same cell order, arriving on the stage barrier asynchronously
+//   warp 1      MMA issuer (converged warp, one elected lane): per stage 8 tcgen05.cp (scale cells -> TMEM) + 4 MMAs
 //   warps 2..5  epilogue: TMEM -> registers -> y (f32 or bf16), * scale2 + bias
 // Accumulators are double buffered (2 x 128 TMEM columns); scale cells take
 // 32 columns per stage.
@@ -53,28 +53,25 @@ struct Shared {
     int abort_flag;
 };
 
-__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     tc5::smem_u32(smem_dst)),
-                 "l"(gmem), "r"(bytes), "r"(tc5::smem_u32(bar))
-                 : "memory");
-}
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 // 512-byte scale cell (32 rows x 16 bytes, no swizzle) -> 4 TMEM columns, broadcast to the 4 lane quarters
+// (called by a converged warp; one elected lane issues)
 __device__ __forceinline__ void sf_copy(uint32_t taddr, uint32_t saddr) {
     const uint64_t desc = (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)1u << 16) | ((uint64_t)8u << 32);
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+    asm volatile(TC5_ELECT "@e tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(desc)
+                 : "memory");
 }
 __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                          uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
-        : "memory");
+    asm volatile(TC5_ELECT
+                 ".reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "@e tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(
+                     d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+                 : "memory");
 }
 template <typename TO>
 __device__ __forceinline__ void store_one(TO* p, float v);
@@ -103,7 +100,7 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            tc5::mbar_init(&sh->full[s], 33);  // producer lane 0 (expect_tx) + 32 gather lanes
+            tc5::mbar_init(&sh->full[s], 33);  // producer lane 0 (expect_tx) + 32 lanes' cp.async arrivals
             tc5::mbar_init(&sh->empty[s], 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
@@ -119,55 +116,72 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         tc5::tmem_alloc(&sh->tmem_base, kTmemCols);
         tc5::tmem_relinquish();
     }
+    // activation scale cells: the gather writes only the rows a token tile has; the rest stay zero
+    for (uint32_t i = threadIdx.x; i < kStages * (kSfBytes / 16u); i += kThreads) {
+        const uint32_t s = i / (kSfBytes / 16u), o = i % (kSfBytes / 16u);
+        reinterpret_cast<uint4*>(tiles + s * kStageBytes + kABytes + kBBytes + kSfBytes)[o] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();
     tc5::fence_before_sync();
     __syncthreads();
     tc5::fence_after_sync();
     const uint32_t tmem_base = sh->tmem_base;
     const tc5::WaitCtx ctx{&sh->abort_flag, err_word};
+    pdk_pdl_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (whole warp)
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        // Activation scale cells of one stage, 16 words per lane:
-        // word (j, l, c) = xs[t0 + c*32 + l][kb*16 + 4j .. 4j+3].  They are fetched one
-        // stage ahead so their latency hides behind the wait for a free stage.
-        uint32_t sfw[16];
-        auto fetch_sf = [&](uint32_t t0, uint32_t kb) {
+        // Activation scale cells of one stage: word (j, l, c) of the 2 KB record is
+        // xs[t0 + c*32 + l][kb*16 + 4j .. 4j+3].  Each lane issues its words as 4-byte
+        // cp.async copies (zero-filled past the batch) and then an asynchronous arrive on
+        // the stage's barrier, so the producer never waits for a load.
+        constexpr uint32_t kSfWords = BN * 4u / 32u;  // words per lane: rows c*32+l with c < BN/32
+        auto gather_sf = [&](uint8_t* sfb, uint64_t* bar, uint32_t t0, uint32_t kb) {
+            const uint32_t dst0 = tc5::smem_u32(sfb);
 #pragma unroll
-            for (uint32_t i = 0; i < 16u; ++i) {
-                const uint32_t w = i * 32u + lane;  // word index inside the 2 KB record
-                const uint32_t c = w & 3u, l = (w >> 2) & 31u, j = w >> 7;
+            for (uint32_t i = 0; i < kSfWords; ++i) {
+                const uint32_t q = i * 32u + lane;           // (j, c, l) with l fastest
+                const uint32_t l = q & 31u, c = (q >> 5) % (BN / 32u), j = q / BN;
                 const uint32_t t = t0 + c * 32u + l;
-                sfw[i] = t < batch ? __ldg(reinterpret_cast<const uint32_t*>(x_sf + (size_t)t * sf_row + kb * 16u + j * 4u))
-                                   : 0u;
+                const uint8_t* src = x_sf + (size_t)min(t, batch - 1u) * sf_row + kb * 16u + j * 4u;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst0 + j * 512u + l * 16u + c * 4u),
+                             "l"(src), "r"(t < batch ? 4u : 0u)
+                             : "memory");
             }
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(tc5::smem_u32(bar)) : "memory");
         };
-        if (blockIdx.x < n_tiles && num_kb > 0u) fetch_sf((blockIdx.x / tiles_w) * BN, 0u);
+        // weight half of a stage: the expected bytes of the whole stage, the W box and its scale cells
+        auto issue_w = [&](uint32_t stg, uint32_t tile_w, uint32_t kb) {
+            uint8_t* a = tiles + stg * kStageBytes;
+            tc5::mbar_arrive_expect_tx_elect(&sh->full[stg], kABytes + kBBytes + kSfBytes);
+            tc5::tma_load_2d_elect(a, &tmap_w, &sh->full[stg], (int32_t)(kb * BKB), (int32_t)(tile_w * BM));
+            tc5::bulk_load_elect(a + kABytes + kBBytes, w_sf_tiled + ((size_t)tile_w * num_kb + kb) * kSfBytes, kSfBytes,
+                                 &sh->full[stg]);
+        };
+        // The weights depend on nothing the previous kernel in the stream writes: the first
+        // tile's first stages stream in before the wait for that kernel; activations after it.
+        uint32_t pre = 0;
+        if (blockIdx.x < n_tiles) {
+            pre = min(num_kb, kStages);
+            for (uint32_t i = 0; i < pre; ++i) issue_w(i, blockIdx.x % tiles_w, i);
+        }
+        pdk_pdl_wait();
         // tiles are walked weight-tile fastest: a wave of CTAs shares one token tile
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const uint32_t w0 = (tile % tiles_w) * BM, t0 = (tile / tiles_w) * BN;
+            const uint32_t tile_w = tile % tiles_w, t0 = (tile / tiles_w) * BN;
             for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                uint8_t* a = tiles + stage * kStageBytes;
-                uint8_t* sfa = a + kABytes + kBBytes;
-                uint8_t* sfb = sfa + kSfBytes;
-                if (lane == 0) {
-                    tc5::mbar_arrive_expect_tx(&sh->full[stage], kABytes + kBBytes + kSfBytes);
-                    tc5::tma_load_2d(a, &tmap_w, &sh->full[stage], (int32_t)(kb * BKB), (int32_t)w0);
-                    tc5::tma_load_2d(a + kABytes, &tmap_x, &sh->full[stage], (int32_t)(kb * BKB), (int32_t)t0);
-                    bulk_copy_g2s(sfa, w_sf_tiled + ((size_t)(tile % tiles_w) * num_kb + kb) * kSfBytes, kSfBytes,
-                                  &sh->full[stage]);
+                const bool early = tile == blockIdx.x && kb < pre;  // first use of the stage, W already issued
+                if (!early) {
+                    ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    issue_w(stage, tile_w, kb);
                 }
-#pragma unroll
-                for (uint32_t i = 0; i < 16u; ++i) reinterpret_cast<uint32_t*>(sfb)[i * 32u + lane] = sfw[i];
-                fence_proxy_async_smem();
-                tc5::mbar_arrive(&sh->full[stage]);
-                // next stage's cells
-                if (kb + 1u < num_kb) fetch_sf(t0, kb + 1u);
-                else if (tile + gridDim.x < n_tiles) fetch_sf(((tile + gridDim.x) / tiles_w) * BN, 0u);
+                uint8_t* a = tiles + stage * kStageBytes;
+                tc5::tma_load_2d_elect(a + kABytes, &tmap_x, &sh->full[stage], (int32_t)(kb * BKB), (int32_t)t0);
+                gather_sf(a + kABytes + kBBytes + kSfBytes, &sh->full[stage], t0, kb);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -175,45 +189,47 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             for (int i = 0; i < 64; ++i) __nanosleep(1000);
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0, iter = 0;
-            bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
-                const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
-                ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
+        // ------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+        uint32_t stage = 0, phase = 0, iter = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
+            const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
+            ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc5::fence_after_sync();
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                ok = tc5::mbar_wait(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc5::fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    ok = tc5::mbar_wait(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
-                    if (!ok) break;
-                    tc5::fence_after_sync();
-                    const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
-                    const uint32_t sfa_addr = a_addr + kABytes + kBBytes, sfb_addr = sfa_addr + kSfBytes;
-                    const uint32_t sfa_t = tmem_base + kSfCol0 + stage * 32u, sfb_t = sfa_t + 16u;
+                fence_proxy_async_smem();  // the gathered cells were written through the generic proxy
+                const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
+                const uint32_t sfa_addr = a_addr + kABytes + kBBytes, sfb_addr = sfa_addr + kSfBytes;
+                const uint32_t sfa_t = tmem_base + kSfCol0 + stage * 32u, sfb_t = sfa_t + 16u;
 #pragma unroll
-                    for (uint32_t j = 0; j < 4u; ++j) {
-                        sf_copy(sfa_t + j * 4u, sfa_addr + j * 512u);
-                        sf_copy(sfb_t + j * 4u, sfb_addr + j * 512u);
-                    }
-                    const uint64_t a_desc = tc5::smem_desc_sw128(a_addr);
-                    const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes);
-#pragma unroll
-                    for (uint32_t j = 0; j < 4u; ++j)  // 64 e2m1 = 32 bytes of K per instruction
-                        mma_nvf4(d_tmem, a_desc + 2u * j, b_desc + 2u * j, kIdesc, sfa_t + j * 4u, sfb_t + j * 4u,
-                                 (kb | j) != 0u);
-                    tc5::mma_commit(&sh->empty[stage]);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                for (uint32_t j = 0; j < 4u; ++j) {
+                    sf_copy(sfa_t + j * 4u, sfa_addr + j * 512u);
+                    sf_copy(sfb_t + j * 4u, sfb_addr + j * 512u);
                 }
-                if (ok) tc5::mma_commit(&sh->tmem_full[buf]);
+                const uint64_t a_desc = tc5::smem_desc_sw128(a_addr);
+                const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes);
+#pragma unroll
+                for (uint32_t j = 0; j < 4u; ++j)  // 64 e2m1 = 32 bytes of K per instruction
+                    mma_nvf4(d_tmem, a_desc + 2u * j, b_desc + 2u * j, kIdesc, sfa_t + j * 4u, sfb_t + j * 4u,
+                             (kb | j) != 0u);
+                tc5::mma_commit_elect(&sh->empty[stage]);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
+            if (ok) tc5::mma_commit_elect(&sh->tmem_full[buf]);
         }
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t quarter = warp & 3u;
         uint32_t iter = 0;
         bool ok = true;
+        pdk_pdl_wait();  // y and bias may still be in use by the previous kernel
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
             const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
             const uint32_t w0 = (tile % tiles_w) * BM, t0 = (tile / tiles_w) * BN;
@@ -260,14 +276,15 @@ int launch_bn(const void* data, const void* scale_tiled, const void* bias, const
     if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, kbytes, batch, kbytes, BKB, BN)) return rc;
     const size_t smem = (size_t)Cfg<BN>::kStages * Cfg<BN>::kStageBytes + sizeof(Shared) + 1024u;
     auto kern = nvf4_gemm_kernel<BN, TO>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static const cudaError_t attr_rc =  // once per process; one caller thread by the pack's contract
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (attr_rc != cudaSuccess) return (int)attr_rc;
     const uint32_t n_tiles = ((out_dim + BM - 1u) / BM) * ((batch + BN - 1u) / BN);
     uint32_t grid = (uint32_t)pdk_sm_count();
     if (grid > n_tiles) grid = n_tiles;
-    kern<<<grid, kThreads, smem, st>>>(tw, tx, (const uint8_t*)scale_tiled, (const uint8_t*)xs, (const float*)bias,
-                                       (TO*)y, scale2, in_dim, out_dim, batch, pdk_error_word());
-    return pdk_launch_status();
+    return pdk_launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, tw, tx, (const uint8_t*)scale_tiled,
+                          (const uint8_t*)xs, (const float*)bias, (TO*)y, scale2, in_dim, out_dim, batch,
+                          pdk_error_word());
 }
 
 template <typename TO>

@@ -18,6 +18,41 @@ static inline bool pdk_aligned(const void* p, uintptr_t a) { return ((uintptr_t)
 // Number of SMs of the current device, read once per process per device.
 int pdk_sm_count();
 
+// Programmatic dependent launch (the reference chains its decode kernels the
+// same way, packs/cuda/src/abi.cuh:4560-4590): the kernel may start while its
+// predecessor in the stream drains.  Kernels launched through this call
+// griddepcontrol.launch_dependents early and griddepcontrol.wait before they
+// touch anything the predecessor may still read or write.  PDK_NO_PDL=1 (read
+// once) launches them as ordinary kernels.
+#include <cstdlib>
+static inline bool pdk_pdl_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("PDK_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return v;
+}
+template <class... KArgs, class... Args>
+static inline int pdk_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdk_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+    return e == cudaSuccess ? pdk_launch_status() : (int)e;
+}
+__device__ __forceinline__ void pdk_pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdk_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float pdk_warp_sum(float v) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);

@@ -6,6 +6,10 @@ never touch the same bytes), one JSON line per case.
     python -m paddock_b200.kbench --op f8row_gemm --m 4096 --n 17408 --k 5120
     python -m paddock_b200.kbench --op q4k_gemv --m 1
     python -m paddock_b200.kbench --op q8_gemv
+    python -m paddock_b200.kbench --op f8row_gemm --out f32 --pack /path/to/another-pack.so
+
+--pack times any library that exports the kernel-pack ABI (table slots only, so
+--out f32 for the GEMMs); the default is this package's own library.
 """
 import argparse
 import json
@@ -95,9 +99,18 @@ def bench_nvf4(ex, a):
     xq = torch.zeros(m * k // 2, dtype=torch.uint8, device="cuda")
     xs = torch.zeros(m * k // 16, dtype=torch.uint8, device="cuda")
     ex.pack.call("quantize_nvf4", x, xq, xs, m * k, stream=st)
-    y = torch.zeros(m * n, dtype=torch.bfloat16, device="cuda")
-    sec = time_launches(lambda i: ex.pack.call("pdk_nvf4_gemm_bf16", ws[i % nc][0], ws[i % nc][1], None, xq, xs, y,
-                                               1.0, k, n, m, stream=st), a.iters)
+    if a.out == "bf16":
+        y = torch.zeros(m * n, dtype=torch.bfloat16, device="cuda")
+        sec = time_launches(lambda i: ex.pack.call("pdk_nvf4_gemm_bf16", ws[i % nc][0], ws[i % nc][1], None, xq, xs,
+                                                   y, 1.0, k, n, m, stream=st), a.iters)
+    else:
+        # the table slot: f32 output; a scale tiling call first, as the engine does at load time
+        y = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+        rowmajor = torch.randint(0x20, 0x48, (n * k // 16,), dtype=torch.uint8, device="cuda")
+        for w in ws:
+            ex.pack.call("nvf4_tc5_tile_scales", rowmajor, w[1], k, n, stream=st)
+        sec = time_launches(lambda i: ex.pack.call("nvf4_gemm_tc5w", ws[i % nc][0], ws[i % nc][1], None, xq, xs, y,
+                                                   1.0, k, n, m, None, 0, stream=st), a.iters)
     return sec, {"bound": "both", "flops": 2.0 * m * n * k, "bytes": nbytes_w + 4 + m * (k // 2 + k // 16) + m * n * 2}
 
 
@@ -142,15 +155,21 @@ def main():
     ap.add_argument("--k", type=int)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--out", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--pack", default=None, help="path of a kernel-pack library to time instead of this package's")
     a = ap.parse_args()
     dm, dn, dk = DEFAULTS[a.op]
     a.m, a.n, a.k = a.m or dm, a.n or dn, a.k or dk
-    ex = GpuExecutor()
+    if a.pack:
+        from .pack import KernelPack
+        ex = GpuExecutor(KernelPack.load(a.pack))
+    else:
+        ex = GpuExecutor()
     sec, info = OPS[a.op](ex, a)
-    err = ex.pack.device_error()
+    err = ex.pack.device_error() if not a.pack else 0
     hbm, bf16, kind = peaks()
     extra = {k: v for k, v in info.items() if k not in ("bound", "bytes", "flops")}
-    line = {**extra, "op": a.op, "m": a.m, "n": a.n, "k": a.k, "us": sec * 1e6, "device_error": err, "peak_kind": kind}
+    line = {**extra, "op": a.op, "m": a.m, "n": a.n, "k": a.k, "us": sec * 1e6, "device_error": err, "peak_kind": kind,
+            "pack": a.pack or "paddock_b200"}
     if info["bound"] in ("hbm", "both"):
         line.update(gbs=info["bytes"] / sec / 1e9, frac_of_hbm=info["bytes"] / sec / 1e9 / hbm)
     if info["bound"] in ("tensor", "both"):
