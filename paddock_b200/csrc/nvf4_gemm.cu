@@ -9,18 +9,19 @@
 // decode widths the kernel is a pure HBM stream (4.5 bits per weight), at
 // prefill widths it is tensor-bound.
 //
-// Tile: 128 weight rows (the MMA's M, one TMEM lane each) x 128 tokens (N) x
-// 256 K per pipeline stage.  Weights are the A operand so that a decode batch
+// Tile: 128 weight rows (the MMA's M, one TMEM lane each) x 128 tokens (N); K
+// in slabs of 256, two slabs per pipeline stage.  Weights are the A operand so that a decode batch
 // is a single token tile and the epilogue writes, per token, 128 consecutive
 // channels.  One persistent CTA per SM:
 //   warp 0      producer: TMA boxes of W and X (128 rows x 128 bytes, 128-byte
 //               swizzle), one 2 KB bulk copy of the pre-tiled weight scale cells,
 //               and a 32-lane cp.async gather of the activation scale cells into
 //               the same cell order, arriving on the stage barrier asynchronously
-//   warp 1      MMA issuer (converged warp, one elected lane): per stage 8 tcgen05.cp (scale cells -> TMEM) + 4 MMAs
+//   warp 1      MMA issuer (converged warp, one elected lane): per slab 8 tcgen05.cp
+//               (scale cells -> TMEM) + 4 MMAs, one commit per stage
 //   warps 2..5  epilogue: TMEM -> registers -> y (f32 or bf16), * scale2 + bias
 // Accumulators are double buffered (2 x 128 TMEM columns); scale cells take
-// 32 columns per stage.
+// 32 columns per slab.
 #include "tc5.cuh"
 
 namespace {
@@ -30,16 +31,24 @@ constexpr uint32_t BKB = 128;           // bytes of K per stage = 256 e2m1
 constexpr uint32_t kABytes = BM * BKB, kSfBytes = 2048;
 constexpr uint32_t kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kMaxStages = 9;
+constexpr uint32_t kMaxStages = 4;
+// Slabs per pipeline stage.  A stage hand-off (barrier wait, fences, commit) costs the
+// issuing warp about as long as the tensor pipe needs for half a slab, and nothing
+// overlaps it; two slabs per hand-off halve that.
+constexpr uint32_t KS = 2;
 
-// Token tile BN: 128 for prefill widths; 32 for decode widths, where the smaller
-// activation box leaves room for 9 stages (162 KB of weights in flight per SM).
+// Token tile BN: 128 for prefill widths (3 stages of two slabs); 32 or 64 for decode
+// widths, where the smaller activation box leaves room for 4 stages (8 slabs, 144 KB of
+// weights in flight per SM).
 template <uint32_t BN>
 struct Cfg {
-    static constexpr uint32_t kStages = BN == 32u ? 9u : 5u;
+    static constexpr uint32_t kStages = BN == 128u ? 3u : 4u;
     static constexpr uint32_t kBBytes = BN * BKB;
-    static constexpr uint32_t kStageBytes = kABytes + kBBytes + 2u * kSfBytes;
+    // a stage = KS slabs: [W boxes][X boxes][W scale records][X scale records]
+    static constexpr uint32_t kOffB = KS * kABytes, kOffSfa = kOffB + KS * kBBytes, kOffSfb = kOffSfa + KS * kSfBytes;
+    static constexpr uint32_t kStageBytes = kOffSfb + KS * kSfBytes;
     static constexpr uint32_t kSfCol0 = 2u * BN;  // scale cells start after the two accumulators
+    static constexpr uint32_t kSfCols = KS * 32u; // TMEM columns of one stage's scale cells
     // e2m1 x e2m1 (format code 1 in the mxf4 encoding), UE4M3 scales, scale ids 0
     static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
 };
@@ -87,7 +96,8 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                  const float* __restrict__ bias, TO* __restrict__ y, float scale2, uint32_t in_dim, uint32_t out_dim,
                  uint32_t batch, unsigned int* err_word) {
     constexpr uint32_t kStages = Cfg<BN>::kStages, kBBytes = Cfg<BN>::kBBytes, kStageBytes = Cfg<BN>::kStageBytes;
-    constexpr uint32_t kSfCol0 = Cfg<BN>::kSfCol0, kIdesc = Cfg<BN>::kIdesc;
+    constexpr uint32_t kSfCol0 = Cfg<BN>::kSfCol0, kIdesc = Cfg<BN>::kIdesc, kSfCols = Cfg<BN>::kSfCols;
+    constexpr uint32_t kOffB = Cfg<BN>::kOffB, kOffSfa = Cfg<BN>::kOffSfa, kOffSfb = Cfg<BN>::kOffSfb;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * kStageBytes);
@@ -96,6 +106,7 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t tiles_w = (out_dim + BM - 1u) / BM, tiles_t = (batch + BN - 1u) / BN;
     const uint32_t n_tiles = tiles_w * tiles_t;
     const uint32_t num_kb = in_dim >> 8;       // 256-element slabs (in_dim % 256 == 0)
+    const uint32_t num_ks = (num_kb + KS - 1u) / KS;  // stages per tile; the last may hold fewer slabs
     const uint32_t sf_row = in_dim >> 4;       // activation scale bytes per token
 
     if (threadIdx.x == 0) {
@@ -117,9 +128,9 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         tc5::tmem_relinquish();
     }
     // activation scale cells: the gather writes only the rows a token tile has; the rest stay zero
-    for (uint32_t i = threadIdx.x; i < kStages * (kSfBytes / 16u); i += kThreads) {
-        const uint32_t s = i / (kSfBytes / 16u), o = i % (kSfBytes / 16u);
-        reinterpret_cast<uint4*>(tiles + s * kStageBytes + kABytes + kBBytes + kSfBytes)[o] = make_uint4(0u, 0u, 0u, 0u);
+    for (uint32_t i = threadIdx.x; i < kStages * (KS * kSfBytes / 16u); i += kThreads) {
+        const uint32_t s = i / (KS * kSfBytes / 16u), o = i % (KS * kSfBytes / 16u);
+        reinterpret_cast<uint4*>(tiles + s * kStageBytes + kOffSfb)[o] = make_uint4(0u, 0u, 0u, 0u);
     }
     fence_proxy_async_smem();
     tc5::fence_before_sync();
@@ -137,51 +148,77 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // xs[t0 + c*32 + l][kb*16 + 4j .. 4j+3].  Each lane issues its words as 4-byte
         // cp.async copies (zero-filled past the batch) and then an asynchronous arrive on
         // the stage's barrier, so the producer never waits for a load.
-        constexpr uint32_t kSfWords = BN * 4u / 32u;  // words per lane: rows c*32+l with c < BN/32
-        auto gather_sf = [&](uint8_t* sfb, uint64_t* bar, uint32_t t0, uint32_t kb) {
-            const uint32_t dst0 = tc5::smem_u32(sfb);
+        constexpr uint32_t kRowGroups = BN / 32u;  // this lane's rows: t0 + c*32 + lane, c < BN/32
+        const uint8_t* sf_src[kRowGroups];          // row base of the current token tile
+        uint32_t sf_size[kRowGroups];               // 4, or 0 past the batch (zero fill)
+        auto set_sf_rows = [&](uint32_t t0) {
 #pragma unroll
-            for (uint32_t i = 0; i < kSfWords; ++i) {
-                const uint32_t q = i * 32u + lane;           // (j, c, l) with l fastest
-                const uint32_t l = q & 31u, c = (q >> 5) % (BN / 32u), j = q / BN;
-                const uint32_t t = t0 + c * 32u + l;
-                const uint8_t* src = x_sf + (size_t)min(t, batch - 1u) * sf_row + kb * 16u + j * 4u;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst0 + j * 512u + l * 16u + c * 4u),
-                             "l"(src), "r"(t < batch ? 4u : 0u)
-                             : "memory");
+            for (uint32_t c = 0; c < kRowGroups; ++c) {
+                const uint32_t t = t0 + c * 32u + lane;
+                sf_src[c] = x_sf + (size_t)min(t, batch - 1u) * sf_row;
+                sf_size[c] = t < batch ? 4u : 0u;
             }
+        };
+        auto gather_sf = [&](uint8_t* sfb, uint64_t* bar, uint32_t kb0, uint32_t nsl) {
+            const uint32_t dst0 = tc5::smem_u32(sfb) + lane * 16u;
+#pragma unroll
+            for (uint32_t u = 0; u < KS; ++u)
+                if (u < nsl)
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j)
+#pragma unroll
+                        for (uint32_t c = 0; c < kRowGroups; ++c)
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst0 + u * kSfBytes +
+                                                                                            j * 512u + c * 4u),
+                                         "l"(sf_src[c] + (kb0 + u) * 16u + j * 4u), "r"(sf_size[c])
+                                         : "memory");
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(tc5::smem_u32(bar)) : "memory");
         };
-        // weight half of a stage: the expected bytes of the whole stage, the W box and its scale cells
-        auto issue_w = [&](uint32_t stg, uint32_t tile_w, uint32_t kb) {
+        // weight half of a stage: the expected bytes of the whole stage, the W boxes and their
+        // scale records (consecutive slabs' records are contiguous: one bulk copy)
+        auto issue_w = [&](uint32_t stg, uint32_t tile_w, uint32_t ks) {
             uint8_t* a = tiles + stg * kStageBytes;
-            tc5::mbar_arrive_expect_tx_elect(&sh->full[stg], kABytes + kBBytes + kSfBytes);
-            tc5::tma_load_2d_elect(a, &tmap_w, &sh->full[stg], (int32_t)(kb * BKB), (int32_t)(tile_w * BM));
-            tc5::bulk_load_elect(a + kABytes + kBBytes, w_sf_tiled + ((size_t)tile_w * num_kb + kb) * kSfBytes, kSfBytes,
+            const uint32_t kb0 = ks * KS, nsl = min(KS, num_kb - kb0);
+            tc5::mbar_arrive_expect_tx_elect(&sh->full[stg], nsl * (kABytes + kBBytes + kSfBytes));
+#pragma unroll
+            for (uint32_t u = 0; u < KS; ++u)
+                if (u < nsl)
+                    tc5::tma_load_2d_elect(a + u * kABytes, &tmap_w, &sh->full[stg], (int32_t)((kb0 + u) * BKB),
+                                           (int32_t)(tile_w * BM));
+            tc5::bulk_load_elect(a + kOffSfa, w_sf_tiled + ((size_t)tile_w * num_kb + kb0) * kSfBytes, nsl * kSfBytes,
                                  &sh->full[stg]);
         };
         // The weights depend on nothing the previous kernel in the stream writes: the first
         // tile's first stages stream in before the wait for that kernel; activations after it.
         uint32_t pre = 0;
         if (blockIdx.x < n_tiles) {
-            pre = min(num_kb, kStages);
-            for (uint32_t i = 0; i < pre; ++i) issue_w(i, blockIdx.x % tiles_w, i);
+            pre = min(num_ks, kStages);
+            for (uint32_t i = 0; i < pre; ++i) issue_w(i, blockIdx.x / tiles_t, i);
         }
         pdk_pdl_wait();
-        // tiles are walked weight-tile fastest: a wave of CTAs shares one token tile
+        // Tiles are walked token-tile fastest: the CTAs of a wave share a few weight tiles
+        // across all token tiles, so a weight tile streams from DRAM once while the small
+        // activation plane stays in L2.  (Weight-tile fastest re-read the whole weight
+        // plane once per token tile under the output stream's L2 churn.)
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const uint32_t tile_w = tile % tiles_w, t0 = (tile / tiles_w) * BN;
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                const bool early = tile == blockIdx.x && kb < pre;  // first use of the stage, W already issued
+            const uint32_t tile_w = tile / tiles_t, t0 = (tile % tiles_t) * BN;
+            set_sf_rows(t0);
+            for (uint32_t ks = 0; ks < num_ks; ++ks) {
+                const bool early = tile == blockIdx.x && ks < pre;  // first use of the stage, W already issued
                 if (!early) {
                     ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
-                    issue_w(stage, tile_w, kb);
+                    issue_w(stage, tile_w, ks);
                 }
                 uint8_t* a = tiles + stage * kStageBytes;
-                tc5::tma_load_2d_elect(a + kABytes, &tmap_x, &sh->full[stage], (int32_t)(kb * BKB), (int32_t)t0);
-                gather_sf(a + kABytes + kBBytes + kSfBytes, &sh->full[stage], t0, kb);
+                const uint32_t kb0 = ks * KS, nsl = min(KS, num_kb - kb0);
+#pragma unroll
+                for (uint32_t u = 0; u < KS; ++u)
+                    if (u < nsl)
+                        tc5::tma_load_2d_elect(a + kOffB + u * kBBytes, &tmap_x, &sh->full[stage],
+                                               (int32_t)((kb0 + u) * BKB), (int32_t)t0);
+                gather_sf(a + kOffSfb, &sh->full[stage], kb0, nsl);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -199,26 +236,31 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             if (!ok) break;
             tc5::fence_after_sync();
             const uint32_t d_tmem = tmem_base + buf * BN;
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+            for (uint32_t ks = 0; ks < num_ks; ++ks) {
                 ok = tc5::mbar_wait(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc5::fence_after_sync();
                 fence_proxy_async_smem();  // the gathered cells were written through the generic proxy
                 const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
-                const uint32_t sfa_addr = a_addr + kABytes + kBBytes, sfb_addr = sfa_addr + kSfBytes;
-                const uint32_t sfa_t = tmem_base + kSfCol0 + stage * 32u, sfb_t = sfa_t + 16u;
+                const uint32_t nsl = min(KS, num_kb - ks * KS);
 #pragma unroll
-                for (uint32_t j = 0; j < 4u; ++j) {
-                    sf_copy(sfa_t + j * 4u, sfa_addr + j * 512u);
-                    sf_copy(sfb_t + j * 4u, sfb_addr + j * 512u);
+                for (uint32_t u = 0; u < KS; ++u) {
+                    if (u >= nsl) break;
+                    const uint32_t sfa_addr = a_addr + kOffSfa + u * kSfBytes, sfb_addr = a_addr + kOffSfb + u * kSfBytes;
+                    const uint32_t sfa_t = tmem_base + kSfCol0 + stage * kSfCols + u * 32u, sfb_t = sfa_t + 16u;
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j) {
+                        sf_copy(sfa_t + j * 4u, sfa_addr + j * 512u);
+                        sf_copy(sfb_t + j * 4u, sfb_addr + j * 512u);
+                    }
+                    const uint64_t a_desc = tc5::smem_desc_sw128(a_addr + u * kABytes);
+                    const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kOffB + u * kBBytes);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j)  // 64 e2m1 = 32 bytes of K per instruction
+                        mma_nvf4(d_tmem, a_desc + 2u * j, b_desc + 2u * j, kIdesc, sfa_t + j * 4u, sfb_t + j * 4u,
+                                 (ks | u | j) != 0u);
                 }
-                const uint64_t a_desc = tc5::smem_desc_sw128(a_addr);
-                const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes);
-#pragma unroll
-                for (uint32_t j = 0; j < 4u; ++j)  // 64 e2m1 = 32 bytes of K per instruction
-                    mma_nvf4(d_tmem, a_desc + 2u * j, b_desc + 2u * j, kIdesc, sfa_t + j * 4u, sfb_t + j * 4u,
-                             (kb | j) != 0u);
                 tc5::mma_commit_elect(&sh->empty[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
@@ -232,7 +274,7 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         pdk_pdl_wait();  // y and bias may still be in use by the previous kernel
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
             const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
-            const uint32_t w0 = (tile % tiles_w) * BM, t0 = (tile / tiles_w) * BN;
+            const uint32_t w0 = (tile / tiles_t) * BM, t0 = (tile % tiles_t) * BN;
             ok = tc5::mbar_wait(&sh->tmem_full[buf], aphase, ctx, tc5::kErrTmemFullWait, buf);
             if (!ok) break;
             tc5::fence_after_sync();
@@ -296,6 +338,7 @@ int launch(const void* data, const void* scale_tiled, const void* bias, const vo
         !pdk_aligned(y, sizeof(TO)))
         return cudaErrorInvalidValue;
     if (batch <= 32u) return launch_bn<32, TO>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
+    if (batch <= 64u) return launch_bn<64, TO>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
     return launch_bn<128, TO>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
 }
 

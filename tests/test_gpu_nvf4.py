@@ -78,7 +78,7 @@ def test_tile_scales_layout(pack):
     assert np.array_equal(d_t.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (8, 128, 512), (64, 384, 5120), (128, 128, 256), (130, 200, 768),
+@pytest.mark.parametrize("m,n,k", [(1, 128, 256), (8, 128, 512), (64, 384, 5120), (33, 256, 1280), (128, 128, 256), (130, 200, 768),
                                    (512, 1024, 5120)])
 @pytest.mark.parametrize("out", ["f32", "bf16"])
 def test_nvf4_gemm_w4a4(pack, m, n, k, out):
