@@ -85,11 +85,15 @@ __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint6
 template <typename TO>
 __device__ __forceinline__ void store_one(TO* p, float v);
 template <>
-__device__ __forceinline__ void store_one<float>(float* p, float v) { *p = v; }
+__device__ __forceinline__ void store_one<float>(float* p, float v) { __stcs(p, v); }  // streaming: written once
 template <>
-__device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+    __stcs(reinterpret_cast<unsigned short*>(p), __bfloat16_as_ushort(__float2bfloat16_rn(v)));
+}
 
-template <uint32_t BN, typename TO>
+// XT: the activation scales come pre-tiled (the weight scales' record layout, one record
+// per 128 tokens and slab) and are bulk-copied; otherwise they are row-major and gathered.
+template <uint32_t BN, typename TO, bool XT>
 __global__ void __launch_bounds__(kThreads, 1)
 nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  const uint8_t* __restrict__ w_sf_tiled, const uint8_t* __restrict__ x_sf,
@@ -111,7 +115,7 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            tc5::mbar_init(&sh->full[s], 33);  // producer lane 0 (expect_tx) + 32 lanes' cp.async arrivals
+            tc5::mbar_init(&sh->full[s], XT ? 1 : 33);  // expect_tx arrival (+ 32 lanes' cp.async arrivals)
             tc5::mbar_init(&sh->empty[s], 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
@@ -179,7 +183,7 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         auto issue_w = [&](uint32_t stg, uint32_t tile_w, uint32_t ks) {
             uint8_t* a = tiles + stg * kStageBytes;
             const uint32_t kb0 = ks * KS, nsl = min(KS, num_kb - kb0);
-            tc5::mbar_arrive_expect_tx_elect(&sh->full[stg], nsl * (kABytes + kBBytes + kSfBytes));
+            tc5::mbar_arrive_expect_tx_elect(&sh->full[stg], nsl * (kABytes + kBBytes + kSfBytes + (XT ? kSfBytes : 0u)));
 #pragma unroll
             for (uint32_t u = 0; u < KS; ++u)
                 if (u < nsl)
@@ -202,7 +206,7 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // plane once per token tile under the output stream's L2 churn.)
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const uint32_t tile_w = tile / tiles_t, t0 = (tile % tiles_t) * BN;
-            set_sf_rows(t0);
+            if (!XT) set_sf_rows(t0);
             for (uint32_t ks = 0; ks < num_ks; ++ks) {
                 const bool early = tile == blockIdx.x && ks < pre;  // first use of the stage, W already issued
                 if (!early) {
@@ -218,7 +222,11 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     if (u < nsl)
                         tc5::tma_load_2d_elect(a + kOffB + u * kBBytes, &tmap_x, &sh->full[stage],
                                                (int32_t)((kb0 + u) * BKB), (int32_t)t0);
-                gather_sf(a + kOffSfb, &sh->full[stage], kb0, nsl);
+                if (XT)
+                    tc5::bulk_load_elect(a + kOffSfb, x_sf + ((size_t)(tile % tiles_t) * num_kb + kb0) * kSfBytes,
+                                         nsl * kSfBytes, &sh->full[stage]);
+                else
+                    gather_sf(a + kOffSfb, &sh->full[stage], kb0, nsl);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -241,7 +249,7 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc5::fence_after_sync();
-                fence_proxy_async_smem();  // the gathered cells were written through the generic proxy
+                if (!XT) fence_proxy_async_smem();  // the gathered cells were written through the generic proxy
                 const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
                 const uint32_t nsl = min(KS, num_kb - ks * KS);
 #pragma unroll
@@ -308,7 +316,7 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     }
 }
 
-template <uint32_t BN, typename TO>
+template <uint32_t BN, typename TO, bool XT>
 int launch_bn(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs, void* y,
               float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
     CUtensorMap tw, tx;
@@ -317,7 +325,7 @@ int launch_bn(const void* data, const void* scale_tiled, const void* bias, const
         return rc;
     if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, kbytes, batch, kbytes, BKB, BN)) return rc;
     const size_t smem = (size_t)Cfg<BN>::kStages * Cfg<BN>::kStageBytes + sizeof(Shared) + 1024u;
-    auto kern = nvf4_gemm_kernel<BN, TO>;
+    auto kern = nvf4_gemm_kernel<BN, TO, XT>;
     static const cudaError_t attr_rc =  // once per process; one caller thread by the pack's contract
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (attr_rc != cudaSuccess) return (int)attr_rc;
@@ -329,6 +337,30 @@ int launch_bn(const void* data, const void* scale_tiled, const void* bias, const
                           pdk_error_word());
 }
 
+// Scratch for the re-tiled activation scales of prefill-width calls: a 4-byte gather per
+// token row and 64 K-elements cost the L2 as many requests again as the operand boxes, one
+// 2 KB bulk copy per slab does not.  The buffer lives in the library (the pack allocates
+// nothing at run time); one slice per stream, for the first kXsfLanes streams that make
+// such calls - further streams, and calls too large for a slice, use the gather.
+constexpr size_t kXsfSliceBytes = 8u << 20;  // batch * in_dim / 16 bytes, padded to 128 tokens
+constexpr int kXsfLanes = 2;
+__device__ __align__(1024) uint8_t g_xsf_scratch[kXsfLanes][kXsfSliceBytes];
+
+uint8_t* xsf_slice(cudaStream_t st, size_t need) {
+    static uint8_t* base = [] {
+        void* p = nullptr;
+        return cudaGetSymbolAddress(&p, g_xsf_scratch) == cudaSuccess ? (uint8_t*)p : (uint8_t*)nullptr;
+    }();
+    static cudaStream_t owner[kXsfLanes];
+    static int n_owner = 0;
+    if (base == nullptr || need > kXsfSliceBytes) return nullptr;
+    for (int i = 0; i < n_owner; ++i)
+        if (owner[i] == st) return base + (size_t)i * kXsfSliceBytes;
+    if (n_owner == kXsfLanes) return nullptr;
+    owner[n_owner] = st;
+    return base + (size_t)(n_owner++) * kXsfSliceBytes;
+}
+
 template <typename TO>
 int launch(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs, void* y,
            float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
@@ -337,9 +369,16 @@ int launch(const void* data, const void* scale_tiled, const void* bias, const vo
     if (!pdk_aligned(data, 16) || !pdk_aligned(xq, 16) || !pdk_aligned(scale_tiled, 16) || !pdk_aligned(xs, 4) ||
         !pdk_aligned(y, sizeof(TO)))
         return cudaErrorInvalidValue;
-    if (batch <= 32u) return launch_bn<32, TO>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
-    if (batch <= 64u) return launch_bn<64, TO>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
-    return launch_bn<128, TO>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
+    if (batch <= 32u)
+        return launch_bn<32, TO, false>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
+    if (batch <= 64u)
+        return launch_bn<64, TO, false>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
+    const size_t need = (size_t)((batch + 127u) / 128u) * (in_dim >> 8) * kSfBytes;
+    if (uint8_t* xt = xsf_slice(st, need)) {
+        if (int rc = pd_nvf4_tc5_tile_scales(xs, xt, in_dim, batch, st)) return rc;
+        return launch_bn<128, TO, true>(data, scale_tiled, bias, xq, xt, y, scale2, in_dim, out_dim, batch, st);
+    }
+    return launch_bn<128, TO, false>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);
 }
 
 }  // namespace
