@@ -112,63 +112,79 @@ f8row_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     tc5::fence_after_sync();
     const uint32_t tmem_base = sh->tmem_base;
     const tc5::WaitCtx ctx{&sh->abort_flag, err_word};
+    pdk_pdl_launch_dependents();
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const uint32_t m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        // ------------------------------------------------------------ TMA producer (whole warp, one lane issues)
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        // The weights depend on nothing the previous kernel in the stream writes: the first
+        // tile's first stages take their weight box before the wait for that kernel.
+        auto issue_w = [&](uint32_t stg, uint32_t n0, uint32_t kb) {
+            uint8_t* a = tiles + stg * kStageBytes;
+            tc5::mbar_arrive_expect_tx_elect(&sh->full[stg], kStageBytes);
+            tc5::tma_load_2d_elect(a + kABytes, &tmap_w, &sh->full[stg], (int32_t)(kb * BK), (int32_t)n0);
+        };
+        uint32_t pre = 0;
+        if (blockIdx.x < n_tiles) {
+            pre = min(num_kb, kStages);
+            for (uint32_t i = 0; i < pre; ++i) issue_w(i, (blockIdx.x / tiles_m) * BN, i);
+        }
+        pdk_pdl_wait();
+        for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const uint32_t m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                const bool early = tile == blockIdx.x && kb < pre;
+                if (!early) {
                     ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
-                    uint8_t* a = tiles + stage * kStageBytes;
-                    tc5::mbar_arrive_expect_tx(&sh->full[stage], kStageBytes);
-                    tc5::tma_load_2d(a, &tmap_x, &sh->full[stage], (int32_t)(kb * BK), (int32_t)m0);
-                    tc5::tma_load_2d(a + kABytes, &tmap_w, &sh->full[stage], (int32_t)(kb * BK), (int32_t)n0);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    issue_w(stage, n0, kb);
                 }
-            }
-            if (!ok) {
-                // copies already issued still land in this CTA's shared memory: give
-                // them time before the CTA may exit
-                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+                tc5::tma_load_2d_elect(tiles + stage * kStageBytes, &tmap_x, &sh->full[stage], (int32_t)(kb * BK),
+                                       (int32_t)m0);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
+        if (!ok && lane == 0) {
+            // copies already issued still land in this CTA's shared memory: give
+            // them time before the CTA may exit
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = tc5::idesc_f32acc(0u, 0u, BM, BN);
-            uint32_t stage = 0, phase = 0, iter = 0;
-            bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
-                const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
-                ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
+        // ------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+        constexpr uint32_t idesc = tc5::idesc_f32acc(0u, 0u, BM, BN);
+        uint32_t stage = 0, phase = 0, iter = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
+            const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
+            ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc5::fence_after_sync();
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                ok = tc5::mbar_wait(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc5::fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    ok = tc5::mbar_wait(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
-                    if (!ok) break;
-                    tc5::fence_after_sync();
-                    const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
-                    const uint64_t a_desc = tc5::smem_desc_sw128(a_addr);
-                    const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes);
+                const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
+                const uint64_t a_desc = tc5::smem_desc_sw128(a_addr);
+                const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes);
 #pragma unroll
-                    for (uint32_t k = 0; k < BK / 32u; ++k)  // 32 bytes of K per instruction: +2 in 16-byte units
-                        tc5::mma_f8f6f4(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0u);
-                    tc5::mma_commit(&sh->empty[stage]);
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                }
-                if (ok) tc5::mma_commit(&sh->tmem_full[buf]);
+                for (uint32_t k = 0; k < BK / 32u; ++k)  // 32 bytes of K per instruction: +2 in 16-byte units
+                    tc5::mma_f8f6f4_elect(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0u);
+                tc5::mma_commit_elect(&sh->empty[stage]);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
+            if (ok) tc5::mma_commit_elect(&sh->tmem_full[buf]);
         }
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may read
         uint32_t iter = 0;
         bool ok = true;
+        pdk_pdl_wait();  // scales and y may still be in use by the previous kernel
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++iter) {
             const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
             const uint32_t m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
@@ -223,14 +239,14 @@ int launch(const void* data, const void* w_scale, const void* xq, const void* x_
         return rc;
     const size_t smem = (size_t)kStages * kStageBytes + sizeof(Shared) + 1024u;
     auto kern = f8row_gemm_kernel<TO>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static const cudaError_t attr_rc =  // once per process; one caller thread by the pack's contract
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (attr_rc != cudaSuccess) return (int)attr_rc;
     const uint32_t n_tiles = ((batch + BM - 1u) / BM) * ((out_dim + BN - 1u) / BN);
     uint32_t grid = (uint32_t)pdk_sm_count();
     if (grid > n_tiles) grid = n_tiles;
-    kern<<<grid, kThreads, smem, st>>>(tx, tw, (const float*)w_scale, (const float*)x_scale, (TO*)y, in_dim, out_dim,
-                                       batch, pdk_error_word());
-    return pdk_launch_status();
+    return pdk_launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, tx, tw, (const float*)w_scale,
+                          (const float*)x_scale, (TO*)y, in_dim, out_dim, batch, pdk_error_word());
 }
 
 }  // namespace
