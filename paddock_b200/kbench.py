@@ -143,14 +143,63 @@ def bench_moe(ex, a):
     return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
 
 
-OPS = {"moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
-DEFAULTS = {"moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+def bench_moe_ep(ex, a):
+    """Config 5 expert-parallel: run under torchrun, one rank per GPU; experts and tokens split over the ranks."""
+    import torch.distributed as dist
+    from . import moe_ep, planes as P
+    world, rank = dist.get_world_size(), dist.get_rank()
+    n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
+    epr = n_expert // world
+    bm = 8 if T * k <= 1024 else 32
+    blocks = epr * embd * ff // 32
+
+    def plane(seed):
+        g = torch.Generator(device="cuda")
+        g.manual_seed(seed * 64 + rank)
+        return P.RepackedMxfp4(torch.randint(0, 256, (blocks * 16,), dtype=torch.uint8, device="cuda", generator=g),
+                               torch.randint(118, 124, (blocks,), dtype=torch.uint8, device="cuda", generator=g))
+
+    shard = moe_ep.GpuExpertShard(ex, P.MoeMxfp4Planes(plane(1), plane(2), plane(3), epr, embd, ff), T * k, bm)
+    lo, hi = (T * rank) // world, (T * (rank + 1)) // world
+    x = synth.bf16_round(synth.normal(T * embd, 7, 1.0, "cuda")).view(T, embd)[lo:hi].contiguous()
+    n_sets = 6 if T <= 64 else 1
+    logits = [synth.normal(T * n_expert, 100 + i, 1.0, "cuda").view(T, n_expert)[lo:hi].contiguous()
+              for i in range(n_sets)]
+    out = torch.zeros(hi - lo, embd, device="cuda")
+
+    def step(i):
+        moe_ep.gpu_ep_forward(ex, shard, x, logits[i % n_sets], out, n_expert, k)
+
+    for i in range(5):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.iters):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / a.iters * 1e-3], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    per_expert = 3 * embd * ff // 32 * 17
+    distinct = 0
+    for i in range(n_sets):
+        full = synth.normal(T * n_expert, 100 + i, 1.0, "cuda").view(T, n_expert)
+        distinct += torch.unique(torch.topk(full, k, dim=1).indices).numel()
+    distinct /= n_sets
+    return float(t.item()), {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2),
+                             "distinct_experts": distinct, "n_gpus": world}
+
+
+OPS = {"moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True, choices=sorted(OPS))
-    ap.add_argument("--m", type=int)
+    ap.add_argument("--m", "--batch", dest="m", type=int, help="tokens (use --batch under torchrun, whose parser claims --m)")
     ap.add_argument("--n", type=int)
     ap.add_argument("--k", type=int)
     ap.add_argument("--iters", type=int, default=50)
@@ -159,6 +208,11 @@ def main():
     a = ap.parse_args()
     dm, dn, dk = DEFAULTS[a.op]
     a.m, a.n, a.k = a.m or dm, a.n or dn, a.k or dk
+    ep = a.op == "moe_ep"
+    if ep:
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     if a.pack:
         from .pack import KernelPack
         ex = GpuExecutor(KernelPack.load(a.pack))
@@ -175,7 +229,11 @@ def main():
     if info["bound"] in ("tensor", "both"):
         tf = info["flops"] / sec / 1e12
         line.update(tflops=tf, frac_of_2x_bf16=tf / (2 * bf16), frac_of_4x_bf16=tf / (4 * bf16))
-    print(json.dumps(line), flush=True)
+    if not ep or dist.get_rank() == 0:
+        print(json.dumps(line), flush=True)
+    if ep:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

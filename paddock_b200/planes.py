@@ -134,22 +134,34 @@ class MoeWorkspace:
         self.part = torch.empty(pairs * planes.embd, dtype=f32, device=dev)
 
 
+def moe_mxfp4_experts(ex, planes, ws, x, rows, alpha=1.702, limit=7.0):
+    """align -> activation step -> gate|up + SwiGLU -> activation step -> down for `rows` token rows whose
+    expert choices and routing weights are already in ws.idx / ws.w ([rows][ws.n_active]); leaves the
+    weighted per-(row, slot) outputs in ws.part.  Five launches."""
+    st = _stream()
+    c = ex.pack.call
+    k, bm = ws.n_active, ws.bm
+    max_blocks = min(ws.max_blocks, min(rows * k, rows * k // bm + planes.n_expert))
+    c("moe_align_bm", ws.idx, ws.sorted_row, ws.sorted_slot, ws.block_expert, rows, k, planes.n_expert, bm,
+      max_blocks, stream=st)
+    c("pdk_moe_prep_act", x, ws.xq, ws.xscale, planes.embd, rows, stream=st)
+    c("pdk_mxfp4_moe_gate_up", planes.gate.data, planes.gate.scale, planes.gate_bias, planes.up.data,
+      planes.up.scale, planes.up_bias, ws.sorted_row, ws.block_expert, ws.xq, ws.xscale, ws.h, planes.embd,
+      planes.ff, bm, max_blocks, alpha, limit, stream=st)
+    c("pdk_moe_prep_act", ws.h, ws.hq, ws.hscale, planes.ff, max_blocks * bm, stream=st)
+    c("pdk_mxfp4_moe_down", planes.down.data, planes.down.scale, planes.down_bias, ws.sorted_row, ws.sorted_slot,
+      ws.block_expert, ws.w, ws.hq, ws.hscale, ws.part, planes.ff, planes.embd, k, bm, max_blocks, stream=st)
+    return 5
+
+
 def moe_mxfp4_forward(ex, planes, ws, x, router_logits, out, alpha=1.702, limit=7.0, router_bias=None):
     """The MoE block the way crates/paddock-engine/src/gpu_model/gpt_oss.rs:2279-2521 walks it:
     top-k -> align -> activation step -> gate|up + SwiGLU -> activation step -> down -> combine.
     x f32[tokens][embd], router_logits f32[tokens][n_expert], out f32[tokens][embd] (accumulated into)."""
     st = _stream()
     c = ex.pack.call
-    T, k, bm = ws.tokens, ws.n_active, ws.bm
+    T, k = ws.tokens, ws.n_active
     c("moe_topk_batch", router_logits, router_bias, planes.n_expert, k, ws.idx, ws.w, T, stream=st)
-    c("moe_align_bm", ws.idx, ws.sorted_row, ws.sorted_slot, ws.block_expert, T, k, planes.n_expert, bm,
-      ws.max_blocks, stream=st)
-    c("pdk_moe_prep_act", x, ws.xq, ws.xscale, planes.embd, T, stream=st)
-    c("pdk_mxfp4_moe_gate_up", planes.gate.data, planes.gate.scale, planes.gate_bias, planes.up.data,
-      planes.up.scale, planes.up_bias, ws.sorted_row, ws.block_expert, ws.xq, ws.xscale, ws.h, planes.embd,
-      planes.ff, bm, ws.max_blocks, alpha, limit, stream=st)
-    c("pdk_moe_prep_act", ws.h, ws.hq, ws.hscale, planes.ff, ws.max_blocks * bm, stream=st)
-    c("pdk_mxfp4_moe_down", planes.down.data, planes.down.scale, planes.down_bias, ws.sorted_row, ws.sorted_slot,
-      ws.block_expert, ws.w, ws.hq, ws.hscale, ws.part, planes.ff, planes.embd, k, bm, ws.max_blocks, stream=st)
+    moe_mxfp4_experts(ex, planes, ws, x, T, alpha, limit)
     c("moe_slot_combine", ws.part, out, planes.embd, k, T, stream=st)
     return 7  # launches
