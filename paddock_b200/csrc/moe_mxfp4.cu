@@ -302,7 +302,7 @@ moe_mxfp4_kernel(const Args a) {
 }
 
 template <uint32_t NT, uint32_t SLOTS, uint32_t KS, bool GATED>
-int launch_cfg(const Args& a, uint32_t max_blocks, cudaStream_t st) {
+int launch_cfg(const Args& a, uint32_t max_blocks, cudaStream_t st, uint32_t waves = 2u) {
     constexpr uint32_t BM = NT * 8u, NP = GATED ? 2u : 1u;
     const size_t smem = (size_t)BM * (a.in_dim * 2u + 64u) + (KS > 1u ? (size_t)2u * SLOTS * KS * 32u * NP * NT * 4u * 4u : 0u);
     if (smem > 220u * 1024u) return cudaErrorNotSupported;
@@ -310,13 +310,26 @@ int launch_cfg(const Args& a, uint32_t max_blocks, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const uint32_t n_tiles = (a.out_dim + 15u) / 16u;
-    // enough row groups that the used blocks fill the machine about twice
-    uint32_t groups = (2u * (uint32_t)pdk_sm_count() + max_blocks - 1u) / max_blocks;
+    // enough row groups that the used blocks fill the machine about `waves` times
+    uint32_t groups = (waves * (uint32_t)pdk_sm_count() + max_blocks - 1u) / max_blocks;
     const uint32_t max_groups = (n_tiles + SLOTS - 1u) / SLOTS;
     if (groups > max_groups) groups = max_groups;
     if (groups < 1u) groups = 1u;
     kern<<<dim3(groups, max_blocks), SLOTS * KS * 32u, smem, st>>>(a);
     return pdk_launch_status();
+}
+
+// Decode blocks (8 tokens): with few blocks a CTA splits K over four warps per tile so that
+// even one token's four experts fill the machine; with many blocks each warp walks the whole
+// K of its tile - one pipeline fill per tile instead of four, no cross-warp fold.
+bool wide_decode(const Args& a, uint32_t max_blocks) {
+    static const int force = [] {
+        const char* e = getenv("PDK_MOE_DECODE_CFG");
+        return e ? atoi(e) : -1;
+    }();
+    if (force >= 0) return force == 1;
+    const uint32_t n_tiles = (a.out_dim + 15u) / 16u;
+    return max_blocks * ((n_tiles + 15u) / 16u) >= 2u * (uint32_t)pdk_sm_count();
 }
 
 int check_common(const Args& a, uint32_t bm, uint32_t max_blocks) {
@@ -347,7 +360,8 @@ PDK_EXPORT int pdk_mxfp4_moe_gate_up(const void* gate_data, const void* gate_sca
     if (int rc = check_common(a, bm, max_blocks)) return rc;
     if (!pdk_aligned(up_data, 4)) return cudaErrorInvalidValue;
     auto st = (cudaStream_t)stream;
-    if (bm == 8u) return launch_cfg<1, 4, 4, true>(a, max_blocks, st);
+    if (bm == 8u) return wide_decode(a, max_blocks) ? launch_cfg<1, 16, 1, true>(a, max_blocks, st, 4u)
+                                                      : launch_cfg<1, 4, 4, true>(a, max_blocks, st);
     return launch_cfg<4, 16, 1, true>(a, max_blocks, st);
 }
 
@@ -367,6 +381,7 @@ PDK_EXPORT int pdk_mxfp4_moe_down(const void* down_data, const void* down_scale,
     if (max_blocks == 0) return 0;
     if (int rc = check_common(a, bm, max_blocks)) return rc;
     auto st = (cudaStream_t)stream;
-    if (bm == 8u) return launch_cfg<1, 4, 4, false>(a, max_blocks, st);
+    if (bm == 8u) return wide_decode(a, max_blocks) ? launch_cfg<1, 16, 1, false>(a, max_blocks, st, 4u)
+                                                      : launch_cfg<1, 4, 4, false>(a, max_blocks, st);
     return launch_cfg<4, 16, 1, false>(a, max_blocks, st);
 }
