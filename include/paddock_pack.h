@@ -230,6 +230,35 @@ int pdk_mxfp4_moe_down(const void* down_data, const void* down_scale, const void
                        const void* hscale, void* part, uint32_t ff, uint32_t embd, uint32_t n_active, uint32_t bm,
                        uint32_t max_blocks, void* stream);
 
+/* ---- MXFP4 expert GEMMs on the block-scaled tensor-core path (no counterpart in the reference,
+ * whose B200 MoE kernels are mma.sync on int8 activations, packs/cuda/src/moe/mmq.cuh:139-626).
+ * The repacked data plane is used as it is; the E8M0 scale plane is re-expressed once at load time
+ * as tiled UE4M3 scale records plus one power-of-two factor per plane; activations are expanded
+ * into four NVFP4 terms per token. */
+
+/* scale u8[n_expert][rows][in_dim/32] -> tiled u8[n_expert][ceil(rows/128)][ceil(in_dim/256)][2048]
+ * and meta (8 bytes of device memory: u32 largest scale byte, f32 scale2).  in_dim % 64 == 0. */
+int pdk_mxfp4_tc5_tile_scales(const void* scale, void* tiled, void* meta, uint32_t rows, uint32_t in_dim,
+                              uint32_t n_expert, void* stream);
+/* Block positions (pd_moe_align_bm order) -> four NVFP4 term rows each:
+ * mode 0: position p = row sorted_row[p] of x f32[rows][dim];  mode 1: position p =
+ * swiglu_oai(x[p], up[p]) of raw gate / up outputs f32[positions][dim].
+ * Positions of unused blocks (block_expert = PDK_MOE_PAD) and padding positions become zero rows.
+ * xq u8[max_blocks*4*bm][dim/2], xs u8[max_blocks*4*bm][dim/16], xstep f32[max_blocks*bm]. */
+int pdk_moe_prep_act_f4(const void* x, const void* up, const void* sorted_row, const void* block_expert, void* xq,
+                        void* xs, void* xstep, uint32_t dim, uint32_t bm, uint32_t max_blocks, uint32_t mode, float alpha, float limit,
+                        void* stream);
+/* Grouped GEMM of one or two planes (w1_data NULL = one) over the term rows.  scatter 0: out_p
+ * f32[max_blocks*bm][out_dim], block order, bias added, no activation function; scatter 1 (one
+ * plane): out0 = part f32[rows*n_active][out_dim] at row (sorted_row, sorted_slot), times topk_w.
+ * in_dim % 64 == 0, bm = 8 or 32. */
+int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w0_meta, const void* w0_bias, void* out0,
+                           const void* w1_data, const void* w1_sf, const void* w1_meta, const void* w1_bias, void* out1,
+                           const void* xq, const void* xs, const void* xstep, const void* block_expert,
+                           const void* sorted_row, const void* sorted_slot, const void* topk_w, uint32_t in_dim,
+                           uint32_t out_dim, uint32_t n_expert, uint32_t bm, uint32_t max_blocks, uint32_t n_active,
+                           uint32_t scatter, void* stream);
+
 /* No counterpart in the reference.  pdk_mxfp4_moe_down + pd_moe_slot_combine for callers that may
  * not allocate device memory (a serving loop that must stay off the allocator, a plug-in handed
  * pointers by its host, a process with a memory budget fixed at start-up): the per-(token, slot)

@@ -1,0 +1,563 @@
+// moe_tc5.cu - MXFP4 expert GEMMs on the block-scaled tcgen05 path.
+//
+// An MXFP4 plane needs no weight transformation to run on kind::mxf4nvf4:
+//   * the repacked data plane is already 16 packed e2m1 bytes per 32 weights.  The
+//     tensor core reads byte j of a block as the element pair (2j, 2j+1) where ggml
+//     means (j, j+16); a dot product does not care as long as the activations are
+//     packed in the same order, and the whole block shares one scale;
+//   * the E8M0 block scale 2^(s-127) becomes two equal UE4M3 per-16 scales
+//     2^(s - emax + 8) plus one per-plane factor scale2 = 2^(emax - 135), emax being
+//     the largest scale byte of the plane.  Powers of two from 2^-9 to 2^8 are exact in
+//     UE4M3, so every block within 17 binades of the plane's largest is exact; smaller
+//     ones flush to zero (below 2^-17 of the largest weight block).
+// Activations keep more than 4 bits by being expanded into four NVFP4 terms,
+//   x * 2^-e = t0 + t1/16 + t2/256 + t3/4096,  t_k = nvfp4(16^k * residual_k),
+// which sit side by side in the token dimension of one MMA (8 tokens x 4 terms = N 32,
+// 32 tokens x 4 terms = N 128); the epilogue adds the four column groups.  What is
+// left of a 16-element group after four terms is below 1e-3 of the group's largest
+// element.  No weight passes through a register: at decode widths the kernel is a
+// pure stream of 4.25 bits per weight.
+//
+// Launch order of one MoE block (host side in planes.py):
+//   pdk_moe_prep_act_f4 (gather by sorted_row)  ->  pdk_mxfp4_moe_gemm_tc5 (gate and up, raw)
+//   pdk_moe_prep_act_f4 (SwiGLU of gate/up)     ->  pdk_mxfp4_moe_gemm_tc5 (down, scattered to
+//   (token, slot) rows and multiplied by the routing weight)  ->  pd_moe_slot_combine
+#include <cuda_fp8.h>
+
+#include "nvf4_tc5.cuh"
+
+namespace {
+
+using namespace nvf4tc5;
+
+// ---------------------------------------------------------------- weight scale planes
+
+__global__ void mxfp4_emax_kernel(const uint8_t* __restrict__ scale, uint64_t n, uint32_t* __restrict__ meta) {
+    uint32_t m = 0u;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        m = max(m, (uint32_t)scale[i]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if ((threadIdx.x & 31u) == 0u && m) atomicMax(meta, m);
+}
+
+// E8M0 byte relative to the plane's largest -> UE4M3 byte of 2^(s - emax + 8)
+__device__ __forceinline__ uint32_t e8m0_to_ue4m3(uint32_t s, uint32_t emax) {
+    const int k = (int)s - (int)emax + 8;  // <= 8
+    if (k >= -6) return (uint32_t)(k + 7) << 3;
+    if (k >= -9) return 1u << (k + 9);     // subnormals 2^-9, 2^-8, 2^-7
+    return 0u;
+}
+
+// scale u8 [expert][rows][nblk]  ->  tiled [expert][row tile][slab][2048]: for row tile rt
+// (128 rows) and slab kb (256 elements = 8 blocks) four 512-byte cells, one per MMA step j:
+//   byte l*16 + c*4 + b of cell j = ue4m3 of block kb*8 + j*2 + b/2 of row rt*128 + c*32 + l
+// (rows past `rows` and blocks past nblk read as 0).  One thread per 4-byte word.
+__global__ void mxfp4_tile_scales_kernel(const uint8_t* __restrict__ scale, uint32_t* __restrict__ tiled,
+                                         uint32_t rows, uint32_t nblk, uint32_t row_tiles, uint32_t num_kb,
+                                         uint32_t* __restrict__ meta) {
+    const uint32_t emax = meta[0];
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+        reinterpret_cast<float*>(meta)[1] = emax >= 9u ? __uint_as_float((emax - 8u) << 23) : 0.0f;  // 2^(emax - 135)
+    const uint32_t expert = blockIdx.y;
+    const uint32_t words = row_tiles * num_kb * 512u;
+    for (uint32_t w = blockIdx.x * blockDim.x + threadIdx.x; w < words; w += gridDim.x * blockDim.x) {
+        const uint32_t c = w & 3u, l = (w >> 2) & 31u, j = (w >> 7) & 3u, rec = w >> 9;
+        const uint32_t kb = rec % num_kb, rt = rec / num_kb;
+        const uint32_t row = rt * 128u + c * 32u + l;
+        uint32_t out = 0u;
+        if (row < rows) {
+            const uint8_t* srow = scale + ((size_t)expert * rows + row) * nblk;
+#pragma unroll
+            for (uint32_t h = 0; h < 2u; ++h) {
+                const uint32_t blk = kb * 8u + j * 2u + h;
+                if (blk < nblk) out |= (e8m0_to_ue4m3(srow[blk], emax) * 0x0101u) << (16u * h);
+            }
+        }
+        tiled[(size_t)expert * words + w] = out;
+    }
+}
+
+// ---------------------------------------------------------------- activations: four NVFP4 terms
+
+__device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
+    const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+    return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+// RN-even onto {0, .5, 1, 1.5, 2, 3, 4, 6}; returns the code and its value
+__device__ __forceinline__ uint32_t e2m1_rn(float v, float& back) {
+    const float a = fabsf(v);
+    uint32_t m;
+    float b;
+    if (a <= 0.25f) { m = 0u; b = 0.0f; }
+    else if (a < 0.75f) { m = 1u; b = 0.5f; }
+    else if (a <= 1.25f) { m = 2u; b = 1.0f; }
+    else if (a < 1.75f) { m = 3u; b = 1.5f; }
+    else if (a <= 2.5f) { m = 4u; b = 2.0f; }
+    else if (a < 3.5f) { m = 5u; b = 3.0f; }
+    else if (a <= 5.0f) { m = 6u; b = 4.0f; }
+    else { m = 7u; b = 6.0f; }
+    back = v < 0.0f ? -b : b;
+    return (v < 0.0f ? 8u : 0u) | m;
+}
+
+struct PrepArgs {
+    const float* x;              // mode 0: [src rows][dim]; mode 1: gate [positions][dim]
+    const float* up;             // mode 1: up [positions][dim]
+    const uint32_t* sorted_row;  // [positions]; PDK_MOE_PAD = padding (zeros are written)
+    const uint32_t* block_expert;  // [blocks]; PDK_MOE_PAD = unused block (its sorted_row entries are not defined)
+    uint8_t* xq;                 // [blocks][4*bm][dim/2]
+    uint8_t* xs;                 // [blocks][4*bm][dim/16]
+    float* xstep;                // [positions] power of two the row was divided by
+    uint32_t dim, bm, mode;
+    float alpha, limit;
+};
+
+// One CTA per block position.  Position (block b, token i) writes the four term rows
+// b*4*bm + k*bm + i.  A 16-element scale group of the tensor core's element order is the
+// two 8-runs (h*8 .. h*8+7) and (16 + h*8 .. 16 + h*8+7) of a 32-element block.
+__global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
+    const uint32_t pos = blockIdx.x, b = pos / a.bm, i = pos % a.bm;
+    const uint32_t src = a.block_expert[b] == PDK_MOE_PAD ? PDK_MOE_PAD : a.sorted_row[pos];
+    const uint32_t groups = a.dim >> 4, kh = a.dim >> 1;
+    const uint32_t tid = threadIdx.x;
+    __shared__ float s_red[8];
+    const bool pad = src == PDK_MOE_PAD;
+    const float* row = a.mode == 0u ? a.x + (size_t)(pad ? 0u : src) * a.dim : a.x + (size_t)pos * a.dim;
+    const float* urow = a.up + (size_t)pos * a.dim;
+
+    auto load8 = [&](uint32_t off, float (&v)[8]) {
+        const float4 p = *reinterpret_cast<const float4*>(row + off);
+        const float4 q = *reinterpret_cast<const float4*>(row + off + 4u);
+        v[0] = p.x; v[1] = p.y; v[2] = p.z; v[3] = p.w; v[4] = q.x; v[5] = q.y; v[6] = q.z; v[7] = q.w;
+        if (a.mode == 1u) {
+            const float4 r = *reinterpret_cast<const float4*>(urow + off);
+            const float4 t = *reinterpret_cast<const float4*>(urow + off + 4u);
+            const float u[8] = {r.x, r.y, r.z, r.w, t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {  // SwiGLU, OpenAI variant (reference/ops.rs:27-36)
+                const float xg = fminf(v[k], a.limit);
+                const float yu = fminf(fmaxf(u[k], -a.limit), a.limit);
+                v[k] = (xg / (1.0f + __expf(-a.alpha * xg))) * (yu + 1.0f);
+            }
+        }
+    };
+
+    // ---- the row's largest magnitude -> the power of two that brings it into [256, 512)
+    float amax = 0.0f;
+    if (!pad)
+        for (uint32_t g = tid; g < groups; g += blockDim.x) {
+            const uint32_t base = (g >> 1) * 32u + (g & 1u) * 8u;
+            float lo[8], hi[8];
+            load8(base, lo);
+            load8(base + 16u, hi);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fmaxf(fabsf(lo[k]), fabsf(hi[k])));
+        }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((tid & 31u) == 0u) s_red[tid >> 5] = amax;
+    __syncthreads();
+    amax = 0.0f;
+    for (uint32_t w = 0; w < (blockDim.x >> 5); ++w) amax = fmaxf(amax, s_red[w]);
+    // amax = m * 2^ex with m in [1, 2): divide by 2^(ex - 8)
+    const int ex = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;
+    const bool live = !pad && amax > 0.0f && ex > -110 && ex < 120;
+    const float inv_step = live ? __uint_as_float((uint32_t)(127 - (ex - 8)) << 23) : 0.0f;
+    if (tid == 0) a.xstep[pos] = live ? __uint_as_float((uint32_t)(127 + (ex - 8)) << 23) : 0.0f;
+
+    // ---- four terms per 16-element group
+    const size_t r0 = (size_t)b * 4u * a.bm + i;
+    for (uint32_t g = tid; g < groups; g += blockDim.x) {
+        float lo[8], hi[8];
+        if (live) {
+            const uint32_t base = (g >> 1) * 32u + (g & 1u) * 8u;
+            load8(base, lo);
+            load8(base + 16u, hi);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            lo[k] = live ? lo[k] * inv_step : 0.0f;
+            hi[k] = live ? hi[k] * inv_step : 0.0f;
+        }
+#pragma unroll
+        for (uint32_t term = 0; term < 4u; ++term) {
+            float m = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) m = fmaxf(m, fmaxf(fabsf(lo[k]), fabsf(hi[k])));
+            uint32_t sb = 0u;
+            float sc = 0.0f, inv = 0.0f;
+            if (m > 0.0f) {
+                sb = (uint32_t)__nv_cvt_float_to_fp8(m * (1.0f / 6.0f), __NV_SATFINITE, __NV_E4M3);
+                if (sb == 0u) sb = 1u;
+                sc = e4m3_to_f32(sb);
+                inv = 1.0f / sc;
+            }
+            uint32_t w0 = 0u, w1 = 0u;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                float bl, bh;
+                const uint32_t byte = e2m1_rn(lo[k] * inv, bl) | (e2m1_rn(hi[k] * inv, bh) << 4);
+                if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
+                lo[k] = (lo[k] - bl * sc) * 16.0f;
+                hi[k] = (hi[k] - bh * sc) * 16.0f;
+            }
+            const size_t r = r0 + (size_t)term * a.bm;
+            *reinterpret_cast<uint2*>(a.xq + r * kh + (size_t)g * 8u) = make_uint2(w0, w1);
+            a.xs[r * groups + g] = (uint8_t)sb;
+        }
+    }
+}
+
+// ---------------------------------------------------------------- grouped GEMM
+
+struct GemmArgs {
+    const uint8_t* w_sf[2];      // tiled UE4M3 weight scales per plane
+    const float* scale2[2];      // per-plane factor (device memory)
+    const float* bias[2];        // [expert][out_dim] or null
+    float* out[2];               // gate / up: [positions][out_dim]; down: part [(row, slot)][out_dim]
+    const uint8_t* x_sf;         // [blocks*BN][in_dim/16]
+    const float* xstep;          // [positions]
+    const uint32_t* block_expert;
+    const uint32_t* sorted_row;
+    const uint32_t* sorted_slot;  // down only
+    const float* topk_w;          // down only
+    uint32_t in_dim, out_dim, max_blocks, n_planes, n_active, scatter;
+    unsigned int* err_word;
+};
+
+// One tile = (block of BN/4 tokens, plane, 128 weight rows of the block's expert), walked
+// by persistent CTAs.  Roles as in the dense NVFP4 GEMM: warp 0 producer (TMA boxes of W
+// and of the block's term rows, bulk copy of the weight scale records, cp.async gather of
+// the activation scale cells), warp 1 MMA issuer, warps 2..5 epilogue.
+template <uint32_t BN>
+__global__ void __launch_bounds__(kThreads, 1)
+moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_constant__ CUtensorMap tmap_w1,
+                    const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
+    constexpr uint32_t kStages = Cfg<BN>::kStages, kBBytes = Cfg<BN>::kBBytes, kStageBytes = Cfg<BN>::kStageBytes;
+    constexpr uint32_t kSfCol0 = Cfg<BN>::kSfCol0, kIdesc = Cfg<BN>::kIdesc, kSfCols = Cfg<BN>::kSfCols;
+    constexpr uint32_t kOffB = Cfg<BN>::kOffB, kOffSfa = Cfg<BN>::kOffSfa, kOffSfb = Cfg<BN>::kOffSfb;
+    constexpr uint32_t BT = BN / 4u;  // tokens per block
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * kStageBytes);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t row_tiles = (a.out_dim + BM - 1u) / BM, per_block = a.n_planes * row_tiles;
+    const uint32_t n_tiles = a.max_blocks * per_block;
+    const uint32_t n_mma = a.in_dim >> 6;                 // 64-element MMA steps (in_dim % 64 == 0)
+    const uint32_t num_kb = (n_mma + 3u) >> 2;            // 256-element slabs, the last may be partial
+    const uint32_t num_ks = (num_kb + KS - 1u) / KS;
+    const uint32_t sf_row = a.in_dim >> 4;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            tc5::mbar_init(&sh->full[s], 33);
+            tc5::mbar_init(&sh->empty[s], 1);
+        }
+        for (uint32_t b = 0; b < 2; ++b) {
+            tc5::mbar_init(&sh->tmem_full[b], 1);
+            tc5::mbar_init(&sh->tmem_empty[b], 4);
+        }
+        sh->abort_flag = 0;
+        tc5::mbar_fence_init();
+        tc5::tma_prefetch_desc(&tmap_w0);
+        tc5::tma_prefetch_desc(&tmap_w1);
+        tc5::tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == 1) {
+        tc5::tmem_alloc(&sh->tmem_base, kTmemCols);
+        tc5::tmem_relinquish();
+    }
+    // activation scale cells: the gather writes only the rows a block has; the rest stay zero
+    for (uint32_t i = threadIdx.x; i < kStages * (KS * kSfBytes / 16u); i += kThreads) {
+        const uint32_t s = i / (KS * kSfBytes / 16u), o = i % (KS * kSfBytes / 16u);
+        reinterpret_cast<uint4*>(tiles + s * kStageBytes + kOffSfb)[o] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();
+    tc5::fence_before_sync();
+    __syncthreads();
+    tc5::fence_after_sync();
+    const uint32_t tmem_base = sh->tmem_base;
+    const tc5::WaitCtx ctx{&sh->abort_flag, a.err_word};
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (whole warp)
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        constexpr uint32_t kRowGroups = BN / 32u;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const uint32_t blk = tile / per_block, rem = tile % per_block;
+            const uint32_t plane = rem / row_tiles, rt = rem % row_tiles;
+            const uint32_t expert = a.block_expert[blk];
+            if (expert == PDK_MOE_PAD) continue;
+            const CUtensorMap* tw = plane ? &tmap_w1 : &tmap_w0;
+            const uint8_t* wsf = a.w_sf[plane] + ((size_t)expert * row_tiles + rt) * num_kb * kSfBytes;
+            const uint8_t* sf_src[kRowGroups];
+#pragma unroll
+            for (uint32_t c = 0; c < kRowGroups; ++c)
+                sf_src[c] = a.x_sf + ((size_t)blk * BN + c * 32u + lane) * sf_row;
+            for (uint32_t ks = 0; ks < num_ks; ++ks) {
+                ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                uint8_t* st = tiles + stage * kStageBytes;
+                const uint32_t kb0 = ks * KS, nsl = min(KS, num_kb - kb0);
+                tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], nsl * (kABytes + kBBytes + kSfBytes));
+#pragma unroll
+                for (uint32_t u = 0; u < KS; ++u)
+                    if (u < nsl) {
+                        tc5::tma_load_2d_elect(st + u * kABytes, tw, &sh->full[stage], (int32_t)((kb0 + u) * BKB),
+                                               (int32_t)(expert * a.out_dim + rt * BM));
+                        tc5::tma_load_2d_elect(st + kOffB + u * kBBytes, &tmap_x, &sh->full[stage],
+                                               (int32_t)((kb0 + u) * BKB), (int32_t)(blk * BN));
+                    }
+                tc5::bulk_load_elect(st + kOffSfa, wsf + (size_t)kb0 * kSfBytes, nsl * kSfBytes, &sh->full[stage]);
+                const uint32_t dst0 = tc5::smem_u32(st + kOffSfb) + lane * 16u;
+#pragma unroll
+                for (uint32_t u = 0; u < KS; ++u)
+                    if (u < nsl)
+#pragma unroll
+                        for (uint32_t j = 0; j < 4u; ++j) {
+                            const uint32_t off = (kb0 + u) * 16u + j * 4u;  // scale bytes of MMA step j
+                            const uint32_t size = off < sf_row ? 4u : 0u;   // past K: zero cells
+#pragma unroll
+                            for (uint32_t c = 0; c < kRowGroups; ++c)
+                                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(
+                                                 dst0 + u * kSfBytes + j * 512u + c * 4u),
+                                             "l"(sf_src[c] + (size ? off : 0u)), "r"(size)
+                                             : "memory");
+                        }
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(
+                                 tc5::smem_u32(&sh->full[stage]))
+                             : "memory");
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok && lane == 0) {
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+        uint32_t stage = 0, phase = 0, iter = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            if (a.block_expert[tile / per_block] == PDK_MOE_PAD) continue;
+            const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
+            ++iter;
+            ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc5::fence_after_sync();
+            const uint32_t d_tmem = tmem_base + buf * BN;
+            for (uint32_t ks = 0; ks < num_ks; ++ks) {
+                ok = tc5::mbar_wait(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc5::fence_after_sync();
+                fence_proxy_async_smem();  // the gathered cells were written through the generic proxy
+                const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
+                const uint32_t nsl = min(KS, num_kb - ks * KS);
+#pragma unroll
+                for (uint32_t u = 0; u < KS; ++u) {
+                    if (u >= nsl) break;
+                    const uint32_t kb = ks * KS + u, steps = min(4u, n_mma - kb * 4u);
+                    const uint32_t sfa_addr = a_addr + kOffSfa + u * kSfBytes, sfb_addr = a_addr + kOffSfb + u * kSfBytes;
+                    const uint32_t sfa_t = tmem_base + kSfCol0 + stage * kSfCols + u * 32u, sfb_t = sfa_t + 16u;
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j)
+                        if (j < steps) {
+                            sf_copy(sfa_t + j * 4u, sfa_addr + j * 512u);
+                            sf_copy(sfb_t + j * 4u, sfb_addr + j * 512u);
+                        }
+                    const uint64_t a_desc = tc5::smem_desc_sw128(a_addr + u * kABytes);
+                    const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kOffB + u * kBBytes);
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j)
+                        if (j < steps)
+                            mma_nvf4(d_tmem, a_desc + 2u * j, b_desc + 2u * j, kIdesc, sfa_t + j * 4u, sfb_t + j * 4u,
+                                     (ks | u | j) != 0u);
+                }
+                tc5::mma_commit_elect(&sh->empty[stage]);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) tc5::mma_commit_elect(&sh->tmem_full[buf]);
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t quarter = warp & 3u;
+        uint32_t iter = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const uint32_t blk = tile / per_block, rem = tile % per_block;
+            const uint32_t plane = rem / row_tiles, rt = rem % row_tiles;
+            const uint32_t expert = a.block_expert[blk];
+            if (expert == PDK_MOE_PAD) continue;
+            const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
+            ++iter;
+            ok = tc5::mbar_wait(&sh->tmem_full[buf], aphase, ctx, tc5::kErrTmemFullWait, buf);
+            if (!ok) break;
+            tc5::fence_after_sync();
+            // lane = weight row; columns = term * BT + token
+            float v[BT];
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * BN;
+            if (BN == 32u) {
+                uint32_t r[32];
+                tc5::tmem_ld_32x32(taddr, r);
+                tc5::tmem_ld_wait();
+#pragma unroll
+                for (uint32_t i = 0; i < BT; ++i)
+                    v[i] = __uint_as_float(r[i]) + __uint_as_float(r[BT + i]) * 0.0625f +
+                           __uint_as_float(r[2u * BT + i]) * 0.00390625f +
+                           __uint_as_float(r[3u * BT + i]) * 0.000244140625f;
+            } else {
+                float c = 1.0f;
+#pragma unroll
+                for (uint32_t term = 0; term < 4u; ++term) {
+                    uint32_t r[32];
+                    tc5::tmem_ld_32x32(taddr + term * 32u, r);
+                    tc5::tmem_ld_wait();
+#pragma unroll
+                    for (uint32_t i = 0; i < 32u; ++i)
+                        if (i < BT) v[i] = term == 0u ? __uint_as_float(r[i]) : fmaf(__uint_as_float(r[i]), c, v[i]);
+                    c *= 0.0625f;
+                }
+            }
+            tc5::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive(&sh->tmem_empty[buf]);  // the accumulator is in registers now
+
+            const uint32_t n = rt * BM + quarter * 32u + lane;
+            if (n < a.out_dim) {
+                const float s2 = *a.scale2[plane];
+                const float bias = a.bias[plane] ? a.bias[plane][(size_t)expert * a.out_dim + n] : 0.0f;
+                float* out = a.out[plane];
+#pragma unroll
+                for (uint32_t i = 0; i < BT; ++i) {
+                    const uint32_t pos = blk * BT + i;
+                    const uint32_t src = a.sorted_row[pos];
+                    if (src == PDK_MOE_PAD) continue;
+                    const float y = fmaf(v[i] * s2, a.xstep[pos], bias);
+                    if (a.scatter) {
+                        const uint32_t pair = src * a.n_active + a.sorted_slot[pos];
+                        out[(size_t)pair * a.out_dim + n] = a.topk_w[pair] * y;
+                    } else {
+                        out[(size_t)pos * a.out_dim + n] = y;
+                    }
+                }
+            }
+        }
+    }
+
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc5::fence_after_sync();
+        tc5::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <uint32_t BN>
+int launch_gemm(const CUtensorMap& tw0, const CUtensorMap& tw1, const CUtensorMap& tx, const GemmArgs& a,
+                cudaStream_t st) {
+    const size_t smem = (size_t)Cfg<BN>::kStages * Cfg<BN>::kStageBytes + sizeof(Shared) + 1024u;
+    auto kern = moe_tc5_gemm_kernel<BN>;
+    static const cudaError_t attr_rc =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (attr_rc != cudaSuccess) return (int)attr_rc;
+    const uint32_t n_tiles = a.max_blocks * a.n_planes * ((a.out_dim + BM - 1u) / BM);
+    uint32_t grid = (uint32_t)pdk_sm_count();
+    if (grid > n_tiles) grid = n_tiles;
+    kern<<<grid, kThreads, smem, st>>>(tw0, tw1, tx, a);
+    return pdk_launch_status();
+}
+
+}  // namespace
+
+// No counterpart in the reference (its B200 MoE kernels run mma.sync on int8 activations):
+// E8M0 scale plane [n_expert][rows][in_dim/32] -> tiled UE4M3 scale records
+// [n_expert][ceil(rows/128)][ceil(in_dim/256)][2048] for pdk_mxfp4_moe_gemm_tc5, plus
+// meta = {u32 largest scale byte, f32 scale2 = 2^(largest - 135)} (8 bytes, device memory).
+// Load-time call; three launches on `stream`.
+PDK_EXPORT int pdk_mxfp4_tc5_tile_scales(const void* scale, void* tiled, void* meta, uint32_t rows, uint32_t in_dim,
+                                         uint32_t n_expert, void* stream) {
+    if (rows == 0 || n_expert == 0) return 0;
+    if (in_dim == 0 || (in_dim & 63u) != 0u || !pdk_aligned(tiled, 16) || !pdk_aligned(meta, 8))
+        return cudaErrorInvalidValue;
+    auto st = (cudaStream_t)stream;
+    const uint32_t nblk = in_dim >> 5, row_tiles = (rows + 127u) / 128u, num_kb = (in_dim + 255u) >> 8;
+    cudaError_t e = cudaMemsetAsync(meta, 0, 8, st);
+    if (e != cudaSuccess) return (int)e;
+    const uint64_t n = (uint64_t)n_expert * rows * nblk;
+    const uint64_t want = (n + 1023u) / 1024u;
+    mxfp4_emax_kernel<<<(uint32_t)(want < 1184u ? want : 1184u), 256, 0, st>>>((const uint8_t*)scale, n, (uint32_t*)meta);
+    const uint32_t words = row_tiles * num_kb * 512u;
+    mxfp4_tile_scales_kernel<<<dim3((words + 255u) / 256u < 64u ? (words + 255u) / 256u : 64u, n_expert), 256, 0, st>>>(
+        (const uint8_t*)scale, (uint32_t*)tiled, rows, nblk, row_tiles, num_kb, (uint32_t*)meta);
+    return pdk_launch_status();
+}
+
+// No counterpart in the reference: block positions -> four NVFP4 term rows each.
+//   mode 0: position p takes row sorted_row[p] of x f32 [rows][dim]            (`up` unused)
+//   mode 1: position p takes swiglu(x[p], up[p]) of the raw gate / up outputs f32 [positions][dim]
+// Writes xq u8 [max_blocks*4*bm][dim/2], xs u8 [max_blocks*4*bm][dim/16], xstep f32 [max_blocks*bm].
+// dim % 32 == 0, bm 8 or 32.
+PDK_EXPORT int pdk_moe_prep_act_f4(const void* x, const void* up, const void* sorted_row, const void* block_expert,
+                                   void* xq, void* xs, void* xstep, uint32_t dim, uint32_t bm, uint32_t max_blocks, uint32_t mode,
+                                   float alpha, float limit, void* stream) {
+    if (max_blocks == 0) return 0;
+    if (dim == 0 || (dim & 31u) != 0u || (bm != 8u && bm != 32u) || mode > 1u) return cudaErrorInvalidValue;
+    if (!pdk_aligned(x, 16) || !pdk_aligned(xq, 16) || (mode == 1u && !pdk_aligned(up, 16))) return cudaErrorInvalidValue;
+    PrepArgs a{};
+    a.x = (const float*)x; a.up = (const float*)up; a.sorted_row = (const uint32_t*)sorted_row;
+    a.block_expert = (const uint32_t*)block_expert;
+    a.xq = (uint8_t*)xq; a.xs = (uint8_t*)xs; a.xstep = (float*)xstep;
+    a.dim = dim; a.bm = bm; a.mode = mode; a.alpha = alpha; a.limit = limit;
+    moe_prep_f4_kernel<<<max_blocks * bm, 256, 0, (cudaStream_t)stream>>>(a);
+    return pdk_launch_status();
+}
+
+// No counterpart in the reference (slots 88 / 89 are its mma.sync kernels on int8 activations):
+// grouped expert GEMM over blocks aligned with block size bm.  Plane p (w*_data repacked MXFP4
+// data [n_expert][out_dim][in_dim/2], w*_sf / w*_meta from pdk_mxfp4_tc5_tile_scales, bias
+// [n_expert][out_dim] or NULL) times the term rows of pdk_moe_prep_act_f4.
+//   scatter 0: out_p f32 [max_blocks*bm][out_dim] in block order, raw (bias added); one or two planes
+//              (w1_data NULL = one)
+//   scatter 1: out0 = part f32 [rows*n_active][out_dim], row (sorted_row, sorted_slot), times topk_w
+// in_dim % 64 == 0.
+PDK_EXPORT int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w0_meta, const void* w0_bias,
+                                      void* out0, const void* w1_data, const void* w1_sf, const void* w1_meta,
+                                      const void* w1_bias, void* out1, const void* xq, const void* xs,
+                                      const void* xstep, const void* block_expert, const void* sorted_row,
+                                      const void* sorted_slot, const void* topk_w, uint32_t in_dim, uint32_t out_dim,
+                                      uint32_t n_expert, uint32_t bm, uint32_t max_blocks, uint32_t n_active,
+                                      uint32_t scatter, void* stream) {
+    if (max_blocks == 0 || out_dim == 0 || n_expert == 0) return 0;
+    if (in_dim == 0 || (in_dim & 63u) != 0u || (bm != 8u && bm != 32u)) return cudaErrorInvalidValue;
+    if (!pdk_aligned(w0_data, 16) || !pdk_aligned(w0_sf, 16) || !pdk_aligned(xq, 16) || !pdk_aligned(xs, 4) ||
+        !pdk_aligned(w0_meta, 8) || (w1_data && (!pdk_aligned(w1_data, 16) || !pdk_aligned(w1_sf, 16))))
+        return cudaErrorInvalidValue;
+    if (scatter && (w1_data || !sorted_slot || !topk_w)) return cudaErrorInvalidValue;
+    const uint32_t bn = 4u * bm, kbytes = in_dim >> 1;
+    CUtensorMap tw0, tw1, tx;
+    const uint64_t wrows = (uint64_t)n_expert * out_dim;
+    if (int rc = pdk_make_tmap_2d(&tw0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w0_data, kbytes, wrows, kbytes, BKB, BM)) return rc;
+    if (int rc = pdk_make_tmap_2d(&tw1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w1_data ? w1_data : w0_data, kbytes, wrows,
+                                  kbytes, BKB, BM))
+        return rc;
+    if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, kbytes, (uint64_t)max_blocks * bn, kbytes,
+                                  BKB, bn))
+        return rc;
+    GemmArgs a{};
+    a.w_sf[0] = (const uint8_t*)w0_sf; a.w_sf[1] = (const uint8_t*)(w1_data ? w1_sf : w0_sf);
+    a.scale2[0] = (const float*)w0_meta + 1; a.scale2[1] = (const float*)(w1_data ? w1_meta : w0_meta) + 1;
+    a.bias[0] = (const float*)w0_bias; a.bias[1] = (const float*)w1_bias;
+    a.out[0] = (float*)out0; a.out[1] = (float*)out1;
+    a.x_sf = (const uint8_t*)xs; a.xstep = (const float*)xstep;
+    a.block_expert = (const uint32_t*)block_expert; a.sorted_row = (const uint32_t*)sorted_row;
+    a.sorted_slot = (const uint32_t*)sorted_slot; a.topk_w = (const float*)topk_w;
+    a.in_dim = in_dim; a.out_dim = out_dim; a.max_blocks = max_blocks; a.n_planes = w1_data ? 2u : 1u;
+    a.n_active = n_active; a.scatter = scatter; a.err_word = pdk_error_word();
+    auto st = (cudaStream_t)stream;
+    return bm == 8u ? launch_gemm<32>(tw0, tw1, tx, a, st) : launch_gemm<128>(tw0, tw1, tx, a, st);
+}

@@ -129,6 +129,8 @@ def bench_moe(ex, a):
         return P.RepackedMxfp4(data, scale)
 
     planes = P.MoeMxfp4Planes(plane(1), plane(2), plane(3), n_expert, embd, ff)
+    if a.moe_path == "tc5":
+        P.prepare_tc5(ex, planes)
     x = synth.bf16_round(synth.normal(T * embd, 7, 1.0, "cuda"))
     ws = P.MoeWorkspace(ex, planes, T, k, bm)
     out = torch.zeros(T * embd, dtype=torch.float32, device="cuda")
@@ -204,6 +206,8 @@ def main():
     ap.add_argument("--k", type=int)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--out", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--moe-path", default="tc5", choices=["tc5", "mma"],
+                    help="expert GEMMs: block-scaled tcgen05 (default) or the mma.sync kernels")
     ap.add_argument("--pack", default=None, help="path of a kernel-pack library to time instead of this package's")
     a = ap.parse_args()
     dm, dn, dk = DEFAULTS[a.op]

@@ -112,6 +112,9 @@ _EXTRA_SIGS = {
     "pdk_mxfp4_moe_gate_up": "pppppppppppuuuuff",
     "pdk_mxfp4_moe_down": "ppppppppppuuuuu",
     "pdk_mxfp4_moe_down_combine_static": "ppppppppppuuuuuu",
+    "pdk_mxfp4_tc5_tile_scales": "pppuuu",
+    "pdk_moe_prep_act_f4": "pppppppuuuuff",
+    "pdk_mxfp4_moe_gemm_tc5": "p" * 17 + "u" * 7,
 }
 _KIND = {"p": C.c_void_p, "u": C.c_uint32, "U": C.c_uint64, "f": C.c_float}
 

@@ -101,6 +101,25 @@ class MoeMxfp4Planes:
     gate_bias: torch.Tensor = None
     up_bias: torch.Tensor = None
     down_bias: torch.Tensor = None
+    tc5: dict = None  # per plane name: (tiled UE4M3 scale records, meta) from prepare_tc5()
+
+
+def prepare_tc5(ex, planes):
+    """Load-time step of the tensor-core expert path: tile each plane's E8M0 scales into UE4M3
+    scale records (pdk_mxfp4_tc5_tile_scales).  Costs 1/8 of the scale plane's bytes again."""
+    if planes.tc5 is not None:
+        return planes
+    out = {}
+    for name, rows, k in (("gate", planes.ff, planes.embd), ("up", planes.ff, planes.embd),
+                          ("down", planes.embd, planes.ff)):
+        n_bytes = planes.n_expert * ((rows + 127) // 128) * ((k + 255) // 256) * 2048
+        tiled = torch.empty(n_bytes, dtype=torch.uint8, device=ex.device)
+        meta = torch.zeros(2, dtype=torch.int32, device=ex.device)
+        ex.pack.call("pdk_mxfp4_tc5_tile_scales", getattr(planes, name).scale, tiled, meta, rows, k, planes.n_expert,
+                     stream=_stream())
+        out[name] = (tiled, meta)
+    planes.tc5 = out
+    return planes
 
 
 def repack_mxfp4(ex, raw_dev):
@@ -132,6 +151,15 @@ class MoeWorkspace:
         self.hq = torch.empty(nb * planes.ff * 2, dtype=torch.uint8, device=dev)
         self.hscale = torch.empty(nb, dtype=f32, device=dev)
         self.part = torch.empty(pairs * planes.embd, dtype=f32, device=dev)
+        # tensor-core path: four NVFP4 term rows per block position, raw gate / up outputs
+        self.x4q = torch.empty(nb * 4 * planes.embd // 2, dtype=torch.uint8, device=dev)
+        self.x4s = torch.empty(nb * 4 * planes.embd // 16, dtype=torch.uint8, device=dev)
+        self.x4step = torch.empty(nb, dtype=f32, device=dev)
+        self.h4q = torch.empty(nb * 4 * planes.ff // 2, dtype=torch.uint8, device=dev)
+        self.h4s = torch.empty(nb * 4 * planes.ff // 16, dtype=torch.uint8, device=dev)
+        self.h4step = torch.empty(nb, dtype=f32, device=dev)
+        self.g_raw = torch.empty(nb * planes.ff, dtype=f32, device=dev)
+        self.u_raw = torch.empty(nb * planes.ff, dtype=f32, device=dev)
 
 
 def moe_mxfp4_experts(ex, planes, ws, x, rows, alpha=1.702, limit=7.0):
@@ -154,6 +182,30 @@ def moe_mxfp4_experts(ex, planes, ws, x, rows, alpha=1.702, limit=7.0):
     return 5
 
 
+def moe_mxfp4_experts_tc5(ex, planes, ws, x, rows, alpha=1.702, limit=7.0):
+    """moe_mxfp4_experts on the block-scaled tensor-core path (planes prepared with prepare_tc5):
+    align -> term rows of x -> gate and up GEMM -> SwiGLU + term rows of h -> down GEMM scattered
+    into ws.part.  Five launches."""
+    st = _stream()
+    c = ex.pack.call
+    k, bm, t = ws.n_active, ws.bm, planes.tc5
+    max_blocks = min(ws.max_blocks, min(rows * k, rows * k // bm + planes.n_expert))
+    c("moe_align_bm", ws.idx, ws.sorted_row, ws.sorted_slot, ws.block_expert, rows, k, planes.n_expert, bm,
+      max_blocks, stream=st)
+    c("pdk_moe_prep_act_f4", x, None, ws.sorted_row, ws.block_expert, ws.x4q, ws.x4s, ws.x4step, planes.embd, bm, max_blocks, 0,
+      alpha, limit, stream=st)
+    c("pdk_mxfp4_moe_gemm_tc5", planes.gate.data, t["gate"][0], t["gate"][1], planes.gate_bias, ws.g_raw,
+      planes.up.data, t["up"][0], t["up"][1], planes.up_bias, ws.u_raw, ws.x4q, ws.x4s, ws.x4step,
+      ws.block_expert, ws.sorted_row, None, None, planes.embd, planes.ff, planes.n_expert, bm, max_blocks, k, 0,
+      stream=st)
+    c("pdk_moe_prep_act_f4", ws.g_raw, ws.u_raw, ws.sorted_row, ws.block_expert, ws.h4q, ws.h4s, ws.h4step, planes.ff, bm,
+      max_blocks, 1, alpha, limit, stream=st)
+    c("pdk_mxfp4_moe_gemm_tc5", planes.down.data, t["down"][0], t["down"][1], planes.down_bias, ws.part,
+      None, None, None, None, None, ws.h4q, ws.h4s, ws.h4step, ws.block_expert, ws.sorted_row, ws.sorted_slot,
+      ws.w, planes.ff, planes.embd, planes.n_expert, bm, max_blocks, k, 1, stream=st)
+    return 5
+
+
 def moe_mxfp4_forward(ex, planes, ws, x, router_logits, out, alpha=1.702, limit=7.0, router_bias=None):
     """The MoE block the way crates/paddock-engine/src/gpu_model/gpt_oss.rs:2279-2521 walks it:
     top-k -> align -> activation step -> gate|up + SwiGLU -> activation step -> down -> combine.
@@ -162,6 +214,9 @@ def moe_mxfp4_forward(ex, planes, ws, x, router_logits, out, alpha=1.702, limit=
     c = ex.pack.call
     T, k = ws.tokens, ws.n_active
     c("moe_topk_batch", router_logits, router_bias, planes.n_expert, k, ws.idx, ws.w, T, stream=st)
-    moe_mxfp4_experts(ex, planes, ws, x, T, alpha, limit)
+    if planes.tc5 is not None:
+        moe_mxfp4_experts_tc5(ex, planes, ws, x, T, alpha, limit)
+    else:
+        moe_mxfp4_experts(ex, planes, ws, x, T, alpha, limit)
     c("moe_slot_combine", ws.part, out, planes.embd, k, T, stream=st)
     return 7  # launches

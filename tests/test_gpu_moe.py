@@ -100,6 +100,37 @@ def test_moe_block_matches_oracle(pack, tokens, n_expert, k, embd, ff, bm, with_
     assert np.max(np.abs(y - ref)) < 1e-2 * np.max(np.abs(ref))
 
 
+@pytest.mark.parametrize("tokens,n_expert,k,embd,ff,bm,with_bias", [
+    (9, 8, 2, 128, 192, 8, True),
+    (40, 8, 4, 128, 64, 32, True),
+    (70, 4, 2, 256, 256, 32, False),
+    (3, 16, 4, 2880, 2880, 8, True),      # config 5 geometry: K = 11 slabs + a quarter
+    (48, 16, 4, 2880, 2880, 32, False),
+])
+def test_moe_block_tensor_core_path_matches_oracle(pack, tokens, n_expert, k, embd, ff, bm, with_bias):
+    """The same block through the block-scaled tcgen05 expert GEMMs (four NVFP4 activation terms)."""
+    ex = P.GpuExecutor(pack)
+    raw, bias = make_layer(n_expert, embd, ff, 900 + tokens + ff, with_bias)
+    planes = P.MoeMxfp4Planes(P.repack_mxfp4(ex, dev(raw["gate"])), P.repack_mxfp4(ex, dev(raw["up"])),
+                              P.repack_mxfp4(ex, dev(raw["down"])), n_expert, embd, ff,
+                              *(dev_f32(bias[n]) if with_bias else None for n in ("gate", "up", "down")))
+    P.prepare_tc5(ex, planes)
+    x = oracle.bf16_round(oracle.fill_normal(tokens * embd, 910, 1.0))
+    logits = oracle.fill_normal(tokens * n_expert, 911, 1.0)
+    ws = P.MoeWorkspace(ex, planes, tokens, k, bm)
+    out = torch.zeros(tokens * embd, dtype=torch.float32, device="cuda")
+    P.moe_mxfp4_forward(ex, planes, ws, dev_f32(x), dev_f32(logits), out)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    idx, w = oracle.moe_topk(logits, n_expert, k)
+    ref = oracle.moe_mxfp4_layer(raw["gate"], raw["up"], raw["down"], x, idx, w, tokens, k, embd, ff,
+                                 bias.get("gate"), bias.get("up"), bias.get("down"))
+    y = out.cpu().numpy().reshape(tokens, embd)
+    assert np.isfinite(y).all()
+    assert rel_l2(y, ref) < 2e-3 < TOL
+    assert np.max(np.abs(y - ref)) < 1e-2 * np.max(np.abs(ref))
+
+
 def test_slot_combine_fixed_order(pack):
     rows, k, embd = 7, 4, 64
     part = oracle.fill_normal(rows * k * embd, 820, 1.0)
