@@ -244,7 +244,8 @@ int pdk_mxfp4_tc5_tile_scales(const void* scale, void* tiled, void* meta, uint32
  * mode 0: position p = row sorted_row[p] of x f32[rows][dim];  mode 1: position p =
  * swiglu_oai(x[p], up[p]) of raw gate / up outputs f32[positions][dim].
  * Positions of unused blocks (block_expert = PDK_MOE_PAD) and padding positions become zero rows.
- * xq u8[max_blocks*4*bm][dim/2], xs u8[max_blocks*4*bm][dim/16], xstep f32[max_blocks*bm]. */
+ * xq u8[max_blocks*4*bm][dim/2], xs u8[max_blocks][ceil(dim/256)][2048] (scale records, the layout
+ * of the tiled weight scales; zero the buffer once), xstep f32[max_blocks*bm]. */
 int pdk_moe_prep_act_f4(const void* x, const void* up, const void* sorted_row, const void* block_expert, void* xq,
                         void* xs, void* xstep, uint32_t dim, uint32_t bm, uint32_t max_blocks, uint32_t mode, float alpha, float limit,
                         void* stream);

@@ -84,21 +84,19 @@ __device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
     const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
     return __half2float(*reinterpret_cast<const __half*>(&h));
 }
-// RN-even onto {0, .5, 1, 1.5, 2, 3, 4, 6}; returns the code and its value
-__device__ __forceinline__ uint32_t e2m1_rn(float v, float& back) {
-    const float a = fabsf(v);
-    uint32_t m;
-    float b;
-    if (a <= 0.25f) { m = 0u; b = 0.0f; }
-    else if (a < 0.75f) { m = 1u; b = 0.5f; }
-    else if (a <= 1.25f) { m = 2u; b = 1.0f; }
-    else if (a < 1.75f) { m = 3u; b = 1.5f; }
-    else if (a <= 2.5f) { m = 4u; b = 2.0f; }
-    else if (a < 3.5f) { m = 5u; b = 3.0f; }
-    else if (a <= 5.0f) { m = 6u; b = 4.0f; }
-    else { m = 7u; b = 6.0f; }
-    back = v < 0.0f ? -b : b;
-    return (v < 0.0f ? 8u : 0u) | m;
+// Two f32 -> one byte of two e2m1 codes (RN-even, saturating; low nibble = lo), and the
+// byte's two values back as f32.
+__device__ __forceinline__ uint32_t e2m1x2_rn(float lo, float hi, float& back_lo, float& back_hi) {
+    uint16_t byte;
+    asm("{\n\t.reg .b8 q;\n\tcvt.rn.satfinite.e2m1x2.f32 q, %1, %2;\n\tmov.b16 %0, {q, 0};\n\t}"
+        : "=h"(byte)
+        : "f"(hi), "f"(lo));
+    uint32_t h2;
+    asm("{\n\t.reg .b8 q, z;\n\tmov.b16 {q, z}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, q;\n\t}" : "=r"(h2) : "h"(byte));
+    const __half2 v = *reinterpret_cast<const __half2*>(&h2);
+    back_lo = __low2float(v);
+    back_hi = __high2float(v);
+    return byte;
 }
 
 struct PrepArgs {
@@ -107,7 +105,7 @@ struct PrepArgs {
     const uint32_t* sorted_row;  // [positions]; PDK_MOE_PAD = padding (zeros are written)
     const uint32_t* block_expert;  // [blocks]; PDK_MOE_PAD = unused block (its sorted_row entries are not defined)
     uint8_t* xq;                 // [blocks][4*bm][dim/2]
-    uint8_t* xs;                 // [blocks][4*bm][dim/16]
+    uint8_t* xs;                 // tiled: [blocks][slab][4 cells][512], the weight scale records' layout
     float* xstep;                // [positions] power of two the row was divided by
     uint32_t dim, bm, mode;
     float alpha, limit;
@@ -168,7 +166,19 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
 
     // ---- four terms per 16-element group
     const size_t r0 = (size_t)b * 4u * a.bm + i;
-    for (uint32_t g = tid; g < groups; g += blockDim.x) {
+    const uint32_t num_kb = (a.dim + 255u) >> 8;
+    uint8_t* xs_blk = a.xs + (size_t)b * num_kb * 2048u;
+    for (uint32_t g = tid; g < num_kb * 16u; g += blockDim.x) {
+        // scale byte of group g and term row r: record g/16, cell (g/4)%4, byte (r%32)*16 + (r/32)*4 + g%4
+        uint8_t* xs_g = xs_blk + (size_t)(g >> 4) * 2048u + ((g >> 2) & 3u) * 512u + (g & 3u);
+        if (g >= groups) {  // past K: the record's cells must read as zero
+#pragma unroll
+            for (uint32_t term = 0; term < 4u; ++term) {
+                const uint32_t r = term * a.bm + i;
+                xs_g[(r & 31u) * 16u + (r >> 5) * 4u] = 0;
+            }
+            continue;
+        }
         float lo[8], hi[8];
         if (live) {
             const uint32_t base = (g >> 1) * 32u + (g & 1u) * 8u;
@@ -197,14 +207,15 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 float bl, bh;
-                const uint32_t byte = e2m1_rn(lo[k] * inv, bl) | (e2m1_rn(hi[k] * inv, bh) << 4);
+                const uint32_t byte = e2m1x2_rn(lo[k] * inv, hi[k] * inv, bl, bh);
                 if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
                 lo[k] = (lo[k] - bl * sc) * 16.0f;
                 hi[k] = (hi[k] - bh * sc) * 16.0f;
             }
             const size_t r = r0 + (size_t)term * a.bm;
             *reinterpret_cast<uint2*>(a.xq + r * kh + (size_t)g * 8u) = make_uint2(w0, w1);
-            a.xs[r * groups + g] = (uint8_t)sb;
+            const uint32_t rr = term * a.bm + i;
+            xs_g[(rr & 31u) * 16u + (rr >> 5) * 4u] = (uint8_t)sb;
         }
     }
 }
@@ -216,7 +227,7 @@ struct GemmArgs {
     const float* scale2[2];      // per-plane factor (device memory)
     const float* bias[2];        // [expert][out_dim] or null
     float* out[2];               // gate / up: [positions][out_dim]; down: part [(row, slot)][out_dim]
-    const uint8_t* x_sf;         // [blocks*BN][in_dim/16]
+    const uint8_t* x_sf;         // tiled [blocks][slab][2048]
     const float* xstep;          // [positions]
     const uint32_t* block_expert;
     const uint32_t* sorted_row;
@@ -228,8 +239,7 @@ struct GemmArgs {
 
 // One tile = (block of BN/4 tokens, plane, 128 weight rows of the block's expert), walked
 // by persistent CTAs.  Roles as in the dense NVFP4 GEMM: warp 0 producer (TMA boxes of W
-// and of the block's term rows, bulk copy of the weight scale records, cp.async gather of
-// the activation scale cells), warp 1 MMA issuer, warps 2..5 epilogue.
+// and of the block's term rows, bulk copies of both operands' scale records), warp 1 MMA issuer, warps 2..5 epilogue.
 template <uint32_t BN>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_constant__ CUtensorMap tmap_w1,
@@ -248,11 +258,10 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
     const uint32_t n_mma = a.in_dim >> 6;                 // 64-element MMA steps (in_dim % 64 == 0)
     const uint32_t num_kb = (n_mma + 3u) >> 2;            // 256-element slabs, the last may be partial
     const uint32_t num_ks = (num_kb + KS - 1u) / KS;
-    const uint32_t sf_row = a.in_dim >> 4;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            tc5::mbar_init(&sh->full[s], 33);
+            tc5::mbar_init(&sh->full[s], 1);
             tc5::mbar_init(&sh->empty[s], 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
@@ -269,12 +278,6 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
         tc5::tmem_alloc(&sh->tmem_base, kTmemCols);
         tc5::tmem_relinquish();
     }
-    // activation scale cells: the gather writes only the rows a block has; the rest stay zero
-    for (uint32_t i = threadIdx.x; i < kStages * (KS * kSfBytes / 16u); i += kThreads) {
-        const uint32_t s = i / (KS * kSfBytes / 16u), o = i % (KS * kSfBytes / 16u);
-        reinterpret_cast<uint4*>(tiles + s * kStageBytes + kOffSfb)[o] = make_uint4(0u, 0u, 0u, 0u);
-    }
-    fence_proxy_async_smem();
     tc5::fence_before_sync();
     __syncthreads();
     tc5::fence_after_sync();
@@ -285,7 +288,6 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
         // ------------------------------------------------------------ producer (whole warp)
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        constexpr uint32_t kRowGroups = BN / 32u;
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const uint32_t blk = tile / per_block, rem = tile % per_block;
             const uint32_t plane = rem / row_tiles, rt = rem % row_tiles;
@@ -293,17 +295,14 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
             if (expert == PDK_MOE_PAD) continue;
             const CUtensorMap* tw = plane ? &tmap_w1 : &tmap_w0;
             const uint8_t* wsf = a.w_sf[plane] + ((size_t)expert * row_tiles + rt) * num_kb * kSfBytes;
-            const uint8_t* sf_src[kRowGroups];
-#pragma unroll
-            for (uint32_t c = 0; c < kRowGroups; ++c)
-                sf_src[c] = a.x_sf + ((size_t)blk * BN + c * 32u + lane) * sf_row;
+            const uint8_t* xsf = a.x_sf + (size_t)blk * num_kb * kSfBytes;
             for (uint32_t ks = 0; ks < num_ks; ++ks) {
                 ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 uint8_t* st = tiles + stage * kStageBytes;
                 const uint32_t kb0 = ks * KS, nsl = min(KS, num_kb - kb0);
-                tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], nsl * (kABytes + kBBytes + kSfBytes));
+                tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], nsl * (kABytes + kBBytes + 2u * kSfBytes));
 #pragma unroll
                 for (uint32_t u = 0; u < KS; ++u)
                     if (u < nsl) {
@@ -313,24 +312,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
                                                (int32_t)((kb0 + u) * BKB), (int32_t)(blk * BN));
                     }
                 tc5::bulk_load_elect(st + kOffSfa, wsf + (size_t)kb0 * kSfBytes, nsl * kSfBytes, &sh->full[stage]);
-                const uint32_t dst0 = tc5::smem_u32(st + kOffSfb) + lane * 16u;
-#pragma unroll
-                for (uint32_t u = 0; u < KS; ++u)
-                    if (u < nsl)
-#pragma unroll
-                        for (uint32_t j = 0; j < 4u; ++j) {
-                            const uint32_t off = (kb0 + u) * 16u + j * 4u;  // scale bytes of MMA step j
-                            const uint32_t size = off < sf_row ? 4u : 0u;   // past K: zero cells
-#pragma unroll
-                            for (uint32_t c = 0; c < kRowGroups; ++c)
-                                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(
-                                                 dst0 + u * kSfBytes + j * 512u + c * 4u),
-                                             "l"(sf_src[c] + (size ? off : 0u)), "r"(size)
-                                             : "memory");
-                        }
-                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(
-                                 tc5::smem_u32(&sh->full[stage]))
-                             : "memory");
+                tc5::bulk_load_elect(st + kOffSfb, xsf + (size_t)kb0 * kSfBytes, nsl * kSfBytes, &sh->full[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -355,7 +337,6 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc5::fence_after_sync();
-                fence_proxy_async_smem();  // the gathered cells were written through the generic proxy
                 const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
                 const uint32_t nsl = min(KS, num_kb - ks * KS);
 #pragma unroll
@@ -500,7 +481,8 @@ PDK_EXPORT int pdk_mxfp4_tc5_tile_scales(const void* scale, void* tiled, void* m
 // No counterpart in the reference: block positions -> four NVFP4 term rows each.
 //   mode 0: position p takes row sorted_row[p] of x f32 [rows][dim]            (`up` unused)
 //   mode 1: position p takes swiglu(x[p], up[p]) of the raw gate / up outputs f32 [positions][dim]
-// Writes xq u8 [max_blocks*4*bm][dim/2], xs u8 [max_blocks*4*bm][dim/16], xstep f32 [max_blocks*bm].
+// Writes xq u8 [max_blocks*4*bm][dim/2], xs u8 [max_blocks][ceil(dim/256)][2048] (scale records in the
+// weight scale records' layout; bytes of term rows a block does not have are left alone), xstep f32 [max_blocks*bm].
 // dim % 32 == 0, bm 8 or 32.
 PDK_EXPORT int pdk_moe_prep_act_f4(const void* x, const void* up, const void* sorted_row, const void* block_expert,
                                    void* xq, void* xs, void* xstep, uint32_t dim, uint32_t bm, uint32_t max_blocks, uint32_t mode,

@@ -153,10 +153,10 @@ class MoeWorkspace:
         self.part = torch.empty(pairs * planes.embd, dtype=f32, device=dev)
         # tensor-core path: four NVFP4 term rows per block position, raw gate / up outputs
         self.x4q = torch.empty(nb * 4 * planes.embd // 2, dtype=torch.uint8, device=dev)
-        self.x4s = torch.empty(nb * 4 * planes.embd // 16, dtype=torch.uint8, device=dev)
+        self.x4s = torch.zeros(self.max_blocks * ((planes.embd + 255) // 256) * 2048, dtype=torch.uint8, device=dev)
         self.x4step = torch.empty(nb, dtype=f32, device=dev)
         self.h4q = torch.empty(nb * 4 * planes.ff // 2, dtype=torch.uint8, device=dev)
-        self.h4s = torch.empty(nb * 4 * planes.ff // 16, dtype=torch.uint8, device=dev)
+        self.h4s = torch.zeros(self.max_blocks * ((planes.ff + 255) // 256) * 2048, dtype=torch.uint8, device=dev)
         self.h4step = torch.empty(nb, dtype=f32, device=dev)
         self.g_raw = torch.empty(nb * planes.ff, dtype=f32, device=dev)
         self.u_raw = torch.empty(nb * planes.ff, dtype=f32, device=dev)
