@@ -252,7 +252,7 @@ int pdk_moe_prep_act_f4(const void* x, const void* up, const void* sorted_row, c
 /* Grouped GEMM of one or two planes (w1_data NULL = one) over the term rows.  scatter 0: out_p
  * f32[max_blocks*bm][out_dim], block order, bias added, no activation function; scatter 1 (one
  * plane): out0 = part f32[rows*n_active][out_dim] at row (sorted_row, sorted_slot), times topk_w.
- * in_dim % 64 == 0, bm = 8 or 32. */
+ * in_dim % 64 == 0, bm = 8 or 32, max_blocks <= 1024 (the block table lives in shared memory). */
 int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w0_meta, const void* w0_bias, void* out0,
                            const void* w1_data, const void* w1_sf, const void* w1_meta, const void* w1_bias, void* out1,
                            const void* xq, const void* xs, const void* xstep, const void* block_expert,

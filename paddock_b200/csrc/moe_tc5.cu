@@ -141,16 +141,20 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
         }
     };
 
-    // ---- the row's largest magnitude -> the power of two that brings it into [256, 512)
+    // ---- the row's largest magnitude -> the power of two that brings it into [256, 512).
+    // When the CTA has a thread per group (dim <= 4096) the row is read once and kept in
+    // registers across the reduction.
+    const uint32_t num_kb = (a.dim + 255u) >> 8;
+    const bool single = num_kb * 16u <= blockDim.x;
+    float lo0[8], hi0[8];
     float amax = 0.0f;
     if (!pad)
         for (uint32_t g = tid; g < groups; g += blockDim.x) {
             const uint32_t base = (g >> 1) * 32u + (g & 1u) * 8u;
-            float lo[8], hi[8];
-            load8(base, lo);
-            load8(base + 16u, hi);
+            load8(base, lo0);
+            load8(base + 16u, hi0);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fmaxf(fabsf(lo[k]), fabsf(hi[k])));
+            for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fmaxf(fabsf(lo0[k]), fabsf(hi0[k])));
         }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
@@ -166,7 +170,6 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
 
     // ---- four terms per 16-element group
     const size_t r0 = (size_t)b * 4u * a.bm + i;
-    const uint32_t num_kb = (a.dim + 255u) >> 8;
     uint8_t* xs_blk = a.xs + (size_t)b * num_kb * 2048u;
     for (uint32_t g = tid; g < num_kb * 16u; g += blockDim.x) {
         // scale byte of group g and term row r: record g/16, cell (g/4)%4, byte (r%32)*16 + (r/32)*4 + g%4
@@ -180,15 +183,15 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
             continue;
         }
         float lo[8], hi[8];
-        if (live) {
+        if (live && !single) {
             const uint32_t base = (g >> 1) * 32u + (g & 1u) * 8u;
-            load8(base, lo);
-            load8(base + 16u, hi);
+            load8(base, lo0);
+            load8(base + 16u, hi0);
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            lo[k] = live ? lo[k] * inv_step : 0.0f;
-            hi[k] = live ? hi[k] * inv_step : 0.0f;
+            lo[k] = live ? lo0[k] * inv_step : 0.0f;
+            hi[k] = live ? hi0[k] * inv_step : 0.0f;
         }
 #pragma unroll
         for (uint32_t term = 0; term < 4u; ++term) {
@@ -251,6 +254,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * kStageBytes);
+    uint32_t* s_expert = reinterpret_cast<uint32_t*>(sh + 1);  // block_expert[], read once per tile by every role
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t row_tiles = (a.out_dim + BM - 1u) / BM, per_block = a.n_planes * row_tiles;
@@ -278,6 +282,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
         tc5::tmem_alloc(&sh->tmem_base, kTmemCols);
         tc5::tmem_relinquish();
     }
+    for (uint32_t i = threadIdx.x; i < a.max_blocks; i += kThreads) s_expert[i] = a.block_expert[i];
     tc5::fence_before_sync();
     __syncthreads();
     tc5::fence_after_sync();
@@ -291,7 +296,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const uint32_t blk = tile / per_block, rem = tile % per_block;
             const uint32_t plane = rem / row_tiles, rt = rem % row_tiles;
-            const uint32_t expert = a.block_expert[blk];
+            const uint32_t expert = s_expert[blk];
             if (expert == PDK_MOE_PAD) continue;
             const CUtensorMap* tw = plane ? &tmap_w1 : &tmap_w0;
             const uint8_t* wsf = a.w_sf[plane] + ((size_t)expert * row_tiles + rt) * num_kb * kSfBytes;
@@ -324,7 +329,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
         uint32_t stage = 0, phase = 0, iter = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            if (a.block_expert[tile / per_block] == PDK_MOE_PAD) continue;
+            if (s_expert[tile / per_block] == PDK_MOE_PAD) continue;
             const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
             ++iter;
             ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
@@ -372,7 +377,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
         for (uint32_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
             const uint32_t blk = tile / per_block, rem = tile % per_block;
             const uint32_t plane = rem / row_tiles, rt = rem % row_tiles;
-            const uint32_t expert = a.block_expert[blk];
+            const uint32_t expert = s_expert[blk];
             if (expert == PDK_MOE_PAD) continue;
             const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
             ++iter;
@@ -408,24 +413,29 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive(&sh->tmem_empty[buf]);  // the accumulator is in registers now
 
+            // lane i < BT fetches token i's routing data once; the loop below broadcasts it
+            const uint32_t my_pos = blk * BT + min(lane, BT - 1u);
+            const uint32_t my_src = a.sorted_row[my_pos];
+            uint32_t my_row = my_pos;  // output row: block position, or the (token, slot) pair
+            float my_wgt = 1.0f;       // routing weight when scattering
+            if (a.scatter && my_src != PDK_MOE_PAD) {
+                my_row = my_src * a.n_active + a.sorted_slot[my_pos];
+                my_wgt = a.topk_w[my_row];
+            }
+            const float my_mul = a.xstep[my_pos] * *a.scale2[plane] * my_wgt;
             const uint32_t n = rt * BM + quarter * 32u + lane;
-            if (n < a.out_dim) {
-                const float s2 = *a.scale2[plane];
-                const float bias = a.bias[plane] ? a.bias[plane][(size_t)expert * a.out_dim + n] : 0.0f;
-                float* out = a.out[plane];
+            float bias = 0.0f;
+            if (n < a.out_dim && a.bias[plane]) bias = a.bias[plane][(size_t)expert * a.out_dim + n];
+            float* out = a.out[plane];
 #pragma unroll
-                for (uint32_t i = 0; i < BT; ++i) {
-                    const uint32_t pos = blk * BT + i;
-                    const uint32_t src = a.sorted_row[pos];
-                    if (src == PDK_MOE_PAD) continue;
-                    const float y = fmaf(v[i] * s2, a.xstep[pos], bias);
-                    if (a.scatter) {
-                        const uint32_t pair = src * a.n_active + a.sorted_slot[pos];
-                        out[(size_t)pair * a.out_dim + n] = a.topk_w[pair] * y;
-                    } else {
-                        out[(size_t)pos * a.out_dim + n] = y;
-                    }
-                }
+            for (uint32_t i = 0; i < BT; ++i) {
+                const uint32_t src = __shfl_sync(0xffffffffu, my_src, i);
+                const uint32_t row = __shfl_sync(0xffffffffu, my_row, i);
+                const float mul = __shfl_sync(0xffffffffu, my_mul, i);
+                const float wgt = __shfl_sync(0xffffffffu, my_wgt, i);
+                if (src == PDK_MOE_PAD || n >= a.out_dim) continue;
+                // (acc * scale2 * step + bias) * routing weight
+                out[(size_t)row * a.out_dim + n] = fmaf(v[i], mul, bias * wgt);
             }
         }
     }
@@ -438,10 +448,12 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
     }
 }
 
+constexpr uint32_t kMaxBlocks = 1024;  // block_expert[] is kept in shared memory
+
 template <uint32_t BN>
 int launch_gemm(const CUtensorMap& tw0, const CUtensorMap& tw1, const CUtensorMap& tx, const GemmArgs& a,
                 cudaStream_t st) {
-    const size_t smem = (size_t)Cfg<BN>::kStages * Cfg<BN>::kStageBytes + sizeof(Shared) + 1024u;
+    const size_t smem = (size_t)Cfg<BN>::kStages * Cfg<BN>::kStageBytes + sizeof(Shared) + kMaxBlocks * 4u + 1024u;
     auto kern = moe_tc5_gemm_kernel<BN>;
     static const cudaError_t attr_rc =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -495,7 +507,8 @@ PDK_EXPORT int pdk_moe_prep_act_f4(const void* x, const void* up, const void* so
     a.block_expert = (const uint32_t*)block_expert;
     a.xq = (uint8_t*)xq; a.xs = (uint8_t*)xs; a.xstep = (float*)xstep;
     a.dim = dim; a.bm = bm; a.mode = mode; a.alpha = alpha; a.limit = limit;
-    moe_prep_f4_kernel<<<max_blocks * bm, 256, 0, (cudaStream_t)stream>>>(a);
+    const uint32_t per_row = ((dim + 255u) >> 8) * 16u;  // scale groups incl. the zero tail of the last record
+    moe_prep_f4_kernel<<<max_blocks * bm, per_row <= 256u ? (per_row + 31u) & ~31u : 256u, 0, (cudaStream_t)stream>>>(a);
     return pdk_launch_status();
 }
 
@@ -506,7 +519,7 @@ PDK_EXPORT int pdk_moe_prep_act_f4(const void* x, const void* up, const void* so
 //   scatter 0: out_p f32 [max_blocks*bm][out_dim] in block order, raw (bias added); one or two planes
 //              (w1_data NULL = one)
 //   scatter 1: out0 = part f32 [rows*n_active][out_dim], row (sorted_row, sorted_slot), times topk_w
-// in_dim % 64 == 0.
+// in_dim % 64 == 0, max_blocks <= 1024.
 PDK_EXPORT int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w0_meta, const void* w0_bias,
                                       void* out0, const void* w1_data, const void* w1_sf, const void* w1_meta,
                                       const void* w1_bias, void* out1, const void* xq, const void* xs,
@@ -515,7 +528,8 @@ PDK_EXPORT int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, co
                                       uint32_t n_expert, uint32_t bm, uint32_t max_blocks, uint32_t n_active,
                                       uint32_t scatter, void* stream) {
     if (max_blocks == 0 || out_dim == 0 || n_expert == 0) return 0;
-    if (in_dim == 0 || (in_dim & 63u) != 0u || (bm != 8u && bm != 32u)) return cudaErrorInvalidValue;
+    if (in_dim == 0 || (in_dim & 63u) != 0u || (bm != 8u && bm != 32u) || max_blocks > kMaxBlocks)
+        return cudaErrorInvalidValue;
     if (!pdk_aligned(w0_data, 16) || !pdk_aligned(w0_sf, 16) || !pdk_aligned(xq, 16) || !pdk_aligned(xs, 4) ||
         !pdk_aligned(w0_meta, 8) || (w1_data && (!pdk_aligned(w1_data, 16) || !pdk_aligned(w1_sf, 16))))
         return cudaErrorInvalidValue;
