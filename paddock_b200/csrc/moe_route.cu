@@ -67,19 +67,22 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* _
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const uint32_t* __restrict__ idx, uint32_t* __restrict__ sorted_row,
                  uint32_t* __restrict__ sorted_slot, uint32_t* __restrict__ block_expert, uint32_t rows,
-                 uint32_t n_active, uint32_t n_expert, uint32_t bm, uint32_t max_blocks) {
+                 uint32_t n_active, uint32_t n_expert, uint32_t bm, uint32_t max_blocks, uint32_t staged) {
     extern __shared__ uint32_t ash[];
     uint32_t* count = ash;               // [n_expert]
     uint32_t* boff = ash + n_expert;     // [n_expert + 1] first block of each expert
+    uint32_t* sidx = boff + n_expert + 1u;  // [npairs] when `staged`: every warp rescans the whole list
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, nwarp = blockDim.x >> 5;
     const uint32_t npairs = rows * n_active;
     for (uint32_t e = tid; e < n_expert; e += blockDim.x) count[e] = 0;
     __syncthreads();
     for (uint32_t p = tid; p < npairs; p += blockDim.x) {
         const uint32_t e = idx[p];
+        if (staged) sidx[p] = e;
         if (e < n_expert) atomicAdd(&count[e], 1u);
     }
     __syncthreads();
+    const uint32_t* pick = staged ? sidx : idx;
     if (tid == 0) {
         uint32_t b = 0;
         for (uint32_t e = 0; e < n_expert; ++e) {
@@ -98,7 +101,7 @@ moe_align_kernel(const uint32_t* __restrict__ idx, uint32_t* __restrict__ sorted
         uint32_t pos = b0 * bm;
         for (uint32_t base = 0; base < npairs; base += 32u) {
             const uint32_t p = base + lane;
-            const bool mine = p < npairs && idx[p] == e;
+            const bool mine = p < npairs && pick[p] == e;
             const uint32_t m = __ballot_sync(0xffffffffu, mine);
             if (mine) {
                 const uint32_t at = pos + __popc(m & ((1u << lane) - 1u));
@@ -115,6 +118,86 @@ moe_align_kernel(const uint32_t* __restrict__ idx, uint32_t* __restrict__ sorted
                 sorted_row[at] = PDK_MOE_PAD;
                 sorted_slot[at] = 0;
             }
+    }
+}
+
+// Same layout, linear work: the pair list is walked in chunks of one pair per thread; a
+// pair's place among its expert's entries is (entries of earlier chunks) + (entries of
+// earlier warps of this chunk) + (earlier lanes of its warp with the same expert, from
+// __match_any_sync).  Needs a [warps][n_expert] table in shared memory.
+__global__ void __launch_bounds__(1024)
+moe_align_rank_kernel(const uint32_t* __restrict__ idx, uint32_t* __restrict__ sorted_row,
+                      uint32_t* __restrict__ sorted_slot, uint32_t* __restrict__ block_expert, uint32_t rows,
+                      uint32_t n_active, uint32_t n_expert, uint32_t bm, uint32_t max_blocks) {
+    extern __shared__ uint32_t ash[];
+    uint32_t* count = ash;                    // [n_expert] entries per expert
+    uint32_t* boff = count + n_expert;        // [n_expert + 1] first block of each expert
+    uint32_t* cursor = boff + n_expert + 1u;  // [n_expert] entries placed by earlier chunks
+    uint32_t* table = cursor + n_expert;      // [nwarp][n_expert]
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    const uint32_t npairs = rows * n_active, cap = max_blocks * bm;
+    for (uint32_t e = tid; e < n_expert; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (uint32_t p = tid; p < npairs; p += blockDim.x) {
+        const uint32_t e = idx[p];
+        if (e < n_expert) atomicAdd(&count[e], 1u);
+    }
+    __syncthreads();
+    if (warp == 0) {  // exclusive scan of the block counts, 32 experts at a time
+        uint32_t carry = 0;
+        for (uint32_t e0 = 0; e0 < n_expert; e0 += 32u) {
+            const uint32_t e = e0 + lane;
+            const uint32_t nb = e < n_expert ? (count[e] + bm - 1u) / bm : 0u;
+            uint32_t inc = nb;
+#pragma unroll
+            for (uint32_t d = 1; d < 32u; d <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, inc, d);
+                if (lane >= d) inc += up;
+            }
+            if (e < n_expert) boff[e] = carry + inc - nb;
+            carry += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) boff[n_expert] = carry;
+    }
+    __syncthreads();
+    const uint32_t used = min(boff[n_expert], max_blocks);
+    for (uint32_t b = used + tid; b < max_blocks; b += blockDim.x) block_expert[b] = PDK_MOE_PAD;
+    for (uint32_t e = tid; e < n_expert; e += blockDim.x) {
+        for (uint32_t b = boff[e]; b < boff[e + 1] && b < max_blocks; ++b) block_expert[b] = e;
+        // padding of the expert's last block
+        for (uint32_t at = boff[e] * bm + count[e]; at < boff[e + 1] * bm && at < cap; ++at) {
+            sorted_row[at] = PDK_MOE_PAD;
+            sorted_slot[at] = 0;
+        }
+    }
+    for (uint32_t base = 0; base < npairs; base += blockDim.x) {
+        for (uint32_t i = tid; i < nwarp * n_expert; i += blockDim.x) table[i] = 0;
+        __syncthreads();
+        const uint32_t p = base + tid;
+        const uint32_t e = p < npairs ? idx[p] : 0xFFFFFFFFu;
+        const bool live = e < n_expert;
+        const uint32_t peers = __match_any_sync(0xffffffffu, live ? e : 0xFFFFFFFFu);
+        const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+        if (live && rank == 0u) table[warp * n_expert + e] = __popc(peers);
+        __syncthreads();
+        for (uint32_t x = tid; x < n_expert; x += blockDim.x) {  // per expert: prefix over the warps
+            uint32_t run = cursor[x];
+            for (uint32_t w = 0; w < nwarp; ++w) {
+                const uint32_t t = table[w * n_expert + x];
+                table[w * n_expert + x] = run;
+                run += t;
+            }
+            cursor[x] = run;
+        }
+        __syncthreads();
+        if (live) {
+            const uint32_t at = boff[e] * bm + table[warp * n_expert + e] + rank;
+            if (at < cap) {
+                sorted_row[at] = p / n_active;
+                sorted_slot[at] = p % n_active;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -201,10 +284,27 @@ PDK_EXPORT int pd_moe_align_bm(const void* idx, void* sorted_row, void* sorted_s
                                void* stream) {
     if (rows == 0 || n_expert == 0) return 0;
     if (bm == 0 || (bm & (bm - 1u)) || n_expert > 4096u) return cudaErrorInvalidValue;
-    const size_t shmem = (size_t)(2u * n_expert + 1u) * sizeof(uint32_t);
+    static const cudaError_t attr_rank =
+        cudaFuncSetAttribute(moe_align_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    const size_t rank_smem = ((size_t)3u * n_expert + 1u + (size_t)32u * n_expert) * sizeof(uint32_t);
+    if (attr_rank == cudaSuccess && rank_smem <= 200u * 1024u) {
+        moe_align_rank_kernel<<<1, 1024, rank_smem, (cudaStream_t)stream>>>(
+            (const uint32_t*)idx, (uint32_t*)sorted_row, (uint32_t*)sorted_slot, (uint32_t*)block_expert, rows, n_active,
+            n_expert, bm, max_blocks);
+        return pdk_launch_status();
+    }
+    // many experts: the scan kernel, one warp per expert
+    size_t shmem = (size_t)(2u * n_expert + 1u) * sizeof(uint32_t);
+    // the pick list is staged in shared memory when it fits (up to 200 KB)
+    const size_t list = (size_t)rows * n_active * sizeof(uint32_t);
+    const uint32_t staged = shmem + list <= 200u * 1024u ? 1u : 0u;
+    if (staged) shmem += list;
+    static const cudaError_t attr_rc =
+        cudaFuncSetAttribute(moe_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (attr_rc != cudaSuccess) return (int)attr_rc;
     moe_align_kernel<<<1, 1024, shmem, (cudaStream_t)stream>>>((const uint32_t*)idx, (uint32_t*)sorted_row,
                                                                (uint32_t*)sorted_slot, (uint32_t*)block_expert, rows,
-                                                               n_active, n_expert, bm, max_blocks);
+                                                               n_active, n_expert, bm, max_blocks, staged);
     return pdk_launch_status();
 }
 
