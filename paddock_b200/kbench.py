@@ -136,7 +136,19 @@ def bench_moe(ex, a):
     out = torch.zeros(T * embd, dtype=torch.float32, device="cuda")
     n_sets = 6 if T <= 64 else 1          # different routings so consecutive steps touch different experts
     logits = [synth.normal(T * n_expert, 100 + i, 1.0, "cuda") for i in range(n_sets)]
-    sec = time_launches(lambda i: P.moe_mxfp4_forward(ex, planes, ws, x, logits[i % n_sets], out), a.iters)
+    if a.graph:
+        # the block's launches replayed from CUDA graphs, one per routing set (what a serving
+        # loop that captures its decode step does)
+        graphs = []
+        for lg in logits:
+            P.moe_mxfp4_forward(ex, planes, ws, x, lg, out)     # first call outside capture
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                P.moe_mxfp4_forward(ex, planes, ws, x, lg, out)
+            graphs.append(g)
+        sec = time_launches(lambda i: graphs[i % n_sets].replay(), a.iters)
+    else:
+        sec = time_launches(lambda i: P.moe_mxfp4_forward(ex, planes, ws, x, logits[i % n_sets], out), a.iters)
     distinct = 0
     for lg in logits:
         distinct += torch.unique(torch.topk(lg.view(T, n_expert), k, dim=1).indices).numel()
@@ -161,7 +173,10 @@ def bench_moe_ep(ex, a):
         return P.RepackedMxfp4(torch.randint(0, 256, (blocks * 16,), dtype=torch.uint8, device="cuda", generator=g),
                                torch.randint(118, 124, (blocks,), dtype=torch.uint8, device="cuda", generator=g))
 
-    shard = moe_ep.GpuExpertShard(ex, P.MoeMxfp4Planes(plane(1), plane(2), plane(3), epr, embd, ff), T * k, bm)
+    local = P.MoeMxfp4Planes(plane(1), plane(2), plane(3), epr, embd, ff)
+    if a.moe_path == "tc5":
+        P.prepare_tc5(ex, local)
+    shard = moe_ep.GpuExpertShard(ex, local, T * k, bm)
     lo, hi = (T * rank) // world, (T * (rank + 1)) // world
     x = synth.bf16_round(synth.normal(T * embd, 7, 1.0, "cuda")).view(T, embd)[lo:hi].contiguous()
     n_sets = 6 if T <= 64 else 1
@@ -208,6 +223,7 @@ def main():
     ap.add_argument("--out", default="bf16", choices=["bf16", "f32"])
     ap.add_argument("--moe-path", default="tc5", choices=["tc5", "mma"],
                     help="expert GEMMs: block-scaled tcgen05 (default) or the mma.sync kernels")
+    ap.add_argument("--graph", action="store_true", help="moe_mxfp4: replay the block from a CUDA graph")
     ap.add_argument("--pack", default=None, help="path of a kernel-pack library to time instead of this package's")
     a = ap.parse_args()
     dm, dn, dk = DEFAULTS[a.op]

@@ -108,13 +108,14 @@ class GpuExpertShard:
         self.launches = 0
 
     def __call__(self, rows, local_expert, weight):
-        from .planes import moe_mxfp4_experts
+        from .planes import moe_mxfp4_experts, moe_mxfp4_experts_tc5
         r = rows.shape[0]
         if r > self.max_rows:
             raise ValueError(f"{r} routed rows exceed the shard's workspace ({self.max_rows})")
         self.ws.idx[:r].copy_(local_expert.to(torch.int32))
         self.ws.w[:r].copy_(weight)
-        self.launches += moe_mxfp4_experts(self.ex, self.planes, self.ws, rows.contiguous(), r)
+        run = moe_mxfp4_experts_tc5 if self.planes.tc5 is not None else moe_mxfp4_experts
+        self.launches += run(self.ex, self.planes, self.ws, rows.contiguous(), r)
         return self.ws.part[: r * self.planes.embd].view(r, self.planes.embd)
 
 
