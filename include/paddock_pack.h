@@ -82,7 +82,12 @@ enum PdkSlot {
     PDK_SLOT_moe_topk_batch = 29,
     PDK_SLOT_moe_align = 34,
     PDK_SLOT_moe_slot_combine = 91,
-    PDK_SLOT_moe_align_bm = 146
+    PDK_SLOT_moe_align_bm = 146,
+    PDK_SLOT_quantize_q8 = 18,
+    PDK_SLOT_quantize_q8_sums = 218,
+    PDK_SLOT_kquant_gemv_w4a8 = 217,
+    PDK_SLOT_kquant_gemm_mma_ks = 212,
+    PDK_SLOT_kquant_gemm_w4a8_sb = 837
 };
 
 /* ---- the drop-in boundary ------------------------------------------------ */
@@ -121,6 +126,26 @@ int pd_kquant_repack(const void* src, void* dst_data, void* dst_scales, uint64_t
 /* slot 204, kquant.cuh:372-653: exact-f32 decode GEMV over repacked planes. */
 int pd_kquant_gemv(const void* data, const void* scales, const void* x, void* y, uint32_t in_dim,
                    uint32_t out_dim, uint32_t dtype, void* stream);
+/* slot 18, packs/cuda/src/gemm/f32_qkv.cuh:283-292 (kernel attn/decode.cuh:2981-3004): per-32
+ * int8 activation quantization, scale = amax / 127 (f32 [n/32]), q = RN(x / scale) in +-127. */
+int pd_quantize_q8(const void* x, void* q, void* scale, uint32_t n, void* stream);
+/* slot 218, f32_qkv.cuh:304-311 (kernel attn/decode.cuh:3041-3068): slot 18 plus the per-16
+ * sums of q as f32 [n/16]. */
+int pd_quantize_q8_sums(const void* x, void* q, void* scale, void* sums, uint32_t n, void* stream);
+/* slot 217, packs/cuda/src/quant/kquant_w4a8.cuh:1266-1330: decode GEMV on the int8 activations of
+ * slot 18 / 218.  The activations are widened (q * scale) inside the kernel; xsums is not needed.
+ * 801 for shapes outside the GEMV kernel's plan. */
+int pd_kquant_gemv_w4a8(const void* data, const void* scales, const void* xq, const void* xs, const void* xsums,
+                        void* y, uint32_t in_dim, uint32_t out_dim, uint32_t dtype, void* stream);
+/* slots 212 and 837, kquant_w4a8.cuh:2364-2430 and kquant_w4a8_sb.cuh:300-353: batch <= 64 on the
+ * same operands, y f32[batch][out_dim]; `part` (>= 8 * out_dim * batch floats by the slots'
+ * contract) holds the widened activations.  in_dim <= 8 * out_dim. */
+int pd_kquant_gemm_mma_ks(const void* data, const void* scales, const void* xq, const void* xs, const void* xsums,
+                          void* part, void* y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, uint32_t dtype,
+                          void* stream);
+int pd_kquant_gemm_w4a8_sb(const void* data, const void* scales, const void* xq, const void* xs, const void* xsums,
+                           void* part, void* y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, uint32_t dtype,
+                           void* stream);
 /* No slot: small-batch sibling of pd_kquant_gemv with f32 activations,
  * x f32[batch][in_dim], y f32[batch][out_dim], batch <= 64.  The reference's
  * small-batch route quantizes activations to int8 first (kquant_w4a8_sb.cuh);

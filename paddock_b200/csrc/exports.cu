@@ -49,6 +49,11 @@ static void fill_table() {
     PDK_SET(moe_align);
     PDK_SET(moe_align_bm);
     PDK_SET(moe_slot_combine);
+    PDK_SET(quantize_q8);
+    PDK_SET(quantize_q8_sums);
+    PDK_SET(kquant_gemv_w4a8);
+    PDK_SET(kquant_gemm_mma_ks);
+    PDK_SET(kquant_gemm_w4a8_sb);
 #undef PDK_SET
 }
 

@@ -151,7 +151,8 @@ struct Q80 {
 template <class F>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ recs, const float* __restrict__ bias,
-               const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim, uint32_t out_dim) {
+               const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim, uint32_t out_dim,
+               const int8_t* __restrict__ xq, const float* __restrict__ xq_scale) {
     using Stage = typename F::Stage;
     constexpr uint32_t DEPTH = F::kDepth;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -216,9 +217,18 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
     {
         const uint32_t groups = in_dim >> 3;
         for (uint32_t grp = tid; grp < groups; grp += kThreads) {
-            const float4 a = *reinterpret_cast<const float4*>(x + grp * 8u);
-            const float4 b = *reinterpret_cast<const float4*>(x + grp * 8u + 4u);
-            const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            float v[8];
+            if (xq == nullptr) {
+                const float4 a = *reinterpret_cast<const float4*>(x + grp * 8u);
+                const float4 b = *reinterpret_cast<const float4*>(x + grp * 8u + 4u);
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            } else {
+                // int8 activations with one f32 scale per 32 (the W4A8 slots' operands)
+                const int2 q = *reinterpret_cast<const int2*>(xq + grp * 8u);
+                const float s = xq_scale[grp >> 2];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (float)(int8_t)((i < 4 ? q.x >> (8 * i) : q.y >> (8 * (i - 4))) & 0xff) * s;
+            }
             float amax = 0.0f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
@@ -350,7 +360,7 @@ bool pdl_enabled() {
 
 template <class F>
 int launch(const void* data, const void* recs, const float* bias, const float* x, float* y, uint32_t in_dim,
-           uint32_t out_dim, cudaStream_t st) {
+           uint32_t out_dim, cudaStream_t st, const int8_t* xq = nullptr, const float* xq_scale = nullptr) {
     const uint32_t n_unit = in_dim >> 8;
     if ((in_dim & 255u) != 0u || n_unit < kSlices) return -1;
     const size_t smem = (size_t)in_dim * 2u + 32u + (size_t)(in_dim >> 5) * 8u + 2u * kSlots * kSlices * 16u * 4u;
@@ -372,7 +382,8 @@ int launch(const void* data, const void* recs, const float* bias, const float* x
     attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, kern, (const uint8_t*)data, (const uint8_t*)recs, bias, x, y, in_dim, out_dim);
+    e = cudaLaunchKernelEx(&cfg, kern, (const uint8_t*)data, (const uint8_t*)recs, bias, x, y, in_dim, out_dim, xq,
+                           xq_scale);
     return e == cudaSuccess ? pdk_launch_status() : (int)e;
 }
 
@@ -389,4 +400,11 @@ int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float*
 int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, const float* x, float* y,
                      uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
     return launch<Q80>(data, scale, bias, x, y, in_dim, out_dim, st);
+}
+
+// Q4_K GEMV on int8 activations (xq int8 [in_dim], one f32 scale per 32): same kernel, the
+// activation staging widens q * scale before it builds its limbs.
+int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq, const float* xq_scale, float* y,
+                          uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
+    return launch<Q4K>(data, scales, nullptr, nullptr, y, in_dim, out_dim, st, xq, xq_scale);
 }

@@ -21,6 +21,8 @@
 
 #include "pdk_common.cuh"
 
+int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq, const float* xq_scale, float* y,
+                          uint32_t in_dim, uint32_t out_dim, cudaStream_t st);
 int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st);
 
@@ -548,4 +550,113 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
     if (batch > 64u) return cudaErrorInvalidValue;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
     return gemm_any(data, scales, (const float*)x, (float*)y, in_dim, out_dim, batch, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------- int8 activation operands (W4A8 slots)
+namespace {
+
+// One warp per 32-element block: scale = amax / 127, q = RN(x / scale) clamped to +-127;
+// optionally the two per-16 sums of q as f32 (packs/cuda/src/attn/decode.cuh:2981-3004, 3041-3068).
+__global__ void quantize_q8_kernel(const float* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale,
+                                   float* __restrict__ sums, uint32_t n_blocks) {
+    const uint32_t b = blockIdx.x * 8u + (threadIdx.x >> 5), d = threadIdx.x & 31u;
+    if (b >= n_blocks) return;
+    const float v = x[(size_t)b * 32u + d];
+    float a = fabsf(v);
+#pragma unroll
+    for (uint32_t s = 16; s > 0; s >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, s));
+    const float scl = a * (1.0f / 127.0f);
+    if (d == 0) scale[b] = scl;
+    const float inv = scl > 0.0f ? 1.0f / scl : 0.0f;
+    int qi = __float2int_rn(v * inv);
+    qi = qi < -127 ? -127 : (qi > 127 ? 127 : qi);
+    q[(size_t)b * 32u + d] = (int8_t)qi;
+    if (sums != nullptr) {
+        int s16 = qi;
+#pragma unroll
+        for (uint32_t s = 8; s > 0; s >>= 1) s16 += __shfl_xor_sync(0xffffffffu, s16, s);
+        if ((d & 15u) == 0u) sums[(size_t)b * 2u + (d >> 4)] = (float)s16;
+    }
+}
+
+// x[i] = q[i] * scale[i / 32]: the f32 activations the batch kernels take
+__global__ void q8_act_widen_kernel(const int8_t* __restrict__ q, const float* __restrict__ scale, float* __restrict__ x,
+                                    uint64_t n4) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const uint32_t w = reinterpret_cast<const uint32_t*>(q)[i];
+    const float s = scale[i >> 3];
+    reinterpret_cast<float4*>(x)[i] = make_float4((float)(int8_t)(w & 0xff) * s, (float)(int8_t)((w >> 8) & 0xff) * s,
+                                                  (float)(int8_t)((w >> 16) & 0xff) * s, (float)(int8_t)(w >> 24) * s);
+}
+
+int w4a8_gemm(const void* data, const void* scales, const void* xq, const void* xs, void* part, void* y,
+              uint32_t in_dim, uint32_t out_dim, uint32_t batch, uint32_t dtype, cudaStream_t st) {
+    if (out_dim == 0 || batch == 0) return 0;
+    if (batch > 64u) return cudaErrorInvalidValue;
+    if (int rc = check_gemv(data, scales, xq, y, in_dim, dtype)) return rc;
+    if (batch == 1u) {
+        const int rc = pdk_q4k_gemv_i8_q8act(data, scales, (const int8_t*)xq, (const float*)xs, (float*)y, in_dim, out_dim, st);
+        if (rc >= 0) return rc;
+    }
+    // the batch kernels take f32 activations: widen q * scale into the caller's partial
+    // buffer (>= 8 * out_dim * batch floats by the slot's contract)
+    if (part == nullptr || !pdk_aligned(part, 16) || !pdk_aligned(xq, 4) || (uint64_t)in_dim > 8ull * out_dim)
+        return cudaErrorInvalidValue;
+    const uint64_t n4 = (uint64_t)batch * in_dim / 4u;
+    q8_act_widen_kernel<<<(uint32_t)((n4 + 255u) / 256u), 256, 0, st>>>((const int8_t*)xq, (const float*)xs, (float*)part, n4);
+    return gemm_any(data, scales, (const float*)part, (float*)y, in_dim, out_dim, batch, st);
+}
+
+}  // namespace
+
+// slot 18, packs/cuda/src/gemm/f32_qkv.cuh:283-292
+PDK_EXPORT int pd_quantize_q8(const void* x, void* q, void* scale, uint32_t n, void* stream) {
+    const uint32_t n_blocks = n >> 5;
+    if (n_blocks == 0) return 0;
+    quantize_q8_kernel<<<(n_blocks + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>((const float*)x, (int8_t*)q, (float*)scale,
+                                                                               nullptr, n_blocks);
+    return pdk_launch_status();
+}
+
+// slot 218, packs/cuda/src/gemm/f32_qkv.cuh:304-311: also the per-16 sums of q (f32 [n/16])
+PDK_EXPORT int pd_quantize_q8_sums(const void* x, void* q, void* scale, void* sums, uint32_t n, void* stream) {
+    const uint32_t n_blocks = n >> 5;
+    if (n_blocks == 0) return 0;
+    if (sums == nullptr) return cudaErrorInvalidValue;
+    quantize_q8_kernel<<<(n_blocks + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>((const float*)x, (int8_t*)q, (float*)scale,
+                                                                               (float*)sums, n_blocks);
+    return pdk_launch_status();
+}
+
+// slot 217, packs/cuda/src/quant/kquant_w4a8.cuh:1266-1330: decode GEMV on int8 activations.
+// xsums (the min term's per-16 sums) is accepted and not needed: the kernel rebuilds its
+// own sums from q * scale.  Shapes outside the GEMV kernel's plan answer "not supported"
+// (there is no scratch argument to widen the activations into).
+PDK_EXPORT int pd_kquant_gemv_w4a8(const void* data, const void* scales, const void* xq, const void* xs,
+                                   const void* xsums, void* y, uint32_t in_dim, uint32_t out_dim, uint32_t dtype,
+                                   void* stream) {
+    (void)xsums;
+    if (out_dim == 0) return 0;
+    if (int rc = check_gemv(data, scales, xq, y, in_dim, dtype)) return rc;
+    const int rc = pdk_q4k_gemv_i8_q8act(data, scales, (const int8_t*)xq, (const float*)xs, (float*)y, in_dim, out_dim,
+                                         (cudaStream_t)stream);
+    return rc >= 0 ? rc : (int)cudaErrorNotSupported;
+}
+
+// slot 212, packs/cuda/src/quant/kquant_w4a8.cuh:2364-2430: batch <= 64, y f32 [batch][out_dim];
+// `part` (>= 8 * out_dim * batch floats) is used as scratch for the widened activations.
+PDK_EXPORT int pd_kquant_gemm_mma_ks(const void* data, const void* scales, const void* xq, const void* xs,
+                                     const void* xsums, void* part, void* y, uint32_t in_dim, uint32_t out_dim,
+                                     uint32_t batch, uint32_t dtype, void* stream) {
+    (void)xsums;
+    return w4a8_gemm(data, scales, xq, xs, part, y, in_dim, out_dim, batch, dtype, (cudaStream_t)stream);
+}
+
+// slot 837, packs/cuda/src/quant/kquant_w4a8_sb.cuh:300-353: same contract as slot 212
+PDK_EXPORT int pd_kquant_gemm_w4a8_sb(const void* data, const void* scales, const void* xq, const void* xs,
+                                      const void* xsums, void* part, void* y, uint32_t in_dim, uint32_t out_dim,
+                                      uint32_t batch, uint32_t dtype, void* stream) {
+    (void)xsums;
+    return w4a8_gemm(data, scales, xq, xs, part, y, in_dim, out_dim, batch, dtype, (cudaStream_t)stream);
 }

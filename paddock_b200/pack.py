@@ -103,6 +103,8 @@ _SIGS = {
     "nvf4_tc5_tile_scales": "ppuu", "nvf4_gemm_tc5w": "ppppppfuuupU",
     "moe_topk_batch": "ppuuppu", "moe_align": "ppppuuuu", "moe_align_bm": "ppppuuuuu", "moe_slot_combine": "ppuuu",
     "kquant_dequant": "ppUu", "kquant_repack": "pppUu", "kquant_gemv": "ppppuuu",
+    "quantize_q8": "pppu", "quantize_q8_sums": "ppppu", "kquant_gemv_w4a8": "ppppppuuu",
+    "kquant_gemm_mma_ks": "pppppppuuuu", "kquant_gemm_w4a8_sb": "pppppppuuuu",
 }
 _EXTRA_SIGS = {
     "pdk_kquant_gemm_f32": "ppppuuuu",

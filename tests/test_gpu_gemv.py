@@ -134,3 +134,51 @@ def test_q4_k_gemv_refuses_bad_shapes(pack):
     assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 99) == 1     # unknown dtype
     assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 13) == 801   # Q5_K not built
     assert pack.status("pdk_kquant_gemm_f32", buf, buf, buf, buf, 256, 4, 65, 12) == 1
+
+
+# ---- int8 activation operands: slots 18 / 218 (quantizers) and 217 / 212 / 837 (W4A8 GEMV / GEMM)
+
+@pytest.mark.parametrize("n", [32, 5120, 16 * 5120])
+def test_quantize_q8_bit_exact(pack, n):
+    x = oracle.fill_normal(n, 700 + n, 1.0)
+    x[:32] = 0.0
+    q_ref, s_ref, sums_ref = oracle.quantize_q8_act(x)
+    d_q = torch.zeros(n, dtype=torch.int8, device="cuda")
+    d_s = torch.zeros(n // 32, dtype=torch.float32, device="cuda")
+    d_sum = torch.zeros(n // 16, dtype=torch.float32, device="cuda")
+    pack.call("quantize_q8_sums", dev_f32(x), d_q, d_s, d_sum, n)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_q.cpu().numpy(), q_ref)
+    assert np.array_equal(d_s.cpu().numpy().view(np.uint32), s_ref.view(np.uint32))
+    assert np.array_equal(d_sum.cpu().numpy(), sums_ref)
+    d_q2 = torch.zeros_like(d_q)
+    d_s2 = torch.zeros_like(d_s)
+    pack.call("quantize_q8", dev_f32(x), d_q2, d_s2, n)
+    torch.cuda.synchronize()
+    assert torch.equal(d_q, d_q2) and torch.equal(d_s, d_s2)
+
+
+@pytest.mark.parametrize("k,n,batch", [(5120, 512, 1), (1024, 96, 1), (5120, 768, 4), (2048, 1000, 16)])
+def test_q4k_w4a8_slots(pack, k, n, batch):
+    """Slots 217 / 212 / 837 against an f64 matmul of the dequantized weights and q * scale."""
+    raw, d_data, d_sc = q4k_planes(pack, oracle.fill_normal(n * k, 710 + n, 0.02), n, k)
+    x = oracle.fill_normal(batch * k, 711, 1.0)
+    q, s, sums = oracle.quantize_q8_act(x)
+    xhat = (q.astype(np.float32).reshape(-1, 32) * s.reshape(-1, 1)).reshape(-1)
+    ref, ab = oracle.matmul_f64(oracle.dequant_q4_k(raw), xhat, k, n, batch, with_abs=True)
+    d_y = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+    d_part = torch.zeros(8 * n * batch, dtype=torch.float32, device="cuda")
+    names = ["kquant_gemm_mma_ks", "kquant_gemm_w4a8_sb"] + (["kquant_gemv_w4a8"] if batch == 1 else [])
+    for name in names:
+        d_y.zero_()
+        if name == "kquant_gemv_w4a8":
+            rc = pack.status(name, d_data, d_sc, dev(q), dev_f32(s), dev_f32(sums), d_y, k, n, 12)
+            if rc == 801:
+                continue                      # K outside the GEMV kernel's plan
+            assert rc == 0
+        else:
+            pack.call(name, d_data, d_sc, dev(q), dev_f32(s), dev_f32(sums), d_part, d_y, k, n, batch, 12)
+        torch.cuda.synchronize()
+        y = d_y.cpu().numpy().reshape(batch, n)
+        # batches above 4 run the bf16-activation kernel: q * scale is rounded to 8 significant bits
+        assert cond_err(y, ref, ab) < (1e-4 if batch <= 4 else 1e-3) < TOL, name

@@ -244,3 +244,32 @@ def test_fp8_row_quantizers(pack, ref):
         s = torch.zeros(rows, dtype=torch.float32, device="cuda")
         return (w.cuda(), q, s, k, rows), [q, s]
     assert_bytes_equal(run_both(pack, ref, "bf16_to_f8row", mkw, 2))
+
+
+def test_q8_activation_quantizers_and_w4a8_gemv(pack, ref):
+    n_el = 8 * 5120
+    x = oracle.fill_normal(n_el, 28, 1.0)
+    x[:32] = 0.0
+
+    def mkq():
+        q = torch.zeros(n_el, dtype=torch.int8, device="cuda")
+        s = torch.zeros(n_el // 32, dtype=torch.float32, device="cuda")
+        sums = torch.zeros(n_el // 16, dtype=torch.float32, device="cuda")
+        return (dev_f32(x), q, s, sums, n_el), [q, s, sums]
+    outs = run_both(pack, ref, "quantize_q8_sums", mkq, 3)
+    assert_bytes_equal(outs)
+
+    k, n = 5120, 512
+    raw, ns = q4k_planes(pack, n, k, 29)
+    d = torch.zeros(ns * 128, dtype=torch.uint8, device="cuda")
+    sc = torch.zeros(ns * 24, dtype=torch.uint8, device="cuda")
+    pack.call("kquant_repack", dev(raw), d, sc, ns, 12)
+    q = outs[0][0][:k]
+    s = outs[0][1][: k // 32 * 4]
+    sums = outs[0][2][: k // 16 * 4]
+
+    def mkg():
+        y = torch.zeros(n, dtype=torch.float32, device="cuda")
+        return (d, sc, dev(q), dev(s), dev(sums), y, k, n, 12), [y]
+    ours, theirs = (o[0].view(np.float32) for o in run_both(pack, ref, "kquant_gemv_w4a8", mkg, 1))
+    assert rel_l2(ours, theirs.astype(np.float64)) < 1e-4 < TOL
