@@ -38,7 +38,7 @@ FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the GEMV kernel, from
 # the ncu capture summarized in profiles/q4k_gemv_i8_config2_m1.md (scaled by rows when sharded)
-NCU_TRAFFIC_BYTES = 79_500_000
+NCU_TRAFFIC_BYTES = 79_560_000
 
 
 def algorithmic_bytes(m, n=N_DIM, k=K_DIM):

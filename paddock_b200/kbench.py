@@ -176,7 +176,8 @@ def bench_moe_ep(ex, a):
     local = P.MoeMxfp4Planes(plane(1), plane(2), plane(3), epr, embd, ff)
     if a.moe_path == "tc5":
         P.prepare_tc5(ex, local)
-    shard = moe_ep.GpuExpertShard(ex, local, T * k, bm)
+    cap = -(-T // world) * k                     # slots every rank sends every peer
+    shard = moe_ep.GpuExpertShard(ex, local, max(T * k, world * cap), bm)
     lo, hi = (T * rank) // world, (T * (rank + 1)) // world
     x = synth.bf16_round(synth.normal(T * embd, 7, 1.0, "cuda")).view(T, embd)[lo:hi].contiguous()
     n_sets = 6 if T <= 64 else 1
@@ -185,7 +186,7 @@ def bench_moe_ep(ex, a):
     out = torch.zeros(hi - lo, embd, device="cuda")
 
     def step(i):
-        moe_ep.gpu_ep_forward(ex, shard, x, logits[i % n_sets], out, n_expert, k)
+        moe_ep.gpu_ep_forward(ex, shard, x, logits[i % n_sets], out, n_expert, k, capacity=cap)
 
     for i in range(5):
         step(i)

@@ -88,6 +88,58 @@ def ep_moe_block(x, idx, w, n_expert, expert_fn, group=None):
     return slots.view(tokens, k, x.shape[1]), d
 
 
+PAD_EXPERT = -1  # local expert index of an unused slot of the fixed-capacity exchange
+
+
+def ep_moe_block_fixed(x, idx, w, n_expert, expert_fn, capacity=None, group=None):
+    """ep_moe_block without the host round trip: every rank sends every peer `capacity` row slots
+    (default: all of its tokens*k pairs, which can never overflow), unused slots marked with
+    PAD_EXPERT, so the split sizes are known without exchanging counts and nothing synchronizes
+    the host.  One all-to-all each way: a slot is the token row as bf16 followed by 8 bytes
+    (local expert i32, routing weight f32).  expert_fn must ignore rows whose expert is
+    PAD_EXPERT (the kernels' alignment step drops indices outside [0, n_expert)); what it
+    returns for them is never read."""
+    world = dist.get_world_size(group)
+    if n_expert % world:
+        raise ValueError(f"{n_expert} experts do not split over {world} ranks")
+    epr = n_expert // world
+    tokens, k = idx.shape
+    embd = x.shape[1]
+    pairs = tokens * k
+    cap = pairs if capacity is None else capacity
+    dev = x.device
+    row_bytes = embd * 2 + 8
+    send = torch.zeros((world * cap, row_bytes), dtype=torch.uint8, device=dev)
+    send[:, embd * 2:embd * 2 + 4] = 0xFF                      # expert = -1 everywhere
+    if pairs:
+        flat_idx, flat_w = idx.reshape(-1), w.reshape(-1)
+        dest = expert_owner(flat_idx, epr)
+        order = torch.argsort(dest, stable=True)
+        counts = torch.bincount(dest, minlength=world)
+        starts = torch.cumsum(counts, 0) - counts
+        dest_sorted = dest.index_select(0, order)
+        slot = dest_sorted * cap + (torch.arange(pairs, device=dev) - starts.index_select(0, dest_sorted))
+        token_of_pair = torch.div(order, k, rounding_mode="floor")
+        rows = torch.empty((pairs, row_bytes), dtype=torch.uint8, device=dev)
+        rows[:, :embd * 2] = x.index_select(0, token_of_pair).to(torch.bfloat16).view(torch.uint8).view(pairs, embd * 2)
+        local_e = (flat_idx.index_select(0, order) - dest_sorted * epr).to(torch.int32)
+        rows[:, embd * 2:embd * 2 + 4] = local_e.view(torch.uint8).view(pairs, 4)
+        rows[:, embd * 2 + 4:] = flat_w.index_select(0, order).contiguous().view(torch.uint8).view(pairs, 4)
+        send.index_copy_(0, slot, rows)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    rx = recv[:, :embd * 2].contiguous().view(torch.bfloat16).view(world * cap, embd).to(torch.float32)
+    re = recv[:, embd * 2:embd * 2 + 4].contiguous().view(torch.int32).view(-1).to(torch.int64)
+    rw = recv[:, embd * 2 + 4:].contiguous().view(torch.float32).view(-1)
+    part = expert_fn(rx, re, rw)
+    back = torch.empty((world * cap, embd), dtype=torch.float32, device=dev)
+    dist.all_to_all_single(back, part.contiguous(), group=group)
+    slots = torch.zeros((pairs, embd), dtype=torch.float32, device=dev)
+    if pairs:
+        slots.index_copy_(0, order, back.index_select(0, slot))
+    return slots.view(tokens, k, embd)
+
+
 def combine_slots(slots, out):
     """out[t] += slots[t][0] + slots[t][1] + ... in slot order (the order of pd_moe_slot_combine)."""
     acc = slots[:, 0].clone()
@@ -112,20 +164,29 @@ class GpuExpertShard:
         r = rows.shape[0]
         if r > self.max_rows:
             raise ValueError(f"{r} routed rows exceed the shard's workspace ({self.max_rows})")
-        self.ws.idx[:r].copy_(local_expert.to(torch.int32))
+        self.ws.idx[:r].copy_(local_expert.to(torch.int32))     # -1 (unused slot) is outside [0, n_expert): dropped
         self.ws.w[:r].copy_(weight)
         run = moe_mxfp4_experts_tc5 if self.planes.tc5 is not None else moe_mxfp4_experts
         self.launches += run(self.ex, self.planes, self.ws, rows.contiguous(), r)
         return self.ws.part[: r * self.planes.embd].view(r, self.planes.embd)
 
 
-def gpu_ep_forward(ex, shard, x, router_logits, out, n_expert, k, group=None, router_bias=None):
-    """Route on this rank, exchange, compute, exchange back, combine into `out` (f32[tokens][embd])."""
+def gpu_ep_forward(ex, shard, x, router_logits, out, n_expert, k, group=None, router_bias=None, capacity=None,
+                   fixed=True):
+    """Route on this rank, exchange, compute, exchange back, combine into `out` (f32[tokens][embd]).
+    fixed=True uses the fixed-capacity exchange (no host synchronization; every rank must pass the
+    same `capacity`, by default the largest per-rank tokens*k, and the shard's workspace must hold
+    world*capacity rows); fixed=False exchanges exact counts first."""
     tokens = x.shape[0]
     idx = torch.empty(tokens * k, dtype=torch.int32, device=x.device)
     w = torch.empty(tokens * k, dtype=torch.float32, device=x.device)
     st = torch.cuda.current_stream().cuda_stream
     ex.pack.call("moe_topk_batch", router_logits, router_bias, n_expert, k, idx, w, tokens, stream=st)
-    slots, d = ep_moe_block(x, idx.view(tokens, k).to(torch.int64), w.view(tokens, k), n_expert, shard, group)
+    d = None
+    if fixed:
+        slots = ep_moe_block_fixed(x, idx.view(tokens, k).to(torch.int64), w.view(tokens, k), n_expert, shard,
+                                   capacity, group)
+    else:
+        slots, d = ep_moe_block(x, idx.view(tokens, k).to(torch.int64), w.view(tokens, k), n_expert, shard, group)
     ex.pack.call("moe_slot_combine", slots.contiguous(), out, x.shape[1], k, tokens, stream=st)
     return d

@@ -33,7 +33,7 @@ def build_planes(P, ex, dev, lo, hi, tc5):
     return P.prepare_tc5(ex, planes) if tc5 else planes
 
 
-def worker(rank, world, port, tokens, tc5, out_path):
+def worker(rank, world, port, tokens, tc5, fixed, out_path):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -44,9 +44,11 @@ def worker(rank, world, port, tokens, tc5, out_path):
     logits = synth.normal(tokens * N_EXPERT, 8, 1.0, dev).view(tokens, N_EXPERT)
     epr = N_EXPERT // world
     lo, hi = (tokens * rank) // world, (tokens * (rank + 1)) // world
-    shard = moe_ep.GpuExpertShard(ex, build_planes(P, ex, dev, rank * epr, (rank + 1) * epr, tc5), tokens * K, BM)
+    cap = -(-tokens // world) * K
+    shard = moe_ep.GpuExpertShard(ex, build_planes(P, ex, dev, rank * epr, (rank + 1) * epr, tc5), max(tokens * K, world * cap), BM)
     out = torch.zeros(hi - lo, EMBD, device=dev)
-    moe_ep.gpu_ep_forward(ex, shard, x[lo:hi].contiguous(), logits[lo:hi].contiguous(), out, N_EXPERT, K)
+    moe_ep.gpu_ep_forward(ex, shard, x[lo:hi].contiguous(), logits[lo:hi].contiguous(), out, N_EXPERT, K, capacity=cap,
+                          fixed=fixed)
     torch.cuda.synchronize()
     parts = [torch.zeros(tokens, EMBD, device=dev) for _ in range(world)]
     padded = torch.zeros(tokens, EMBD, device=dev)
@@ -64,13 +66,14 @@ def worker(rank, world, port, tokens, tc5, out_path):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("fixed", [False, True], ids=["counted", "fixed-capacity"])
 @pytest.mark.parametrize("tc5", [False, True], ids=["mma", "tensor-core"])
 @pytest.mark.parametrize("tokens", [1, 37])
-def test_two_gpu_block_is_bit_identical(tmp_path, tokens, tc5):
+def test_two_gpu_block_is_bit_identical(tmp_path, tokens, tc5, fixed):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     out = str(tmp_path / "y.npy")
-    mp.spawn(worker, args=(2, free_port(), tokens, tc5, out), nprocs=2, join=True)
+    mp.spawn(worker, args=(2, free_port(), tokens, tc5, fixed, out), nprocs=2, join=True)
     y, ref = np.load(out)
     assert np.isfinite(ref).all() and np.abs(ref).max() > 0
     assert np.array_equal(y.view(np.uint32), ref.view(np.uint32))

@@ -51,6 +51,18 @@ def worker(rank, world, port, tokens, out_path):
                                    torch.from_numpy(w[lo:hi]), N_EXPERT, expert_fn)
     out = moe_ep.combine_slots(slots, torch.zeros(hi - lo, EMBD))
     assert sum(d.send_counts) == (hi - lo) * K
+
+    # the fixed-capacity exchange (no counts, unused slots marked) must give the same sums
+    def expert_fn_padded(rows, local_expert, weight):
+        live = local_expert >= 0
+        y = torch.zeros(rows.shape[0], EMBD)
+        if live.any():
+            y[live] = expert_fn(rows[live], local_expert[live], weight[live])
+        return y
+    cap = ((tokens + world - 1) // world) * K              # the same on every rank
+    slots_fixed = moe_ep.ep_moe_block_fixed(torch.from_numpy(x[lo:hi]), torch.from_numpy(idx[lo:hi].astype(np.int64)),
+                                            torch.from_numpy(w[lo:hi]), N_EXPERT, expert_fn_padded, cap)
+    assert torch.equal(slots_fixed, slots)
     gathered = [None] * world
     dist.all_gather_object(gathered, (lo, hi, out.numpy(), d.n_recv))
     if rank == 0:
