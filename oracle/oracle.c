@@ -188,6 +188,82 @@ int orc_dequant_q4_k(const uint8_t* data, size_t n_bytes, float* out, size_t n_o
     return 0;
 }
 
+/* crates/paddock-engine/tests/gpu_kquant_parity.rs:39-69 (Q5_K arm): the Q4_K walk with a
+ * fifth bit per weight; source order is d, dmin, scales[12], qh[32], qs[128] (176 bytes). */
+int orc_dequant_q5_k(const uint8_t* data, size_t n_bytes, float* out, size_t n_out) {
+    if (n_bytes % 176) return -1;
+    size_t n_super = n_bytes / 176;
+    if (n_out != n_super * 256) return -2;
+#pragma omp parallel for schedule(static)
+    for (size_t b = 0; b < n_super; ++b) {
+        const uint8_t* s = data + b * 176;
+        float d = orc_f16_to_f32((uint16_t)(s[0] | (s[1] << 8)));
+        float dmin = orc_f16_to_f32((uint16_t)(s[2] | (s[3] << 8)));
+        const uint8_t* scales = s + 4;
+        const uint8_t* qh = s + 16;
+        const uint8_t* qs = s + 48;
+        for (int j = 0; j < 8; ++j) {
+            uint32_t sc, m;
+            orc_scale_min_k4(scales, j, &sc, &m);
+            float dj = d * (float)sc;
+            float mj = dmin * (float)m;
+            const uint8_t* qg = qs + (j >> 1) * 32;
+            for (int l = 0; l < 32; ++l) {
+                uint32_t v = (j & 1) ? (uint32_t)(qg[l] >> 4) : (uint32_t)(qg[l] & 0xF);
+                if ((qh[l] >> j) & 1) v += 16;
+                float p = dj * (float)v;
+                out[b * 256 + j * 32 + l] = p - mj;
+            }
+        }
+    }
+    return 0;
+}
+
+/* gpu_kquant_parity.rs:70-94 (Q6_K arm): ql[128], qh[64], i8 scales[16], f16 d (210 bytes);
+ * y = (d * scale) * q with q in [-32, 31], two separate f32 multiplies. */
+int orc_dequant_q6_k(const uint8_t* data, size_t n_bytes, float* out, size_t n_out) {
+    if (n_bytes % 210) return -1;
+    size_t n_super = n_bytes / 210;
+    if (n_out != n_super * 256) return -2;
+#pragma omp parallel for schedule(static)
+    for (size_t b = 0; b < n_super; ++b) {
+        const uint8_t* s = data + b * 210;
+        const uint8_t *ql = s, *qh = s + 128;
+        const int8_t* sc = (const int8_t*)(s + 192);
+        float d = orc_f16_to_f32((uint16_t)(s[208] | (s[209] << 8)));
+        for (int nh = 0; nh < 2; ++nh)
+            for (int l = 0; l < 32; ++l) {
+                int is = l / 16;
+                uint8_t qlo = ql[nh * 64 + l], qlh = ql[nh * 64 + 32 + l], h = qh[nh * 32 + l];
+                int q[4] = {((qlo & 0xF) | ((h & 3) << 4)) - 32, ((qlh & 0xF) | (((h >> 2) & 3) << 4)) - 32,
+                            ((qlo >> 4) | (((h >> 4) & 3) << 4)) - 32, ((qlh >> 4) | (((h >> 6) & 3) << 4)) - 32};
+                for (int r = 0; r < 4; ++r) {
+                    float ds = d * (float)sc[nh * 8 + r * 2 + is];
+                    out[b * 256 + nh * 128 + r * 32 + l] = ds * (float)q[r];
+                }
+            }
+    }
+    return 0;
+}
+
+/* gpu_kquant_parity.rs:117-128 (Q4_0 arm): 32-weight blocks { f16 d, 16 nibble bytes };
+ * byte k holds weight k (low) and k + 16 (high); value = d * (q - 8). */
+int orc_dequant_q4_0(const uint8_t* data, size_t n_bytes, float* out, size_t n_out) {
+    if (n_bytes % 18) return -1;
+    size_t n_blk = n_bytes / 18;
+    if (n_out != n_blk * 32) return -2;
+#pragma omp parallel for schedule(static)
+    for (size_t b = 0; b < n_blk; ++b) {
+        const uint8_t* s = data + b * 18;
+        float d = orc_f16_to_f32((uint16_t)(s[0] | (s[1] << 8)));
+        for (int k = 0; k < 16; ++k) {
+            out[b * 32 + k] = d * (float)((int)(s[2 + k] & 0xF) - 8);
+            out[b * 32 + 16 + k] = d * (float)((int)(s[2 + k] >> 4) - 8);
+        }
+    }
+    return 0;
+}
+
 /* crates/paddock-models/src/modelopt.rs:408-424: op order (e2m1*e4m3)*scale2;
  * byte j holds elements 2j (low nibble) and 2j+1 (high nibble). */
 void orc_dequant_nvfp4(const uint8_t* data, const uint8_t* scale, float scale2, float* out,

@@ -34,6 +34,9 @@ uint8_t  orc_e2m1_rn(float v);               /* quant/e2m1.cuh:12-26 */
 int orc_dequant_mxfp4(const uint8_t* data, size_t n_bytes, float* out, size_t n_out);
 int orc_dequant_q8_0(const uint8_t* data, size_t n_bytes, float* out, size_t n_out);
 int orc_dequant_q4_k(const uint8_t* data, size_t n_bytes, float* out, size_t n_out);
+int orc_dequant_q5_k(const uint8_t* data, size_t n_bytes, float* out, size_t n_out);
+int orc_dequant_q6_k(const uint8_t* data, size_t n_bytes, float* out, size_t n_out);
+int orc_dequant_q4_0(const uint8_t* data, size_t n_bytes, float* out, size_t n_out);
 void orc_scale_min_k4(const uint8_t* scales12, int j, uint32_t* sc, uint32_t* m);
 /* NVFP4 plane: data u8[N][K/2], scale e4m3[N][K/16], scale2; w=(e2m1*e4m3)*scale2 */
 void orc_dequant_nvfp4(const uint8_t* data, const uint8_t* scale, float scale2,

@@ -21,6 +21,13 @@
 
 #include "pdk_common.cuh"
 
+// kquant_more.cu: Q5_K, Q6_K, Q4_0
+bool pdk_kq_more_has(uint32_t dtype);
+int pdk_kq_more_dequant(const void* src, void* dst, uint64_t n_super, uint32_t dtype, cudaStream_t st);
+int pdk_kq_more_repack(const void* src, void* dst_data, void* dst_scales, uint64_t n_super, uint32_t dtype,
+                       cudaStream_t st);
+int pdk_kq_more_gemm(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                     uint32_t batch, uint32_t dtype, cudaStream_t st);
 int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq, const float* xq_scale, float* y,
                           uint32_t in_dim, uint32_t out_dim, cudaStream_t st);
 int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
@@ -498,11 +505,8 @@ int gemm_any(const void* data, const void* scales, const float* x, float* y, uin
 }
 
 int check_gemv(const void* data, const void* scales, const void* x, const void* y, uint32_t in_dim, uint32_t dtype) {
-    if (dtype != PDK_KQ_Q4K) {
-        if (dtype == PDK_KQ_Q5K || dtype == PDK_KQ_Q6K || dtype == PDK_KQ_IQ4XS || dtype == PDK_KQ_Q4_0)
-            return cudaErrorNotSupported;
-        return cudaErrorInvalidValue;
-    }
+    if (dtype != PDK_KQ_Q4K && !pdk_kq_more_has(dtype))
+        return dtype == PDK_KQ_IQ4XS ? cudaErrorNotSupported : cudaErrorInvalidValue;
     if (in_dim == 0u || (in_dim & 255u) != 0u) return cudaErrorInvalidValue;
     if (!pdk_aligned(data, 16) || !pdk_aligned(scales, 8) || !pdk_aligned(x, 16) || !pdk_aligned(y, 4))
         return cudaErrorInvalidValue;
@@ -513,9 +517,8 @@ int check_gemv(const void* data, const void* scales, const void* x, const void* 
 
 PDK_EXPORT int pd_kquant_dequant(const void* src, void* dst, uint64_t n_super, uint32_t dtype, void* stream) {
     if (n_super == 0) return 0;
-    if (dtype != PDK_KQ_Q4K)
-        return (dtype == PDK_KQ_Q5K || dtype == PDK_KQ_Q6K || dtype == PDK_KQ_IQ4XS || dtype == PDK_KQ_Q4_0)
-                   ? cudaErrorNotSupported : cudaErrorInvalidValue;
+    if (pdk_kq_more_has(dtype)) return pdk_kq_more_dequant(src, dst, n_super, dtype, (cudaStream_t)stream);
+    if (dtype != PDK_KQ_Q4K) return dtype == PDK_KQ_IQ4XS ? cudaErrorNotSupported : cudaErrorInvalidValue;
     if (!pdk_aligned(src, 2) || !pdk_aligned(dst, 4)) return cudaErrorInvalidValue;
     const uint64_t blocks = (n_super + 7u) / 8u;
     if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
@@ -526,9 +529,9 @@ PDK_EXPORT int pd_kquant_dequant(const void* src, void* dst, uint64_t n_super, u
 PDK_EXPORT int pd_kquant_repack(const void* src, void* dst_data, void* dst_scales, uint64_t n_super, uint32_t dtype,
                                 void* stream) {
     if (n_super == 0) return 0;
-    if (dtype != PDK_KQ_Q4K)
-        return (dtype == PDK_KQ_Q5K || dtype == PDK_KQ_Q6K || dtype == PDK_KQ_IQ4XS || dtype == PDK_KQ_Q4_0)
-                   ? cudaErrorNotSupported : cudaErrorInvalidValue;
+    if (pdk_kq_more_has(dtype))
+        return pdk_kq_more_repack(src, dst_data, dst_scales, n_super, dtype, (cudaStream_t)stream);
+    if (dtype != PDK_KQ_Q4K) return dtype == PDK_KQ_IQ4XS ? cudaErrorNotSupported : cudaErrorInvalidValue;
     if (!pdk_aligned(src, 4) || !pdk_aligned(dst_data, 4)) return cudaErrorInvalidValue;
     const uint64_t blocks = (n_super + 7u) / 8u;
     if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
@@ -541,6 +544,8 @@ PDK_EXPORT int pd_kquant_gemv(const void* data, const void* scales, const void* 
                               uint32_t out_dim, uint32_t dtype, void* stream) {
     if (out_dim == 0) return 0;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
+    if (dtype != PDK_KQ_Q4K)
+        return pdk_kq_more_gemm(data, scales, (const float*)x, (float*)y, in_dim, out_dim, 1u, dtype, (cudaStream_t)stream);
     return gemm_any(data, scales, (const float*)x, (float*)y, in_dim, out_dim, 1u, (cudaStream_t)stream);
 }
 
@@ -549,6 +554,9 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
     if (out_dim == 0 || batch == 0) return 0;
     if (batch > 64u) return cudaErrorInvalidValue;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
+    if (dtype != PDK_KQ_Q4K)
+        return pdk_kq_more_gemm(data, scales, (const float*)x, (float*)y, in_dim, out_dim, batch, dtype,
+                                (cudaStream_t)stream);
     return gemm_any(data, scales, (const float*)x, (float*)y, in_dim, out_dim, batch, (cudaStream_t)stream);
 }
 
@@ -595,6 +603,7 @@ int w4a8_gemm(const void* data, const void* scales, const void* xq, const void* 
     if (out_dim == 0 || batch == 0) return 0;
     if (batch > 64u) return cudaErrorInvalidValue;
     if (int rc = check_gemv(data, scales, xq, y, in_dim, dtype)) return rc;
+    if (dtype != PDK_KQ_Q4K) return cudaErrorNotSupported;
     if (batch == 1u) {
         const int rc = pdk_q4k_gemv_i8_q8act(data, scales, (const int8_t*)xq, (const float*)xs, (float*)y, in_dim, out_dim, st);
         if (rc >= 0) return rc;
@@ -639,6 +648,7 @@ PDK_EXPORT int pd_kquant_gemv_w4a8(const void* data, const void* scales, const v
     (void)xsums;
     if (out_dim == 0) return 0;
     if (int rc = check_gemv(data, scales, xq, y, in_dim, dtype)) return rc;
+    if (dtype != PDK_KQ_Q4K) return cudaErrorNotSupported;
     const int rc = pdk_q4k_gemv_i8_q8act(data, scales, (const int8_t*)xq, (const float*)xs, (float*)y, in_dim, out_dim,
                                          (cudaStream_t)stream);
     return rc >= 0 ? rc : (int)cudaErrorNotSupported;

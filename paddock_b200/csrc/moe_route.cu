@@ -15,6 +15,9 @@ namespace {
 __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, uint32_t n_expert,
                                 uint32_t k, uint32_t* __restrict__ out_idx, float* __restrict__ out_w,
                                 uint32_t batch) {
+    // dependent launch: may start while the previous kernel of the stream drains; its results are awaited here
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();
     const uint32_t token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (token >= batch) return;
     const uint32_t lane = threadIdx.x & 31u;
@@ -136,6 +139,9 @@ moe_align_rank_kernel(const uint32_t* __restrict__ idx, uint32_t* __restrict__ s
     uint32_t* table = cursor + n_expert;      // [nwarp][n_expert]
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, nwarp = blockDim.x >> 5;
     const uint32_t npairs = rows * n_active, cap = max_blocks * bm;
+    // dependent launch: may start while the previous kernel of the stream drains; its results are awaited here
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();
     for (uint32_t e = tid; e < n_expert; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
     __syncthreads();
     for (uint32_t p = tid; p < npairs; p += blockDim.x) {
@@ -252,6 +258,9 @@ moe_prep_act_kernel(const float* __restrict__ x, uint8_t* __restrict__ xq, float
 // ---------------------------------------------------------------- slot combine
 __global__ void moe_slot_combine_kernel(const float4* __restrict__ part, float4* __restrict__ residual,
                                         uint32_t embd4, uint32_t n_active, uint32_t rows) {
+    // dependent launch: may start while the previous kernel of the stream drains; its results are awaited here
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)rows * embd4) return;
     const size_t t = i / embd4, r = i % embd4;
@@ -272,10 +281,8 @@ PDK_EXPORT int pd_moe_topk_batch(const void* logits, const void* bias, uint32_t 
                                  void* out_w, uint32_t batch, void* stream) {
     if (batch == 0) return 0;
     if (n_expert == 0 || n_expert > 512u || k == 0 || k > 16u || k > n_expert) return cudaErrorInvalidValue;
-    moe_topk_kernel<<<(batch + 3u) / 4u, 128, 0, (cudaStream_t)stream>>>((const float*)logits, (const float*)bias,
-                                                                        n_expert, k, (uint32_t*)out_idx,
-                                                                        (float*)out_w, batch);
-    return pdk_launch_status();
+    return pdk_launch_pdl(moe_topk_kernel, dim3((batch + 3u) / 4u), dim3(128), 0, (cudaStream_t)stream,
+                          (const float*)logits, (const float*)bias, n_expert, k, (uint32_t*)out_idx, (float*)out_w, batch);
 }
 
 // slot 146, packs/cuda/src/gemm/f32_qkv.cuh:1269-1279 (kernel attn/decode.cuh:2316-2396)
@@ -288,10 +295,9 @@ PDK_EXPORT int pd_moe_align_bm(const void* idx, void* sorted_row, void* sorted_s
         cudaFuncSetAttribute(moe_align_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     const size_t rank_smem = ((size_t)3u * n_expert + 1u + (size_t)32u * n_expert) * sizeof(uint32_t);
     if (attr_rank == cudaSuccess && rank_smem <= 200u * 1024u) {
-        moe_align_rank_kernel<<<1, 1024, rank_smem, (cudaStream_t)stream>>>(
-            (const uint32_t*)idx, (uint32_t*)sorted_row, (uint32_t*)sorted_slot, (uint32_t*)block_expert, rows, n_active,
-            n_expert, bm, max_blocks);
-        return pdk_launch_status();
+        return pdk_launch_pdl(moe_align_rank_kernel, dim3(1), dim3(1024), rank_smem, (cudaStream_t)stream,
+                              (const uint32_t*)idx, (uint32_t*)sorted_row, (uint32_t*)sorted_slot,
+                              (uint32_t*)block_expert, rows, n_active, n_expert, bm, max_blocks);
     }
     // many experts: the scan kernel, one warp per expert
     size_t shmem = (size_t)(2u * n_expert + 1u) * sizeof(uint32_t);
@@ -331,7 +337,6 @@ PDK_EXPORT int pd_moe_slot_combine(const void* part, void* residual, uint32_t em
     if (rows == 0 || embd == 0) return 0;
     if ((embd & 3u) != 0u || !pdk_aligned(part, 16) || !pdk_aligned(residual, 16)) return cudaErrorInvalidValue;
     const size_t total = (size_t)rows * (embd >> 2);
-    moe_slot_combine_kernel<<<(uint32_t)((total + 255u) / 256u), 256, 0, (cudaStream_t)stream>>>(
-        (const float4*)part, (float4*)residual, embd >> 2, n_active, rows);
-    return pdk_launch_status();
+    return pdk_launch_pdl(moe_slot_combine_kernel, dim3((uint32_t)((total + 255u) / 256u)), dim3(256), 0,
+                          (cudaStream_t)stream, (const float4*)part, (float4*)residual, embd >> 2, n_active, rows);
 }

@@ -115,6 +115,9 @@ struct PrepArgs {
 // b*4*bm + k*bm + i.  A 16-element scale group of the tensor core's element order is the
 // two 8-runs (h*8 .. h*8+7) and (16 + h*8 .. 16 + h*8+7) of a 32-element block.
 __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
+    // dependent launch: may start while the previous kernel of the stream drains; its results are awaited here
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();
     const uint32_t pos = blockIdx.x, b = pos / a.bm, i = pos % a.bm;
     const uint32_t src = a.block_expert[b] == PDK_MOE_PAD ? PDK_MOE_PAD : a.sorted_row[pos];
     const uint32_t groups = a.dim >> 4, kh = a.dim >> 1;
@@ -282,6 +285,10 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
         tc5::tmem_alloc(&sh->tmem_base, kTmemCols);
         tc5::tmem_relinquish();
     }
+    // dependent launch: barriers and tensor memory are set up while the previous kernel drains;
+    // everything below reads what it wrote
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();
     for (uint32_t i = threadIdx.x; i < a.max_blocks; i += kThreads) s_expert[i] = a.block_expert[i];
     tc5::fence_before_sync();
     __syncthreads();
@@ -461,8 +468,7 @@ int launch_gemm(const CUtensorMap& tw0, const CUtensorMap& tw1, const CUtensorMa
     const uint32_t n_tiles = a.max_blocks * a.n_planes * ((a.out_dim + BM - 1u) / BM);
     uint32_t grid = (uint32_t)pdk_sm_count();
     if (grid > n_tiles) grid = n_tiles;
-    kern<<<grid, kThreads, smem, st>>>(tw0, tw1, tx, a);
-    return pdk_launch_status();
+    return pdk_launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, tw0, tw1, tx, a);
 }
 
 }  // namespace
@@ -508,8 +514,8 @@ PDK_EXPORT int pdk_moe_prep_act_f4(const void* x, const void* up, const void* so
     a.xq = (uint8_t*)xq; a.xs = (uint8_t*)xs; a.xstep = (float*)xstep;
     a.dim = dim; a.bm = bm; a.mode = mode; a.alpha = alpha; a.limit = limit;
     const uint32_t per_row = ((dim + 255u) >> 8) * 16u;  // scale groups incl. the zero tail of the last record
-    moe_prep_f4_kernel<<<max_blocks * bm, per_row <= 256u ? (per_row + 31u) & ~31u : 256u, 0, (cudaStream_t)stream>>>(a);
-    return pdk_launch_status();
+    return pdk_launch_pdl(moe_prep_f4_kernel, dim3(max_blocks * bm),
+                          dim3(per_row <= 256u ? (per_row + 31u) & ~31u : 256u), 0, (cudaStream_t)stream, a);
 }
 
 // No counterpart in the reference (slots 88 / 89 are its mma.sync kernels on int8 activations):

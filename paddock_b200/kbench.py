@@ -114,9 +114,81 @@ def bench_nvf4(ex, a):
     return sec, {"bound": "both", "flops": 2.0 * m * n * k, "bytes": nbytes_w + 4 + m * (k // 2 + k // 16) + m * n * 2}
 
 
+def bench_moe_other_pack(ex, a):
+    """Config 5 through another pack's int8-activation chain, the way the reference engine drives it
+    (crates/paddock-engine/src/gpu_model/gpt_oss.rs:715-735, 2393-2440): gate|up interleaved once
+    (slot 155), then per call top-k, align (32-row blocks), quantize_q8 (18), gate_up_mmq (88),
+    down_mmq (89), slot_combine."""
+    import ctypes as C
+    from . import planes as P
+    pk = ex.pack
+    n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
+    st = torch.cuda.current_stream().cuda_stream
+    interleave = pk.fn_at(155, "pppuU")
+    gate_up = pk.fn_at(88, "pppppppppppp" + "uuu" + "fff")
+    down = pk.fn_at(89, "pppppppppp" + "uuuu")
+    nblk = embd // 32
+    blocks = n_expert * ff * nblk
+
+    def rnd(n, lo, hi, seed):
+        g = torch.Generator(device="cuda")
+        g.manual_seed(seed)
+        return torch.randint(lo, hi, (n,), dtype=torch.uint8, device="cuda", generator=g)
+
+    g_data, u_data, d_data = rnd(blocks * 16, 0, 256, 1), rnd(blocks * 16, 0, 256, 2), rnd(blocks * 16, 0, 256, 3)
+    g_scale, u_scale, d_scale = rnd(blocks, 118, 124, 4), rnd(blocks, 118, 124, 5), rnd(blocks, 118, 124, 6)
+    gu = torch.zeros(n_expert * ff * ((nblk + 3) // 4) * 128, dtype=torch.uint8, device="cuda")
+    rc = interleave(g_data.data_ptr(), u_data.data_ptr(), gu.data_ptr(), nblk, n_expert * ff, st)
+    assert rc == 0, rc
+    dummy = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    zb_ff = torch.zeros(n_expert * ff, device="cuda")
+    zb_embd = torch.zeros(n_expert * embd, device="cuda")
+    pairs, bm = T * k, 32
+    max_blocks = min(pairs, pairs // bm + n_expert)
+    nb = max_blocks * bm
+    idx = torch.zeros(pairs, dtype=torch.int32, device="cuda")
+    w = torch.zeros(pairs, device="cuda")
+    s_row = torch.zeros(nb, dtype=torch.int32, device="cuda")
+    s_slot = torch.zeros(nb, dtype=torch.int32, device="cuda")
+    b_exp = torch.zeros(max_blocks, dtype=torch.int32, device="cuda")
+    x = synth.bf16_round(synth.normal(T * embd, 7, 1.0, "cuda"))
+    xq = torch.zeros(T * embd, dtype=torch.int8, device="cuda")
+    xs = torch.zeros(T * embd // 32, device="cuda")
+    fq = torch.zeros(nb * ff, dtype=torch.int8, device="cuda")
+    fs = torch.zeros(nb * ff // 32, device="cuda")
+    part = torch.zeros(pairs * max(ff, embd), device="cuda")
+    out = torch.zeros(T * embd, device="cuda")
+    n_sets = 6 if T <= 64 else 1
+    logits = [synth.normal(T * n_expert, 100 + i, 1.0, "cuda") for i in range(n_sets)]
+
+    def step(i):
+        pk.call("moe_topk_batch", logits[i % n_sets], None, n_expert, k, idx, w, T, stream=st)
+        pk.call("moe_align", idx, s_row, s_slot, b_exp, T, k, n_expert, max_blocks, stream=st)
+        pk.call("quantize_q8", x, xq, xs, T * embd, stream=st)
+        rc = gate_up(gu.data_ptr(), g_scale.data_ptr(), zb_ff.data_ptr(), dummy.data_ptr(), u_scale.data_ptr(),
+                     zb_ff.data_ptr(), s_row.data_ptr(), b_exp.data_ptr(), xq.data_ptr(), xs.data_ptr(), fq.data_ptr(),
+                     fs.data_ptr(), embd, ff, max_blocks, 1.702, 7.0, 1.0, st)
+        assert rc == 0, rc
+        rc = down(d_data.data_ptr(), d_scale.data_ptr(), zb_embd.data_ptr(), s_row.data_ptr(), s_slot.data_ptr(),
+                  b_exp.data_ptr(), w.data_ptr(), fq.data_ptr(), fs.data_ptr(), part.data_ptr(), ff, embd, k, max_blocks,
+                  st)
+        assert rc == 0, rc
+        pk.call("moe_slot_combine", part, out, embd, k, T, stream=st)
+
+    sec = time_launches(step, a.iters)
+    distinct = 0
+    for lg in logits:
+        distinct += torch.unique(torch.topk(lg.view(T, n_expert), k, dim=1).indices).numel()
+    distinct /= n_sets
+    per_expert = 3 * embd * ff // 32 * 17
+    return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
+
+
 def bench_moe(ex, a):
     """BASELINE config 5: 128 experts, top-4, hidden = ff = 2880, T = --m tokens."""
     from . import planes as P
+    if a.pack:
+        return bench_moe_other_pack(ex, a)
     n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
     bm = 8 if T * k <= 1024 else 32
     blocks_per_plane = n_expert * embd * ff // 32

@@ -186,6 +186,14 @@ class KernelPack:
             self._fns[name] = _proto(_SIGS[name])(addr)
         return self._fns[name]
 
+    def fn_at(self, idx, sig):
+        """Slot `idx` with signature string `sig` (for slots this package does not name, e.g. when
+        timing another pack)."""
+        addr = self.slot_ptr(idx)
+        if addr == 0:
+            raise MissingOp(f"slot {idx}")
+        return _proto(sig)(addr)
+
     def extra(self, symbol):
         """A named export that has no table slot."""
         if symbol not in self._fns:

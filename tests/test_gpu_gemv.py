@@ -132,7 +132,7 @@ def test_q4_k_gemv_refuses_bad_shapes(pack):
     buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     assert pack.status("kquant_gemv", buf, buf, buf, buf, 128, 4, 12) == 1     # K not a multiple of 256
     assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 99) == 1     # unknown dtype
-    assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 13) == 801   # Q5_K not built
+    assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 23) == 801   # IQ4_XS: known, not built
     assert pack.status("pdk_kquant_gemm_f32", buf, buf, buf, buf, 256, 4, 65, 12) == 1
 
 
@@ -182,3 +182,50 @@ def test_q4k_w4a8_slots(pack, k, n, batch):
         y = d_y.cpu().numpy().reshape(batch, n)
         # batches above 4 run the bf16-activation kernel: q * scale is rounded to 8 significant bits
         assert cond_err(y, ref, ab) < (1e-4 if batch <= 4 else 1e-3) < TOL, name
+
+
+# ---- Q5_K, Q6_K, Q4_0 through the same slots
+
+def raw_kquant(name, n_super, seed):
+    """Random blocks of the raw ggml layout with finite f16 scales."""
+    nbytes, elems = oracle.KQUANT_LAYOUT[name]
+    n_blocks = n_super * 256 // elems
+    rng = np.random.default_rng(seed)
+    raw = rng.integers(0, 256, (n_blocks, nbytes), dtype=np.uint8)
+    d = (rng.random(n_blocks) * 0.01 + 1e-4).astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
+    if name == "q6_k":
+        raw[:, 208:210] = d
+    else:
+        raw[:, 0:2] = d
+        if name == "q5_k":
+            raw[:, 2:4] = (rng.random(n_blocks) * 0.01).astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
+    return raw.reshape(-1)
+
+
+KQ = {"q5_k": (13, 160), "q6_k": (14, 192), "q4_0": (2, 128)}
+
+
+@pytest.mark.parametrize("name", sorted(KQ))
+def test_more_kquants_dequant_repack_gemv(pack, name):
+    dtype, datab = KQ[name]
+    k, n = 1024, 70
+    ns = n * k // 256
+    raw = raw_kquant(name, ns, 720 + dtype)
+    want = oracle.dequant_kquant(name, raw)
+    d_y = torch.zeros(ns * 256, dtype=torch.float32, device="cuda")
+    pack.call("kquant_dequant", dev(raw), d_y, ns, dtype)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_y.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    d_data = torch.zeros(ns * datab, dtype=torch.uint8, device="cuda")
+    d_sc = torch.zeros(ns * 24, dtype=torch.uint8, device="cuda")
+    pack.call("kquant_repack", dev(raw), d_data, d_sc, ns, dtype)
+    for batch in (1, 5):
+        x = bf16_activations(batch * k, seed_for(2, 7 + batch))
+        d_out = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+        if batch == 1:
+            pack.call("kquant_gemv", d_data, d_sc, dev_f32(x), d_out, k, n, dtype)
+        else:
+            pack.call("pdk_kquant_gemm_f32", d_data, d_sc, dev_f32(x), d_out, k, n, batch, dtype)
+        torch.cuda.synchronize()
+        ref, ab = oracle.matmul_f64(want, x, k, n, batch, with_abs=True)
+        assert cond_err(d_out.cpu().numpy().reshape(batch, n), ref, ab) < 1e-5 < TOL

@@ -273,3 +273,30 @@ def test_q8_activation_quantizers_and_w4a8_gemv(pack, ref):
         return (d, sc, dev(q), dev(s), dev(sums), y, k, n, 12), [y]
     ours, theirs = (o[0].view(np.float32) for o in run_both(pack, ref, "kquant_gemv_w4a8", mkg, 1))
     assert rel_l2(ours, theirs.astype(np.float64)) < 1e-4 < TOL
+
+
+@pytest.mark.parametrize("name,dtype,datab", [("q5_k", 13, 160), ("q6_k", 14, 192), ("q4_0", 2, 128)])
+def test_more_kquants_against_reference_pack(pack, ref, name, dtype, datab):
+    from test_gpu_gemv import raw_kquant
+    k, n = 1024, 64
+    ns = n * k // 256
+    raw = raw_kquant(name, ns, 30 + dtype)
+
+    def mkd():
+        out = torch.zeros(ns * 256, dtype=torch.float32, device="cuda")
+        return (dev(raw), out, ns, dtype), [out]
+    assert_bytes_equal(run_both(pack, ref, "kquant_dequant", mkd, 1))
+
+    def mkr():
+        d = torch.zeros(ns * datab, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(ns * 24, dtype=torch.uint8, device="cuda")
+        return (dev(raw), d, s, ns, dtype), [d, s]
+    planes = run_both(pack, ref, "kquant_repack", mkr, 2)
+    assert_bytes_equal(planes)
+    x = oracle.bf16_round(oracle.fill_normal(k, 31, 1.0))
+
+    def mkg():
+        y = torch.zeros(n, dtype=torch.float32, device="cuda")
+        return (dev(planes[0][0]), dev(planes[0][1]), dev_f32(x), y, k, n, dtype), [y]
+    ours, theirs = (o[0].view(np.float32) for o in run_both(pack, ref, "kquant_gemv", mkg, 1))
+    assert rel_l2(ours, theirs.astype(np.float64)) < 1e-5 < TOL
