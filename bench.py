@@ -211,13 +211,16 @@ def run_ours(args, rank, world, local_rank):
     e1.record()
     barrier()
     total_ms = e0.elapsed_time(e1)
-    # keep the same load running until the clock sampler has a few dozen samples
-    t_end = time.time() + 0.4
-    i = 0
-    while time.time() < t_end:
+    # keep the same load running until the clock sampler has a few dozen samples (about 0.4 s).
+    # The step count must be the same on every rank - a step holds a collective - so it is
+    # derived from the slowest rank's timed region, not from each rank's own clock.
+    agreed = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+    n_extra = int(min(50000, max(64, 400.0 / max(agreed.item() / args.steps, 1e-3))))
+    for i in range(n_extra):
         step(i)
-        i += 1
-        if i % 64 == 0:
+        if i % 64 == 63:
             torch.cuda.synchronize()
     torch.cuda.synchronize()
     sampler.stop()
