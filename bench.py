@@ -114,6 +114,8 @@ def cpu_baseline(steps, warmup, rows=N_DIM // 4):
     ascending-k matvec, on all host threads.  Returns (GB/s, cores, sample, ms)."""
     import numpy as np
     import oracle
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm uses every host core
+    oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     w = oracle.fill_normal(rows * K_DIM, 0x5EED0200, 0.02)
     raw = oracle.quantize_q4_k(w)
     del w
@@ -143,7 +145,7 @@ def run_reference(args, rank):
         "impl": "reference", "metric": "q4k_gemv_weight_gbs", "value": gbs, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": max(warm, 1), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": workload_config(args.gpus),
+        "data": "synthetic", "config": workload_config(args.gpus, args.exchange),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -151,9 +153,11 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus):
+def workload_config(n_gpus, exchange="peer"):
+    how = ("each rank's GEMV stores its band into every rank's y over NVLink (peer memory)" if exchange == "peer"
+           else "NCCL all-gather of y")
     return {"workload": "Q4_K decode GEMV M=1 K=5120 N=25600 (BASELINE config 2), f32 activations holding bf16 values",
-            "sharding": "none" if n_gpus == 1 else f"N rows / {n_gpus} ranks + NCCL all-gather of y",
+            "sharding": "none" if n_gpus == 1 else f"N rows / {n_gpus} ranks, {how}",
             "l2": "cold: steps rotate over weight-plane clones totalling > 2x the 126 MB L2"}
 
 
@@ -186,7 +190,28 @@ def run_ours(args, rank, world, local_rank):
     y_host = torch.zeros(N_DIM, dtype=torch.float32).pin_memory()
     torch.cuda.synchronize()
 
+    # N > 1: the row bands are exchanged by the GEMV kernel's own stores into every rank's y over
+    # NVLink (peer memory); --exchange nccl keeps the kernel local and all-gathers y with NCCL.
+    peer_out = None
+    first_row, _ = shard.row_band(N_DIM, world, rank, align=16)
+    if world > 1 and args.exchange == "peer":
+        peer_out = shard.PeerOutput(N_DIM)
+        y_all = peer_out.local
+        # the two exchanges must agree bit for bit
+        ex.kquant_gemv(planes[0], x, y)
+        check = torch.zeros(N_DIM, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(check, y)
+        shard.gemv_into_peers(ex, planes[0], x, peer_out, first_row)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        if not torch.equal(check, y_all):
+            raise RuntimeError("peer-store exchange differs from the all-gather")
+
     def step(i):
+        if peer_out is not None:
+            shard.gemv_into_peers(ex, planes[i % n_clones], x, peer_out, first_row)
+            return
         ex.kquant_gemv(planes[i % n_clones], x, y)
         if world > 1:
             dist.all_gather_into_tensor(y_all, y)
@@ -273,7 +298,7 @@ def run_ours(args, rank, world, local_rank):
             "metric": "q4k_gemv_weight_gbs", "value": bytes_step / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": workload_config(world),
+            "data": "synthetic", "config": workload_config(world, args.exchange),
             "e2e": {"value": bytes_step / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": K_DIM * 4, "d2h_bytes_per_step": N_DIM * 4,
                     "ms_per_step": e2e_ms / args.steps},
@@ -299,6 +324,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the row bands of y reach every rank")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -255,6 +255,14 @@ int pdk_mxfp4_moe_down(const void* down_data, const void* down_scale, const void
                        const void* hscale, void* part, uint32_t ff, uint32_t embd, uint32_t n_active, uint32_t bm,
                        uint32_t max_blocks, void* stream);
 
+/* No counterpart in the reference.  Q4_K decode GEMV of one rank's row band whose epilogue stores
+ * the band into every rank's full-length y over NVLink (y_ptrs: host array of n_ranks <= 8 device
+ * pointers valid on this GPU, own buffer included; rows row0 .. row0 + out_dim) - the all-gather
+ * of a row-sharded layer done by the kernel's own stores.  Ordering against consumers on other
+ * ranks is the caller's (barrier or flag).  801 outside the GEMV kernel's plan. */
+int pdk_q4k_gemv_shard(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
+                       uint32_t n_ranks, uint32_t row0, uint32_t in_dim, uint32_t out_dim, void* stream);
+
 /* ---- MXFP4 expert GEMMs on the block-scaled tensor-core path (no counterpart in the reference,
  * whose B200 MoE kernels are mma.sync on int8 activations, packs/cuda/src/moe/mmq.cuh:139-626).
  * The repacked data plane is used as it is; the E8M0 scale plane is re-expressed once at load time

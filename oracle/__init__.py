@@ -73,6 +73,7 @@ _moe = _sig("orc_moe_mxfp4_layer", None, _u8p, _u8p, _u8p, C.c_void_p, C.c_void_
             _u32p, _f32p, _f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float)
 _fill = _sig("orc_fill_normal", None, _f32p, C.c_size_t, C.c_uint64, C.c_float)
 num_threads = _sig("orc_num_threads", C.c_int)
+set_num_threads = _sig("orc_set_num_threads", None, C.c_int)
 
 
 class DequantError(ValueError):

@@ -707,3 +707,12 @@ int orc_num_threads(void) {
     return 1;
 #endif
 }
+
+/* Threads the following calls may use (a launcher may have exported OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

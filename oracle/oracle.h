@@ -84,6 +84,7 @@ void orc_fill_normal(float* out, size_t n, uint64_t seed, float sigma);
 
 /* timing helper for the CPU baseline: threads the library will use */
 int orc_num_threads(void);
+void orc_set_num_threads(int n);
 
 #ifdef __cplusplus
 }

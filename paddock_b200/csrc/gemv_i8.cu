@@ -148,11 +148,19 @@ struct Q80 {
 
 // Shared memory: limb planes int8 [2][K] (hi, lo), 32 zero bytes,
 // xmeta float2 [K/32] = {step s_j, s_j * sum_i v_ji}, red f32 [2][kSlots][kSlices][16].
+// Row-sharded output: when n > 0 the kernel stores row r of its band at ptr[p][row0 + r] for
+// every p < n - the full-length y of each rank, peer memory over NVLink included - instead of
+// y[r].  Plain peer stores; the caller orders them (a barrier, or a flag the consumer waits on).
+struct PeerOut {
+    float* ptr[8];
+    uint32_t n, row0;
+};
+
 template <class F>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ recs, const float* __restrict__ bias,
                const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim, uint32_t out_dim,
-               const int8_t* __restrict__ xq, const float* __restrict__ xq_scale) {
+               const int8_t* __restrict__ xq, const float* __restrict__ xq_scale, const PeerOut peers) {
     using Stage = typename F::Stage;
     constexpr uint32_t DEPTH = F::kDepth;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -328,7 +336,11 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
                 const uint32_t row = c_tile * 16u + r;
                 if (row < out_dim) {
                     if (bias) v += bias[row];
-                    y[row] = v;
+                    if (peers.n == 0u) {
+                        y[row] = v;
+                    } else {
+                        for (uint32_t p = 0; p < peers.n; ++p) peers.ptr[p][peers.row0 + row] = v;
+                    }
                 }
             }
             acc_g = acc_g8 = 0.0f;
@@ -360,7 +372,8 @@ bool pdl_enabled() {
 
 template <class F>
 int launch(const void* data, const void* recs, const float* bias, const float* x, float* y, uint32_t in_dim,
-           uint32_t out_dim, cudaStream_t st, const int8_t* xq = nullptr, const float* xq_scale = nullptr) {
+           uint32_t out_dim, cudaStream_t st, const int8_t* xq = nullptr, const float* xq_scale = nullptr,
+           const PeerOut* peers = nullptr) {
     const uint32_t n_unit = in_dim >> 8;
     if ((in_dim & 255u) != 0u || n_unit < kSlices) return -1;
     const size_t smem = (size_t)in_dim * 2u + 32u + (size_t)(in_dim >> 5) * 8u + 2u * kSlots * kSlices * 16u * 4u;
@@ -382,8 +395,10 @@ int launch(const void* data, const void* recs, const float* bias, const float* x
     attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    PeerOut po{};
+    if (peers) po = *peers;
     e = cudaLaunchKernelEx(&cfg, kern, (const uint8_t*)data, (const uint8_t*)recs, bias, x, y, in_dim, out_dim, xq,
-                           xq_scale);
+                           xq_scale, po);
     return e == cudaSuccess ? pdk_launch_status() : (int)e;
 }
 
@@ -407,4 +422,28 @@ int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, con
 int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq, const float* xq_scale, float* y,
                           uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
     return launch<Q4K>(data, scales, nullptr, nullptr, y, in_dim, out_dim, st, xq, xq_scale);
+}
+
+// No counterpart in the reference (its multi-GPU story is one process per GPU, replicas only):
+// Q4_K decode GEMV of one rank's row band that writes its band straight into every rank's
+// full-length y (y_ptrs[0..n_ranks), device pointers valid on this GPU: its own buffer and the
+// peers' buffers mapped over NVLink) at rows row0 .. row0 + out_dim.  The exchange that an
+// all-gather would do is the kernel's own stores.  The stores are complete when the kernel
+// is; the caller orders consumers after it (stream order locally, a barrier or flag across
+// ranks).  n_ranks <= 8.  Returns 801 for shapes outside the GEMV kernel's plan.
+PDK_EXPORT int pdk_q4k_gemv_shard(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
+                                  uint32_t n_ranks, uint32_t row0, uint32_t in_dim, uint32_t out_dim, void* stream) {
+    if (out_dim == 0) return 0;
+    if (n_ranks == 0 || n_ranks > 8u || y_ptrs == nullptr) return cudaErrorInvalidValue;
+    if (!pdk_aligned(data, 16) || !pdk_aligned(scales, 8) || !pdk_aligned(x, 16)) return cudaErrorInvalidValue;
+    PeerOut po{};
+    for (uint32_t p = 0; p < n_ranks; ++p) {
+        if (y_ptrs[p] == nullptr || !pdk_aligned(y_ptrs[p], 4)) return cudaErrorInvalidValue;
+        po.ptr[p] = (float*)y_ptrs[p];
+    }
+    po.n = n_ranks;
+    po.row0 = row0;
+    const int rc = launch<Q4K>(data, scales, nullptr, (const float*)x, nullptr, in_dim, out_dim, (cudaStream_t)stream,
+                               nullptr, nullptr, &po);
+    return rc >= 0 ? rc : (int)cudaErrorNotSupported;
 }

@@ -114,6 +114,7 @@ _EXTRA_SIGS = {
     "pdk_mxfp4_moe_gate_up": "pppppppppppuuuuff",
     "pdk_mxfp4_moe_down": "ppppppppppuuuuu",
     "pdk_mxfp4_moe_down_combine_static": "ppppppppppuuuuuu",
+    "pdk_q4k_gemv_shard": "ppppuuuu",
     "pdk_mxfp4_tc5_tile_scales": "pppuuu",
     "pdk_moe_prep_act_f4": "pppppppuuuuff",
     "pdk_mxfp4_moe_gemm_tc5": "p" * 17 + "u" * 7,

@@ -26,3 +26,35 @@ def raw_band_bytes(n_rows, in_dim, world, rank, block_elems, block_bytes):
 def gathered_to_token_major(gathered, world, batch, rows_per_rank):
     """[G][M][N/G] all-gather result -> [M][N] view (no copy for M = 1)."""
     return gathered.view(world, batch, rows_per_rank).permute(1, 0, 2).reshape(batch, world * rows_per_rank)
+
+
+class PeerOutput:
+    """A full-length f32 output vector allocated symmetrically on every rank of `group`, with every
+    rank's copy mapped into this process over NVLink.  `ptrs` is the host array of device pointers
+    pdk_q4k_gemv_shard takes; `local` is this rank's copy as a tensor.  Multicast binding is switched
+    off (only plain peer stores are used)."""
+
+    def __init__(self, n, group=None):
+        import ctypes
+        import os
+        import torch
+        import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        self.local = symm_mem.empty(n, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        self.local.zero_()
+        self.handle = symm_mem.rendezvous(self.local, group.group_name)
+        self.world = self.handle.world_size
+        self.ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
+
+    def ptrs_address(self):
+        import ctypes
+        return ctypes.addressof(self.ptrs)
+
+
+def gemv_into_peers(ex, w, x, out, row0):
+    """This rank's Q4_K row band times x, stored at rows row0.. of every rank's `out` (PeerOutput)."""
+    import torch
+    ex.pack.call("pdk_q4k_gemv_shard", w.data, w.scales, x, out.ptrs_address(), out.world, row0, w.dims[0], w.dims[1],
+                 stream=torch.cuda.current_stream().cuda_stream)
