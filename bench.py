@@ -208,12 +208,18 @@ def run_ours(args, rank, world, local_rank):
         if not torch.equal(check, y_all):
             raise RuntimeError("peer-store exchange differs from the all-gather")
 
+    # one pre-bound launcher per plane clone (arguments converted once; the call is the C ABI entry)
+    st = torch.cuda.current_stream().cuda_stream
+    if peer_out is not None:
+        bound = [ex.pack.bind("pdk_q4k_gemv_shard", p.data, p.scales, x, peer_out.ptrs_address(), world, first_row,
+                              p.dims[0], p.dims[1], stream=st) for p in planes]
+    else:
+        bound = [ex.pack.bind("kquant_gemv", p.data, p.scales, x, y, p.dims[0], p.dims[1], p.ty, stream=st)
+                 for p in planes]
+
     def step(i):
-        if peer_out is not None:
-            shard.gemv_into_peers(ex, planes[i % n_clones], x, peer_out, first_row)
-            return
-        ex.kquant_gemv(planes[i % n_clones], x, y)
-        if world > 1:
+        bound[i % n_clones]()
+        if world > 1 and peer_out is None:
             dist.all_gather_into_tensor(y_all, y)
 
     def barrier():

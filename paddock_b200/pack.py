@@ -218,6 +218,20 @@ class KernelPack:
         if rc != 0:
             raise LaunchError(name, rc)
 
+    def bind(self, name, *args, stream=0):
+        """A zero-argument callable that launches `name` with these arguments (converted once): for
+        loops where the per-call argument marshalling would rival a short kernel's run time.  The
+        tensors behind the pointers must outlive it; it raises LaunchError like call()."""
+        f = self.extra(name) if name in _EXTRA_SIGS else self.fn(name)
+        conv = tuple(_arg(a) for a in args) + (stream,)
+
+        def launch():
+            rc = f(*conv)
+            if rc != 0:
+                raise LaunchError(name, rc)
+        launch.keep = args
+        return launch
+
     def status(self, name, *args, stream=0):
         """Like call() but returns the raw status instead of raising."""
         f = self.extra(name) if name in _EXTRA_SIGS else self.fn(name)

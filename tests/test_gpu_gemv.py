@@ -229,3 +229,23 @@ def test_more_kquants_dequant_repack_gemv(pack, name):
         torch.cuda.synchronize()
         ref, ab = oracle.matmul_f64(want, x, k, n, batch, with_abs=True)
         assert cond_err(d_out.cpu().numpy().reshape(batch, n), ref, ab) < 1e-5 < TOL
+
+
+def test_q4k_gemv_shard_stores_band_into_every_output(pack):
+    """pdk_q4k_gemv_shard with two destination vectors on one GPU (the multi-GPU case points the
+    second at a peer's buffer): both receive the band at row0, bit-identical to kquant_gemv."""
+    import ctypes
+    k, n, full, row0 = 5120, 512, 2048, 1024
+    w = oracle.fill_normal(n * k, 730, 0.02)
+    raw, d_data, d_sc = q4k_planes(pack, w, n, k)
+    x = dev_f32(bf16_activations(k, seed_for(2, 9)))
+    d_ref = torch.zeros(n, dtype=torch.float32, device="cuda")
+    pack.call("kquant_gemv", d_data, d_sc, x, d_ref, k, n, 12)
+    outs = [torch.full((full,), -1.0, dtype=torch.float32, device="cuda") for _ in range(2)]
+    ptrs = (ctypes.c_void_p * 2)(*[o.data_ptr() for o in outs])
+    pack.call("pdk_q4k_gemv_shard", d_data, d_sc, x, ctypes.addressof(ptrs), 2, row0, k, n)
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o[row0:row0 + n], d_ref)
+        assert bool((o[:row0] == -1.0).all()) and bool((o[row0 + n:] == -1.0).all())
+    assert pack.status("pdk_q4k_gemv_shard", d_data, d_sc, x, ctypes.addressof(ptrs), 9, row0, k, n) == 1
