@@ -255,6 +255,13 @@ int pdk_mxfp4_moe_down(const void* down_data, const void* down_scale, const void
                        const void* hscale, void* part, uint32_t ff, uint32_t embd, uint32_t n_active, uint32_t bm,
                        uint32_t max_blocks, void* stream);
 
+/* No counterpart in the reference (whose mbarrier waits spin without a bound).  Self-test of the
+ * bounded wait under every tcgen05 kernel of this pack: one warp waits on a barrier that nothing
+ * arrives on; returns 0 when the wait gave up after about budget_us microseconds (1..100000)
+ * and the kernel returned normally, after which pdk_device_error() reads 0x507.  scratch = 4
+ * bytes of device memory.  Synchronizes the stream. */
+int pdk_selftest_bounded_wait(uint32_t budget_us, void* scratch, void* stream);
+
 /* No counterpart in the reference.  Q4_K decode GEMV of one rank's row band whose epilogue stores
  * the band into every rank's full-length y over NVLink (y_ptrs: host array of n_ranks <= 8 device
  * pointers valid on this GPU, own buffer included; rows row0 .. row0 + out_dim) - the all-gather

@@ -130,3 +130,43 @@ int pdk_make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : cudaErrorInvalidValue;
 }
+
+// ---------------------------------------------------------------- bounded-wait self-test
+namespace {
+// One warp waits on a barrier that nothing ever arrives on.  The wait must give up after
+// `budget_ns`, record kErrTestWait in the error word and let the kernel return normally.
+__global__ void bounded_wait_selftest_kernel(unsigned long long budget_ns, unsigned int* err_word, unsigned int* done) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        tc5::mbar_init(&bar, 1);
+        abort_flag = 0;
+        tc5::mbar_fence_init();
+    }
+    __syncthreads();
+    const tc5::WaitCtx ctx{&abort_flag, err_word};
+    const bool ok = tc5::mbar_wait(&bar, 0u, ctx, tc5::kErrTestWait, 7u, budget_ns);
+    __syncthreads();
+    if (threadIdx.x == 0) *done = ok ? 2u : 1u;  // 1 = gave up as designed
+}
+}  // namespace
+
+// No counterpart in the reference (whose mbarrier waits are unbounded).  Runs the timed-out
+// path of the wait every tcgen05 kernel here is built on: returns 0 when the wait gave up after
+// about budget_us microseconds (1..100000) and the kernel exited normally; pdk_device_error()
+// then reads (kErrTestWait << 8 | 7).  `scratch` is 4 bytes of device memory.  Synchronizes.
+PDK_EXPORT int pdk_selftest_bounded_wait(uint32_t budget_us, void* scratch, void* stream) {
+    if (budget_us == 0 || budget_us > 100000u || scratch == nullptr) return cudaErrorInvalidValue;
+    auto st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(scratch, 0, 4, st);
+    if (e != cudaSuccess) return (int)e;
+    bounded_wait_selftest_kernel<<<1, 32, 0, st>>>((unsigned long long)budget_us * 1000ull, pdk_error_word(),
+                                                   (unsigned int*)scratch);
+    if (int rc = pdk_launch_status()) return rc;
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return (int)e;
+    unsigned int done = 0;
+    e = cudaMemcpy(&done, scratch, 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return (int)e;
+    return done == 1u ? 0 : (int)cudaErrorUnknown;
+}

@@ -74,14 +74,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // caller must then abandon its loop).  `abort_flag` lets the other roles of the
 // CTA leave early once one of them has given up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, unsigned int code,
-                                          unsigned int detail) {
+                                          unsigned int detail, unsigned long long budget_ns = kWaitBudgetNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 63u) == 0u) {
             if (*ctx.abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+            if (globaltimer_ns() - t0 > budget_ns) {
                 *ctx.abort_flag = 1;
                 report(ctx.err, code, detail);
                 return false;

@@ -84,3 +84,20 @@ def test_f8row_gemm_refuses_bad_shapes(pack):
     assert pack.status("f8row_gemm", buf, buf, buf, buf, buf, 100, 8, 8) == 1        # K % 16
     assert pack.status("f8row_gemm", buf.data_ptr() + 8, buf, buf, buf, buf, 128, 8, 8) == 1
     assert pack.status("f8row_gemm", buf, buf, buf, buf, buf, 128, 0, 8) == 0
+
+
+def test_bounded_wait_gives_up_and_reports(pack):
+    """The wait under every tcgen05 kernel: a barrier nothing arrives on must time out after the
+    budget, leave its code in the error word and let the kernel return; the context stays usable."""
+    import time
+    scratch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert pack.device_error() == 0
+    t0 = time.perf_counter()
+    assert pack.status("pdk_selftest_bounded_wait", 2000, scratch) == 0      # 2 ms budget
+    dt = time.perf_counter() - t0
+    assert 0.001 < dt < 1.0
+    assert pack.device_error() == (5 << 8 | 7)
+    assert pack.device_error() == 0                                          # read clears
+    assert pack.status("pdk_selftest_bounded_wait", 0, scratch) == 1
+    y = torch.ones(8, device="cuda") * 2                                     # the context still works
+    assert float(y.sum()) == 16.0
