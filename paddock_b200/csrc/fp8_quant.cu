@@ -131,6 +131,22 @@ int pdk_make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_
     return r == CUDA_SUCCESS ? 0 : cudaErrorInvalidValue;
 }
 
+int pdk_make_tmap_2d_dense(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
+                           uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_inner, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    if (((uintptr_t)base & 15u) || (pitch & 15u) || box_inner > 256u || ((box_inner * elem_bytes) & 15u) || box_rows > 256u)
+        return cudaErrorInvalidValue;
+    const cuuint64_t gdim[2] = {inner, rows};
+    const cuuint64_t gstride[1] = {pitch};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estride[2] = {1u, 1u};
+    const CUresult r = enc(map, dtype, 2u, const_cast<void*>(base), gdim, gstride, box, estride,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : cudaErrorInvalidValue;
+}
+
 // ---------------------------------------------------------------- bounded-wait self-test
 namespace {
 // One warp waits on a barrier that nothing ever arrives on.  The wait must give up after

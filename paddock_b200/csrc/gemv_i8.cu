@@ -339,7 +339,9 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
                     if (peers.n == 0u) {
                         y[row] = v;
                     } else {
-                        for (uint32_t p = 0; p < peers.n; ++p) peers.ptr[p][peers.row0 + row] = v;
+#pragma unroll
+                        for (uint32_t p = 0; p < 8u; ++p)  // constant indices: the pointers stay in the parameter bank
+                            if (p < peers.n) peers.ptr[p][peers.row0 + row] = v;
                     }
                 }
             }

@@ -36,6 +36,12 @@ template <>
 __device__ __forceinline__ void store_one<__nv_bfloat16>(__nv_bfloat16* p, float v) {
     __stcs(reinterpret_cast<unsigned short*>(p), __bfloat16_as_ushort(__float2bfloat16_rn(v)));
 }
+template <typename TO>
+__device__ __forceinline__ void store_one_smem(TO* p, float v);
+template <>
+__device__ __forceinline__ void store_one_smem<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_one_smem<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 // XT: the activation scales come pre-tiled (the weight scales' record layout, one record
 // per 128 tokens and slab) and are bulk-copied; otherwise they are row-major and gathered.
@@ -44,13 +50,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  const uint8_t* __restrict__ w_sf_tiled, const uint8_t* __restrict__ x_sf,
                  const float* __restrict__ bias, TO* __restrict__ y, float scale2, uint32_t in_dim, uint32_t out_dim,
-                 uint32_t batch, unsigned int* err_word) {
+                 uint32_t batch, unsigned int* err_word, const __grid_constant__ CUtensorMap tmap_y,
+                 const uint32_t tma_out) {
     constexpr uint32_t kStages = Cfg<BN>::kStages, kBBytes = Cfg<BN>::kBBytes, kStageBytes = Cfg<BN>::kStageBytes;
     constexpr uint32_t kSfCol0 = Cfg<BN>::kSfCol0, kIdesc = Cfg<BN>::kIdesc, kSfCols = Cfg<BN>::kSfCols;
     constexpr uint32_t kOffB = Cfg<BN>::kOffB, kOffSfa = Cfg<BN>::kOffSfa, kOffSfb = Cfg<BN>::kOffSfb;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * kStageBytes);
+    // tma_out: output staging [32 tokens][128 channels] behind the control block (16-byte aligned)
+    TO* stage_out = reinterpret_cast<TO*>(tiles + kStages * kStageBytes + 128u);
+    static_assert(sizeof(Shared) <= 128u, "control block");
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t tiles_w = (out_dim + BM - 1u) / BM, tiles_t = (batch + BN - 1u) / BN;
@@ -240,6 +250,20 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 uint32_t r[32];
                 tc5::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + buf * BN + c * 32u, r);
                 tc5::tmem_ld_wait();
+                if (tma_out) {
+                    // the four epilogue warps fill a dense [32 tokens][128 channels] box, one thread
+                    // stores it with TMA (whole lines; rows and channels past the end are clipped)
+                    if (threadIdx.x == 64u) tc5::tma_store_wait_read();
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+                    for (uint32_t i = 0; i < 32u; ++i)
+                        store_one_smem<TO>(stage_out + i * BM + quarter * 32u + lane,
+                                           fmaf(__uint_as_float(r[i]), scale2, b));
+                    fence_proxy_async_smem();
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    if (threadIdx.x == 64u) tc5::tma_store_2d(&tmap_y, stage_out, (int32_t)w0, (int32_t)(t0 + c * 32u));
+                    continue;
+                }
                 if (n < out_dim) {
 #pragma unroll
                     for (uint32_t i = 0; i < 32u; ++i) {
@@ -254,6 +278,7 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
     }
 
+    if (tma_out && threadIdx.x == 64u) tc5::tma_store_wait_all();  // the staging box is read until then
     tc5::fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -270,7 +295,15 @@ int launch_bn(const void* data, const void* scale_tiled, const void* bias, const
     if (int rc = pdk_make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, data, kbytes, out_dim, kbytes, BKB, BM))
         return rc;
     if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, kbytes, batch, kbytes, BKB, BN)) return rc;
-    const size_t smem = (size_t)Cfg<BN>::kStages * Cfg<BN>::kStageBytes + sizeof(Shared) + 1024u;
+    // bf16 outputs at prefill width leave through a staged TMA store (whole 256-byte rows)
+    // when y qualifies for a tensor map; everything else stores from registers
+    CUtensorMap ty = tw;
+    uint32_t tma_out = 0u;
+    if (BN == 128u && sizeof(TO) == 2u && pdk_aligned(y, 16) && (out_dim & 7u) == 0u &&
+        pdk_make_tmap_2d_dense(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, out_dim, batch, (uint64_t)out_dim * 2u, BM,
+                               32u) == 0)
+        tma_out = 1u;
+    const size_t smem = (size_t)Cfg<BN>::kStages * Cfg<BN>::kStageBytes + 128u + (BN == 128u ? 32u * BM * 2u : 0u) + 1024u;
     auto kern = nvf4_gemm_kernel<BN, TO, XT>;
     static const cudaError_t attr_rc =  // once per process; one caller thread by the pack's contract
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -280,7 +313,7 @@ int launch_bn(const void* data, const void* scale_tiled, const void* bias, const
     if (grid > n_tiles) grid = n_tiles;
     return pdk_launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, tw, tx, (const uint8_t*)scale_tiled,
                           (const uint8_t*)xs, (const float*)bias, (TO*)y, scale2, in_dim, out_dim, batch,
-                          pdk_error_word());
+                          pdk_error_word(), ty, tma_out);
 }
 
 // Scratch for the re-tiled activation scales of prefill-width calls: a 4-byte gather per

@@ -132,6 +132,20 @@ __device__ __forceinline__ void bulk_load_elect(void* smem_dst, const void* gmem
                  : "memory");
 }
 
+// 2-D tiled store of a dense (unswizzled) shared-memory box; rows / columns past the tensor's
+// extent are clipped by the hardware.  One thread issues; tma_store_wait_read() before the box
+// is overwritten.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(m),
+                 "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- tensor memory -----------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols) {  // one full warp
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
@@ -228,3 +242,6 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Returns 0 or a cudaError_t.
 int pdk_make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
                      uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_inner, uint32_t box_rows);
+// The same without swizzle (dense boxes, for stores): box_inner up to 256 elements.
+int pdk_make_tmap_2d_dense(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
+                           uint64_t inner, uint64_t rows, uint64_t pitch, uint32_t box_inner, uint32_t box_rows);

@@ -27,7 +27,8 @@ def test_topk_matches_oracle(pack, tokens, n_expert, k):
     assert np.allclose(d_w.cpu().numpy().reshape(tokens, k), w_ref, rtol=2e-6, atol=0)
 
 
-@pytest.mark.parametrize("tokens,n_expert,k,bm", [(1, 128, 4, 8), (64, 128, 4, 8), (200, 16, 4, 32), (1024, 128, 4, 32)])
+@pytest.mark.parametrize("tokens,n_expert,k,bm", [(1, 128, 4, 8), (64, 128, 4, 8), (200, 16, 4, 32), (1024, 128, 4, 32),
+                                                    (1500, 8, 2, 32), (60, 2048, 2, 8)])   # many chunks; the scan kernel (experts > 1500)
 def test_align_is_a_stable_grouping(pack, tokens, n_expert, k, bm):
     rng = np.random.default_rng(tokens)
     idx = np.stack([rng.permutation(n_expert)[:k] for _ in range(tokens)]).astype(np.uint32)
