@@ -300,6 +300,26 @@ int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w
                            uint32_t out_dim, uint32_t n_expert, uint32_t bm, uint32_t max_blocks, uint32_t n_active,
                            uint32_t scatter, void* stream);
 
+/* ---- NVFP4 expert planes on the same grouped GEMM (plane layout of
+ * crates/paddock-engine/src/gpu/types.rs:176-226, Row order: data [expert*rows][in/2], scale e4m3
+ * [expert*rows][in/16], scale2 f32[expert]).  No slot: the reference's NVFP4 MoE kernels read its
+ * Tiled64 / CutBlk orders. */
+/* scale -> tiled records u8[n_expert][ceil(rows/128)][ceil(in_dim/256)][2048]; in_dim % 64 == 0 */
+int pdk_nvf4_moe_tile_scales(const void* scale, void* tiled, uint32_t rows, uint32_t in_dim, uint32_t n_expert,
+                             void* stream);
+/* pdk_moe_prep_act_f4 with the natural element order of NVFP4 planes.  mode 0 gather; mode 1 gated
+ * unit (min(g, limit) * sigmoid(alpha * that)) * (clamp(u, +-limit) + up_add); mode 2 relu(x)^2. */
+int pdk_moe_prep_act_f4n(const void* x, const void* up, const void* sorted_row, const void* block_expert, void* xq,
+                         void* xs, void* xstep, uint32_t dim, uint32_t bm, uint32_t max_blocks, uint32_t mode,
+                         float alpha, float limit, float up_add, void* stream);
+/* pdk_mxfp4_moe_gemm_tc5 with w*_sf from pdk_nvf4_moe_tile_scales and w*_scale2 f32[n_expert] */
+int pdk_nvf4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w0_scale2, const void* w0_bias, void* out0,
+                          const void* w1_data, const void* w1_sf, const void* w1_scale2, const void* w1_bias, void* out1,
+                          const void* xq, const void* xs, const void* xstep, const void* block_expert,
+                          const void* sorted_row, const void* sorted_slot, const void* topk_w, uint32_t in_dim,
+                          uint32_t out_dim, uint32_t n_expert, uint32_t bm, uint32_t max_blocks, uint32_t n_active,
+                          uint32_t scatter, void* stream);
+
 /* No counterpart in the reference.  pdk_mxfp4_moe_down + pd_moe_slot_combine for callers that may
  * not allocate device memory (a serving loop that must stay off the allocator, a plug-in handed
  * pointers by its host, a process with a memory budget fixed at start-up): the per-(token, slot)

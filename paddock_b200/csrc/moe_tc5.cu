@@ -78,6 +78,23 @@ __global__ void mxfp4_tile_scales_kernel(const uint8_t* __restrict__ scale, uint
     }
 }
 
+// NVFP4 expert planes carry UE4M3 per-16 scales already: scale u8 [expert][rows][in_dim/16]
+// -> the same records, byte l*16 + c*4 + b of cell j = scale[row rt*128 + c*32 + l][kb*16 + j*4 + b].
+__global__ void nvf4_moe_tile_scales_kernel(const uint8_t* __restrict__ scale, uint32_t* __restrict__ tiled,
+                                            uint32_t rows, uint32_t sf_row, uint32_t row_tiles, uint32_t num_kb) {
+    const uint32_t expert = blockIdx.y;
+    const uint32_t words = row_tiles * num_kb * 512u;
+    for (uint32_t w = blockIdx.x * blockDim.x + threadIdx.x; w < words; w += gridDim.x * blockDim.x) {
+        const uint32_t c = w & 3u, l = (w >> 2) & 31u, j = (w >> 7) & 3u, rec = w >> 9;
+        const uint32_t kb = rec % num_kb, rt = rec / num_kb;
+        const uint32_t row = rt * 128u + c * 32u + l, off = kb * 16u + j * 4u;
+        uint32_t out = 0u;
+        if (row < rows && off < sf_row)  // sf_row % 4 == 0
+            out = *reinterpret_cast<const uint32_t*>(scale + ((size_t)expert * rows + row) * sf_row + off);
+        tiled[(size_t)expert * words + w] = out;
+    }
+}
+
 // ---------------------------------------------------------------- activations: four NVFP4 terms
 
 __device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
@@ -107,8 +124,9 @@ struct PrepArgs {
     uint8_t* xq;                 // [blocks][4*bm][dim/2]
     uint8_t* xs;                 // tiled: [blocks][slab][4 cells][512], the weight scale records' layout
     float* xstep;                // [positions] power of two the row was divided by
-    uint32_t dim, bm, mode;
-    float alpha, limit;
+    uint32_t dim, bm, mode;  // mode 0 gather, 1 gated (x = gate, up), 2 relu(x)^2 of x [positions][dim]
+    uint32_t natural;        // 0: ggml MXFP4 element order (byte j = elements j, j+16); 1: byte j = elements 2j, 2j+1
+    float alpha, limit, up_add;
 };
 
 // One CTA per block position.  Position (block b, token i) writes the four term rows
@@ -136,12 +154,25 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
             const float4 t = *reinterpret_cast<const float4*>(urow + off + 4u);
             const float u[8] = {r.x, r.y, r.z, r.w, t.x, t.y, t.z, t.w};
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {  // SwiGLU, OpenAI variant (reference/ops.rs:27-36)
+            for (int k = 0; k < 8; ++k) {
+                // gated unit: (xg * sigmoid(alpha * xg)) * (yu + up_add); OpenAI variant (reference/ops.rs:27-36)
+                // = alpha 1.702, limit 7, up_add 1; plain SwiGLU = alpha 1, limit inf, up_add 0
                 const float xg = fminf(v[k], a.limit);
                 const float yu = fminf(fmaxf(u[k], -a.limit), a.limit);
-                v[k] = (xg / (1.0f + __expf(-a.alpha * xg))) * (yu + 1.0f);
+                v[k] = (xg / (1.0f + __expf(-a.alpha * xg))) * (yu + a.up_add);
+            }
+        } else if (a.mode == 2u) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float r = fmaxf(v[k], 0.0f);
+                v[k] = r * r;
             }
         }
+    };
+    // first element of scale group g's two 8-runs
+    auto run_base = [&](uint32_t g, uint32_t& lo_at, uint32_t& hi_at) {
+        if (a.natural) { lo_at = g * 16u; hi_at = g * 16u + 8u; }
+        else { lo_at = (g >> 1) * 32u + (g & 1u) * 8u; hi_at = lo_at + 16u; }
     };
 
     // ---- the row's largest magnitude -> the power of two that brings it into [256, 512).
@@ -153,9 +184,10 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
     float amax = 0.0f;
     if (!pad)
         for (uint32_t g = tid; g < groups; g += blockDim.x) {
-            const uint32_t base = (g >> 1) * 32u + (g & 1u) * 8u;
-            load8(base, lo0);
-            load8(base + 16u, hi0);
+            uint32_t lo_at, hi_at;
+            run_base(g, lo_at, hi_at);
+            load8(lo_at, lo0);
+            load8(hi_at, hi0);
 #pragma unroll
             for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fmaxf(fabsf(lo0[k]), fabsf(hi0[k])));
         }
@@ -187,9 +219,10 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
         }
         float lo[8], hi[8];
         if (live && !single) {
-            const uint32_t base = (g >> 1) * 32u + (g & 1u) * 8u;
-            load8(base, lo0);
-            load8(base + 16u, hi0);
+            uint32_t lo_at, hi_at;
+            run_base(g, lo_at, hi_at);
+            load8(lo_at, lo0);
+            load8(hi_at, hi0);
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -211,12 +244,28 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
             }
             uint32_t w0 = 0u, w1 = 0u;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                float bl, bh;
-                const uint32_t byte = e2m1x2_rn(lo[k] * inv, hi[k] * inv, bl, bh);
-                if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
-                lo[k] = (lo[k] - bl * sc) * 16.0f;
-                hi[k] = (hi[k] - bh * sc) * 16.0f;
+            if (!a.natural) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {  // byte k = (lo run k, hi run k)
+                    float bl, bh;
+                    const uint32_t byte = e2m1x2_rn(lo[k] * inv, hi[k] * inv, bl, bh);
+                    if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
+                    lo[k] = (lo[k] - bl * sc) * 16.0f;
+                    hi[k] = (hi[k] - bh * sc) * 16.0f;
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {  // byte k = lo run (2k, 2k+1); byte 4+k = hi run (2k, 2k+1)
+                    float b0, b1;
+                    uint32_t byte = e2m1x2_rn(lo[2 * k] * inv, lo[2 * k + 1] * inv, b0, b1);
+                    w0 |= byte << (8 * k);
+                    lo[2 * k] = (lo[2 * k] - b0 * sc) * 16.0f;
+                    lo[2 * k + 1] = (lo[2 * k + 1] - b1 * sc) * 16.0f;
+                    byte = e2m1x2_rn(hi[2 * k] * inv, hi[2 * k + 1] * inv, b0, b1);
+                    w1 |= byte << (8 * k);
+                    hi[2 * k] = (hi[2 * k] - b0 * sc) * 16.0f;
+                    hi[2 * k + 1] = (hi[2 * k + 1] - b1 * sc) * 16.0f;
+                }
             }
             const size_t r = r0 + (size_t)term * a.bm;
             *reinterpret_cast<uint2*>(a.xq + r * kh + (size_t)g * 8u) = make_uint2(w0, w1);
@@ -230,7 +279,7 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
 
 struct GemmArgs {
     const uint8_t* w_sf[2];      // tiled UE4M3 weight scales per plane
-    const float* scale2[2];      // per-plane factor (device memory)
+    const float* scale2[2];      // per-plane factor (device memory), or per expert when scale2_per_expert
     const float* bias[2];        // [expert][out_dim] or null
     float* out[2];               // gate / up: [positions][out_dim]; down: part [(row, slot)][out_dim]
     const uint8_t* x_sf;         // tiled [blocks][slab][2048]
@@ -239,7 +288,7 @@ struct GemmArgs {
     const uint32_t* sorted_row;
     const uint32_t* sorted_slot;  // down only
     const float* topk_w;          // down only
-    uint32_t in_dim, out_dim, max_blocks, n_planes, n_active, scatter;
+    uint32_t in_dim, out_dim, max_blocks, n_planes, n_active, scatter, scale2_per_expert;
     unsigned int* err_word;
 };
 
@@ -429,7 +478,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
                 my_row = my_src * a.n_active + a.sorted_slot[my_pos];
                 my_wgt = a.topk_w[my_row];
             }
-            const float my_mul = a.xstep[my_pos] * *a.scale2[plane] * my_wgt;
+            const float my_mul = a.xstep[my_pos] * a.scale2[plane][a.scale2_per_expert ? expert : 0u] * my_wgt;
             const uint32_t n = rt * BM + quarter * 32u + lane;
             float bias = 0.0f;
             if (n < a.out_dim && a.bias[plane]) bias = a.bias[plane][(size_t)expert * a.out_dim + n];
@@ -502,20 +551,39 @@ PDK_EXPORT int pdk_mxfp4_tc5_tile_scales(const void* scale, void* tiled, void* m
 // Writes xq u8 [max_blocks*4*bm][dim/2], xs u8 [max_blocks][ceil(dim/256)][2048] (scale records in the
 // weight scale records' layout; bytes of term rows a block does not have are left alone), xstep f32 [max_blocks*bm].
 // dim % 32 == 0, bm 8 or 32.
-PDK_EXPORT int pdk_moe_prep_act_f4(const void* x, const void* up, const void* sorted_row, const void* block_expert,
-                                   void* xq, void* xs, void* xstep, uint32_t dim, uint32_t bm, uint32_t max_blocks, uint32_t mode,
-                                   float alpha, float limit, void* stream) {
+static int prep_impl(const void* x, const void* up, const void* sorted_row, const void* block_expert, void* xq, void* xs,
+                     void* xstep, uint32_t dim, uint32_t bm, uint32_t max_blocks, uint32_t mode, uint32_t natural,
+                     float alpha, float limit, float up_add, void* stream) {
     if (max_blocks == 0) return 0;
-    if (dim == 0 || (dim & 31u) != 0u || (bm != 8u && bm != 32u) || mode > 1u) return cudaErrorInvalidValue;
+    if (dim == 0 || (dim & 31u) != 0u || (bm != 8u && bm != 32u) || mode > 2u) return cudaErrorInvalidValue;
     if (!pdk_aligned(x, 16) || !pdk_aligned(xq, 16) || (mode == 1u && !pdk_aligned(up, 16))) return cudaErrorInvalidValue;
     PrepArgs a{};
     a.x = (const float*)x; a.up = (const float*)up; a.sorted_row = (const uint32_t*)sorted_row;
     a.block_expert = (const uint32_t*)block_expert;
     a.xq = (uint8_t*)xq; a.xs = (uint8_t*)xs; a.xstep = (float*)xstep;
-    a.dim = dim; a.bm = bm; a.mode = mode; a.alpha = alpha; a.limit = limit;
+    a.dim = dim; a.bm = bm; a.mode = mode; a.natural = natural; a.alpha = alpha; a.limit = limit; a.up_add = up_add;
     const uint32_t per_row = ((dim + 255u) >> 8) * 16u;  // scale groups incl. the zero tail of the last record
     return pdk_launch_pdl(moe_prep_f4_kernel, dim3(max_blocks * bm),
                           dim3(per_row <= 256u ? (per_row + 31u) & ~31u : 256u), 0, (cudaStream_t)stream, a);
+}
+
+PDK_EXPORT int pdk_moe_prep_act_f4(const void* x, const void* up, const void* sorted_row, const void* block_expert,
+                                   void* xq, void* xs, void* xstep, uint32_t dim, uint32_t bm, uint32_t max_blocks,
+                                   uint32_t mode, float alpha, float limit, void* stream) {
+    if (mode > 1u) return cudaErrorInvalidValue;
+    return prep_impl(x, up, sorted_row, block_expert, xq, xs, xstep, dim, bm, max_blocks, mode, 0u, alpha, limit, 1.0f,
+                     stream);
+}
+
+// The same for NVFP4 expert planes: term rows packed in the natural element order (byte j = elements
+// 2j, 2j+1, as ModelOpt checkpoints store their weights).  mode 0 gather; mode 1 gated unit
+// (min(g, limit) * sigmoid(alpha * that)) * (clamp(u, +-limit) + up_add) - plain SwiGLU is alpha 1,
+// limit inf, up_add 0; mode 2 relu(x)^2 of x f32 [positions][dim] (the non-gated experts).
+PDK_EXPORT int pdk_moe_prep_act_f4n(const void* x, const void* up, const void* sorted_row, const void* block_expert,
+                                    void* xq, void* xs, void* xstep, uint32_t dim, uint32_t bm, uint32_t max_blocks,
+                                    uint32_t mode, float alpha, float limit, float up_add, void* stream) {
+    return prep_impl(x, up, sorted_row, block_expert, xq, xs, xstep, dim, bm, max_blocks, mode, 1u, alpha, limit, up_add,
+                     stream);
 }
 
 // No counterpart in the reference (slots 88 / 89 are its mma.sync kernels on int8 activations):
@@ -526,18 +594,17 @@ PDK_EXPORT int pdk_moe_prep_act_f4(const void* x, const void* up, const void* so
 //              (w1_data NULL = one)
 //   scatter 1: out0 = part f32 [rows*n_active][out_dim], row (sorted_row, sorted_slot), times topk_w
 // in_dim % 64 == 0, max_blocks <= 1024.
-PDK_EXPORT int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w0_meta, const void* w0_bias,
-                                      void* out0, const void* w1_data, const void* w1_sf, const void* w1_meta,
-                                      const void* w1_bias, void* out1, const void* xq, const void* xs,
-                                      const void* xstep, const void* block_expert, const void* sorted_row,
-                                      const void* sorted_slot, const void* topk_w, uint32_t in_dim, uint32_t out_dim,
-                                      uint32_t n_expert, uint32_t bm, uint32_t max_blocks, uint32_t n_active,
-                                      uint32_t scatter, void* stream) {
+static int gemm_impl(const void* w0_data, const void* w0_sf, const float* w0_scale2, const void* w0_bias, void* out0,
+                     const void* w1_data, const void* w1_sf, const float* w1_scale2, const void* w1_bias, void* out1,
+                     const void* xq, const void* xs, const void* xstep, const void* block_expert, const void* sorted_row,
+                     const void* sorted_slot, const void* topk_w, uint32_t in_dim, uint32_t out_dim, uint32_t n_expert,
+                     uint32_t bm, uint32_t max_blocks, uint32_t n_active, uint32_t scatter, uint32_t scale2_per_expert,
+                     void* stream) {
     if (max_blocks == 0 || out_dim == 0 || n_expert == 0) return 0;
     if (in_dim == 0 || (in_dim & 63u) != 0u || (bm != 8u && bm != 32u) || max_blocks > kMaxBlocks)
         return cudaErrorInvalidValue;
     if (!pdk_aligned(w0_data, 16) || !pdk_aligned(w0_sf, 16) || !pdk_aligned(xq, 16) || !pdk_aligned(xs, 4) ||
-        !pdk_aligned(w0_meta, 8) || (w1_data && (!pdk_aligned(w1_data, 16) || !pdk_aligned(w1_sf, 16))))
+        !pdk_aligned(w0_scale2, 4) || (w1_data && (!pdk_aligned(w1_data, 16) || !pdk_aligned(w1_sf, 16))))
         return cudaErrorInvalidValue;
     if (scatter && (w1_data || !sorted_slot || !topk_w)) return cudaErrorInvalidValue;
     const uint32_t bn = 4u * bm, kbytes = in_dim >> 1;
@@ -552,7 +619,8 @@ PDK_EXPORT int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, co
         return rc;
     GemmArgs a{};
     a.w_sf[0] = (const uint8_t*)w0_sf; a.w_sf[1] = (const uint8_t*)(w1_data ? w1_sf : w0_sf);
-    a.scale2[0] = (const float*)w0_meta + 1; a.scale2[1] = (const float*)(w1_data ? w1_meta : w0_meta) + 1;
+    a.scale2[0] = w0_scale2; a.scale2[1] = w1_data ? w1_scale2 : w0_scale2;
+    a.scale2_per_expert = scale2_per_expert;
     a.bias[0] = (const float*)w0_bias; a.bias[1] = (const float*)w1_bias;
     a.out[0] = (float*)out0; a.out[1] = (float*)out1;
     a.x_sf = (const uint8_t*)xs; a.xstep = (const float*)xstep;
@@ -562,4 +630,50 @@ PDK_EXPORT int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, co
     a.n_active = n_active; a.scatter = scatter; a.err_word = pdk_error_word();
     auto st = (cudaStream_t)stream;
     return bm == 8u ? launch_gemm<32>(tw0, tw1, tx, a, st) : launch_gemm<128>(tw0, tw1, tx, a, st);
+}
+
+PDK_EXPORT int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w0_meta, const void* w0_bias,
+                                      void* out0, const void* w1_data, const void* w1_sf, const void* w1_meta,
+                                      const void* w1_bias, void* out1, const void* xq, const void* xs,
+                                      const void* xstep, const void* block_expert, const void* sorted_row,
+                                      const void* sorted_slot, const void* topk_w, uint32_t in_dim, uint32_t out_dim,
+                                      uint32_t n_expert, uint32_t bm, uint32_t max_blocks, uint32_t n_active,
+                                      uint32_t scatter, void* stream) {
+    if (!pdk_aligned(w0_meta, 8) || w0_meta == nullptr || (w1_data && w1_meta == nullptr)) return cudaErrorInvalidValue;
+    return gemm_impl(w0_data, w0_sf, (const float*)w0_meta + 1, w0_bias, out0, w1_data, w1_sf,
+                     w1_meta ? (const float*)w1_meta + 1 : nullptr, w1_bias, out1, xq, xs, xstep, block_expert, sorted_row,
+                     sorted_slot, topk_w, in_dim, out_dim, n_expert, bm, max_blocks, n_active, scatter, 0u, stream);
+}
+
+// ---- NVFP4 expert planes (crates/paddock-engine/src/gpu/types.rs:176-226: data [expert*rows][in/2],
+// scale e4m3 [expert*rows][in/16], scale2 f32 [expert]) on the same grouped GEMM.  No counterpart slot
+// is served: the reference's NVFP4 MoE kernels take its Tiled64 / CutBlk plane orders.
+
+// scale -> tiled records [n_expert][ceil(rows/128)][ceil(in_dim/256)][2048].  in_dim % 64 == 0.
+PDK_EXPORT int pdk_nvf4_moe_tile_scales(const void* scale, void* tiled, uint32_t rows, uint32_t in_dim,
+                                        uint32_t n_expert, void* stream) {
+    if (rows == 0 || n_expert == 0) return 0;
+    if (in_dim == 0 || (in_dim & 63u) != 0u || !pdk_aligned(tiled, 16) || !pdk_aligned(scale, 4))
+        return cudaErrorInvalidValue;
+    const uint32_t row_tiles = (rows + 127u) / 128u, num_kb = (in_dim + 255u) >> 8;
+    const uint32_t words = row_tiles * num_kb * 512u;
+    nvf4_moe_tile_scales_kernel<<<dim3((words + 255u) / 256u < 64u ? (words + 255u) / 256u : 64u, n_expert), 256, 0,
+                                  (cudaStream_t)stream>>>((const uint8_t*)scale, (uint32_t*)tiled, rows, in_dim >> 4,
+                                                          row_tiles, num_kb);
+    return pdk_launch_status();
+}
+
+// pdk_mxfp4_moe_gemm_tc5 with NVFP4 planes: w*_sf from pdk_nvf4_moe_tile_scales, w*_scale2 f32 [n_expert],
+// term rows from pdk_moe_prep_act_f4n.
+PDK_EXPORT int pdk_nvf4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w0_scale2, const void* w0_bias,
+                                     void* out0, const void* w1_data, const void* w1_sf, const void* w1_scale2,
+                                     const void* w1_bias, void* out1, const void* xq, const void* xs, const void* xstep,
+                                     const void* block_expert, const void* sorted_row, const void* sorted_slot,
+                                     const void* topk_w, uint32_t in_dim, uint32_t out_dim, uint32_t n_expert,
+                                     uint32_t bm, uint32_t max_blocks, uint32_t n_active, uint32_t scatter,
+                                     void* stream) {
+    if (w0_scale2 == nullptr || (w1_data && w1_scale2 == nullptr)) return cudaErrorInvalidValue;
+    return gemm_impl(w0_data, w0_sf, (const float*)w0_scale2, w0_bias, out0, w1_data, w1_sf, (const float*)w1_scale2,
+                     w1_bias, out1, xq, xs, xstep, block_expert, sorted_row, sorted_slot, topk_w, in_dim, out_dim,
+                     n_expert, bm, max_blocks, n_active, scatter, 1u, stream);
 }

@@ -119,6 +119,9 @@ _EXTRA_SIGS = {
     "pdk_mxfp4_tc5_tile_scales": "pppuuu",
     "pdk_moe_prep_act_f4": "pppppppuuuuff",
     "pdk_mxfp4_moe_gemm_tc5": "p" * 17 + "u" * 7,
+    "pdk_nvf4_moe_tile_scales": "ppuuu",
+    "pdk_moe_prep_act_f4n": "pppppppuuuufff",
+    "pdk_nvf4_moe_gemm_tc5": "p" * 17 + "u" * 7,
 }
 _KIND = {"p": C.c_void_p, "u": C.c_uint32, "U": C.c_uint64, "f": C.c_float}
 

@@ -220,3 +220,59 @@ def moe_mxfp4_forward(ex, planes, ws, x, router_logits, out, alpha=1.702, limit=
         moe_mxfp4_experts(ex, planes, ws, x, T, alpha, limit)
     c("moe_slot_combine", ws.part, out, planes.embd, k, T, stream=st)
     return 7  # launches
+
+
+# ---- NVFP4 expert planes (gpu/types.rs:176-226, Row order) on the same grouped GEMM
+
+@dataclass
+class Nvf4MoePlane:
+    data: torch.Tensor      # u8 [n_expert*rows][in_dim/2]
+    scale: torch.Tensor     # e4m3 [n_expert*rows][in_dim/16]
+    scale2: torch.Tensor    # f32 [n_expert]
+    n_expert: int
+    rows: int
+    in_dim: int
+    tiled: torch.Tensor = None
+
+
+def nvf4_moe_prepare(ex, plane):
+    """Load-time: tile the plane's per-16 scales into scale records (pdk_nvf4_moe_tile_scales)."""
+    if plane.tiled is None:
+        n = plane.n_expert * ((plane.rows + 127) // 128) * ((plane.in_dim + 255) // 256) * 2048
+        plane.tiled = torch.empty(n, dtype=torch.uint8, device=ex.device)
+        ex.pack.call("pdk_nvf4_moe_tile_scales", plane.scale, plane.tiled, plane.rows, plane.in_dim, plane.n_expert,
+                     stream=_stream())
+    return plane
+
+
+def moe_nvf4_forward(ex, gate, up, down, ws, x, router_logits, out, gated=True, alpha=1.0, limit=float("inf"),
+                     up_add=0.0, router_bias=None):
+    """NVFP4 MoE block: top-k -> align -> term rows -> up (and gate) GEMM -> activation + term rows -> down
+    GEMM -> combine.  gated: silu-gated unit (plain SwiGLU by default); else relu(up x)^2 (gate ignored).
+    ws is a MoeWorkspace built for an object with n_expert / embd / ff attributes."""
+    st = _stream()
+    c = ex.pack.call
+    T, k, bm = ws.tokens, ws.n_active, ws.bm
+    n_expert, embd, ff = up.n_expert, up.in_dim, up.rows
+    c("moe_topk_batch", router_logits, router_bias, n_expert, k, ws.idx, ws.w, T, stream=st)
+    max_blocks = min(ws.max_blocks, min(T * k, T * k // bm + n_expert))
+    c("moe_align_bm", ws.idx, ws.sorted_row, ws.sorted_slot, ws.block_expert, T, k, n_expert, bm, max_blocks, stream=st)
+    c("pdk_moe_prep_act_f4n", x, None, ws.sorted_row, ws.block_expert, ws.x4q, ws.x4s, ws.x4step, embd, bm, max_blocks, 0,
+      alpha, limit, up_add, stream=st)
+    if gated:
+        c("pdk_nvf4_moe_gemm_tc5", gate.data, gate.tiled, gate.scale2, None, ws.g_raw, up.data, up.tiled, up.scale2, None,
+          ws.u_raw, ws.x4q, ws.x4s, ws.x4step, ws.block_expert, ws.sorted_row, None, None, embd, ff, n_expert, bm,
+          max_blocks, k, 0, stream=st)
+        c("pdk_moe_prep_act_f4n", ws.g_raw, ws.u_raw, ws.sorted_row, ws.block_expert, ws.h4q, ws.h4s, ws.h4step, ff, bm,
+          max_blocks, 1, alpha, limit, up_add, stream=st)
+    else:
+        c("pdk_nvf4_moe_gemm_tc5", up.data, up.tiled, up.scale2, None, ws.u_raw, None, None, None, None, None, ws.x4q,
+          ws.x4s, ws.x4step, ws.block_expert, ws.sorted_row, None, None, embd, ff, n_expert, bm, max_blocks, k, 0,
+          stream=st)
+        c("pdk_moe_prep_act_f4n", ws.u_raw, None, ws.sorted_row, ws.block_expert, ws.h4q, ws.h4s, ws.h4step, ff, bm,
+          max_blocks, 2, alpha, limit, up_add, stream=st)
+    c("pdk_nvf4_moe_gemm_tc5", down.data, down.tiled, down.scale2, None, ws.part, None, None, None, None, None, ws.h4q,
+      ws.h4s, ws.h4step, ws.block_expert, ws.sorted_row, ws.sorted_slot, ws.w, ff, embd, n_expert, bm, max_blocks, k, 1,
+      stream=st)
+    c("moe_slot_combine", ws.part, out, embd, k, T, stream=st)
+    return 7

@@ -145,3 +145,59 @@ def test_slot_combine_fixed_order(pack):
         acc = acc + p[:, s]
     want = res.reshape(rows, embd) + acc
     assert np.array_equal(d_res.cpu().numpy().reshape(rows, embd), want)
+
+
+# ---- NVFP4 expert planes on the same grouped tensor-core GEMM
+
+def nvf4_expert_plane(ex, n_expert, rows, cols, seed):
+    """Per expert: N(0, 0.02) weights, scale2 = absmax / (6 * 448), NVFP4 blocks (the ModelOpt recipe)."""
+    data, scale, scale2, deq = [], [], [], []
+    for e in range(n_expert):
+        w = oracle.fill_normal(rows * cols, seed + e, 0.02)
+        s2 = np.float32(np.abs(w).max() / (6.0 * 448.0))
+        q, s = oracle.quantize_nvf4(w, float(s2))
+        data.append(q); scale.append(s); scale2.append(s2)
+        deq.append(oracle.dequant_nvfp4(q.reshape(rows, cols // 2), s.reshape(rows, cols // 16), s2, cols, rows))
+    plane = P.Nvf4MoePlane(dev(np.concatenate(data)), dev(np.concatenate(scale)), dev_f32(np.array(scale2, np.float32)),
+                           n_expert, rows, cols)
+    return P.nvf4_moe_prepare(ex, plane), np.stack(deq).astype(np.float64)
+
+
+@pytest.mark.parametrize("tokens,n_expert,k,embd,ff,bm,gated", [
+    (9, 8, 2, 128, 192, 8, True),
+    (40, 8, 4, 256, 128, 32, True),
+    (21, 4, 2, 1344, 320, 8, False),        # K = 5 slabs and a quarter, relu^2 experts
+])
+def test_nvf4_moe_block_matches_f64(pack, tokens, n_expert, k, embd, ff, bm, gated):
+    ex = P.GpuExecutor(pack)
+    gate, wg = nvf4_expert_plane(ex, n_expert, ff, embd, 1000)
+    up, wu = nvf4_expert_plane(ex, n_expert, ff, embd, 2000)
+    down, wd = nvf4_expert_plane(ex, n_expert, embd, ff, 3000)
+    x = oracle.bf16_round(oracle.fill_normal(tokens * embd, 4000, 1.0)).reshape(tokens, embd)
+    logits = oracle.fill_normal(tokens * n_expert, 4001, 1.0)
+
+    class Shape:
+        pass
+    shape = Shape()
+    shape.n_expert, shape.embd, shape.ff = n_expert, embd, ff
+    ws = P.MoeWorkspace(ex, shape, tokens, k, bm)
+    out = torch.zeros(tokens * embd, dtype=torch.float32, device="cuda")
+    P.moe_nvf4_forward(ex, gate, up, down, ws, dev_f32(x), dev_f32(logits), out, gated=gated)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    idx, w = oracle.moe_topk(logits, n_expert, k)
+    idx, w = idx.reshape(tokens, k), w.reshape(tokens, k)
+    ref = np.zeros((tokens, embd))
+    for t in range(tokens):
+        for s in range(k):
+            e = idx[t, s]
+            u = wu[e] @ x[t].astype(np.float64)
+            if gated:
+                g = wg[e] @ x[t].astype(np.float64)
+                h = g / (1.0 + np.exp(-g)) * u
+            else:
+                h = np.maximum(u, 0.0) ** 2
+            ref[t] += w[t, s] * (wd[e] @ h)
+    y = out.cpu().numpy().reshape(tokens, embd)
+    assert np.isfinite(y).all()
+    assert rel_l2(y, ref) < 2e-3 < TOL
