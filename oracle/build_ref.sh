@@ -5,13 +5,14 @@
 # is a second, independent checker (the reference's own GPU results for the
 # same C-ABI slots).  Nothing in the product links, loads or calls it.
 #
-#   oracle/build_ref.sh [/path/to/paddock]     (default /root/reference)
+#   oracle/build_ref.sh [/path/to/paddock]     (default: $PADDOCK_REFERENCE, else the checkout
+#                                               mounted next to the repository)
 #
 # Flags follow the reference's packs/cuda/build.sh for an arch list of "100":
 # plain sm_100 + the sm_100a feature target, PD_TC5_HOST and PD_BS_HOST.
 set -euo pipefail
 here="$(cd "$(dirname "$0")" && pwd)"
-ref="${1:-/root/reference}"
+ref="${1:-${PADDOCK_REFERENCE:-$(cd "$here/../.." && pwd)/reference}}"
 src="$ref/packs/cuda/pack.cu"
 out="$here/_ref/pd-cuda-ref.so"
 [ -f "$src" ] || { echo "reference checkout not found at $ref: skipping"; exit 0; }

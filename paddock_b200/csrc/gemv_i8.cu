@@ -34,9 +34,13 @@
 
 namespace {
 
-constexpr uint32_t kSlots = 4;    // 16-row tiles in flight per CTA
+constexpr uint32_t kSlots = 2;    // 16-row tiles in flight per CTA; two CTAs per SM (see kCtasPerSm)
 constexpr uint32_t kSlices = 4;   // K slices per tile, one warp each
 constexpr uint32_t kThreads = kSlots * kSlices * 32;
+// Two half-size CTAs per SM instead of one: under a dependent launch the next kernel's CTAs move
+// into the half-SMs that this kernel's last CTAs free and start streaming their weights while the
+// rest of this kernel is still in its last round, so back-to-back GEMVs overlap tail and head.
+constexpr uint32_t kCtasPerSm = 2;
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
@@ -157,7 +161,7 @@ struct PeerOut {
 };
 
 template <class F>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ recs, const float* __restrict__ bias,
                const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim, uint32_t out_dim,
                const int8_t* __restrict__ xq, const float* __restrict__ xq_scale, const PeerOut peers) {
@@ -384,7 +388,7 @@ int launch(const void* data, const void* recs, const float* bias, const float* x
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const uint32_t n_tiles = (out_dim + 15u) / 16u;
-    uint32_t grid = (uint32_t)pdk_sm_count();
+    uint32_t grid = (uint32_t)pdk_sm_count() * kCtasPerSm;
     const uint32_t need = (n_tiles + kSlots - 1u) / kSlots;
     if (grid > need) grid = need;
     cudaLaunchConfig_t cfg = {};

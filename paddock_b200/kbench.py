@@ -282,8 +282,43 @@ def bench_moe_ep(ex, a):
                              "distinct_experts": distinct, "n_gpus": world}
 
 
-OPS = {"moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
-DEFAULTS = {"moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+def bench_moe_nvf4(ex, a):
+    """The config 5 geometry with NVFP4 expert planes (per-16 UE4M3 scales, scale2 per expert), plain SwiGLU."""
+    from . import planes as P
+    n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
+    bm = 8 if T * k <= 1024 else 32
+
+    def plane(rows, cols, seed):
+        g = torch.Generator(device="cuda")
+        g.manual_seed(seed)
+        p = P.Nvf4MoePlane(
+            torch.randint(0, 256, (n_expert * rows * cols // 2,), dtype=torch.uint8, device="cuda", generator=g),
+            torch.randint(0x28, 0x40, (n_expert * rows * cols // 16,), dtype=torch.uint8, device="cuda", generator=g),
+            torch.full((n_expert,), 1e-3, device="cuda"), n_expert, rows, cols)
+        return P.nvf4_moe_prepare(ex, p)
+
+    gate, up, down = plane(ff, embd, 1), plane(ff, embd, 2), plane(embd, ff, 3)
+
+    class Shape:
+        pass
+    shape = Shape()
+    shape.n_expert, shape.embd, shape.ff = n_expert, embd, ff
+    ws = P.MoeWorkspace(ex, shape, T, k, bm)
+    x = synth.bf16_round(synth.normal(T * embd, 7, 1.0, "cuda"))
+    out = torch.zeros(T * embd, dtype=torch.float32, device="cuda")
+    n_sets = 6 if T <= 64 else 1
+    logits = [synth.normal(T * n_expert, 100 + i, 1.0, "cuda") for i in range(n_sets)]
+    sec = time_launches(lambda i: P.moe_nvf4_forward(ex, gate, up, down, ws, x, logits[i % n_sets], out), a.iters)
+    distinct = 0
+    for lg in logits:
+        distinct += torch.unique(torch.topk(lg.view(T, n_expert), k, dim=1).indices).numel()
+    distinct /= n_sets
+    per_expert = 3 * embd * ff // 16 * 9          # 4 bits + one scale byte per 16
+    return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
+
+
+OPS = {"moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
 def main():
