@@ -34,13 +34,12 @@
 
 namespace {
 
-constexpr uint32_t kSlots = 2;    // 16-row tiles in flight per CTA; two CTAs per SM (see kCtasPerSm)
+constexpr uint32_t kSlots = 4;    // 16-row tiles in flight per CTA
 constexpr uint32_t kSlices = 4;   // K slices per tile, one warp each
 constexpr uint32_t kThreads = kSlots * kSlices * 32;
-// Two half-size CTAs per SM instead of one: under a dependent launch the next kernel's CTAs move
-// into the half-SMs that this kernel's last CTAs free and start streaming their weights while the
-// rest of this kernel is still in its last round, so back-to-back GEMVs overlap tail and head.
-constexpr uint32_t kCtasPerSm = 2;
+// One CTA per SM.  Two half-size CTAs per SM (so that under a dependent launch the next kernel's
+// CTAs could move into half-SMs as they free up) measured 4 % slower back to back: 18.2 vs 17.4 us.
+constexpr uint32_t kCtasPerSm = 1;
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
