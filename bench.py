@@ -109,6 +109,50 @@ class ClockSampler:
                 "sm_max_mhz": self.max_mhz, "samples": len(self.samples), "reasons": sorted(self.reasons)}
 
 
+class Cudart:
+    """The handful of CUDA runtime calls the end-to-end loop makes per step, bound with ctypes."""
+
+    def __init__(self):
+        import ctypes as C
+        self.C = C
+        lib = None
+        for name in ("libcudart.so.12", "libcudart.so"):
+            try:
+                lib = C.CDLL(name)
+                break
+            except OSError:
+                continue
+        if lib is None:
+            raise RuntimeError("libcudart not found")
+        self.lib = lib
+        lib.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+        lib.cudaEventCreateWithFlags.argtypes = [C.POINTER(C.c_void_p), C.c_uint]
+        lib.cudaEventRecord.argtypes = [C.c_void_p, C.c_void_p]
+        lib.cudaStreamWaitEvent.argtypes = [C.c_void_p, C.c_void_p, C.c_uint]
+        lib.cudaEventSynchronize.argtypes = [C.c_void_p]
+
+    def _ok(self, rc):
+        if rc != 0:
+            raise RuntimeError(f"CUDA runtime error {rc}")
+
+    def event(self):
+        e = self.C.c_void_p()
+        self._ok(self.lib.cudaEventCreateWithFlags(self.C.byref(e), 2))      # cudaEventDisableTiming
+        return e
+
+    def copy(self, dst, src, n, kind, stream):                               # kind 1 = H2D, 2 = D2H
+        self._ok(self.lib.cudaMemcpyAsync(dst, src, n, kind, stream))
+
+    def record(self, ev, stream):
+        self._ok(self.lib.cudaEventRecord(ev, stream))
+
+    def wait(self, stream, ev):
+        self._ok(self.lib.cudaStreamWaitEvent(stream, ev, 0))
+
+    def sync_event(self, ev):
+        self._ok(self.lib.cudaEventSynchronize(ev))
+
+
 def cpu_baseline(steps, warmup, rows=N_DIM // 4):
     """Reference CPU path for one step: dequant_q4_k of the plane + scalar f32
     ascending-k matvec, on all host threads.  Returns (GB/s, cores, sample, ms)."""
@@ -266,54 +310,58 @@ def run_ours(args, rank, world, local_rank):
     kern_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
 
     # ---- end to end: pinned host activations in, outputs back, every step.
-    # N = 1: the way a decode loop runs it - two steps in flight on three streams (copy in, kernel,
+    # N = 1: the way a decode loop runs it - three steps in flight on three streams (copy in, kernel,
     # copy out), each step's input copied from pinned memory into its own device buffer and its
-    # result read back and waited for by the host one step later.  N > 1 keeps one step in flight.
+    # result read back and waited for by the host two steps later.  N > 1 keeps one step in flight.
     e2e_mode = "serial"
     if world == 1:
-        e2e_mode = "2 steps in flight: H2D / kernel / D2H on three streams, host waits for step i-1's result"
+        e2e_mode = "3 steps in flight: H2D / kernel / D2H on three streams, host waits for step i-2's result"
         s_in, s_k, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-        xb = [torch.empty_like(x) for _ in range(2)]
-        yb = [torch.empty_like(y) for _ in range(2)]
-        yh = [torch.zeros(N_DIM, dtype=torch.float32).pin_memory() for _ in range(2)]
-        ev_in = [torch.cuda.Event() for _ in range(2)]
-        ev_k = [torch.cuda.Event() for _ in range(2)]
-        ev_out = [torch.cuda.Event() for _ in range(2)]
+        D = 3  # buffers = steps in flight
+        xb = [torch.empty_like(x) for _ in range(D)]
+        yb = [torch.empty_like(y) for _ in range(D)]
+        yh = [torch.zeros(N_DIM, dtype=torch.float32).pin_memory() for _ in range(D)]
         launch = [[ex.pack.bind("kquant_gemv", p.data, p.scales, xb[b], yb[b], p.dims[0], p.dims[1], p.ty,
-                                stream=s_k.cuda_stream) for b in range(2)] for p in planes]
+                                stream=s_k.cuda_stream) for b in range(D)] for p in planes]
+        # copies, events and waits go straight to the CUDA runtime (a torch call costs the host
+        # several microseconds each, more than this step's kernel leaves room for)
+        rt = Cudart()
+        ev_in, ev_k, ev_out = ([rt.event() for _ in range(D)] for _ in range(3))
+        q_in, q_k, q_out = s_in.cuda_stream, s_k.cuda_stream, s_out.cuda_stream
+        x_src, x_bytes = x_host.data_ptr(), x_host.numel() * 4
+        xd, yd, yhp = [t.data_ptr() for t in xb], [t.data_ptr() for t in yb], [t.data_ptr() for t in yh]
+        y_bytes = y.numel() * 4
 
         def e2e_step(i):
-            b = i & 1
-            with torch.cuda.stream(s_in):
-                s_in.wait_event(ev_k[b])          # the kernel of step i-2 has consumed this buffer
-                xb[b].copy_(x_host, non_blocking=True)
-                ev_in[b].record(s_in)
-            with torch.cuda.stream(s_k):
-                s_k.wait_event(ev_in[b])
-                s_k.wait_event(ev_out[b])         # step i-2's result has left this buffer
-                launch[i % n_clones][b]()
-                ev_k[b].record(s_k)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_k[b])
-                yh[b].copy_(yb[b], non_blocking=True)
-                ev_out[b].record(s_out)
-            if i > 0:
-                ev_out[1 - b].synchronize()       # the host has step i-1's result
+            b = i % D
+            rt.wait(q_in, ev_k[b])               # the kernel of step i-D has consumed this buffer
+            rt.copy(xd[b], x_src, x_bytes, 1, q_in)
+            rt.record(ev_in[b], q_in)
+            rt.wait(q_k, ev_in[b])
+            rt.wait(q_k, ev_out[b])              # step i-D's result has left this buffer
+            launch[i % n_clones][b]()
+            rt.record(ev_k[b], q_k)
+            rt.wait(q_out, ev_k[b])
+            rt.copy(yhp[b], yd[b], y_bytes, 2, q_out)
+            rt.record(ev_out[b], q_out)
+            if i >= D - 1:
+                rt.sync_event(ev_out[(i + 1) % D])   # the host has step i-(D-1)'s result
 
         torch.cuda.synchronize()
-        for i in range(4):
+        for i in range(2 * D):
             e2e_step(i)
         torch.cuda.synchronize()
         w0 = time.perf_counter()
         for i in range(args.steps):
             e2e_step(i)
-        ev_out[(args.steps - 1) & 1].synchronize()
+        for j in range(D):
+            rt.sync_event(ev_out[j])
         e2e_ms = (time.perf_counter() - w0) * 1e3   # three streams: host clock around the fully drained loop
         torch.cuda.synchronize()
         # the pipelined loop must produce the same y as a plain call
         ex.kquant_gemv(planes[(args.steps - 1) % n_clones], x, y)
         torch.cuda.synchronize()
-        if not torch.equal(yh[(args.steps - 1) & 1][:y.numel()], y.cpu()):
+        if not torch.equal(yh[(args.steps - 1) % D][:y.numel()], y.cpu()):
             raise RuntimeError("pipelined end-to-end loop returned a different y")
     else:
         for i in range(3):
