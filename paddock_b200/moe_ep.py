@@ -115,7 +115,8 @@ def ep_moe_block_fixed(x, idx, w, n_expert, expert_fn, capacity=None, group=None
         flat_idx, flat_w = idx.reshape(-1), w.reshape(-1)
         dest = expert_owner(flat_idx, epr)
         order = torch.argsort(dest, stable=True)
-        counts = torch.bincount(dest, minlength=world)
+        # per-destination counts without bincount (which synchronizes the host to size its output)
+        counts = (dest.unsqueeze(1) == torch.arange(world, device=dev).unsqueeze(0)).sum(0)
         starts = torch.cumsum(counts, 0) - counts
         dest_sorted = dest.index_select(0, order)
         slot = dest_sorted * cap + (torch.arange(pairs, device=dev) - starts.index_select(0, dest_sorted))
