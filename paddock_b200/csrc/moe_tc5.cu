@@ -124,7 +124,10 @@ struct PrepArgs {
     uint8_t* xq;                 // [blocks][4*bm][dim/2]
     uint8_t* xs;                 // tiled: [blocks][slab][4 cells][512], the weight scale records' layout
     float* xstep;                // [positions] power of two the row was divided by
-    uint32_t dim, bm, mode;  // mode 0 gather, 1 gated (x = gate, up), 2 relu(x)^2 of x [positions][dim]
+    uint32_t dim, bm, mode;  // mode 0 gather, 1 gated (x = gate, up), 2 relu(x)^2 of x [positions][dim],
+                             // 3 one row: position 0 = x, the rest padding; the kernel writes the tables itself
+    uint32_t* tables;        // mode 3: sorted_row[bm], block_expert[1] (written here), then f32 scale2 = table_scale2
+    float table_scale2;
     uint32_t natural;        // 0: ggml MXFP4 element order (byte j = elements j, j+16); 1: byte j = elements 2j, 2j+1
     float alpha, limit, up_add;
 };
@@ -137,12 +140,24 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
     pdk_pdl_launch_dependents();
     pdk_pdl_wait();
     const uint32_t pos = blockIdx.x, b = pos / a.bm, i = pos % a.bm;
-    const uint32_t src = a.block_expert[b] == PDK_MOE_PAD ? PDK_MOE_PAD : a.sorted_row[pos];
-    const uint32_t groups = a.dim >> 4, kh = a.dim >> 1;
     const uint32_t tid = threadIdx.x;
+    uint32_t src;
+    if (a.mode == 3u) {
+        src = pos == 0u ? 0u : PDK_MOE_PAD;
+        if (tid == 0) {
+            a.tables[pos] = src;
+            if (pos == 0u) {
+                a.tables[a.bm] = 0u;  // block 0 belongs to expert 0
+                reinterpret_cast<float*>(a.tables)[a.bm + 1u] = a.table_scale2;
+            }
+        }
+    } else {
+        src = a.block_expert[b] == PDK_MOE_PAD ? PDK_MOE_PAD : a.sorted_row[pos];
+    }
+    const uint32_t groups = a.dim >> 4, kh = a.dim >> 1;
     __shared__ float s_red[8];
     const bool pad = src == PDK_MOE_PAD;
-    const float* row = a.mode == 0u ? a.x + (size_t)(pad ? 0u : src) * a.dim : a.x + (size_t)pos * a.dim;
+    const float* row = (a.mode == 0u || a.mode == 3u) ? a.x + (size_t)(pad ? 0u : src) * a.dim : a.x + (size_t)pos * a.dim;
     const float* urow = a.up + (size_t)pos * a.dim;
 
     auto load8 = [&](uint32_t off, float (&v)[8]) {
@@ -295,7 +310,10 @@ struct GemmArgs {
 // One tile = (block of BN/4 tokens, plane, 128 weight rows of the block's expert), walked
 // by persistent CTAs.  Roles as in the dense NVFP4 GEMM: warp 0 producer (TMA boxes of W
 // and of the block's term rows, bulk copies of both operands' scale records), warp 1 MMA issuer, warps 2..5 epilogue.
-template <uint32_t BN>
+// WG: the weight scales are the row-major plane [rows][in_dim/16] (one expert) and the producer
+// gathers them with 4-byte cp.async copies instead of bulk-copying pre-tiled records - for
+// callers whose slot hands over the checkpoint's own scale plane (the W4A16 decode GEMV).
+template <uint32_t BN, bool WG>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_constant__ CUtensorMap tmap_w1,
                     const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
@@ -317,7 +335,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            tc5::mbar_init(&sh->full[s], 1);
+            tc5::mbar_init(&sh->full[s], WG ? 33 : 1);  // expect_tx arrival (+ 32 lanes' cp.async arrivals)
             tc5::mbar_init(&sh->empty[s], 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
@@ -363,7 +381,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
                 if (!ok) break;
                 uint8_t* st = tiles + stage * kStageBytes;
                 const uint32_t kb0 = ks * KS, nsl = min(KS, num_kb - kb0);
-                tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], nsl * (kABytes + kBBytes + 2u * kSfBytes));
+                tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], nsl * (kABytes + kBBytes + (WG ? 1u : 2u) * kSfBytes));
 #pragma unroll
                 for (uint32_t u = 0; u < KS; ++u)
                     if (u < nsl) {
@@ -372,7 +390,32 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
                         tc5::tma_load_2d_elect(st + kOffB + u * kBBytes, &tmap_x, &sh->full[stage],
                                                (int32_t)((kb0 + u) * BKB), (int32_t)(blk * BN));
                     }
-                tc5::bulk_load_elect(st + kOffSfa, wsf + (size_t)kb0 * kSfBytes, nsl * kSfBytes, &sh->full[stage]);
+                if (!WG) {
+                    tc5::bulk_load_elect(st + kOffSfa, wsf + (size_t)kb0 * kSfBytes, nsl * kSfBytes, &sh->full[stage]);
+                } else {
+                    // cell j of slab u: byte l*16 + c*4 + b = scale[rt*128 + c*32 + l][(kb0+u)*16 + j*4 + b]
+                    const uint32_t sf_row = a.in_dim >> 4;
+                    const uint32_t dst0 = tc5::smem_u32(st + kOffSfa) + lane * 16u;
+#pragma unroll
+                    for (uint32_t u = 0; u < KS; ++u)
+                        if (u < nsl)
+#pragma unroll
+                            for (uint32_t j = 0; j < 4u; ++j) {
+                                const uint32_t off = (kb0 + u) * 16u + j * 4u;
+#pragma unroll
+                                for (uint32_t c = 0; c < 4u; ++c) {
+                                    const uint32_t row = rt * BM + c * 32u + lane;
+                                    const uint32_t size = (row < a.out_dim && off < sf_row) ? 4u : 0u;
+                                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(
+                                                     dst0 + u * kSfBytes + j * 512u + c * 4u),
+                                                 "l"(a.w_sf[plane] + (size ? (size_t)row * sf_row + off : 0u)), "r"(size)
+                                                 : "memory");
+                                }
+                            }
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(
+                                     tc5::smem_u32(&sh->full[stage]))
+                                 : "memory");
+                }
                 tc5::bulk_load_elect(st + kOffSfb, xsf + (size_t)kb0 * kSfBytes, nsl * kSfBytes, &sh->full[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
@@ -398,6 +441,7 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc5::fence_after_sync();
+                if (WG) fence_proxy_async_smem();  // the gathered cells were written through the generic proxy
                 const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
                 const uint32_t nsl = min(KS, num_kb - ks * KS);
 #pragma unroll
@@ -506,11 +550,11 @@ moe_tc5_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w0, const __grid_co
 
 constexpr uint32_t kMaxBlocks = 1024;  // block_expert[] is kept in shared memory
 
-template <uint32_t BN>
+template <uint32_t BN, bool WG = false>
 int launch_gemm(const CUtensorMap& tw0, const CUtensorMap& tw1, const CUtensorMap& tx, const GemmArgs& a,
                 cudaStream_t st) {
     const size_t smem = (size_t)Cfg<BN>::kStages * Cfg<BN>::kStageBytes + sizeof(Shared) + kMaxBlocks * 4u + 1024u;
-    auto kern = moe_tc5_gemm_kernel<BN>;
+    auto kern = moe_tc5_gemm_kernel<BN, WG>;
     static const cudaError_t attr_rc =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (attr_rc != cudaSuccess) return (int)attr_rc;
@@ -676,4 +720,70 @@ PDK_EXPORT int pdk_nvf4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, con
     return gemm_impl(w0_data, w0_sf, (const float*)w0_scale2, w0_bias, out0, w1_data, w1_sf, (const float*)w1_scale2,
                      w1_bias, out1, xq, xs, xstep, block_expert, sorted_row, sorted_slot, topk_w, in_dim, out_dim,
                      n_expert, bm, max_blocks, n_active, scatter, 1u, stream);
+}
+
+// ---------------------------------------------------------------- W4A16 decode GEMV on the same kernels
+// pd_nvf4_gemv (slot 394) hands over the checkpoint's NVFP4 plane (row-major scales) and one f32
+// activation vector.  On the tensor-core route the vector becomes four NVFP4 term rows (one
+// "block" of one token) in a library-resident scratch slice and the grouped GEMM runs with one
+// expert, gathering the weight scales from the row-major plane.  Two launches; the plane is
+// streamed once at 4.5 bits per weight.  One scratch slice per stream for the first two streams
+// that come here (the pack allocates nothing); other callers get -1 and take the plain kernel.
+namespace {
+constexpr uint32_t kGemvMaxK = 16384;
+constexpr size_t kGemvXs = 128, kGemvXq = kGemvXs + (size_t)(kGemvMaxK / 256u) * 2048u;
+constexpr size_t kGemvSlice = ((kGemvXq + 32u * (kGemvMaxK / 2u)) + 1023u) & ~(size_t)1023u;
+constexpr int kGemvLanes = 2;
+__device__ __align__(1024) uint8_t g_gemv_scratch[kGemvLanes][kGemvSlice];
+
+uint8_t* gemv_slice(cudaStream_t st) {
+    static uint8_t* base = [] {
+        void* p = nullptr;
+        return cudaGetSymbolAddress(&p, g_gemv_scratch) == cudaSuccess ? (uint8_t*)p : (uint8_t*)nullptr;
+    }();
+    static cudaStream_t owner[kGemvLanes];
+    static int n_owner = 0;
+    if (base == nullptr) return nullptr;
+    for (int i = 0; i < n_owner; ++i)
+        if (owner[i] == st) return base + (size_t)i * kGemvSlice;
+    if (n_owner == kGemvLanes) return nullptr;
+    owner[n_owner] = st;
+    return base + (size_t)(n_owner++) * kGemvSlice;
+}
+}  // namespace
+
+// 0 / cudaError_t, or -1 when the route does not apply (in_dim not a multiple of 64 or above 16384,
+// no scratch slice for this stream) and the caller should use its own kernel.
+int pdk_nvf4_gemv_tc5(const void* data, const void* scale, const void* bias, const void* x, void* y, float scale2,
+                      uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
+    if ((in_dim & 63u) != 0u || in_dim > kGemvMaxK || !pdk_aligned(data, 16) || !pdk_aligned(scale, 4) ||
+        !pdk_aligned(x, 16))
+        return -1;
+    uint8_t* sl = gemv_slice(st);
+    if (sl == nullptr) return -1;
+    uint32_t* tables = reinterpret_cast<uint32_t*>(sl);          // sorted_row[8], block_expert[1], f32 scale2
+    float* xstep = reinterpret_cast<float*>(sl + 64);
+    uint8_t* xs = sl + kGemvXs;
+    uint8_t* xq = sl + kGemvXq;
+    PrepArgs pa{};
+    pa.x = (const float*)x; pa.xq = xq; pa.xs = xs; pa.xstep = xstep;
+    pa.dim = in_dim; pa.bm = 8u; pa.mode = 3u; pa.natural = 1u; pa.tables = tables; pa.table_scale2 = scale2;
+    const uint32_t per_row = ((in_dim + 255u) >> 8) * 16u;
+    if (int rc = pdk_launch_pdl(moe_prep_f4_kernel, dim3(8), dim3(per_row <= 256u ? (per_row + 31u) & ~31u : 256u), 0,
+                                st, pa))
+        return rc;
+    const uint32_t kbytes = in_dim >> 1;
+    CUtensorMap tw, tx;
+    if (int rc = pdk_make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, data, kbytes, out_dim, kbytes, BKB, BM)) return rc;
+    if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, kbytes, 32u, kbytes, BKB, 32u)) return rc;
+    GemmArgs a{};
+    a.w_sf[0] = a.w_sf[1] = (const uint8_t*)scale;
+    a.scale2[0] = a.scale2[1] = reinterpret_cast<const float*>(tables) + 9;
+    a.bias[0] = (const float*)bias;
+    a.out[0] = (float*)y;
+    a.x_sf = xs; a.xstep = xstep;
+    a.block_expert = tables + 8; a.sorted_row = tables;
+    a.in_dim = in_dim; a.out_dim = out_dim; a.max_blocks = 1u; a.n_planes = 1u; a.n_active = 1u;
+    a.err_word = pdk_error_word();
+    return launch_gemm<32, true>(tw, tw, tx, a, st);
 }

@@ -9,6 +9,9 @@
 
 #include "pdk_common.cuh"
 
+int pdk_nvf4_gemv_tc5(const void* data, const void* scale, const void* bias, const void* x, void* y, float scale2,
+                      uint32_t in_dim, uint32_t out_dim, cudaStream_t st);
+
 namespace {
 
 __device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
@@ -184,6 +187,16 @@ PDK_EXPORT int pd_nvf4_gemv(const void* data, const void* scale, const void* bia
     if (out_dim == 0) return 0;
     if ((in_dim & 31u) != 0u || in_dim == 0u) return cudaErrorInvalidValue;
     if (!pdk_aligned(data, 16) || !pdk_aligned(scale, 2) || !pdk_aligned(x, 16)) return cudaErrorInvalidValue;
+    // tensor-core route (activations as four NVFP4 terms, moe_tc5.cu); PDK_NVF4_GEMV_PLAIN=1 keeps the
+    // plain kernel (A/B switch, read once)
+    static const bool plain = [] {
+        const char* e = getenv("PDK_NVF4_GEMV_PLAIN");
+        return e && e[0] == '1';
+    }();
+    if (!plain) {
+        const int rc = pdk_nvf4_gemv_tc5(data, scale, bias, x, y, scale2, in_dim, out_dim, (cudaStream_t)stream);
+        if (rc >= 0) return rc;
+    }
     nvf4_gemv_kernel<<<(out_dim + 7u) / 8u, 256, 0, (cudaStream_t)stream>>>(
         (const uint8_t*)data, (const uint8_t*)scale, (const float*)bias, (const float*)x, (float*)y, scale2, in_dim,
         out_dim);

@@ -302,6 +302,21 @@ def bench_moe_ep(ex, a):
                              "distinct_experts": distinct, "n_gpus": world}
 
 
+def bench_nvf4_gemv(ex, a):
+    """Slot 394: W4A16 decode GEMV over an NVFP4 plane (f32 activations), config 4 geometry."""
+    n, k = a.n, a.k
+    st = torch.cuda.current_stream().cuda_stream
+    nbytes = n * k // 2 + n * k // 16
+    nc = clones_for(nbytes)
+    ws = [(torch.randint(0, 256, (n * k // 2,), dtype=torch.uint8, device="cuda"),
+           torch.randint(0x20, 0x48, (n * k // 16,), dtype=torch.uint8, device="cuda")) for _ in range(nc)]
+    x = synth.bf16_round(synth.normal(k, 5, 1.0, "cuda"))
+    y = torch.zeros(n, dtype=torch.float32, device="cuda")
+    sec = time_launches(lambda i: ex.pack.call("nvf4_gemv", ws[i % nc][0], ws[i % nc][1], None, x, y, 1.0, k, n,
+                                               stream=st), a.iters)
+    return sec, {"bound": "hbm", "bytes": nbytes + 4 + k * 4 + n * 4}
+
+
 def bench_moe_nvf4(ex, a):
     """The config 5 geometry with NVFP4 expert planes (per-16 UE4M3 scales, scale2 per expert), plain SwiGLU."""
     from . import planes as P
@@ -337,8 +352,8 @@ def bench_moe_nvf4(ex, a):
     return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
 
 
-OPS = {"moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
-DEFAULTS = {"moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+OPS = {"nvf4_gemv": bench_nvf4_gemv, "moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
 def main():
