@@ -32,6 +32,9 @@ int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq
                           uint32_t in_dim, uint32_t out_dim, cudaStream_t st);
 int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st);
+// q4k_batch_i8.cu: 1..16 tokens, f32 or int8 activations; -1 = shape outside its plan
+int pdk_q4k_batch_i8(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale,
+                     float* y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
 
 namespace {
 
@@ -477,11 +480,37 @@ bool force_plain() {
     return v;
 }
 
+// PDK_Q4K_BATCH_BF16=1 keeps the bf16 tensor-core kernel for 2..16 tokens (A/B switch, read once).
+bool force_bf16_batch() {
+    static const bool v = [] {
+        const char* e = getenv("PDK_Q4K_BATCH_BF16");
+        return e && e[0] == '1';
+    }();
+    return v;
+}
+
 int gemm_any(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
              uint32_t batch, cudaStream_t st) {
     if (!force_plain() && batch == 1u) {
         const int rc = pdk_q4k_gemv_i8(data, scales, x, y, in_dim, out_dim, st);
         if (rc != -1) return rc;
+    }
+    if (!force_plain() && !force_bf16_batch()) {
+        // 2..16 tokens per launch on the int8 tensor path
+        uint32_t b = 0;
+        int rc = 0;
+        while (b < batch && rc == 0) {
+            const uint32_t take = batch - b < 16u ? batch - b : 16u;
+            rc = pdk_q4k_batch_i8(data, scales, x + (size_t)b * in_dim, nullptr, nullptr, y + (size_t)b * out_dim, in_dim,
+                                  out_dim, take, st);
+            if (rc == 0) b += take;
+        }
+        if (rc > 0) return rc;
+        if (b == batch) return 0;
+        // rc == -1: the limb planes do not fit; the bf16 kernel or the plain route take what is left
+        x += (size_t)b * in_dim;
+        y += (size_t)b * out_dim;
+        batch -= b;
     }
     if (!force_plain()) {
         uint32_t b = 0;
@@ -607,6 +636,20 @@ int w4a8_gemm(const void* data, const void* scales, const void* xq, const void* 
     if (batch == 1u) {
         const int rc = pdk_q4k_gemv_i8_q8act(data, scales, (const int8_t*)xq, (const float*)xs, (float*)y, in_dim, out_dim, st);
         if (rc >= 0) return rc;
+    }
+    if (!force_plain() && !force_bf16_batch() && pdk_aligned(xq, 8)) {
+        uint32_t b = 0;
+        int rc = 0;
+        while (b < batch && rc == 0) {
+            const uint32_t take = batch - b < 16u ? batch - b : 16u;
+            rc = pdk_q4k_batch_i8(data, scales, nullptr, (const int8_t*)xq + (size_t)b * in_dim,
+                                  (const float*)xs + (size_t)b * (in_dim >> 5), (float*)y + (size_t)b * out_dim, in_dim,
+                                  out_dim, take, st);
+            if (rc == 0) b += take;
+        }
+        if (rc > 0) return rc;
+        if (b == batch) return 0;
+        if (b != 0) return cudaErrorNotSupported;  // cannot happen: the plan depends on in_dim only
     }
     // the batch kernels take f32 activations: widen q * scale into the caller's partial
     // buffer (>= 8 * out_dim * batch floats by the slot's contract)

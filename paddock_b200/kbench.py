@@ -33,11 +33,30 @@ def peaks():
         return 6650.0, 1590.0, "fallback"
 
 
+GRAPH_REPLAY = False  # --graph: the timed launches are captured once into a CUDA graph and replayed
+
+
 def time_launches(fn, iters, warmup=5):
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if GRAPH_REPLAY:
+        side = torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            fn(0)                       # one launch on the capturing stream before capture (per-stream scratch)
+            side.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(iters):
+                    fn(i)
+            g.replay()
+            side.synchronize()
+            e0.record()
+            g.replay()
+            e1.record()
+            side.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e-3
     e0.record()
     for i in range(iters):
         fn(i)
@@ -62,6 +81,45 @@ def bench_q4k(ex, a):
         sec = time_launches(lambda i: ex.kquant_gemm_f32(planes[i % len(planes)], x, y, m), a.iters)
     nbytes = n * k // 256 * 144 + m * k * 2 + m * n * 4
     return sec, {"bound": "hbm", "bytes": nbytes}
+
+
+def bench_q4k_w4a8(ex, a):
+    """The reference's small-batch chain for a Q4_K plane (crates/paddock-engine/src/gpu/kquant.rs:1020-1038):
+    quantize_q8_sums per token, then kquant_gemm_w4a8_sb (kquant_gemv_w4a8 at one token).  Table slots
+    only, so --pack times another library on the same operands.  `us` is the GEMM alone; `us_chain`
+    includes the per-token activation quantizers."""
+    k, n, m = a.k, a.n, a.m
+    st = torch.cuda.current_stream().cuda_stream
+    raw = synth.quantize_q4_k(synth.normal(n * k, 1, 0.02, "cuda"))
+    ours = GpuExecutor()
+    planes = [ours.repack_kquant_raw(raw, k, n) for _ in range(clones_for(n * k // 256 * 152))]
+    x = synth.bf16_round(synth.normal(m * k, 2, 1.0, "cuda"))
+    xq = torch.zeros(m * k, dtype=torch.int8, device="cuda")
+    xs = torch.zeros(m * k // 32, dtype=torch.float32, device="cuda")
+    xsum = torch.zeros(m * k // 16, dtype=torch.float32, device="cuda")
+    part = torch.zeros(8 * n * m, dtype=torch.float32, device="cuda")
+    y = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+
+    def quant():
+        for t in range(m):
+            ex.pack.call("quantize_q8_sums", x[t * k:], xq[t * k:], xs[t * k // 32:], xsum[t * k // 16:], k, stream=st)
+
+    def gemm(i):
+        w = planes[i % len(planes)]
+        if m == 1:
+            ex.pack.call("kquant_gemv_w4a8", w.data, w.scales, xq, xs, xsum, y, k, n, 12, stream=st)
+        else:
+            ex.pack.call("kquant_gemm_w4a8_sb", w.data, w.scales, xq, xs, xsum, part, y, k, n, m, 12, stream=st)
+
+    quant()
+    sec = time_launches(gemm, a.iters)
+
+    def chain(i):
+        quant()
+        gemm(i)
+    sec_chain = time_launches(chain, a.iters)
+    nbytes = n * k // 256 * 144 + m * k * 2 + m * n * 4
+    return sec, {"bound": "hbm", "bytes": nbytes, "us_chain": sec_chain * 1e6}
 
 
 def bench_q8(ex, a):
@@ -352,8 +410,8 @@ def bench_moe_nvf4(ex, a):
     return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
 
 
-OPS = {"nvf4_gemv": bench_nvf4_gemv, "moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
-DEFAULTS = {"nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+OPS = {"q4k_w4a8": bench_q4k_w4a8, "nvf4_gemv": bench_nvf4_gemv, "moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"q4k_w4a8": (4, 25600, 5120), "nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
 def main():
@@ -366,12 +424,14 @@ def main():
     ap.add_argument("--out", default="bf16", choices=["bf16", "f32"])
     ap.add_argument("--moe-path", default="tc5", choices=["tc5", "mma"],
                     help="expert GEMMs: block-scaled tcgen05 (default) or the mma.sync kernels")
-    ap.add_argument("--graph", action="store_true", help="moe_mxfp4: replay the block from a CUDA graph")
+    ap.add_argument("--graph", action="store_true", help="replay the timed launches from a CUDA graph (moe_mxfp4, moe_ep, q4k_gemv, q8_gemv, nvf4_gemv)")
     ap.add_argument("--pack", default=None, help="path of a kernel-pack library to time instead of this package's")
     a = ap.parse_args()
     dm, dn, dk = DEFAULTS[a.op]
     a.m, a.n, a.k = a.m or dm, a.n or dn, a.k or dk
     ep = a.op == "moe_ep"
+    global GRAPH_REPLAY
+    GRAPH_REPLAY = a.graph and a.op in ("q4k_gemv", "q8_gemv", "nvf4_gemv")
     if ep:
         import torch.distributed as dist
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
