@@ -35,6 +35,9 @@ int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float*
 // q4k_batch_i8.cu: 1..16 tokens, f32 or int8 activations; -1 = shape outside its plan
 int pdk_q4k_batch_i8(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale,
                      float* y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
+// q4k_tc5.cu: 1..32 tokens on tcgen05 (f16 weights); same operands and return convention
+int pdk_q4k_tc5(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale, float* y,
+                uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
 
 namespace {
 
@@ -489,6 +492,45 @@ bool force_bf16_batch() {
     return v;
 }
 
+// From how many tokens on the tcgen05 kernel takes a call (PDK_Q4K_TC5_MIN, read once; 0 = never).
+uint32_t tc5_min_tokens() {
+    static const uint32_t v = [] {
+        const char* e = getenv("PDK_Q4K_TC5_MIN");
+        return e ? (uint32_t)atoi(e) : 9u;
+    }();
+    return v;
+}
+
+// 2 <= tokens on the tensor paths: up to 32 tokens per launch on tcgen05 from tc5_min_tokens() on,
+// up to 16 on the int8 path below that.  Activations f32 (x) or int8 with per-32 scales (xq, xs).
+// Returns the number of tokens done (all of them unless a shape is outside both plans), or
+// -(cudaError_t) - 1 on a launch error.
+int small_batch(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xs, float* y,
+                uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
+    uint32_t b = 0;
+    while (b < batch) {
+        const uint32_t left = batch - b;
+        const float* xb = x ? x + (size_t)b * in_dim : nullptr;
+        const int8_t* qb = xq ? xq + (size_t)b * in_dim : nullptr;
+        const float* sb = xs ? xs + (size_t)b * (in_dim >> 5) : nullptr;
+        float* yb = y + (size_t)b * out_dim;
+        uint32_t take = 0;
+        int rc = -1;
+        if (tc5_min_tokens() != 0u && left >= tc5_min_tokens()) {
+            take = left < 32u ? left : 32u;
+            rc = pdk_q4k_tc5(data, scales, xb, qb, sb, yb, in_dim, out_dim, take, st);
+        }
+        if (rc == -1) {
+            take = left < 16u ? left : 16u;
+            rc = pdk_q4k_batch_i8(data, scales, xb, qb, sb, yb, in_dim, out_dim, take, st);
+        }
+        if (rc == -1) break;
+        if (rc != 0) return -rc - 1;
+        b += take;
+    }
+    return (int)b;
+}
+
 int gemm_any(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
              uint32_t batch, cudaStream_t st) {
     if (!force_plain() && batch == 1u) {
@@ -496,21 +538,13 @@ int gemm_any(const void* data, const void* scales, const float* x, float* y, uin
         if (rc != -1) return rc;
     }
     if (!force_plain() && !force_bf16_batch()) {
-        // 2..16 tokens per launch on the int8 tensor path
-        uint32_t b = 0;
-        int rc = 0;
-        while (b < batch && rc == 0) {
-            const uint32_t take = batch - b < 16u ? batch - b : 16u;
-            rc = pdk_q4k_batch_i8(data, scales, x + (size_t)b * in_dim, nullptr, nullptr, y + (size_t)b * out_dim, in_dim,
-                                  out_dim, take, st);
-            if (rc == 0) b += take;
-        }
-        if (rc > 0) return rc;
-        if (b == batch) return 0;
-        // rc == -1: the limb planes do not fit; the bf16 kernel or the plain route take what is left
-        x += (size_t)b * in_dim;
-        y += (size_t)b * out_dim;
-        batch -= b;
+        const int done = small_batch(data, scales, x, nullptr, nullptr, y, in_dim, out_dim, batch, st);
+        if (done < 0) return -done - 1;
+        if ((uint32_t)done == batch) return 0;
+        // outside both plans: the bf16 kernel or the plain route take what is left
+        x += (size_t)done * in_dim;
+        y += (size_t)done * out_dim;
+        batch -= (uint32_t)done;
     }
     if (!force_plain()) {
         uint32_t b = 0;
@@ -638,18 +672,11 @@ int w4a8_gemm(const void* data, const void* scales, const void* xq, const void* 
         if (rc >= 0) return rc;
     }
     if (!force_plain() && !force_bf16_batch() && pdk_aligned(xq, 8)) {
-        uint32_t b = 0;
-        int rc = 0;
-        while (b < batch && rc == 0) {
-            const uint32_t take = batch - b < 16u ? batch - b : 16u;
-            rc = pdk_q4k_batch_i8(data, scales, nullptr, (const int8_t*)xq + (size_t)b * in_dim,
-                                  (const float*)xs + (size_t)b * (in_dim >> 5), (float*)y + (size_t)b * out_dim, in_dim,
-                                  out_dim, take, st);
-            if (rc == 0) b += take;
-        }
-        if (rc > 0) return rc;
-        if (b == batch) return 0;
-        if (b != 0) return cudaErrorNotSupported;  // cannot happen: the plan depends on in_dim only
+        const int done = small_batch(data, scales, nullptr, (const int8_t*)xq, (const float*)xs, (float*)y, in_dim,
+                                     out_dim, batch, st);
+        if (done < 0) return -done - 1;
+        if ((uint32_t)done == batch) return 0;
+        if (done != 0) return cudaErrorNotSupported;  // cannot happen: the plans depend on in_dim only
     }
     // the batch kernels take f32 activations: widen q * scale into the caller's partial
     // buffer (>= 8 * out_dim * batch floats by the slot's contract)

@@ -1,0 +1,491 @@
+// q4k_tc5.cu - Q4_K GEMM for 9..32 tokens per launch on the tcgen05 tensor cores (W4A16).
+//
+// With more than a handful of tokens the per-(block, token) integer fold of q4k_batch_i8.cu
+// outgrows the weight stream.  Here the CUDA cores touch each weight once, whatever the token
+// count: 16 producer warps turn the packed nibbles into f16 weights
+//     w = q * f16(d * sc) - f16(dmin * m)          (two weights per instruction)
+// and write them into shared memory as the K-major, 128-byte-swizzled A operand of
+// tcgen05.mma kind::f16 (128 weight rows x 256 K per stage).  The B operand is the activation
+// tile: a small kernel in front scales each token by a power of two into the f16 range and
+// splits it into two f16 terms x = hi + lo (exact for bf16-valued activations, 22 bits
+// otherwise), stored as 2 * tokens rows of a library-resident f16 matrix that TMA boxes are
+// cut from.  The accumulator [128 rows][hi columns | lo columns] stays in tensor memory over
+// the whole K range of a work item; the epilogue adds the two column groups, undoes the token
+// scale and adds into y.
+//
+// A work item is (128-row tile, half of K): twice as many items as tiles keeps 148 SMs evenly
+// loaded at 200 tiles.  The two halves of a tile add into y with red.global.add.f32; y is
+// zeroed by the kernel in front, and with exactly two addends per element the sum does not
+// depend on their order.
+//
+// Precision class: f16-rounded block scales (relative 2^-12, independent per 32-weight block)
+// and one f16 rounding per weight; measured rel-L2 against the f64 product of the dequantized
+// operands is below 1e-4.
+#include <cuda_fp16.h>
+
+#include "tc5.cuh"
+
+namespace {
+
+constexpr uint32_t BM = 128;          // weight rows per work item (MMA M)
+constexpr uint32_t kProdWarps = 16;   // dequantizing warps; warps 0..3 also drain the accumulator
+constexpr uint32_t kTmaWarp = kProdWarps, kMmaWarp = kProdWarps + 1;
+constexpr uint32_t kThreads = (kProdWarps + 2) * 32;
+constexpr uint32_t kStages = 2;       // one stage = one Q4_K super-block column (256 K) of 128 rows
+constexpr uint32_t kSlabBytes = BM * 128u;        // [128 rows][64 f16], 8-row groups of 1024 bytes
+constexpr uint32_t kABytes = 4u * kSlabBytes;     // 65536
+constexpr uint32_t kDepth = 4;        // producer register stages (loads run three units ahead: 67 KB per SM in flight)
+constexpr uint32_t kMaxK = 16384;
+
+template <uint32_t NC>  // B columns = 2 * (tokens rounded up to 16 or 32)
+struct Cfg {
+    static constexpr uint32_t kBSlab = NC * 128u;
+    static constexpr uint32_t kBBytes = 4u * kBSlab;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kTmemCols = 2u * NC;  // two accumulators
+    static constexpr uint32_t kIdesc = tc5::idesc_f32acc(0u, 0u, BM, NC);
+};
+
+struct Shared {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mma_f16_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(TC5_ELECT
+                 ".reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+
+// TMEM -> registers: 32 lanes x 16 columns of 32 bits per warp
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t h2_dup(float v) {
+    const __half2 h = __float2half2_rn(v);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// ---------------------------------------------------------------- activations -> f16 hi / lo rows
+//
+// xh f16 [NC][K]: row t = hi term of token t, row NC/2 + t = lo term; tokscale f32 [NC/2] = the
+// power of two the token was divided by (0 for unused columns).  One CTA per token column; the
+// CTAs past the token columns zero y.
+constexpr uint32_t kActThreads = 1024, kZeroCtas = 32;
+__global__ void __launch_bounds__(kActThreads)
+q4k_act_f16_kernel(const float* __restrict__ x, const int8_t* __restrict__ xq, const float* __restrict__ xq_scale,
+                   __half* __restrict__ xh, float* __restrict__ tokscale, float* __restrict__ y, uint32_t in_dim,
+                   uint32_t out_dim, uint32_t batch, uint32_t half_cols) {
+    __shared__ float wmax[kActThreads / 32u];
+    const uint32_t tok = blockIdx.x, tid = threadIdx.x;
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();  // the scratch and y may still be in use by the previous kernels in the stream
+    if (tok >= half_cols) {
+        // y is f32 [batch][out_dim], 4-byte aligned by contract: scalar stores
+        const size_t n = (size_t)batch * out_dim;
+        for (size_t i = (size_t)(tok - half_cols) * kActThreads + tid; i < n; i += (size_t)kZeroCtas * kActThreads) y[i] = 0.0f;
+        return;
+    }
+    __half* hi = xh + (size_t)tok * in_dim;
+    __half* lo = xh + (size_t)(half_cols + tok) * in_dim;
+    auto load8 = [&](uint32_t k, float (&v)[8]) {
+        const size_t e0 = (size_t)tok * in_dim + k;
+        if (xq == nullptr) {
+            const float4 a = *reinterpret_cast<const float4*>(x + e0);
+            const float4 b = *reinterpret_cast<const float4*>(x + e0 + 4u);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+            const int2 q = *reinterpret_cast<const int2*>(xq + e0);
+            const float s = xq_scale[e0 >> 5];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = (float)(int8_t)((i < 4 ? q.x >> (8 * i) : q.y >> (8 * (i - 4))) & 0xff) * s;
+        }
+    };
+    if (tok >= batch) {
+        for (uint32_t k = tid * 8u; k < in_dim; k += kActThreads * 8u) {
+            *reinterpret_cast<uint4*>(hi + k) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(lo + k) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (tid == 0) tokscale[tok] = 0.0f;
+        return;
+    }
+    float amax = 0.0f;
+    for (uint32_t k = tid * 8u; k < in_dim; k += kActThreads * 8u) {
+        float v[8];
+        load8(k, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((tid & 31u) == 0u) wmax[tid >> 5] = amax;
+    __syncthreads();
+    amax = wmax[0];
+#pragma unroll
+    for (uint32_t i = 1; i < kActThreads / 32u; ++i) amax = fmaxf(amax, wmax[i]);
+    // amax < 2^ex  ->  x * 2^(14 - ex) stays below 2^14, inside the f16 range
+    float mul = 0.0f, back = 0.0f;
+    if (amax > 0.0f && amax < 3.0e38f) {
+        int ex;
+        (void)frexpf(amax, &ex);
+        ex = max(-100, min(100, ex));
+        mul = ldexpf(1.0f, 14 - ex);
+        back = ldexpf(1.0f, ex - 14);
+    }
+    for (uint32_t k = tid * 8u; k < in_dim; k += kActThreads * 8u) {
+        float v[8];
+        load8(k, v);
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float a = v[2 * i] * mul, b = v[2 * i + 1] * mul;
+            const __half2 hh = __floats2half2_rn(a, b);
+            const __half2 ll = __floats2half2_rn(a - __low2float(hh), b - __high2float(hh));
+            h[i] = *reinterpret_cast<const uint32_t*>(&hh);
+            l[i] = *reinterpret_cast<const uint32_t*>(&ll);
+        }
+        *reinterpret_cast<uint4*>(hi + k) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(lo + k) = make_uint4(l[0], l[1], l[2], l[3]);
+    }
+    if (tid == 0) tokscale[tok] = back;
+}
+
+// ---------------------------------------------------------------- the GEMM
+
+// What a producer thread holds of one unit: of ONE row, the 16-byte chunks c and c + 4 of the
+// row's 128 packed bytes (chunk c = 16 low nibbles of block 2G and 16 high nibbles of block
+// 2G+1, G = c / 2), and the row's scales.  The 8 lanes of a quarter-warp hold the same chunks
+// of 8 consecutive rows: their 16-byte stores into the swizzled tile then fall on 8 different
+// chunk positions (all 32 banks), and a warp's load covers 64 contiguous bytes of each row.
+struct PStage {
+    uint4 q[2];
+    uint32_t dd;     // {f16 d, f16 dmin}
+    uint32_t sm[2];  // per chunk: sc[2G] | sc[2G+1] << 8 | m[2G] << 16 | m[2G+1] << 24
+};
+
+// 32 weights of one row -> four 16-byte chunks of the row's 128-byte line in k-slab G:
+// chunks 2h, 2h+1 (block 2G, elements 16h..16h+15) and 4+2h, 5+2h (block 2G+1), h = c & 1.
+__device__ __forceinline__ void dequant_store(const uint4& q, uint32_t dd, uint32_t sm, uint8_t* line, uint32_t h,
+                                              uint32_t swz) {
+    const __half2 dh = *reinterpret_cast<const __half2*>(&dd);
+    const float d = __low2float(dh), dmin = __high2float(dh);
+    // w = dsc * (q - 8) + (8 dsc - dmin m): the centred nibble halves what the scale's f16 rounding costs
+    const float dsc_lo = d * (float)(sm & 0xffu), dsc_hi = d * (float)((sm >> 8) & 0xffu);
+    const uint32_t s_lo = h2_dup(dsc_lo);
+    const uint32_t s_hi = h2_dup(dsc_hi * 0.0625f);  // the high nibble arrives as 16 q
+    const uint32_t o_lo = h2_dup(fmaf(8.0f, dsc_lo, -dmin * (float)((sm >> 16) & 0xffu)));
+    const uint32_t o_hi = h2_dup(fmaf(8.0f, dsc_hi, -dmin * (float)(sm >> 24)));
+    const uint32_t magic = 0x64086408u;     // f16 1032 twice: (0x6400 | q) - 1032 = q - 8
+    const uint32_t magic_hi = 0x64806480u;  // f16 1152 twice: (0x6400 | q << 4) - 1152 = 16 (q - 8)
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t lo[8], hi[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t p01 = prmt(w[i], 0x64646464u, 0x4140u);  // bytes {b0, 0x64, b1, 0x64}
+        const uint32_t p23 = prmt(w[i], 0x64646464u, 0x4342u);
+        lo[2 * i] = h2_fma(h2_sub(p01 & 0x640F640Fu, magic), s_lo, o_lo);
+        lo[2 * i + 1] = h2_fma(h2_sub(p23 & 0x640F640Fu, magic), s_lo, o_lo);
+        hi[2 * i] = h2_fma(h2_sub(p01 & 0x64F064F0u, magic_hi), s_hi, o_hi);
+        hi[2 * i + 1] = h2_fma(h2_sub(p23 & 0x64F064F0u, magic_hi), s_hi, o_hi);
+    }
+    *reinterpret_cast<uint4*>(line + (((2u * h) ^ swz) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    *reinterpret_cast<uint4*>(line + (((2u * h + 1u) ^ swz) << 4)) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+    *reinterpret_cast<uint4*>(line + (((4u + 2u * h) ^ swz) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4*>(line + (((5u + 2u * h) ^ swz) << 4)) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+}
+
+template <uint32_t NC>
+__global__ void __launch_bounds__(kThreads, 1)  // 18 warps: 5 on one scheduler, 96 registers per thread
+q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ data,
+               const uint8_t* __restrict__ recs, const float* __restrict__ tokscale, float* __restrict__ y,
+               uint32_t in_dim, uint32_t out_dim, uint32_t batch, uint32_t ksplit, unsigned int* err_word) {
+    using C = Cfg<NC>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * C::kStageBytes);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t n_unit = in_dim >> 8, upi = n_unit / ksplit;  // units per item
+    const uint32_t n_items = ((out_dim + BM - 1u) / BM) * ksplit;
+    const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
+    const uint32_t total = my_items * upi;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            tc5::mbar_init(&sh->full[s], kProdWarps + 1u);  // one arrival per producer warp + the TMA warp's
+            tc5::mbar_init(&sh->empty[s], 1);
+        }
+        for (uint32_t b = 0; b < 2; ++b) {
+            tc5::mbar_init(&sh->tmem_full[b], 1);
+            tc5::mbar_init(&sh->tmem_empty[b], 4);
+        }
+        sh->abort_flag = 0;
+        tc5::mbar_fence_init();
+        tc5::tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == kMmaWarp) {
+        tc5::tmem_alloc(&sh->tmem_base, C::kTmemCols);
+        tc5::tmem_relinquish();
+    }
+    tc5::fence_before_sync();
+    __syncthreads();
+    tc5::fence_after_sync();
+    const uint32_t tmem_base = sh->tmem_base;
+    const tc5::WaitCtx ctx{&sh->abort_flag, err_word};
+    pdk_pdl_launch_dependents();
+
+    if (warp < kProdWarps) {
+        // ------------------------------------------------------------ dequantizing producers
+        const uint32_t cq = lane >> 3, h = cq & 1u;      // chunks cq and cq + 4: k-slabs G0 and G0 + 2
+        const uint32_t G0 = cq >> 1;
+        const uint32_t r_in = warp * 8u + (lane & 7u);   // row inside the tile
+        const size_t row_data = (size_t)n_unit * 128u, row_rec = (size_t)n_unit * 24u;
+        // load cursor over this CTA's (item, unit) sequence
+        uint32_t l_item = blockIdx.x, l_u = 0;
+        const uint8_t* pd = data;
+        const uint8_t* pr = recs;
+        auto set_item = [&](uint32_t item) {
+            const uint32_t tile = item / ksplit, u0 = (item % ksplit) * upi;
+            const uint32_t row = min(tile * BM + r_in, out_dim - 1u);
+            pd = data + row * row_data + (size_t)u0 * 128u + cq * 16u;
+            pr = recs + row * row_rec + (size_t)u0 * 24u;
+        };
+        auto issue = [&](PStage& s) {
+            s.q[0] = pdk_ldg_stream16(pd + (size_t)l_u * 128u);
+            s.q[1] = pdk_ldg_stream16(pd + (size_t)l_u * 128u + 64u);
+            const uint8_t* rec = pr + (size_t)l_u * 24u;
+            s.dd = __ldg(reinterpret_cast<const uint32_t*>(rec));
+#pragma unroll
+            for (uint32_t i = 0; i < 2u; ++i) {
+                const uint32_t G = G0 + 2u * i;
+                s.sm[i] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(rec + 4u + 2u * G)) |
+                          ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(rec + 12u + 2u * G)) << 16);
+            }
+            if (++l_u == upi) {
+                l_u = 0;
+                l_item += gridDim.x;
+                if (l_item < n_items) set_item(l_item);
+            }
+        };
+        PStage st[kDepth];
+        if (total > 0u) {
+            set_item(blockIdx.x);
+#pragma unroll
+            for (uint32_t d = 0; d + 1u < kDepth; ++d)
+                if (d < total) issue(st[d]);
+        }
+        uint32_t stage = 0, phase = 0, c_u = 0, c_item = blockIdx.x, iter = 0;
+        bool ok = true;
+        // line of row r in a k-slab: 8-row groups of 1024 bytes, 128 bytes per row, 16-byte chunks XOR (r & 7)
+        const uint32_t line_off = (r_in >> 3) * 1024u + (r_in & 7u) * 128u;
+        auto consume = [&](const PStage& s) {
+            ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            uint8_t* a = tiles + stage * C::kStageBytes + line_off;
+            dequant_store(s.q[0], s.dd, s.sm[0], a + G0 * kSlabBytes, h, r_in & 7u);
+            dequant_store(s.q[1], s.dd, s.sm[1], a + (G0 + 2u) * kSlabBytes, h, r_in & 7u);
+            fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive(&sh->full[stage]);
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            if (++c_u == upi) {
+                // ---- the item's last unit is written: warps 0..3 drain its accumulator
+                c_u = 0;
+                if (warp < 4u) {
+                    const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
+                    if (iter == 0u) pdk_pdl_wait();  // tokscale and the zeroed y are the previous kernel's output
+                    ok = tc5::mbar_wait(&sh->tmem_full[buf], aphase, ctx, tc5::kErrTmemFullWait, buf);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) return;
+                    tc5::fence_after_sync();
+                    const uint32_t row = (c_item / ksplit) * BM + warp * 32u + lane;
+                    constexpr uint32_t HC = NC / 2u;  // token columns
+#pragma unroll 1
+                    for (uint32_t t0 = 0; t0 < HC; t0 += 16u) {
+                        uint32_t a[16], b[16];
+                        tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + buf * NC + t0, a);       // hi terms
+                        tmem_ld_32x16(tmem_base + ((warp * 32u) << 16) + buf * NC + HC + t0, b);  // lo terms
+                        tc5::tmem_ld_wait();
+                        if (row < out_dim) {
+#pragma unroll
+                            for (uint32_t i = 0; i < 16u; ++i) {
+                                const uint32_t tok = t0 + i;
+                                if (tok < batch)
+                                    atomicAdd(y + (size_t)tok * out_dim + row,
+                                              (__uint_as_float(a[i]) + __uint_as_float(b[i])) * __ldg(tokscale + tok));
+                            }
+                        }
+                    }
+                    tc5::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) tc5::mbar_arrive(&sh->tmem_empty[buf]);
+                }
+                c_item += gridDim.x;
+                ++iter;
+            }
+        };
+        for (uint32_t q = 0; q < total && ok; q += kDepth) {
+#pragma unroll
+            for (uint32_t d = 0; d < kDepth; ++d) {
+                if (q + d >= total || !ok) break;
+                if (q + d + kDepth - 1u < total) issue(st[(d + kDepth - 1u) % kDepth]);
+                consume(st[d]);
+            }
+        }
+    } else if (warp == kTmaWarp) {
+        // ------------------------------------------------------------ activation tiles (whole warp, one lane issues)
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        pdk_pdl_wait();  // the f16 rows are the previous kernel's output
+        for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const uint32_t u0 = (item % ksplit) * upi;
+            for (uint32_t u = 0; u < upi; ++u) {
+                ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, 0x10u + stage);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                uint8_t* b = tiles + stage * C::kStageBytes + kABytes;
+                tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], C::kBBytes);
+#pragma unroll
+                for (uint32_t j = 0; j < 4u; ++j)
+                    tc5::tma_load_2d_elect(b + j * C::kBSlab, &tmap_x, &sh->full[stage], (int32_t)((u0 + u) * 256u + j * 64u), 0);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok && lane == 0)
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);  // copies in flight still land in this CTA's shared memory
+    } else {
+        // ------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+        uint32_t stage = 0, phase = 0, iter = 0;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++iter) {
+            const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
+            ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc5::fence_after_sync();
+            const uint32_t d_tmem = tmem_base + buf * NC;
+            for (uint32_t u = 0; u < upi; ++u) {
+                ok = tc5::mbar_wait(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc5::fence_after_sync();
+                const uint32_t a_addr = tc5::smem_u32(tiles + stage * C::kStageBytes);
+#pragma unroll
+                for (uint32_t j = 0; j < 4u; ++j) {
+                    const uint64_t a_desc = tc5::smem_desc_sw128(a_addr + j * kSlabBytes);
+                    const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes + j * C::kBSlab);
+#pragma unroll
+                    for (uint32_t k = 0; k < 4u; ++k)  // 16 f16 = 32 bytes of K per instruction: +2 in 16-byte units
+                        mma_f16_elect(d_tmem, a_desc + 2u * k, b_desc + 2u * k, C::kIdesc, (u | j | k) != 0u);
+                }
+                tc5::mma_commit_elect(&sh->empty[stage]);
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) tc5::mma_commit_elect(&sh->tmem_full[buf]);
+        }
+    }
+
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc5::fence_after_sync();
+        tc5::tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// Scratch for the f16 activation rows and the token scales: lives in the library (the pack
+// allocates nothing at run time), one slice per stream for the first kLanes streams.
+constexpr size_t kXhBytes = (size_t)64 * kMaxK * 2u;
+constexpr size_t kSliceBytes = kXhBytes + 1024u;
+constexpr int kLanes = 2;
+__device__ __align__(1024) uint8_t g_q4k_xh[kLanes][kSliceBytes];
+
+uint8_t* xh_slice(cudaStream_t st) {
+    static uint8_t* base = [] {
+        void* p = nullptr;
+        return cudaGetSymbolAddress(&p, g_q4k_xh) == cudaSuccess ? (uint8_t*)p : (uint8_t*)nullptr;
+    }();
+    static cudaStream_t owner[kLanes];
+    static int n_owner = 0;
+    if (base == nullptr) return nullptr;
+    for (int i = 0; i < n_owner; ++i)
+        if (owner[i] == st) return base + (size_t)i * kSliceBytes;
+    if (n_owner == kLanes) return nullptr;
+    owner[n_owner] = st;
+    return base + (size_t)(n_owner++) * kSliceBytes;
+}
+
+template <uint32_t NC>
+int launch(const void* data, const void* recs, const float* x, const int8_t* xq, const float* xq_scale, float* y,
+           uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
+    using C = Cfg<NC>;
+    const uint32_t n_unit = in_dim >> 8;
+    if ((in_dim & 255u) != 0u || in_dim > kMaxK || n_unit == 0u) return -1;
+    uint8_t* slice = xh_slice(st);
+    if (slice == nullptr) return -1;
+    __half* xh = reinterpret_cast<__half*>(slice);
+    float* tokscale = reinterpret_cast<float*>(slice + kXhBytes);
+    CUtensorMap tx;
+    if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, in_dim, NC, (uint64_t)in_dim * 2u, 64u, NC))
+        return rc;
+    const size_t smem = (size_t)kStages * C::kStageBytes + sizeof(Shared) + 1024u;
+    auto kern = q4k_tc5_kernel<NC>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    if (int rc = pdk_launch_pdl(q4k_act_f16_kernel, dim3(NC / 2u + kZeroCtas), dim3(kActThreads), 0, st, x, xq, xq_scale, xh, tokscale, y,
+                                in_dim, out_dim, batch, NC / 2u))
+        return rc;
+    // two K halves per tile unless the row has an odd number of super-blocks
+    const uint32_t ksplit = (n_unit & 1u) == 0u ? 2u : 1u;
+    const uint32_t n_items = ((out_dim + BM - 1u) / BM) * ksplit;
+    uint32_t grid = (uint32_t)pdk_sm_count();
+    if (grid > n_items) grid = n_items;
+    return pdk_launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, tx, (const uint8_t*)data, (const uint8_t*)recs,
+                          (const float*)tokscale, y, in_dim, out_dim, batch, ksplit, pdk_error_word());
+}
+
+}  // namespace
+
+// Q4_K GEMM for 1 <= batch <= 32 tokens on the tcgen05 path: y f32 [batch][out_dim].
+// Activations are f32 x [batch][in_dim] or (x == nullptr) int8 xq with one f32 scale per 32
+// elements.  Returns 0 / a cudaError_t, or -1 when the shape is outside the kernel's plan (K not
+// a multiple of 256 or above 16384, more streams than scratch slices) and the caller should
+// take another route.  Two launches: the f16 activation rows (which also zeroes y), then the GEMM.
+int pdk_q4k_tc5(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale, float* y,
+                uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
+    if (batch == 0u || batch > 32u) return -1;
+    if (batch <= 16u) return launch<32>(data, scales, x, xq, xq_scale, y, in_dim, out_dim, batch, st);
+    return launch<64>(data, scales, x, xq, xq_scale, y, in_dim, out_dim, batch, st);
+}
