@@ -2,10 +2,12 @@
 //
 // With more than a handful of tokens the per-(block, token) integer fold of q4k_batch_i8.cu
 // outgrows the weight stream.  Here the CUDA cores touch each weight once, whatever the token
-// count: 16 producer warps turn the packed nibbles into f16 weights
-//     w = q * f16(d * sc) - f16(dmin * m)          (two weights per instruction)
+// count: TMA brings the packed bytes and the scale records of 128 rows into a shared-memory
+// ring (six super-block columns in flight per SM), and 16 producer warps turn the nibbles into
+// f16 weights
+//     w = (q - 8) * f16(d * sc) + f16(8 d sc - dmin m)          (two weights per instruction)
 // and write them into shared memory as the K-major, 128-byte-swizzled A operand of
-// tcgen05.mma kind::f16 (128 weight rows x 256 K per stage).  The B operand is the activation
+// tcgen05.mma kind::f16 (128 weight rows x 128 K per stage).  The B operand is the activation
 // tile: a small kernel in front scales each token by a power of two into the f16 range and
 // splits it into two f16 terms x = hi + lo (exact for bf16-valued activations, 22 bits
 // otherwise), stored as 2 * tokens rows of a library-resident f16 matrix that TMA boxes are
@@ -29,24 +31,32 @@ namespace {
 
 constexpr uint32_t BM = 128;          // weight rows per work item (MMA M)
 constexpr uint32_t kProdWarps = 16;   // dequantizing warps; warps 0..3 also drain the accumulator
-constexpr uint32_t kTmaWarp = kProdWarps, kMmaWarp = kProdWarps + 1;
-constexpr uint32_t kThreads = (kProdWarps + 2) * 32;
-constexpr uint32_t kStages = 2;       // one stage = one Q4_K super-block column (256 K) of 128 rows
+constexpr uint32_t kRawWarp = kProdWarps, kActWarp = kProdWarps + 1, kMmaWarp = kProdWarps + 2;
+constexpr uint32_t kThreads = (kProdWarps + 3) * 32;
+constexpr uint32_t kStages = 3;       // operand stages: half a Q4_K super-block column (128 K) of 128 rows
 constexpr uint32_t kSlabBytes = BM * 128u;        // [128 rows][64 f16], 8-row groups of 1024 bytes
-constexpr uint32_t kABytes = 4u * kSlabBytes;     // 65536
-constexpr uint32_t kDepth = 4;        // producer register stages (loads run three units ahead: 67 KB per SM in flight)
+constexpr uint32_t kABytes = 2u * kSlabBytes;     // 32768
+// Packed weights wait in shared memory, not in registers: a ring of TMA boxes, each two
+// super-block columns of the tile - 2 x [128 rows][128 bytes] (128-byte swizzle, so that the
+// 8 rows of a quarter-warp read fall on distinct banks) and [128 rows][48 bytes] of scale
+// records.  Two boxes = four columns = 76 KB per SM in flight, independent of the producers.
+constexpr uint32_t kRawStages = 2;
+constexpr uint32_t kRawData = BM * 128u, kRawRec = BM * 48u;
+constexpr uint32_t kRawStageBytes = 2u * kRawData + kRawRec;  // 38912
 constexpr uint32_t kMaxK = 16384;
 
 template <uint32_t NC>  // B columns = 2 * (tokens rounded up to 16 or 32)
 struct Cfg {
     static constexpr uint32_t kBSlab = NC * 128u;
-    static constexpr uint32_t kBBytes = 4u * kBSlab;
+    static constexpr uint32_t kBBytes = 2u * kBSlab;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
     static constexpr uint32_t kTmemCols = 2u * NC;  // two accumulators
     static constexpr uint32_t kIdesc = tc5::idesc_f32acc(0u, 0u, BM, NC);
 };
 
 struct Shared {
+    uint64_t raw_full[kRawStages];
+    uint64_t raw_empty[kRawStages];
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t tmem_full[2];
@@ -54,6 +64,38 @@ struct Shared {
     uint32_t tmem_base;
     int abort_flag;
 };
+
+// mbarrier wait that lets the hardware park the thread (up to the hint, in nanoseconds) instead
+// of spinning: sixteen producer warps polling a barrier took issue slots from the warps still
+// working.  Bounded like tc5::mbar_wait: after the budget the error word is set and false returned.
+__device__ __forceinline__ bool mbar_try_wait_park(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(tc5::smem_u32(bar)), "r"(parity), "r"(20000u)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_park(uint64_t* bar, uint32_t parity, const tc5::WaitCtx& ctx, unsigned int code,
+                                               unsigned int detail) {
+    if (mbar_try_wait_park(bar, parity)) return true;
+    const unsigned long long t0 = tc5::globaltimer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait_park(bar, parity)) {
+        if ((++spins & 15u) == 0u) {
+            if (*ctx.abort_flag) return false;
+            if (tc5::globaltimer_ns() - t0 > tc5::kWaitBudgetNs) {
+                *ctx.abort_flag = 1;
+                tc5::report(ctx.err, code, detail);
+                return false;
+            }
+        }
+    }
+    return true;
+}
 
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -183,17 +225,6 @@ q4k_act_f16_kernel(const float* __restrict__ x, const int8_t* __restrict__ xq, c
 
 // ---------------------------------------------------------------- the GEMM
 
-// What a producer thread holds of one unit: of ONE row, the 16-byte chunks c and c + 4 of the
-// row's 128 packed bytes (chunk c = 16 low nibbles of block 2G and 16 high nibbles of block
-// 2G+1, G = c / 2), and the row's scales.  The 8 lanes of a quarter-warp hold the same chunks
-// of 8 consecutive rows: their 16-byte stores into the swizzled tile then fall on 8 different
-// chunk positions (all 32 banks), and a warp's load covers 64 contiguous bytes of each row.
-struct PStage {
-    uint4 q[2];
-    uint32_t dd;     // {f16 d, f16 dmin}
-    uint32_t sm[2];  // per chunk: sc[2G] | sc[2G+1] << 8 | m[2G] << 16 | m[2G+1] << 24
-};
-
 // 32 weights of one row -> four 16-byte chunks of the row's 128-byte line in k-slab G:
 // chunks 2h, 2h+1 (block 2G, elements 16h..16h+15) and 4+2h, 5+2h (block 2G+1), h = c & 1.
 __device__ __forceinline__ void dequant_store(const uint4& q, uint32_t dd, uint32_t sm, uint8_t* line, uint32_t h,
@@ -226,24 +257,27 @@ __device__ __forceinline__ void dequant_store(const uint4& q, uint32_t dd, uint3
 }
 
 template <uint32_t NC>
-__global__ void __launch_bounds__(kThreads, 1)  // 18 warps: 5 on one scheduler, 96 registers per thread
-q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ data,
-               const uint8_t* __restrict__ recs, const float* __restrict__ tokscale, float* __restrict__ y,
+__global__ void __launch_bounds__(kThreads, 1)  // 19 warps: 5 on a scheduler, 96 registers per thread
+q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+               const __grid_constant__ CUtensorMap tmap_r, const float* __restrict__ tokscale, float* __restrict__ y,
                uint32_t in_dim, uint32_t out_dim, uint32_t batch, uint32_t ksplit, unsigned int* err_word) {
     using C = Cfg<NC>;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint8_t* tiles = ring + kRawStages * kRawStageBytes;
     Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * C::kStageBytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t n_unit = in_dim >> 8, upi = n_unit / ksplit;  // units per item
+    const uint32_t n_unit = in_dim >> 8, upi = n_unit / ksplit;  // units per item (even)
     const uint32_t n_items = ((out_dim + BM - 1u) / BM) * ksplit;
-    const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
-    const uint32_t total = my_items * upi;
 
     if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kRawStages; ++s) {
+            tc5::mbar_init(&sh->raw_full[s], 1);
+            tc5::mbar_init(&sh->raw_empty[s], kProdWarps);
+        }
         for (uint32_t s = 0; s < kStages; ++s) {
-            tc5::mbar_init(&sh->full[s], kProdWarps + 1u);  // one arrival per producer warp + the TMA warp's
+            tc5::mbar_init(&sh->full[s], kProdWarps + 1u);  // one arrival per producer warp + the activation loader's
             tc5::mbar_init(&sh->empty[s], 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
@@ -253,6 +287,8 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
         sh->abort_flag = 0;
         tc5::mbar_fence_init();
         tc5::tma_prefetch_desc(&tmap_x);
+        tc5::tma_prefetch_desc(&tmap_w);
+        tc5::tma_prefetch_desc(&tmap_r);
     }
     if (warp == kMmaWarp) {
         tc5::tmem_alloc(&sh->tmem_base, C::kTmemCols);
@@ -267,68 +303,53 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
 
     if (warp < kProdWarps) {
         // ------------------------------------------------------------ dequantizing producers
-        const uint32_t cq = lane >> 3, h = cq & 1u;      // chunks cq and cq + 4: k-slabs G0 and G0 + 2
-        const uint32_t G0 = cq >> 1;
-        const uint32_t r_in = warp * 8u + (lane & 7u);   // row inside the tile
-        const size_t row_data = (size_t)n_unit * 128u, row_rec = (size_t)n_unit * 24u;
-        // load cursor over this CTA's (item, unit) sequence
-        uint32_t l_item = blockIdx.x, l_u = 0;
-        const uint8_t* pd = data;
-        const uint8_t* pr = recs;
-        auto set_item = [&](uint32_t item) {
-            const uint32_t tile = item / ksplit, u0 = (item % ksplit) * upi;
-            const uint32_t row = min(tile * BM + r_in, out_dim - 1u);
-            pd = data + row * row_data + (size_t)u0 * 128u + cq * 16u;
-            pr = recs + row * row_rec + (size_t)u0 * 24u;
-        };
-        auto issue = [&](PStage& s) {
-            s.q[0] = pdk_ldg_stream16(pd + (size_t)l_u * 128u);
-            s.q[1] = pdk_ldg_stream16(pd + (size_t)l_u * 128u + 64u);
-            const uint8_t* rec = pr + (size_t)l_u * 24u;
-            s.dd = __ldg(reinterpret_cast<const uint32_t*>(rec));
-#pragma unroll
-            for (uint32_t i = 0; i < 2u; ++i) {
-                const uint32_t G = G0 + 2u * i;
-                s.sm[i] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(rec + 4u + 2u * G)) |
-                          ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(rec + 12u + 2u * G)) << 16);
-            }
-            if (++l_u == upi) {
-                l_u = 0;
-                l_item += gridDim.x;
-                if (l_item < n_items) set_item(l_item);
-            }
-        };
-        PStage st[kDepth];
-        if (total > 0u) {
-            set_item(blockIdx.x);
-#pragma unroll
-            for (uint32_t d = 0; d + 1u < kDepth; ++d)
-                if (d < total) issue(st[d]);
-        }
-        uint32_t stage = 0, phase = 0, c_u = 0, c_item = blockIdx.x, iter = 0;
+        // A thread owns one row of the tile and, per half unit, one 16-byte chunk of its packed
+        // bytes: chunk c = 4 * half + cq (16 low nibbles of block 2G, 16 high nibbles of block
+        // 2G+1, G = c / 2).  The 8 lanes of a quarter-warp hold the same chunk of 8 consecutive
+        // rows: their 16-byte accesses to the swizzled tiles fall on 8 different chunk positions.
+        const uint32_t cq = lane >> 3, h = cq & 1u;
+        const uint32_t r_in = warp * 8u + (lane & 7u), swz = r_in & 7u;
+        const uint32_t line_off = (r_in >> 3) * 1024u + swz * 128u;  // the row's 128-byte line in a tile
+        const uint32_t halves_per_item = upi * 2u;
+        const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
+        const uint32_t total = my_items * halves_per_item;
+        uint32_t stage = 0, phase = 0, rs = 0, rphase = 0, c_h = 0, c_item = blockIdx.x, iter = 0;
         bool ok = true;
-        // line of row r in a k-slab: 8-row groups of 1024 bytes, 128 bytes per row, 16-byte chunks XOR (r & 7)
-        const uint32_t line_off = (r_in >> 3) * 1024u + (r_in & 7u) * 128u;
-        auto consume = [&](const PStage& s) {
-            ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
+        for (uint32_t n = 0; n < total && ok; ++n) {
+            const uint32_t sub = n & 3u, j = sub >> 1, half = sub & 1u;  // unit j of the box, half of the unit
+            if (sub == 0u) {
+                ok = mbar_wait_park(&sh->raw_full[rs], rphase, ctx, tc5::kErrFullWait, 0x20u + rs);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
+            const uint8_t* raw = ring + rs * kRawStageBytes;
+            const uint32_t c = half * 4u + cq, G = c >> 1;
+            const uint4 q = *reinterpret_cast<const uint4*>(raw + j * kRawData + line_off + ((c ^ swz) << 4));
+            const uint8_t* rec = raw + 2u * kRawData + r_in * 48u + j * 24u;
+            const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);
+            const uint32_t sm = (uint32_t)*reinterpret_cast<const uint16_t*>(rec + 4u + 2u * G) |
+                                ((uint32_t)*reinterpret_cast<const uint16_t*>(rec + 12u + 2u * G) << 16);
+            ok = mbar_wait_park(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) return;
-            uint8_t* a = tiles + stage * C::kStageBytes + line_off;
-            dequant_store(s.q[0], s.dd, s.sm[0], a + G0 * kSlabBytes, h, r_in & 7u);
-            dequant_store(s.q[1], s.dd, s.sm[1], a + (G0 + 2u) * kSlabBytes, h, r_in & 7u);
+            if (!ok) break;
+            dequant_store(q, dd, sm, tiles + stage * C::kStageBytes + (cq >> 1) * kSlabBytes + line_off, h, swz);
             fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
             __syncwarp();
-            if (lane == 0) tc5::mbar_arrive(&sh->full[stage]);
+            if (lane == 0) {
+                tc5::mbar_arrive(&sh->full[stage]);
+                if (sub == 3u) tc5::mbar_arrive(&sh->raw_empty[rs]);  // every lane has consumed its bytes of the box
+            }
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
-            if (++c_u == upi) {
-                // ---- the item's last unit is written: warps 0..3 drain its accumulator
-                c_u = 0;
+            if (sub == 3u && ++rs == kRawStages) { rs = 0; rphase ^= 1u; }
+            if (++c_h == halves_per_item) {
+                // ---- the item's last half unit is written: warps 0..3 drain its accumulator
+                c_h = 0;
                 if (warp < 4u) {
                     const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
                     if (iter == 0u) pdk_pdl_wait();  // tokscale and the zeroed y are the previous kernel's output
-                    ok = tc5::mbar_wait(&sh->tmem_full[buf], aphase, ctx, tc5::kErrTmemFullWait, buf);
+                    ok = mbar_wait_park(&sh->tmem_full[buf], aphase, ctx, tc5::kErrTmemFullWait, buf);
                     ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) return;
+                    if (!ok) break;
                     tc5::fence_after_sync();
                     const uint32_t row = (c_item / ksplit) * BM + warp * 32u + lane;
                     constexpr uint32_t HC = NC / 2u;  // token columns
@@ -355,60 +376,74 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
                 c_item += gridDim.x;
                 ++iter;
             }
-        };
-        for (uint32_t q = 0; q < total && ok; q += kDepth) {
-#pragma unroll
-            for (uint32_t d = 0; d < kDepth; ++d) {
-                if (q + d >= total || !ok) break;
-                if (q + d + kDepth - 1u < total) issue(st[(d + kDepth - 1u) % kDepth]);
-                consume(st[d]);
+        }
+    } else if (warp == kRawWarp) {
+        // ------------------------------------------------------------ packed weights and scale records (TMA)
+        // Weights depend on nothing the previous kernel in the stream writes: no wait for it.
+        uint32_t rs = 0, rphase = 0;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const uint32_t row0 = (item / ksplit) * BM, u0 = (item % ksplit) * upi;
+            for (uint32_t u = 0; u < upi; u += 2u) {
+                ok = mbar_wait_park(&sh->raw_empty[rs], rphase ^ 1u, ctx, tc5::kErrEmptyWait, 0x20u + rs);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                uint8_t* raw = ring + rs * kRawStageBytes;
+                tc5::mbar_arrive_expect_tx_elect(&sh->raw_full[rs], kRawStageBytes);
+                tc5::tma_load_2d_elect(raw, &tmap_w, &sh->raw_full[rs], (int32_t)((u0 + u) * 128u), (int32_t)row0);
+                tc5::tma_load_2d_elect(raw + kRawData, &tmap_w, &sh->raw_full[rs], (int32_t)((u0 + u + 1u) * 128u), (int32_t)row0);
+                tc5::tma_load_2d_elect(raw + 2u * kRawData, &tmap_r, &sh->raw_full[rs], (int32_t)((u0 + u) * 24u), (int32_t)row0);
+                if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
             }
         }
-    } else if (warp == kTmaWarp) {
-        // ------------------------------------------------------------ activation tiles (whole warp, one lane issues)
+        if (!ok && lane == 0)
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);  // copies in flight still land in this CTA's shared memory
+    } else if (warp == kActWarp) {
+        // ------------------------------------------------------------ activation tiles (TMA)
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         pdk_pdl_wait();  // the f16 rows are the previous kernel's output
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const uint32_t u0 = (item % ksplit) * upi;
-            for (uint32_t u = 0; u < upi; ++u) {
-                ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, 0x10u + stage);
+            for (uint32_t hu = 0; hu < upi * 2u; ++hu) {
+                ok = mbar_wait_park(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, 0x10u + stage);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 uint8_t* b = tiles + stage * C::kStageBytes + kABytes;
                 tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], C::kBBytes);
 #pragma unroll
-                for (uint32_t j = 0; j < 4u; ++j)
-                    tc5::tma_load_2d_elect(b + j * C::kBSlab, &tmap_x, &sh->full[stage], (int32_t)((u0 + u) * 256u + j * 64u), 0);
+                for (uint32_t j = 0; j < 2u; ++j)
+                    tc5::tma_load_2d_elect(b + j * C::kBSlab, &tmap_x, &sh->full[stage],
+                                           (int32_t)(u0 * 256u + hu * 128u + j * 64u), 0);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
         if (!ok && lane == 0)
-            for (int i = 0; i < 64; ++i) __nanosleep(1000);  // copies in flight still land in this CTA's shared memory
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
     } else {
         // ------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
         uint32_t stage = 0, phase = 0, iter = 0;
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++iter) {
             const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
-            ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
+            ok = mbar_wait_park(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc5::fence_after_sync();
             const uint32_t d_tmem = tmem_base + buf * NC;
-            for (uint32_t u = 0; u < upi; ++u) {
-                ok = tc5::mbar_wait(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
+            for (uint32_t hu = 0; hu < upi * 2u; ++hu) {
+                ok = mbar_wait_park(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc5::fence_after_sync();
                 const uint32_t a_addr = tc5::smem_u32(tiles + stage * C::kStageBytes);
 #pragma unroll
-                for (uint32_t j = 0; j < 4u; ++j) {
+                for (uint32_t j = 0; j < 2u; ++j) {
                     const uint64_t a_desc = tc5::smem_desc_sw128(a_addr + j * kSlabBytes);
                     const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes + j * C::kBSlab);
 #pragma unroll
                     for (uint32_t k = 0; k < 4u; ++k)  // 16 f16 = 32 bytes of K per instruction: +2 in 16-byte units
-                        mma_f16_elect(d_tmem, a_desc + 2u * k, b_desc + 2u * k, C::kIdesc, (u | j | k) != 0u);
+                        mma_f16_elect(d_tmem, a_desc + 2u * k, b_desc + 2u * k, C::kIdesc, (hu | j | k) != 0u);
                 }
                 tc5::mma_commit_elect(&sh->empty[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -452,28 +487,35 @@ int launch(const void* data, const void* recs, const float* x, const int8_t* xq,
            uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
     using C = Cfg<NC>;
     const uint32_t n_unit = in_dim >> 8;
-    if ((in_dim & 255u) != 0u || in_dim > kMaxK || n_unit == 0u) return -1;
+    // the scale records travel in 48-byte boxes (two super-blocks), 16-byte aligned rows
+    if ((in_dim & 255u) != 0u || in_dim > kMaxK || n_unit == 0u || (n_unit & 1u) != 0u || !pdk_aligned(recs, 16)) return -1;
     uint8_t* slice = xh_slice(st);
     if (slice == nullptr) return -1;
     __half* xh = reinterpret_cast<__half*>(slice);
     float* tokscale = reinterpret_cast<float*>(slice + kXhBytes);
-    CUtensorMap tx;
+    CUtensorMap tx, tw, tr;
     if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, in_dim, NC, (uint64_t)in_dim * 2u, 64u, NC))
         return rc;
-    const size_t smem = (size_t)kStages * C::kStageBytes + sizeof(Shared) + 1024u;
+    // rows past out_dim read as zeros (d = 0: zero weights)
+    if (int rc = pdk_make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, data, in_dim / 2u, out_dim, in_dim / 2u, 128u, BM))
+        return rc;
+    if (int rc = pdk_make_tmap_2d_dense(&tr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, recs, (uint64_t)n_unit * 24u, out_dim,
+                                        (uint64_t)n_unit * 24u, 48u, BM))
+        return rc;
+    const size_t smem = (size_t)kRawStages * kRawStageBytes + (size_t)kStages * C::kStageBytes + sizeof(Shared) + 1024u;
     auto kern = q4k_tc5_kernel<NC>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    if (int rc = pdk_launch_pdl(q4k_act_f16_kernel, dim3(NC / 2u + kZeroCtas), dim3(kActThreads), 0, st, x, xq, xq_scale, xh, tokscale, y,
-                                in_dim, out_dim, batch, NC / 2u))
+    if (int rc = pdk_launch_pdl(q4k_act_f16_kernel, dim3(NC / 2u + kZeroCtas), dim3(kActThreads), 0, st, x, xq, xq_scale, xh,
+                                tokscale, y, in_dim, out_dim, batch, NC / 2u))
         return rc;
-    // two K halves per tile unless the row has an odd number of super-blocks
-    const uint32_t ksplit = (n_unit & 1u) == 0u ? 2u : 1u;
+    // two K halves per tile when each half is a whole number of record boxes
+    const uint32_t ksplit = (n_unit & 3u) == 0u ? 2u : 1u;
     const uint32_t n_items = ((out_dim + BM - 1u) / BM) * ksplit;
     uint32_t grid = (uint32_t)pdk_sm_count();
     if (grid > n_items) grid = n_items;
-    return pdk_launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, tx, (const uint8_t*)data, (const uint8_t*)recs,
-                          (const float*)tokscale, y, in_dim, out_dim, batch, ksplit, pdk_error_word());
+    return pdk_launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, tx, tw, tr, (const float*)tokscale, y, in_dim,
+                          out_dim, batch, ksplit, pdk_error_word());
 }
 
 }  // namespace
@@ -481,7 +523,8 @@ int launch(const void* data, const void* recs, const float* x, const int8_t* xq,
 // Q4_K GEMM for 1 <= batch <= 32 tokens on the tcgen05 path: y f32 [batch][out_dim].
 // Activations are f32 x [batch][in_dim] or (x == nullptr) int8 xq with one f32 scale per 32
 // elements.  Returns 0 / a cudaError_t, or -1 when the shape is outside the kernel's plan (K not
-// a multiple of 256 or above 16384, more streams than scratch slices) and the caller should
+// a multiple of 512 or above 16384, scale records not 16-byte aligned, more streams than scratch
+// slices) and the caller should
 // take another route.  Two launches: the f16 activation rows (which also zeroes y), then the GEMM.
 int pdk_q4k_tc5(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale, float* y,
                 uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
