@@ -1,4 +1,4 @@
-// gemv_i8.cu - single-token decode GEMV for Q4_K and Q8_0 planes.
+// gemv_i8.cu - single-token decode GEMV for Q4_K, Q5_K, Q4_0 and Q8_0 planes.
 //
 // Both formats are integer codes with one f32-class scale per 32 weights, and
 // the GEMV is HBM-bound (4.5 / 8.5 bits per weight, each read once), so the
@@ -108,6 +108,106 @@ struct Q4K {
             const float m0 = (float)((s.sm[1] >> 16) & 0xffu), m1 = (float)(s.sm[1] >> 24);
             acc_g8 += __low2float(dh) * (s0 * f[2] + s1 * f[3]) - __high2float(dh) * (m0 * X0 + m1 * X1);
         }
+    }
+};
+
+// Q5_K repacked (kquant_more.cu): 128 bytes of low nibbles in the Q4_K convention, then 32 bytes
+// of high bits (bit j of byte l = bit 4 of element l of block j); the record is Q4_K's.
+struct Q5K {
+    static constexpr uint32_t kDepth = 3;
+    static constexpr uint32_t kDataBytes = 160;
+    static constexpr uint32_t kRecBytes = 24;
+    struct Stage {
+        uint4 q[4];      // as Q4K
+        uint2 hb[2];     // high-bit bytes 8t..8t+7 of row g / row g+8 (the other lanes of the row hold the rest)
+        uint32_t dd[2];
+        uint32_t sm[2];
+    };
+    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
+                                                const uint8_t* r1, uint32_t t) {
+        s.q[0] = pdk_ldg_stream16(d0 + t * 32u);
+        s.q[1] = pdk_ldg_stream16(d0 + t * 32u + 16u);
+        s.q[2] = pdk_ldg_stream16(d1 + t * 32u);
+        s.q[3] = pdk_ldg_stream16(d1 + t * 32u + 16u);
+        s.hb[0] = pdk_ldg_stream8(d0 + 128u + t * 8u);
+        s.hb[1] = pdk_ldg_stream8(d1 + 128u + t * 8u);
+        s.dd[0] = __ldg(reinterpret_cast<const uint32_t*>(r0));
+        s.dd[1] = __ldg(reinterpret_cast<const uint32_t*>(r1));
+        s.sm[0] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r0 + 4u + 2u * t)) |
+                  ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r0 + 12u + 2u * t)) << 16);
+        s.sm[1] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r1 + 4u + 2u * t)) |
+                  ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r1 + 12u + 2u * t)) << 16);
+    }
+    __device__ static __forceinline__ uint32_t word(const uint4& v, uint32_t i) {
+        return i == 0u ? v.x : i == 1u ? v.y : i == 2u ? v.z : v.w;
+    }
+    // mma i: nibbles of word i as in Q4K, plus bit 2t (block 2t) / 2t+1 (block 2t+1) of the
+    // high-bit bytes 4i..4i+3 - held by lane i/2 of the row's four - as bit 4 of each code
+    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint32_t lane = threadIdx.x & 31u, t2 = 2u * (lane & 3u), src = (lane & 28u) | (i >> 1);
+        const uint32_t wl = word(s.q[i >> 2], i & 3u), wh = word(s.q[2u + (i >> 2)], i & 3u);
+        const uint32_t hl = (__shfl_sync(0xffffffffu, (i & 1u) ? s.hb[0].y : s.hb[0].x, src) >> t2) << 4;
+        const uint32_t hh = (__shfl_sync(0xffffffffu, (i & 1u) ? s.hb[1].y : s.hb[1].x, src) >> t2) << 4;
+        a0 = (wl & 0x0F0F0F0Fu) | (hl & 0x10101010u);
+        a1 = (wh & 0x0F0F0F0Fu) | (hh & 0x10101010u);
+        a2 = ((wl >> 4) & 0x0F0F0F0Fu) | ((hl >> 1) & 0x10101010u);
+        a3 = ((wh >> 4) & 0x0F0F0F0Fu) | ((hh >> 1) & 0x10101010u);
+    }
+    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float X0, float X1,
+                                                float& acc_g, float& acc_g8) {
+        {
+            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[0]);
+            const float s0 = (float)(s.sm[0] & 0xffu), s1 = (float)((s.sm[0] >> 8) & 0xffu);
+            const float m0 = (float)((s.sm[0] >> 16) & 0xffu), m1 = (float)(s.sm[0] >> 24);
+            acc_g += __low2float(dh) * (s0 * f[0] + s1 * f[1]) - __high2float(dh) * (m0 * X0 + m1 * X1);
+        }
+        {
+            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[1]);
+            const float s0 = (float)(s.sm[1] & 0xffu), s1 = (float)((s.sm[1] >> 8) & 0xffu);
+            const float m0 = (float)((s.sm[1] >> 16) & 0xffu), m1 = (float)(s.sm[1] >> 24);
+            acc_g8 += __low2float(dh) * (s0 * f[2] + s1 * f[3]) - __high2float(dh) * (m0 * X0 + m1 * X1);
+        }
+    }
+};
+
+// Q4_0 repacked (kquant_more.cu): the data plane is in the Q4_K nibble convention, the record
+// holds eight f16 block scales; w = d (q - 8), so the activation sums carry the -8.
+struct Q40 {
+    static constexpr uint32_t kDepth = 3;
+    static constexpr uint32_t kDataBytes = 128;
+    static constexpr uint32_t kRecBytes = 24;
+    struct Stage {
+        uint4 q[4];
+        uint32_t dd[2];  // {f16 d[2t], f16 d[2t+1]} of the two rows
+    };
+    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
+                                                const uint8_t* r1, uint32_t t) {
+        s.q[0] = pdk_ldg_stream16(d0 + t * 32u);
+        s.q[1] = pdk_ldg_stream16(d0 + t * 32u + 16u);
+        s.q[2] = pdk_ldg_stream16(d1 + t * 32u);
+        s.q[3] = pdk_ldg_stream16(d1 + t * 32u + 16u);
+        s.dd[0] = __ldg(reinterpret_cast<const uint32_t*>(r0 + 4u * t));
+        s.dd[1] = __ldg(reinterpret_cast<const uint32_t*>(r1 + 4u * t));
+    }
+    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint4& lo = s.q[i >> 2];
+        const uint4& hi = s.q[2u + (i >> 2)];
+        const uint32_t wl = (i & 3u) == 0u ? lo.x : (i & 3u) == 1u ? lo.y : (i & 3u) == 2u ? lo.z : lo.w;
+        const uint32_t wh = (i & 3u) == 0u ? hi.x : (i & 3u) == 1u ? hi.y : (i & 3u) == 2u ? hi.z : hi.w;
+        a0 = wl & 0x0F0F0F0Fu;
+        a1 = wh & 0x0F0F0F0Fu;
+        a2 = (wl >> 4) & 0x0F0F0F0Fu;
+        a3 = (wh >> 4) & 0x0F0F0F0Fu;
+    }
+    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float X0, float X1,
+                                                float& acc_g, float& acc_g8) {
+        const __half2 d0 = *reinterpret_cast<const __half2*>(&s.dd[0]);
+        const __half2 d1 = *reinterpret_cast<const __half2*>(&s.dd[1]);
+        const float o0 = -8.0f * X0, o1 = -8.0f * X1;
+        acc_g += __low2float(d0) * (f[0] + o0) + __high2float(d0) * (f[1] + o1);
+        acc_g8 += __low2float(d1) * (f[2] + o0) + __high2float(d1) * (f[3] + o1);
     }
 };
 
@@ -415,6 +515,16 @@ int launch(const void* data, const void* recs, const float* bias, const float* x
 int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st) {
     return launch<Q4K>(data, scales, nullptr, x, y, in_dim, out_dim, st);
+}
+
+int pdk_q4_0_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                     uint32_t out_dim, cudaStream_t st) {
+    return launch<Q40>(data, scales, nullptr, x, y, in_dim, out_dim, st);
+}
+
+int pdk_q5k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                    uint32_t out_dim, cudaStream_t st) {
+    return launch<Q5K>(data, scales, nullptr, x, y, in_dim, out_dim, st);
 }
 
 int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, const float* x, float* y,

@@ -32,6 +32,10 @@ int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq
                           uint32_t in_dim, uint32_t out_dim, cudaStream_t st);
 int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st);
+int pdk_q4_0_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                     uint32_t out_dim, cudaStream_t st);
+int pdk_q5k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                    uint32_t out_dim, cudaStream_t st);
 // q4k_batch_i8.cu: 1..16 tokens, f32 or int8 activations; -1 = shape outside its plan
 int pdk_q4k_batch_i8(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale,
                      float* y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
@@ -607,6 +611,12 @@ PDK_EXPORT int pd_kquant_gemv(const void* data, const void* scales, const void* 
                               uint32_t out_dim, uint32_t dtype, void* stream) {
     if (out_dim == 0) return 0;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
+    if ((dtype == PDK_KQ_Q4_0 || dtype == PDK_KQ_Q5K) && !force_plain() && pdk_aligned(data, 16)) {
+        const int rc = dtype == PDK_KQ_Q4_0
+                           ? pdk_q4_0_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, (cudaStream_t)stream)
+                           : pdk_q5k_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, (cudaStream_t)stream);
+        if (rc != -1) return rc;
+    }
     if (dtype != PDK_KQ_Q4K)
         return pdk_kq_more_gemm(data, scales, (const float*)x, (float*)y, in_dim, out_dim, 1u, dtype, (cudaStream_t)stream);
     return gemm_any(data, scales, (const float*)x, (float*)y, in_dim, out_dim, 1u, (cudaStream_t)stream);
@@ -617,6 +627,12 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
     if (out_dim == 0 || batch == 0) return 0;
     if (batch > 64u) return cudaErrorInvalidValue;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
+    if ((dtype == PDK_KQ_Q4_0 || dtype == PDK_KQ_Q5K) && batch == 1u && !force_plain() && pdk_aligned(data, 16)) {
+        const int rc = dtype == PDK_KQ_Q4_0
+                           ? pdk_q4_0_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, (cudaStream_t)stream)
+                           : pdk_q5k_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, (cudaStream_t)stream);
+        if (rc != -1) return rc;
+    }
     if (dtype != PDK_KQ_Q4K)
         return pdk_kq_more_gemm(data, scales, (const float*)x, (float*)y, in_dim, out_dim, batch, dtype,
                                 (cudaStream_t)stream);

@@ -69,8 +69,45 @@ def clones_for(nbytes):
     return max(2, -(-2 * L2_BYTES // max(nbytes, 1)) + 1)
 
 
+KQ_MORE = {"q5_k": (13, 176, 256), "q6_k": (14, 210, 256), "q4_0": (2, 18, 32)}  # ggml id, block bytes, elements
+
+
+def raw_kquant_blocks(name, n_elems):
+    """Random raw ggml blocks with small finite f16 scales (there is no quantizer for these formats)."""
+    _, nbytes, elems = KQ_MORE[name]
+    n_blocks = n_elems // elems
+    g = torch.Generator(device="cuda").manual_seed(7)
+    raw = torch.randint(0, 256, (n_blocks, nbytes), dtype=torch.uint8, device="cuda", generator=g)
+    d = (torch.rand(n_blocks, device="cuda", generator=g) * 0.01 + 1e-4).to(torch.float16).view(torch.uint8).view(n_blocks, 2)
+    if name == "q6_k":
+        raw[:, 208:210] = d
+    else:
+        raw[:, 0:2] = d
+        if name == "q5_k":
+            raw[:, 2:4] = d.flip(0)
+    return raw.reshape(-1)
+
+
 def bench_q4k(ex, a):
     k, n, m = a.k, a.n, a.m
+    if a.dtype != "q4_k":
+        ty, nbytes, elems = KQ_MORE[a.dtype]
+        raw = raw_kquant_blocks(a.dtype, n * k)
+        data_b = {"q5_k": 160, "q6_k": 192, "q4_0": 128}[a.dtype]
+        from .planes import RepackedKQ
+        planes = []
+        for _ in range(clones_for(n * k // 256 * (data_b + 24))):
+            data = torch.empty(n * k // 256 * data_b, dtype=torch.uint8, device="cuda")
+            scales = torch.empty(n * k // 256 * 24, dtype=torch.uint8, device="cuda")
+            ex.pack.call("kquant_repack", raw, data, scales, n * k // 256, ty, stream=torch.cuda.current_stream().cuda_stream)
+            planes.append(RepackedKQ(data, scales, (k, n), ty))
+        x = synth.bf16_round(synth.normal(m * k, 2, 1.0, "cuda"))
+        y = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+        if m == 1:
+            sec = time_launches(lambda i: ex.kquant_gemv(planes[i % len(planes)], x, y), a.iters)
+        else:
+            sec = time_launches(lambda i: ex.kquant_gemm_f32(planes[i % len(planes)], x, y, m), a.iters)
+        return sec, {"bound": "hbm", "bytes": n * k // elems * nbytes + m * k * 2 + m * n * 4, "dtype": a.dtype}
     raw = synth.quantize_q4_k(synth.normal(n * k, 1, 0.02, "cuda"))
     planes = [ex.repack_kquant_raw(raw, k, n) for _ in range(clones_for(n * k // 256 * 152))]
     x = synth.bf16_round(synth.normal(m * k, 2, 1.0, "cuda"))
@@ -425,6 +462,7 @@ def main():
     ap.add_argument("--moe-path", default="tc5", choices=["tc5", "mma"],
                     help="expert GEMMs: block-scaled tcgen05 (default) or the mma.sync kernels")
     ap.add_argument("--graph", action="store_true", help="replay the timed launches from a CUDA graph (moe_mxfp4, moe_ep, q4k_gemv, q8_gemv, nvf4_gemv)")
+    ap.add_argument("--dtype", default="q4_k", choices=["q4_k", "q5_k", "q6_k", "q4_0"], help="q4k_gemv: the plane's format")
     ap.add_argument("--pack", default=None, help="path of a kernel-pack library to time instead of this package's")
     a = ap.parse_args()
     dm, dn, dk = DEFAULTS[a.op]

@@ -245,10 +245,11 @@ def raw_kquant(name, n_super, seed):
 KQ = {"q5_k": (13, 160), "q6_k": (14, 192), "q4_0": (2, 128)}
 
 
+@pytest.mark.parametrize("k,n", [(1024, 70), (5120, 333), (512, 40)])
 @pytest.mark.parametrize("name", sorted(KQ))
-def test_more_kquants_dequant_repack_gemv(pack, name):
+def test_more_kquants_dequant_repack_gemv(pack, name, k, n):
+    """(512, 40) is below the tensor-core GEMV's four super-blocks per row: the plain kernel's route."""
     dtype, datab = KQ[name]
-    k, n = 1024, 70
     ns = n * k // 256
     raw = raw_kquant(name, ns, 720 + dtype)
     want = oracle.dequant_kquant(name, raw)

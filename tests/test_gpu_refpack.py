@@ -299,4 +299,5 @@ def test_more_kquants_against_reference_pack(pack, ref, name, dtype, datab):
         y = torch.zeros(n, dtype=torch.float32, device="cuda")
         return (dev(planes[0][0]), dev(planes[0][1]), dev_f32(x), y, k, n, dtype), [y]
     ours, theirs = (o[0].view(np.float32) for o in run_both(pack, ref, "kquant_gemv", mkg, 1))
-    assert rel_l2(ours, theirs.astype(np.float64)) < 1e-5 < TOL
+    # Q5_K and Q4_0 run the integer tensor-core GEMV (15-bit block-floating activations), as Q4_K does
+    assert rel_l2(ours, theirs.astype(np.float64)) < 1e-4 < TOL
