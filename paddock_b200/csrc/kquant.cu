@@ -36,6 +36,8 @@ int pdk_q4_0_gemv_i8(const void* data, const void* scales, const float* x, float
                      uint32_t out_dim, cudaStream_t st);
 int pdk_q5k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st);
+int pdk_q6k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                    uint32_t out_dim, cudaStream_t st);  // gemv_q6k.cu
 // q4k_batch_i8.cu: 1..16 tokens, f32 or int8 activations; -1 = shape outside its plan
 int pdk_q4k_batch_i8(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale,
                      float* y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
@@ -571,6 +573,15 @@ int gemm_any(const void* data, const void* scales, const float* x, float* y, uin
     return plain_batch(data, scales, x, y, in_dim, out_dim, batch, st);
 }
 
+// Q4_0 / Q5_K / Q6_K decode GEMV on the integer tensor path; -1 = shape outside the kernels' plan
+int more_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                 uint32_t dtype, cudaStream_t st) {
+    if (dtype == PDK_KQ_Q4_0) return pdk_q4_0_gemv_i8(data, scales, x, y, in_dim, out_dim, st);
+    if (dtype == PDK_KQ_Q5K) return pdk_q5k_gemv_i8(data, scales, x, y, in_dim, out_dim, st);
+    if (dtype == PDK_KQ_Q6K) return pdk_q6k_gemv_i8(data, scales, x, y, in_dim, out_dim, st);
+    return -1;
+}
+
 int check_gemv(const void* data, const void* scales, const void* x, const void* y, uint32_t in_dim, uint32_t dtype) {
     if (dtype != PDK_KQ_Q4K && !pdk_kq_more_has(dtype))
         return dtype == PDK_KQ_IQ4XS ? cudaErrorNotSupported : cudaErrorInvalidValue;
@@ -611,10 +622,8 @@ PDK_EXPORT int pd_kquant_gemv(const void* data, const void* scales, const void* 
                               uint32_t out_dim, uint32_t dtype, void* stream) {
     if (out_dim == 0) return 0;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
-    if ((dtype == PDK_KQ_Q4_0 || dtype == PDK_KQ_Q5K) && !force_plain() && pdk_aligned(data, 16)) {
-        const int rc = dtype == PDK_KQ_Q4_0
-                           ? pdk_q4_0_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, (cudaStream_t)stream)
-                           : pdk_q5k_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, (cudaStream_t)stream);
+    if (dtype != PDK_KQ_Q4K && !force_plain() && pdk_aligned(data, 16)) {
+        const int rc = more_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, dtype, (cudaStream_t)stream);
         if (rc != -1) return rc;
     }
     if (dtype != PDK_KQ_Q4K)
@@ -627,10 +636,8 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
     if (out_dim == 0 || batch == 0) return 0;
     if (batch > 64u) return cudaErrorInvalidValue;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
-    if ((dtype == PDK_KQ_Q4_0 || dtype == PDK_KQ_Q5K) && batch == 1u && !force_plain() && pdk_aligned(data, 16)) {
-        const int rc = dtype == PDK_KQ_Q4_0
-                           ? pdk_q4_0_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, (cudaStream_t)stream)
-                           : pdk_q5k_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, (cudaStream_t)stream);
+    if (dtype != PDK_KQ_Q4K && batch == 1u && !force_plain() && pdk_aligned(data, 16)) {
+        const int rc = more_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, dtype, (cudaStream_t)stream);
         if (rc != -1) return rc;
     }
     if (dtype != PDK_KQ_Q4K)

@@ -1,9 +1,9 @@
 // kquant_more.cu - the other resident formats behind the k-quant slots: Q5_K, Q6_K and
 // Q4_0 (packs/cuda/src/quant/kquant.cuh:37-80 for the layouts, :144-250 dequant, :255-345
-// repack, :372-653 GEMV).  Dequant and repack are bit- and byte-exact; the GEMV / small
-// batch GEMM is a plain f32 kernel (one warp per output row, lane l takes element l of each
-// 32-element sub-block so every load instruction covers whole lines) - these formats carry a
-// minority of a model's tensors and do not have the tensor-core streaming kernel yet.
+// repack, :372-653 GEMV).  Dequant and repack are bit- and byte-exact.  The GEMM here is a
+// plain f32 kernel (one warp per output row, lane l takes element l of each 32-element
+// sub-block so every load instruction covers whole lines): it serves more than one token and
+// the shapes the tensor-core decode kernels (gemv_i8.cu, gemv_q6k.cu) decline.
 //
 // Repacked planes (the reference's byte budgets):
 //   Q5_K  data 160 B/sb = qs[128] then qh[32];  record 24 B {f16 d, f16 dmin, u8 sc[8], u8 m[8], pad4}
