@@ -3,7 +3,7 @@
 // With more than a handful of tokens the per-(block, token) integer fold of q4k_batch_i8.cu
 // outgrows the weight stream.  Here the CUDA cores touch each weight once, whatever the token
 // count: TMA brings the packed bytes and the scale records of 128 rows into a shared-memory
-// ring (six super-block columns in flight per SM), and 16 producer warps turn the nibbles into
+// ring (four super-block columns in flight per SM), and 8 producer warps turn the nibbles into
 // f16 weights
 //     w = (q - 8) * f16(d * sc) + f16(8 d sc - dmin m)          (two weights per instruction)
 // and write them into shared memory as the K-major, 128-byte-swizzled A operand of
@@ -30,10 +30,10 @@
 namespace {
 
 constexpr uint32_t BM = 128;          // weight rows per work item (MMA M)
-constexpr uint32_t kProdWarps = 16;   // dequantizing warps; warps 0..3 also drain the accumulator
+constexpr uint32_t kProdWarps = 8;    // dequantizing warps; warps 0..3 also drain the accumulator
 constexpr uint32_t kRawWarp = kProdWarps, kActWarp = kProdWarps + 1, kMmaWarp = kProdWarps + 2;
 constexpr uint32_t kThreads = (kProdWarps + 3) * 32;
-constexpr uint32_t kStages = 3;       // operand stages: half a Q4_K super-block column (128 K) of 128 rows
+constexpr uint32_t kMaxStages = 3;    // operand stages: half a Q4_K super-block column (128 K) of 128 rows
 constexpr uint32_t kSlabBytes = BM * 128u;        // [128 rows][64 f16], 8-row groups of 1024 bytes
 constexpr uint32_t kABytes = 2u * kSlabBytes;     // 32768
 // Packed weights wait in shared memory, not in registers: a ring of TMA boxes, each two
@@ -45,11 +45,21 @@ constexpr uint32_t kRawData = BM * 128u, kRawRec = BM * 48u;
 constexpr uint32_t kRawStageBytes = 2u * kRawData + kRawRec;  // 38912
 constexpr uint32_t kMaxK = 16384;
 
-template <uint32_t NC>  // B columns = 2 * (tokens rounded up to 16 or 32)
+// NC = B columns = 2 * (tokens rounded up to 16 or 32).  BRAW: the activation tiles of two
+// super-block columns travel in the weight ring's boxes (everything the tensor core waits for
+// then arrives long before it is needed; with the tiles fetched per operand stage, the L2 round
+// trip between "stage free" and "stage full" bounded the kernel whatever the producers did).
+// The ring then holds 70 KB per box: it fits for NC = 32 only, NC = 64 fetches per operand stage.
+template <uint32_t NC>
 struct Cfg {
+    static constexpr bool BRAW = NC <= 32u;
     static constexpr uint32_t kBSlab = NC * 128u;
-    static constexpr uint32_t kBBytes = 2u * kBSlab;
-    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kBBytes = 2u * kBSlab;  // per half unit
+    static constexpr uint32_t kStages = BRAW ? 2u : 3u;
+    static constexpr uint32_t kStageBytes = kABytes + (BRAW ? 0u : kBBytes);
+    static constexpr uint32_t kRawBytes = kRawStageBytes + (BRAW ? 4u * kBBytes : 0u);
+    static constexpr uint32_t kFullCount = kProdWarps + (BRAW ? 0u : 1u);
+    static constexpr uint32_t kRawEmptyCount = kProdWarps + (BRAW ? 1u : 0u);
     static constexpr uint32_t kTmemCols = 2u * NC;  // two accumulators
     static constexpr uint32_t kIdesc = tc5::idesc_f32acc(0u, 0u, BM, NC);
 };
@@ -57,8 +67,8 @@ struct Cfg {
 struct Shared {
     uint64_t raw_full[kRawStages];
     uint64_t raw_empty[kRawStages];
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
@@ -257,14 +267,15 @@ __device__ __forceinline__ void dequant_store(const uint4& q, uint32_t dd, uint3
 }
 
 template <uint32_t NC>
-__global__ void __launch_bounds__(kThreads, 1)  // 19 warps: 5 on a scheduler, 96 registers per thread
+__global__ void __launch_bounds__(kThreads, 1)
 q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                const __grid_constant__ CUtensorMap tmap_r, const float* __restrict__ tokscale, float* __restrict__ y,
                uint32_t in_dim, uint32_t out_dim, uint32_t batch, uint32_t ksplit, unsigned int* err_word) {
     using C = Cfg<NC>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
-    uint8_t* tiles = ring + kRawStages * kRawStageBytes;
+    constexpr uint32_t kStages = C::kStages;
+    uint8_t* tiles = ring + kRawStages * C::kRawBytes;
     Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * C::kStageBytes);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -274,10 +285,10 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kRawStages; ++s) {
             tc5::mbar_init(&sh->raw_full[s], 1);
-            tc5::mbar_init(&sh->raw_empty[s], kProdWarps);
+            tc5::mbar_init(&sh->raw_empty[s], C::kRawEmptyCount);
         }
         for (uint32_t s = 0; s < kStages; ++s) {
-            tc5::mbar_init(&sh->full[s], kProdWarps + 1u);  // one arrival per producer warp + the activation loader's
+            tc5::mbar_init(&sh->full[s], C::kFullCount);  // one arrival per producer warp (+ the activation loader's)
             tc5::mbar_init(&sh->empty[s], 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
@@ -303,12 +314,14 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 
     if (warp < kProdWarps) {
         // ------------------------------------------------------------ dequantizing producers
-        // A thread owns one row of the tile and, per half unit, one 16-byte chunk of its packed
-        // bytes: chunk c = 4 * half + cq (16 low nibbles of block 2G, 16 high nibbles of block
-        // 2G+1, G = c / 2).  The 8 lanes of a quarter-warp hold the same chunk of 8 consecutive
-        // rows: their 16-byte accesses to the swizzled tiles fall on 8 different chunk positions.
-        const uint32_t cq = lane >> 3, h = cq & 1u;
-        const uint32_t r_in = warp * 8u + (lane & 7u), swz = r_in & 7u;
+        // A thread owns one row of the tile and, per half unit, the row's whole 128-byte line of
+        // one k-slab: the two 16-byte chunks 2G, 2G+1 of its packed bytes (chunk 2G + h = 16 low
+        // nibbles of block 2G, elements 16h.., and 16 high nibbles of block 2G+1), G = 2 * half + sl.
+        // One scale preparation and one barrier round per 64 weights.  The 8 lanes of a
+        // quarter-warp hold 8 consecutive rows of the same slab: their 16-byte accesses to the
+        // swizzled tiles fall on 8 different chunk positions.
+        const uint32_t sl = lane >> 4;
+        const uint32_t r_in = warp * 16u + (lane & 15u), swz = r_in & 7u;
         const uint32_t line_off = (r_in >> 3) * 1024u + swz * 128u;  // the row's 128-byte line in a tile
         const uint32_t halves_per_item = upi * 2u;
         const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
@@ -322,9 +335,10 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
-            const uint8_t* raw = ring + rs * kRawStageBytes;
-            const uint32_t c = half * 4u + cq, G = c >> 1;
-            const uint4 q = *reinterpret_cast<const uint4*>(raw + j * kRawData + line_off + ((c ^ swz) << 4));
+            const uint8_t* raw = ring + rs * C::kRawBytes;
+            const uint32_t G = half * 2u + sl;
+            const uint4 q0 = *reinterpret_cast<const uint4*>(raw + j * kRawData + line_off + (((2u * G) ^ swz) << 4));
+            const uint4 q1 = *reinterpret_cast<const uint4*>(raw + j * kRawData + line_off + (((2u * G + 1u) ^ swz) << 4));
             const uint8_t* rec = raw + 2u * kRawData + r_in * 48u + j * 24u;
             const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);
             const uint32_t sm = (uint32_t)*reinterpret_cast<const uint16_t*>(rec + 4u + 2u * G) |
@@ -332,7 +346,9 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             ok = mbar_wait_park(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            dequant_store(q, dd, sm, tiles + stage * C::kStageBytes + (cq >> 1) * kSlabBytes + line_off, h, swz);
+            uint8_t* line = tiles + stage * C::kStageBytes + sl * kSlabBytes + line_off;
+            dequant_store(q0, dd, sm, line, 0u, swz);
+            dequant_store(q1, dd, sm, line, 1u, swz);
             fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) {
@@ -381,24 +397,35 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         // ------------------------------------------------------------ packed weights and scale records (TMA)
         // Weights depend on nothing the previous kernel in the stream writes: no wait for it.
         uint32_t rs = 0, rphase = 0;
-        bool ok = true;
+        bool ok = true, waited = false;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const uint32_t row0 = (item / ksplit) * BM, u0 = (item % ksplit) * upi;
             for (uint32_t u = 0; u < upi; u += 2u) {
                 ok = mbar_wait_park(&sh->raw_empty[rs], rphase ^ 1u, ctx, tc5::kErrEmptyWait, 0x20u + rs);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                uint8_t* raw = ring + rs * kRawStageBytes;
-                tc5::mbar_arrive_expect_tx_elect(&sh->raw_full[rs], kRawStageBytes);
+                uint8_t* raw = ring + rs * C::kRawBytes;
+                tc5::mbar_arrive_expect_tx_elect(&sh->raw_full[rs], C::kRawBytes);
                 tc5::tma_load_2d_elect(raw, &tmap_w, &sh->raw_full[rs], (int32_t)((u0 + u) * 128u), (int32_t)row0);
                 tc5::tma_load_2d_elect(raw + kRawData, &tmap_w, &sh->raw_full[rs], (int32_t)((u0 + u + 1u) * 128u), (int32_t)row0);
                 tc5::tma_load_2d_elect(raw + 2u * kRawData, &tmap_r, &sh->raw_full[rs], (int32_t)((u0 + u) * 24u), (int32_t)row0);
+                if (C::BRAW) {
+                    if (!waited) {  // the f16 rows are the previous kernel's output; the weights above are not
+                        pdk_pdl_wait();
+                        waited = true;
+                    }
+#pragma unroll
+                    for (uint32_t j = 0; j < 8u; ++j)  // 4 half units x 2 k-slabs of 64
+                        tc5::tma_load_2d_elect(raw + kRawStageBytes + j * C::kBSlab, &tmap_x, &sh->raw_full[rs],
+                                               (int32_t)((u0 + u) * 256u + j * 64u), 0);
+                }
                 if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
             }
         }
         if (!ok && lane == 0)
             for (int i = 0; i < 64; ++i) __nanosleep(1000);  // copies in flight still land in this CTA's shared memory
     } else if (warp == kActWarp) {
+        if (!C::BRAW) {
         // ------------------------------------------------------------ activation tiles (TMA)
         uint32_t stage = 0, phase = 0;
         bool ok = true;
@@ -420,9 +447,10 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         }
         if (!ok && lane == 0)
             for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
     } else {
         // ------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
-        uint32_t stage = 0, phase = 0, iter = 0;
+        uint32_t stage = 0, phase = 0, iter = 0, rs = 0, rphase = 0;
         bool ok = true;
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++iter) {
             const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
@@ -432,21 +460,32 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             tc5::fence_after_sync();
             const uint32_t d_tmem = tmem_base + buf * NC;
             for (uint32_t hu = 0; hu < upi * 2u; ++hu) {
+                if (C::BRAW && (hu & 3u) == 0u) {  // the activation tiles of this pair of units are in the weight box
+                    ok = mbar_wait_park(&sh->raw_full[rs], rphase, ctx, tc5::kErrFullWait, 0x30u + rs);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                }
                 ok = mbar_wait_park(&sh->full[stage], phase, ctx, tc5::kErrFullWait, stage);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc5::fence_after_sync();
                 const uint32_t a_addr = tc5::smem_u32(tiles + stage * C::kStageBytes);
+                const uint32_t b_addr = C::BRAW ? tc5::smem_u32(ring + rs * C::kRawBytes + kRawStageBytes) + (hu & 3u) * C::kBBytes
+                                                : a_addr + kABytes;
 #pragma unroll
                 for (uint32_t j = 0; j < 2u; ++j) {
                     const uint64_t a_desc = tc5::smem_desc_sw128(a_addr + j * kSlabBytes);
-                    const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes + j * C::kBSlab);
+                    const uint64_t b_desc = tc5::smem_desc_sw128(b_addr + j * C::kBSlab);
 #pragma unroll
                     for (uint32_t k = 0; k < 4u; ++k)  // 16 f16 = 32 bytes of K per instruction: +2 in 16-byte units
                         mma_f16_elect(d_tmem, a_desc + 2u * k, b_desc + 2u * k, C::kIdesc, (hu | j | k) != 0u);
                 }
                 tc5::mma_commit_elect(&sh->empty[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                if (C::BRAW && (hu & 3u) == 3u) {  // the box's activation tiles have been read
+                    tc5::mma_commit_elect(&sh->raw_empty[rs]);
+                    if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
+                }
             }
             if (ok) tc5::mma_commit_elect(&sh->tmem_full[buf]);
         }
@@ -502,7 +541,7 @@ int launch(const void* data, const void* recs, const float* x, const int8_t* xq,
     if (int rc = pdk_make_tmap_2d_dense(&tr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, recs, (uint64_t)n_unit * 24u, out_dim,
                                         (uint64_t)n_unit * 24u, 48u, BM))
         return rc;
-    const size_t smem = (size_t)kRawStages * kRawStageBytes + (size_t)kStages * C::kStageBytes + sizeof(Shared) + 1024u;
+    const size_t smem = (size_t)kRawStages * C::kRawBytes + (size_t)C::kStages * C::kStageBytes + sizeof(Shared) + 1024u;
     auto kern = q4k_tc5_kernel<NC>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
