@@ -6,8 +6,8 @@
 // ring (four super-block columns in flight per SM), and 8 producer warps turn the nibbles into
 // f16 weights
 //     w = (q - 8) * f16(d * sc) + f16(8 d sc - dmin m)          (two weights per instruction)
-// and write them into shared memory as the K-major, 128-byte-swizzled A operand of
-// tcgen05.mma kind::f16 (128 weight rows x 128 K per stage).  The B operand is the activation
+// and store them from registers into tensor memory, where tcgen05.mma kind::f16 takes its A
+// operand (128 weight rows = 128 lanes, 128 K = 64 columns per stage, three stages).  The B operand is the activation
 // tile: a small kernel in front scales each token by a power of two into the f16 range and
 // splits it into two f16 terms x = hi + lo (exact for bf16-valued activations, 22 bits
 // otherwise), stored as 2 * tokens rows of a library-resident f16 matrix that TMA boxes are
@@ -34,8 +34,6 @@ constexpr uint32_t kProdWarps = 8;    // dequantizing warps; warps 0..3 also dra
 constexpr uint32_t kRawWarp = kProdWarps, kActWarp = kProdWarps + 1, kMmaWarp = kProdWarps + 2;
 constexpr uint32_t kThreads = (kProdWarps + 3) * 32;
 constexpr uint32_t kMaxStages = 3;    // operand stages: half a Q4_K super-block column (128 K) of 128 rows
-constexpr uint32_t kSlabBytes = BM * 128u;        // [128 rows][64 f16], 8-row groups of 1024 bytes
-constexpr uint32_t kABytes = 2u * kSlabBytes;     // 32768
 // Packed weights wait in shared memory, not in registers: a ring of TMA boxes, each two
 // super-block columns of the tile - 2 x [128 rows][128 bytes] (128-byte swizzle, so that the
 // 8 rows of a quarter-warp read fall on distinct banks) and [128 rows][48 bytes] of scale
@@ -55,12 +53,14 @@ struct Cfg {
     static constexpr bool BRAW = NC <= 32u;
     static constexpr uint32_t kBSlab = NC * 128u;
     static constexpr uint32_t kBBytes = 2u * kBSlab;  // per half unit
-    static constexpr uint32_t kStages = BRAW ? 2u : 3u;
-    static constexpr uint32_t kStageBytes = kABytes + (BRAW ? 0u : kBBytes);
+    static constexpr uint32_t kStages = 3u;                          // A operand stages in tensor memory
+    static constexpr uint32_t kStageBytes = BRAW ? 0u : kBBytes;     // shared-memory stage: the activation tile, if not in the ring
     static constexpr uint32_t kRawBytes = kRawStageBytes + (BRAW ? 4u * kBBytes : 0u);
     static constexpr uint32_t kFullCount = kProdWarps + (BRAW ? 0u : 1u);
     static constexpr uint32_t kRawEmptyCount = kProdWarps + (BRAW ? 1u : 0u);
-    static constexpr uint32_t kTmemCols = 2u * NC;  // two accumulators
+    static constexpr uint32_t kACol0 = 2u * NC;                      // after the two accumulators
+    static constexpr uint32_t kACols = 64u;                          // per stage: 128 K as f16 pairs
+    static constexpr uint32_t kTmemCols = NC <= 32u ? 256u : 512u;   // 2 NC + 3 * 64, rounded up to a power of two
     static constexpr uint32_t kIdesc = tc5::idesc_f32acc(0u, 0u, BM, NC);
 };
 
@@ -105,18 +105,6 @@ __device__ __forceinline__ bool mbar_wait_park(uint64_t* bar, uint32_t parity, c
         }
     }
     return true;
-}
-
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void mma_f16_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                              uint32_t accumulate) {
-    asm volatile(TC5_ELECT
-                 ".reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-                 : "memory");
 }
 
 // TMEM -> registers: 32 lanes x 16 columns of 32 bits per warp
@@ -235,10 +223,28 @@ q4k_act_f16_kernel(const float* __restrict__ x, const int8_t* __restrict__ xq, c
 
 // ---------------------------------------------------------------- the GEMM
 
-// 32 weights of one row -> four 16-byte chunks of the row's 128-byte line in k-slab G:
-// chunks 2h, 2h+1 (block 2G, elements 16h..16h+15) and 4+2h, 5+2h (block 2G+1), h = c & 1.
-__device__ __forceinline__ void dequant_store(const uint4& q, uint32_t dd, uint32_t sm, uint8_t* line, uint32_t h,
-                                              uint32_t swz) {
+// 8 registers -> 8 consecutive 32-bit columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// A operand from tensor memory (row i of the 128 in lane i, two f16 of consecutive k per
+// 32-bit column), B operand from shared memory
+__device__ __forceinline__ void mma_f16_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(TC5_ELECT
+                 ".reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+
+// 32 weights of one row (16 low nibbles of block 2G, 16 high nibbles of block 2G+1) -> f16 pairs
+__device__ __forceinline__ void dequant_regs(const uint4& q, uint32_t dd, uint32_t sm, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
     const __half2 dh = *reinterpret_cast<const __half2*>(&dd);
     const float d = __low2float(dh), dmin = __high2float(dh);
     // w = dsc * (q - 8) + (8 dsc - dmin m): the centred nibble halves what the scale's f16 rounding costs
@@ -250,7 +256,6 @@ __device__ __forceinline__ void dequant_store(const uint4& q, uint32_t dd, uint3
     const uint32_t magic = 0x64086408u;     // f16 1032 twice: (0x6400 | q) - 1032 = q - 8
     const uint32_t magic_hi = 0x64806480u;  // f16 1152 twice: (0x6400 | q << 4) - 1152 = 16 (q - 8)
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    uint32_t lo[8], hi[8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t p01 = prmt(w[i], 0x64646464u, 0x4140u);  // bytes {b0, 0x64, b1, 0x64}
@@ -260,10 +265,6 @@ __device__ __forceinline__ void dequant_store(const uint4& q, uint32_t dd, uint3
         hi[2 * i] = h2_fma(h2_sub(p01 & 0x64F064F0u, magic_hi), s_hi, o_hi);
         hi[2 * i + 1] = h2_fma(h2_sub(p23 & 0x64F064F0u, magic_hi), s_hi, o_hi);
     }
-    *reinterpret_cast<uint4*>(line + (((2u * h) ^ swz) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    *reinterpret_cast<uint4*>(line + (((2u * h + 1u) ^ swz) << 4)) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-    *reinterpret_cast<uint4*>(line + (((4u + 2u * h) ^ swz) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-    *reinterpret_cast<uint4*>(line + (((5u + 2u * h) ^ swz) << 4)) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
 }
 
 template <uint32_t NC>
@@ -314,15 +315,16 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 
     if (warp < kProdWarps) {
         // ------------------------------------------------------------ dequantizing producers
-        // A thread owns one row of the tile and, per half unit, the row's whole 128-byte line of
-        // one k-slab: the two 16-byte chunks 2G, 2G+1 of its packed bytes (chunk 2G + h = 16 low
-        // nibbles of block 2G, elements 16h.., and 16 high nibbles of block 2G+1), G = 2 * half + sl.
-        // One scale preparation and one barrier round per 64 weights.  The 8 lanes of a
-        // quarter-warp hold 8 consecutive rows of the same slab: their 16-byte accesses to the
-        // swizzled tiles fall on 8 different chunk positions.
-        const uint32_t sl = lane >> 4;
-        const uint32_t r_in = warp * 16u + (lane & 15u), swz = r_in & 7u;
-        const uint32_t line_off = (r_in >> 3) * 1024u + swz * 128u;  // the row's 128-byte line in a tile
+        // A thread owns one row of the tile - the tensor-memory lane its warp may write: warp w
+        // serves lanes 32 (w % 4).. - and, per half unit, 64 K of it (k-slab sl = w / 4): the two
+        // 16-byte chunks 2G, 2G+1 of the row's packed bytes, G = 2 * half + sl.  The f16 pairs go
+        // straight from registers into the A operand's tensor-memory columns: no shared-memory
+        // copy of the dequantized weights, nothing for the tensor core to fetch but the small
+        // activation tile.  The 8 lanes of a quarter-warp hold 8 consecutive rows: their 16-byte
+        // reads of the swizzled weight box fall on 8 different chunk positions.
+        const uint32_t qd = warp & 3u, sl = warp >> 2;
+        const uint32_t r_in = qd * 32u + lane, swz = r_in & 7u;
+        const uint32_t line_off = (r_in >> 3) * 1024u + swz * 128u;  // the row's 128-byte line in a weight box
         const uint32_t halves_per_item = upi * 2u;
         const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
         const uint32_t total = my_items * halves_per_item;
@@ -346,10 +348,20 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             ok = mbar_wait_park(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            uint8_t* line = tiles + stage * C::kStageBytes + sl * kSlabBytes + line_off;
-            dequant_store(q0, dd, sm, line, 0u, swz);
-            dequant_store(q1, dd, sm, line, 1u, swz);
-            fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+            tc5::fence_after_sync();  // the MMAs that read this stage's columns are complete
+            {
+                // columns of slab sl: block 2G elements 0..15 | 16..31 | block 2G+1 elements 0..15 | 16..31
+                uint32_t lo0[8], hi0[8], lo1[8], hi1[8];
+                dequant_regs(q0, dd, sm, lo0, hi0);
+                dequant_regs(q1, dd, sm, lo1, hi1);
+                const uint32_t ta = tmem_base + ((qd * 32u) << 16) + C::kACol0 + stage * C::kACols + sl * 32u;
+                tmem_st_32x8(ta, lo0);
+                tmem_st_32x8(ta + 8u, lo1);
+                tmem_st_32x8(ta + 16u, hi0);
+                tmem_st_32x8(ta + 24u, hi1);
+            }
+            tmem_st_wait();
+            tc5::fence_before_sync();  // tensor-memory stores -> ordered before the arrival the MMA warp waits for
             __syncwarp();
             if (lane == 0) {
                 tc5::mbar_arrive(&sh->full[stage]);
@@ -436,7 +448,7 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 ok = mbar_wait_park(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, 0x10u + stage);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                uint8_t* b = tiles + stage * C::kStageBytes + kABytes;
+                uint8_t* b = tiles + stage * C::kStageBytes;
                 tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], C::kBBytes);
 #pragma unroll
                 for (uint32_t j = 0; j < 2u; ++j)
@@ -469,16 +481,15 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc5::fence_after_sync();
-                const uint32_t a_addr = tc5::smem_u32(tiles + stage * C::kStageBytes);
+                const uint32_t a_tmem = tmem_base + C::kACol0 + stage * C::kACols;
                 const uint32_t b_addr = C::BRAW ? tc5::smem_u32(ring + rs * C::kRawBytes + kRawStageBytes) + (hu & 3u) * C::kBBytes
-                                                : a_addr + kABytes;
+                                                : tc5::smem_u32(tiles + stage * C::kStageBytes);
 #pragma unroll
                 for (uint32_t j = 0; j < 2u; ++j) {
-                    const uint64_t a_desc = tc5::smem_desc_sw128(a_addr + j * kSlabBytes);
                     const uint64_t b_desc = tc5::smem_desc_sw128(b_addr + j * C::kBSlab);
 #pragma unroll
-                    for (uint32_t k = 0; k < 4u; ++k)  // 16 f16 = 32 bytes of K per instruction: +2 in 16-byte units
-                        mma_f16_elect(d_tmem, a_desc + 2u * k, b_desc + 2u * k, C::kIdesc, (hu | j | k) != 0u);
+                    for (uint32_t k = 0; k < 4u; ++k)  // 16 f16 of K per instruction: 8 columns of A, 32 bytes of B
+                        mma_f16_ts_elect(d_tmem, a_tmem + j * 32u + k * 8u, b_desc + 2u * k, C::kIdesc, (hu | j | k) != 0u);
                 }
                 tc5::mma_commit_elect(&sh->empty[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
