@@ -7,7 +7,7 @@
 // f16 weights
 //     w = (q - 8) * f16(d * sc) + f16(8 d sc - dmin m)          (two weights per instruction)
 // and store them from registers into tensor memory, where tcgen05.mma kind::f16 takes its A
-// operand (128 weight rows = 128 lanes, 128 K = 64 columns per stage, three stages).  The B operand is the activation
+// operand (128 weight rows = 128 lanes, 256 K = 128 columns per stage).  The B operand is the activation
 // tile: a small kernel in front scales each token by a power of two into the f16 range and
 // splits it into two f16 terms x = hi + lo (exact for bf16-valued activations, 22 bits
 // otherwise), stored as 2 * tokens rows of a library-resident f16 matrix that TMA boxes are
@@ -33,7 +33,7 @@ constexpr uint32_t BM = 128;          // weight rows per work item (MMA M)
 constexpr uint32_t kProdWarps = 8;    // dequantizing warps; warps 0..3 also drain the accumulator
 constexpr uint32_t kRawWarp = kProdWarps, kActWarp = kProdWarps + 1, kMmaWarp = kProdWarps + 2;
 constexpr uint32_t kThreads = (kProdWarps + 3) * 32;
-constexpr uint32_t kMaxStages = 3;    // operand stages: half a Q4_K super-block column (128 K) of 128 rows
+constexpr uint32_t kMaxStages = 3;    // operand stages: one Q4_K super-block column (256 K) of 128 rows
 // Packed weights wait in shared memory, not in registers: a ring of TMA boxes, each two
 // super-block columns of the tile - 2 x [128 rows][128 bytes] (128-byte swizzle, so that the
 // 8 rows of a quarter-warp read fall on distinct banks) and [128 rows][48 bytes] of scale
@@ -53,14 +53,14 @@ struct Cfg {
     static constexpr bool BRAW = NC <= 32u;
     static constexpr uint32_t kBSlab = NC * 128u;
     static constexpr uint32_t kBBytes = 2u * kBSlab;  // per half unit
-    static constexpr uint32_t kStages = 3u;                          // A operand stages in tensor memory
-    static constexpr uint32_t kStageBytes = BRAW ? 0u : kBBytes;     // shared-memory stage: the activation tile, if not in the ring
+    static constexpr uint32_t kStages = BRAW ? 3u : 2u;              // A operand stages in tensor memory: one super-block column each
+    static constexpr uint32_t kStageBytes = BRAW ? 0u : 2u * kBBytes;  // shared-memory stage: the activation tile, if not in the ring
     static constexpr uint32_t kRawBytes = kRawStageBytes + (BRAW ? 4u * kBBytes : 0u);
     static constexpr uint32_t kFullCount = kProdWarps + (BRAW ? 0u : 1u);
     static constexpr uint32_t kRawEmptyCount = kProdWarps + (BRAW ? 1u : 0u);
     static constexpr uint32_t kACol0 = 2u * NC;                      // after the two accumulators
-    static constexpr uint32_t kACols = 64u;                          // per stage: 128 K as f16 pairs
-    static constexpr uint32_t kTmemCols = NC <= 32u ? 256u : 512u;   // 2 NC + 3 * 64, rounded up to a power of two
+    static constexpr uint32_t kACols = 128u;                         // per stage: 256 K as f16 pairs
+    static constexpr uint32_t kTmemCols = 512u;                      // 2 NC + kStages * 128 <= 512
     static constexpr uint32_t kIdesc = tc5::idesc_f32acc(0u, 0u, BM, NC);
 };
 
@@ -316,45 +316,48 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     if (warp < kProdWarps) {
         // ------------------------------------------------------------ dequantizing producers
         // A thread owns one row of the tile - the tensor-memory lane its warp may write: warp w
-        // serves lanes 32 (w % 4).. - and, per half unit, 64 K of it (k-slab sl = w / 4): the two
-        // 16-byte chunks 2G, 2G+1 of the row's packed bytes, G = 2 * half + sl.  The f16 pairs go
-        // straight from registers into the A operand's tensor-memory columns: no shared-memory
-        // copy of the dequantized weights, nothing for the tensor core to fetch but the small
-        // activation tile.  The 8 lanes of a quarter-warp hold 8 consecutive rows: their 16-byte
-        // reads of the swizzled weight box fall on 8 different chunk positions.
-        const uint32_t qd = warp & 3u, sl = warp >> 2;
+        // serves lanes 32 (w % 4).. - and, per unit, half of its 256 K (hf = w / 4): the four
+        // 16-byte chunks 4 hf .. 4 hf + 3 of the row's packed bytes, i.e. k-slabs G = 2 hf, 2 hf + 1.
+        // The f16 pairs go straight from registers into the A operand's tensor-memory columns:
+        // no shared-memory copy of the dequantized weights, nothing for the tensor core to
+        // fetch but the small activation tile, and one barrier round per 128 weights of a row.
+        // The 8 lanes of a quarter-warp hold 8 consecutive rows: their 16-byte reads of the
+        // swizzled weight box fall on 8 different chunk positions.
+        const uint32_t qd = warp & 3u, hf = warp >> 2;
         const uint32_t r_in = qd * 32u + lane, swz = r_in & 7u;
         const uint32_t line_off = (r_in >> 3) * 1024u + swz * 128u;  // the row's 128-byte line in a weight box
-        const uint32_t halves_per_item = upi * 2u;
         const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
-        const uint32_t total = my_items * halves_per_item;
-        uint32_t stage = 0, phase = 0, rs = 0, rphase = 0, c_h = 0, c_item = blockIdx.x, iter = 0;
+        const uint32_t total = my_items * upi;
+        uint32_t stage = 0, phase = 0, rs = 0, rphase = 0, c_u = 0, c_item = blockIdx.x, iter = 0;
         bool ok = true;
         for (uint32_t n = 0; n < total && ok; ++n) {
-            const uint32_t sub = n & 3u, j = sub >> 1, half = sub & 1u;  // unit j of the box, half of the unit
-            if (sub == 0u) {
+            const uint32_t j = n & 1u;  // unit j of the box
+            if (j == 0u) {
                 ok = mbar_wait_park(&sh->raw_full[rs], rphase, ctx, tc5::kErrFullWait, 0x20u + rs);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
             const uint8_t* raw = ring + rs * C::kRawBytes;
-            const uint32_t G = half * 2u + sl;
-            const uint4 q0 = *reinterpret_cast<const uint4*>(raw + j * kRawData + line_off + (((2u * G) ^ swz) << 4));
-            const uint4 q1 = *reinterpret_cast<const uint4*>(raw + j * kRawData + line_off + (((2u * G + 1u) ^ swz) << 4));
+            uint4 q[4];
+#pragma unroll
+            for (uint32_t i = 0; i < 4u; ++i)
+                q[i] = *reinterpret_cast<const uint4*>(raw + j * kRawData + line_off + (((hf * 4u + i) ^ swz) << 4));
             const uint8_t* rec = raw + 2u * kRawData + r_in * 48u + j * 24u;
             const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);
-            const uint32_t sm = (uint32_t)*reinterpret_cast<const uint16_t*>(rec + 4u + 2u * G) |
-                                ((uint32_t)*reinterpret_cast<const uint16_t*>(rec + 12u + 2u * G) << 16);
+            const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(rec + 4u + 4u * hf);   // sc[4 hf .. 4 hf + 3]
+            const uint32_t m4 = *reinterpret_cast<const uint32_t*>(rec + 12u + 4u * hf);   // m[4 hf .. 4 hf + 3]
             ok = mbar_wait_park(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc5::fence_after_sync();  // the MMAs that read this stage's columns are complete
-            {
-                // columns of slab sl: block 2G elements 0..15 | 16..31 | block 2G+1 elements 0..15 | 16..31
+#pragma unroll
+            for (uint32_t g2 = 0; g2 < 2u; ++g2) {
+                // slab G = 2 hf + g2: block 2G elements 0..15 | 16..31 | block 2G+1 elements 0..15 | 16..31
+                const uint32_t sm = ((sc4 >> (16u * g2)) & 0xffffu) | (((m4 >> (16u * g2)) & 0xffffu) << 16);
                 uint32_t lo0[8], hi0[8], lo1[8], hi1[8];
-                dequant_regs(q0, dd, sm, lo0, hi0);
-                dequant_regs(q1, dd, sm, lo1, hi1);
-                const uint32_t ta = tmem_base + ((qd * 32u) << 16) + C::kACol0 + stage * C::kACols + sl * 32u;
+                dequant_regs(q[2u * g2], dd, sm, lo0, hi0);
+                dequant_regs(q[2u * g2 + 1u], dd, sm, lo1, hi1);
+                const uint32_t ta = tmem_base + ((qd * 32u) << 16) + C::kACol0 + stage * C::kACols + (2u * hf + g2) * 32u;
                 tmem_st_32x8(ta, lo0);
                 tmem_st_32x8(ta + 8u, lo1);
                 tmem_st_32x8(ta + 16u, hi0);
@@ -365,13 +368,13 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             __syncwarp();
             if (lane == 0) {
                 tc5::mbar_arrive(&sh->full[stage]);
-                if (sub == 3u) tc5::mbar_arrive(&sh->raw_empty[rs]);  // every lane has consumed its bytes of the box
+                if (j == 1u) tc5::mbar_arrive(&sh->raw_empty[rs]);  // every lane has consumed its bytes of the box
             }
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
-            if (sub == 3u && ++rs == kRawStages) { rs = 0; rphase ^= 1u; }
-            if (++c_h == halves_per_item) {
-                // ---- the item's last half unit is written: warps 0..3 drain its accumulator
-                c_h = 0;
+            if (j == 1u && ++rs == kRawStages) { rs = 0; rphase ^= 1u; }
+            if (++c_u == upi) {
+                // ---- the item's last unit is written: warps 0..3 drain its accumulator
+                c_u = 0;
                 if (warp < 4u) {
                     const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
                     if (iter == 0u) pdk_pdl_wait();  // tokscale and the zeroed y are the previous kernel's output
@@ -444,16 +447,15 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         pdk_pdl_wait();  // the f16 rows are the previous kernel's output
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const uint32_t u0 = (item % ksplit) * upi;
-            for (uint32_t hu = 0; hu < upi * 2u; ++hu) {
+            for (uint32_t u = 0; u < upi; ++u) {
                 ok = mbar_wait_park(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, 0x10u + stage);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 uint8_t* b = tiles + stage * C::kStageBytes;
-                tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], C::kBBytes);
+                tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], C::kStageBytes);
 #pragma unroll
-                for (uint32_t j = 0; j < 2u; ++j)
-                    tc5::tma_load_2d_elect(b + j * C::kBSlab, &tmap_x, &sh->full[stage],
-                                           (int32_t)(u0 * 256u + hu * 128u + j * 64u), 0);
+                for (uint32_t j = 0; j < 4u; ++j)
+                    tc5::tma_load_2d_elect(b + j * C::kBSlab, &tmap_x, &sh->full[stage], (int32_t)((u0 + u) * 256u + j * 64u), 0);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -471,8 +473,8 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             if (!ok) break;
             tc5::fence_after_sync();
             const uint32_t d_tmem = tmem_base + buf * NC;
-            for (uint32_t hu = 0; hu < upi * 2u; ++hu) {
-                if (C::BRAW && (hu & 3u) == 0u) {  // the activation tiles of this pair of units are in the weight box
+            for (uint32_t u = 0; u < upi; ++u) {
+                if (C::BRAW && (u & 1u) == 0u) {  // the activation tiles of this pair of units are in the weight box
                     ok = mbar_wait_park(&sh->raw_full[rs], rphase, ctx, tc5::kErrFullWait, 0x30u + rs);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
@@ -482,18 +484,18 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 if (!ok) break;
                 tc5::fence_after_sync();
                 const uint32_t a_tmem = tmem_base + C::kACol0 + stage * C::kACols;
-                const uint32_t b_addr = C::BRAW ? tc5::smem_u32(ring + rs * C::kRawBytes + kRawStageBytes) + (hu & 3u) * C::kBBytes
+                const uint32_t b_addr = C::BRAW ? tc5::smem_u32(ring + rs * C::kRawBytes + kRawStageBytes) + (u & 1u) * 2u * C::kBBytes
                                                 : tc5::smem_u32(tiles + stage * C::kStageBytes);
 #pragma unroll
-                for (uint32_t j = 0; j < 2u; ++j) {
+                for (uint32_t j = 0; j < 4u; ++j) {
                     const uint64_t b_desc = tc5::smem_desc_sw128(b_addr + j * C::kBSlab);
 #pragma unroll
                     for (uint32_t k = 0; k < 4u; ++k)  // 16 f16 of K per instruction: 8 columns of A, 32 bytes of B
-                        mma_f16_ts_elect(d_tmem, a_tmem + j * 32u + k * 8u, b_desc + 2u * k, C::kIdesc, (hu | j | k) != 0u);
+                        mma_f16_ts_elect(d_tmem, a_tmem + j * 32u + k * 8u, b_desc + 2u * k, C::kIdesc, (u | j | k) != 0u);
                 }
                 tc5::mma_commit_elect(&sh->empty[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
-                if (C::BRAW && (hu & 3u) == 3u) {  // the box's activation tiles have been read
+                if (C::BRAW && (u & 1u) == 1u) {  // the box's activation tiles have been read
                     tc5::mma_commit_elect(&sh->raw_empty[rs]);
                     if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
                 }
