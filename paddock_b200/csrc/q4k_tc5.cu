@@ -7,8 +7,8 @@
 // f16 weights
 //     w = (q - 8) * f16(d * sc) + f16(8 d sc - dmin m)          (two weights per instruction)
 // and store them from registers into tensor memory, where tcgen05.mma kind::f16 takes its A
-// operand (128 weight rows = 128 lanes, 256 K = 128 columns per stage).  The B operand is the activation
-// tile: a small kernel in front scales each token by a power of two into the f16 range and
+// operand (128 weight rows = 128 lanes, 256 K = 128 columns per stage): the dequantized weights
+// never exist in shared memory.  The B operand is the activation tile: a small kernel in front scales each token by a power of two into the f16 range and
 // splits it into two f16 terms x = hi + lo (exact for bf16-valued activations, 22 bits
 // otherwise), stored as 2 * tokens rows of a library-resident f16 matrix that TMA boxes are
 // cut from.  The accumulator [128 rows][hi columns | lo columns] stays in tensor memory over
@@ -22,7 +22,7 @@
 //
 // Precision class: f16-rounded block scales (relative 2^-12, independent per 32-weight block)
 // and one f16 rounding per weight; measured rel-L2 against the f64 product of the dequantized
-// operands is below 1e-4.
+// operands is 3e-4, the condition-relative error 3e-5.
 #include <cuda_fp16.h>
 
 #include "tc5.cuh"
