@@ -636,9 +636,15 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
     if (out_dim == 0 || batch == 0) return 0;
     if (batch > 64u) return cudaErrorInvalidValue;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
-    if (dtype != PDK_KQ_Q4K && batch == 1u && !force_plain() && pdk_aligned(data, 16)) {
-        const int rc = more_gemv_i8(data, scales, (const float*)x, (float*)y, in_dim, out_dim, dtype, (cudaStream_t)stream);
-        if (rc != -1) return rc;
+    if (dtype != PDK_KQ_Q4K && !force_plain() && pdk_aligned(data, 16)) {
+        // Q4_0 / Q5_K / Q6_K have no batch kernel on the tensor path yet: one decode GEMV per token
+        // (17-25 us each at config 2's shape, the later ones partly from L2) beats the plain f32
+        // kernel's 165 us per four tokens
+        int rc = 0;
+        for (uint32_t b = 0; b < batch && rc == 0; ++b)
+            rc = more_gemv_i8(data, scales, (const float*)x + (size_t)b * in_dim, (float*)y + (size_t)b * out_dim, in_dim,
+                              out_dim, dtype, (cudaStream_t)stream);
+        if (rc != -1) return rc;  // -1 can only come from the first call: the plan depends on the shape alone
     }
     if (dtype != PDK_KQ_Q4K)
         return pdk_kq_more_gemm(data, scales, (const float*)x, (float*)y, in_dim, out_dim, batch, dtype,
