@@ -142,7 +142,7 @@ __device__ __forceinline__ uint32_t h2_dup(float v) {
 // xh f16 [NC][K]: row t = hi term of token t, row NC/2 + t = lo term; tokscale f32 [NC/2] = the
 // power of two the token was divided by (0 for unused columns).  One CTA per token column; the
 // CTAs past the token columns zero y.
-constexpr uint32_t kActThreads = 1024, kZeroCtas = 32;
+constexpr uint32_t kActThreads = 1024, kZeroCtas = 32;  // kActThreads / 32 == 32: the partial maxima fit one warp
 __global__ void __launch_bounds__(kActThreads)
 q4k_act_f16_kernel(const float* __restrict__ x, const int8_t* __restrict__ xq, const float* __restrict__ xq_scale,
                    __half* __restrict__ xh, float* __restrict__ tokscale, float* __restrict__ y, uint32_t in_dim,
@@ -180,20 +180,26 @@ q4k_act_f16_kernel(const float* __restrict__ x, const int8_t* __restrict__ xq, c
         if (tid == 0) tokscale[tok] = 0.0f;
         return;
     }
+    // each thread keeps its (at most two) groups of 8 elements in registers across the block-wide maximum
+    constexpr uint32_t kGroups = kMaxK / (kActThreads * 8u);
+    float v[kGroups][8];
     float amax = 0.0f;
-    for (uint32_t k = tid * 8u; k < in_dim; k += kActThreads * 8u) {
-        float v[8];
-        load8(k, v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    for (uint32_t gi = 0; gi < kGroups; ++gi) {
+        const uint32_t k = (gi * kActThreads + tid) * 8u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[gi][i] = 0.0f;
+        if (k < in_dim) load8(k, v[gi]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[gi][i]));
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
     if ((tid & 31u) == 0u) wmax[tid >> 5] = amax;
     __syncthreads();
-    amax = wmax[0];
+    amax = wmax[tid & 31u];  // kActThreads / 32 = 32 partial maxima: one per lane
 #pragma unroll
-    for (uint32_t i = 1; i < kActThreads / 32u; ++i) amax = fmaxf(amax, wmax[i]);
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
     // amax < 2^ex  ->  x * 2^(14 - ex) stays below 2^14, inside the f16 range
     float mul = 0.0f, back = 0.0f;
     if (amax > 0.0f && amax < 3.0e38f) {
@@ -203,13 +209,14 @@ q4k_act_f16_kernel(const float* __restrict__ x, const int8_t* __restrict__ xq, c
         mul = ldexpf(1.0f, 14 - ex);
         back = ldexpf(1.0f, ex - 14);
     }
-    for (uint32_t k = tid * 8u; k < in_dim; k += kActThreads * 8u) {
-        float v[8];
-        load8(k, v);
+#pragma unroll
+    for (uint32_t gi = 0; gi < kGroups; ++gi) {
+        const uint32_t k = (gi * kActThreads + tid) * 8u;
+        if (k >= in_dim) break;
         uint32_t h[4], l[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float a = v[2 * i] * mul, b = v[2 * i + 1] * mul;
+            const float a = v[gi][2 * i] * mul, b = v[gi][2 * i + 1] * mul;
             const __half2 hh = __floats2half2_rn(a, b);
             const __half2 ll = __floats2half2_rn(a - __low2float(hh), b - __high2float(hh));
             h[i] = *reinterpret_cast<const uint32_t*>(&hh);
