@@ -75,6 +75,7 @@ enum PdkSlot {
     PDK_SLOT_bf16_to_f8row = 375,
     PDK_SLOT_f8row_gemm_tc5x = 855,
     PDK_SLOT_quantize_nvf4 = 119,
+    PDK_SLOT_add_rmsnorm_quant_nvf4_batch = 436,
     PDK_SLOT_nvf4_dequant = 393,
     PDK_SLOT_nvf4_gemv = 394,
     PDK_SLOT_nvf4_gemm_tc5w = 852,
@@ -185,6 +186,12 @@ unsigned int pdk_device_error(void);
  * q u8[n/2] + scale u8[n/16]; scale = RN_e4m3(amax/6), at least the smallest subnormal when
  * amax > 0; element = RN-even e2m1 of v/scale.  n % 32 == 0. */
 int pd_quantize_nvf4(const void* x, void* q, void* scale, uint32_t n, void* stream);
+/* Slot 436 (packs/cuda/src/quant/nvf4.cuh:545-571; caller gpu_model/nemotron MoE prologue): the
+ * producer in front of an NVFP4 GEMM.  x f32 [batch][n] += proj (null: no residual), written back;
+ * out f32 [batch][n] = x * inv * w with inv = 1 / sqrtf(mean(x^2) + eps); q u8 [batch][n/2] and
+ * scale e4m3 [batch][n/16] = pd_quantize_nvf4 of each row of out.  n % 32 == 0, n <= 51200. */
+int pd_add_rmsnorm_quant_nvf4_batch(void* x, const void* proj, const void* w, void* out, void* q, void* scale,
+                                    uint32_t n, float eps, uint32_t batch, void* stream);
 /* slot 393, packs/cuda/src/quant/nvf4.cuh:4365-4403: y f32[out][in] = (e2m1 * e4m3) * scale2. */
 int pd_nvf4_dequant(const void* data, const void* scale, float scale2, void* y, uint32_t in_dim,
                     uint32_t out_dim, void* stream);

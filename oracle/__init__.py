@@ -189,6 +189,21 @@ def quantize_nvf4(x, scale2=1.0):
     return q, s
 
 
+def add_rmsnorm(x, proj, w, eps):
+    """Residual add + RMSNorm of each row, the arithmetic of packs/cuda/src/quant/nvf4.cuh:455-543:
+    v = x + proj in f32; f32 squares accumulated in f64; inv = 1 / sqrtf((float)(sum / n) + eps);
+    out = (v * inv) * w in f32.  x, proj f32 [rows][n] (proj may be None), w f32 [n].
+    Returns (v, out)."""
+    x = np.asarray(x, np.float32)
+    v = x if proj is None else (x + np.asarray(proj, np.float32)).astype(np.float32)
+    n = v.shape[-1]
+    total = (v * v).astype(np.float32).astype(np.float64).sum(axis=-1)
+    mean = (total / float(n)).astype(np.float32) + np.float32(eps)
+    inv = (np.float32(1.0) / np.sqrt(mean.astype(np.float32))).astype(np.float32)
+    out = ((v * inv[..., None]).astype(np.float32) * np.asarray(w, np.float32)).astype(np.float32)
+    return v, out
+
+
 def quantize_mxfp4(w):
     w = _f32(w)
     out = np.empty(w.size // 32 * 17, np.uint8)

@@ -41,6 +41,7 @@ static void fill_table() {
     PDK_SET(bf16_to_f8row);
     PDK_SET(f8row_gemm_tc5x);
     PDK_SET(quantize_nvf4);
+    PDK_SET(add_rmsnorm_quant_nvf4_batch);
     PDK_SET(nvf4_dequant);
     PDK_SET(nvf4_gemv);
     PDK_SET(nvf4_gemm_tc5w);

@@ -71,6 +71,78 @@ __global__ void quantize_nvf4_kernel(const float* __restrict__ x, uint8_t* __res
     if ((lane & 1u) == 0u) scale[i >> 4] = (uint8_t)sb;
 }
 
+// Fused producer in front of an NVFP4 GEMM: residual add, RMSNorm and the NVFP4 quantizer in one
+// pass over the row.  One CTA per row; the summed row waits in shared memory between the
+// square-sum and the normalisation, so x and proj are read once.  Sum of squares: f32 products
+// accumulated in f64; inv = 1 / sqrtf((float)(sum / n) + eps); out = v * inv * w in that order
+// (packs/cuda/src/quant/nvf4.cuh:455-543); the quantizer is quantize_nvf4_kernel's, 8 elements
+// per thread, the lane pair closing each 16-element block.
+constexpr uint32_t kNormMaxThreads = 384;
+__global__ void __launch_bounds__(kNormMaxThreads)
+add_rmsnorm_quant_nvf4_kernel(float* __restrict__ x, const float* __restrict__ proj, const float* __restrict__ w,
+                              float* __restrict__ out, uint8_t* __restrict__ q, uint8_t* __restrict__ scale, uint32_t n,
+                              float eps) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ double wsum[kNormMaxThreads / 32u];
+    __shared__ float s_inv;
+    const uint32_t b = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, nth = blockDim.x;  // nth % 32 == 0
+    float* xb = x + (size_t)b * n;
+    const float* pb = proj ? proj + (size_t)b * n : nullptr;
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();
+    double acc = 0.0;
+    for (uint32_t i = tid; i < (n >> 2); i += nth) {
+        float4 v = reinterpret_cast<const float4*>(xb)[i];
+        if (pb) {
+            const float4 pv = reinterpret_cast<const float4*>(pb)[i];
+            v.x += pv.x; v.y += pv.y; v.z += pv.z; v.w += pv.w;
+            reinterpret_cast<float4*>(xb)[i] = v;
+        }
+        reinterpret_cast<float4*>(row)[i] = v;
+        acc += (double)(v.x * v.x) + (double)(v.y * v.y) + (double)(v.z * v.z) + (double)(v.w * v.w);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0u) wsum[tid >> 5] = acc;
+    __syncthreads();
+    if (tid == 0u) {
+        double total = 0.0;
+        for (uint32_t i = 0; i < (nth >> 5); ++i) total += wsum[i];
+        s_inv = 1.0f / sqrtf((float)(total / (double)n) + eps);
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    float* ob = out + (size_t)b * n;
+    uint8_t* qb = q + (size_t)b * (n >> 1);
+    uint8_t* sb = scale + (size_t)b * (n >> 4);
+    // n % 32 == 0 and an even thread count: a lane pair is never split across the loop bound
+    for (uint32_t j = tid; j < (n >> 3); j += nth) {
+        const uint32_t i = j << 3;
+        const float4 v0 = *reinterpret_cast<const float4*>(row + i), v1 = *reinterpret_cast<const float4*>(row + i + 4u);
+        const float4 w0 = *reinterpret_cast<const float4*>(w + i), w1 = *reinterpret_cast<const float4*>(w + i + 4u);
+        const float r[8] = {v0.x * inv * w0.x, v0.y * inv * w0.y, v0.z * inv * w0.z, v0.w * inv * w0.w,
+                            v1.x * inv * w1.x, v1.y * inv * w1.y, v1.z * inv * w1.z, v1.w * inv * w1.w};
+        *reinterpret_cast<float4*>(ob + i) = make_float4(r[0], r[1], r[2], r[3]);
+        *reinterpret_cast<float4*>(ob + i + 4u) = make_float4(r[4], r[5], r[6], r[7]);
+        float amax = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(r[k]));
+        amax = fmaxf(amax, __shfl_xor_sync(0x3u << (lane & 30u), amax, 1));
+        uint32_t sbyte = 0u;
+        float qinv = 0.0f;
+        if (amax > 0.0f) {
+            sbyte = (uint32_t)__nv_cvt_float_to_fp8(amax * (1.0f / 6.0f), __NV_SATFINITE, __NV_E4M3);
+            if (sbyte == 0u) sbyte = 1u;
+            qinv = 1.0f / e4m3_to_f32((uint8_t)sbyte);
+        }
+        uint32_t p = 0u;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) p |= e2m1_rn(r[k] * qinv) << (4 * k);
+        *reinterpret_cast<uint32_t*>(qb + (i >> 1)) = p;
+        if ((lane & 1u) == 0u) sb[i >> 4] = (uint8_t)sbyte;
+    }
+}
+
 // One CTA per output row; (e2m1 * e4m3) * scale2 with two separate roundings.
 __global__ void nvf4_dequant_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ scale, float scale2,
                                     float* __restrict__ y, uint32_t in_dim) {
@@ -155,6 +227,31 @@ PDK_EXPORT int pd_quantize_nvf4(const void* x, void* q, void* scale, uint32_t n,
     quantize_nvf4_kernel<<<(n / 8u + 255u) / 256u, 256, 0, (cudaStream_t)stream>>>((const float*)x, (uint8_t*)q,
                                                                                     (uint8_t*)scale, n);
     return pdk_launch_status();
+}
+
+// slot 436, packs/cuda/src/quant/nvf4.cuh:545-571: x f32 [batch][n] += proj (proj may be null),
+// out f32 [batch][n] = rmsnorm(x) * w, q / scale = pd_quantize_nvf4 of each row of out.
+PDK_EXPORT int pd_add_rmsnorm_quant_nvf4_batch(void* x, const void* proj, const void* w, void* out, void* q, void* scale,
+                                               uint32_t n, float eps, uint32_t batch, void* stream) {
+    if (n == 0 || batch == 0) return 0;
+    if ((n & 31u) != 0u || !pdk_aligned(x, 16) || !pdk_aligned(proj, 16) || !pdk_aligned(w, 16) || !pdk_aligned(out, 16) ||
+        !pdk_aligned(q, 4))
+        return cudaErrorInvalidValue;
+    const size_t smem = (size_t)n * sizeof(float);
+    if (smem > 200u * 1024u) return cudaErrorNotSupported;
+    if (smem > 48u * 1024u) {
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_quant_nvf4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    // a block width that walks the row's n/8 eight-element groups in whole rounds, if there is one
+    // between 192 and 384 threads (measured at 4096 rows of 5120: 320 threads 74 us, 512 104 us, 1024 140 us)
+    const uint32_t n8 = n >> 3;
+    uint32_t nth = 0;
+    for (uint32_t c = kNormMaxThreads; c >= 192u && nth == 0u; c -= 32u)
+        if (n8 % c == 0u) nth = c;
+    if (nth == 0u) nth = n8 < 256u ? (n8 + 31u) & ~31u : 256u;
+    return pdk_launch_pdl(add_rmsnorm_quant_nvf4_kernel, dim3(batch), dim3(nth), smem, (cudaStream_t)stream, (float*)x,
+                          (const float*)proj, (const float*)w, (float*)out, (uint8_t*)q, (uint8_t*)scale, n, eps);
 }
 
 // slot 393, packs/cuda/src/quant/nvf4.cuh:4365-4403

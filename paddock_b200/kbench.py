@@ -159,6 +159,21 @@ def bench_q4k_w4a8(ex, a):
     return sec, {"bound": "hbm", "bytes": nbytes, "us_chain": sec_chain * 1e6}
 
 
+def bench_norm_nvf4(ex, a):
+    """Slot 436, the fused residual-add + RMSNorm + NVFP4 quantizer in front of an NVFP4 GEMM:
+    --m rows of --k elements.  Table slot only, so --pack times another library."""
+    n, batch = a.k, a.m
+    x = synth.normal(batch * n, 11, 1.0, "cuda")
+    proj = synth.normal(batch * n, 12, 0.01, "cuda")
+    w = torch.ones(n, dtype=torch.float32, device="cuda")
+    out = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+    q = torch.zeros(batch * n // 2, dtype=torch.uint8, device="cuda")
+    s = torch.zeros(batch * n // 16, dtype=torch.uint8, device="cuda")
+    sec = time_launches(lambda i: ex.pack.call("add_rmsnorm_quant_nvf4_batch", x, proj, w, out, q, s, n, 1e-6, batch,
+                                               stream=torch.cuda.current_stream().cuda_stream), a.iters)
+    return sec, {"bound": "hbm", "bytes": batch * n * (4 + 4 + 4 + 4) + batch * n * 9 // 16 + n * 4}
+
+
 def bench_q8(ex, a):
     k, n = a.k, a.n
     raw = synth.quantize_q8_0(synth.normal(n * k, 3, 0.02, "cuda"))
@@ -447,8 +462,8 @@ def bench_moe_nvf4(ex, a):
     return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
 
 
-OPS = {"q4k_w4a8": bench_q4k_w4a8, "nvf4_gemv": bench_nvf4_gemv, "moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
-DEFAULTS = {"q4k_w4a8": (4, 25600, 5120), "nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+OPS = {"norm_nvf4": bench_norm_nvf4, "q4k_w4a8": bench_q4k_w4a8, "nvf4_gemv": bench_nvf4_gemv, "moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"norm_nvf4": (64, 0, 5120), "q4k_w4a8": (4, 25600, 5120), "nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
 def main():
@@ -469,7 +484,7 @@ def main():
     a.m, a.n, a.k = a.m or dm, a.n or dn, a.k or dk
     ep = a.op == "moe_ep"
     global GRAPH_REPLAY
-    GRAPH_REPLAY = a.graph and a.op in ("q4k_gemv", "q8_gemv", "nvf4_gemv")
+    GRAPH_REPLAY = a.graph and a.op in ("q4k_gemv", "q8_gemv", "nvf4_gemv", "norm_nvf4")
     if ep:
         import torch.distributed as dist
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))

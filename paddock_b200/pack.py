@@ -99,7 +99,7 @@ _SIGS = {
     "q8_0_gemv_repacked": "pppppuu", "q8_0_gemm_repacked": "pppppuuu",
     "quantize_e4m3_row": "pppuu", "bf16_to_f8row": "pppuu",
     "f8row_gemm": "pppppuuu", "f8row_gemm_tc5x": "pppppuuu",
-    "quantize_nvf4": "pppu", "nvf4_dequant": "ppfpuu", "nvf4_gemv": "pppppfuu",
+    "quantize_nvf4": "pppu", "add_rmsnorm_quant_nvf4_batch": "ppppppufu", "nvf4_dequant": "ppfpuu", "nvf4_gemv": "pppppfuu",
     "nvf4_tc5_tile_scales": "ppuu", "nvf4_gemm_tc5w": "ppppppfuuupU",
     "moe_topk_batch": "ppuuppu", "moe_align": "ppppuuuu", "moe_align_bm": "ppppuuuuu", "moe_slot_combine": "ppuuu",
     "kquant_dequant": "ppUu", "kquant_repack": "pppUu", "kquant_gemv": "ppppuuu",

@@ -110,3 +110,39 @@ def test_nvf4_gemm_w4a4(pack, m, n, k, out):
         assert rel_l2(y, ref) < 1e-4
     else:
         assert rel_l2(y, ref) < 2e-2   # bf16 rounding of acc + bias with |bias| >> |acc|
+
+
+@pytest.mark.parametrize("n,batch,residual", [(5120, 3, True), (2880 + 32, 1, True), (64, 5, False), (17408, 2, True)])
+def test_add_rmsnorm_quant_nvf4_batch(pack, n, batch, residual):
+    """Slot 436: the summed row is written back bit-exactly, the normed row matches the oracle's
+    arithmetic to an ulp of the scale, and the NVFP4 planes are exactly the quantizer's output on
+    the normed row the kernel wrote."""
+    x = oracle.fill_normal(batch * n, 4100 + n, 1.5).reshape(batch, n)
+    proj = oracle.fill_normal(batch * n, 4101 + n, 0.5).reshape(batch, n) if residual else None
+    w = (1.0 + 0.1 * oracle.fill_normal(n, 4102, 1.0)).astype(np.float32)
+    x[0, :16] = 0.0
+    if residual:
+        proj[0, :16] = 0.0                       # an all-zero 16-block: scale byte 0
+    eps = 1e-6
+    v_ref, out_ref = oracle.add_rmsnorm(x, proj, w, eps)
+    d_x = dev_f32(x.reshape(-1))
+    d_out = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+    d_q = torch.zeros(batch * n // 2, dtype=torch.uint8, device="cuda")
+    d_s = torch.zeros(batch * n // 16, dtype=torch.uint8, device="cuda")
+    pack.call("add_rmsnorm_quant_nvf4_batch", d_x, dev_f32(proj.reshape(-1)) if residual else None, dev_f32(w), d_out, d_q,
+              d_s, n, eps, batch)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_x.cpu().numpy().view(np.uint32), v_ref.reshape(-1).view(np.uint32))
+    out = d_out.cpu().numpy().reshape(batch, n)
+    assert np.allclose(out, out_ref, rtol=4e-7, atol=0)
+    for b in range(batch):
+        q_ref, s_ref = oracle.quantize_nvf4(out[b])
+        assert np.array_equal(d_q.cpu().numpy().reshape(batch, -1)[b], q_ref)
+        assert np.array_equal(d_s.cpu().numpy().reshape(batch, -1)[b], s_ref)
+    assert d_s.cpu().numpy()[0] == 0
+
+
+def test_add_rmsnorm_quant_nvf4_refuses_bad_shapes(pack):
+    buf = torch.zeros(4096, dtype=torch.float32, device="cuda")
+    assert pack.status("add_rmsnorm_quant_nvf4_batch", buf, None, buf, buf, buf, buf, 48, 1e-6, 1) == 1
+    assert pack.status("add_rmsnorm_quant_nvf4_batch", buf, None, buf, buf, buf, buf, 0, 1e-6, 1) == 0

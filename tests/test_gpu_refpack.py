@@ -301,3 +301,24 @@ def test_more_kquants_against_reference_pack(pack, ref, name, dtype, datab):
     ours, theirs = (o[0].view(np.float32) for o in run_both(pack, ref, "kquant_gemv", mkg, 1))
     # Q5_K and Q4_0 run the integer tensor-core GEMV (15-bit block-floating activations), as Q4_K does
     assert rel_l2(ours, theirs.astype(np.float64)) < 1e-4 < TOL
+
+
+def test_add_rmsnorm_quant_nvf4_against_reference_pack(pack, ref):
+    """Slot 436 on both packs: the summed rows are identical, the normed rows agree to an ulp of the
+    norm scale, and the scale bytes differ, if at all, only where that ulp crosses a rounding tie."""
+    n, batch, eps = 5120, 4, 1e-6
+    x = oracle.fill_normal(batch * n, 5200, 1.5)
+    proj = oracle.fill_normal(batch * n, 5201, 0.5)
+    w = (1.0 + 0.1 * oracle.fill_normal(n, 5202, 1.0)).astype(np.float32)
+
+    def mk():
+        dx = dev_f32(x)
+        out = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+        q = torch.zeros(batch * n // 2, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(batch * n // 16, dtype=torch.uint8, device="cuda")
+        return (dx, dev_f32(proj), dev_f32(w), out, q, s, n, eps, batch), [dx, out, s, q]
+    ours, theirs = run_both(pack, ref, "add_rmsnorm_quant_nvf4_batch", mk, 4)
+    assert np.array_equal(ours[0], theirs[0])
+    assert np.allclose(ours[1].view(np.float32), theirs[1].view(np.float32), rtol=4e-7, atol=0)
+    assert np.mean(ours[2] != theirs[2]) < 1e-3
+    assert np.mean(ours[3] != theirs[3]) < 1e-3

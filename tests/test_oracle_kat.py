@@ -278,3 +278,22 @@ def test_fill_normal_is_thread_count_independent_and_normal():
     b = oracle.fill_normal(100001, 5, 2.0)
     assert np.array_equal(a, b)
     assert abs(a.mean()) < 0.03 and abs(a.std() - 2.0) < 0.03
+
+
+def test_add_rmsnorm_hand_values():
+    """The fused producer's norm (packs/cuda/src/quant/nvf4.cuh:455-543) on values worked by hand:
+    a row of 32 with 3 and 4 in front has mean square 25/32; eps = 0."""
+    import numpy as np
+    x = np.zeros((1, 32), np.float32)
+    x[0, 0], x[0, 1] = 1.0, 4.0
+    proj = np.zeros((1, 32), np.float32)
+    proj[0, 0] = 2.0
+    w = np.full(32, 2.0, np.float32)
+    v, out = oracle.add_rmsnorm(x, proj, w, 0.0)
+    assert v[0, 0] == 3.0 and v[0, 1] == 4.0
+    inv = np.float32(1.0) / np.sqrt(np.float32(25.0 / 32.0))
+    assert out[0, 0] == np.float32(np.float32(3.0) * inv) * np.float32(2.0)
+    assert abs(float(out[0, 1]) - 8.0 / (25.0 / 32.0) ** 0.5) < 1e-6
+    assert not out[0, 2:].any()
+    v2, out2 = oracle.add_rmsnorm(x, None, w, 0.0)
+    assert v2[0, 0] == 1.0 and abs(float(out2[0, 1]) - 8.0 / (17.0 / 32.0) ** 0.5) < 1e-6
