@@ -44,6 +44,8 @@ int pdk_q4k_batch_i8(const void* data, const void* scales, const float* x, const
 // q4k_tc5.cu: 1..32 tokens on tcgen05 (f16 weights); same operands and return convention
 int pdk_q4k_tc5(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale, float* y,
                 uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
+int pdk_q4_0_tc5(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                 uint32_t batch, cudaStream_t st);
 
 namespace {
 
@@ -636,8 +638,23 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
     if (out_dim == 0 || batch == 0) return 0;
     if (batch > 64u) return cudaErrorInvalidValue;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
+    if (dtype == PDK_KQ_Q4_0 && batch >= 4u && !force_plain() && tc5_min_tokens() != 0u) {
+        // Q4_0 shares Q4_K's nibble planes: from four tokens on the tcgen05 kernel (32 us per 32 tokens at config 2's
+        // shape) beats one 17 us decode GEMV per token
+        uint32_t b = 0;
+        int rc = 0;
+        while (b < batch && rc == 0) {
+            const uint32_t take = batch - b < 32u ? batch - b : 32u;
+            rc = pdk_q4_0_tc5(data, scales, (const float*)x + (size_t)b * in_dim, (float*)y + (size_t)b * out_dim, in_dim,
+                              out_dim, take, (cudaStream_t)stream);
+            if (rc == 0) b += take;
+        }
+        if (rc > 0) return rc;
+        if (b == batch) return 0;
+        if (b != 0) return cudaErrorNotSupported;  // cannot happen: the plan depends on the shape alone
+    }
     if (dtype != PDK_KQ_Q4K && !force_plain() && pdk_aligned(data, 16)) {
-        // Q4_0 / Q5_K / Q6_K have no batch kernel on the tensor path yet: one decode GEMV per token
+        // Q5_K / Q6_K (and Q4_0 below four tokens) have no batch kernel on the tensor path yet: one decode GEMV per token
         // (17-25 us each at config 2's shape, the later ones partly from L2) beats the plain f32
         // kernel's 165 us per four tokens
         int rc = 0;

@@ -1,4 +1,4 @@
-// q4k_tc5.cu - Q4_K GEMM for 9..32 tokens per launch on the tcgen05 tensor cores (W4A16).
+// q4k_tc5.cu - Q4_K (and Q4_0) GEMM for 9..32 tokens per launch on the tcgen05 tensor cores (W4A16).
 //
 // With more than a handful of tokens the per-(block, token) integer fold of q4k_batch_i8.cu
 // outgrows the weight stream.  Here the CUDA cores touch each weight once, whatever the token
@@ -250,16 +250,39 @@ __device__ __forceinline__ void mma_f16_ts_elect(uint32_t d_tmem, uint32_t a_tme
                  : "memory");
 }
 
-// 32 weights of one row (16 low nibbles of block 2G, 16 high nibbles of block 2G+1) -> f16 pairs
-__device__ __forceinline__ void dequant_regs(const uint4& q, uint32_t dd, uint32_t sm, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+// The two f16x2 multipliers and offsets of a k-slab (blocks 2G, 2G+1): w = s * (q - 8) + o, the
+// high nibble arriving as 16 q.
+struct SlabScale {
+    uint32_t s_lo, s_hi, o_lo, o_hi;
+};
+// Q4_K: w = d sc q - dmin m = dsc (q - 8) + (8 dsc - dmin m); the centred nibble halves what the
+// scale's f16 rounding costs.  sm = sc[2G] | sc[2G+1] << 8 | m[2G] << 16 | m[2G+1] << 24.
+__device__ __forceinline__ SlabScale scale_q4k(uint32_t dd, uint32_t sm) {
     const __half2 dh = *reinterpret_cast<const __half2*>(&dd);
     const float d = __low2float(dh), dmin = __high2float(dh);
-    // w = dsc * (q - 8) + (8 dsc - dmin m): the centred nibble halves what the scale's f16 rounding costs
     const float dsc_lo = d * (float)(sm & 0xffu), dsc_hi = d * (float)((sm >> 8) & 0xffu);
-    const uint32_t s_lo = h2_dup(dsc_lo);
-    const uint32_t s_hi = h2_dup(dsc_hi * 0.0625f);  // the high nibble arrives as 16 q
-    const uint32_t o_lo = h2_dup(fmaf(8.0f, dsc_lo, -dmin * (float)((sm >> 16) & 0xffu)));
-    const uint32_t o_hi = h2_dup(fmaf(8.0f, dsc_hi, -dmin * (float)(sm >> 24)));
+    SlabScale r;
+    r.s_lo = h2_dup(dsc_lo);
+    r.s_hi = h2_dup(dsc_hi * 0.0625f);
+    r.o_lo = h2_dup(fmaf(8.0f, dsc_lo, -dmin * (float)((sm >> 16) & 0xffu)));
+    r.o_hi = h2_dup(fmaf(8.0f, dsc_hi, -dmin * (float)(sm >> 24)));
+    return r;
+}
+// Q4_0 (repacked into the Q4_K nibble convention, kquant_more.cu): w = d[block] (q - 8).
+// dpair = {f16 d[2G], f16 d[2G+1]}.
+__device__ __forceinline__ SlabScale scale_q4_0(uint32_t dpair) {
+    const __half2 dh = *reinterpret_cast<const __half2*>(&dpair);
+    SlabScale r;
+    r.s_lo = h2_dup(__low2float(dh));
+    r.s_hi = h2_dup(__high2float(dh) * 0.0625f);
+    r.o_lo = 0u;
+    r.o_hi = 0u;
+    return r;
+}
+
+// 32 weights of one row (16 low nibbles of block 2G, 16 high nibbles of block 2G+1) -> f16 pairs
+__device__ __forceinline__ void dequant_regs(const uint4& q, const SlabScale& sc, uint32_t (&lo)[8], uint32_t (&hi)[8]) {
+    const uint32_t s_lo = sc.s_lo, s_hi = sc.s_hi, o_lo = sc.o_lo, o_hi = sc.o_hi;
     const uint32_t magic = 0x64086408u;     // f16 1032 twice: (0x6400 | q) - 1032 = q - 8
     const uint32_t magic_hi = 0x64806480u;  // f16 1152 twice: (0x6400 | q << 4) - 1152 = 16 (q - 8)
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
@@ -274,7 +297,7 @@ __device__ __forceinline__ void dequant_regs(const uint4& q, uint32_t dd, uint32
     }
 }
 
-template <uint32_t NC>
+template <uint32_t NC, bool Q40>
 __global__ void __launch_bounds__(kThreads, 1)
 q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                const __grid_constant__ CUtensorMap tmap_r, const float* __restrict__ tokscale, float* __restrict__ y,
@@ -350,9 +373,10 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             for (uint32_t i = 0; i < 4u; ++i)
                 q[i] = *reinterpret_cast<const uint4*>(raw + j * kRawData + line_off + (((hf * 4u + i) ^ swz) << 4));
             const uint8_t* rec = raw + 2u * kRawData + r_in * 48u + j * 24u;
-            const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);
-            const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(rec + 4u + 4u * hf);   // sc[4 hf .. 4 hf + 3]
-            const uint32_t m4 = *reinterpret_cast<const uint32_t*>(rec + 12u + 4u * hf);   // m[4 hf .. 4 hf + 3]
+            // Q4_K record {f16 d, f16 dmin, sc[8], m[8], pad}: sc / m[4 hf .. 4 hf + 3]; Q4_0 record {f16 d[8], pad}: d[4 hf .. 4 hf + 3]
+            const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec + (Q40 ? 8u * hf : 0u));
+            const uint32_t sc4 = *reinterpret_cast<const uint32_t*>(rec + 4u + (Q40 ? 8u : 4u) * hf);
+            const uint32_t m4 = Q40 ? 0u : *reinterpret_cast<const uint32_t*>(rec + 12u + 4u * hf);
             ok = mbar_wait_park(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -360,10 +384,11 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
 #pragma unroll
             for (uint32_t g2 = 0; g2 < 2u; ++g2) {
                 // slab G = 2 hf + g2: block 2G elements 0..15 | 16..31 | block 2G+1 elements 0..15 | 16..31
-                const uint32_t sm = ((sc4 >> (16u * g2)) & 0xffffu) | (((m4 >> (16u * g2)) & 0xffffu) << 16);
+                const SlabScale ss = Q40 ? scale_q4_0(g2 == 0u ? dd : sc4)
+                                         : scale_q4k(dd, ((sc4 >> (16u * g2)) & 0xffffu) | (((m4 >> (16u * g2)) & 0xffffu) << 16));
                 uint32_t lo0[8], hi0[8], lo1[8], hi1[8];
-                dequant_regs(q[2u * g2], dd, sm, lo0, hi0);
-                dequant_regs(q[2u * g2 + 1u], dd, sm, lo1, hi1);
+                dequant_regs(q[2u * g2], ss, lo0, hi0);
+                dequant_regs(q[2u * g2 + 1u], ss, lo1, hi1);
                 const uint32_t ta = tmem_base + ((qd * 32u) << 16) + C::kACol0 + stage * C::kACols + (2u * hf + g2) * 32u;
                 tmem_st_32x8(ta, lo0);
                 tmem_st_32x8(ta + 8u, lo1);
@@ -541,7 +566,7 @@ uint8_t* xh_slice(cudaStream_t st) {
     return base + (size_t)(n_owner++) * kSliceBytes;
 }
 
-template <uint32_t NC>
+template <uint32_t NC, bool Q40>
 int launch(const void* data, const void* recs, const float* x, const int8_t* xq, const float* xq_scale, float* y,
            uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
     using C = Cfg<NC>;
@@ -562,7 +587,7 @@ int launch(const void* data, const void* recs, const float* x, const int8_t* xq,
                                         (uint64_t)n_unit * 24u, 48u, BM))
         return rc;
     const size_t smem = (size_t)kRawStages * C::kRawBytes + (size_t)C::kStages * C::kStageBytes + sizeof(Shared) + 1024u;
-    auto kern = q4k_tc5_kernel<NC>;
+    auto kern = q4k_tc5_kernel<NC, Q40>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     if (int rc = pdk_launch_pdl(q4k_act_f16_kernel, dim3(NC / 2u + kZeroCtas), dim3(kActThreads), 0, st, x, xq, xq_scale, xh,
@@ -588,6 +613,14 @@ int launch(const void* data, const void* recs, const float* x, const int8_t* xq,
 int pdk_q4k_tc5(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale, float* y,
                 uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
     if (batch == 0u || batch > 32u) return -1;
-    if (batch <= 16u) return launch<32>(data, scales, x, xq, xq_scale, y, in_dim, out_dim, batch, st);
-    return launch<64>(data, scales, x, xq, xq_scale, y, in_dim, out_dim, batch, st);
+    if (batch <= 16u) return launch<32, false>(data, scales, x, xq, xq_scale, y, in_dim, out_dim, batch, st);
+    return launch<64, false>(data, scales, x, xq, xq_scale, y, in_dim, out_dim, batch, st);
+}
+
+// The same for a repacked Q4_0 plane (f32 activations).
+int pdk_q4_0_tc5(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                 uint32_t batch, cudaStream_t st) {
+    if (batch == 0u || batch > 32u) return -1;
+    if (batch <= 16u) return launch<32, true>(data, scales, x, nullptr, nullptr, y, in_dim, out_dim, batch, st);
+    return launch<64, true>(data, scales, x, nullptr, nullptr, y, in_dim, out_dim, batch, st);
 }

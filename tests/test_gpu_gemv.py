@@ -260,7 +260,7 @@ def test_more_kquants_dequant_repack_gemv(pack, name, k, n):
     d_data = torch.zeros(ns * datab, dtype=torch.uint8, device="cuda")
     d_sc = torch.zeros(ns * 24, dtype=torch.uint8, device="cuda")
     pack.call("kquant_repack", dev(raw), d_data, d_sc, ns, dtype)
-    for batch in (1, 5):
+    for batch in (1, 5, 20):
         x = bf16_activations(batch * k, seed_for(2, 7 + batch))
         d_out = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
         if batch == 1:
@@ -269,7 +269,9 @@ def test_more_kquants_dequant_repack_gemv(pack, name, k, n):
             pack.call("pdk_kquant_gemm_f32", d_data, d_sc, dev_f32(x), d_out, k, n, batch, dtype)
         torch.cuda.synchronize()
         ref, ab = oracle.matmul_f64(want, x, k, n, batch, with_abs=True)
-        assert cond_err(d_out.cpu().numpy().reshape(batch, n), ref, ab) < 1e-5 < TOL
+        # Q4_0 from four tokens on (and K a multiple of 512) runs the f16-weight tcgen05 kernel
+        tol = 1e-4 if (name == "q4_0" and batch >= 4 and k % 512 == 0) else 1e-5
+        assert cond_err(d_out.cpu().numpy().reshape(batch, n), ref, ab) < tol < TOL
 
 
 def test_q4k_gemv_shard_stores_band_into_every_output(pack):
