@@ -114,7 +114,7 @@ struct Q4K {
 // Q5_K repacked (kquant_more.cu): 128 bytes of low nibbles in the Q4_K convention, then 32 bytes
 // of high bits (bit j of byte l = bit 4 of element l of block j); the record is Q4_K's.
 struct Q5K {
-    static constexpr uint32_t kDepth = 3;
+    static constexpr uint32_t kDepth = 2;
     static constexpr uint32_t kDataBytes = 160;
     static constexpr uint32_t kRecBytes = 24;
     struct Stage {
