@@ -178,10 +178,14 @@ def bench_q8(ex, a):
     k, n = a.k, a.n
     raw = synth.quantize_q8_0(synth.normal(n * k, 3, 0.02, "cuda"))
     planes = [ex.repack_q8_blocks(raw, k, n) for _ in range(clones_for(n * k // 32 * 34))]
-    x = synth.bf16_round(synth.normal(k, 4, 1.0, "cuda"))
-    y = torch.zeros(n, dtype=torch.float32, device="cuda")
-    sec = time_launches(lambda i: ex.q8_0_gemv_repacked(planes[i % len(planes)], None, x, y), a.iters)
-    return sec, {"bound": "hbm", "bytes": n * k // 32 * 34 + k * 2 + n * 4}
+    m = a.m
+    x = synth.bf16_round(synth.normal(m * k, 4, 1.0, "cuda"))
+    y = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+    if m == 1:
+        sec = time_launches(lambda i: ex.q8_0_gemv_repacked(planes[i % len(planes)], None, x, y), a.iters)
+    else:
+        sec = time_launches(lambda i: ex.q8_0_gemm_repacked(planes[i % len(planes)], None, x, y, m), a.iters)
+    return sec, {"bound": "hbm", "bytes": n * k // 32 * 34 + m * k * 2 + m * n * 4}
 
 
 def bench_f8(ex, a):
