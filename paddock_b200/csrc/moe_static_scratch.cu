@@ -67,7 +67,9 @@ PDK_EXPORT int pdk_mxfp4_moe_down_combine_static(const void* down_data, const vo
                                                  uint32_t rows, uint32_t bm, uint32_t max_blocks, void* stream) {
     t_refusal[0] = 0;
     if (rows == 0 || embd == 0 || n_active == 0 || max_blocks == 0) return 0;
-    const uint64_t need = (uint64_t)rows * n_active * embd;
+    // three 32-bit factors can pass 2^64: compare stepwise, so a wrapped product never slips through
+    const uint64_t pairs = (uint64_t)rows * n_active;
+    const uint64_t need = pairs <= kStaticPartFloats ? pairs * embd : ~0ull;
     if (need > kStaticPartFloats) {
         snprintf(t_refusal, sizeof(t_refusal),
                  "rows*n_active*embd = %llu floats exceeds the static partial buffer of %llu floats",

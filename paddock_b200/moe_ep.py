@@ -91,14 +91,19 @@ def ep_moe_block(x, idx, w, n_expert, expert_fn, group=None):
 PAD_EXPERT = -1  # local expert index of an unused slot of the fixed-capacity exchange
 
 
-def ep_moe_block_fixed(x, idx, w, n_expert, expert_fn, capacity=None, group=None):
+def ep_moe_block_fixed(x, idx, w, n_expert, expert_fn, capacity=None, group=None, dropped=None):
     """ep_moe_block without the host round trip: every rank sends every peer `capacity` row slots
     (default: all of its tokens*k pairs, which can never overflow), unused slots marked with
     PAD_EXPERT, so the split sizes are known without exchanging counts and nothing synchronizes
     the host.  One all-to-all each way: a slot is the token row as bf16 followed by 8 bytes
     (local expert i32, routing weight f32).  expert_fn must ignore rows whose expert is
     PAD_EXPERT (the kernels' alignment step drops indices outside [0, n_expert)); what it
-    returns for them is never read."""
+    returns for them is never read.
+
+    A capacity below tokens*k can overflow when routing is skewed: pairs beyond a destination's
+    `capacity` slots (in token order) are dropped - they are not sent, contribute zero to their
+    token, and are counted into `dropped` (a one-element int64 device tensor the caller reads
+    whenever it likes; nothing here waits for it).  Every rank must pass the same capacity."""
     world = dist.get_world_size(group)
     if n_expert % world:
         raise ValueError(f"{n_expert} experts do not split over {world} ranks")
@@ -106,10 +111,14 @@ def ep_moe_block_fixed(x, idx, w, n_expert, expert_fn, capacity=None, group=None
     tokens, k = idx.shape
     embd = x.shape[1]
     pairs = tokens * k
-    cap = pairs if capacity is None else capacity
+    cap = pairs if capacity is None else int(capacity)
+    if cap < 0:
+        raise ValueError("capacity must not be negative")
     dev = x.device
     row_bytes = embd * 2 + 8
-    send = torch.zeros((world * cap, row_bytes), dtype=torch.uint8, device=dev)
+    n_slots = world * cap
+    # one more row than is sent: the dump slot overflowing pairs are parked in
+    send = torch.zeros((n_slots + 1, row_bytes), dtype=torch.uint8, device=dev)
     send[:, embd * 2:embd * 2 + 4] = 0xFF                      # expert = -1 everywhere
     if pairs:
         flat_idx, flat_w = idx.reshape(-1), w.reshape(-1)
@@ -119,22 +128,27 @@ def ep_moe_block_fixed(x, idx, w, n_expert, expert_fn, capacity=None, group=None
         counts = (dest.unsqueeze(1) == torch.arange(world, device=dev).unsqueeze(0)).sum(0)
         starts = torch.cumsum(counts, 0) - counts
         dest_sorted = dest.index_select(0, order)
-        slot = dest_sorted * cap + (torch.arange(pairs, device=dev) - starts.index_select(0, dest_sorted))
+        rank_in_dest = torch.arange(pairs, device=dev) - starts.index_select(0, dest_sorted)
+        overflow = rank_in_dest >= cap
+        slot = torch.where(overflow, torch.full_like(rank_in_dest, n_slots), dest_sorted * cap + rank_in_dest)
+        if dropped is not None:
+            dropped += overflow.sum()
         token_of_pair = torch.div(order, k, rounding_mode="floor")
         rows = torch.empty((pairs, row_bytes), dtype=torch.uint8, device=dev)
         rows[:, :embd * 2] = x.index_select(0, token_of_pair).to(torch.bfloat16).view(torch.uint8).view(pairs, embd * 2)
         local_e = (flat_idx.index_select(0, order) - dest_sorted * epr).to(torch.int32)
         rows[:, embd * 2:embd * 2 + 4] = local_e.view(torch.uint8).view(pairs, 4)
         rows[:, embd * 2 + 4:] = flat_w.index_select(0, order).contiguous().view(torch.uint8).view(pairs, 4)
-        send.index_copy_(0, slot, rows)
+        send.index_copy_(0, slot, rows)                         # several dropped pairs may land on the dump row
+    send = send[:n_slots]
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
-    rx = recv[:, :embd * 2].contiguous().view(torch.bfloat16).view(world * cap, embd).to(torch.float32)
+    rx = recv[:, :embd * 2].contiguous().view(torch.bfloat16).view(n_slots, embd).to(torch.float32)
     re = recv[:, embd * 2:embd * 2 + 4].contiguous().view(torch.int32).view(-1).to(torch.int64)
     rw = recv[:, embd * 2 + 4:].contiguous().view(torch.float32).view(-1)
     part = expert_fn(rx, re, rw)
-    back = torch.empty((world * cap, embd), dtype=torch.float32, device=dev)
-    dist.all_to_all_single(back, part.contiguous(), group=group)
+    back = torch.zeros((n_slots + 1, embd), dtype=torch.float32, device=dev)   # row n_slots stays zero: dropped pairs
+    dist.all_to_all_single(back[:n_slots], part.contiguous(), group=group)
     slots = torch.zeros((pairs, embd), dtype=torch.float32, device=dev)
     if pairs:
         slots.index_copy_(0, order, back.index_select(0, slot))

@@ -94,3 +94,54 @@ def test_single_token_lives_on_rank_0(tmp_path):
 def test_expert_owner():
     idx = torch.tensor([0, 15, 16, 127])
     assert moe_ep.expert_owner(idx, 16).tolist() == [0, 0, 1, 7]
+
+
+def skew_worker(rank, world, port, out_path):
+    """Every token routes both of its choices to rank 1's experts, and the capacity is smaller
+    than what one rank sends there: the pairs beyond it must be dropped (zero contribution,
+    counted), the others must come back exact, and nothing may spill into another rank's slots."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    tokens, cap = 6, 5                                    # 12 pairs per rank, all bound for rank 1; 5 slots
+    epr = N_EXPERT // world
+    x = torch.from_numpy(oracle.bf16_round(oracle.fill_normal(tokens * EMBD, 40 + rank, 1.0)).reshape(tokens, EMBD))
+    idx = torch.tensor([[epr + (t % epr), epr + ((t + 1) % epr)] for t in range(tokens)], dtype=torch.int64)
+    w = torch.full((tokens, K), 0.5)
+
+    def expert_fn(rows, local_expert, weight):            # "expert e" scales its rows by (e + 2) * weight
+        live = local_expert >= 0
+        assert not live.any() or rank == 1                # rank 0 owns none of the chosen experts
+        y = torch.zeros(rows.shape[0], EMBD)
+        y[live] = rows[live] * ((local_expert[live] + 2).float() * weight[live]).unsqueeze(1)
+        return y
+    dropped = torch.zeros(1, dtype=torch.int64)
+    slots = moe_ep.ep_moe_block_fixed(x, idx, w, N_EXPERT, expert_fn, cap, dropped=dropped)
+    want = torch.zeros(tokens, K, EMBD)
+    for p in range(cap):                                  # the first `cap` pairs in token order survive
+        t, s = divmod(p, K)
+        want[t, s] = x[t] * ((idx[t, s] - epr + 2).float() * 0.5)
+    ok = torch.equal(slots, want) and int(dropped) == tokens * K - cap
+    gathered = [None] * world
+    dist.all_gather_object(gathered, ok)
+    if rank == 0:
+        np.save(out_path, np.array(gathered))
+    dist.destroy_process_group()
+
+
+def test_fixed_capacity_overflow_is_dropped_and_counted(tmp_path):
+    out = str(tmp_path / "skew.npy")
+    mp.spawn(skew_worker, args=(2, free_port(), out), nprocs=2, join=True)
+    assert np.load(out).all()
+
+
+def test_fixed_capacity_rejects_negative():
+    import pytest
+    with pytest.raises(ValueError):
+        # world size is read first: a single-process group is enough to reach the check
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()))
+        dist.init_process_group("gloo", rank=0, world_size=1)
+        try:
+            moe_ep.ep_moe_block_fixed(torch.zeros(1, EMBD), torch.zeros(1, K, dtype=torch.int64), torch.zeros(1, K),
+                                      N_EXPERT, lambda r, e, w: r, capacity=-1)
+        finally:
+            dist.destroy_process_group()

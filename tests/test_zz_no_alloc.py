@@ -69,4 +69,10 @@ def test_static_scratch_refuses_oversize(pack):
                      2880, 4096, 4, rows, 8, 4)
     assert st == 1                          # cudaErrorInvalidValue, nothing launched
     assert b"exceeds the static partial buffer" in lib.pdk_static_last_refusal()
+    # three factors whose product wraps past 2^64 (to 2^32 - 1 ... and below the capacity for some
+    # triples) must be refused like any other oversize request
+    for rows, k, embd in ((0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF), (0x80000000, 0x80000000, 4), (1 << 16, 1 << 16, 1 << 16)):
+        st = pack.status("pdk_mxfp4_moe_down_combine_static", buf, buf, None, buf, buf, buf, buf, buf, buf, buf,
+                         2880, embd, k, rows, 8, 4)
+        assert st == 1
     torch.cuda.synchronize()
