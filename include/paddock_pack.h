@@ -262,6 +262,14 @@ int pdk_mxfp4_moe_down(const void* down_data, const void* down_scale, const void
                        const void* hscale, void* part, uint32_t ff, uint32_t embd, uint32_t n_active, uint32_t bm,
                        uint32_t max_blocks, void* stream);
 
+/* No counterpart in the reference.  A few launchers (the small-batch k-quant GEMMs, the NVFP4
+ * W4A16 GEMV, the prefill-width NVFP4 GEMM) keep per-call scratch in the library, one slice per
+ * (device, stream) for the first two streams of a device that make such calls; further streams
+ * take the launchers' scratch-free routes.  Before destroying a stream that made such calls,
+ * with the stream idle and its device current, call this so that a later stream can take its
+ * slices over.  Thread-safe. */
+void pdk_stream_release(void* stream);
+
 /* No counterpart in the reference (whose mbarrier waits spin without a bound).  Self-test of the
  * bounded wait under every tcgen05 kernel of this pack: one warp waits on a barrier that nothing
  * arrives on; returns 0 when the wait gave up after about budget_us microseconds (1..100000)

@@ -3,10 +3,10 @@ reference's examples/*_kbench.rs): CUDA-event timing after warm-up, cold L2 for
 the memory-bound operators (operand clones rotated so consecutive launches
 never touch the same bytes), one JSON line per case.
 
-    python -m paddock_b200.kbench --op f8row_gemm --m 4096 --n 17408 --k 5120
-    python -m paddock_b200.kbench --op q4k_gemv --m 1
-    python -m paddock_b200.kbench --op q8_gemv
-    python -m paddock_b200.kbench --op f8row_gemm --out f32 --pack /path/to/another-pack.so
+    python kbench.py --op f8row_gemm --m 4096 --n 17408 --k 5120
+    python kbench.py --op q4k_gemv --m 1
+    python kbench.py --op q8_gemv
+    python kbench.py --op f8row_gemm --out f32 --pack /path/to/another-pack.so
 
 --pack times any library that exports the kernel-pack ABI (table slots only, so
 --out f32 for the GEMMs); the default is this package's own library.
@@ -17,14 +17,14 @@ import os
 
 import torch
 
-from . import synth
-from .planes import GpuExecutor
+from paddock_b200 import synth
+from paddock_b200.planes import GpuExecutor
 
 L2_BYTES = 126 << 20
 
 
 def peaks():
-    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    p = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     try:
         with open(p) as f:
             d = json.load(f)
@@ -94,7 +94,7 @@ def bench_q4k(ex, a):
         ty, nbytes, elems = KQ_MORE[a.dtype]
         raw = raw_kquant_blocks(a.dtype, n * k)
         data_b = {"q5_k": 160, "q6_k": 192, "q4_0": 128}[a.dtype]
-        from .planes import RepackedKQ
+        from paddock_b200.planes import RepackedKQ
         planes = []
         for _ in range(clones_for(n * k // 256 * (data_b + 24))):
             data = torch.empty(n * k // 256 * data_b, dtype=torch.uint8, device="cuda")
@@ -234,7 +234,7 @@ def bench_moe_other_pack(ex, a):
     (slot 155), then per call top-k, align (32-row blocks), quantize_q8 (18), gate_up_mmq (88),
     down_mmq (89), slot_combine."""
     import ctypes as C
-    from . import planes as P
+    from paddock_b200 import planes as P
     pk = ex.pack
     n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
     st = torch.cuda.current_stream().cuda_stream
@@ -299,8 +299,8 @@ def bench_moe_other_pack(ex, a):
 
 
 def bench_moe(ex, a):
-    """BASELINE config 5: 128 experts, top-4, hidden = ff = 2880, T = --m tokens."""
-    from . import planes as P
+    """MXFP4 MoE block: 128 experts, top-4, hidden = ff = 2880 by default, T = --m tokens."""
+    from paddock_b200 import planes as P
     if a.pack:
         return bench_moe_other_pack(ex, a)
     n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
@@ -346,7 +346,7 @@ def bench_moe(ex, a):
 def bench_moe_ep(ex, a):
     """Config 5 expert-parallel: run under torchrun, one rank per GPU; experts and tokens split over the ranks."""
     import torch.distributed as dist
-    from . import moe_ep, planes as P
+    from paddock_b200 import moe_ep, planes as P
     world, rank = dist.get_world_size(), dist.get_rank()
     n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
     epr = n_expert // world
@@ -433,7 +433,7 @@ def bench_nvf4_gemv(ex, a):
 
 def bench_moe_nvf4(ex, a):
     """The config 5 geometry with NVFP4 expert planes (per-16 UE4M3 scales, scale2 per expert), plain SwiGLU."""
-    from . import planes as P
+    from paddock_b200 import planes as P
     n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
     bm = 8 if T * k <= 1024 else 32
 
@@ -494,7 +494,7 @@ def main():
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     if a.pack:
-        from .pack import KernelPack
+        from paddock_b200.pack import KernelPack
         ex = GpuExecutor(KernelPack.load(a.pack))
     else:
         ex = GpuExecutor()

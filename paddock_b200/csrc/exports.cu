@@ -16,6 +16,52 @@ int pdk_sm_count() {
     return cached[dev];
 }
 
+// ---- per-(device, stream) scratch slices (pdk_common.cuh)
+#include <mutex>
+namespace {
+std::mutex g_slice_mu;
+PdkSliceTable* g_slice_tables = nullptr;
+}  // namespace
+
+PdkSliceTable::PdkSliceTable(void* (*r)(), size_t bytes, int n)
+    : resolve(r), slice_bytes(bytes), lanes(n < kMaxLanes ? n : kMaxLanes), base{}, owner{}, used{}, next(nullptr) {
+    std::lock_guard<std::mutex> lock(g_slice_mu);
+    next = g_slice_tables;
+    g_slice_tables = this;
+}
+
+uint8_t* PdkSliceTable::slice(cudaStream_t st) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+    std::lock_guard<std::mutex> lock(g_slice_mu);
+    if (base[dev] == nullptr) {
+        base[dev] = (uint8_t*)resolve();
+        if (base[dev] == nullptr) return nullptr;
+    }
+    int free_lane = -1;
+    for (int i = 0; i < lanes; ++i) {
+        if (used[dev][i] && owner[dev][i] == st) return base[dev] + (size_t)i * slice_bytes;
+        if (!used[dev][i] && free_lane < 0) free_lane = i;
+    }
+    if (free_lane < 0) return nullptr;
+    used[dev][free_lane] = true;
+    owner[dev][free_lane] = st;
+    return base[dev] + (size_t)free_lane * slice_bytes;
+}
+
+// No counterpart in the reference.  The small-batch k-quant GEMMs, the NVFP4 W4A16 GEMV and the
+// prefill-width NVFP4 GEMM keep per-call scratch in the library, one slice per (device, stream),
+// two streams per device.  A caller that destroys a stream calls this first (current device =
+// the stream's) so that a later stream can take the slices over; the stream must be idle.
+PDK_EXPORT void pdk_stream_release(void* stream) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PdkSliceTable::kMaxDev) return;
+    std::lock_guard<std::mutex> lock(g_slice_mu);
+    for (PdkSliceTable* t = g_slice_tables; t != nullptr; t = t->next)
+        for (int i = 0; i < t->lanes; ++i)
+            if (t->used[dev][i] && t->owner[dev][i] == (cudaStream_t)stream) t->used[dev][i] = false;
+}
+
 static const PdkPackInfo g_info = {
     PDK_PACK_MAGIC, PDK_PACK_ABI_VERSION, {'c', 'u', 'd', 'a', '-', 's', 'm', '1', '0', '0', 'a', 0, 0, 0, 0, 0},
     {0u, 1u, 0u}};

@@ -30,7 +30,7 @@
 // read one contiguous 128-byte (Q4_K) or 256-byte (Q8_0) run.
 #include <cstdlib>
 
-#include "pdk_common.cuh"
+#include "gemv_i8_traits.cuh"
 
 namespace {
 
@@ -41,224 +41,14 @@ constexpr uint32_t kThreads = kSlots * kSlices * 32;
 // CTAs could move into half-SMs as they free up) measured 4 % slower back to back: 18.2 vs 17.4 us.
 constexpr uint32_t kCtasPerSm = 1;
 
-__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                       uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 __device__ __forceinline__ void bar_sync(uint32_t id, uint32_t count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-// ---------------------------------------------------------------------------
-// Format traits.  A "unit" is 256 weights of one row (a Q4_K super-block, or
-// eight Q8_0 blocks).  Lane t owns blocks 2t and 2t+1 of the unit.
-// ---------------------------------------------------------------------------
-struct Q4K {
-    static constexpr uint32_t kDepth = 3;
-    static constexpr uint32_t kDataBytes = 128;  // per row per unit
-    static constexpr uint32_t kRecBytes = 24;
-    struct Stage {
-        uint4 q[4];      // row g: bytes 0..15 / 16..31 of ggml group t; row g+8 likewise
-        uint32_t dd[2];  // {f16 d, f16 dmin} of the two rows
-        uint32_t sm[2];  // sc[2t] | sc[2t+1]<<8 | m[2t]<<16 | m[2t+1]<<24
-    };
-    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
-                                                const uint8_t* r1, uint32_t t) {
-        s.q[0] = pdk_ldg_stream16(d0 + t * 32u);
-        s.q[1] = pdk_ldg_stream16(d0 + t * 32u + 16u);
-        s.q[2] = pdk_ldg_stream16(d1 + t * 32u);
-        s.q[3] = pdk_ldg_stream16(d1 + t * 32u + 16u);
-        s.dd[0] = __ldg(reinterpret_cast<const uint32_t*>(r0));
-        s.dd[1] = __ldg(reinterpret_cast<const uint32_t*>(r1));
-        s.sm[0] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r0 + 4u + 2u * t)) |
-                  ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r0 + 12u + 2u * t)) << 16);
-        s.sm[1] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r1 + 4u + 2u * t)) |
-                  ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r1 + 12u + 2u * t)) << 16);
-    }
-    // A registers of mma i (i = 0..7): word i of the lane's 32 bytes, low nibbles
-    // (block 2t) in k-slots 4t..4t+3, high nibbles (block 2t+1) in slots 16+4t..
-    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
-                                                  uint32_t& a2, uint32_t& a3) {
-        const uint4& lo = s.q[i >> 2];
-        const uint4& hi = s.q[2u + (i >> 2)];
-        const uint32_t wl = (i & 3u) == 0u ? lo.x : (i & 3u) == 1u ? lo.y : (i & 3u) == 2u ? lo.z : lo.w;
-        const uint32_t wh = (i & 3u) == 0u ? hi.x : (i & 3u) == 1u ? hi.y : (i & 3u) == 2u ? hi.z : hi.w;
-        a0 = wl & 0x0F0F0F0Fu;
-        a1 = wh & 0x0F0F0F0Fu;
-        a2 = (wl >> 4) & 0x0F0F0F0Fu;
-        a3 = (wh >> 4) & 0x0F0F0F0Fu;
-    }
-    // f[0..1]: row g blocks 2t, 2t+1 (already times the activation step); f[2..3]: row g+8.
-    // X0, X1: the blocks' activation sums.
-    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float X0, float X1,
-                                                float& acc_g, float& acc_g8) {
-        {
-            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[0]);
-            const float s0 = (float)(s.sm[0] & 0xffu), s1 = (float)((s.sm[0] >> 8) & 0xffu);
-            const float m0 = (float)((s.sm[0] >> 16) & 0xffu), m1 = (float)(s.sm[0] >> 24);
-            acc_g += __low2float(dh) * (s0 * f[0] + s1 * f[1]) - __high2float(dh) * (m0 * X0 + m1 * X1);
-        }
-        {
-            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[1]);
-            const float s0 = (float)(s.sm[1] & 0xffu), s1 = (float)((s.sm[1] >> 8) & 0xffu);
-            const float m0 = (float)((s.sm[1] >> 16) & 0xffu), m1 = (float)(s.sm[1] >> 24);
-            acc_g8 += __low2float(dh) * (s0 * f[2] + s1 * f[3]) - __high2float(dh) * (m0 * X0 + m1 * X1);
-        }
-    }
-};
-
-// Q5_K repacked (kquant_more.cu): 128 bytes of low nibbles in the Q4_K convention, then 32 bytes
-// of high bits (bit j of byte l = bit 4 of element l of block j); the record is Q4_K's.
-struct Q5K {
-    static constexpr uint32_t kDepth = 2;
-    static constexpr uint32_t kDataBytes = 160;
-    static constexpr uint32_t kRecBytes = 24;
-    struct Stage {
-        uint4 q[4];      // as Q4K
-        uint2 hb[2];     // high-bit bytes 8t..8t+7 of row g / row g+8 (the other lanes of the row hold the rest)
-        uint32_t dd[2];
-        uint32_t sm[2];
-    };
-    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
-                                                const uint8_t* r1, uint32_t t) {
-        s.q[0] = pdk_ldg_stream16(d0 + t * 32u);
-        s.q[1] = pdk_ldg_stream16(d0 + t * 32u + 16u);
-        s.q[2] = pdk_ldg_stream16(d1 + t * 32u);
-        s.q[3] = pdk_ldg_stream16(d1 + t * 32u + 16u);
-        s.hb[0] = pdk_ldg_stream8(d0 + 128u + t * 8u);
-        s.hb[1] = pdk_ldg_stream8(d1 + 128u + t * 8u);
-        s.dd[0] = __ldg(reinterpret_cast<const uint32_t*>(r0));
-        s.dd[1] = __ldg(reinterpret_cast<const uint32_t*>(r1));
-        s.sm[0] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r0 + 4u + 2u * t)) |
-                  ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r0 + 12u + 2u * t)) << 16);
-        s.sm[1] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r1 + 4u + 2u * t)) |
-                  ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r1 + 12u + 2u * t)) << 16);
-    }
-    __device__ static __forceinline__ uint32_t word(const uint4& v, uint32_t i) {
-        return i == 0u ? v.x : i == 1u ? v.y : i == 2u ? v.z : v.w;
-    }
-    // mma i: nibbles of word i as in Q4K, plus bit 2t (block 2t) / 2t+1 (block 2t+1) of the
-    // high-bit bytes 4i..4i+3 - held by lane i/2 of the row's four - as bit 4 of each code
-    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
-                                                  uint32_t& a2, uint32_t& a3) {
-        const uint32_t lane = threadIdx.x & 31u, t2 = 2u * (lane & 3u), src = (lane & 28u) | (i >> 1);
-        const uint32_t wl = word(s.q[i >> 2], i & 3u), wh = word(s.q[2u + (i >> 2)], i & 3u);
-        const uint32_t hl = (__shfl_sync(0xffffffffu, (i & 1u) ? s.hb[0].y : s.hb[0].x, src) >> t2) << 4;
-        const uint32_t hh = (__shfl_sync(0xffffffffu, (i & 1u) ? s.hb[1].y : s.hb[1].x, src) >> t2) << 4;
-        a0 = (wl & 0x0F0F0F0Fu) | (hl & 0x10101010u);
-        a1 = (wh & 0x0F0F0F0Fu) | (hh & 0x10101010u);
-        a2 = ((wl >> 4) & 0x0F0F0F0Fu) | ((hl >> 1) & 0x10101010u);
-        a3 = ((wh >> 4) & 0x0F0F0F0Fu) | ((hh >> 1) & 0x10101010u);
-    }
-    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float X0, float X1,
-                                                float& acc_g, float& acc_g8) {
-        {
-            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[0]);
-            const float s0 = (float)(s.sm[0] & 0xffu), s1 = (float)((s.sm[0] >> 8) & 0xffu);
-            const float m0 = (float)((s.sm[0] >> 16) & 0xffu), m1 = (float)(s.sm[0] >> 24);
-            acc_g += __low2float(dh) * (s0 * f[0] + s1 * f[1]) - __high2float(dh) * (m0 * X0 + m1 * X1);
-        }
-        {
-            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[1]);
-            const float s0 = (float)(s.sm[1] & 0xffu), s1 = (float)((s.sm[1] >> 8) & 0xffu);
-            const float m0 = (float)((s.sm[1] >> 16) & 0xffu), m1 = (float)(s.sm[1] >> 24);
-            acc_g8 += __low2float(dh) * (s0 * f[2] + s1 * f[3]) - __high2float(dh) * (m0 * X0 + m1 * X1);
-        }
-    }
-};
-
-// Q4_0 repacked (kquant_more.cu): the data plane is in the Q4_K nibble convention, the record
-// holds eight f16 block scales; w = d (q - 8), so the activation sums carry the -8.
-struct Q40 {
-    static constexpr uint32_t kDepth = 3;
-    static constexpr uint32_t kDataBytes = 128;
-    static constexpr uint32_t kRecBytes = 24;
-    struct Stage {
-        uint4 q[4];
-        uint32_t dd[2];  // {f16 d[2t], f16 d[2t+1]} of the two rows
-    };
-    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
-                                                const uint8_t* r1, uint32_t t) {
-        s.q[0] = pdk_ldg_stream16(d0 + t * 32u);
-        s.q[1] = pdk_ldg_stream16(d0 + t * 32u + 16u);
-        s.q[2] = pdk_ldg_stream16(d1 + t * 32u);
-        s.q[3] = pdk_ldg_stream16(d1 + t * 32u + 16u);
-        s.dd[0] = __ldg(reinterpret_cast<const uint32_t*>(r0 + 4u * t));
-        s.dd[1] = __ldg(reinterpret_cast<const uint32_t*>(r1 + 4u * t));
-    }
-    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
-                                                  uint32_t& a2, uint32_t& a3) {
-        const uint4& lo = s.q[i >> 2];
-        const uint4& hi = s.q[2u + (i >> 2)];
-        const uint32_t wl = (i & 3u) == 0u ? lo.x : (i & 3u) == 1u ? lo.y : (i & 3u) == 2u ? lo.z : lo.w;
-        const uint32_t wh = (i & 3u) == 0u ? hi.x : (i & 3u) == 1u ? hi.y : (i & 3u) == 2u ? hi.z : hi.w;
-        a0 = wl & 0x0F0F0F0Fu;
-        a1 = wh & 0x0F0F0F0Fu;
-        a2 = (wl >> 4) & 0x0F0F0F0Fu;
-        a3 = (wh >> 4) & 0x0F0F0F0Fu;
-    }
-    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float X0, float X1,
-                                                float& acc_g, float& acc_g8) {
-        const __half2 d0 = *reinterpret_cast<const __half2*>(&s.dd[0]);
-        const __half2 d1 = *reinterpret_cast<const __half2*>(&s.dd[1]);
-        const float o0 = -8.0f * X0, o1 = -8.0f * X1;
-        acc_g += __low2float(d0) * (f[0] + o0) + __high2float(d0) * (f[1] + o1);
-        acc_g8 += __low2float(d1) * (f[2] + o0) + __high2float(d1) * (f[3] + o1);
-    }
-};
-
-struct Q80 {
-    static constexpr uint32_t kDepth = 2;
-    static constexpr uint32_t kDataBytes = 256;  // 8 blocks of 32 int8
-    static constexpr uint32_t kRecBytes = 16;    // 8 f16 scales
-    struct Stage {
-        uint4 q[8];      // row g: blocks 2t, 2t+1 (64 bytes); row g+8 likewise
-        uint32_t dd[2];  // {f16 d[2t], f16 d[2t+1]} of the two rows
-    };
-    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
-                                                const uint8_t* r1, uint32_t t) {
-#pragma unroll
-        for (uint32_t i = 0; i < 4u; ++i) {
-            s.q[i] = pdk_ldg_stream16(d0 + t * 64u + i * 16u);
-            s.q[4u + i] = pdk_ldg_stream16(d1 + t * 64u + i * 16u);
-        }
-        s.dd[0] = __ldg(reinterpret_cast<const uint32_t*>(r0 + 4u * t));
-        s.dd[1] = __ldg(reinterpret_cast<const uint32_t*>(r1 + 4u * t));
-    }
-    __device__ static __forceinline__ uint32_t word(const uint4& v, uint32_t i) {
-        return i == 0u ? v.x : i == 1u ? v.y : i == 2u ? v.z : v.w;
-    }
-    // mma i: word i of block 2t in slots 4t..4t+3, word i of block 2t+1 in slots 16+4t..
-    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
-                                                  uint32_t& a2, uint32_t& a3) {
-        a0 = word(s.q[i >> 2], i & 3u);
-        a2 = word(s.q[2u + (i >> 2)], i & 3u);
-        a1 = word(s.q[4u + (i >> 2)], i & 3u);
-        a3 = word(s.q[6u + (i >> 2)], i & 3u);
-    }
-    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float, float, float& acc_g,
-                                                float& acc_g8) {
-        const __half2 d0 = *reinterpret_cast<const __half2*>(&s.dd[0]);
-        const __half2 d1 = *reinterpret_cast<const __half2*>(&s.dd[1]);
-        acc_g += __low2float(d0) * f[0] + __high2float(d0) * f[1];
-        acc_g8 += __low2float(d1) * f[2] + __high2float(d1) * f[3];
-    }
-};
+using namespace gemv_i8;
 
 // Shared memory: limb planes int8 [2][K] (hi, lo), 32 zero bytes,
 // xmeta float2 [K/32] = {step s_j, s_j * sum_i v_ji}, red f32 [2][kSlots][kSlices][16].
-// Row-sharded output: when n > 0 the kernel stores row r of its band at ptr[p][row0 + r] for
-// every p < n - the full-length y of each rank, peer memory over NVLink included - instead of
-// y[r].  Plain peer stores; the caller orders them (a barrier, or a flag the consumer waits on).
-struct PeerOut {
-    float* ptr[8];
-    uint32_t n, row0;
-};
-
 template <class F>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ recs, const float* __restrict__ bias,
@@ -299,7 +89,7 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
         r1 = recs + rb * row_rec;
     };
     auto issue = [&](Stage& s) {
-        F::load(s, p0 + (size_t)l_u * F::kDataBytes, p1 + (size_t)l_u * F::kDataBytes,
+        F::template load<false>(s, p0 + (size_t)l_u * F::kDataBytes, p1 + (size_t)l_u * F::kDataBytes,
                 r0 + (size_t)l_u * F::kRecBytes, r1 + (size_t)l_u * F::kRecBytes, t);
         if (++l_u == u_hi) {
             l_u = u_lo;
@@ -323,56 +113,7 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // ---- activations -> block floating point limbs (8 elements per thread,
-    //      the 4 lanes of a block agree on the step through two shuffles)
-    {
-        const uint32_t groups = in_dim >> 3;
-        for (uint32_t grp = tid; grp < groups; grp += kThreads) {
-            float v[8];
-            if (xq == nullptr) {
-                const float4 a = *reinterpret_cast<const float4*>(x + grp * 8u);
-                const float4 b = *reinterpret_cast<const float4*>(x + grp * 8u + 4u);
-                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-            } else {
-                // int8 activations with one f32 scale per 32 (the W4A8 slots' operands)
-                const int2 q = *reinterpret_cast<const int2*>(xq + grp * 8u);
-                const float s = xq_scale[grp >> 2];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = (float)(int8_t)((i < 4 ? q.x >> (8 * i) : q.y >> (8 * (i - 4))) & 0xff) * s;
-            }
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            // amax < 2^ex  ->  step 2^(ex-14) keeps |v| <= 2^14
-            int ex = 0;
-            float step = 1.0f, inv = 0.0f;
-            if (amax > 0.0f && amax < 3.0e38f) {
-                (void)frexpf(amax, &ex);
-                ex = max(ex, -110);
-                step = ldexpf(1.0f, ex - 14);
-                inv = ldexpf(1.0f, 14 - ex);
-            }
-            uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
-            int isum = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                int q = __float2int_rn(v[i] * inv);
-                q = max(-16384, min(16384, q));
-                const int h = (q + 128) >> 8, l = q - (h << 8);
-                hi[i >> 2] |= ((uint32_t)h & 0xffu) << (8 * (i & 3));
-                lo[i >> 2] |= ((uint32_t)l & 0xffu) << (8 * (i & 3));
-                isum += q;
-            }
-            *reinterpret_cast<uint2*>(xs_hi + (size_t)grp * 8u) = make_uint2(hi[0], hi[1]);
-            *reinterpret_cast<uint2*>(xs_lo + (size_t)grp * 8u) = make_uint2(lo[0], lo[1]);
-            isum += __shfl_xor_sync(0xffffffffu, isum, 1);
-            isum += __shfl_xor_sync(0xffffffffu, isum, 2);
-            if ((grp & 3u) == 0u) xmeta[grp >> 2] = make_float2(step, step * (float)isum);
-        }
-        if (tid < 8u) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
-    }
+    act_limbs(x, xq, xq_scale, in_dim, xs_hi, xs_lo, zeros, xmeta, tid, kThreads);
     __syncthreads();
 
     // B operand source of this lane: block 2t feeds k-slots 4t..4t+3 of column
@@ -509,56 +250,39 @@ int launch(const void* data, const void* recs, const float* bias, const float* x
 
 }  // namespace
 
-// Both return 0 / a cudaError_t, or -1 when the shape is outside the kernel's
-// plan (K not a multiple of 256, fewer than four units per row, or activations
-// too long for shared memory) and the caller should take another route.
-int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+// The register-staged kernel: the route for the shapes the ring kernel (gemv_ring.cu) declines.
+// All return 0 / a cudaError_t, or -1 when the shape is outside this kernel's plan too (K not a
+// multiple of 256, fewer than four units per row, or activations too long for shared memory).
+int pdk_q4k_gemv_i8_regs(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st) {
     return launch<Q4K>(data, scales, nullptr, x, y, in_dim, out_dim, st);
 }
 
-int pdk_q4_0_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+int pdk_q4_0_gemv_i8_regs(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                      uint32_t out_dim, cudaStream_t st) {
     return launch<Q40>(data, scales, nullptr, x, y, in_dim, out_dim, st);
 }
 
-int pdk_q5k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+int pdk_q5k_gemv_i8_regs(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st) {
     return launch<Q5K>(data, scales, nullptr, x, y, in_dim, out_dim, st);
 }
 
-int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, const float* x, float* y,
+int pdk_q8_0_gemv_i8_regs(const void* data, const void* scale, const float* bias, const float* x, float* y,
                      uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
     return launch<Q80>(data, scale, bias, x, y, in_dim, out_dim, st);
 }
 
 // Q4_K GEMV on int8 activations (xq int8 [in_dim], one f32 scale per 32): same kernel, the
 // activation staging widens q * scale before it builds its limbs.
-int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq, const float* xq_scale, float* y,
+int pdk_q4k_gemv_i8_q8act_regs(const void* data, const void* scales, const int8_t* xq, const float* xq_scale, float* y,
                           uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
     return launch<Q4K>(data, scales, nullptr, nullptr, y, in_dim, out_dim, st, xq, xq_scale);
 }
 
-// No counterpart in the reference (its multi-GPU story is one process per GPU, replicas only):
-// Q4_K decode GEMV of one rank's row band that writes its band straight into every rank's
-// full-length y (y_ptrs[0..n_ranks), device pointers valid on this GPU: its own buffer and the
-// peers' buffers mapped over NVLink) at rows row0 .. row0 + out_dim.  The exchange that an
-// all-gather would do is the kernel's own stores.  The stores are complete when the kernel
-// is; the caller orders consumers after it (stream order locally, a barrier or flag across
-// ranks).  n_ranks <= 8.  Returns 801 for shapes outside the GEMV kernel's plan.
-PDK_EXPORT int pdk_q4k_gemv_shard(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
-                                  uint32_t n_ranks, uint32_t row0, uint32_t in_dim, uint32_t out_dim, void* stream) {
-    if (out_dim == 0) return 0;
-    if (n_ranks == 0 || n_ranks > 8u || y_ptrs == nullptr) return cudaErrorInvalidValue;
-    if (!pdk_aligned(data, 16) || !pdk_aligned(scales, 8) || !pdk_aligned(x, 16)) return cudaErrorInvalidValue;
-    PeerOut po{};
-    for (uint32_t p = 0; p < n_ranks; ++p) {
-        if (y_ptrs[p] == nullptr || !pdk_aligned(y_ptrs[p], 4)) return cudaErrorInvalidValue;
-        po.ptr[p] = (float*)y_ptrs[p];
-    }
-    po.n = n_ranks;
-    po.row0 = row0;
-    const int rc = launch<Q4K>(data, scales, nullptr, (const float*)x, nullptr, in_dim, out_dim, (cudaStream_t)stream,
-                               nullptr, nullptr, &po);
-    return rc >= 0 ? rc : (int)cudaErrorNotSupported;
+// The Q4_K GEMV of one rank's row band with the peer-store epilogue (see gemv_ring.cu:
+// pdk_q4k_gemv_shard); -1 = shape outside this kernel's plan.
+int pdk_q4k_gemv_peers_regs(const void* data, const void* scales, const float* x, const gemv_i8::PeerOut* po,
+                            uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
+    return launch<Q4K>(data, scales, nullptr, x, nullptr, in_dim, out_dim, st, nullptr, nullptr, po);
 }

@@ -1,0 +1,377 @@
+// gemv_i8_traits.cuh - format traits shared by the decode GEMV kernels on the int8 tensor path
+// (gemv_i8.cu: operands prefetched into registers; gemv_ring.cu: operands staged in a
+// shared-memory ring by bulk copies).
+//
+// A "unit" is 256 weights of one row (a Q4_K / Q5_K super-block, eight Q4_0 or Q8_0 blocks).
+// Lane (g, t) of a warp holds rows g and g + 8 of a 16-row tile and owns blocks 2t and 2t+1 of
+// the unit.  `load<kShared>` fills a Stage from the unit's data / record bytes of the two rows:
+// streaming global loads (kShared = false) or plain loads from a staged copy (kShared = true).
+#pragma once
+#include "pdk_common.cuh"
+
+namespace gemv_i8 {
+
+template <bool kShared>
+__device__ __forceinline__ uint4 ld16(const void* p) {
+    if constexpr (kShared) return *reinterpret_cast<const uint4*>(p);
+    else return pdk_ldg_stream16(p);
+}
+template <bool kShared>
+__device__ __forceinline__ uint2 ld8(const void* p) {
+    if constexpr (kShared) return *reinterpret_cast<const uint2*>(p);
+    else return pdk_ldg_stream8(p);
+}
+template <bool kShared>
+__device__ __forceinline__ uint32_t ld4(const void* p) {
+    if constexpr (kShared) return *reinterpret_cast<const uint32_t*>(p);
+    else return __ldg(reinterpret_cast<const uint32_t*>(p));
+}
+template <bool kShared>
+__device__ __forceinline__ uint32_t ld2(const void* p) {
+    if constexpr (kShared) return (uint32_t)*reinterpret_cast<const uint16_t*>(p);
+    else return (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p));
+}
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The same with unsigned A bytes (codes 0..255 against signed activation limbs).
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Non-volatile forms: the compiler may interleave independent accumulator chains.
+__device__ __forceinline__ void mma_s8_nv(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8s8_nv(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                            uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------------------
+// Format traits.  A "unit" is 256 weights of one row (a Q4_K super-block, or
+// eight Q8_0 blocks).  Lane t owns blocks 2t and 2t+1 of the unit.
+// ---------------------------------------------------------------------------
+struct Q4K {
+    static constexpr uint32_t kDepth = 3;
+    static constexpr uint32_t kDataBytes = 128;  // per row per unit
+    static constexpr uint32_t kRecBytes = 24;
+    struct Stage {
+        uint4 q[4];      // row g: bytes 0..15 / 16..31 of ggml group t; row g+8 likewise
+        uint32_t dd[2];  // {f16 d, f16 dmin} of the two rows
+        uint32_t sm[2];  // sc[2t] | sc[2t+1]<<8 | m[2t]<<16 | m[2t+1]<<24
+    };
+    template <bool kShared>
+    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
+                                                const uint8_t* r1, uint32_t t) {
+        s.q[0] = ld16<kShared>(d0 + t * 32u);
+        s.q[1] = ld16<kShared>(d0 + t * 32u + 16u);
+        s.q[2] = ld16<kShared>(d1 + t * 32u);
+        s.q[3] = ld16<kShared>(d1 + t * 32u + 16u);
+        s.dd[0] = ld4<kShared>(r0);
+        s.dd[1] = ld4<kShared>(r1);
+        s.sm[0] = ld2<kShared>(r0 + 4u + 2u * t) |
+                  (ld2<kShared>(r0 + 12u + 2u * t) << 16);
+        s.sm[1] = ld2<kShared>(r1 + 4u + 2u * t) |
+                  (ld2<kShared>(r1 + 12u + 2u * t) << 16);
+    }
+    // A registers of mma i (i = 0..7): word i of the lane's 32 bytes, low nibbles
+    // (block 2t) in k-slots 4t..4t+3, high nibbles (block 2t+1) in slots 16+4t..
+    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint4& lo = s.q[i >> 2];
+        const uint4& hi = s.q[2u + (i >> 2)];
+        const uint32_t wl = (i & 3u) == 0u ? lo.x : (i & 3u) == 1u ? lo.y : (i & 3u) == 2u ? lo.z : lo.w;
+        const uint32_t wh = (i & 3u) == 0u ? hi.x : (i & 3u) == 1u ? hi.y : (i & 3u) == 2u ? hi.z : hi.w;
+        a0 = wl & 0x0F0F0F0Fu;
+        a1 = wh & 0x0F0F0F0Fu;
+        a2 = (wl >> 4) & 0x0F0F0F0Fu;
+        a3 = (wh >> 4) & 0x0F0F0F0Fu;
+    }
+    // The ring kernel's form: codes stay where they are in the byte.  a0 / a1 = low nibbles, a2 / a3 =
+    // the high nibbles left in place (16 x code, an unsigned byte), so a word costs two ANDs per
+    // row instead of two ANDs and two shifts; the sums of blocks 2t+1 come out 16 times too large
+    // and are shifted back (exactly: every product is a multiple of 16) before the f32 conversion.
+    static constexpr bool kUnsignedA = true;
+    static constexpr int kHiShift = 4;
+    __device__ static __forceinline__ void a_frag(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint4& lo = s.q[i >> 2];
+        const uint4& hi = s.q[2u + (i >> 2)];
+        const uint32_t wl = (i & 3u) == 0u ? lo.x : (i & 3u) == 1u ? lo.y : (i & 3u) == 2u ? lo.z : lo.w;
+        const uint32_t wh = (i & 3u) == 0u ? hi.x : (i & 3u) == 1u ? hi.y : (i & 3u) == 2u ? hi.z : hi.w;
+        a0 = wl & 0x0F0F0F0Fu;
+        a1 = wh & 0x0F0F0F0Fu;
+        a2 = wl & 0xF0F0F0F0u;
+        a3 = wh & 0xF0F0F0F0u;
+    }
+    // f[0..1]: row g blocks 2t, 2t+1 (already times the activation step); f[2..3]: row g+8.
+    // X0, X1: the blocks' activation sums.
+    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float X0, float X1,
+                                                float& acc_g, float& acc_g8) {
+        {
+            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[0]);
+            const float s0 = (float)(s.sm[0] & 0xffu), s1 = (float)((s.sm[0] >> 8) & 0xffu);
+            const float m0 = (float)((s.sm[0] >> 16) & 0xffu), m1 = (float)(s.sm[0] >> 24);
+            acc_g += __low2float(dh) * (s0 * f[0] + s1 * f[1]) - __high2float(dh) * (m0 * X0 + m1 * X1);
+        }
+        {
+            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[1]);
+            const float s0 = (float)(s.sm[1] & 0xffu), s1 = (float)((s.sm[1] >> 8) & 0xffu);
+            const float m0 = (float)((s.sm[1] >> 16) & 0xffu), m1 = (float)(s.sm[1] >> 24);
+            acc_g8 += __low2float(dh) * (s0 * f[2] + s1 * f[3]) - __high2float(dh) * (m0 * X0 + m1 * X1);
+        }
+    }
+};
+
+// Q5_K repacked (kquant_more.cu): 128 bytes of low nibbles in the Q4_K convention, then 32 bytes
+// of high bits (bit j of byte l = bit 4 of element l of block j); the record is Q4_K's.
+struct Q5K {
+    static constexpr uint32_t kDepth = 2;
+    static constexpr uint32_t kDataBytes = 160;
+    static constexpr uint32_t kRecBytes = 24;
+    struct Stage {
+        uint4 q[4];      // as Q4K
+        uint2 hb[2];     // high-bit bytes 8t..8t+7 of row g / row g+8 (the other lanes of the row hold the rest)
+        uint32_t dd[2];
+        uint32_t sm[2];
+    };
+    template <bool kShared>
+    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
+                                                const uint8_t* r1, uint32_t t) {
+        s.q[0] = ld16<kShared>(d0 + t * 32u);
+        s.q[1] = ld16<kShared>(d0 + t * 32u + 16u);
+        s.q[2] = ld16<kShared>(d1 + t * 32u);
+        s.q[3] = ld16<kShared>(d1 + t * 32u + 16u);
+        s.hb[0] = ld8<kShared>(d0 + 128u + t * 8u);
+        s.hb[1] = ld8<kShared>(d1 + 128u + t * 8u);
+        s.dd[0] = ld4<kShared>(r0);
+        s.dd[1] = ld4<kShared>(r1);
+        s.sm[0] = ld2<kShared>(r0 + 4u + 2u * t) |
+                  (ld2<kShared>(r0 + 12u + 2u * t) << 16);
+        s.sm[1] = ld2<kShared>(r1 + 4u + 2u * t) |
+                  (ld2<kShared>(r1 + 12u + 2u * t) << 16);
+    }
+    __device__ static __forceinline__ uint32_t word(const uint4& v, uint32_t i) {
+        return i == 0u ? v.x : i == 1u ? v.y : i == 2u ? v.z : v.w;
+    }
+    // mma i: nibbles of word i as in Q4K, plus bit 2t (block 2t) / 2t+1 (block 2t+1) of the
+    // high-bit bytes 4i..4i+3 - held by lane i/2 of the row's four - as bit 4 of each code
+    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint32_t lane = threadIdx.x & 31u, t2 = 2u * (lane & 3u), src = (lane & 28u) | (i >> 1);
+        const uint32_t wl = word(s.q[i >> 2], i & 3u), wh = word(s.q[2u + (i >> 2)], i & 3u);
+        const uint32_t hl = (__shfl_sync(0xffffffffu, (i & 1u) ? s.hb[0].y : s.hb[0].x, src) >> t2) << 4;
+        const uint32_t hh = (__shfl_sync(0xffffffffu, (i & 1u) ? s.hb[1].y : s.hb[1].x, src) >> t2) << 4;
+        a0 = (wl & 0x0F0F0F0Fu) | (hl & 0x10101010u);
+        a1 = (wh & 0x0F0F0F0Fu) | (hh & 0x10101010u);
+        a2 = ((wl >> 4) & 0x0F0F0F0Fu) | ((hl >> 1) & 0x10101010u);
+        a3 = ((wh >> 4) & 0x0F0F0F0Fu) | ((hh >> 1) & 0x10101010u);
+    }
+    static constexpr bool kUnsignedA = true;
+    static constexpr int kHiShift = 0;
+    __device__ static __forceinline__ void a_frag(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        a_regs(s, i, a0, a1, a2, a3);
+    }
+    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float X0, float X1,
+                                                float& acc_g, float& acc_g8) {
+        {
+            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[0]);
+            const float s0 = (float)(s.sm[0] & 0xffu), s1 = (float)((s.sm[0] >> 8) & 0xffu);
+            const float m0 = (float)((s.sm[0] >> 16) & 0xffu), m1 = (float)(s.sm[0] >> 24);
+            acc_g += __low2float(dh) * (s0 * f[0] + s1 * f[1]) - __high2float(dh) * (m0 * X0 + m1 * X1);
+        }
+        {
+            const __half2 dh = *reinterpret_cast<const __half2*>(&s.dd[1]);
+            const float s0 = (float)(s.sm[1] & 0xffu), s1 = (float)((s.sm[1] >> 8) & 0xffu);
+            const float m0 = (float)((s.sm[1] >> 16) & 0xffu), m1 = (float)(s.sm[1] >> 24);
+            acc_g8 += __low2float(dh) * (s0 * f[2] + s1 * f[3]) - __high2float(dh) * (m0 * X0 + m1 * X1);
+        }
+    }
+};
+
+// Q4_0 repacked (kquant_more.cu): the data plane is in the Q4_K nibble convention, the record
+// holds eight f16 block scales; w = d (q - 8), so the activation sums carry the -8.
+struct Q40 {
+    static constexpr uint32_t kDepth = 3;
+    static constexpr uint32_t kDataBytes = 128;
+    static constexpr uint32_t kRecBytes = 24;
+    struct Stage {
+        uint4 q[4];
+        uint32_t dd[2];  // {f16 d[2t], f16 d[2t+1]} of the two rows
+    };
+    template <bool kShared>
+    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
+                                                const uint8_t* r1, uint32_t t) {
+        s.q[0] = ld16<kShared>(d0 + t * 32u);
+        s.q[1] = ld16<kShared>(d0 + t * 32u + 16u);
+        s.q[2] = ld16<kShared>(d1 + t * 32u);
+        s.q[3] = ld16<kShared>(d1 + t * 32u + 16u);
+        s.dd[0] = ld4<kShared>(r0 + 4u * t);
+        s.dd[1] = ld4<kShared>(r1 + 4u * t);
+    }
+    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint4& lo = s.q[i >> 2];
+        const uint4& hi = s.q[2u + (i >> 2)];
+        const uint32_t wl = (i & 3u) == 0u ? lo.x : (i & 3u) == 1u ? lo.y : (i & 3u) == 2u ? lo.z : lo.w;
+        const uint32_t wh = (i & 3u) == 0u ? hi.x : (i & 3u) == 1u ? hi.y : (i & 3u) == 2u ? hi.z : hi.w;
+        a0 = wl & 0x0F0F0F0Fu;
+        a1 = wh & 0x0F0F0F0Fu;
+        a2 = (wl >> 4) & 0x0F0F0F0Fu;
+        a3 = (wh >> 4) & 0x0F0F0F0Fu;
+    }
+    // The ring kernel's form: codes stay where they are in the byte.  a0 / a1 = low nibbles, a2 / a3 =
+    // the high nibbles left in place (16 x code, an unsigned byte), so a word costs two ANDs per
+    // row instead of two ANDs and two shifts; the sums of blocks 2t+1 come out 16 times too large
+    // and are shifted back (exactly: every product is a multiple of 16) before the f32 conversion.
+    static constexpr bool kUnsignedA = true;
+    static constexpr int kHiShift = 4;
+    __device__ static __forceinline__ void a_frag(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint4& lo = s.q[i >> 2];
+        const uint4& hi = s.q[2u + (i >> 2)];
+        const uint32_t wl = (i & 3u) == 0u ? lo.x : (i & 3u) == 1u ? lo.y : (i & 3u) == 2u ? lo.z : lo.w;
+        const uint32_t wh = (i & 3u) == 0u ? hi.x : (i & 3u) == 1u ? hi.y : (i & 3u) == 2u ? hi.z : hi.w;
+        a0 = wl & 0x0F0F0F0Fu;
+        a1 = wh & 0x0F0F0F0Fu;
+        a2 = wl & 0xF0F0F0F0u;
+        a3 = wh & 0xF0F0F0F0u;
+    }
+    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float X0, float X1,
+                                                float& acc_g, float& acc_g8) {
+        const __half2 d0 = *reinterpret_cast<const __half2*>(&s.dd[0]);
+        const __half2 d1 = *reinterpret_cast<const __half2*>(&s.dd[1]);
+        const float o0 = -8.0f * X0, o1 = -8.0f * X1;
+        acc_g += __low2float(d0) * (f[0] + o0) + __high2float(d0) * (f[1] + o1);
+        acc_g8 += __low2float(d1) * (f[2] + o0) + __high2float(d1) * (f[3] + o1);
+    }
+};
+
+struct Q80 {
+    static constexpr uint32_t kDepth = 2;
+    static constexpr uint32_t kDataBytes = 256;  // 8 blocks of 32 int8
+    static constexpr uint32_t kRecBytes = 16;    // 8 f16 scales
+    struct Stage {
+        uint4 q[8];      // row g: blocks 2t, 2t+1 (64 bytes); row g+8 likewise
+        uint32_t dd[2];  // {f16 d[2t], f16 d[2t+1]} of the two rows
+    };
+    template <bool kShared>
+    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
+                                                const uint8_t* r1, uint32_t t) {
+#pragma unroll
+        for (uint32_t i = 0; i < 4u; ++i) {
+            s.q[i] = ld16<kShared>(d0 + t * 64u + i * 16u);
+            s.q[4u + i] = ld16<kShared>(d1 + t * 64u + i * 16u);
+        }
+        s.dd[0] = ld4<kShared>(r0 + 4u * t);
+        s.dd[1] = ld4<kShared>(r1 + 4u * t);
+    }
+    __device__ static __forceinline__ uint32_t word(const uint4& v, uint32_t i) {
+        return i == 0u ? v.x : i == 1u ? v.y : i == 2u ? v.z : v.w;
+    }
+    // mma i: word i of block 2t in slots 4t..4t+3, word i of block 2t+1 in slots 16+4t..
+    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        a0 = word(s.q[i >> 2], i & 3u);
+        a2 = word(s.q[2u + (i >> 2)], i & 3u);
+        a1 = word(s.q[4u + (i >> 2)], i & 3u);
+        a3 = word(s.q[6u + (i >> 2)], i & 3u);
+    }
+    static constexpr bool kUnsignedA = false;
+    static constexpr int kHiShift = 0;
+    __device__ static __forceinline__ void a_frag(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        a_regs(s, i, a0, a1, a2, a3);
+    }
+    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float, float, float& acc_g,
+                                                float& acc_g8) {
+        const __half2 d0 = *reinterpret_cast<const __half2*>(&s.dd[0]);
+        const __half2 d1 = *reinterpret_cast<const __half2*>(&s.dd[1]);
+        acc_g += __low2float(d0) * f[0] + __high2float(d0) * f[1];
+        acc_g8 += __low2float(d1) * f[2] + __high2float(d1) * f[3];
+    }
+};
+
+// Row-sharded output: when n > 0 the kernel stores row r of its band at ptr[p][row0 + r] for
+// every p < n - the full-length y of each rank, peer memory over NVLink included - instead of
+// y[r].  Plain peer stores; the caller orders them (a barrier, or a flag the consumer waits on).
+struct PeerOut {
+    float* ptr[8];
+    uint32_t n, row0;
+};
+
+// Activations -> block floating point limbs, by `nthreads` threads of a CTA (whole warps): per
+// 32-element block a power-of-two step and 15-bit integers kept as two int8 limbs
+// (xs_hi, xs_lo: int8 [in_dim]), xmeta[block] = {step, step * sum of the block's integers},
+// and a 32-byte zero line.  x f32 [in_dim], or int8 xq with one f32 scale per 32.  8 elements
+// per thread; the 4 lanes of a block agree on the step through two shuffles.
+__device__ __forceinline__ void act_limbs(const float* __restrict__ x, const int8_t* __restrict__ xq,
+                                          const float* __restrict__ xq_scale, uint32_t in_dim, uint8_t* xs_hi,
+                                          uint8_t* xs_lo, uint8_t* zeros, float2* xmeta, uint32_t tid,
+                                          uint32_t nthreads)
+    {
+        const uint32_t groups = in_dim >> 3;
+        for (uint32_t grp = tid; grp < groups; grp += nthreads) {
+            float v[8];
+            if (xq == nullptr) {
+                const float4 a = *reinterpret_cast<const float4*>(x + grp * 8u);
+                const float4 b = *reinterpret_cast<const float4*>(x + grp * 8u + 4u);
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            } else {
+                // int8 activations with one f32 scale per 32 (the W4A8 slots' operands)
+                const int2 q = *reinterpret_cast<const int2*>(xq + grp * 8u);
+                const float s = xq_scale[grp >> 2];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (float)(int8_t)((i < 4 ? q.x >> (8 * i) : q.y >> (8 * (i - 4))) & 0xff) * s;
+            }
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            // amax < 2^ex  ->  step 2^(ex-14) keeps |v| <= 2^14
+            float step = 1.0f, inv = 0.0f;
+            if (amax > 0.0f && amax < 3.0e38f) {
+                // frexp's exponent from the bits (denormals land on the clamp), powers of two built in place
+                const int ex = max((int)(__float_as_uint(amax) >> 23) - 126, -110);
+                step = __uint_as_float((uint32_t)(ex + 113) << 23);
+                inv = __uint_as_float((uint32_t)(141 - ex) << 23);
+            }
+            uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+            int isum = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                int q = __float2int_rn(v[i] * inv);
+                q = max(-16384, min(16384, q));
+                const int h = (q + 128) >> 8, l = q - (h << 8);
+                hi[i >> 2] |= ((uint32_t)h & 0xffu) << (8 * (i & 3));
+                lo[i >> 2] |= ((uint32_t)l & 0xffu) << (8 * (i & 3));
+                isum += q;
+            }
+            *reinterpret_cast<uint2*>(xs_hi + (size_t)grp * 8u) = make_uint2(hi[0], hi[1]);
+            *reinterpret_cast<uint2*>(xs_lo + (size_t)grp * 8u) = make_uint2(lo[0], lo[1]);
+            isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+            isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+            if ((grp & 3u) == 0u) xmeta[grp >> 2] = make_float2(step, step * (float)isum);
+        }
+        if (tid < 8u) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
+    }
+
+}  // namespace gemv_i8

@@ -1,0 +1,594 @@
+// gemv_ring.cu - single-token decode GEMV for Q4_K, Q4_0 and Q8_0 planes with the weights staged
+// in shared memory by TMA, every warp running its own ring.
+//
+// The arithmetic is that of gemv_i8.cu (integer dot products on mma m16n8k32, activations as two
+// int8 limbs of a 15-bit block floating point, block-diagonal B operand, f32 scale fold); what
+// differs is how the bytes reach the SM.  A decode GEMV reads every weight once, so its time is
+// the time HBM needs, provided enough bytes are in flight: about 7 MB over the chip.  Loads
+// issued from registers cap that at (threads x registers spent on staging); here every warp keeps
+// D tiled TMA copies outstanding into its own shared-memory stages, 150-190 KB per SM whatever
+// the warps hold in registers, and requests them at kernel start, before the wait on the previous
+// kernel in the stream (programmatic dependent launch).
+//
+//   * A CTA (one per SM) owns a contiguous range of 16-row tiles; warp w takes units w, w + W, ...
+//     of every tile (unit = 256 weights of a row).  Per (tile, unit) the warp's elected lane issues
+//     one 2-D TMA copy of the 16 rows x 128 bytes of packed weights (two for Q8_0's 256 bytes) and
+//     one of the rows' scale records.  The planes stay in the byte layout the repack slots write
+//     (super-block local: the engine concatenates planes at super-block offsets); the tensor maps
+//     describe them as [rows][row bytes].
+//   * The weight boxes are written with the 128-byte swizzle, which puts the 16-byte chunks that
+//     the eight rows of one mma fragment load touch into eight different bank groups: fragment
+//     loads are conflict free, and the shared-memory port carries each byte twice (in and out).
+//   * A warp is the only reader of its stages: it waits on its own mbarrier, moves the fragments
+//     to registers, and re-arms the stage itself after the mma sequence has consumed them.  No
+//     producer warp, no cross-warp hand-shake in the weight path, so a warp that falls behind
+//     delays nobody's loads.  When W equals the units of a row (K = 5120: 20 warps) a warp meets
+//     the same slice of the activations in every tile and keeps its B operand in registers.
+//   * Per tile each warp leaves 16 partial row sums in one of kRedBufs shared buffers and arrives
+//     on the buffer's mbarrier without waiting; warp (tile mod W) adds the W partials in warp order
+//     once they are all there - it looks once per iteration - and stores y (or, row sharded, the
+//     band into every rank's y).
+//
+// Every wait is bounded (tc5::mbar_wait): a wait that runs out records a code in the device
+// error word and raises the CTA's abort flag; every warp then stops computing, and before it
+// leaves waits (bounded again) for the copies it still has in flight.
+#include <cstdlib>
+
+#include "gemv_i8_traits.cuh"
+#include "tc5.cuh"
+
+namespace {
+
+using namespace gemv_i8;
+
+constexpr uint32_t kMaxWarps = 12;
+constexpr uint32_t kMaxDepth = 4;
+constexpr uint32_t kRedBufs = 8;
+constexpr uint32_t kSmemMax = 232448;  // 227 KB per CTA on sm_100
+constexpr uint32_t kBoxBytes = 2048;   // 16 rows x 128 bytes
+
+struct RingPlan {
+    uint32_t W;          // warps
+    uint32_t D;          // stages per warp
+    uint32_t invariant;  // W == pairs per row: a warp's pair never changes
+    uint32_t off_xmeta, off_red, off_bar, off_rec, off_data, smem_bytes;
+};
+
+enum : unsigned int { kErrRingFull = 0x11, kErrRingFold = 0x13, kErrRingDrain = 0x14, kErrRingFree = 0x15 };
+
+// ---------------------------------------------------------------------------
+// Ring traits: how a unit of a tile is read back from its boxes.  Stage, fold and kUnsignedA come
+// from the shared traits.  The mma scheme differs from gemv_i8.cu's: one mma carries both
+// activation limbs.  Its 32 k-slots are 8 weights of each of four blocks (lane t: block
+// blk(p, t), slots 4t..4t+3 and 16+4t..16+4t+3), its eight columns are (block, limb) pairs, and
+// column 2b + l is non-zero only in block b's slots.  Four mmas (j = 0..3) finish four blocks,
+// two passes the unit's eight: 8 mmas per unit, and lane (g, t) ends up holding the high- and
+// low-limb sums of blocks blk(0, t) and blk(1, t) for rows g and g + 8, which it folds with
+// their scales.
+// ---------------------------------------------------------------------------
+// Physical offset of 16-byte chunk c of row r in a box written with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) { return r * 128u + ((c ^ (r & 7u)) << 4); }
+__device__ __forceinline__ uint32_t word4(const uint4& v, uint32_t i) { return i == 0u ? v.x : i == 1u ? v.y : i == 2u ? v.z : v.w; }
+
+// load_ring arguments: `box` = the unit's first data box, o0 / o1 = swz(g, 2t) / swz(g, 2t + 1)
+// (rows g + 8 lie 1024 bytes further), `rec` = row g's record of the unit (row g + 8: 8 box rows on).
+struct RQ4K : Q4K {
+    static constexpr uint32_t kDataBoxes = 1;
+    // pass p of lane t feeds block 2t + p: the low (p = 0) or high nibbles of ggml group t, whose
+    // first 16 bytes (chunk 2t) sit in k-slots 4t.. and whose second 16 (chunk 2t+1) in slots 16+4t..
+    __device__ static __forceinline__ uint32_t blk(uint32_t p, uint32_t t) { return 2u * t + p; }
+    __device__ static __forceinline__ void a_pass(const Stage& s, uint32_t p, uint32_t j, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint32_t mask = p ? 0xF0F0F0F0u : 0x0F0F0F0Fu;  // high nibbles stay in place: 16 x code, shifted back after
+        a0 = word4(s.q[0], j) & mask;
+        a1 = word4(s.q[2], j) & mask;
+        a2 = word4(s.q[1], j) & mask;
+        a3 = word4(s.q[3], j) & mask;
+    }
+    __device__ static __forceinline__ void load_ring(Stage& s, const uint8_t* box, const uint8_t* rec, uint32_t rec8,
+                                                     uint32_t o0, uint32_t o1, uint32_t t) {
+        s.q[0] = *reinterpret_cast<const uint4*>(box + o0);
+        s.q[1] = *reinterpret_cast<const uint4*>(box + o1);
+        s.q[2] = *reinterpret_cast<const uint4*>(box + o0 + 1024u);
+        s.q[3] = *reinterpret_cast<const uint4*>(box + o1 + 1024u);
+        const uint8_t* r1 = rec + rec8;
+        s.dd[0] = *reinterpret_cast<const uint32_t*>(rec);
+        s.dd[1] = *reinterpret_cast<const uint32_t*>(r1);
+        s.sm[0] = (uint32_t)*reinterpret_cast<const uint16_t*>(rec + 4u + 2u * t) |
+                  ((uint32_t)*reinterpret_cast<const uint16_t*>(rec + 12u + 2u * t) << 16);
+        s.sm[1] = (uint32_t)*reinterpret_cast<const uint16_t*>(r1 + 4u + 2u * t) |
+                  ((uint32_t)*reinterpret_cast<const uint16_t*>(r1 + 12u + 2u * t) << 16);
+    }
+};
+
+struct RQ40 : Q40 {
+    static constexpr uint32_t kDataBoxes = 1;
+    __device__ static __forceinline__ uint32_t blk(uint32_t p, uint32_t t) { return 2u * t + p; }
+    __device__ static __forceinline__ void a_pass(const Stage& s, uint32_t p, uint32_t j, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        const uint32_t mask = p ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
+        a0 = word4(s.q[0], j) & mask;
+        a1 = word4(s.q[2], j) & mask;
+        a2 = word4(s.q[1], j) & mask;
+        a3 = word4(s.q[3], j) & mask;
+    }
+    __device__ static __forceinline__ void load_ring(Stage& s, const uint8_t* box, const uint8_t* rec, uint32_t rec8,
+                                                     uint32_t o0, uint32_t o1, uint32_t t) {
+        s.q[0] = *reinterpret_cast<const uint4*>(box + o0);
+        s.q[1] = *reinterpret_cast<const uint4*>(box + o1);
+        s.q[2] = *reinterpret_cast<const uint4*>(box + o0 + 1024u);
+        s.q[3] = *reinterpret_cast<const uint4*>(box + o1 + 1024u);
+        s.dd[0] = *reinterpret_cast<const uint32_t*>(rec + 4u * t);
+        s.dd[1] = *reinterpret_cast<const uint32_t*>(rec + rec8 + 4u * t);
+    }
+};
+
+struct RQ80 : Q80 {
+    static constexpr uint32_t kDataBoxes = 2;  // blocks 0..3 | blocks 4..7 of the unit
+    // pass p of lane t feeds block t + 4p: box p holds blocks 4p..4p+3, chunk 2t its block t's first
+    // 16 bytes (k-slots 4t..), chunk 2t+1 the second 16 (slots 16+4t..)
+    __device__ static __forceinline__ uint32_t blk(uint32_t p, uint32_t t) { return t + 4u * p; }
+    __device__ static __forceinline__ void a_pass(const Stage& s, uint32_t p, uint32_t j, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        a0 = word4(s.q[2u * p], j);
+        a1 = word4(s.q[4u + 2u * p], j);
+        a2 = word4(s.q[2u * p + 1u], j);
+        a3 = word4(s.q[5u + 2u * p], j);
+    }
+    __device__ static __forceinline__ void load_ring(Stage& s, const uint8_t* box, const uint8_t* rec, uint32_t rec8,
+                                                     uint32_t o0, uint32_t o1, uint32_t t) {
+        s.q[0] = *reinterpret_cast<const uint4*>(box + o0);
+        s.q[1] = *reinterpret_cast<const uint4*>(box + o1);
+        s.q[2] = *reinterpret_cast<const uint4*>(box + kBoxBytes + o0);
+        s.q[3] = *reinterpret_cast<const uint4*>(box + kBoxBytes + o1);
+        s.q[4] = *reinterpret_cast<const uint4*>(box + o0 + 1024u);
+        s.q[5] = *reinterpret_cast<const uint4*>(box + o1 + 1024u);
+        s.q[6] = *reinterpret_cast<const uint4*>(box + kBoxBytes + o0 + 1024u);
+        s.q[7] = *reinterpret_cast<const uint4*>(box + kBoxBytes + o1 + 1024u);
+        const uint8_t* r0 = rec + 2u * t;  // f16 d[t] | d[t + 4] << 16
+        s.dd[0] = (uint32_t)*reinterpret_cast<const uint16_t*>(r0) | ((uint32_t)*reinterpret_cast<const uint16_t*>(r0 + 8u) << 16);
+        s.dd[1] = (uint32_t)*reinterpret_cast<const uint16_t*>(r0 + rec8) |
+                  ((uint32_t)*reinterpret_cast<const uint16_t*>(r0 + rec8 + 8u) << 16);
+    }
+};
+
+template <class F>
+__global__ void __launch_bounds__(kMaxWarps * 32u, 1)
+gemv_ring_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant__ CUtensorMap rmap,
+                 const float* __restrict__ bias, const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim,
+                 uint32_t out_dim, const int8_t* __restrict__ xq, const float* __restrict__ xq_scale, const PeerOut peers,
+                 const RingPlan pl, unsigned int* __restrict__ err) {
+    using Stage = typename F::Stage;
+    constexpr uint32_t kUnitData = F::kDataBoxes * kBoxBytes;       // one unit's boxes
+    constexpr uint32_t kRecRow = 2u * F::kRecBytes;                 // a pair's records of one row
+    constexpr uint32_t kStageData = 2u * kUnitData, kStageRec = 16u * kRecRow;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t n_pair = in_dim >> 9;
+    uint8_t* xs_hi = smem;
+    uint8_t* xs_lo = smem + in_dim;
+    uint8_t* zeros = smem + 2u * (size_t)in_dim;
+    float2* xmeta = reinterpret_cast<float2*>(smem + pl.off_xmeta);
+    float* red = reinterpret_cast<float*>(smem + pl.off_red);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + pl.off_bar);  // [W][kMaxDepth]
+    uint64_t* red_full = full + kMaxWarps * kMaxDepth;
+    uint64_t* red_free = red_full + kRedBufs;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(red_free + kRedBufs);
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t W = pl.W, D = pl.D;
+    const uint32_t n_tiles = (out_dim + 15u) >> 4;
+    const uint32_t tile_lo = (uint32_t)((uint64_t)blockIdx.x * n_tiles / gridDim.x);
+    const uint32_t tile_hi = (uint32_t)((uint64_t)(blockIdx.x + 1u) * n_tiles / gridDim.x);
+    const uint32_t my_tiles = tile_hi - tile_lo;
+    // this warp's pairs of a tile: warp, warp + W, ... below n_pair
+    const uint32_t my_pairs = warp < n_pair ? (n_pair - warp + W - 1u) / W : 0u;
+    const uint32_t total = my_tiles * my_pairs;
+
+    uint64_t* my_full = full + warp * kMaxDepth;
+    uint8_t* my_data = smem + pl.off_data + (size_t)warp * D * kStageData;
+    uint8_t* my_rec = smem + pl.off_rec + (size_t)warp * D * kStageRec;
+
+    // (tile, pair) number i of this warp -> stage i % D; issue = arm the barrier, then the copies.
+    // Called by the whole (converged) warp: one elected lane issues, so addresses and the
+    // tensor-map pointers stay in uniform registers.
+    auto issue = [&](uint32_t stage, uint32_t tl, uint32_t pr) {
+        uint64_t* bar = my_full + stage;
+        tc5::mbar_arrive_expect_tx_elect(bar, kStageData + kStageRec);
+        const int32_t row = (int32_t)((tile_lo + tl) * 16u);
+#pragma unroll
+        for (uint32_t b = 0; b < 2u * F::kDataBoxes; ++b)
+            tc5::tma_load_2d_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
+                                   (int32_t)(pr * 2u * F::kDataBytes + b * 128u), row);
+        tc5::tma_load_2d_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(pr * kRecRow), row);
+    };
+
+    // ---- prologue: every warp arms its own barriers and requests its first D stages; only then
+    // does the CTA meet (shared barriers of the tile fold) and wait for the previous kernel
+    if (lane == 0u) {
+        for (uint32_t s = 0; s < D; ++s) tc5::mbar_init(my_full + s, 1u);
+        tc5::mbar_fence_init();
+    }
+    __syncwarp();
+    uint32_t i_tl = 0, i_pr = warp, issued = 0;  // issue cursor
+    auto issue_next = [&]() {
+        issue(issued % D, i_tl, i_pr);
+        ++issued;
+        i_pr += W;
+        if (i_pr >= n_pair) { i_pr = warp; ++i_tl; }
+    };
+    // the first stage of every warp goes out alone: it is what the first iteration waits for, and
+    // it arrives sooner when the chip's first burst is a quarter of the ring
+    if (total > 0u) issue_next();
+    if (tid == 0u) {
+        for (uint32_t b = 0; b < kRedBufs; ++b) {
+            tc5::mbar_init(&red_full[b], W);
+            tc5::mbar_init(&red_free[b], 1u);
+        }
+        *abort_flag = 0;
+        tc5::mbar_fence_init();
+    }
+    // Programmatic dependent launch: the next kernel of the stream may start its prologue (its own
+    // first requests: weights never depend on this kernel) as soon as this one's CTAs have all started.
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();  // x (and y's previous contents) belong to the previous kernel until here
+    const bool invariant = pl.invariant != 0u;
+    if (invariant) {
+        // a warp only ever meets its own pair's 512 activations: it builds their limbs itself
+        const uint32_t off = warp * 512u;
+        act_limbs(x + off, xq ? xq + off : nullptr, xq_scale ? xq_scale + (off >> 5) : nullptr, 512u, xs_hi + off,
+                  xs_lo + off, zeros, xmeta + (off >> 5), lane, 32u);
+        while (issued < D && issued < total) issue_next();
+        __syncthreads();   // the zero line and the fold barriers are shared
+    } else {
+        act_limbs(x, xq, xq_scale, in_dim, xs_hi, xs_lo, zeros, xmeta, tid, W * 32u);
+        while (issued < D && issued < total) issue_next();
+        __syncthreads();
+    }
+    const tc5::WaitCtx ctx{abort_flag, err};
+
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    // B operand of this lane: columns 2b, 2b + 1 are the high and low limb of local block b, so
+    // lane (g, t) feeds limb g & 1 of block blk(p, t) when g >> 1 == t, and zeros otherwise.
+    const bool role = (g >> 1) == t;
+    const uint8_t* my_limb = (g & 1u) ? xs_lo : xs_hi;
+    uint32_t vb[2][2][8];  // [unit of the pair][pass]: words 0..3 -> b0 of mma j, words 4..7 -> b1
+    float4 xm[2];          // per unit: {step, sum} of blocks blk(0, t) and blk(1, t), the two this lane folds
+    auto load_b = [&](uint32_t pr) {
+#pragma unroll
+        for (uint32_t i = 0; i < 2u; ++i) {
+            const uint32_t u = 2u * pr + i;
+#pragma unroll
+            for (uint32_t p = 0; p < 2u; ++p) {
+                const uint8_t* src = role ? my_limb + u * 256u + F::blk(p, t) * 32u : zeros;
+                const uint4 a = *reinterpret_cast<const uint4*>(src);
+                const uint4 b = *reinterpret_cast<const uint4*>(src + 16u);
+                vb[i][p][0] = a.x; vb[i][p][1] = a.y; vb[i][p][2] = a.z; vb[i][p][3] = a.w;
+                vb[i][p][4] = b.x; vb[i][p][5] = b.y; vb[i][p][6] = b.z; vb[i][p][7] = b.w;
+            }
+            const float2 m0 = xmeta[u * 8u + F::blk(0u, t)], m1 = xmeta[u * 8u + F::blk(1u, t)];
+            xm[i] = make_float4(m0.x, m0.y, m1.x, m1.y);
+        }
+    };
+    if (invariant && warp < n_pair) load_b(warp);
+
+    // per-lane offsets inside a stage
+    const uint32_t o0 = swz(g, 2u * t), o1 = swz(g, 2u * t + 1u);
+    const uint32_t rec_g = g * kRecRow, rec8 = 8u * kRecRow;
+
+    // ---- tile fold.  Per tile each warp leaves 16 partial row sums in buffer tl % kRedBufs and
+    // arrives on the buffer's barrier (fire and forget).  The tile belongs to warp tl % W, which
+    // looks at the barrier once per later iteration and, when all W warps have arrived, adds the
+    // partials in warp order, stores y and hands the buffer back; it blocks only before taking on
+    // another tile, and at the end.  A buffer is written again (tile tl + kRedBufs) only after
+    // its fold.
+    constexpr uint32_t kNone = 0xffffffffu;
+    uint32_t pend = kNone;  // local index of the tile this warp still has to fold
+    bool alive = true;
+    auto fold_tile = [&](uint32_t tl_f) {
+        const uint32_t rbf = tl_f % kRedBufs;
+        const float* rbuf = red + (size_t)rbf * (W * 16u);
+        const uint32_t row = (tile_lo + tl_f) * 16u + lane;
+        float v = 0.0f;
+        if (lane < 16u)
+            for (uint32_t w = 0; w < W; ++w) v += rbuf[w * 16u + lane];
+        __syncwarp();
+        if (lane == 0u) tc5::mbar_arrive(&red_free[rbf]);
+        if (lane < 16u && row < out_dim) {
+            if (bias) v += bias[row];
+            if (peers.n == 0u) {
+                y[row] = v;
+            } else {
+#pragma unroll
+                for (uint32_t p = 0; p < 8u; ++p)  // constant indices: the pointers stay in the parameter bank
+                    if (p < peers.n) peers.ptr[p][peers.row0 + row] = v;
+            }
+        }
+    };
+    auto poll_fold = [&](bool block) {
+        if (pend == kNone || !alive) return;
+        const uint32_t rbf = pend % kRedBufs, ph = (pend / kRedBufs) & 1u;
+        bool done;
+        if (block) {
+            alive = __all_sync(0xffffffffu, tc5::mbar_wait(&red_full[rbf], ph, ctx, kErrRingFold, rbf));
+            done = alive;
+        } else {
+            done = __all_sync(0xffffffffu, tc5::mbar_try_wait(&red_full[rbf], ph));
+        }
+        if (done) {
+            fold_tile(pend);
+            pend = kNone;
+        }
+    };
+
+    uint32_t stage = 0, phase = 0;       // consume cursor
+    uint32_t rb = 0, rb_phase = 0, owner = 0;
+    for (uint32_t tl = 0; tl < my_tiles; ++tl) {
+        float acc_g = 0.0f, acc_g8 = 0.0f;
+        for (uint32_t pr = warp; pr < n_pair; pr += W) {
+            if (alive) alive = __all_sync(0xffffffffu, tc5::mbar_wait(my_full + stage, phase, ctx, kErrRingFull, stage));
+            if (alive) {
+                Stage st[2];
+                const uint8_t* sd = my_data + stage * kStageData;
+                const uint8_t* sr = my_rec + stage * kStageRec + rec_g;
+                F::load_ring(st[0], sd, sr, rec8, o0, o1, t);
+                F::load_ring(st[1], sd + kUnitData, sr + F::kRecBytes, rec8, o0, o1, t);
+                if (!invariant) load_b(pr);
+                // four independent accumulator chains: [unit][pass], {hi, lo} of row g, {hi, lo} of row g + 8
+                int c[2][2][4] = {};
+#pragma unroll
+                for (uint32_t j = 0; j < 4u; ++j) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 2u; ++i) {
+#pragma unroll
+                        for (uint32_t p = 0; p < 2u; ++p) {
+                            uint32_t a0, a1, a2, a3;
+                            F::a_pass(st[i], p, j, a0, a1, a2, a3);
+                            if constexpr (F::kUnsignedA) mma_u8s8_nv(c[i][p], a0, a1, a2, a3, vb[i][p][j], vb[i][p][4u + j]);
+                            else mma_s8_nv(c[i][p], a0, a1, a2, a3, vb[i][p][j], vb[i][p][4u + j]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < 2u; ++i) {
+                    float f[4];
+                    f[0] = (float)(c[i][0][0] * 256 + c[i][0][1]) * xm[i].x;
+                    f[1] = (float)((c[i][1][0] * 256 + c[i][1][1]) >> F::kHiShift) * xm[i].z;
+                    f[2] = (float)(c[i][0][2] * 256 + c[i][0][3]) * xm[i].x;
+                    f[3] = (float)((c[i][1][2] * 256 + c[i][1][3]) >> F::kHiShift) * xm[i].z;
+                    F::fold(st[i], f, xm[i].y, xm[i].w, acc_g, acc_g8);
+                }
+                // Every register the stage's loads filled has been consumed by now, so those loads
+                // are complete: the stage can take its next copy.
+                __syncwarp();
+                if (issued < total) issue_next();
+            }
+            if (++stage == D) { stage = 0; phase ^= 1u; }
+        }
+        float a = acc_g, b = acc_g8;
+        a += __shfl_xor_sync(0xffffffffu, a, 1);
+        b += __shfl_xor_sync(0xffffffffu, b, 1);
+        a += __shfl_xor_sync(0xffffffffu, a, 2);
+        b += __shfl_xor_sync(0xffffffffu, b, 2);
+        float* rbuf = red + (size_t)rb * (W * 16u);
+        if (alive && tl >= kRedBufs)
+            alive = __all_sync(0xffffffffu, tc5::mbar_wait(&red_free[rb], rb_phase ^ 1u, ctx, kErrRingFree, rb));
+        if (alive) {
+            if (t == 0u) {
+                rbuf[warp * 16u + g] = a;
+                rbuf[warp * 16u + g + 8u] = b;
+            }
+            __syncwarp();
+            if (lane == 0u) tc5::mbar_arrive(&red_full[rb]);  // release: the partials above are visible to the folding warp
+        }
+        if (owner == warp) {
+            poll_fold(true);   // the previous tile of this warp, if it is still waiting (W tiles ago)
+            pend = tl;
+        }
+        poll_fold(false);
+        if (++owner == W) owner = 0;
+        if (++rb == kRedBufs) { rb = 0; rb_phase ^= 1u; }
+    }
+    poll_fold(true);
+    if (!alive) {
+        // a wait ran out somewhere in the CTA: the copies this warp still has in flight must land
+        // before its shared memory can go to another CTA.  At most D are outstanding, one per stage.
+        const unsigned long long t0 = tc5::globaltimer_ns();
+        for (uint32_t s = 0; s < D && s < issued; ++s) {
+            // the last copy into stage s is number n = the largest n < issued with n % D == s
+            const uint32_t n = issued - 1u - ((issued - 1u - s) % D);
+            while (!tc5::mbar_try_wait(my_full + s, (n / D) & 1u)) {
+                if (tc5::globaltimer_ns() - t0 > tc5::kWaitBudgetNs) {
+                    if (lane == 0u) tc5::report(err, kErrRingDrain, s);
+                    break;
+                }
+            }
+        }
+    }
+}
+
+template <class F>
+bool make_plan(uint32_t in_dim, RingPlan& best) {
+    if (in_dim == 0u || (in_dim & 511u) != 0u) return false;  // whole pairs of units
+    const uint32_t n_pair = in_dim >> 9;
+    if (n_pair < 4u) return false;
+    constexpr uint32_t kStage = 2u * F::kDataBoxes * kBoxBytes + 32u * F::kRecBytes;
+    double best_cost = 1e30;
+    bool found = false;
+    for (uint32_t W = kMaxWarps; W >= 4u; --W) {
+        RingPlan p{};
+        p.W = W;
+        const uint32_t rounds = (n_pair + W - 1u) / W;
+        p.invariant = (W == n_pair) ? 1u : 0u;
+        p.off_xmeta = (2u * in_dim + 32u + 15u) & ~15u;
+        p.off_red = p.off_xmeta + (in_dim >> 5) * 8u;
+        p.off_bar = p.off_red + kRedBufs * W * 64u;
+        p.off_rec = (p.off_bar + (kMaxWarps * kMaxDepth + 2u * kRedBufs) * 8u + 16u + 127u) & ~127u;
+        const uint32_t fixed = p.off_rec;
+        if (fixed + 1024u + 2u * W * kStage > kSmemMax) continue;
+        p.D = (kSmemMax - fixed - 1024u) / (W * kStage);
+        if (p.D > kMaxDepth) p.D = kMaxDepth;
+        p.off_data = (p.off_rec + W * p.D * 32u * F::kRecBytes + 1023u) & ~1023u;  // swizzled boxes start on 1 KB
+        p.smem_bytes = p.off_data + W * p.D * 2u * F::kDataBoxes * kBoxBytes;
+        if (p.smem_bytes > kSmemMax) continue;
+        double cost = (double)(rounds * W) / (double)n_pair;   // idle warps in a tile's last round
+        if (p.D < 3u) cost += 0.04 * (3u - p.D);
+        if (W < 8u) cost += 0.03 * (8u - W);
+        cost -= 1e-9 * (double)(W * p.D * kStage);            // ties: more bytes in flight
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = p;
+            found = true;
+        }
+    }
+    return found;
+}
+
+// PDK_GEMV_REGS=1 sends every call to the register-staged kernel (A/B switch, read once).
+bool force_regs() {
+    static const bool v = [] {
+        const char* e = getenv("PDK_GEMV_REGS");
+        return e && e[0] == '1';
+    }();
+    return v;
+}
+
+// Tensor maps of the planes a thread used last (weights stay where they are, so a decode loop
+// encodes each plane's maps once): [rows][row bytes] uint8, data boxes 128 x 16 swizzled, record
+// boxes of a unit pair's records x 16 dense.
+struct MapEntry {
+    const void *data, *recs;
+    uint32_t in_dim, out_dim, rec_box;
+    CUtensorMap dmap, rmap;
+};
+template <class F>
+int plane_maps(const void* data, const void* recs, uint32_t in_dim, uint32_t out_dim, const MapEntry** out) {
+    constexpr int kEntries = 16;
+    thread_local MapEntry cache[kEntries];
+    thread_local int next = 0, used = 0;
+    for (int i = 0; i < used; ++i) {
+        const MapEntry& e = cache[i];
+        if (e.data == data && e.recs == recs && e.in_dim == in_dim && e.out_dim == out_dim && e.rec_box == 2u * F::kRecBytes) {
+            *out = &e;
+            return 0;
+        }
+    }
+    MapEntry& e = cache[next];
+    const uint32_t n_unit = in_dim >> 8;
+    int rc = pdk_make_tmap_2d(&e.dmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1u, data, (uint64_t)n_unit * F::kDataBytes, out_dim,
+                              (uint64_t)n_unit * F::kDataBytes, 128u, 16u);
+    if (rc == 0)
+        rc = pdk_make_tmap_2d_dense(&e.rmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1u, recs, (uint64_t)n_unit * F::kRecBytes,
+                                    out_dim, (uint64_t)n_unit * F::kRecBytes, 2u * F::kRecBytes, 16u);
+    if (rc != 0) {
+        e.data = nullptr;
+        return rc;
+    }
+    e.data = data; e.recs = recs; e.in_dim = in_dim; e.out_dim = out_dim; e.rec_box = 2u * F::kRecBytes;
+    *out = &e;
+    next = (next + 1) % kEntries;
+    if (used < kEntries) ++used;
+    return 0;
+}
+
+template <class F>
+int launch_ring(const void* data, const void* recs, const float* bias, const float* x, float* y, uint32_t in_dim,
+                uint32_t out_dim, cudaStream_t st, const int8_t* xq = nullptr, const float* xq_scale = nullptr,
+                const PeerOut* peers = nullptr) {
+    if (force_regs() || !pdk_aligned(recs, 16)) return -1;  // tensor maps start on 16 bytes
+    RingPlan pl;
+    if (!make_plan<F>(in_dim, pl)) return -1;
+    const MapEntry* maps = nullptr;
+    if (plane_maps<F>(data, recs, in_dim, out_dim, &maps) != 0) return -1;
+    auto kern = gemv_ring_kernel<F>;
+    static bool attr_set[64] = {false};  // per device, per format (one instance of this function per F)
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax);
+        if (e != cudaSuccess) return (int)e;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    unsigned int* err = pdk_error_word();
+    if (err == nullptr) return (int)cudaErrorUnknown;
+    const uint32_t n_tiles = (out_dim + 15u) / 16u;
+    uint32_t grid = (uint32_t)pdk_sm_count();
+    if (grid > n_tiles) grid = n_tiles;
+    PeerOut po{};
+    if (peers) po = *peers;
+    return pdk_launch_pdl(kern, dim3(grid), dim3(pl.W * 32u), (size_t)pl.smem_bytes, st, maps->dmap, maps->rmap, bias, x, y,
+                          in_dim, out_dim, xq, xq_scale, po, pl, err);
+}
+
+}  // namespace
+
+// gemv_i8.cu: the register-staged kernel
+int pdk_q4k_gemv_i8_regs(const void*, const void*, const float*, float*, uint32_t, uint32_t, cudaStream_t);
+int pdk_q4_0_gemv_i8_regs(const void*, const void*, const float*, float*, uint32_t, uint32_t, cudaStream_t);
+int pdk_q5k_gemv_i8_regs(const void*, const void*, const float*, float*, uint32_t, uint32_t, cudaStream_t);
+int pdk_q8_0_gemv_i8_regs(const void*, const void*, const float*, const float*, float*, uint32_t, uint32_t, cudaStream_t);
+int pdk_q4k_gemv_i8_q8act_regs(const void*, const void*, const int8_t*, const float*, float*, uint32_t, uint32_t,
+                               cudaStream_t);
+int pdk_q4k_gemv_peers_regs(const void*, const void*, const float*, const gemv_i8::PeerOut*, uint32_t, uint32_t,
+                            cudaStream_t);
+
+// Decode GEMV entry points of the int8 tensor path.  Each returns 0 / a cudaError_t, or -1 when the
+// shape is outside both kernels' plans (K not a multiple of 256, fewer than four units per row, or
+// activations too long for shared memory) and the caller should take another route.  The ring
+// kernel takes K >= 2048 (even super-block counts for the formats with 24-byte records); the
+// register-staged kernel takes the rest, and Q5_K.
+int pdk_q4k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                    uint32_t out_dim, cudaStream_t st) {
+    const int rc = launch_ring<RQ4K>(data, scales, nullptr, x, y, in_dim, out_dim, st);
+    return rc != -1 ? rc : pdk_q4k_gemv_i8_regs(data, scales, x, y, in_dim, out_dim, st);
+}
+
+int pdk_q4_0_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                     uint32_t out_dim, cudaStream_t st) {
+    const int rc = launch_ring<RQ40>(data, scales, nullptr, x, y, in_dim, out_dim, st);
+    return rc != -1 ? rc : pdk_q4_0_gemv_i8_regs(data, scales, x, y, in_dim, out_dim, st);
+}
+
+int pdk_q5k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
+                    uint32_t out_dim, cudaStream_t st) {
+    return pdk_q5k_gemv_i8_regs(data, scales, x, y, in_dim, out_dim, st);
+}
+
+int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, const float* x, float* y,
+                     uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
+    const int rc = launch_ring<RQ80>(data, scale, bias, x, y, in_dim, out_dim, st);
+    return rc != -1 ? rc : pdk_q8_0_gemv_i8_regs(data, scale, bias, x, y, in_dim, out_dim, st);
+}
+
+// Q4_K GEMV on int8 activations (xq int8 [in_dim], one f32 scale per 32): same kernels, the
+// activation staging widens q * scale before it builds its limbs.
+int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq, const float* xq_scale, float* y,
+                          uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
+    const int rc = launch_ring<RQ4K>(data, scales, nullptr, nullptr, y, in_dim, out_dim, st, xq, xq_scale);
+    return rc != -1 ? rc : pdk_q4k_gemv_i8_q8act_regs(data, scales, xq, xq_scale, y, in_dim, out_dim, st);
+}
+
+// No counterpart in the reference (its multi-GPU story is one process per GPU, replicas only):
+// Q4_K decode GEMV of one rank's row band that writes its band straight into every rank's
+// full-length y (y_ptrs[0..n_ranks), device pointers valid on this GPU: its own buffer and the
+// peers' buffers mapped over NVLink) at rows row0 .. row0 + out_dim.  The exchange that an
+// all-gather would do is the kernel's own stores.  The stores are complete when the kernel
+// is; the caller orders consumers after it (stream order locally, a barrier or flag across
+// ranks).  n_ranks <= 8.  Returns 801 for shapes outside the GEMV kernels' plans.
+PDK_EXPORT int pdk_q4k_gemv_shard(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
+                                  uint32_t n_ranks, uint32_t row0, uint32_t in_dim, uint32_t out_dim, void* stream) {
+    if (out_dim == 0) return 0;
+    if (n_ranks == 0 || n_ranks > 8u || y_ptrs == nullptr) return cudaErrorInvalidValue;
+    if (!pdk_aligned(data, 16) || !pdk_aligned(scales, 8) || !pdk_aligned(x, 16)) return cudaErrorInvalidValue;
+    gemv_i8::PeerOut po{};
+    for (uint32_t p = 0; p < n_ranks; ++p) {
+        if (y_ptrs[p] == nullptr || !pdk_aligned(y_ptrs[p], 4)) return cudaErrorInvalidValue;
+        po.ptr[p] = (float*)y_ptrs[p];
+    }
+    po.n = n_ranks;
+    po.row0 = row0;
+    int rc = launch_ring<RQ4K>(data, scales, nullptr, (const float*)x, nullptr, in_dim, out_dim, (cudaStream_t)stream,
+                               nullptr, nullptr, &po);
+    if (rc == -1) rc = pdk_q4k_gemv_peers_regs(data, scales, (const float*)x, &po, in_dim, out_dim, (cudaStream_t)stream);
+    return rc >= 0 ? rc : (int)cudaErrorNotSupported;
+}

@@ -651,7 +651,12 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
         }
         if (rc > 0) return rc;
         if (b == batch) return 0;
-        if (b != 0) return cudaErrorNotSupported;  // cannot happen: the plan depends on the shape alone
+        // -1: the shape is outside the kernel's plan, or this stream has no scratch slice (both hold for
+        // the whole call, so b is 0 here unless slices were released meanwhile): the routes below
+        // take what is left
+        x = (const float*)x + (size_t)b * in_dim;
+        y = (float*)y + (size_t)b * out_dim;
+        batch -= b;
     }
     if (dtype != PDK_KQ_Q4K && !force_plain() && pdk_aligned(data, 16)) {
         // Q5_K / Q6_K (and Q4_0 below four tokens) have no batch kernel on the tensor path yet: one decode GEMV per token
@@ -661,7 +666,7 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
         for (uint32_t b = 0; b < batch && rc == 0; ++b)
             rc = more_gemv_i8(data, scales, (const float*)x + (size_t)b * in_dim, (float*)y + (size_t)b * out_dim, in_dim,
                               out_dim, dtype, (cudaStream_t)stream);
-        if (rc != -1) return rc;  // -1 can only come from the first call: the plan depends on the shape alone
+        if (rc != -1) return rc;  // -1 comes from the first call (the plan depends on the shape alone): nothing is done yet
     }
     if (dtype != PDK_KQ_Q4K)
         return pdk_kq_more_gemm(data, scales, (const float*)x, (float*)y, in_dim, out_dim, batch, dtype,
@@ -722,7 +727,11 @@ int w4a8_gemm(const void* data, const void* scales, const void* xq, const void* 
                                      out_dim, batch, st);
         if (done < 0) return -done - 1;
         if ((uint32_t)done == batch) return 0;
-        if (done != 0) return cudaErrorNotSupported;  // cannot happen: the plans depend on in_dim only
+        // outside both plans, or no scratch slice for this stream: the widening route takes what is left
+        xq = (const int8_t*)xq + (size_t)done * in_dim;
+        xs = (const float*)xs + (size_t)done * (in_dim >> 5);
+        y = (float*)y + (size_t)done * out_dim;
+        batch -= (uint32_t)done;
     }
     // the batch kernels take f32 activations: widen q * scale into the caller's partial
     // buffer (>= 8 * out_dim * batch floats by the slot's contract)

@@ -736,20 +736,8 @@ constexpr size_t kGemvSlice = ((kGemvXq + 32u * (kGemvMaxK / 2u)) + 1023u) & ~(s
 constexpr int kGemvLanes = 2;
 __device__ __align__(1024) uint8_t g_gemv_scratch[kGemvLanes][kGemvSlice];
 
-uint8_t* gemv_slice(cudaStream_t st) {
-    static uint8_t* base = [] {
-        void* p = nullptr;
-        return cudaGetSymbolAddress(&p, g_gemv_scratch) == cudaSuccess ? (uint8_t*)p : (uint8_t*)nullptr;
-    }();
-    static cudaStream_t owner[kGemvLanes];
-    static int n_owner = 0;
-    if (base == nullptr) return nullptr;
-    for (int i = 0; i < n_owner; ++i)
-        if (owner[i] == st) return base + (size_t)i * kGemvSlice;
-    if (n_owner == kGemvLanes) return nullptr;
-    owner[n_owner] = st;
-    return base + (size_t)(n_owner++) * kGemvSlice;
-}
+PDK_SLICE_TABLE(gemv_slice_table, g_gemv_scratch, kGemvSlice, kGemvLanes);
+uint8_t* gemv_slice(cudaStream_t st) { return gemv_slice_table.slice(st); }
 }  // namespace
 
 // 0 / cudaError_t, or -1 when the route does not apply (in_dim not a multiple of 64 or above 16384,

@@ -325,19 +325,10 @@ constexpr size_t kXsfSliceBytes = 8u << 20;  // batch * in_dim / 16 bytes, padde
 constexpr int kXsfLanes = 2;
 __device__ __align__(1024) uint8_t g_xsf_scratch[kXsfLanes][kXsfSliceBytes];
 
+PDK_SLICE_TABLE(xsf_slice_table, g_xsf_scratch, kXsfSliceBytes, kXsfLanes);
 uint8_t* xsf_slice(cudaStream_t st, size_t need) {
-    static uint8_t* base = [] {
-        void* p = nullptr;
-        return cudaGetSymbolAddress(&p, g_xsf_scratch) == cudaSuccess ? (uint8_t*)p : (uint8_t*)nullptr;
-    }();
-    static cudaStream_t owner[kXsfLanes];
-    static int n_owner = 0;
-    if (base == nullptr || need > kXsfSliceBytes) return nullptr;
-    for (int i = 0; i < n_owner; ++i)
-        if (owner[i] == st) return base + (size_t)i * kXsfSliceBytes;
-    if (n_owner == kXsfLanes) return nullptr;
-    owner[n_owner] = st;
-    return base + (size_t)(n_owner++) * kXsfSliceBytes;
+    if (need > kXsfSliceBytes) return nullptr;
+    return xsf_slice_table.slice(st);
 }
 
 template <typename TO>

@@ -75,6 +75,35 @@ __device__ __forceinline__ uint32_t pdk_and_or(uint32_t a, uint32_t m, uint32_t 
     return d;
 }
 
+// ---------------------------------------------------------------------------
+// Library-resident scratch, one slice per (device, stream).
+//
+// A few launchers keep per-call scratch in `static __device__` arrays (the pack allocates
+// nothing).  Calls on different streams can overlap on the GPU, so every (device, stream) pair
+// that makes such a call gets a slice of its own, up to the array's lane count per device;
+// further streams get nullptr and the caller takes its scratch-free route.  The table is shared
+// by host threads (a mutex guards it), the array's device address is resolved per device, and
+// pdk_stream_release() gives the slices of a stream that is about to be destroyed back.
+// ---------------------------------------------------------------------------
+struct PdkSliceTable {
+    static constexpr int kMaxDev = 64, kMaxLanes = 4;
+    void* (*resolve)();        // device address of the array on the current device, or nullptr
+    size_t slice_bytes;
+    int lanes;                 // <= kMaxLanes
+    uint8_t* base[kMaxDev];
+    cudaStream_t owner[kMaxDev][kMaxLanes];
+    bool used[kMaxDev][kMaxLanes];
+    PdkSliceTable* next;       // registry walked by pdk_stream_release
+    PdkSliceTable(void* (*r)(), size_t bytes, int n);
+    uint8_t* slice(cudaStream_t st);
+};
+#define PDK_SLICE_TABLE(name, symbol, bytes, n)                                             \
+    static void* name##_resolve() {                                                         \
+        void* p = nullptr;                                                                  \
+        return cudaGetSymbolAddress(&p, symbol) == cudaSuccess ? p : nullptr;               \
+    }                                                                                       \
+    static PdkSliceTable name(name##_resolve, bytes, n)
+
 __device__ __forceinline__ uint2 pdk_ldg_stream8(const void* p) {
     uint2 r;
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));

@@ -358,20 +358,8 @@ constexpr size_t kImgSliceBytes = 232448;  // the largest image a CTA's shared m
 constexpr int kImgLanes = 2;
 __device__ __align__(1024) uint8_t g_q4k_img[kImgLanes][kImgSliceBytes];
 
-uint8_t* img_slice(cudaStream_t st) {
-    static uint8_t* base = [] {
-        void* p = nullptr;
-        return cudaGetSymbolAddress(&p, g_q4k_img) == cudaSuccess ? (uint8_t*)p : (uint8_t*)nullptr;
-    }();
-    static cudaStream_t owner[kImgLanes];
-    static int n_owner = 0;
-    if (base == nullptr) return nullptr;
-    for (int i = 0; i < n_owner; ++i)
-        if (owner[i] == st) return base + (size_t)i * kImgSliceBytes;
-    if (n_owner == kImgLanes) return nullptr;
-    owner[n_owner] = st;
-    return base + (size_t)(n_owner++) * kImgSliceBytes;
-}
+PDK_SLICE_TABLE(img_slice_table, g_q4k_img, kImgSliceBytes, kImgLanes);
+uint8_t* img_slice(cudaStream_t st) { return img_slice_table.slice(st); }
 
 template <uint32_t NT, uint32_t DEPTH, bool EARLY>
 int launch(const void* data, const void* recs, const float* x, const int8_t* xq, const float* xq_scale, float* y,

@@ -551,20 +551,8 @@ constexpr size_t kSliceBytes = kXhBytes + 1024u;
 constexpr int kLanes = 2;
 __device__ __align__(1024) uint8_t g_q4k_xh[kLanes][kSliceBytes];
 
-uint8_t* xh_slice(cudaStream_t st) {
-    static uint8_t* base = [] {
-        void* p = nullptr;
-        return cudaGetSymbolAddress(&p, g_q4k_xh) == cudaSuccess ? (uint8_t*)p : (uint8_t*)nullptr;
-    }();
-    static cudaStream_t owner[kLanes];
-    static int n_owner = 0;
-    if (base == nullptr) return nullptr;
-    for (int i = 0; i < n_owner; ++i)
-        if (owner[i] == st) return base + (size_t)i * kSliceBytes;
-    if (n_owner == kLanes) return nullptr;
-    owner[n_owner] = st;
-    return base + (size_t)(n_owner++) * kSliceBytes;
-}
+PDK_SLICE_TABLE(xh_slice_table, g_q4k_xh, kSliceBytes, kLanes);
+uint8_t* xh_slice(cudaStream_t st) { return xh_slice_table.slice(st); }
 
 template <uint32_t NC, bool Q40>
 int launch(const void* data, const void* recs, const float* x, const int8_t* xq, const float* xq_scale, float* y,

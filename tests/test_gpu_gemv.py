@@ -99,6 +99,62 @@ def test_q4_k_gemv_shapes(pack, k, n):
     assert rel_l2(y, ref[0]) < 1e-4 < TOL
 
 
+# Shapes chosen for the ring-staged decode GEMV's plans: 8 units per row (the smallest it takes),
+# stages that do not divide the row (18, 22, 68, 108 units), an odd unit count (43: the ring
+# kernel declines Q4_K's 24-byte records there and the register-staged kernel runs), fewer than 16
+# rows, a last tile of one row, and more tiles than SMs so that the ring wraps many times.
+RING_SHAPES = [(2048, 7), (2048, 4099), (4608, 33), (5632, 100), (11008, 49), (17408, 161), (27648, 40), (4096, 16 * 148 * 3 + 1)]
+
+
+@pytest.mark.parametrize("k,n", RING_SHAPES)
+def test_q4_k_gemv_ring_plans(pack, k, n):
+    w = oracle.fill_normal(n * k, seed_for(2, 7 * k + n), 0.02)
+    x = bf16_activations(k, seed_for(2, 3))
+    raw, d_data, d_sc = q4k_planes(pack, w, n, k)
+    d_y = torch.full((n + 8,), 7.0, dtype=torch.float32, device="cuda")
+    pack.call("kquant_gemv", d_data, d_sc, dev_f32(x), d_y, k, n, 12)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    ref, ab = oracle.matmul_f64(oracle.dequant_q4_k(raw), x, k, n, 1, with_abs=True)
+    y = d_y.cpu().numpy()
+    assert (y[n:] == 7.0).all()          # nothing written past the last row
+    assert cond_err(y[:n], ref[0], ab[0]) < 1e-5
+    assert rel_l2(y[:n], ref[0]) < 1e-4 < TOL
+
+
+@pytest.mark.parametrize("k,n", RING_SHAPES)
+def test_q8_0_gemv_ring_plans(pack, k, n):
+    w = oracle.fill_normal(n * k, seed_for(0, 7 * k + n), 0.02)
+    x = bf16_activations(k, seed_for(0, 3))
+    raw, d_data, d_scale = q8_planes(pack, w, n, k)
+    bias = oracle.fill_normal(n, 9, 0.1)
+    d_y = torch.full((n + 8,), 7.0, dtype=torch.float32, device="cuda")
+    pack.call("q8_0_gemv_repacked", d_data, d_scale, dev_f32(bias), dev_f32(x), d_y, k, n)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    ref, ab = oracle.matmul_f64(oracle.dequant_q8_0(raw), x, k, n, 1, with_abs=True)
+    y = d_y.cpu().numpy()
+    assert (y[n:] == 7.0).all()
+    assert cond_err(y[:n] - bias, ref[0], ab[0]) < 1e-5
+    assert rel_l2(y[:n] - bias, ref[0]) < 1e-4 < TOL
+
+
+def test_gemv_ring_back_to_back_is_deterministic(pack):
+    """Twenty dependent launches in a row (each starts its ring fill while its predecessor drains)
+    leave bit-identical results."""
+    k, n = 5120, 4000
+    w = oracle.fill_normal(n * k, seed_for(2, 77), 0.02)
+    x = dev_f32(bf16_activations(k, seed_for(2, 78)))
+    raw, d_data, d_sc = q4k_planes(pack, w, n, k)
+    ys = [torch.zeros(n, dtype=torch.float32, device="cuda") for _ in range(20)]
+    for y in ys:
+        pack.call("kquant_gemv", d_data, d_sc, x, y, k, n, 12)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    for y in ys[1:]:
+        assert torch.equal(y, ys[0])
+
+
 @pytest.mark.parametrize("batch", [1, 4, 16])
 def test_q4_k_small_batch_config2_band(pack, batch):
     """BASELINE config 2 (K=5120, M in {1,4,16}) on a 1536-row band of N=25600."""
@@ -292,3 +348,40 @@ def test_q4k_gemv_shard_stores_band_into_every_output(pack):
         assert torch.equal(o[row0:row0 + n], d_ref)
         assert bool((o[:row0] == -1.0).all()) and bool((o[row0 + n:] == -1.0).all())
     assert pack.status("pdk_q4k_gemv_shard", d_data, d_sc, x, ctypes.addressof(ptrs), 9, row0, k, n) == 1
+
+
+def test_small_batch_scratch_is_per_stream(pack):
+    """The small-batch Q4_K GEMM keeps its activation image in library scratch, one slice per
+    (device, stream), two streams per device.  Three streams: the first two get slices, the third
+    takes the scratch-free route (same results within its own precision class); releasing a
+    stream hands its slice to the next newcomer."""
+    k, n, batch = 2048, 300, 4
+    w = oracle.fill_normal(n * k, seed_for(2, 900), 0.02)
+    x = bf16_activations(batch * k, seed_for(2, 901))
+    raw, d_data, d_sc = q4k_planes(pack, w, n, k)
+    ref, ab = oracle.matmul_f64(oracle.dequant_q4_k(raw), x, k, n, batch, with_abs=True)
+    d_x = dev_f32(x)
+    import ctypes
+    rel = pack._lib.pdk_stream_release
+    rel.argtypes, rel.restype = [ctypes.c_void_p], None
+    streams = [torch.cuda.Stream() for _ in range(3)]
+    outs = []
+    torch.cuda.synchronize()
+    rel(torch.cuda.current_stream().cuda_stream)    # earlier tests ran this route on the default stream
+    for st in streams:
+        y = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+        pack.call("pdk_kquant_gemm_f32", d_data, d_sc, d_x, y, k, n, batch, 12, stream=st.cuda_stream)
+        outs.append(y)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    for y in outs:
+        got = y.cpu().numpy().reshape(batch, n)
+        assert cond_err(got, ref, ab) < 1e-4 and rel_l2(got, ref) < 1e-3 < TOL
+    assert torch.equal(outs[0], outs[1])            # both on the integer tensor path
+    rel(streams[0].cuda_stream)
+    y3 = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+    pack.call("pdk_kquant_gemm_f32", d_data, d_sc, d_x, y3, k, n, batch, 12, stream=streams[2].cuda_stream)
+    torch.cuda.synchronize()
+    assert torch.equal(y3, outs[0])                 # the third stream now runs the scratch route too
+    for st in streams[1:]:
+        rel(st.cuda_stream)
