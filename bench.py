@@ -3,8 +3,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One "step" is one decode GEMV of BASELINE config 2 (Q4_K, M=1, K=5120,
-N=25600) through the kernel-pack C ABI.  Prints ONE JSON line:
+One "step" is one Q4_K decode GEMV (M=1, K=5120, N=25600) through the
+kernel-pack C ABI.  Prints ONE JSON line:
 
   value     weight GB/s = algorithmic bytes per step / device time per step,
             planes resident in HBM, cold L2 (the plane is cloned so that
@@ -15,7 +15,12 @@ N=25600) through the kernel-pack C ABI.  Prints ONE JSON line:
   roofline  achieved GB/s of the GEMV kernel (per-launch CUDA events) against
             the measured HBM copy bandwidth;
   cpu_baseline  the reference's CPU path (dequant + scalar f32 matvec), ported
-            in oracle/, timed on this host's cores.
+            in oracle/, timed on this host's cores;
+  configs   at N = 1, after the headline region: one record per further
+            benchmark shape (Q8_0 GEMV, Q4_K at 4 / 16 tokens, FP8 and NVFP4
+            GEMMs, the MXFP4 MoE block), each with its time, achieved GB/s or
+            TFLOP/s, the fraction of the named denominator and a spot check of
+            the result against an f32 product of the decoded operands.
 
 With --gpus N > 1 (launched under torchrun) the N rows are sharded across the
 ranks and the outputs are all-gathered with NCCL (strong scaling).
@@ -36,8 +41,9 @@ K_DIM = 5120
 N_DIM = 25600
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the GEMV kernel, from
-# the ncu capture summarized in profiles/q4k_gemv_i8_config2_m1.md (scaled by rows when sharded)
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch of the GEMV kernel from an
+# ncu capture (scaled by rows when sharded): the planes as laid out in HBM (152 bytes per 256
+# weights, of which 144 are the format's) plus y
 NCU_TRAFFIC_BYTES = 79_560_000
 
 
@@ -183,11 +189,13 @@ def run_reference(args, rank):
     if rank != 0:
         return
     steps = min(args.steps, 20)
-    warm = min(args.warmup, 2)
-    gbs, cores, sample, ms = cpu_baseline(steps, max(warm, 1))
+    warm = max(args.warmup, 3)
+    rows = N_DIM // 4
+    gbs, cores, sample, ms = cpu_baseline(steps, warm, rows)
     line = {
         "impl": "reference", "metric": "q4k_gemv_weight_gbs", "value": gbs, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": max(warm, 1), "ms_per_step": ms,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": ms * (N_DIM / rows),
+        "ms_per_sample_pass": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(args.gpus, args.exchange),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
@@ -200,9 +208,48 @@ def run_reference(args, rank):
 def workload_config(n_gpus, exchange="peer"):
     how = ("each rank's GEMV stores its band into every rank's y over NVLink (peer memory)" if exchange == "peer"
            else "NCCL all-gather of y")
-    return {"workload": "Q4_K decode GEMV M=1 K=5120 N=25600 (BASELINE config 2), f32 activations holding bf16 values",
+    return {"workload": "Q4_K decode GEMV M=1 K=5120 N=25600, f32 activations holding bf16 values",
             "sharding": "none" if n_gpus == 1 else f"N rows / {n_gpus} ranks, {how}",
             "l2": "cold: steps rotate over weight-plane clones totalling > 2x the 126 MB L2"}
+
+
+def other_configs(ex, quick):
+    """One record per further benchmark shape, timed after the headline region (N = 1 only).
+    Each is kbench's case for the shape: CUDA-event time, cold L2 for the memory-bound ones, and a
+    spot check of the result against an f32 product of the decoded operands."""
+    import gc
+    import torch
+    import kbench
+    it = 10 if quick else 30
+    cases = [("q8_0_gemv_n17408", kbench.Case("q8_gemv", graph=True, iters=it)),
+             ("q4k_m4_n25600", kbench.Case("q4k_gemv", m=4, graph=True, iters=it)),
+             ("q4k_m16_n25600", kbench.Case("q4k_gemv", m=16, graph=True, iters=it))]
+    cases += [(f"fp8_m4096_n{n}", kbench.Case("f8row_gemm", m=4096, n=n, iters=max(5, it // 3))) for n in (5120, 17408, 27648)]
+    cases += [(f"nvf4_m{m}_n17408", kbench.Case("nvf4_gemm", m=m, iters=it if m <= 512 else max(5, it // 3)))
+              for m in (1, 8, 64, 512, 8192)]
+    cases += [(f"moe_mxfp4_t{t}", kbench.Case("moe_mxfp4", m=t, graph=(t == 1), iters=it if t <= 64 else max(5, it // 3)))
+              for t in (1, 64, 1024)]
+    out = {}
+    for name, case in cases:
+        try:
+            r = kbench.run_case(ex, case)
+            rec = {"us": r["us"], "parity_ok": r.get("parity_ok"), "parity_rel_l2": r.get("parity_rel_l2"),
+                   "device_error": r["device_error"]}
+            if case.op == "f8row_gemm":
+                rec.update(achieved=r["tflops"], unit="TFLOP/s", frac=r["frac_of_2x_bf16"], denominator="2 x measured bf16 burst")
+            elif case.op == "nvf4_gemm" and case.m >= 512:
+                rec.update(achieved=r["tflops"], unit="TFLOP/s", frac=r["frac_of_4x_bf16"], denominator="4 x measured bf16 burst",
+                           gbs=r["gbs"], frac_of_hbm=r["frac_of_hbm"])
+            else:
+                rec.update(achieved=r["gbs"], unit="GB/s", frac=r["frac_of_hbm"], denominator="measured HBM copy")
+            if "distinct_experts" in r:
+                rec["distinct_experts"] = r["distinct_experts"]
+            out[name] = rec
+        except Exception as err:                 # a failing case must not lose the headline line
+            out[name] = {"error": str(err)[:200]}
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
 
 
 def run_ours(args, rank, world, local_rank):
@@ -447,6 +494,10 @@ def run_ours(args, rank, world, local_rank):
         if world == 1:
             gbs, cores, sample, _ = cpu_baseline(3, 1)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+            if args.configs:
+                del planes, bound
+                torch.cuda.empty_cache()
+                line["configs"] = other_configs(ex, quick=args.steps < 50)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -460,6 +511,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="time K direct launches instead of one replay of a CUDA graph holding them")
+    ap.add_argument("--no-configs", dest="configs", action="store_false",
+                    help="N = 1: skip the records of the other benchmark shapes")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the row bands of y reach every rank")
     args = ap.parse_args()

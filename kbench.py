@@ -65,6 +65,13 @@ def time_launches(fn, iters, warmup=5):
     return e0.elapsed_time(e1) / iters * 1e-3
 
 
+def rel_err(got, ref):
+    """rel-L2 of a device result against a device reference (one host read)."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ref = ref.float()
+    return float((got.float() - ref).norm() / ref.norm().clamp_min(1e-30))
+
+
 def clones_for(nbytes):
     return max(2, -(-2 * L2_BYTES // max(nbytes, 1)) + 1)
 
@@ -117,7 +124,12 @@ def bench_q4k(ex, a):
     else:
         sec = time_launches(lambda i: ex.kquant_gemm_f32(planes[i % len(planes)], x, y, m), a.iters)
     nbytes = n * k // 256 * 144 + m * k * 2 + m * n * 4
-    return sec, {"bound": "hbm", "bytes": nbytes}
+    # spot check: the last call's first rows against an f32 product of the dequantized plane
+    rows = min(n, 512)
+    wd = torch.empty(rows * k, dtype=torch.float32, device="cuda")
+    ex.pack.call("kquant_dequant", raw, wd, rows * k // 256, 12, stream=torch.cuda.current_stream().cuda_stream)
+    err = rel_err(y.view(m, n)[:, :rows], x.view(m, k) @ wd.view(rows, k).t())
+    return sec, {"bound": "hbm", "bytes": nbytes, "parity_rel_l2": err, "parity_ok": err < 1e-3}
 
 
 def bench_q4k_w4a8(ex, a):
@@ -185,7 +197,12 @@ def bench_q8(ex, a):
         sec = time_launches(lambda i: ex.q8_0_gemv_repacked(planes[i % len(planes)], None, x, y), a.iters)
     else:
         sec = time_launches(lambda i: ex.q8_0_gemm_repacked(planes[i % len(planes)], None, x, y, m), a.iters)
-    return sec, {"bound": "hbm", "bytes": n * k // 32 * 34 + m * k * 2 + m * n * 4}
+    rows = min(n, 512)
+    p = planes[(a.iters - 1) % len(planes)] if not GRAPH_REPLAY else planes[(a.iters - 1) % len(planes)]
+    wd = p.data.view(n, k // 32, 32)[:rows].float() * p.scale.view(n, k // 32, 1)[:rows].float()
+    err = rel_err(y.view(m, n)[:, :rows], x.view(m, k) @ wd.reshape(rows, k).t())
+    return sec, {"bound": "hbm", "bytes": n * k // 32 * 34 + m * k * 2 + m * n * 4, "parity_rel_l2": err,
+                 "parity_ok": err < 1e-3}
 
 
 def bench_f8(ex, a):
@@ -198,7 +215,13 @@ def bench_f8(ex, a):
     name = "pdk_f8row_gemm_bf16" if a.out == "bf16" else "f8row_gemm"
     st = torch.cuda.current_stream().cuda_stream
     sec = time_launches(lambda i: ex.pack.call(name, w, ws, xq, xs, y, k, n, m, stream=st), a.iters)
-    return sec, {"bound": "tensor", "flops": 2.0 * m * n * k}
+    # spot check: a corner of y against an f32 product of the decoded operands
+    rows, toks = min(n, 384), min(m, 96)
+    wd = w.view(n, k)[:rows].view(torch.float8_e4m3fn).float() * ws[:rows, None]
+    xd = xq.view(m, k)[:toks].view(torch.float8_e4m3fn).float() * xs[:toks, None]
+    err = rel_err(y.view(m, n)[:toks, :rows], xd @ wd.t())
+    return sec, {"bound": "tensor", "flops": 2.0 * m * n * k, "parity_rel_l2": err,
+                 "parity_ok": err < (5e-3 if a.out == "bf16" else 1e-4)}
 
 
 def bench_nvf4(ex, a):
@@ -213,19 +236,29 @@ def bench_nvf4(ex, a):
     xq = torch.zeros(m * k // 2, dtype=torch.uint8, device="cuda")
     xs = torch.zeros(m * k // 16, dtype=torch.uint8, device="cuda")
     ex.pack.call("quantize_nvf4", x, xq, xs, m * k, stream=st)
+    # the scale planes are tiled from a row-major plane, as the engine does at load time
+    rowmajor = torch.randint(0x20, 0x48, (n * k // 16,), dtype=torch.uint8, device="cuda")
+    for w in ws:
+        ex.pack.call("nvf4_tc5_tile_scales", rowmajor, w[1], k, n, stream=st)
     if a.out == "bf16":
         y = torch.zeros(m * n, dtype=torch.bfloat16, device="cuda")
-        sec = time_launches(lambda i: ex.pack.call("pdk_nvf4_gemm_bf16", ws[i % nc][0], ws[i % nc][1], None, xq, xs,
-                                                   y, 1.0, k, n, m, stream=st), a.iters)
+        call = lambda i: ex.pack.call("pdk_nvf4_gemm_bf16", ws[i % nc][0], ws[i % nc][1], None, xq, xs, y, 1.0, k, n, m,
+                                      stream=st)
     else:
-        # the table slot: f32 output; a scale tiling call first, as the engine does at load time
-        y = torch.zeros(m * n, dtype=torch.float32, device="cuda")
-        rowmajor = torch.randint(0x20, 0x48, (n * k // 16,), dtype=torch.uint8, device="cuda")
-        for w in ws:
-            ex.pack.call("nvf4_tc5_tile_scales", rowmajor, w[1], k, n, stream=st)
-        sec = time_launches(lambda i: ex.pack.call("nvf4_gemm_tc5w", ws[i % nc][0], ws[i % nc][1], None, xq, xs, y,
-                                                   1.0, k, n, m, None, 0, stream=st), a.iters)
-    return sec, {"bound": "both", "flops": 2.0 * m * n * k, "bytes": nbytes_w + 4 + m * (k // 2 + k // 16) + m * n * 2}
+        y = torch.zeros(m * n, dtype=torch.float32, device="cuda")   # the table slot writes f32
+        call = lambda i: ex.pack.call("nvf4_gemm_tc5w", ws[i % nc][0], ws[i % nc][1], None, xq, xs, y, 1.0, k, n, m, None,
+                                      0, stream=st)
+    sec = time_launches(call, a.iters)
+    # spot check: clone 0's first rows against an f32 product of the dequantized operands
+    call(0)
+    rows, toks = min(n, 256), min(m, 64)
+    wd = torch.empty(rows * k, dtype=torch.float32, device="cuda")
+    xd = torch.empty(toks * k, dtype=torch.float32, device="cuda")
+    ex.pack.call("nvf4_dequant", ws[0][0], rowmajor, 1.0, wd, k, rows, stream=st)
+    ex.pack.call("nvf4_dequant", xq, xs, 1.0, xd, k, toks, stream=st)
+    err = rel_err(y.view(m, n)[:toks, :rows], xd.view(toks, k) @ wd.view(rows, k).t())
+    return sec, {"bound": "both", "flops": 2.0 * m * n * k, "bytes": nbytes_w + 4 + m * (k // 2 + k // 16) + m * n * 2,
+                 "parity_rel_l2": err, "parity_ok": err < (5e-3 if a.out == "bf16" else 1e-4)}
 
 
 def bench_moe_other_pack(ex, a):
@@ -340,7 +373,20 @@ def bench_moe(ex, a):
         distinct += torch.unique(torch.topk(lg.view(T, n_expert), k, dim=1).indices).numel()
     distinct /= n_sets
     per_expert = 3 * embd * ff // 32 * 17
-    return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
+    info = {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
+    if a.moe_path == "tc5":
+        # spot check: the same call through the other expert path (independent kernels: mma.sync on
+        # weights decoded in registers), both starting from a zeroed output
+        out.zero_()
+        P.moe_mxfp4_forward(ex, planes, ws, x, logits[0], out)
+        got = out.clone()
+        saved, planes.tc5 = planes.tc5, None
+        out.zero_()
+        P.moe_mxfp4_forward(ex, planes, ws, x, logits[0], out)
+        planes.tc5 = saved
+        err = rel_err(got, out)
+        info.update(parity_rel_l2=err, parity_ok=err < 5e-3)
+    return sec, info
 
 
 def bench_moe_ep(ex, a):
@@ -417,7 +463,7 @@ def bench_moe_ep(ex, a):
 
 
 def bench_nvf4_gemv(ex, a):
-    """Slot 394: W4A16 decode GEMV over an NVFP4 plane (f32 activations), config 4 geometry."""
+    """Slot 394: W4A16 decode GEMV over an NVFP4 plane (f32 activations), K=5120 N=17408 by default."""
     n, k = a.n, a.k
     st = torch.cuda.current_stream().cuda_stream
     nbytes = n * k // 2 + n * k // 16
@@ -432,7 +478,7 @@ def bench_nvf4_gemv(ex, a):
 
 
 def bench_moe_nvf4(ex, a):
-    """The config 5 geometry with NVFP4 expert planes (per-16 UE4M3 scales, scale2 per expert), plain SwiGLU."""
+    """The MoE benchmark geometry (128 experts, top-4, 2880 / 2880) with NVFP4 expert planes (per-16 UE4M3 scales, scale2 per expert), plain SwiGLU."""
     from paddock_b200 import planes as P
     n_expert, k, embd, ff, T = 128, 4, a.k, a.n, a.m
     bm = 8 if T * k <= 1024 else 32
@@ -470,6 +516,34 @@ OPS = {"norm_nvf4": bench_norm_nvf4, "q4k_w4a8": bench_q4k_w4a8, "nvf4_gemv": be
 DEFAULTS = {"norm_nvf4": (64, 0, 5120), "q4k_w4a8": (4, 25600, 5120), "nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
+class Case:
+    """Arguments of one timed case (the command line's, or bench.py's)."""
+
+    def __init__(self, op, m=None, n=None, k=None, iters=50, out="bf16", moe_path="tc5", graph=False, dtype="q4_k",
+                 pack=None):
+        dm, dn, dk = DEFAULTS[op]
+        self.op, self.m, self.n, self.k = op, m or dm, n or dn, k or dk
+        self.iters, self.out, self.moe_path, self.graph, self.dtype, self.pack = iters, out, moe_path, graph, dtype, pack
+
+
+def run_case(ex, a):
+    """Time one case; returns the JSON-able record the command line prints."""
+    global GRAPH_REPLAY
+    GRAPH_REPLAY = a.graph and a.op in ("q4k_gemv", "q8_gemv", "nvf4_gemv", "norm_nvf4")
+    sec, info = OPS[a.op](ex, a)
+    err = ex.pack.device_error() if not a.pack else 0
+    hbm, bf16, kind = peaks()
+    extra = {k: v for k, v in info.items() if k not in ("bound", "bytes", "flops")}
+    line = {**extra, "op": a.op, "m": a.m, "n": a.n, "k": a.k, "us": sec * 1e6, "device_error": err, "peak_kind": kind,
+            "pack": a.pack or "paddock_b200"}
+    if info["bound"] in ("hbm", "both"):
+        line.update(gbs=info["bytes"] / sec / 1e9, frac_of_hbm=info["bytes"] / sec / 1e9 / hbm)
+    if info["bound"] in ("tensor", "both"):
+        tf = info["flops"] / sec / 1e12
+        line.update(tflops=tf, frac_of_2x_bf16=tf / (2 * bf16), frac_of_4x_bf16=tf / (4 * bf16))
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True, choices=sorted(OPS))
@@ -483,12 +557,9 @@ def main():
     ap.add_argument("--graph", action="store_true", help="replay the timed launches from a CUDA graph (moe_mxfp4, moe_ep, q4k_gemv, q8_gemv, nvf4_gemv)")
     ap.add_argument("--dtype", default="q4_k", choices=["q4_k", "q5_k", "q6_k", "q4_0"], help="q4k_gemv: the plane's format")
     ap.add_argument("--pack", default=None, help="path of a kernel-pack library to time instead of this package's")
-    a = ap.parse_args()
-    dm, dn, dk = DEFAULTS[a.op]
-    a.m, a.n, a.k = a.m or dm, a.n or dn, a.k or dk
+    args = ap.parse_args()
+    a = Case(args.op, args.m, args.n, args.k, args.iters, args.out, args.moe_path, args.graph, args.dtype, args.pack)
     ep = a.op == "moe_ep"
-    global GRAPH_REPLAY
-    GRAPH_REPLAY = a.graph and a.op in ("q4k_gemv", "q8_gemv", "nvf4_gemv", "norm_nvf4")
     if ep:
         import torch.distributed as dist
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
@@ -498,17 +569,7 @@ def main():
         ex = GpuExecutor(KernelPack.load(a.pack))
     else:
         ex = GpuExecutor()
-    sec, info = OPS[a.op](ex, a)
-    err = ex.pack.device_error() if not a.pack else 0
-    hbm, bf16, kind = peaks()
-    extra = {k: v for k, v in info.items() if k not in ("bound", "bytes", "flops")}
-    line = {**extra, "op": a.op, "m": a.m, "n": a.n, "k": a.k, "us": sec * 1e6, "device_error": err, "peak_kind": kind,
-            "pack": a.pack or "paddock_b200"}
-    if info["bound"] in ("hbm", "both"):
-        line.update(gbs=info["bytes"] / sec / 1e9, frac_of_hbm=info["bytes"] / sec / 1e9 / hbm)
-    if info["bound"] in ("tensor", "both"):
-        tf = info["flops"] / sec / 1e12
-        line.update(tflops=tf, frac_of_2x_bf16=tf / (2 * bf16), frac_of_4x_bf16=tf / (4 * bf16))
+    line = run_case(ex, a)
     if not ep or dist.get_rank() == 0:
         print(json.dumps(line), flush=True)
     if ep:

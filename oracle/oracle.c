@@ -376,7 +376,7 @@ void orc_quantize_q4_k(const float* w, size_t n, uint8_t* out) {
     }
 }
 
-/* BASELINE config 3 recipe: per row s = absmax/448 (f32), q = e4m3_rn(w/s) */
+/* The FP8 benchmark recipe: per row s = absmax/448 (f32), q = e4m3_rn(w/s) */
 void orc_quantize_fp8_absmax(const float* w, uint32_t rows, uint32_t k, uint8_t* q, float* scale) {
 #pragma omp parallel for schedule(static)
     for (size_t r = 0; r < rows; ++r) {
@@ -418,7 +418,7 @@ void orc_quantize_nvf4(const float* x, size_t n, uint8_t* q, uint8_t* scale) {
     orc_quantize_nvf4_global(x, n, 1.0f, q, scale);
 }
 
-/* Same with a per-tensor global scale (the checkpoint/BASELINE config 4 form):
+/* Same with a per-tensor global scale (the checkpoint's and the NVFP4 benchmark's form):
  * block scale byte = RN_e4m3(amax/(6*scale2)), element = e2m1_rn(v/(e4m3*scale2)). */
 void orc_quantize_nvf4_global(const float* x, size_t n, float scale2, uint8_t* q, uint8_t* scale) {
     size_t blocks = n / 16;

@@ -317,61 +317,76 @@ struct PeerOut {
     uint32_t n, row0;
 };
 
-// Activations -> block floating point limbs, by `nthreads` threads of a CTA (whole warps): per
-// 32-element block a power-of-two step and 15-bit integers kept as two int8 limbs
-// (xs_hi, xs_lo: int8 [in_dim]), xmeta[block] = {step, step * sum of the block's integers},
-// and a 32-byte zero line.  x f32 [in_dim], or int8 xq with one f32 scale per 32.  8 elements
-// per thread; the 4 lanes of a block agree on the step through two shuffles.
+// Activations -> block floating point limbs: per 32-element block a power-of-two step and 15-bit
+// integers kept as two int8 limbs, v = 256 * hi + lo (xs_hi, xs_lo: int8 [in_dim]), and
+// xmeta[block] = {step, step * sum of the block's integers}.  x f32 [in_dim], or int8 xq with one
+// f32 scale per 32.  A thread handles groups of 8 elements; the 4 lanes of a block agree on the
+// step through two shuffles, so whole warps must call with consecutive groups.
+//
+// limb_load8: the group's 8 values; limb_store8: their limbs and the block's meta entry.
+__device__ __forceinline__ void limb_load8(const float* __restrict__ x, const int8_t* __restrict__ xq,
+                                           const float* __restrict__ xq_scale, uint32_t grp, float (&v)[8]) {
+    if (xq == nullptr) {
+        const float4 a = *reinterpret_cast<const float4*>(x + grp * 8u);
+        const float4 b = *reinterpret_cast<const float4*>(x + grp * 8u + 4u);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        // int8 activations with one f32 scale per 32 (the W4A8 slots' operands)
+        const int2 q = *reinterpret_cast<const int2*>(xq + grp * 8u);
+        const float s = xq_scale[grp >> 2];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (float)(int8_t)((i < 4 ? q.x >> (8 * i) : q.y >> (8 * (i - 4))) & 0xff) * s;
+    }
+}
+__device__ __forceinline__ void limb_store8(const float (&v)[8], uint32_t grp, uint8_t* xs_hi, uint8_t* xs_lo,
+                                            float2* xmeta) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    // amax < 2^ex  ->  step 2^(ex-14) keeps |v| <= 2^14 (no clamp needed: |x| <= amax; an infinite or
+    // NaN block gets inv = 0 and all-zero limbs)
+    float step = 1.0f, inv = 0.0f;
+    if (amax > 0.0f && amax < 3.0e38f) {
+        // frexp's exponent from the bits (denormals land on the clamp), powers of two built in place
+        const int ex = max((int)(__float_as_uint(amax) >> 23) - 126, -110);
+        step = __uint_as_float((uint32_t)(ex + 113) << 23);
+        inv = __uint_as_float((uint32_t)(141 - ex) << 23);
+    }
+    // lo limb = the integer's low byte (two's complement), hi limb = byte 1 of (q + 128): then
+    // q = 256 * hi + lo with lo in [-128, 127]; four of each are gathered with byte permutes
+    int q[8], r[8], isum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        q[i] = __float2int_rn(v[i] * inv);
+        r[i] = q[i] + 128;
+        isum += q[i];
+    }
+    uint2 lo, hi;
+    lo.x = __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+    lo.y = __byte_perm(__byte_perm(q[4], q[5], 0x0040), __byte_perm(q[6], q[7], 0x0040), 0x5410);
+    hi.x = __byte_perm(__byte_perm(r[0], r[1], 0x0051), __byte_perm(r[2], r[3], 0x0051), 0x5410);
+    hi.y = __byte_perm(__byte_perm(r[4], r[5], 0x0051), __byte_perm(r[6], r[7], 0x0051), 0x5410);
+    *reinterpret_cast<uint2*>(xs_hi + (size_t)grp * 8u) = hi;
+    *reinterpret_cast<uint2*>(xs_lo + (size_t)grp * 8u) = lo;
+    isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+    isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+    if ((grp & 3u) == 0u) xmeta[grp >> 2] = make_float2(step, step * (float)isum);
+}
+
+// All of x by `nthreads` threads of a CTA (whole warps), plus the 32-byte zero line.
 __device__ __forceinline__ void act_limbs(const float* __restrict__ x, const int8_t* __restrict__ xq,
                                           const float* __restrict__ xq_scale, uint32_t in_dim, uint8_t* xs_hi,
                                           uint8_t* xs_lo, uint8_t* zeros, float2* xmeta, uint32_t tid,
-                                          uint32_t nthreads)
-    {
-        const uint32_t groups = in_dim >> 3;
-        for (uint32_t grp = tid; grp < groups; grp += nthreads) {
-            float v[8];
-            if (xq == nullptr) {
-                const float4 a = *reinterpret_cast<const float4*>(x + grp * 8u);
-                const float4 b = *reinterpret_cast<const float4*>(x + grp * 8u + 4u);
-                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-            } else {
-                // int8 activations with one f32 scale per 32 (the W4A8 slots' operands)
-                const int2 q = *reinterpret_cast<const int2*>(xq + grp * 8u);
-                const float s = xq_scale[grp >> 2];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = (float)(int8_t)((i < 4 ? q.x >> (8 * i) : q.y >> (8 * (i - 4))) & 0xff) * s;
-            }
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            // amax < 2^ex  ->  step 2^(ex-14) keeps |v| <= 2^14
-            float step = 1.0f, inv = 0.0f;
-            if (amax > 0.0f && amax < 3.0e38f) {
-                // frexp's exponent from the bits (denormals land on the clamp), powers of two built in place
-                const int ex = max((int)(__float_as_uint(amax) >> 23) - 126, -110);
-                step = __uint_as_float((uint32_t)(ex + 113) << 23);
-                inv = __uint_as_float((uint32_t)(141 - ex) << 23);
-            }
-            uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
-            int isum = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                int q = __float2int_rn(v[i] * inv);
-                q = max(-16384, min(16384, q));
-                const int h = (q + 128) >> 8, l = q - (h << 8);
-                hi[i >> 2] |= ((uint32_t)h & 0xffu) << (8 * (i & 3));
-                lo[i >> 2] |= ((uint32_t)l & 0xffu) << (8 * (i & 3));
-                isum += q;
-            }
-            *reinterpret_cast<uint2*>(xs_hi + (size_t)grp * 8u) = make_uint2(hi[0], hi[1]);
-            *reinterpret_cast<uint2*>(xs_lo + (size_t)grp * 8u) = make_uint2(lo[0], lo[1]);
-            isum += __shfl_xor_sync(0xffffffffu, isum, 1);
-            isum += __shfl_xor_sync(0xffffffffu, isum, 2);
-            if ((grp & 3u) == 0u) xmeta[grp >> 2] = make_float2(step, step * (float)isum);
-        }
-        if (tid < 8u) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
+                                          uint32_t nthreads) {
+    const uint32_t groups = in_dim >> 3;
+    for (uint32_t grp = tid; grp < groups; grp += nthreads) {
+        float v[8];
+        limb_load8(x, xq, xq_scale, grp, v);
+        limb_store8(v, grp, xs_hi, xs_lo, xmeta);
     }
+    if (tid < 8u) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
+}
 
 }  // namespace gemv_i8

@@ -233,11 +233,16 @@ gemv_ring_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant
     pdk_pdl_wait();  // x (and y's previous contents) belong to the previous kernel until here
     const bool invariant = pl.invariant != 0u;
     if (invariant) {
-        // a warp only ever meets its own pair's 512 activations: it builds their limbs itself
-        const uint32_t off = warp * 512u;
-        act_limbs(x + off, xq ? xq + off : nullptr, xq_scale ? xq_scale + (off >> 5) : nullptr, 512u, xs_hi + off,
-                  xs_lo + off, zeros, xmeta + (off >> 5), lane, 32u);
+        // A warp only ever meets its own pair's 512 activations: it builds their limbs itself.  The
+        // loads of x go out before the rest of the ring is requested, so they do not queue behind it.
+        const uint32_t g0 = warp * 64u + lane;   // groups of 8 elements: this lane's two
+        float v0[8], v1[8];
+        limb_load8(x, xq, xq_scale, g0, v0);
+        limb_load8(x, xq, xq_scale, g0 + 32u, v1);
         while (issued < D && issued < total) issue_next();
+        limb_store8(v0, g0, xs_hi, xs_lo, xmeta);
+        limb_store8(v1, g0 + 32u, xs_hi, xs_lo, xmeta);
+        if (tid < 8u) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
         __syncthreads();   // the zero line and the fold barriers are shared
     } else {
         act_limbs(x, xq, xq_scale, in_dim, xs_hi, xs_lo, zeros, xmeta, tid, W * 32u);

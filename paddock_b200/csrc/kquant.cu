@@ -639,8 +639,8 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
     if (batch > 64u) return cudaErrorInvalidValue;
     if (int rc = check_gemv(data, scales, x, y, in_dim, dtype)) return rc;
     if (dtype == PDK_KQ_Q4_0 && batch >= 4u && !force_plain() && tc5_min_tokens() != 0u) {
-        // Q4_0 shares Q4_K's nibble planes: from four tokens on the tcgen05 kernel (32 us per 32 tokens at config 2's
-        // shape) beats one 17 us decode GEMV per token
+        // Q4_0 shares Q4_K's nibble planes: from four tokens on the tcgen05 kernel (32 us per 32 tokens at K=5120,
+        // N=25600) beats one 17 us decode GEMV per token
         uint32_t b = 0;
         int rc = 0;
         while (b < batch && rc == 0) {
@@ -660,7 +660,7 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
     }
     if (dtype != PDK_KQ_Q4K && !force_plain() && pdk_aligned(data, 16)) {
         // Q5_K / Q6_K (and Q4_0 below four tokens) have no batch kernel on the tensor path yet: one decode GEMV per token
-        // (17-25 us each at config 2's shape, the later ones partly from L2) beats the plain f32
+        // (17-25 us each at K=5120 N=25600, the later ones partly from L2) beats the plain f32
         // kernel's 165 us per four tokens
         int rc = 0;
         for (uint32_t b = 0; b < batch && rc == 0; ++b)

@@ -165,7 +165,7 @@ PDK_EXPORT int pd_q8_0_gemm_repacked(const void* data, const void* scale, const 
     auto st = (cudaStream_t)stream;
     if (!force_plain()) {
         // There is no batch kernel on the tensor path for Q8_0 yet: one decode GEMV per token (18 us each at
-        // config 1's shape) beats the plain f32 kernel below (169 us per four tokens)
+        // K=5120 N=17408) beats the plain f32 kernel below (169 us per four tokens)
         int rc = 0;
         for (uint32_t t = 0; t < batch && rc == 0; ++t)
             rc = pdk_q8_0_gemv_i8(data, scale, (const float*)bias, xf + (size_t)t * in_dim, yf + (size_t)t * out_dim, in_dim,

@@ -22,7 +22,7 @@ def test_block_layouts_and_sizing():
     assert F.byte_size(12, 100) is None                     # partial_blocks_are_rejected
     assert F.block_layout(8) == (32, 34) and F.block_layout(12) == (256, 144)
     assert F.block_layout(39) == (32, 17) and F.block_layout(40) == (64, 36) and F.block_layout(30) == (1, 2)
-    # BASELINE plane sizes
+    # plane sizes of the benchmark shapes
     assert F.byte_size(8, 17408 * 5120) == 94_699_520
     assert F.byte_size(12, 25600 * 5120) == 73_728_000
 

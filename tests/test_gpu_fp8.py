@@ -1,6 +1,6 @@
 """FP8 E4M3 row-scaled path: quantizers bit-exact against the oracle, tcgen05
 GEMM within 1e-2 (in practice ~1e-6) of an f64 matmul of the dequantized
-operands (BASELINE config 3)."""
+operands (the FP8 prefill benchmark: 4096 tokens, K=5120)."""
 import numpy as np
 import pytest
 import torch
@@ -41,7 +41,7 @@ def test_bf16_to_f8row_bit_exact(pack):
 def fp8_case(m, n, k, seed):
     w = oracle.fill_normal(n * k, seed, 0.02)
     x = oracle.bf16_round(oracle.fill_normal(m * k, seed + 1, 1.0))
-    wq, ws = oracle.quantize_fp8_absmax(w, n, k)      # BASELINE config 3: scale = absmax / 448
+    wq, ws = oracle.quantize_fp8_absmax(w, n, k)      # the FP8 benchmark recipe: scale = absmax / 448
     xq, xs = oracle.quantize_fp8_absmax(x, m, k)
     wd = oracle.dequant_fp8_channel(wq, ws, k, n)
     xd = oracle.dequant_fp8_channel(xq, xs, k, m)

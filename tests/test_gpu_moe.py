@@ -1,4 +1,4 @@
-"""MXFP4 MoE (BASELINE config 5): router and alignment against the oracle /
+"""MXFP4 MoE (128 experts, top-4, 2880 / 2880 in the benchmark): router and alignment against the oracle /
 their invariants, then the whole block (top-k -> align -> gate|up + SwiGLU ->
 down -> combine) within 1e-2 of the oracle's f64 walk over dequantized experts."""
 import numpy as np
@@ -77,7 +77,7 @@ def make_layer(n_expert, embd, ff, seed, with_bias):
     (5, 8, 2, 128, 160, 8, False),
     (40, 8, 4, 128, 64, 32, True),
     (70, 4, 2, 256, 256, 32, False),
-    (3, 16, 4, 2880, 2880, 8, True),      # config 5 geometry, a few tokens
+    (3, 16, 4, 2880, 2880, 8, True),      # the benchmark geometry, a few tokens
     (48, 16, 4, 2880, 2880, 32, False),
 ])
 def test_moe_block_matches_oracle(pack, tokens, n_expert, k, embd, ff, bm, with_bias):
@@ -105,7 +105,7 @@ def test_moe_block_matches_oracle(pack, tokens, n_expert, k, embd, ff, bm, with_
     (9, 8, 2, 128, 192, 8, True),
     (40, 8, 4, 128, 64, 32, True),
     (70, 4, 2, 256, 256, 32, False),
-    (3, 16, 4, 2880, 2880, 8, True),      # config 5 geometry: K = 11 slabs + a quarter
+    (3, 16, 4, 2880, 2880, 8, True),      # the benchmark geometry: K = 11 slabs + a quarter
     (48, 16, 4, 2880, 2880, 32, False),
 ])
 def test_moe_block_tensor_core_path_matches_oracle(pack, tokens, n_expert, k, embd, ff, bm, with_bias):

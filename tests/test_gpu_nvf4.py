@@ -1,4 +1,4 @@
-"""NVFP4 path (BASELINE config 4): quantizer and dequant bit-exact against the
+"""NVFP4 path (K=5120, N=17408 in the benchmark): quantizer and dequant bit-exact against the
 oracle, W4A16 GEMV and the block-scaled tcgen05 W4A4 GEMM within 1e-2 of an
 f64 matmul of the dequantized operands."""
 import numpy as np
@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 
 def nvf4_weights(n, k, seed):
-    """BASELINE recipe: per-tensor scale2 = absmax / (6 * 448), e4m3 block scales, e2m1 elements."""
+    """The benchmark recipe: per-tensor scale2 = absmax / (6 * 448), e4m3 block scales, e2m1 elements."""
     w = oracle.fill_normal(n * k, seed, 0.02)
     scale2 = float(np.abs(w).max() / (6.0 * 448.0))
     q, s = oracle.quantize_nvf4(w, scale2)
