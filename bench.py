@@ -299,14 +299,24 @@ def run_ours(args, rank, world, local_rank):
         if not torch.equal(check, y_all):
             raise RuntimeError("peer-store exchange differs from the all-gather")
 
-    # one pre-bound launcher per plane clone (arguments converted once; the call is the C ABI entry)
+    # One pre-bound launcher per plane clone (arguments converted once; the call is the C ABI entry).
+    # N > 1, peer exchange: a step is the sharded GEMV, whose last CTA raises this rank's flag on every
+    # rank once its band is stored there, followed by the device-side wait for every rank's flag -
+    # what a consumer of y needs before it may read - so no step relies on a host barrier.  Both
+    # calls count their steps on the device, so their arguments never change.
     st = torch.cuda.current_stream().cuda_stream
-    if peer_out is not None:
-        bound = [ex.pack.bind("pdk_q4k_gemv_shard", p.data, p.scales, x, peer_out.ptrs_address(), world, first_row,
-                              p.dims[0], p.dims[1], stream=st) for p in planes]
-    else:
-        bound = [ex.pack.bind("kquant_gemv", p.data, p.scales, x, y, p.dims[0], p.dims[1], p.ty, stream=st)
-                 for p in planes]
+
+    def bind_all(stream, xin, yout):
+        if peer_out is not None:
+            gem = [ex.pack.bind("pdk_q4k_gemv_shard_sync", p.data, p.scales, xin, peer_out.ptrs_address(),
+                                peer_out.flag_ptrs_address(), peer_out.ctr, world, rank, first_row, 0, p.dims[0],
+                                p.dims[1], stream=stream) for p in planes]
+            wait = ex.pack.bind("pdk_peer_flags_wait", peer_out.flags, world, 0, 2000000, stream=stream)
+            return [(lambda g=g: (g(), wait())) for g in gem]
+        return [ex.pack.bind("kquant_gemv", p.data, p.scales, xin, yout, p.dims[0], p.dims[1], p.ty, stream=stream)
+                for p in planes]
+
+    bound = bind_all(st, x, y)
 
     def step(i):
         bound[i % n_clones]()
@@ -336,12 +346,7 @@ def run_ours(args, rank, world, local_rank):
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             g_st = side.cuda_stream
-            if peer_out is not None:
-                g_bound = [ex.pack.bind("pdk_q4k_gemv_shard", p.data, p.scales, x, peer_out.ptrs_address(), world,
-                                        first_row, p.dims[0], p.dims[1], stream=g_st) for p in planes]
-            else:
-                g_bound = [ex.pack.bind("kquant_gemv", p.data, p.scales, x, y, p.dims[0], p.dims[1], p.ty, stream=g_st)
-                           for p in planes]
+            g_bound = bind_all(g_st, x, y)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 for i in range(args.steps):
@@ -389,7 +394,6 @@ def run_ours(args, rank, world, local_rank):
     # N = 1: the way a decode loop runs it - three steps in flight on three streams (copy in, kernel,
     # copy out), each step's input copied from pinned memory into its own device buffer and its
     # result read back and waited for by the host two steps later.  N > 1 keeps one step in flight.
-    e2e_mode = "serial"
     if world == 1:
         e2e_mode = "3 steps in flight: H2D / kernel / D2H on three streams, host waits for step i-2's result"
         s_in, s_k, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
@@ -440,22 +444,30 @@ def run_ours(args, rank, world, local_rank):
         if not torch.equal(yh[(args.steps - 1) % D][:y.numel()], y.cpu()):
             raise RuntimeError("pipelined end-to-end loop returned a different y")
     else:
+        # N > 1: one step in flight (every rank's y is single-buffered: a rank may only run ahead of
+        # its peers' read-back when y is double-buffered and a second, "consumed" signal flows back -
+        # not built); copies and waits through the CUDA runtime directly, as at N = 1.
+        e2e_mode = "1 step in flight: H2D, sharded GEMV + flag wait (or NCCL all-gather), D2H of the full y, host wait"
+        rt = Cudart()
+        ev = rt.event()
+        x_src, x_bytes = x_host.data_ptr(), x_host.numel() * 4
+        y_dst, y_src, y_bytes = y_host.data_ptr(), y_all.data_ptr(), y_all.numel() * 4
+
+        def e2e_step(i):
+            rt.copy(x.data_ptr(), x_src, x_bytes, 1, st)
+            step(i)
+            rt.copy(y_dst, y_src, y_bytes, 2, st)
+            rt.record(ev, st)
+            rt.sync_event(ev)
+
         for i in range(3):
-            x.copy_(x_host, non_blocking=True)
-            step(i)
-            y_host[:y_all.numel()].copy_(y_all, non_blocking=True)
+            e2e_step(i)
         barrier()
-        t0 = torch.cuda.Event(enable_timing=True)
-        t1 = torch.cuda.Event(enable_timing=True)
-        t0.record()
+        w0 = time.perf_counter()
         for i in range(args.steps):
-            x.copy_(x_host, non_blocking=True)
-            step(i)
-            y_host[:y_all.numel()].copy_(y_all, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-        t1.record()
+            e2e_step(i)
+        e2e_ms = (time.perf_counter() - w0) * 1e3
         barrier()
-        e2e_ms = t0.elapsed_time(t1)
 
     times = torch.tensor([total_ms, e2e_ms, kern_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -471,8 +483,8 @@ def run_ours(args, rank, world, local_rank):
         # kernel's back-to-back launch duration; with a collective in the step the
         # separately event-bracketed launches are used instead
         event_us = kern_ms * 1e3
-        if world == 1:
-            kern_ms = ms_step
+        if graph is not None:
+            kern_ms = ms_step       # the step is this rank's kernel (N > 1: plus the flag wait that follows it)
         achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
         line = {
             "metric": "q4k_gemv_weight_gbs", "value": bytes_step / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
@@ -486,7 +498,7 @@ def run_ours(args, rank, world, local_rank):
             "launch": "one replay of a CUDA graph holding the K launches" if graph is not None else "K direct launches",
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES * rows // N_DIM, "peak_kind": peak_kind,
-                         "kernel": "gemv_i8_kernel<Q4K>", "us_per_launch": kern_ms * 1e3,
+                         "kernel": "gemv_ring_kernel<RQ4K>", "us_per_launch": kern_ms * 1e3,
                          "us_per_launch_event_bracketed": event_us,
                          "algorithmic_bytes_per_launch": kern_bytes},
             "clocks": sampler.summary(),

@@ -285,6 +285,22 @@ int pdk_selftest_bounded_wait(uint32_t budget_us, void* scratch, void* stream);
 int pdk_q4k_gemv_shard(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
                        uint32_t n_ranks, uint32_t row0, uint32_t in_dim, uint32_t out_dim, void* stream);
 
+/* No counterpart in the reference.  pdk_q4k_gemv_shard with a completion signal, so that a step
+ * needs no host barrier: once its band is stored in every rank's y, rank `rank` stores the step
+ * number into word `rank` of every rank's flag array (flag_ptrs[p]: rank p's array of 16 u32
+ * words, zeroed at set-up, mapped like y_ptrs: words 0..7 flags, word 8 the count of waits).
+ * ctr: two zeroed u32 words of this rank's own memory, not shared between streams (CTA counter,
+ * count of signalled steps).  step != 0 names the step (growing from call to call); step == 0
+ * takes the rank's count plus one, so a captured launch can be replayed. */
+int pdk_q4k_gemv_shard_sync(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
+                            const void* const* flag_ptrs, void* ctr, uint32_t n_ranks, uint32_t rank,
+                            uint32_t row0, uint32_t step, uint32_t in_dim, uint32_t out_dim, void* stream);
+/* No counterpart in the reference.  Device-side wait (one small kernel in `stream`) until all
+ * n_ranks <= 8 flag words of this rank's flag array have reached the step (`step`, or with
+ * step == 0 the array's count of waits plus one); bounded: after budget_us microseconds the
+ * kernel records 0x16 << 8 | late-rank in the device error word and returns. */
+int pdk_peer_flags_wait(void* flags, uint32_t n_ranks, uint32_t step, uint32_t budget_us, void* stream);
+
 /* ---- MXFP4 expert GEMMs on the block-scaled tensor-core path (no counterpart in the reference,
  * whose B200 MoE kernels are mma.sync on int8 activations, packs/cuda/src/moe/mmq.cuh:139-626).
  * The repacked data plane is used as it is; the E8M0 scale plane is re-expressed once at load time

@@ -205,6 +205,10 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
             });
         }
     }
+    if (peers.n != 0u && peers.signal != 0u) {   // uniform over the grid
+        __syncthreads();
+        if (tid == 0u) peer_signal(peers);
+    }
 }
 
 // PDK_NO_PDL=1 launches without programmatic stream serialization (A/B switch, read once).

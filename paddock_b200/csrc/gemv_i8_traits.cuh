@@ -311,11 +311,37 @@ struct Q80 {
 
 // Row-sharded output: when n > 0 the kernel stores row r of its band at ptr[p][row0 + r] for
 // every p < n - the full-length y of each rank, peer memory over NVLink included - instead of
-// y[r].  Plain peer stores; the caller orders them (a barrier, or a flag the consumer waits on).
+// y[r].  Plain peer stores.  With signal != 0 the kernel also tells every rank when its band is
+// complete: its CTAs count themselves out on ctr[0] (this rank's memory, zero between launches)
+// after a system-scope fence, and the last one stores the step number into flag[p][rank] of every
+// rank p, where a consumer waits for it (pdk_peer_flags_wait).  The step number is `step`, or,
+// when that is 0, one more than the rank's own count ctr[1], which the kernel then advances - so
+// that a captured launch can be replayed.  With signal == 0 the caller orders the stores itself.
 struct PeerOut {
     float* ptr[8];
-    uint32_t n, row0;
+    uint32_t* flag[8];
+    uint32_t* ctr;
+    uint32_t n, row0, rank, step, signal;
 };
+
+// Called by one thread of each CTA after a CTA-wide barrier that follows the CTA's last store.
+__device__ __forceinline__ void peer_signal(const PeerOut& po) {
+    if (po.n == 0u || po.signal == 0u) return;
+    __threadfence_system();                            // this CTA's stores, seen through the barrier, before the count
+    const uint32_t prev = atomicAdd(po.ctr, 1u);
+    if (prev == gridDim.x - 1u) {
+        po.ctr[0] = 0u;                                // the next launch on this stream counts from zero
+        uint32_t step = po.step;
+        if (step == 0u) {
+            step = po.ctr[1] + 1u;
+            po.ctr[1] = step;
+        }
+        __threadfence_system();                        // every CTA's stores before the flags
+#pragma unroll
+        for (uint32_t p = 0; p < 8u; ++p)
+            if (p < po.n) *reinterpret_cast<volatile uint32_t*>(po.flag[p] + po.rank) = step;
+    }
+}
 
 // Activations -> block floating point limbs: per 32-element block a power-of-two step and 15-bit
 // integers kept as two int8 limbs, v = 256 * hi + lo (xs_hi, xs_lo: int8 [in_dim]), and

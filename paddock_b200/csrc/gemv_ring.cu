@@ -227,6 +227,10 @@ gemv_ring_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant
         *abort_flag = 0;
         tc5::mbar_fence_init();
     }
+    if (tid < 8u) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
+    // The CTA meets once, here, where it would wait for the previous kernel anyway: the fold
+    // barriers and the zero line are shared, everything after is per warp (invariant plans).
+    __syncthreads();
     // Programmatic dependent launch: the next kernel of the stream may start its prologue (its own
     // first requests: weights never depend on this kernel) as soon as this one's CTAs have all started.
     pdk_pdl_launch_dependents();
@@ -242,10 +246,14 @@ gemv_ring_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant
         while (issued < D && issued < total) issue_next();
         limb_store8(v0, g0, xs_hi, xs_lo, xmeta);
         limb_store8(v1, g0 + 32u, xs_hi, xs_lo, xmeta);
-        if (tid < 8u) reinterpret_cast<uint32_t*>(zeros)[tid] = 0u;
-        __syncthreads();   // the zero line and the fold barriers are shared
+        __syncwarp();
     } else {
-        act_limbs(x, xq, xq_scale, in_dim, xs_hi, xs_lo, zeros, xmeta, tid, W * 32u);
+        const uint32_t groups = in_dim >> 3;
+        for (uint32_t grp = tid; grp < groups; grp += W * 32u) {
+            float v[8];
+            limb_load8(x, xq, xq_scale, grp, v);
+            limb_store8(v, grp, xs_hi, xs_lo, xmeta);
+        }
         while (issued < D && issued < total) issue_next();
         __syncthreads();
     }
@@ -394,6 +402,10 @@ gemv_ring_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant
         if (++rb == kRedBufs) { rb = 0; rb_phase ^= 1u; }
     }
     poll_fold(true);
+    if (peers.n != 0u && peers.signal != 0u) {   // uniform over the grid
+        __syncthreads();
+        if (tid == 0u) peer_signal(peers);
+    }
     if (!alive) {
         // a wait ran out somewhere in the CTA: the copies this warp still has in flight must land
         // before its shared memory can go to another CTA.  At most D are outstanding, one per stage.
@@ -573,15 +585,10 @@ int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq
     return rc != -1 ? rc : pdk_q4k_gemv_i8_q8act_regs(data, scales, xq, xq_scale, y, in_dim, out_dim, st);
 }
 
-// No counterpart in the reference (its multi-GPU story is one process per GPU, replicas only):
-// Q4_K decode GEMV of one rank's row band that writes its band straight into every rank's
-// full-length y (y_ptrs[0..n_ranks), device pointers valid on this GPU: its own buffer and the
-// peers' buffers mapped over NVLink) at rows row0 .. row0 + out_dim.  The exchange that an
-// all-gather would do is the kernel's own stores.  The stores are complete when the kernel
-// is; the caller orders consumers after it (stream order locally, a barrier or flag across
-// ranks).  n_ranks <= 8.  Returns 801 for shapes outside the GEMV kernels' plans.
-PDK_EXPORT int pdk_q4k_gemv_shard(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
-                                  uint32_t n_ranks, uint32_t row0, uint32_t in_dim, uint32_t out_dim, void* stream) {
+namespace {
+int shard_launch(const void* data, const void* scales, const void* x, const void* const* y_ptrs, const void* const* flag_ptrs,
+                 void* ctr, uint32_t n_ranks, uint32_t rank, uint32_t row0, uint32_t step, bool signal, uint32_t in_dim,
+                 uint32_t out_dim, cudaStream_t st) {
     if (out_dim == 0) return 0;
     if (n_ranks == 0 || n_ranks > 8u || y_ptrs == nullptr) return cudaErrorInvalidValue;
     if (!pdk_aligned(data, 16) || !pdk_aligned(scales, 8) || !pdk_aligned(x, 16)) return cudaErrorInvalidValue;
@@ -592,8 +599,93 @@ PDK_EXPORT int pdk_q4k_gemv_shard(const void* data, const void* scales, const vo
     }
     po.n = n_ranks;
     po.row0 = row0;
-    int rc = launch_ring<RQ4K>(data, scales, nullptr, (const float*)x, nullptr, in_dim, out_dim, (cudaStream_t)stream,
-                               nullptr, nullptr, &po);
-    if (rc == -1) rc = pdk_q4k_gemv_peers_regs(data, scales, (const float*)x, &po, in_dim, out_dim, (cudaStream_t)stream);
+    if (signal) {
+        if (flag_ptrs == nullptr || ctr == nullptr || rank >= n_ranks || !pdk_aligned(ctr, 4))
+            return cudaErrorInvalidValue;
+        for (uint32_t p = 0; p < n_ranks; ++p) {
+            if (flag_ptrs[p] == nullptr || !pdk_aligned(flag_ptrs[p], 4)) return cudaErrorInvalidValue;
+            po.flag[p] = (uint32_t*)flag_ptrs[p];
+        }
+        po.ctr = (uint32_t*)ctr;
+        po.rank = rank;
+        po.step = step;
+        po.signal = 1u;
+    }
+    int rc = launch_ring<RQ4K>(data, scales, nullptr, (const float*)x, nullptr, in_dim, out_dim, st, nullptr, nullptr, &po);
+    if (rc == -1) rc = pdk_q4k_gemv_peers_regs(data, scales, (const float*)x, &po, in_dim, out_dim, st);
     return rc >= 0 ? rc : (int)cudaErrorNotSupported;
+}
+
+// One warp: lane p waits until flags[p] has reached the step (wrap-around safe), for at most
+// budget_ns; a lane that gives up records kErrFlagWait << 8 | p in the device error word.  The
+// step is `step`, or, when that is 0, one more than the count of waits kept in flags[8], which
+// the kernel then advances.
+enum : unsigned int { kErrFlagWait = 0x16 };
+__global__ void peer_flags_wait_kernel(uint32_t* flags, uint32_t n_ranks, uint32_t step, unsigned long long budget_ns,
+                                       unsigned int* err) {
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();   // ordered after the kernel before it in the stream (this rank's own band)
+    const uint32_t p = threadIdx.x;
+    const uint32_t target = step != 0u ? step : flags[8] + 1u;
+    __syncwarp();
+    if (step == 0u && p == 0u) flags[8] = target;
+    if (p >= n_ranks) return;
+    const volatile uint32_t* f = flags + p;
+    const unsigned long long t0 = tc5::globaltimer_ns();
+    uint32_t spins = 0;
+    while ((int32_t)(*f - target) < 0) {
+        if ((++spins & 31u) == 0u && tc5::globaltimer_ns() - t0 > budget_ns) {
+            tc5::report(err, kErrFlagWait, p);
+            return;
+        }
+    }
+    __threadfence_system();   // acquire: the bands stored before the flags are visible to what follows
+}
+}  // namespace
+
+// No counterpart in the reference (its multi-GPU story is one process per GPU, replicas only):
+// Q4_K decode GEMV of one rank's row band that writes its band straight into every rank's
+// full-length y (y_ptrs[0..n_ranks), device pointers valid on this GPU: its own buffer and the
+// peers' buffers mapped over NVLink) at rows row0 .. row0 + out_dim.  The exchange that an
+// all-gather would do is the kernel's own stores.  This form signals nothing: the stores are
+// complete when the kernel is, and the caller orders consumers after it (stream order locally,
+// a barrier across ranks).  n_ranks <= 8.  Returns 801 for shapes outside the GEMV kernels' plans.
+PDK_EXPORT int pdk_q4k_gemv_shard(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
+                                  uint32_t n_ranks, uint32_t row0, uint32_t in_dim, uint32_t out_dim, void* stream) {
+    return shard_launch(data, scales, x, y_ptrs, nullptr, nullptr, n_ranks, 0u, row0, 0u, false, in_dim, out_dim,
+                        (cudaStream_t)stream);
+}
+
+// The same with a completion signal, so that a step needs no host barrier: after its band is
+// stored everywhere, rank `rank` stores the step number into word `rank` of every rank's flag
+// array (flag_ptrs[p] = rank p's array, mapped like y_ptrs; 16 u32 words, zeroed once at set-up:
+// words 0..7 the flags, word 8 the count of pdk_peer_flags_wait calls).  ctr = two zeroed u32
+// words of this rank's own memory, not shared between streams: the kernel's CTAs count
+// themselves out on word 0, word 1 counts the rank's signalled steps.  step != 0 names the step
+// (it must grow from call to call); step == 0 takes word 1 plus one, which lets a captured
+// launch be replayed.  A consumer of y on rank p runs pdk_peer_flags_wait on its own flag array
+// first.  The band is written with plain stores: a rank must not start step s + 1 before its
+// consumers of step s are done with y (the wait kernel in the same stream gives that order), or y
+// is double buffered.
+PDK_EXPORT int pdk_q4k_gemv_shard_sync(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
+                                       const void* const* flag_ptrs, void* ctr, uint32_t n_ranks, uint32_t rank,
+                                       uint32_t row0, uint32_t step, uint32_t in_dim, uint32_t out_dim, void* stream) {
+    return shard_launch(data, scales, x, y_ptrs, flag_ptrs, ctr, n_ranks, rank, row0, step, true, in_dim, out_dim,
+                        (cudaStream_t)stream);
+}
+
+// Waits on the device (one small kernel in `stream`) until every one of the n_ranks <= 8 flag
+// words of `flags` (this rank's own 16-word flag array) has reached the step: `step`, or, when
+// that is 0, one more than the array's count of such waits (word 8), which the kernel advances.
+// The wait is bounded: after budget_us microseconds (1 .. 10,000,000) the kernel records
+// 0x16 << 8 | rank-that-is-late in the device error word (pdk_device_error) and returns; the
+// context stays usable.  What follows in the stream sees every rank's band of that step.
+PDK_EXPORT int pdk_peer_flags_wait(void* flags, uint32_t n_ranks, uint32_t step, uint32_t budget_us, void* stream) {
+    if (flags == nullptr || n_ranks == 0u || n_ranks > 8u || budget_us == 0u || budget_us > 10000000u ||
+        !pdk_aligned(flags, 4))
+        return cudaErrorInvalidValue;
+    unsigned int* err = pdk_error_word();
+    if (err == nullptr) return (int)cudaErrorUnknown;
+    return pdk_launch_pdl(peer_flags_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (uint32_t*)flags, n_ranks, step,
+                          (unsigned long long)budget_us * 1000ull, err);
 }

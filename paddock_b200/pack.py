@@ -115,6 +115,8 @@ _EXTRA_SIGS = {
     "pdk_mxfp4_moe_down": "ppppppppppuuuuu",
     "pdk_mxfp4_moe_down_combine_static": "ppppppppppuuuuuu",
     "pdk_q4k_gemv_shard": "ppppuuuu",
+    "pdk_q4k_gemv_shard_sync": "ppppppuuuuuu",
+    "pdk_peer_flags_wait": "puuu",
     "pdk_selftest_bounded_wait": "up",
     "pdk_mxfp4_tc5_tile_scales": "pppuuu",
     "pdk_moe_prep_act_f4": "pppppppuuuuff",

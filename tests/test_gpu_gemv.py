@@ -385,3 +385,54 @@ def test_small_batch_scratch_is_per_stream(pack):
     assert torch.equal(y3, outs[0])                 # the third stream now runs the scratch route too
     for st in streams[1:]:
         rel(st.cuda_stream)
+
+
+def test_q4k_gemv_shard_sync_raises_flags_and_wait_is_bounded(pack):
+    """The sharded GEMV with its completion signal, two "ranks" played on one GPU (both y vectors and
+    both flag arrays are local): the band lands in both outputs, word `rank` of both flag arrays
+    reads the step, the CTA counter is back at zero, a wait for that step returns at once, and a
+    wait for a step nobody signals gives up after its budget with its code in the error word.
+    Explicit step numbers first, then the self-counting form a captured launch replays."""
+    import ctypes
+    k, n, row0 = 5120, 1030, 64
+    w = oracle.fill_normal(n * k, seed_for(2, 950), 0.02)
+    x = bf16_activations(k, seed_for(2, 951))
+    raw, d_data, d_sc = q4k_planes(pack, w, n, k)
+    ys = [torch.full((row0 + n + 8,), 3.0, dtype=torch.float32, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(2)]
+    ctr = torch.zeros(2, dtype=torch.int32, device="cuda")
+    yp = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in ys])
+    fp = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in flags])
+    d_x = dev_f32(x)
+    for step in (1, 2, 7):
+        pack.call("pdk_q4k_gemv_shard_sync", d_data, d_sc, d_x, ctypes.addressof(yp), ctypes.addressof(fp), ctr, 2, 1,
+                  row0, step, k, n)
+        torch.cuda.synchronize()
+        assert [int(f[1]) for f in flags] == [step, step] and [int(f[0]) for f in flags] == [0, 0]
+        assert ctr.tolist() == [0, 0]
+    assert pack.device_error() == 0
+    ref, ab = oracle.matmul_f64(oracle.dequant_q4_k(raw), x, k, n, 1, with_abs=True)
+    for y in ys:
+        got = y.cpu().numpy()
+        assert (got[:row0] == 3.0).all() and (got[row0 + n:] == 3.0).all()
+        assert cond_err(got[row0:row0 + n], ref[0], ab[0]) < 1e-5
+    # a wait on word 1 for the step that was signalled passes; for the next step it runs out of budget
+    only1 = flags[0][1:]
+    pack.call("pdk_peer_flags_wait", only1, 1, 7, 1000)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    pack.call("pdk_peer_flags_wait", only1, 1, 8, 2000)                    # 2 ms budget, nobody signals step 8
+    torch.cuda.synchronize()
+    assert pack.device_error() == (0x16 << 8 | 0)
+    assert pack.status("pdk_peer_flags_wait", only1, 9, 1, 1000) == 1       # more than 8 ranks
+    # self-counting steps: rank 0 of one, three launches and three waits, arguments unchanged
+    flags1 = torch.zeros(16, dtype=torch.int32, device="cuda")
+    ctr1 = torch.zeros(2, dtype=torch.int32, device="cuda")
+    fp1 = (ctypes.c_void_p * 1)(flags1.data_ptr())
+    for i in range(3):
+        pack.call("pdk_q4k_gemv_shard_sync", d_data, d_sc, d_x, ctypes.addressof(yp), ctypes.addressof(fp1), ctr1, 1, 0,
+                  row0, 0, k, n)
+        pack.call("pdk_peer_flags_wait", flags1, 1, 0, 100000)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    assert int(flags1[0]) == 3 and int(flags1[8]) == 3 and ctr1.tolist() == [0, 3]
