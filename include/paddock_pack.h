@@ -88,7 +88,12 @@ enum PdkSlot {
     PDK_SLOT_quantize_q8_sums = 218,
     PDK_SLOT_kquant_gemv_w4a8 = 217,
     PDK_SLOT_kquant_gemm_mma_ks = 212,
-    PDK_SLOT_kquant_gemm_w4a8_sb = 837
+    PDK_SLOT_kquant_gemm_w4a8_sb = 837,
+    PDK_SLOT_mxfp4_moe_gate_up_mmq = 88,
+    PDK_SLOT_mxfp4_moe_down_mmq = 89,
+    PDK_SLOT_mxfp4_moe_gate_up_dp4a_b = 92,
+    PDK_SLOT_mxfp4_moe_down_dp4a_b = 93,
+    PDK_SLOT_mxfp4_gu_interleave = 155
 };
 
 /* ---- the drop-in boundary ------------------------------------------------ */
@@ -241,6 +246,37 @@ int pd_moe_align_bm(const void* idx, void* sorted_row, void* sorted_slot, void* 
  * part[t*n_active + slot]; f32, embd % 4 == 0. */
 int pd_moe_slot_combine(const void* part, void* residual, uint32_t embd, uint32_t n_active, uint32_t rows,
                         void* stream);
+/* slot 155, packs/cuda/src/gemm/f32_qkv.cuh:1474-1505 (caller gpt_oss.rs:715-735): fuse the
+ * repacked gate and up planes (n_kb 16-byte blocks per row) into one plane of `rows` rows with row
+ * pitch ceil(n_kb / 4) * 128 bytes.  The fused plane is only ever read by slots of the same pack,
+ * so its contents are the pack's own: here a row is [gate row | up row | padding]. */
+int pd_mxfp4_gu_interleave(const void* gate, const void* up, void* dst, uint32_t n_kb, uint64_t rows, void* stream);
+/* slot 88, packs/cuda/src/moe/mmq.cuh:550-571: gate + up + SwiGLU (xg * sigmoid(alpha xg) * (yu + up_add))
+ * over the 32-row blocks of pd_moe_align.  gate_data = the fused plane of slot 155 (up_data, the
+ * engine's dummy, is not read); xq int8[tokens][in_dim], xs f32[tokens][in_dim/32]; the result
+ * leaves as fq int8[max_blocks*32][ff] with fs f32[..][ff/32] (amax / 127 per 32, round to nearest). */
+int pd_mxfp4_moe_gate_up_mmq(const void* gate_data, const void* gate_scale, const void* gate_bias, const void* up_data,
+                             const void* up_scale, const void* up_bias, const void* sorted_row,
+                             const void* block_expert, const void* xq, const void* xs, void* fq, void* fs,
+                             uint32_t in_dim, uint32_t ff, uint32_t max_blocks, float alpha, float limit, float up_add,
+                             void* stream);
+/* slot 89, packs/cuda/src/moe/mmq.cuh:592-626: part f32[rows*n_active][embd] = topk_w * (W_down h + bias)
+ * per (token, slot), h = the fq / fs of slot 88. */
+int pd_mxfp4_moe_down_mmq(const void* down_data, const void* down_scale, const void* down_bias, const void* sorted_row,
+                          const void* sorted_slot, const void* block_expert, const void* topk_w, const void* fq,
+                          const void* fs, void* part, uint32_t ff, uint32_t embd, uint32_t n_active,
+                          uint32_t max_blocks, void* stream);
+/* slots 92 / 93, packs/cuda/src/gemm/f32_qkv.cuh:370-398: the unsorted decode pair (the engine's
+ * route up to 8 tokens on this GPU, gpt_oss.rs:104-135): pair (token, slot) reads expert idx[pair].
+ * gate_up: out f32[batch][n_active][ff], SwiGLU with up + 1.  down: residual f32[batch][embd] +=
+ * the token's slots in order; at most 262,144 f32 of per-pair rows (batch*n_active*embd). */
+int pd_mxfp4_moe_gate_up_dp4a_b(const void* gate_data, const void* gate_scale, const void* gate_bias,
+                                const void* up_data, const void* up_scale, const void* up_bias, const void* idx,
+                                const void* xq, const void* xs, void* out, uint32_t in_dim, uint32_t ff,
+                                uint32_t n_active, uint32_t batch, float alpha, float limit, void* stream);
+int pd_mxfp4_moe_down_dp4a_b(const void* down_data, const void* down_scale, const void* down_bias, const void* idx,
+                             const void* topk_w, const void* fused_q, const void* fused_s, void* residual, uint32_t ff,
+                             uint32_t embd, uint32_t n_active, uint32_t batch, void* stream);
 /* No slot.  Activation step in front of the expert GEMMs; the reference quantizes to int8 at this
  * point (pd_quantize_q8, packs/cuda/src/attn/decode.cuh:2981-3004).  x f32[rows][dim] ->
  * xq f16[rows][dim] (2*dim bytes per row, mma fragment order) + xscale f32[rows] (power-of-two

@@ -101,6 +101,11 @@ static void fill_table() {
     PDK_SET(kquant_gemv_w4a8);
     PDK_SET(kquant_gemm_mma_ks);
     PDK_SET(kquant_gemm_w4a8_sb);
+    PDK_SET(mxfp4_gu_interleave);
+    PDK_SET(mxfp4_moe_gate_up_mmq);
+    PDK_SET(mxfp4_moe_down_mmq);
+    PDK_SET(mxfp4_moe_gate_up_dp4a_b);
+    PDK_SET(mxfp4_moe_down_dp4a_b);
 #undef PDK_SET
 }
 

@@ -67,6 +67,15 @@ struct Args {
     float* out;               // GATED: h [max_blocks*BM][out_dim];  else part [rows*n_active][out_dim]
     uint32_t in_dim, out_dim, n_active;
     float alpha, limit;
+    // ---- the reference's slot operands (pd_mxfp4_moe_*_mmq / *_dp4a_b), all zero on the pdk_ entry points
+    const int8_t* xq8;        // int8 activations [src rows][in_dim] with xs32 f32 [src rows][in_dim/32] instead of xq / xscale
+    const float* xs32;
+    int8_t* out8;             // GATED: h as int8 [max_blocks*BM][out_dim] with outs f32 [..][out_dim/32] instead of `out`
+    float* outs;
+    uint32_t w0_pitch, w1_pitch;  // bytes between the rows of the data planes (0 = in_dim/2: a plain plane)
+    uint32_t direct;          // 1: block b is pair b (one token), its expert block_expert[b], its source row b / n_active
+                              // (GATED) or b (down), its output row b
+    float up_add;             // SwiGLU: (up + up_add)
 };
 
 // GATED: two planes + SwiGLU, activations gathered through sorted_row, output
@@ -88,6 +97,8 @@ moe_mxfp4_kernel(const Args a) {
     float* red = reinterpret_cast<float*>(smem + (size_t)BM * pitch);  // [2][SLOTS][KS][32][NP*NT*4]
     __shared__ uint32_t s_src[BM];
     __shared__ float s_scale[BM];
+    __shared__ float s_inv[BM];
+    __shared__ uint32_t s_amax[BM];
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3u;
@@ -96,12 +107,15 @@ moe_mxfp4_kernel(const Args a) {
     // ---- stage the block's activations
     if (tid < BM) {
         const uint32_t pos = block * BM + tid;
-        const uint32_t src = GATED ? a.sorted_row[pos] : (a.sorted_row[pos] == PDK_MOE_PAD ? PDK_MOE_PAD : pos);
+        uint32_t src;
+        if (a.direct) src = tid == 0u ? (GATED ? block / a.n_active : block) : PDK_MOE_PAD;
+        else src = GATED ? a.sorted_row[pos] : (a.sorted_row[pos] == PDK_MOE_PAD ? PDK_MOE_PAD : pos);
         s_src[tid] = src;
-        s_scale[tid] = src == PDK_MOE_PAD ? 0.0f : a.xscale[src];
+        s_scale[tid] = (src == PDK_MOE_PAD || a.xq8) ? 0.0f : a.xscale[src];
+        s_amax[tid] = 0u;
     }
     __syncthreads();
-    {
+    if (a.xq8 == nullptr) {
         const uint32_t chunks = in_dim >> 3;  // 16-byte chunks per token
         for (uint32_t i = tid; i < BM * chunks; i += blockDim.x) {
             const uint32_t tok = i / chunks, c = i % chunks;
@@ -109,6 +123,50 @@ moe_mxfp4_kernel(const Args a) {
             if (s_src[tok] != PDK_MOE_PAD)
                 v = *reinterpret_cast<const uint4*>(a.xq + (size_t)s_src[tok] * in_dim * 2u + (size_t)c * 16u);
             *reinterpret_cast<uint4*>(xs + (size_t)tok * pitch + (size_t)c * 16u) = v;
+        }
+    } else {
+        // int8 activations with one f32 scale per 32: the row's largest |q * s| picks a power-of-two
+        // step for the row, then q * s / step is rounded to f16 (11 bits against the operand's 7) and
+        // laid out in fragment order, as pdk_moe_prep_act would have
+        for (uint32_t i = tid; i < BM * nblk; i += blockDim.x) {
+            const uint32_t tok = i / nblk, kb = i % nblk, src = s_src[tok];
+            if (src == PDK_MOE_PAD) continue;
+            const int4 q0 = *reinterpret_cast<const int4*>(a.xq8 + (size_t)src * in_dim + (size_t)kb * 32u);
+            const int4 q1 = *reinterpret_cast<const int4*>(a.xq8 + (size_t)src * in_dim + (size_t)kb * 32u + 16u);
+            const int w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            int m = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) m = max(m, abs((int)(int8_t)(w[j] >> (8 * b))));
+            const float v = (float)m * fabsf(a.xs32[(size_t)src * nblk + kb]);
+            if (v == v && v < 3.0e38f) atomicMax(&s_amax[tok], __float_as_uint(v));
+        }
+        __syncthreads();
+        if (tid < BM) {
+            const float amax = __uint_as_float(s_amax[tid]);
+            int e = 0;
+            if (amax > 0.0f) e = max((int)(__float_as_uint(amax) >> 23) - 126 - 15, -100);   // amax / 2^e in [2^14, 2^15)
+            s_scale[tid] = s_src[tid] == PDK_MOE_PAD ? 0.0f : __uint_as_float((uint32_t)(e + 127) << 23);
+            s_inv[tid] = __uint_as_float((uint32_t)(127 - e) << 23);
+        }
+        __syncthreads();
+        for (uint32_t i = tid; i < BM * nblk * 4u; i += blockDim.x) {   // one thread per (token, block, t): 8 elements
+            const uint32_t tok = i / (nblk * 4u), r = i % (nblk * 4u), kb = r >> 2, tt = r & 3u, src = s_src[tok];
+            uint4 o = make_uint4(0u, 0u, 0u, 0u);
+            if (src != PDK_MOE_PAD) {
+                const int8_t* q = a.xq8 + (size_t)src * in_dim + (size_t)kb * 32u;
+                const int lo = *reinterpret_cast<const int*>(q + 4u * tt), hi = *reinterpret_cast<const int*>(q + 16u + 4u * tt);
+                const float f = a.xs32[(size_t)src * nblk + kb] * s_inv[tok];
+                auto el = [&](int wv, int b) { return (float)(int8_t)(wv >> (8 * b)) * f; };
+                const __half2 h0 = __floats2half2_rn(el(lo, 0), el(lo, 2)), h1 = __floats2half2_rn(el(lo, 1), el(lo, 3));
+                const __half2 h2 = __floats2half2_rn(el(hi, 0), el(hi, 2)), h3 = __floats2half2_rn(el(hi, 1), el(hi, 3));
+                o.x = *reinterpret_cast<const uint32_t*>(&h0);
+                o.y = *reinterpret_cast<const uint32_t*>(&h1);
+                o.z = *reinterpret_cast<const uint32_t*>(&h2);
+                o.w = *reinterpret_cast<const uint32_t*>(&h3);
+            }
+            *reinterpret_cast<uint4*>(xs + (size_t)tok * pitch + (size_t)kb * 64u + tt * 16u) = o;
         }
     }
     __syncthreads();
@@ -125,13 +183,14 @@ moe_mxfp4_kernel(const Args a) {
         const uint32_t r0 = min(tile * 16u + g, out_dim - 1u), r1 = min(tile * 16u + g + 8u, out_dim - 1u);
         const uint8_t* d[NP][2];
         const uint8_t* s[NP][2];
-        d[0][0] = a.w0_data + (plane_rows + r0) * nblk * 16u;
-        d[0][1] = a.w0_data + (plane_rows + r1) * nblk * 16u;
+        const size_t p0 = a.w0_pitch ? a.w0_pitch : nblk * 16u, p1 = a.w1_pitch ? a.w1_pitch : nblk * 16u;
+        d[0][0] = a.w0_data + (plane_rows + r0) * p0;
+        d[0][1] = a.w0_data + (plane_rows + r1) * p0;
         s[0][0] = a.w0_scale + (plane_rows + r0) * nblk;
         s[0][1] = a.w0_scale + (plane_rows + r1) * nblk;
         if (GATED) {
-            d[NP - 1][0] = a.w1_data + (plane_rows + r0) * nblk * 16u;
-            d[NP - 1][1] = a.w1_data + (plane_rows + r1) * nblk * 16u;
+            d[NP - 1][0] = a.w1_data + (plane_rows + r0) * p1;
+            d[NP - 1][1] = a.w1_data + (plane_rows + r1) * p1;
             s[NP - 1][0] = a.w1_scale + (plane_rows + r0) * nblk;
             s[NP - 1][1] = a.w1_scale + (plane_rows + r1) * nblk;
         }
@@ -274,37 +333,86 @@ moe_mxfp4_kernel(const Args a) {
         }
 
         // ---- epilogue: lane holds rows (g, g+8) x tokens (n*8 + 2t, +1)
+        float hv[NT][4];
 #pragma unroll
         for (uint32_t n = 0; n < NT; ++n)
 #pragma unroll
             for (uint32_t q = 0; q < 4u; ++q) {
                 const uint32_t row = tile * 16u + g + (q >> 1) * 8u;
                 const uint32_t tok = n * 8u + 2u * t + (q & 1u);
+                hv[n][q] = 0.0f;
                 if (row >= out_dim || s_src[tok] == PDK_MOE_PAD) continue;
                 const float xsc = s_scale[tok];
                 float v0 = acc[0][n][q] * xsc;
                 if (a.w0_bias) v0 += a.w0_bias[plane_rows + row];
+                const size_t orow = a.direct ? block : (size_t)block * BM + tok;
                 if (GATED) {
                     float v1 = acc[NP - 1][n][q] * xsc;
                     if (a.w1_bias) v1 += a.w1_bias[plane_rows + row];
-                    // SwiGLU, OpenAI variant: gate clamped from above, up symmetrically, up + 1
+                    // SwiGLU, OpenAI variant: gate clamped from above, up symmetrically, up + up_add
                     const float xg = fminf(v0, a.limit);
                     const float yu = fminf(fmaxf(v1, -a.limit), a.limit);
-                    const float h = (xg / (1.0f + __expf(-a.alpha * xg))) * (yu + 1.0f);
-                    a.out[((size_t)block * BM + tok) * out_dim + row] = h;
+                    const float h = (xg / (1.0f + __expf(-a.alpha * xg))) * (yu + a.up_add);
+                    hv[n][q] = h;
+                    if (a.out8 == nullptr) a.out[orow * out_dim + row] = h;
                 } else {
                     const uint32_t pos = block * BM + tok;
-                    const uint32_t pair = a.sorted_row[pos] * a.n_active + a.sorted_slot[pos];
+                    const uint32_t pair = a.direct ? block : a.sorted_row[pos] * a.n_active + a.sorted_slot[pos];
                     a.out[(size_t)pair * out_dim + row] = a.topk_w[pair] * v0;
                 }
             }
+        if (GATED && KS == 1u && a.out8 != nullptr) {
+            // h leaves as int8 with one f32 scale per 32 consecutive rows of a token (the slot's
+            // hand-off to the down GEMM): tiles 2j and 2j + 1 belong to neighbouring warps, which
+            // exchange their per-token maxima through shared memory (out_dim % 32 == 0, so both
+            // take the same trips round this loop)
+            float cm[NT][2];
+#pragma unroll
+            for (uint32_t n = 0; n < NT; ++n)
+#pragma unroll
+                for (uint32_t j = 0; j < 2u; ++j) {
+                    float m = fmaxf(fabsf(hv[n][j]), fabsf(hv[n][2u + j]));
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+                    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+                    cm[n][j] = m;
+                }
+            float* pb = red + ((size_t)(iter & 1u) * SLOTS + slot) * BM;       // `red` is unused when KS == 1
+            const float* partner = red + ((size_t)(iter & 1u) * SLOTS + (slot ^ 1u)) * BM;
+            if (g == 0u)
+#pragma unroll
+                for (uint32_t n = 0; n < NT; ++n) {
+                    pb[n * 8u + 2u * t] = cm[n][0];
+                    pb[n * 8u + 2u * t + 1u] = cm[n][1];
+                }
+            bar_sync(8u + (slot >> 1), 64u);
+            const uint32_t nb32 = out_dim >> 5;
+#pragma unroll
+            for (uint32_t n = 0; n < NT; ++n)
+#pragma unroll
+                for (uint32_t j = 0; j < 2u; ++j) {
+                    const uint32_t tok = n * 8u + 2u * t + j;
+                    if (s_src[tok] == PDK_MOE_PAD) continue;
+                    const float amax = fmaxf(cm[n][j], partner[tok]);
+                    const float d = amax / 127.0f, id = d > 0.0f ? 1.0f / d : 0.0f;
+                    const size_t orow = (size_t)block * BM + tok;
+                    if (g == 0u && (slot & 1u) == 0u) a.outs[orow * nb32 + (tile >> 1)] = d;
+#pragma unroll
+                    for (uint32_t h = 0; h < 2u; ++h) {
+                        const uint32_t row = tile * 16u + g + h * 8u;
+                        const int q = max(-127, min(127, __float2int_rn(hv[n][2u * h + j] * id)));
+                        a.out8[orow * out_dim + row] = (int8_t)q;
+                    }
+                }
+        }
     }
 }
 
 template <uint32_t NT, uint32_t SLOTS, uint32_t KS, bool GATED>
 int launch_cfg(const Args& a, uint32_t max_blocks, cudaStream_t st, uint32_t waves = 2u) {
     constexpr uint32_t BM = NT * 8u, NP = GATED ? 2u : 1u;
-    const size_t smem = (size_t)BM * (a.in_dim * 2u + 64u) + (KS > 1u ? (size_t)2u * SLOTS * KS * 32u * NP * NT * 4u * 4u : 0u);
+    const size_t smem = (size_t)BM * (a.in_dim * 2u + 64u) +
+                        (KS > 1u ? (size_t)2u * SLOTS * KS * 32u * NP * NT * 4u * 4u : (size_t)2u * SLOTS * BM * 4u);
     if (smem > 220u * 1024u) return cudaErrorNotSupported;
     auto kern = moe_mxfp4_kernel<NT, SLOTS, KS, GATED>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -335,7 +443,8 @@ bool wide_decode(const Args& a, uint32_t max_blocks) {
 int check_common(const Args& a, uint32_t bm, uint32_t max_blocks) {
     if (bm != 8u && bm != 32u) return cudaErrorInvalidValue;
     if (a.in_dim == 0u || (a.in_dim & 31u) != 0u || a.out_dim == 0u || max_blocks == 0u) return cudaErrorInvalidValue;
-    if (!pdk_aligned(a.w0_data, 4) || !pdk_aligned(a.xq, 16) || !pdk_aligned(a.out, 4)) return cudaErrorInvalidValue;
+    if (!pdk_aligned(a.w0_data, 4) || !pdk_aligned(a.xq, 16) || !pdk_aligned(a.xq8, 16) || !pdk_aligned(a.out, 4))
+        return cudaErrorInvalidValue;
     if (max_blocks > 65535u) return cudaErrorInvalidValue;
     return 0;
 }
@@ -355,7 +464,7 @@ PDK_EXPORT int pdk_mxfp4_moe_gate_up(const void* gate_data, const void* gate_sca
     a.w1_data = (const uint8_t*)up_data; a.w1_scale = (const uint8_t*)up_scale; a.w1_bias = (const float*)up_bias;
     a.sorted_row = (const uint32_t*)sorted_row; a.block_expert = (const uint32_t*)block_expert;
     a.xq = (const uint8_t*)xq; a.xscale = (const float*)xscale; a.out = (float*)h;
-    a.in_dim = in_dim; a.out_dim = ff; a.alpha = alpha; a.limit = limit;
+    a.in_dim = in_dim; a.out_dim = ff; a.alpha = alpha; a.limit = limit; a.up_add = 1.0f;
     if (max_blocks == 0) return 0;
     if (int rc = check_common(a, bm, max_blocks)) return rc;
     if (!pdk_aligned(up_data, 4)) return cudaErrorInvalidValue;
@@ -384,4 +493,147 @@ PDK_EXPORT int pdk_mxfp4_moe_down(const void* down_data, const void* down_scale,
     if (bm == 8u) return wide_decode(a, max_blocks) ? launch_cfg<1, 16, 1, false>(a, max_blocks, st, 4u)
                                                       : launch_cfg<1, 4, 4, false>(a, max_blocks, st);
     return launch_cfg<4, 16, 1, false>(a, max_blocks, st);
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// The reference's own MoE slots for MXFP4 experts, served by the kernel above with int8
+// activations staged as f16 (11 bits for the operand's 7) and, between gate|up and down, h handed
+// over as int8 with one f32 scale per 32, exactly the buffers the engine allocates.
+//
+// The gate and up planes reach these slots fused into one plane by slot 155, whose contents are
+// private to the pack.  This pack's fused row is [gate row | up row | padding to the reference's
+// pitch]: both halves stay plain 16-byte-block rows, so the GEMM reads them like any other plane.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+__global__ void gu_interleave_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ dst,
+                                     uint32_t n_kb, uint64_t total) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one 16-byte block of gate and of up
+    if (i >= total) return;
+    const uint64_t r = i / n_kb;
+    const uint32_t b = (uint32_t)(i % n_kb);
+    const uint64_t pitch16 = (uint64_t)((n_kb + 3u) >> 2) * 8u;           // row pitch in 16-byte units
+    dst[r * pitch16 + b] = gate[i];
+    dst[r * pitch16 + n_kb + b] = up[i];
+}
+
+inline uint32_t fused_pitch(uint32_t in_dim) { return (((in_dim >> 5) + 3u) >> 2) * 128u; }
+
+// per-(device, stream) scratch of the decode pair: part f32 [batch * n_active][embd]
+constexpr size_t kPairPartBytes = 1u << 20;
+__device__ __align__(256) uint8_t g_pair_part[2][kPairPartBytes];
+PDK_SLICE_TABLE(pair_part_table, g_pair_part, kPairPartBytes, 2);
+
+}  // namespace
+
+// slot 155, packs/cuda/src/gemm/f32_qkv.cuh:1474-1505: gate and up planes (16-byte blocks,
+// n_kb per row) -> one plane of `rows` rows with the reference's pitch ceil(n_kb / 4) * 128.
+PDK_EXPORT int pd_mxfp4_gu_interleave(const void* gate, const void* up, void* dst, uint32_t n_kb, uint64_t rows,
+                                      void* stream) {
+    if (rows == 0 || n_kb == 0) return 0;
+    if (!pdk_aligned(gate, 16) || !pdk_aligned(up, 16) || !pdk_aligned(dst, 16)) return cudaErrorInvalidValue;
+    const uint64_t total = rows * n_kb;
+    if ((total + 255u) / 256u > 0x7fffffffull) return cudaErrorInvalidValue;
+    gu_interleave_kernel<<<(uint32_t)((total + 255u) / 256u), 256, 0, (cudaStream_t)stream>>>(
+        (const uint4*)gate, (const uint4*)up, (uint4*)dst, n_kb, total);
+    return pdk_launch_status();
+}
+
+// slot 88, packs/cuda/src/moe/mmq.cuh:550-571: gate + up + SwiGLU over 32-row expert blocks.
+// gate_data = the fused plane of slot 155 (up_data is the engine's 16-byte dummy and is not
+// read), xq int8 [tokens][in_dim] with xs f32 per 32, fq int8 [max_blocks*32][ff] with fs f32 per 32.
+PDK_EXPORT int pd_mxfp4_moe_gate_up_mmq(const void* gate_data, const void* gate_scale, const void* gate_bias,
+                                        const void* up_data, const void* up_scale, const void* up_bias,
+                                        const void* sorted_row, const void* block_expert, const void* xq, const void* xs,
+                                        void* fq, void* fs, uint32_t in_dim, uint32_t ff, uint32_t max_blocks, float alpha,
+                                        float limit, float up_add, void* stream) {
+    (void)up_data;
+    if (ff == 0 || max_blocks == 0) return 0;
+    if ((in_dim & 31u) || (ff & 31u) || in_dim == 0u) return cudaErrorInvalidValue;
+    if (!pdk_aligned(gate_data, 16) || !pdk_aligned(xs, 4) || !pdk_aligned(fq, 4) || !pdk_aligned(fs, 4))
+        return cudaErrorInvalidValue;
+    Args a{};
+    a.w0_data = (const uint8_t*)gate_data; a.w0_scale = (const uint8_t*)gate_scale; a.w0_bias = (const float*)gate_bias;
+    a.w1_data = (const uint8_t*)gate_data + (size_t)(in_dim >> 5) * 16u; a.w1_scale = (const uint8_t*)up_scale;
+    a.w1_bias = (const float*)up_bias;
+    a.w0_pitch = a.w1_pitch = fused_pitch(in_dim);
+    a.sorted_row = (const uint32_t*)sorted_row; a.block_expert = (const uint32_t*)block_expert;
+    a.xq8 = (const int8_t*)xq; a.xs32 = (const float*)xs; a.out8 = (int8_t*)fq; a.outs = (float*)fs;
+    a.out = (float*)fs;   // not written on this path; check_common wants a pointer
+    a.in_dim = in_dim; a.out_dim = ff; a.alpha = alpha; a.limit = limit; a.up_add = up_add;
+    if (int rc = check_common(a, 32u, max_blocks)) return rc;
+    return launch_cfg<4, 16, 1, true>(a, max_blocks, (cudaStream_t)stream);
+}
+
+// slot 89, packs/cuda/src/moe/mmq.cuh:592-626: down projection of the int8 h of slot 88 into
+// per-(token, slot) rows part f32 [rows * n_active][embd], each times its routing weight.
+PDK_EXPORT int pd_mxfp4_moe_down_mmq(const void* down_data, const void* down_scale, const void* down_bias,
+                                     const void* sorted_row, const void* sorted_slot, const void* block_expert,
+                                     const void* topk_w, const void* fq, const void* fs, void* part, uint32_t ff,
+                                     uint32_t embd, uint32_t n_active, uint32_t max_blocks, void* stream) {
+    if (embd == 0 || max_blocks == 0) return 0;
+    if ((ff & 31u) || ff == 0u) return cudaErrorInvalidValue;
+    if (!pdk_aligned(fs, 4)) return cudaErrorInvalidValue;
+    Args a{};
+    a.w0_data = (const uint8_t*)down_data; a.w0_scale = (const uint8_t*)down_scale; a.w0_bias = (const float*)down_bias;
+    a.sorted_row = (const uint32_t*)sorted_row; a.sorted_slot = (const uint32_t*)sorted_slot;
+    a.block_expert = (const uint32_t*)block_expert; a.topk_w = (const float*)topk_w;
+    a.xq8 = (const int8_t*)fq; a.xs32 = (const float*)fs; a.out = (float*)part;
+    a.in_dim = ff; a.out_dim = embd; a.n_active = n_active;
+    if (int rc = check_common(a, 32u, max_blocks)) return rc;
+    return launch_cfg<4, 16, 1, false>(a, max_blocks, (cudaStream_t)stream);
+}
+
+// slot 92, packs/cuda/src/gemm/f32_qkv.cuh:370-383: the decode form of gate + up + SwiGLU
+// (up + 1): no sorting, pair (token, slot) reads expert idx[pair]; out f32 [batch][n_active][ff].
+PDK_EXPORT int pd_mxfp4_moe_gate_up_dp4a_b(const void* gate_data, const void* gate_scale, const void* gate_bias,
+                                           const void* up_data, const void* up_scale, const void* up_bias, const void* idx,
+                                           const void* xq, const void* xs, void* out, uint32_t in_dim, uint32_t ff,
+                                           uint32_t n_active, uint32_t batch, float alpha, float limit, void* stream) {
+    (void)up_data;
+    if (ff == 0 || n_active == 0 || batch == 0) return 0;
+    if ((in_dim & 31u) || in_dim == 0u) return cudaErrorInvalidValue;
+    if (!pdk_aligned(gate_data, 16) || !pdk_aligned(xs, 4)) return cudaErrorInvalidValue;
+    Args a{};
+    a.w0_data = (const uint8_t*)gate_data; a.w0_scale = (const uint8_t*)gate_scale; a.w0_bias = (const float*)gate_bias;
+    a.w1_data = (const uint8_t*)gate_data + (size_t)(in_dim >> 5) * 16u; a.w1_scale = (const uint8_t*)up_scale;
+    a.w1_bias = (const float*)up_bias;
+    a.w0_pitch = a.w1_pitch = fused_pitch(in_dim);
+    a.block_expert = (const uint32_t*)idx;
+    a.xq8 = (const int8_t*)xq; a.xs32 = (const float*)xs; a.out = (float*)out;
+    a.in_dim = in_dim; a.out_dim = ff; a.n_active = n_active; a.alpha = alpha; a.limit = limit; a.up_add = 1.0f;
+    a.direct = 1u;
+    const uint32_t pairs = batch * n_active;
+    if (int rc = check_common(a, 8u, pairs)) return rc;
+    auto st = (cudaStream_t)stream;
+    return wide_decode(a, pairs) ? launch_cfg<1, 16, 1, true>(a, pairs, st, 4u) : launch_cfg<1, 4, 4, true>(a, pairs, st);
+}
+
+// slot 93, packs/cuda/src/gemm/f32_qkv.cuh:385-398: the decode form of down: residual f32
+// [batch][embd] += sum over a token's slots, in slot order, of weight * (W_down h + bias), with h
+// int8 [batch * n_active][ff] and one f32 scale per 32.  The per-pair rows pass through a
+// library-resident scratch slice (1 MiB per stream, two streams per device: 801 beyond either).
+PDK_EXPORT int pd_mxfp4_moe_down_dp4a_b(const void* down_data, const void* down_scale, const void* down_bias,
+                                        const void* idx, const void* topk_w, const void* fused_q, const void* fused_s,
+                                        void* residual, uint32_t ff, uint32_t embd, uint32_t n_active, uint32_t batch,
+                                        void* stream) {
+    if (embd == 0 || n_active == 0 || batch == 0) return 0;
+    if ((ff & 31u) || ff == 0u || (embd & 3u)) return cudaErrorInvalidValue;
+    if (!pdk_aligned(fused_s, 4) || !pdk_aligned(residual, 16)) return cudaErrorInvalidValue;
+    const uint64_t pairs = (uint64_t)batch * n_active;
+    if (pairs > 65535u || pairs * embd * sizeof(float) > kPairPartBytes) return cudaErrorNotSupported;
+    auto st = (cudaStream_t)stream;
+    float* part = reinterpret_cast<float*>(pair_part_table.slice(st));
+    if (part == nullptr) return cudaErrorNotSupported;
+    Args a{};
+    a.w0_data = (const uint8_t*)down_data; a.w0_scale = (const uint8_t*)down_scale; a.w0_bias = (const float*)down_bias;
+    a.block_expert = (const uint32_t*)idx; a.topk_w = (const float*)topk_w;
+    a.xq8 = (const int8_t*)fused_q; a.xs32 = (const float*)fused_s; a.out = part;
+    a.in_dim = ff; a.out_dim = embd; a.n_active = n_active; a.direct = 1u;
+    if (int rc = check_common(a, 8u, (uint32_t)pairs)) return rc;
+    const int rc = wide_decode(a, (uint32_t)pairs) ? launch_cfg<1, 16, 1, false>(a, (uint32_t)pairs, st, 4u)
+                                                   : launch_cfg<1, 4, 4, false>(a, (uint32_t)pairs, st);
+    if (rc != 0) return rc;
+    return pd_moe_slot_combine(part, residual, embd, n_active, batch, stream);
 }

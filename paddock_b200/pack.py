@@ -105,6 +105,9 @@ _SIGS = {
     "kquant_dequant": "ppUu", "kquant_repack": "pppUu", "kquant_gemv": "ppppuuu",
     "quantize_q8": "pppu", "quantize_q8_sums": "ppppu", "kquant_gemv_w4a8": "ppppppuuu",
     "kquant_gemm_mma_ks": "pppppppuuuu", "kquant_gemm_w4a8_sb": "pppppppuuuu",
+    "mxfp4_gu_interleave": "pppuU", "mxfp4_moe_gate_up_mmq": "pppppppppppp" + "uuu" + "fff",
+    "mxfp4_moe_down_mmq": "pppppppppp" + "uuuu", "mxfp4_moe_gate_up_dp4a_b": "pppppppppp" + "uuuu" + "ff",
+    "mxfp4_moe_down_dp4a_b": "pppppppp" + "uuuu",
 }
 _EXTRA_SIGS = {
     "pdk_kquant_gemm_f32": "ppppuuuu",

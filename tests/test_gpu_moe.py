@@ -201,3 +201,109 @@ def test_nvf4_moe_block_matches_f64(pack, tokens, n_expert, k, embd, ff, bm, gat
     y = out.cpu().numpy().reshape(tokens, embd)
     assert np.isfinite(y).all()
     assert rel_l2(y, ref) < 2e-3 < TOL
+
+
+# ---- the reference's own MoE slots (155 / 88 / 89 and the decode pair 92 / 93): int8 activations
+
+def _q8_roundtrip(v):
+    """What pd_quantize_q8 keeps of a vector: per 32, d = amax / 127, q = round(v / d)."""
+    q, s, _ = oracle.quantize_q8_act(np.ascontiguousarray(v, np.float32).reshape(-1), with_sums=False)
+    return (q.astype(np.float32).reshape(-1, 32) * s[:, None]).reshape(np.shape(v)).astype(np.float64)
+
+
+def _slot_layer_ref(raw, x, idx, w, tokens, k, embd, ff, n_expert, quantized):
+    """f64 walk of the block over dequantized experts; quantized: activations pass through int8 where
+    the slot chain passes them (x before gate|up, h before down)."""
+    deq = {n: oracle.dequant_mxfp4(raw[n]).astype(np.float64) for n in raw}
+    wg, wu = deq["gate"].reshape(n_expert, ff, embd), deq["up"].reshape(n_expert, ff, embd)
+    wd = deq["down"].reshape(n_expert, embd, ff)
+    xx = _q8_roundtrip(x.reshape(tokens, embd)) if quantized else x.reshape(tokens, embd).astype(np.float64)
+    out = np.zeros((tokens, embd))
+    for t in range(tokens):
+        for s in range(k):
+            e = idx[t, s]
+            g, u = wg[e] @ xx[t], wu[e] @ xx[t]
+            xg, yu = np.minimum(g, 7.0), np.clip(u, -7.0, 7.0)
+            h = xg / (1.0 + np.exp(-1.702 * xg)) * (yu + 1.0)
+            if quantized:
+                h = _q8_roundtrip(h)
+            out[t] += w[t, s] * (wd[e] @ h)
+    return out
+
+
+def _fused_planes(pack, raw, n_expert, embd, ff):
+    ex = P.GpuExecutor(pack)
+    g, u, d = (P.repack_mxfp4(ex, dev(raw[n])) for n in ("gate", "up", "down"))
+    n_kb = embd // 32
+    fused = torch.zeros(n_expert * ff * ((n_kb + 3) // 4) * 128, dtype=torch.uint8, device="cuda")
+    pack.call("mxfp4_gu_interleave", g.data, u.data, fused, n_kb, n_expert * ff)
+    return fused, g.scale, u.scale, d
+
+
+@pytest.mark.parametrize("tokens,n_expert,k,embd,ff", [(9, 8, 2, 128, 160), (70, 4, 2, 256, 256), (40, 16, 4, 2880, 2880)])
+def test_moe_reference_slots_sorted_chain(pack, tokens, n_expert, k, embd, ff):
+    """quantize_q8 -> moe_align -> gate_up_mmq (88) -> down_mmq (89) -> slot_combine, the chain
+    crates/paddock-engine/src/gpu_model/gpt_oss.rs:2393-2440 runs above 8 tokens, on the plane slot 155 fused."""
+    raw, _ = make_layer(n_expert, embd, ff, 1300 + tokens + ff, False)
+    fused, gs, us, down = _fused_planes(pack, raw, n_expert, embd, ff)
+    x = oracle.bf16_round(oracle.fill_normal(tokens * embd, 1310, 1.0))
+    logits = oracle.fill_normal(tokens * n_expert, 1311, 1.0)
+    idx, w = oracle.moe_topk(logits, n_expert, k)
+    pairs, bm = tokens * k, 32
+    max_blocks = (pairs + n_expert * (bm - 1) + bm - 1) // bm
+    nb = max_blocks * bm
+    i32, f32 = torch.int32, torch.float32
+    d_idx, d_w = dev(idx.astype(np.uint32)).view(i32), dev_f32(w.reshape(-1))
+    s_row, s_slot = torch.zeros(nb, dtype=i32, device="cuda"), torch.zeros(nb, dtype=i32, device="cuda")
+    b_exp = torch.zeros(max_blocks, dtype=i32, device="cuda")
+    xq, xs = torch.zeros(tokens * embd, dtype=torch.int8, device="cuda"), torch.zeros(tokens * embd // 32, dtype=f32, device="cuda")
+    fq, fs = torch.zeros(nb * ff, dtype=torch.int8, device="cuda"), torch.zeros(nb * ff // 32, dtype=f32, device="cuda")
+    part = torch.zeros(pairs * embd, dtype=f32, device="cuda")
+    out = torch.zeros(tokens * embd, dtype=f32, device="cuda")
+    dummy = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    pack.call("moe_align", d_idx, s_row, s_slot, b_exp, tokens, k, n_expert, max_blocks)
+    pack.call("quantize_q8", dev_f32(x), xq, xs, tokens * embd)
+    pack.call("mxfp4_moe_gate_up_mmq", fused, gs, None, dummy, us, None, s_row, b_exp, xq, xs, fq, fs, embd, ff, max_blocks,
+              1.702, 7.0, 1.0)
+    pack.call("mxfp4_moe_down_mmq", down.data, down.scale, None, s_row, s_slot, b_exp, d_w, fq, fs, part, ff, embd, k,
+              max_blocks)
+    pack.call("moe_slot_combine", part, out, embd, k, tokens)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    y = out.cpu().numpy().reshape(tokens, embd)
+    assert np.isfinite(y).all()
+    same_class = _slot_layer_ref(raw, x, idx, w, tokens, k, embd, ff, n_expert, True)
+    exact = _slot_layer_ref(raw, x, idx, w, tokens, k, embd, ff, n_expert, False)
+    assert rel_l2(y, same_class) < 5e-3                 # the same int8 activations: what is left is f16 staging and rounding ties
+    assert rel_l2(y, exact) < 3e-2                      # the int8 activation class against the unquantized walk
+
+
+@pytest.mark.parametrize("tokens,n_expert,k,embd,ff", [(1, 8, 2, 128, 160), (3, 16, 4, 2880, 2880), (8, 4, 2, 256, 96)])
+def test_moe_reference_slots_decode_pair(pack, tokens, n_expert, k, embd, ff):
+    """quantize_q8 -> gate_up_dp4a_b (92) -> quantize_q8 -> down_dp4a_b (93): the unsorted chain of
+    gpt_oss.rs:2441-2480 for up to 8 tokens; the result accumulates into the residual."""
+    raw, _ = make_layer(n_expert, embd, ff, 1400 + tokens + ff, False)
+    fused, gs, us, down = _fused_planes(pack, raw, n_expert, embd, ff)
+    x = oracle.bf16_round(oracle.fill_normal(tokens * embd, 1410, 1.0))
+    logits = oracle.fill_normal(tokens * n_expert, 1411, 1.0)
+    idx, w = oracle.moe_topk(logits, n_expert, k)
+    pairs = tokens * k
+    f32 = torch.float32
+    d_idx, d_w = dev(idx.astype(np.uint32)).view(torch.int32), dev_f32(w.reshape(-1))
+    xq, xs = torch.zeros(tokens * embd, dtype=torch.int8, device="cuda"), torch.zeros(tokens * embd // 32, dtype=f32, device="cuda")
+    h = torch.zeros(pairs * ff, dtype=f32, device="cuda")
+    hq, hs = torch.zeros(pairs * ff, dtype=torch.int8, device="cuda"), torch.zeros(pairs * ff // 32, dtype=f32, device="cuda")
+    res0 = oracle.fill_normal(tokens * embd, 1412, 1.0)
+    res = dev_f32(res0)
+    dummy = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    pack.call("quantize_q8", dev_f32(x), xq, xs, tokens * embd)
+    pack.call("mxfp4_moe_gate_up_dp4a_b", fused, gs, None, dummy, us, None, d_idx, xq, xs, h, embd, ff, k, tokens, 1.702, 7.0)
+    pack.call("quantize_q8", h, hq, hs, pairs * ff)
+    pack.call("mxfp4_moe_down_dp4a_b", down.data, down.scale, None, d_idx, d_w, hq, hs, res, ff, embd, k, tokens)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    y = res.cpu().numpy().reshape(tokens, embd) - res0.reshape(tokens, embd)
+    same_class = _slot_layer_ref(raw, x, idx, w, tokens, k, embd, ff, n_expert, True)
+    assert rel_l2(y, same_class) < 5e-3
+    assert pack.status("mxfp4_moe_down_dp4a_b", down.data, down.scale, None, d_idx, d_w, hq, hs, res, ff, 1 << 20, k,
+                       tokens) == 801                   # per-pair rows beyond the scratch slice

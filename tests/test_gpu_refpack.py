@@ -322,3 +322,68 @@ def test_add_rmsnorm_quant_nvf4_against_reference_pack(pack, ref):
     assert np.allclose(ours[1].view(np.float32), theirs[1].view(np.float32), rtol=4e-7, atol=0)
     assert np.mean(ours[2] != theirs[2]) < 1e-3
     assert np.mean(ours[3] != theirs[3]) < 1e-3
+
+
+def _moe_slot_chain(p, raw, x, idx, w, tokens, n_expert, k, embd, ff, decode):
+    """The engine's MoE chain through pack `p`'s own slots (its own fused gate|up plane);
+    decode: the unsorted pair 92 / 93, else align -> 88 -> 89 -> combine."""
+    i32, f32, i8 = torch.int32, torch.float32, torch.int8
+    z = lambda n, dt: torch.zeros(n, dtype=dt, device="cuda")
+    planes = {}
+    for name in ("gate", "up", "down"):
+        nb = raw[name].size // 17
+        data, scale = z(nb * 16, torch.uint8), z(nb, torch.uint8)
+        p.call("mxfp4_repack", dev(raw[name]), data, scale, nb)
+        planes[name] = (data, scale)
+    n_kb = embd // 32
+    fused = z(n_expert * ff * ((n_kb + 3) // 4) * 128, torch.uint8)
+    p.call("mxfp4_gu_interleave", planes["gate"][0], planes["up"][0], fused, n_kb, n_expert * ff)
+    d_idx, d_w = dev(idx.astype(np.uint32)).view(i32), dev_f32(w.reshape(-1))
+    zb_ff, zb_embd = z(n_expert * ff, f32), z(n_expert * embd, f32)
+    xq, xs = z(tokens * embd, i8), z(tokens * embd // 32, f32)
+    dummy = z(16, torch.uint8)
+    out = z(tokens * embd, f32)
+    pairs = tokens * k
+    p.call("quantize_q8", dev_f32(x), xq, xs, tokens * embd)
+    if decode:
+        h, hq, hs = z(pairs * ff, f32), z(pairs * ff, i8), z(pairs * ff // 32, f32)
+        p.call("mxfp4_moe_gate_up_dp4a_b", fused, planes["gate"][1], zb_ff, dummy, planes["up"][1], zb_ff, d_idx, xq, xs, h,
+               embd, ff, k, tokens, 1.702, 7.0)
+        p.call("quantize_q8", h, hq, hs, pairs * ff)
+        p.call("mxfp4_moe_down_dp4a_b", planes["down"][0], planes["down"][1], zb_embd, d_idx, d_w, hq, hs, out, ff, embd, k,
+               tokens)
+    else:
+        bm = 32
+        max_blocks = (pairs + n_expert * (bm - 1) + bm - 1) // bm
+        nb = max_blocks * bm
+        s_row, s_slot, b_exp = z(nb, i32), z(nb, i32), z(max_blocks, i32)
+        fq, fs, part = z(nb * ff, i8), z(nb * ff // 32, f32), z(pairs * max(ff, embd), f32)
+        p.call("moe_align", d_idx, s_row, s_slot, b_exp, tokens, k, n_expert, max_blocks)
+        p.call("mxfp4_moe_gate_up_mmq", fused, planes["gate"][1], zb_ff, dummy, planes["up"][1], zb_ff, s_row, b_exp, xq, xs,
+               fq, fs, embd, ff, max_blocks, 1.702, 7.0, 1.0)
+        p.call("mxfp4_moe_down_mmq", planes["down"][0], planes["down"][1], zb_embd, s_row, s_slot, b_exp, d_w, fq, fs, part,
+               ff, embd, k, max_blocks)
+        p.call("moe_slot_combine", part, out, embd, k, tokens)
+    torch.cuda.synchronize()
+    return out.cpu().numpy().reshape(tokens, embd)
+
+
+@pytest.mark.parametrize("tokens,decode", [(40, False), (3, True)])
+def test_mxfp4_moe_slot_chain_against_reference(pack, ref, tokens, decode):
+    """Slots 155 / 88 / 89 / 91 (and the decode pair 92 / 93) of both packs on the same raw planes,
+    tokens and routing: the same int8 activation class, so the blocks agree far inside the
+    activation quantization's own error (about 1e-2 of the result)."""
+    n_expert, k, embd, ff = 16, 4, 2880, 2880
+    raw = {n: oracle.quantize_mxfp4(oracle.fill_normal(n_expert * ff * embd, 1500 + i, 0.02))
+           for i, n in enumerate(("gate", "up", "down"))}
+    x = oracle.bf16_round(oracle.fill_normal(tokens * embd, 1510, 1.0))
+    logits = oracle.fill_normal(tokens * n_expert, 1511, 1.0)
+    idx, w = oracle.moe_topk(logits, n_expert, k)
+    try:
+        theirs = _moe_slot_chain(ref, raw, x, idx, w, tokens, n_expert, k, embd, ff, decode)
+    except MissingOp as e:
+        pytest.skip(f"reference pack: {e}")
+    ours = _moe_slot_chain(pack, raw, x, idx, w, tokens, n_expert, k, embd, ff, decode)
+    assert pack.device_error() == 0
+    assert np.isfinite(ours).all()
+    assert rel_l2(ours, theirs.astype(np.float64)) < 5e-3 < TOL
