@@ -512,6 +512,29 @@ def run_ours(args, rank, world, local_rank):
                 del planes, bound
                 torch.cuda.empty_cache()
                 line["configs"] = other_configs(ex, quick=args.steps < 50)
+    if world > 1 and args.configs:
+        # the other sharded shapes (every rank runs them; rank 0 reports): FP8 prefill GEMM with its
+        # output channels sharded, and the expert-parallel MXFP4 MoE block
+        import kbench
+        del planes, bound
+        torch.cuda.empty_cache()
+        sharded = {}
+        quick = args.steps < 50
+        for name, case in (("fp8_m4096_n27648_nshard", kbench.Case("f8_shard", iters=5 if quick else 10)),
+                           ("moe_mxfp4_t64_expert_parallel", kbench.Case("moe_ep", m=64, graph=True, iters=10 if quick else 30)),
+                           ("moe_mxfp4_t1024_expert_parallel", kbench.Case("moe_ep", m=1024, graph=True, iters=5 if quick else 10))):
+            try:
+                r = kbench.run_case(ex, case)
+                keep = ("us", "n_gpus", "us_gemm_only", "us_gemm_nccl_allgather", "us_gemm_peer_stores", "m_chunks",
+                        "exchange_bytes_per_rank", "parity_ok", "tflops", "gbs", "frac_of_hbm", "frac_of_2x_bf16",
+                        "distinct_experts", "device_error")
+                sharded[name] = {k: r[k] for k in keep if k in r}
+            except Exception as err:
+                sharded[name] = {"error": str(err)[:200]}
+            torch.cuda.empty_cache()
+        if rank == 0:
+            line["configs"] = sharded
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

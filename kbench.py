@@ -462,6 +462,105 @@ def bench_moe_ep(ex, a):
                              "distinct_experts": distinct, "n_gpus": world}
 
 
+def bench_f8_shard(ex, a):
+    """FP8 row-scaled GEMM with the output channels sharded over the ranks (run under torchrun): each rank holds
+    N / G weight rows and computes its band y[:, band] (bf16).  Three timings, max over ranks: the GEMM alone;
+    GEMM + NCCL all-gather of the bands ([G][M][N/G], the baseline exchange); GEMM + peer stores, where the band
+    is cut into M-chunks and every chunk is copied into its place in every rank's full [M][N] y (symmetric memory,
+    plain stores over NVLink on side streams) while the next chunk's GEMM runs."""
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    world, rank = dist.get_world_size(), dist.get_rank()
+    m, n, k = a.m, a.n, a.k
+    nb = n // world
+    g = torch.Generator(device="cuda")
+    g.manual_seed(17 + rank)
+    w = torch.randint(0, 0x7E, (nb * k,), dtype=torch.uint8, device="cuda", generator=g)
+    g.manual_seed(5)
+    xq = torch.randint(0, 0x7E, (m * k,), dtype=torch.uint8, device="cuda", generator=g)
+    ws = torch.rand(nb, device="cuda") + 0.5
+    xs = torch.rand(m, device="cuda") + 0.5
+    y_band = torch.zeros(m, nb, dtype=torch.bfloat16, device="cuda")
+    gathered = torch.zeros(world, m, nb, dtype=torch.bfloat16, device="cuda")
+    y_full = symm_mem.empty(m * n, dtype=torch.bfloat16, device="cuda")
+    hdl = symm_mem.rendezvous(y_full, dist.group.WORLD.group_name)
+    peers = [hdl.get_buffer(p, (m, n), torch.bfloat16) for p in range(world)]
+    st = torch.cuda.current_stream()
+    chunks = 4 if m % 512 == 0 else 1
+    mc = m // chunks
+    evs = [torch.cuda.Event() for _ in range(chunks)]
+
+    def gemm(rows0, rows):
+        ex.pack.call("pdk_f8row_gemm_bf16", w, ws, xq[rows0 * k:], xs[rows0:], y_band[rows0:], k, nb, rows,
+                     stream=st.cuda_stream)
+
+    def step_gemm(i):
+        gemm(0, m)
+
+    def step_nccl(i):
+        gemm(0, m)
+        dist.all_gather_into_tensor(gathered.view(-1), y_band.view(-1))
+
+    # 2-D copies through the CUDA runtime: the copy engines move the chunks over NVLink while the
+    # SMs run the next chunk's GEMM (a strided torch copy kernel measured slower and takes SMs)
+    import ctypes as C
+    rt = None
+    for nm in ("libcudart.so.12", "libcudart.so"):
+        try:
+            rt = C.CDLL(nm)
+            break
+        except OSError:
+            continue
+    rt.cudaMemcpy2DAsync.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_void_p]
+    side = [torch.cuda.Stream() for _ in range(max(1, min(world, 4)))]
+    dst_base = [peers[p].data_ptr() + rank * nb * 2 for p in range(world)]
+    src_base = y_band.data_ptr()
+
+    def step_peer(i):
+        for c in range(chunks):
+            gemm(c * mc, mc)
+            evs[c].record(st)
+            for d in range(world):
+                p = (rank + d) % world            # start with the own copy, then walk the ring
+                s2 = side[d % len(side)]
+                s2.wait_event(evs[c])
+                rc = rt.cudaMemcpy2DAsync(dst_base[p] + c * mc * n * 2, n * 2, src_base + c * mc * nb * 2, nb * 2, nb * 2, mc,
+                                          4, s2.cuda_stream)       # 4 = cudaMemcpyDefault
+                if rc != 0:
+                    raise RuntimeError(f"cudaMemcpy2DAsync: {rc}")
+        for s2 in side:
+            st.wait_stream(s2)
+
+    def timed(fn):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(a.iters):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / a.iters * 1e-3], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    t_gemm, t_nccl, t_peer = timed(step_gemm), timed(step_nccl), timed(step_peer)
+    # the peer exchange must leave the same y everywhere as the all-gather does
+    torch.cuda.synchronize()
+    dist.barrier()
+    want = gathered.permute(1, 0, 2).reshape(m, n)
+    same = bool(torch.equal(want, y_full.view(m, n)))
+    flag = torch.tensor([1 if same else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return t_peer, {"bound": "tensor", "flops": 2.0 * m * n * k, "n_gpus": world, "us_gemm_only": t_gemm * 1e6,
+                    "us_gemm_nccl_allgather": t_nccl * 1e6, "us_gemm_peer_stores": t_peer * 1e6, "m_chunks": chunks,
+                    "exchange_bytes_per_rank": m * nb * 2 * (world - 1), "parity_ok": bool(flag.item())}
+
+
 def bench_nvf4_gemv(ex, a):
     """Slot 394: W4A16 decode GEMV over an NVFP4 plane (f32 activations), K=5120 N=17408 by default."""
     n, k = a.n, a.k
@@ -512,8 +611,8 @@ def bench_moe_nvf4(ex, a):
     return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
 
 
-OPS = {"norm_nvf4": bench_norm_nvf4, "q4k_w4a8": bench_q4k_w4a8, "nvf4_gemv": bench_nvf4_gemv, "moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
-DEFAULTS = {"norm_nvf4": (64, 0, 5120), "q4k_w4a8": (4, 25600, 5120), "nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+OPS = {"f8_shard": bench_f8_shard, "norm_nvf4": bench_norm_nvf4, "q4k_w4a8": bench_q4k_w4a8, "nvf4_gemv": bench_nvf4_gemv, "moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"f8_shard": (4096, 27648, 5120), "norm_nvf4": (64, 0, 5120), "q4k_w4a8": (4, 25600, 5120), "nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
 class Case:
@@ -559,7 +658,7 @@ def main():
     ap.add_argument("--pack", default=None, help="path of a kernel-pack library to time instead of this package's")
     args = ap.parse_args()
     a = Case(args.op, args.m, args.n, args.k, args.iters, args.out, args.moe_path, args.graph, args.dtype, args.pack)
-    ep = a.op == "moe_ep"
+    ep = a.op in ("moe_ep", "f8_shard")
     if ep:
         import torch.distributed as dist
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
