@@ -16,6 +16,8 @@ ref="${1:-${PADDOCK_REFERENCE:-$(cd "$here/../.." && pwd)/reference}}"
 src="$ref/packs/cuda/pack.cu"
 out="$here/_ref/pd-cuda-ref.so"
 [ -f "$src" ] || { echo "reference checkout not found at $ref: skipping"; exit 0; }
+# the slot list the ABI tests pin the header against
+python "$here/../tests/golden/gen_kernel_table.py" "$ref"
 mkdir -p "$here/_ref"
 if [ -f "$out" ] && [ "$out" -nt "$src" ]; then
     echo "up to date: $out"; exit 0

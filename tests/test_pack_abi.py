@@ -126,3 +126,23 @@ def test_loader_min_copies_a_shorter_table(tmp_path):
     assert all(p.slot_ptr(i) == 0 for i in range(packmod.TABLE_SLOTS))
     with pytest.raises(pb.MissingOp):
         p.fn("q8_0_gemv_repacked")
+
+
+def test_slot_indices_and_argument_counts_match_the_reference_table():
+    """Every PDK_SLOT_* index of the header is the index of the member of that name in the
+    reference's KernelTableV1 (tests/golden/kernel_table_v1.json, generated from
+    packs/cuda/src/abi.cuh by tests/golden/gen_kernel_table.py), and every served slot is bound
+    here with as many arguments as the reference declares."""
+    import json
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kernel_table_v1.json")
+    members = json.load(open(golden))["members"]
+    assert len(members) == packmod.TABLE_SLOTS
+    by_name = {name: (idx, args) for idx, name, args in members}
+    assert [m[0] for m in members] == list(range(len(members)))
+    assert len(packmod.SLOTS) >= 34
+    for name, idx in packmod.SLOTS.items():
+        assert name in by_name, name
+        assert by_name[name][0] == idx, (name, idx, by_name[name][0])
+        if name in packmod._SIGS:
+            n_ref = len([a for a in by_name[name][1].split(",") if a.strip()])
+            assert len(packmod._SIGS[name]) + 1 == n_ref, (name, packmod._SIGS[name], by_name[name][1])   # + the stream
