@@ -57,6 +57,36 @@ int pdk_gguf_tensor_bytes(const PdkGguf* g, const char* name, const void** data,
 int pdk_gguf_meta_u64(const PdkGguf* g, const char* key, uint64_t* value);
 int pdk_gguf_meta_str(const PdkGguf* g, const char* key, const char** value);
 
+/* ---- split GGUF families (crates/paddock-models/src/split.rs:13-62, mapped.rs:176-345) -------- */
+
+enum PdkMapError {
+    PDK_MAP_OK = 0, PDK_MAP_IO = 1, PDK_MAP_PARSE = 2, PDK_MAP_NO_SUCH_TENSOR = 3, PDK_MAP_OUT_OF_RANGE = 4,
+    PDK_MAP_UNSIZABLE = 5, PDK_MAP_NOT_FIRST_SPLIT = 6, PDK_MAP_SPLIT_NAME_MISMATCH = 7, PDK_MAP_SHARD_MISMATCH = 8,
+    PDK_MAP_MISSING_SPLIT_KEY = 9, PDK_MAP_TENSOR_COUNT_MISMATCH = 10, PDK_MAP_DUPLICATE_ACROSS_SHARDS = 11,
+    PDK_MAP_TOO_MANY_SPLITS = 12
+};
+/* "<prefix>-%05d-of-%05d.gguf" (1-based shard number): 0 and the fields, or 1 for any other name */
+int pdk_split_name_parse(const char* path, char* prefix, size_t prefix_len, uint32_t* no_1based, uint32_t* count);
+typedef struct PdkGgufFamily PdkGgufFamily;
+/* One file, or - when its split.count exceeds 1 - the whole family, one mapping per shard, opened
+ * through the FIRST shard: every sibling's split.no / split.count is checked against its place,
+ * a tensor name may appear in one shard only, and split.tensors.count of the first shard must
+ * equal the union.  Any failure is an error; a family never loads as a smaller model. */
+int pdk_gguf_family_open(const char* path, PdkGgufFamily** out, char* err, size_t err_len);
+void pdk_gguf_family_close(PdkGgufFamily* f);
+uint64_t pdk_gguf_family_shard_count(const PdkGgufFamily* f);
+uint64_t pdk_gguf_family_tensor_count(const PdkGgufFamily* f);
+uint64_t pdk_gguf_family_total_len(const PdkGgufFamily* f);
+/* shard 0 carries the model's metadata; the handle stays owned by the family */
+const PdkGguf* pdk_gguf_family_shard(const PdkGgufFamily* f, uint64_t shard);
+const char* pdk_gguf_family_shard_path(const PdkGgufFamily* f, uint64_t shard);
+/* i-th tensor of the union: shards in family order, file order inside a shard */
+int pdk_gguf_family_tensor_at(const PdkGgufFamily* f, uint64_t i, const char** name, uint32_t* n_dims,
+                              uint64_t dims[8], uint32_t* raw_type, uint64_t* n_bytes, uint32_t* shard);
+/* zero-copy bytes of a named tensor out of the shard that holds it */
+int pdk_gguf_family_tensor_bytes(const PdkGgufFamily* f, const char* name, const void** data, uint64_t* n_bytes,
+                                 uint32_t* raw_type, uint32_t* n_dims, uint64_t dims[8], uint32_t* shard);
+
 /* ---- safetensors (crates/paddock-models/src/safetensors.rs:102-190, 336-420) ------------------ */
 
 enum PdkStDtype {

@@ -100,9 +100,13 @@ enum PdkSlot {
 
 /* abi.rs:42, packs/cuda/src/exports.cuh:757.  Static storage. */
 const PdkPackInfo* paddock_pack_info(void);
-/* abi.rs:46, packs/cuda/src/exports.cuh:2114-2118.  Static storage; slots this
- * pack does not implement, or that the current device cannot run, are NULL. */
+/* abi.rs:46, packs/cuda/src/exports.cuh:2114-2400.  Static storage; slots this pack does not
+ * implement are NULL, and so is every slot when the device that is current at the first call is
+ * not of compute capability 10.0 (the only one sm_100a code loads on). */
 const PdkKernelTableV1* paddock_pack_kernels_v1(void);
+/* Diagnostics, no counterpart in the reference: the table as paddock_pack_kernels_v1 resolves it
+ * for a device of the given compute capability, written to caller storage (PDK_TABLE_BYTES). */
+int pdk_kernels_for_cc(int cc_major, int cc_minor, PdkKernelTableV1* out);
 
 /* ---- Q8_0 (packs/cuda/src/deltanet/core.cuh:2552-3090) -------------------- */
 

@@ -68,9 +68,16 @@ static const PdkPackInfo g_info = {
 
 static PdkKernelTableV1 g_table;
 
-static void fill_table() {
+// Every kernel of this library is built for sm_100a alone, and such code loads only on a device
+// of compute capability 10.0 exactly (a 10.3 or 12.x die rejects it at the first launch).  So the
+// table is resolved against the device, as packs/cuda/src/exports.cuh:2118-2400 does for its
+// block-scale families: any other capability gets an empty table and the engine reports every
+// operator as missing at load time instead of failing at the first call.
+static void fill_table_for(PdkKernelTableV1& g_table, int cc_major, int cc_minor) {
+    memset(&g_table, 0, sizeof(g_table));
     g_table.size = PDK_TABLE_BYTES;
     g_table.reserved = 0;
+    if (cc_major != 10 || cc_minor != 0) return;
 #define PDK_SET(name) g_table.slot[PDK_SLOT_##name] = (void*)&pd_##name
     PDK_SET(mxfp4_dequant_f32);
     PDK_SET(q8_0_dequant_f32);
@@ -109,10 +116,35 @@ static void fill_table() {
 #undef PDK_SET
 }
 
+// Resolution uses the device that is current at the first fetch (the engine binds its device
+// before it loads a pack, loader.rs:253-283).  Without a device to ask (no driver, no GPU) the
+// table is left as built: nothing can launch there anyway and every launcher returns the error.
+static void fill_table() {
+    int dev = 0, major = 10, minor = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) {
+        int a = 0, b = 0;
+        if (cudaDeviceGetAttribute(&a, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&b, cudaDevAttrComputeCapabilityMinor, dev) == cudaSuccess) {
+            major = a;
+            minor = b;
+        }
+    }
+    (void)cudaGetLastError();
+    fill_table_for(g_table, major, minor);
+}
+
 PDK_EXPORT const PdkPackInfo* paddock_pack_info(void) { return &g_info; }
 
 PDK_EXPORT const PdkKernelTableV1* paddock_pack_kernels_v1(void) {
     static const bool once = (fill_table(), true);
     (void)once;
     return &g_table;
+}
+
+// Diagnostics: the table as it would be resolved on a device of the given compute capability,
+// written to caller storage of PDK_TABLE_BYTES bytes.
+PDK_EXPORT int pdk_kernels_for_cc(int cc_major, int cc_minor, PdkKernelTableV1* out) {
+    if (out == nullptr) return 1;
+    fill_table_for(*out, cc_major, cc_minor);
+    return 0;
 }

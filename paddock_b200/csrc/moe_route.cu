@@ -9,9 +9,22 @@
 namespace {
 
 // ---------------------------------------------------------------- top-k router
-// One warp per token.  k rounds of argmax over logits + bias with strict ">",
-// ties to the lowest expert index; weights = softmax over the k selected
-// logits.  Up to 512 experts (16 register slots per lane), k <= 16.
+// One warp per token, up to 512 experts (16 per lane), k <= 16.  The selection rule - largest
+// logit + bias first, equal values to the lower expert index - is folded into one unsigned
+// 64-bit sort key per expert: the float's bits mapped so that unsigned order equals float order
+// in the high word, the complemented expert index in the low word.  A round is then a plain
+// 64-bit maximum over the warp; the winner's lane marks its slot as taken in a bit mask.
+// Key 0 stands for "no expert" (every real key has a non-zero high word).
+__device__ __forceinline__ uint64_t topk_key(float value, uint32_t expert) {
+    const uint32_t bits = __float_as_uint(value + 0.0f);                    // -0 joins +0, as float compare has it
+    const uint32_t ordered = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+    return ((uint64_t)ordered << 32) | (uint64_t)(0xffffffffu - expert);
+}
+__device__ __forceinline__ float topk_key_value(uint64_t key) {
+    const uint32_t ordered = (uint32_t)(key >> 32);
+    return __uint_as_float((ordered & 0x80000000u) ? (ordered & 0x7fffffffu) : ~ordered);
+}
+
 __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, uint32_t n_expert,
                                 uint32_t k, uint32_t* __restrict__ out_idx, float* __restrict__ out_w,
                                 uint32_t batch) {
@@ -21,41 +34,35 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* _
     const uint32_t token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (token >= batch) return;
     const uint32_t lane = threadIdx.x & 31u;
-    const float* row = logits + (size_t)token * n_expert;
-    float v[16];
+    const float* scores = logits + (size_t)token * n_expert;
+    uint64_t key[16];
 #pragma unroll
     for (uint32_t j = 0; j < 16u; ++j) {
-        const uint32_t i = lane + 32u * j;
-        v[j] = i < n_expert ? row[i] + (bias ? bias[i] : 0.0f) : -1e30f;
+        const uint32_t expert = 32u * j + lane;
+        key[j] = expert < n_expert ? topk_key(scores[expert] + (bias ? bias[expert] : 0.0f), expert) : 0ull;
     }
-    float sel = 0.0f;  // lane s keeps the s-th selected logit
-    for (uint32_t s = 0; s < k; ++s) {
-        float best = -1e30f;
-        uint32_t bi = 0;
-#pragma unroll
-        for (uint32_t j = 0; j < 16u; ++j) {
-            const uint32_t i = lane + 32u * j;
-            if (v[j] > best) { best = v[j]; bi = i; }
-        }
-#pragma unroll
-        for (uint32_t off = 16; off > 0; off >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
-            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
-            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-        }
-        if (lane == s) sel = best;
-        if (lane == 0) out_idx[(size_t)token * k + s] = bi;
+    uint32_t taken = 0;      // bit j: this lane's j-th expert has been selected
+    float picked = 0.0f;     // lane r keeps the value of the r-th pick
+    for (uint32_t round = 0; round < k; ++round) {
+        uint64_t top = 0ull;
 #pragma unroll
         for (uint32_t j = 0; j < 16u; ++j)
-            if (lane + 32u * j == bi) v[j] = -1e30f;
-    }
-    float mm = lane < k ? sel : -1e30f;
+            if (!((taken >> j) & 1u) && key[j] > top) top = key[j];
 #pragma unroll
-    for (uint32_t off = 16; off > 0; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
-    // sum in ascending slot order, as a scalar walk would
-    const float e = lane < k ? __expf(sel - mm) : 0.0f;
+        for (uint32_t step = 1; step < 32u; step <<= 1) {
+            const uint64_t other = __shfl_xor_sync(0xffffffffu, top, step);
+            top = other > top ? other : top;
+        }
+        const uint32_t expert = 0xffffffffu - (uint32_t)top;
+        if ((expert & 31u) == lane) taken |= 1u << (expert >> 5);
+        if (lane == round) picked = topk_key_value(top);
+        if (lane == 0) out_idx[(size_t)token * k + round] = expert;
+    }
+    // softmax over the k picks; lane 0 holds the largest, the sum runs in pick order as a scalar walk would
+    const float peak = __shfl_sync(0xffffffffu, picked, 0);
+    const float e = lane < k ? __expf(picked - peak) : 0.0f;
     float sum = 0.0f;
-    for (uint32_t s = 0; s < k; ++s) sum += __shfl_sync(0xffffffffu, e, s);
+    for (uint32_t r = 0; r < k; ++r) sum += __shfl_sync(0xffffffffu, e, r);
     if (lane < k) out_w[(size_t)token * k + lane] = e / sum;
 }
 

@@ -42,104 +42,114 @@ __device__ __forceinline__ uint32_t e2m1_rn(float v) {
     return s | m;
 }
 
-// One thread per 8 elements (half a block); the lane pair closes the 16-element
-// amax.  scale byte = RN_e4m3(amax / 6), floored at the smallest subnormal when
-// amax > 0; elements = e2m1_rn(v / scale).
+// The NVFP4 rule for one 16-element block (packs/cuda/src/quant/e2m1.cuh): scale byte =
+// RN_e4m3(amax / 6), raised to the smallest subnormal when amax > 0 rounds to zero; elements =
+// e2m1_rn(v / decode(scale byte)).  A block whose amax is 0 stores scale 0 and codes 0.
+struct Nvf4BlockScale {
+    uint32_t byte;   // the e4m3 scale as stored
+    float recip;     // 1 / its value, 0 for an all-zero block
+};
+__device__ __forceinline__ Nvf4BlockScale nvf4_block_scale(float amax) {
+    Nvf4BlockScale s = {0u, 0.0f};
+    if (amax > 0.0f) {
+        s.byte = (uint32_t)__nv_cvt_float_to_fp8(amax * (1.0f / 6.0f), __NV_SATFINITE, __NV_E4M3);
+        if (s.byte == 0u) s.byte = 1u;
+        s.recip = 1.0f / e4m3_to_f32((uint8_t)s.byte);
+    }
+    return s;
+}
+__device__ __forceinline__ float amax4(const float4& v) {
+    return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+// four values -> four e2m1 codes, first value in the low nibble
+__device__ __forceinline__ uint32_t nvf4_codes4(const float4& v, float recip) {
+    return e2m1_rn(v.x * recip) | e2m1_rn(v.y * recip) << 4 | e2m1_rn(v.z * recip) << 8 | e2m1_rn(v.w * recip) << 12;
+}
+
+// One thread per 8 elements (half a block); the lane pair closes the 16-element amax.
 __global__ void quantize_nvf4_kernel(const float* __restrict__ x, uint8_t* __restrict__ q,
                                      uint8_t* __restrict__ scale, uint32_t n) {
     const uint32_t i = (blockIdx.x * 256u + threadIdx.x) * 8u;
     if (i >= n) return;  // n % 32 == 0: lane pairs leave together
     const float4 a = *reinterpret_cast<const float4*>(x + i);
     const float4 b = *reinterpret_cast<const float4*>(x + i + 4u);
-    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    float amax = 0.0f;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
     const uint32_t lane = threadIdx.x & 31u;
+    float amax = fmaxf(amax4(a), amax4(b));
     amax = fmaxf(amax, __shfl_xor_sync(0x3u << (lane & 30u), amax, 1));
-    uint32_t sb = 0u;
-    float inv = 0.0f;
-    if (amax > 0.0f) {
-        sb = (uint32_t)__nv_cvt_float_to_fp8(amax * (1.0f / 6.0f), __NV_SATFINITE, __NV_E4M3);
-        if (sb == 0u) sb = 1u;
-        inv = 1.0f / e4m3_to_f32((uint8_t)sb);
-    }
-    uint32_t p = 0u;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) p |= e2m1_rn(v[k] * inv) << (4 * k);
-    *reinterpret_cast<uint32_t*>(q + (i >> 1)) = p;
-    if ((lane & 1u) == 0u) scale[i >> 4] = (uint8_t)sb;
+    const Nvf4BlockScale s = nvf4_block_scale(amax);
+    *reinterpret_cast<uint32_t*>(q + (i >> 1)) = nvf4_codes4(a, s.recip) | nvf4_codes4(b, s.recip) << 16;
+    if ((lane & 1u) == 0u) scale[i >> 4] = (uint8_t)s.byte;
 }
 
-// Fused producer in front of an NVFP4 GEMM: residual add, RMSNorm and the NVFP4 quantizer in one
-// pass over the row.  One CTA per row; the summed row waits in shared memory between the
-// square-sum and the normalisation, so x and proj are read once.  Sum of squares: f32 products
-// accumulated in f64; inv = 1 / sqrtf((float)(sum / n) + eps); out = v * inv * w in that order
-// (packs/cuda/src/quant/nvf4.cuh:455-543); the quantizer is quantize_nvf4_kernel's, 8 elements
-// per thread, the lane pair closing each 16-element block.
+// Fused producer in front of an NVFP4 GEMM (the contract of packs/cuda/src/quant/nvf4.cuh:545-571):
+// x += proj, out = rmsnorm(x) * w, q / scale = the NVFP4 planes of out.  One CTA per row, and the
+// summed row never leaves the register file: thread t holds the row's float4 number t, t + T,
+// t + 2T, ... (T threads, kChunks of them), so every load and store of a warp is one contiguous
+// 512-byte run and nothing is staged in shared memory.  Mean square: f32 products accumulated in
+// f64, per thread, then per warp, then over the warps in warp order; scale = 1 / sqrtf((float)
+// (sum / n) + eps); out = v * scale * w, multiplied in that order.  A 16-element NVFP4 block is
+// four neighbouring float4, i.e. four neighbouring lanes: two shuffles close its amax and each
+// lane emits its own four codes.
 constexpr uint32_t kNormMaxThreads = 384;
+template <int kChunks>
 __global__ void __launch_bounds__(kNormMaxThreads)
 add_rmsnorm_quant_nvf4_kernel(float* __restrict__ x, const float* __restrict__ proj, const float* __restrict__ w,
                               float* __restrict__ out, uint8_t* __restrict__ q, uint8_t* __restrict__ scale, uint32_t n,
                               float eps) {
-    extern __shared__ __align__(16) float row[];
-    __shared__ double wsum[kNormMaxThreads / 32u];
-    __shared__ float s_inv;
-    const uint32_t b = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, nth = blockDim.x;  // nth % 32 == 0
-    float* xb = x + (size_t)b * n;
-    const float* pb = proj ? proj + (size_t)b * n : nullptr;
+    __shared__ double warp_sq[kNormMaxThreads / 32u];
+    const uint32_t t = threadIdx.x, width = blockDim.x, n4 = n >> 2;   // width % 32 == 0, n4 % 4 == 0
+    const size_t row4 = (size_t)blockIdx.x * n4;
+    float4* x4 = reinterpret_cast<float4*>(x) + row4;
     pdk_pdl_launch_dependents();
     pdk_pdl_wait();
-    double acc = 0.0;
-    for (uint32_t i = tid; i < (n >> 2); i += nth) {
-        float4 v = reinterpret_cast<const float4*>(xb)[i];
-        if (pb) {
-            const float4 pv = reinterpret_cast<const float4*>(pb)[i];
-            v.x += pv.x; v.y += pv.y; v.z += pv.z; v.w += pv.w;
-            reinterpret_cast<float4*>(xb)[i] = v;
+
+    float4 held[kChunks];
+    double sq = 0.0;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const uint32_t at = (uint32_t)c * width + t;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (at < n4) {
+            v = x4[at];
+            if (proj != nullptr) {
+                const float4 add = (reinterpret_cast<const float4*>(proj) + row4)[at];
+                v.x += add.x; v.y += add.y; v.z += add.z; v.w += add.w;
+                x4[at] = v;
+            }
         }
-        reinterpret_cast<float4*>(row)[i] = v;
-        acc += (double)(v.x * v.x) + (double)(v.y * v.y) + (double)(v.z * v.z) + (double)(v.w * v.w);
+        held[c] = v;
+        sq += (double)(v.x * v.x) + (double)(v.y * v.y) + (double)(v.z * v.z) + (double)(v.w * v.w);
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0u) wsum[tid >> 5] = acc;
+    for (int d = 1; d < 32; d <<= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+    if ((t & 31u) == 0u) warp_sq[t >> 5] = sq;
     __syncthreads();
-    if (tid == 0u) {
-        double total = 0.0;
-        for (uint32_t i = 0; i < (nth >> 5); ++i) total += wsum[i];
-        s_inv = 1.0f / sqrtf((float)(total / (double)n) + eps);
-    }
-    __syncthreads();
-    const float inv = s_inv;
-    float* ob = out + (size_t)b * n;
-    uint8_t* qb = q + (size_t)b * (n >> 1);
-    uint8_t* sb = scale + (size_t)b * (n >> 4);
-    // n % 32 == 0 and an even thread count: a lane pair is never split across the loop bound
-    for (uint32_t j = tid; j < (n >> 3); j += nth) {
-        const uint32_t i = j << 3;
-        const float4 v0 = *reinterpret_cast<const float4*>(row + i), v1 = *reinterpret_cast<const float4*>(row + i + 4u);
-        const float4 w0 = *reinterpret_cast<const float4*>(w + i), w1 = *reinterpret_cast<const float4*>(w + i + 4u);
-        const float r[8] = {v0.x * inv * w0.x, v0.y * inv * w0.y, v0.z * inv * w0.z, v0.w * inv * w0.w,
-                            v1.x * inv * w1.x, v1.y * inv * w1.y, v1.z * inv * w1.z, v1.w * inv * w1.w};
-        *reinterpret_cast<float4*>(ob + i) = make_float4(r[0], r[1], r[2], r[3]);
-        *reinterpret_cast<float4*>(ob + i + 4u) = make_float4(r[4], r[5], r[6], r[7]);
-        float amax = 0.0f;
+    double total = 0.0;
+    for (uint32_t i = 0; i < (width >> 5); ++i) total += warp_sq[i];   // every thread, same order: no second barrier
+    const float norm = 1.0f / sqrtf((float)(total / (double)n) + eps);
+
+    float4* out4 = reinterpret_cast<float4*>(out) + row4;
+    uint16_t* codes = reinterpret_cast<uint16_t*>(q + (size_t)blockIdx.x * (n >> 1));
+    uint8_t* srow = scale + (size_t)blockIdx.x * (n >> 4);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(r[k]));
-        amax = fmaxf(amax, __shfl_xor_sync(0x3u << (lane & 30u), amax, 1));
-        uint32_t sbyte = 0u;
-        float qinv = 0.0f;
-        if (amax > 0.0f) {
-            sbyte = (uint32_t)__nv_cvt_float_to_fp8(amax * (1.0f / 6.0f), __NV_SATFINITE, __NV_E4M3);
-            if (sbyte == 0u) sbyte = 1u;
-            qinv = 1.0f / e4m3_to_f32((uint8_t)sbyte);
+    for (int c = 0; c < kChunks; ++c) {
+        const uint32_t at = (uint32_t)c * width + t;
+        const bool live = at < n4;   // the same for the four lanes of a block: n4 and width are multiples of 4
+        float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (live) {
+            const float4 g = reinterpret_cast<const float4*>(w)[at];
+            const float4 v = held[c];
+            r = make_float4(v.x * norm * g.x, v.y * norm * g.y, v.z * norm * g.z, v.w * norm * g.w);
+            out4[at] = r;
         }
-        uint32_t p = 0u;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) p |= e2m1_rn(r[k] * qinv) << (4 * k);
-        *reinterpret_cast<uint32_t*>(qb + (i >> 1)) = p;
-        if ((lane & 1u) == 0u) sb[i >> 4] = (uint8_t)sbyte;
+        float amax = amax4(r);
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const Nvf4BlockScale s = nvf4_block_scale(amax);
+        if (live) {
+            codes[at] = (uint16_t)nvf4_codes4(r, s.recip);
+            if ((t & 3u) == 0u) srow[at >> 2] = (uint8_t)s.byte;
+        }
     }
 }
 
@@ -237,21 +247,28 @@ PDK_EXPORT int pd_add_rmsnorm_quant_nvf4_batch(void* x, const void* proj, const 
     if ((n & 31u) != 0u || !pdk_aligned(x, 16) || !pdk_aligned(proj, 16) || !pdk_aligned(w, 16) || !pdk_aligned(out, 16) ||
         !pdk_aligned(q, 4))
         return cudaErrorInvalidValue;
-    const size_t smem = (size_t)n * sizeof(float);
-    if (smem > 200u * 1024u) return cudaErrorNotSupported;
-    if (smem > 48u * 1024u) {
-        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_quant_nvf4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
+    // the fewest float4 per thread (a power of two) that fits the row into one CTA of at most
+    // kNormMaxThreads threads: 5120 -> 4 per thread, 320 threads
+    const uint32_t n4 = n >> 2;
+    uint32_t chunks = 1;
+    while (chunks < 32u && (n4 + chunks - 1u) / chunks > kNormMaxThreads) chunks <<= 1;
+    const uint32_t width = ((n4 + chunks - 1u) / chunks + 31u) & ~31u;
+    if (width > kNormMaxThreads) return cudaErrorNotSupported;   // rows beyond 49152 elements
+#define PDK_NORM_CASE(C)                                                                                          \
+    case C:                                                                                                       \
+        return pdk_launch_pdl(add_rmsnorm_quant_nvf4_kernel<C>, dim3(batch), dim3(width), 0, (cudaStream_t)stream, \
+                              (float*)x, (const float*)proj, (const float*)w, (float*)out, (uint8_t*)q,           \
+                              (uint8_t*)scale, n, eps)
+    switch (chunks) {
+        PDK_NORM_CASE(1);
+        PDK_NORM_CASE(2);
+        PDK_NORM_CASE(4);
+        PDK_NORM_CASE(8);
+        PDK_NORM_CASE(16);
+        PDK_NORM_CASE(32);
     }
-    // a block width that walks the row's n/8 eight-element groups in whole rounds, if there is one
-    // between 192 and 384 threads (measured at 4096 rows of 5120: 320 threads 74 us, 512 104 us, 1024 140 us)
-    const uint32_t n8 = n >> 3;
-    uint32_t nth = 0;
-    for (uint32_t c = kNormMaxThreads; c >= 192u && nth == 0u; c -= 32u)
-        if (n8 % c == 0u) nth = c;
-    if (nth == 0u) nth = n8 < 256u ? (n8 + 31u) & ~31u : 256u;
-    return pdk_launch_pdl(add_rmsnorm_quant_nvf4_kernel, dim3(batch), dim3(nth), smem, (cudaStream_t)stream, (float*)x,
-                          (const float*)proj, (const float*)w, (float*)out, (uint8_t*)q, (uint8_t*)scale, n, eps);
+#undef PDK_NORM_CASE
+    return cudaErrorNotSupported;
 }
 
 // slot 393, packs/cuda/src/quant/nvf4.cuh:4365-4403

@@ -12,6 +12,8 @@ _ERR = 256
 
 GGUF_ERRORS = ["Ok", "BadMagic", "UnsupportedVersion", "Truncated", "CountTooLarge", "BadUtf8", "UnknownValueType",
                "ArrayTooDeep", "BadAlignment", "BadTensor", "DuplicateTensor", "Io", "NotFound"]
+MAP_ERRORS = ["Ok", "Io", "Parse", "NoSuchTensor", "OutOfRange", "Unsizable", "NotFirstSplit", "SplitNameMismatch",
+              "ShardMismatch", "MissingSplitKey", "TensorCountMismatch", "DuplicateAcrossShards", "TooManySplits"]
 ST_DTYPES = ["F8_E4M3", "BF16", "F16", "F32", "I64", "U8", "U32", "OTHER"]
 
 
@@ -112,6 +114,81 @@ class Gguf:
     def meta_str(self, key):
         v = C.c_char_p()
         return v.value.decode() if _LIB.pdk_gguf_meta_str(self._h, key.encode(), C.byref(v)) == 0 else None
+
+
+def parse_split_name(path):
+    """split.rs:37-62: ("<prefix>", no_1based, count) of a "<prefix>-00002-of-00003.gguf" name, else None."""
+    prefix, no, count = C.create_string_buffer(4096), C.c_uint32(), C.c_uint32()
+    if _LIB.pdk_split_name_parse(str(path).encode(), prefix, C.c_size_t(4096), C.byref(no), C.byref(count)) != 0:
+        return None
+    return prefix.value.decode(), no.value, count.value
+
+
+class MappedGguf:
+    """mapped.rs:176-345: one GGUF file or a split family opened through its first shard; tensors
+    resolve to the shard that holds them, metadata comes from the first shard."""
+
+    def __init__(self, path):
+        self._h = None
+        h, err = C.c_void_p(), C.create_string_buffer(_ERR)
+        rc = _LIB.pdk_gguf_family_open(str(path).encode(), C.byref(h), err, _ERR)
+        if rc != 0:
+            raise FormatError(MAP_ERRORS[rc], err.value.decode(errors="replace"))
+        self._h = h
+        for fn in ("shard_count", "tensor_count", "total_len"):
+            getattr(_LIB, "pdk_gguf_family_" + fn).restype = C.c_uint64
+        _LIB.pdk_gguf_family_shard.restype = C.c_void_p
+        _LIB.pdk_gguf_family_shard_path.restype = C.c_char_p
+
+    def close(self):
+        if self._h:
+            _LIB.pdk_gguf_family_close(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def shard_count(self):
+        return _LIB.pdk_gguf_family_shard_count(self._h)
+
+    def tensor_count(self):
+        return _LIB.pdk_gguf_family_tensor_count(self._h)
+
+    def total_len(self):
+        return _LIB.pdk_gguf_family_total_len(self._h)
+
+    def shard_path(self, shard):
+        return _LIB.pdk_gguf_family_shard_path(self._h, C.c_uint64(shard)).decode()
+
+    def meta_u64(self, key):
+        v = C.c_uint64()
+        first = C.c_void_p(_LIB.pdk_gguf_family_shard(self._h, C.c_uint64(0)))
+        return v.value if _LIB.pdk_gguf_meta_u64(first, key.encode(), C.byref(v)) == 0 else None
+
+    def meta_str(self, key):
+        v = C.c_char_p()
+        first = C.c_void_p(_LIB.pdk_gguf_family_shard(self._h, C.c_uint64(0)))
+        return v.value.decode() if _LIB.pdk_gguf_meta_str(first, key.encode(), C.byref(v)) == 0 else None
+
+    def tensor_infos(self):
+        """(name, dims, raw type, bytes, shard) of every tensor, shards in family order."""
+        out = []
+        for i in range(self.tensor_count()):
+            name, nd, dims = C.c_char_p(), C.c_uint32(), (C.c_uint64 * 8)()
+            ty, nb, shard = C.c_uint32(), C.c_uint64(), C.c_uint32()
+            _LIB.pdk_gguf_family_tensor_at(self._h, C.c_uint64(i), C.byref(name), C.byref(nd), dims, C.byref(ty),
+                                           C.byref(nb), C.byref(shard))
+            out.append((name.value.decode(), list(dims[:nd.value]), ty.value, nb.value, shard.value))
+        return out
+
+    def tensor_bytes(self, name):
+        """(numpy uint8 view into the holding shard's mapping, raw type, dims, shard)."""
+        ptr, nb, ty, nd, dims = C.c_void_p(), C.c_uint64(), C.c_uint32(), C.c_uint32(), (C.c_uint64 * 8)()
+        shard = C.c_uint32()
+        rc = _LIB.pdk_gguf_family_tensor_bytes(self._h, name.encode(), C.byref(ptr), C.byref(nb), C.byref(ty),
+                                               C.byref(nd), dims, C.byref(shard))
+        if rc != 0:
+            raise FormatError(MAP_ERRORS[rc], name)
+        return _view(ptr, nb.value, self), ty.value, list(dims[:nd.value]), shard.value
 
 
 class Safetensors:

@@ -431,3 +431,197 @@ PDKH_EXPORT int pdk_gguf_meta_str(const PdkGguf* g, const char* key, const char*
     if (value) *value = it->second.s.c_str();
     return PDK_GGUF_OK;
 }
+
+// ---- split families (crates/paddock-models/src/split.rs, mapped.rs:176-290) --------------------
+// A model shipped as N whole GGUF files `<prefix>-%05d-of-%05d.gguf` (numbers 1-based in the
+// name).  Every shard carries split.no (0-based) and split.count; the first one also carries
+// split.tensors.count, the size of the union.  A family opens through its first shard only; a
+// shard that is absent, out of place or short of tensors is an error, never a smaller model.
+
+namespace {
+constexpr uint64_t kMaxSplits = 2048;   // the field is a u16 and real families are single digits
+
+struct SplitName {
+    std::string prefix;
+    uint32_t no = 0, count = 0;   // no is 1-based
+    std::string sibling(uint32_t no_1based) const {
+        char tail[40];
+        snprintf(tail, sizeof tail, "-%05u-of-%05u.gguf", no_1based, count);
+        return prefix + tail;
+    }
+};
+
+// exactly "<prefix>-DDDDD-of-DDDDD.gguf", prefix not empty, 1 <= no <= count
+bool parse_split_name(const std::string& path, SplitName* out) {
+    static const char kExt[] = ".gguf";
+    const size_t tail = 1 + 5 + 4 + 5 + 5;   // "-" no "-of-" count ".gguf"
+    if (path.size() <= tail || path.compare(path.size() - 5, 5, kExt) != 0) return false;
+    const size_t at = path.size() - tail;
+    if (path[at] != '-' || path.compare(at + 6, 4, "-of-") != 0) return false;
+    uint32_t field[2] = {0, 0};
+    const size_t start[2] = {at + 1, at + 10};
+    for (int f = 0; f < 2; ++f)
+        for (size_t i = 0; i < 5; ++i) {
+            const char ch = path[start[f] + i];
+            if (ch < '0' || ch > '9') return false;
+            field[f] = field[f] * 10u + (uint32_t)(ch - '0');
+        }
+    if (field[0] == 0 || field[1] == 0 || field[0] > field[1]) return false;
+    out->prefix = path.substr(0, at);
+    out->no = field[0];
+    out->count = field[1];
+    return true;
+}
+}  // namespace
+
+struct PdkGgufFamily {
+    std::vector<PdkGguf*> shards;
+    std::vector<std::string> paths;
+    std::vector<std::pair<uint32_t, uint32_t>> order;                       // (shard, index in shard), family order
+    std::unordered_map<std::string, std::pair<uint32_t, uint32_t>> by_name;
+    ~PdkGgufFamily() {
+        for (PdkGguf* g : shards) pdk_gguf_close(g);
+    }
+};
+
+PDKH_EXPORT int pdk_split_name_parse(const char* path, char* prefix, size_t prefix_len, uint32_t* no_1based,
+                                     uint32_t* count) {
+    SplitName n;
+    if (!path || !parse_split_name(path, &n)) return 1;
+    if (prefix && prefix_len) snprintf(prefix, prefix_len, "%s", n.prefix.c_str());
+    if (no_1based) *no_1based = n.no;
+    if (count) *count = n.count;
+    return 0;
+}
+
+static int family_fail(PdkGgufFamily* f, int code) {
+    delete f;
+    return code;
+}
+
+PDKH_EXPORT int pdk_gguf_family_open(const char* path, PdkGgufFamily** out, char* err, size_t err_len) {
+    if (!out || !path) return PDK_MAP_IO;
+    *out = nullptr;
+    PdkGgufFamily* f = new PdkGgufFamily();
+    PdkGguf* first = nullptr;
+    int rc = pdk_gguf_open(path, &first, err, err_len);
+    if (rc != PDK_GGUF_OK) return family_fail(f, rc == PDK_GGUF_IO ? PDK_MAP_IO : PDK_MAP_PARSE);
+    f->shards.push_back(first);
+    f->paths.push_back(path);
+
+    uint64_t split_count = 0;
+    if (pdk_gguf_meta_u64(first, "split.count", &split_count) != PDK_GGUF_OK) split_count = 0;
+    if (split_count > 1) {
+        if (split_count > kMaxSplits) {
+            set_err(err, err_len, "split.count %llu exceeds the cap of %llu", (unsigned long long)split_count,
+                    (unsigned long long)kMaxSplits);
+            return family_fail(f, PDK_MAP_TOO_MANY_SPLITS);
+        }
+        uint64_t no = 0;
+        if (pdk_gguf_meta_u64(first, "split.no", &no) != PDK_GGUF_OK) {
+            set_err(err, err_len, "%s: split model without split.no", path);
+            return family_fail(f, PDK_MAP_MISSING_SPLIT_KEY);
+        }
+        // the file name is the only locator of the siblings, so it has to agree with the metadata first
+        SplitName name;
+        if (!parse_split_name(path, &name) || name.count != split_count) {
+            set_err(err, err_len, "%s: split.count = %llu but the name is not ...-00001-of-%05llu.gguf", path,
+                    (unsigned long long)split_count, (unsigned long long)split_count);
+            return family_fail(f, PDK_MAP_SPLIT_NAME_MISMATCH);
+        }
+        if (no != 0) {
+            set_err(err, err_len, "%s is shard %u of %u: load the model through %s", path, name.no, name.count,
+                    name.sibling(1).c_str());
+            return family_fail(f, PDK_MAP_NOT_FIRST_SPLIT);
+        }
+        for (uint64_t idx = 1; idx < split_count; ++idx) {
+            const std::string sib = name.sibling((uint32_t)idx + 1u);
+            PdkGguf* g = nullptr;
+            rc = pdk_gguf_open(sib.c_str(), &g, err, err_len);
+            if (rc != PDK_GGUF_OK) return family_fail(f, rc == PDK_GGUF_IO ? PDK_MAP_IO : PDK_MAP_PARSE);
+            f->shards.push_back(g);
+            f->paths.push_back(sib);
+            const char* keys[2] = {"split.no", "split.count"};
+            const uint64_t want[2] = {idx, split_count};
+            for (int k = 0; k < 2; ++k) {
+                uint64_t got = 0;
+                if (pdk_gguf_meta_u64(g, keys[k], &got) != PDK_GGUF_OK) {
+                    set_err(err, err_len, "%s: split model without %s", sib.c_str(), keys[k]);
+                    return family_fail(f, PDK_MAP_MISSING_SPLIT_KEY);
+                }
+                if (got != want[k]) {
+                    set_err(err, err_len, "%s: %s = %llu, expected %llu", sib.c_str(), keys[k], (unsigned long long)got,
+                            (unsigned long long)want[k]);
+                    return family_fail(f, PDK_MAP_SHARD_MISMATCH);
+                }
+            }
+        }
+    }
+
+    for (uint32_t s = 0; s < f->shards.size(); ++s) {
+        const std::vector<Tensor>& ts = f->shards[s]->tensors;
+        for (uint32_t i = 0; i < ts.size(); ++i) {
+            auto ins = f->by_name.emplace(ts[i].name, std::make_pair(s, i));
+            if (!ins.second) {
+                set_err(err, err_len, "tensor %s appears in shard %u and in shard %u", ts[i].name.c_str(),
+                        ins.first->second.first, s);
+                return family_fail(f, PDK_MAP_DUPLICATE_ACROSS_SHARDS);
+            }
+            f->order.emplace_back(s, i);
+        }
+    }
+    if (split_count > 1) {
+        uint64_t expected = 0;
+        if (pdk_gguf_meta_u64(first, "split.tensors.count", &expected) != PDK_GGUF_OK) {
+            set_err(err, err_len, "%s: split model without split.tensors.count", path);
+            return family_fail(f, PDK_MAP_MISSING_SPLIT_KEY);
+        }
+        if (expected != f->by_name.size()) {
+            set_err(err, err_len, "split.tensors.count says %llu tensors but the %zu shards hold %zu",
+                    (unsigned long long)expected, f->shards.size(), f->by_name.size());
+            return family_fail(f, PDK_MAP_TENSOR_COUNT_MISMATCH);
+        }
+    }
+    *out = f;
+    return PDK_MAP_OK;
+}
+
+PDKH_EXPORT void pdk_gguf_family_close(PdkGgufFamily* f) { delete f; }
+PDKH_EXPORT uint64_t pdk_gguf_family_shard_count(const PdkGgufFamily* f) { return f->shards.size(); }
+PDKH_EXPORT uint64_t pdk_gguf_family_tensor_count(const PdkGgufFamily* f) { return f->order.size(); }
+PDKH_EXPORT uint64_t pdk_gguf_family_total_len(const PdkGgufFamily* f) {
+    uint64_t n = 0;
+    for (const PdkGguf* g : f->shards) n += g->len;
+    return n;
+}
+PDKH_EXPORT const PdkGguf* pdk_gguf_family_shard(const PdkGgufFamily* f, uint64_t shard) {
+    return shard < f->shards.size() ? f->shards[(size_t)shard] : nullptr;
+}
+PDKH_EXPORT const char* pdk_gguf_family_shard_path(const PdkGgufFamily* f, uint64_t shard) {
+    return shard < f->paths.size() ? f->paths[(size_t)shard].c_str() : nullptr;
+}
+
+PDKH_EXPORT int pdk_gguf_family_tensor_at(const PdkGgufFamily* f, uint64_t i, const char** name, uint32_t* n_dims,
+                                          uint64_t dims[8], uint32_t* raw_type, uint64_t* n_bytes, uint32_t* shard) {
+    if (i >= f->order.size()) return PDK_MAP_NO_SUCH_TENSOR;
+    const auto at = f->order[(size_t)i];
+    fill_info(f->shards[at.first]->tensors[at.second], name, n_dims, dims, raw_type, nullptr, n_bytes);
+    if (shard) *shard = at.first;
+    return PDK_MAP_OK;
+}
+
+PDKH_EXPORT int pdk_gguf_family_tensor_bytes(const PdkGgufFamily* f, const char* name, const void** data,
+                                             uint64_t* n_bytes, uint32_t* raw_type, uint32_t* n_dims, uint64_t dims[8],
+                                             uint32_t* shard) {
+    auto it = f->by_name.find(name);
+    if (it == f->by_name.end()) return PDK_MAP_NO_SUCH_TENSOR;
+    const PdkGguf* g = f->shards[it->second.first];
+    const Tensor& t = g->tensors[it->second.second];
+    if (!t.sized) return PDK_MAP_UNSIZABLE;
+    if (g->data_offset > g->len || t.offset > g->len - g->data_offset || t.n_bytes > g->len - g->data_offset - t.offset)
+        return PDK_MAP_OUT_OF_RANGE;
+    fill_info(t, nullptr, n_dims, dims, raw_type, nullptr, n_bytes);
+    if (data) *data = g->bytes + g->data_offset + t.offset;
+    if (shard) *shard = it->second.first;
+    return PDK_MAP_OK;
+}

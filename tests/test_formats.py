@@ -251,3 +251,98 @@ def test_nvfp4_gguf_repack_refuses_signed_scale_and_short_tensor():
     for src, rows, k in ((blk, 1, 64), (np.zeros(35, np.uint8), 1, 64), (np.zeros(36, np.uint8), 1, 32)):
         with pytest.raises(F.FormatError):
             F.nvfp4_gguf_repack_rows(src, rows, k)
+
+
+# ---- split families (split.rs:64-100, mapped.rs tests) ------------------------------------------
+def test_split_names_parse_strictly():
+    assert F.parse_split_name("/m/gpt-oss-120b-mxfp4-00001-of-00003.gguf") == ("/m/gpt-oss-120b-mxfp4", 1, 3)
+    for name in ["model.gguf", "model-1-of-3.gguf", "model-00000-of-00003.gguf", "model-00004-of-00003.gguf",
+                 "model-00001-of-00000.gguf", "-00001-of-00002.gguf", "model-00001-of-00003.notgguf",
+                 "model-abcde-of-00003.gguf"]:
+        assert F.parse_split_name(name) is None, name
+
+
+def u16kv(key, v):
+    return (key, 2, struct.pack("<H", v))
+
+
+def i32kv(key, v):
+    return (key, 5, struct.pack("<i", v))
+
+
+def write_family(tmp_path, n_shards, total=None, stem="fam", **over):
+    """n_shards files of one Q8_0 tensor each; `over` patches single shards' metadata."""
+    payloads = []
+    for s in range(n_shards):
+        p = q8_payload(2, 64, 50 + s)
+        payloads.append(p)
+        kv = [u16kv("split.no", over.get("no", {}).get(s, s)), u16kv("split.count", over.get("count", {}).get(s, n_shards))]
+        if s in over.get("drop_no", ()):
+            kv = kv[1:]
+        if s == 0:
+            kv.append(("general.architecture", 8, gstr("llama")))
+            if total is not False:
+                kv.append(i32kv("split.tensors.count", n_shards if total is None else total))
+        name = over.get("names", {}).get(s, f"blk.{s}.w")
+        (tmp_path / f"{stem}-{s + 1:05d}-of-{n_shards:05d}.gguf").write_bytes(build_gguf([(name, [64, 2], 8, p)], kv))
+    return str(tmp_path / f"{stem}-00001-of-{n_shards:05d}.gguf"), payloads
+
+
+def test_split_family_resolves_each_tensor_to_its_shard(tmp_path):
+    first, payloads = write_family(tmp_path, 3)
+    m = F.MappedGguf(first)
+    assert m.shard_count() == 3 and m.tensor_count() == 3
+    assert m.meta_str("general.architecture") == "llama" and m.meta_u64("split.count") == 3
+    assert [(t[0], t[4]) for t in m.tensor_infos()] == [("blk.0.w", 0), ("blk.1.w", 1), ("blk.2.w", 2)]
+    for s in range(3):
+        data, ty, dims, shard = m.tensor_bytes(f"blk.{s}.w")
+        assert (ty, dims, shard) == (8, [64, 2], s) and data.tobytes() == payloads[s]
+        assert m.shard_path(s).endswith(f"fam-{s + 1:05d}-of-00003.gguf")
+    import os
+    assert m.total_len() == sum(os.path.getsize(m.shard_path(s)) for s in range(3))
+    with pytest.raises(F.FormatError) as e:
+        m.tensor_bytes("blk.9.w")
+    assert e.value.kind == "NoSuchTensor"
+    m.close()
+
+
+def test_single_file_keeps_its_behaviour(tmp_path):
+    p = q8_payload(2, 64, 7)
+    path = tmp_path / "plain.gguf"
+    path.write_bytes(build_gguf([("w", [64, 2], 8, p)], [u16kv("split.count", 1)]))
+    m = F.MappedGguf(str(path))
+    assert m.shard_count() == 1 and m.tensor_bytes("w")[0].tobytes() == p
+
+
+def test_split_family_errors_are_load_errors(tmp_path):
+    def kind(path):
+        with pytest.raises(F.FormatError) as e:
+            F.MappedGguf(path)
+        return e.value.kind
+
+    d = lambda n: (tmp_path / n).mkdir() or tmp_path / n
+    first, _ = write_family(d("a"), 3)
+    assert kind(first.replace("00001-of", "00002-of")) == "NotFirstSplit"      # opened through the second shard
+    import os
+    os.remove(first.replace("00001-of", "00003-of"))
+    assert kind(first) == "Io"                                                  # a sibling is missing
+    first, _ = write_family(d("b"), 2, no={1: 0})
+    assert kind(first) == "ShardMismatch"                                       # a copy of shard 1 in shard 2's place
+    first, _ = write_family(d("c"), 2, count={1: 3})
+    assert kind(first) == "ShardMismatch"
+    first, _ = write_family(d("d"), 2, drop_no=(1,))
+    assert kind(first) == "MissingSplitKey"
+    first, _ = write_family(d("e"), 2, total=5)
+    assert kind(first) == "TensorCountMismatch"
+    first, _ = write_family(d("f"), 2, total=False)
+    assert kind(first) == "MissingSplitKey"
+    first, _ = write_family(d("g"), 2, names={1: "blk.0.w"})
+    assert kind(first) == "DuplicateAcrossShards"
+    # metadata says split, the name does not follow the convention
+    odd = d("h") / "model.gguf"
+    odd.write_bytes(build_gguf([("w", [64, 2], 8, q8_payload(2, 64, 1))],
+                               [u16kv("split.no", 0), u16kv("split.count", 2), i32kv("split.tensors.count", 2)]))
+    assert kind(str(odd)) == "SplitNameMismatch"
+    big = d("i") / "m-00001-of-04000.gguf"
+    big.write_bytes(build_gguf([], [u16kv("split.no", 0), u16kv("split.count", 4000)]))
+    assert kind(str(big)) == "TooManySplits"

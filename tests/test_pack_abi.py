@@ -146,3 +146,24 @@ def test_slot_indices_and_argument_counts_match_the_reference_table():
         if name in packmod._SIGS:
             n_ref = len([a for a in by_name[name][1].split(",") if a.strip()])
             assert len(packmod._SIGS[name]) + 1 == n_ref, (name, packmod._SIGS[name], by_name[name][1])   # + the stream
+
+
+def test_table_is_resolved_against_the_device_capability():
+    """packs/cuda/src/exports.cuh:2118-2400 NULLs what the running die cannot execute; sm_100a
+    code loads on compute capability 10.0 only, so any other device gets an empty table."""
+    lib = C.CDLL(pb.lib_path())
+    buf = (C.c_uint8 * packmod.TABLE_BYTES)()
+    fn = lib.pdk_kernels_for_cc
+    fn.argtypes = [C.c_int, C.c_int, C.c_void_p]
+    fn.restype = C.c_int
+
+    def filled(major, minor):
+        assert fn(major, minor, C.addressof(buf)) == 0
+        words = (C.c_uint64 * (packmod.TABLE_BYTES // 8)).from_buffer(buf)
+        assert words[0] & 0xffffffff == packmod.TABLE_BYTES
+        return sum(1 for i in range(packmod.TABLE_SLOTS) if words[1 + i])
+
+    assert filled(10, 0) == len(packmod.SLOTS)
+    for cc in [(9, 0), (10, 3), (12, 0), (12, 1), (8, 9)]:
+        assert filled(*cc) == 0
+    assert fn(10, 0, None) == 1
