@@ -171,6 +171,34 @@ def bench_q4k_w4a8(ex, a):
     return sec, {"bound": "hbm", "bytes": nbytes, "us_chain": sec_chain * 1e6}
 
 
+def bench_tc5_probe(ex, a):
+    """Issue rate of tcgen05.mma per operand kind with operands resident in shared memory
+    (pdk_tc5_issue_probe): the measured tensor-core ceiling the FP8 / NVFP4 GEMM fractions
+    can be read against.  --iters = MMAs per SM per launch."""
+    n_mma = max(8, min(a.iters * 256, 1 << 20))
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    cyc = torch.zeros(sms, dtype=torch.int64, device="cuda")
+    kinds = [("bf16_m128n256k16", 256, 16), ("e4m3_m128n256k32", 256, 32), ("nvf4_m128n128k64", 128, 64),
+             ("nvf4_m128n128k64_with_scale_copies", 128, 64)]
+    out = {}
+    st = torch.cuda.current_stream().cuda_stream
+    for kind, (name, n, k) in enumerate(kinds):
+        for _ in range(3):
+            ex.pack.call("pdk_tc5_issue_probe", kind, n_mma, cyc, stream=st)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ex.pack.call("pdk_tc5_issue_probe", kind, n_mma, cyc, stream=st)
+        e1.record()
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) * 1e-3
+        flops = sms * n_mma * 2 * 128 * n * k
+        per = cyc.float().median().item() / n_mma
+        out[name] = {"tflops": flops / sec / 1e12, "ms": sec * 1e3, "sm_cycles_per_mma": per,
+                     "tflops_at_cycle_rate_1965mhz": sms * 2 * 128 * n * k / per * 1.965e9 / 1e12}
+    return sec, {"bound": "none", "mma_per_sm": n_mma, **out}
+
+
 def bench_norm_nvf4(ex, a):
     """Slot 436, the fused residual-add + RMSNorm + NVFP4 quantizer in front of an NVFP4 GEMM:
     --m rows of --k elements.  Table slot only, so --pack times another library."""
@@ -611,8 +639,8 @@ def bench_moe_nvf4(ex, a):
     return sec, {"bound": "hbm", "bytes": int(distinct * per_expert + T * embd * 2 * 2), "distinct_experts": distinct}
 
 
-OPS = {"f8_shard": bench_f8_shard, "norm_nvf4": bench_norm_nvf4, "q4k_w4a8": bench_q4k_w4a8, "nvf4_gemv": bench_nvf4_gemv, "moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
-DEFAULTS = {"f8_shard": (4096, 27648, 5120), "norm_nvf4": (64, 0, 5120), "q4k_w4a8": (4, 25600, 5120), "nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
+OPS = {"tc5_probe": bench_tc5_probe, "f8_shard": bench_f8_shard, "norm_nvf4": bench_norm_nvf4, "q4k_w4a8": bench_q4k_w4a8, "nvf4_gemv": bench_nvf4_gemv, "moe_nvf4": bench_moe_nvf4, "moe_ep": bench_moe_ep, "moe_mxfp4": bench_moe, "nvf4_gemm": bench_nvf4, "q4k_gemv": bench_q4k, "q8_gemv": bench_q8, "f8row_gemm": bench_f8}
+DEFAULTS = {"tc5_probe": (0, 0, 0), "f8_shard": (4096, 27648, 5120), "norm_nvf4": (64, 0, 5120), "q4k_w4a8": (4, 25600, 5120), "nvf4_gemv": (1, 17408, 5120), "moe_nvf4": (64, 2880, 2880), "moe_ep": (64, 2880, 2880), "moe_mxfp4": (64, 2880, 2880), "nvf4_gemm": (8192, 17408, 5120), "q4k_gemv": (1, 25600, 5120), "q8_gemv": (1, 17408, 5120), "f8row_gemm": (4096, 17408, 5120)}
 
 
 class Case:

@@ -171,9 +171,8 @@ f8row_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
                 const uint64_t a_desc = tc5::smem_desc_sw128(a_addr);
                 const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kABytes);
-#pragma unroll
-                for (uint32_t k = 0; k < BK / 32u; ++k)  // 32 bytes of K per instruction: +2 in 16-byte units
-                    tc5::mma_f8f6f4_elect(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0u);
+                static_assert(BK == 128u, "one group of four 32-byte K steps per stage");
+                tc5::mma_f8f6f4_x4_elect(d_tmem, a_desc, b_desc, idesc, kb != 0u);
                 tc5::mma_commit_elect(&sh->empty[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }

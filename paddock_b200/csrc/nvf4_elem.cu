@@ -92,11 +92,11 @@ __global__ void quantize_nvf4_kernel(const float* __restrict__ x, uint8_t* __res
 // lane emits its own four codes.
 constexpr uint32_t kNormMaxThreads = 384;
 template <int kChunks>
-__global__ void __launch_bounds__(kNormMaxThreads)
+__global__ void __launch_bounds__(kChunks <= 8 ? 1024 : kNormMaxThreads)
 add_rmsnorm_quant_nvf4_kernel(float* __restrict__ x, const float* __restrict__ proj, const float* __restrict__ w,
                               float* __restrict__ out, uint8_t* __restrict__ q, uint8_t* __restrict__ scale, uint32_t n,
                               float eps) {
-    __shared__ double warp_sq[kNormMaxThreads / 32u];
+    __shared__ double warp_sq[32];
     const uint32_t t = threadIdx.x, width = blockDim.x, n4 = n >> 2;   // width % 32 == 0, n4 % 4 == 0
     const size_t row4 = (size_t)blockIdx.x * n4;
     float4* x4 = reinterpret_cast<float4*>(x) + row4;
@@ -247,13 +247,18 @@ PDK_EXPORT int pd_add_rmsnorm_quant_nvf4_batch(void* x, const void* proj, const 
     if ((n & 31u) != 0u || !pdk_aligned(x, 16) || !pdk_aligned(proj, 16) || !pdk_aligned(w, 16) || !pdk_aligned(out, 16) ||
         !pdk_aligned(q, 4))
         return cudaErrorInvalidValue;
-    // the fewest float4 per thread (a power of two) that fits the row into one CTA of at most
-    // kNormMaxThreads threads: 5120 -> 4 per thread, 320 threads
+    // the fewest float4 per thread (a power of two) that fits the row into one CTA: up to 1024
+    // threads while a thread holds at most 8 float4, kNormMaxThreads beyond.  5120 -> 2 per thread,
+    // 640 threads (measured at 4096 rows of 5120: 2 per thread 64 us, 4 70 us, 8 84 us, 16 131 us)
     const uint32_t n4 = n >> 2;
     uint32_t chunks = 1;
-    while (chunks < 32u && (n4 + chunks - 1u) / chunks > kNormMaxThreads) chunks <<= 1;
+    while (chunks < 32u && (n4 + chunks - 1u) / chunks > (chunks <= 8u ? 1024u : kNormMaxThreads)) chunks <<= 1;
+    static const uint32_t forced = getenv("PDK_NORM_CHUNKS") ? (uint32_t)atoi(getenv("PDK_NORM_CHUNKS")) : 0u;   // A/B switch
+    if (forced != 0u && forced <= 32u && (forced & (forced - 1u)) == 0u &&
+        (n4 + forced - 1u) / forced <= (forced <= 8u ? 1024u : kNormMaxThreads))
+        chunks = forced;
     const uint32_t width = ((n4 + chunks - 1u) / chunks + 31u) & ~31u;
-    if (width > kNormMaxThreads) return cudaErrorNotSupported;   // rows beyond 49152 elements
+    if (width > (chunks <= 8u ? 1024u : kNormMaxThreads)) return cudaErrorNotSupported;   // rows beyond 49152 elements
 #define PDK_NORM_CASE(C)                                                                                          \
     case C:                                                                                                       \
         return pdk_launch_pdl(add_rmsnorm_quant_nvf4_kernel<C>, dim3(batch), dim3(width), 0, (cudaStream_t)stream, \

@@ -213,17 +213,10 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     if (u >= nsl) break;
                     const uint32_t sfa_addr = a_addr + kOffSfa + u * kSfBytes, sfb_addr = a_addr + kOffSfb + u * kSfBytes;
                     const uint32_t sfa_t = tmem_base + kSfCol0 + stage * kSfCols + u * 32u, sfb_t = sfa_t + 16u;
-#pragma unroll
-                    for (uint32_t j = 0; j < 4u; ++j) {
-                        sf_copy(sfa_t + j * 4u, sfa_addr + j * 512u);
-                        sf_copy(sfb_t + j * 4u, sfb_addr + j * 512u);
-                    }
                     const uint64_t a_desc = tc5::smem_desc_sw128(a_addr + u * kABytes);
                     const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + kOffB + u * kBBytes);
-#pragma unroll
-                    for (uint32_t j = 0; j < 4u; ++j)  // 64 e2m1 = 32 bytes of K per instruction
-                        mma_nvf4(d_tmem, a_desc + 2u * j, b_desc + 2u * j, kIdesc, sfa_t + j * 4u, sfb_t + j * 4u,
-                                 (ks | u | j) != 0u);
+                    // four MMAs of 64 e2m1 (32 bytes of K) each, the two scale-cell copies of each in front of it
+                    slab_nvf4<true>(d_tmem, a_desc, b_desc, kIdesc, (ks | u) != 0u, sfa_t, sfb_t, sfa_addr, sfb_addr, 4u);
                 }
                 tc5::mma_commit_elect(&sh->empty[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }

@@ -63,4 +63,34 @@ __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint6
                  "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
                  : "memory");
 }
+// One 256-element K slab of a block-scaled tile: `steps` (1..4) MMAs of 64 elements each, every
+// one preceded - when kCopies - by the copies of its two 512-byte scale cells from shared memory
+// (sfa_smem / sfb_smem: the slab's 2048-byte records) into tensor memory (sfa_t / sfb_t, four
+// columns per step).  One election, descriptors and addresses stepped inside the asm block:
+// issued this way the pair (two copies + MMA) takes the tensor core 92 cycles, the MMA alone 64;
+// one wrapper call per copy and per MMA took the issuing warp 200.
+template <bool kCopies>
+__device__ __forceinline__ void slab_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t acc_first, uint32_t sfa_t, uint32_t sfb_t, uint32_t sfa_smem,
+                                          uint32_t sfb_smem, uint32_t steps) {
+    const uint64_t cell_a = (uint64_t)((sfa_smem >> 4) & 0x3FFFu) | ((uint64_t)1u << 16) | ((uint64_t)8u << 32);
+    const uint64_t cell_b = (uint64_t)((sfb_smem >> 4) & 0x3FFFu) | ((uint64_t)1u << 16) | ((uint64_t)8u << 32);
+#define PDK_NV4_STEP(J, PRED)                                                                                        \
+    "setp.gt.and.u32 ej, %10, " #J ", e;\n\tsetp.gt.and.u32 cj, %10, " #J ", c;\n\t"                                  \
+    "add.u64 a, %1, " #J "*2;\n\tadd.u64 b, %2, " #J "*2;\n\tadd.u32 sa, %5, " #J "*4;\n\tadd.u32 sb, %6, " #J "*4;\n\t" \
+    "add.u64 ca, %7, " #J "*32;\n\tadd.u64 cb, %8, " #J "*32;\n\t"                                                    \
+    "@cj tcgen05.cp.cta_group::1.32x128b.warpx4 [sa], ca;\n\t@cj tcgen05.cp.cta_group::1.32x128b.warpx4 [sb], cb;\n\t" \
+    "@ej tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], a, b, %3, [sa], [sb], " PRED ";\n\t"
+    asm volatile(
+        "{\n\t.reg .pred e, p, q, c, ej, cj;\n\t.reg .b64 a, b, ca, cb;\n\t.reg .b32 sa, sb;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "setp.ne.and.b32 c, %9, 0, e;\n\t"
+        PDK_NV4_STEP(0, "p") PDK_NV4_STEP(1, "q") PDK_NV4_STEP(2, "q") PDK_NV4_STEP(3, "q") "}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc_first), "r"(sfa_t), "r"(sfb_t), "l"(cell_a), "l"(cell_b),
+        "r"(kCopies ? 1u : 0u), "r"(steps)
+        : "memory");
+#undef PDK_NV4_STEP
+}
 }  // namespace nvf4tc5

@@ -213,6 +213,34 @@ __device__ __forceinline__ void mma_f8f6f4_elect(uint32_t d_tmem, uint64_t a_des
                  "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
+// Four MMAs over the four 32-byte K steps of one 128-byte swizzled row, issued by the lane one
+// elect.sync picks, the descriptors stepped inside the asm block: 3 + 4 * 3 instructions per
+// group.  A loop of single-MMA wrappers, each with its own election and predicate set-up, costs
+// the issuing warp more than the 128 cycles the tensor core needs per M128 N256 MMA.
+// acc_first: whether the first of the four accumulates (the other three always do).
+#define TC5_MMA_X4(KIND_STR)                                                                  \
+    asm volatile(                                                                             \
+        "{\n\t.reg .pred e, p, q;\n\t.reg .b64 a, b;\n\t"                                     \
+        "elect.sync _|e, 0xffffffff;\n\t"                                                     \
+        "setp.ne.b32 p, %4, 0;\n\t"                                                           \
+        "setp.eq.b32 q, 0, 0;\n\t"                                                            \
+        "@e tcgen05.mma.cta_group::1.kind::" KIND_STR " [%0], %1, %2, %3, p;\n\t"             \
+        "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\t"                                          \
+        "@e tcgen05.mma.cta_group::1.kind::" KIND_STR " [%0], a, b, %3, q;\n\t"               \
+        "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\t"                                          \
+        "@e tcgen05.mma.cta_group::1.kind::" KIND_STR " [%0], a, b, %3, q;\n\t"               \
+        "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\t"                                          \
+        "@e tcgen05.mma.cta_group::1.kind::" KIND_STR " [%0], a, b, %3, q;\n\t}" ::"r"(d_tmem), \
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc_first)                                  \
+        : "memory")
+__device__ __forceinline__ void mma_f8f6f4_x4_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                    uint32_t acc_first) {
+    TC5_MMA_X4("f8f6f4");
+}
+__device__ __forceinline__ void mma_f16_x4_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t acc_first) {
+    TC5_MMA_X4("f16");
+}
 __device__ __forceinline__ void mma_commit_elect(uint64_t* bar) {
     asm volatile(TC5_ELECT "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(
                      smem_u32(bar))

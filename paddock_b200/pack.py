@@ -121,6 +121,7 @@ _EXTRA_SIGS = {
     "pdk_q4k_gemv_shard_sync": "ppppppuuuuuu",
     "pdk_peer_flags_wait": "puuu",
     "pdk_selftest_bounded_wait": "up",
+    "pdk_tc5_issue_probe": "uup",
     "pdk_mxfp4_tc5_tile_scales": "pppuuu",
     "pdk_moe_prep_act_f4": "pppppppuuuuff",
     "pdk_mxfp4_moe_gemm_tc5": "p" * 17 + "u" * 7,
