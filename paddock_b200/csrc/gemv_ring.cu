@@ -537,6 +537,261 @@ int launch_ring(const void* data, const void* recs, const float* bias, const flo
                           in_dim, out_dim, xq, xq_scale, po, pl, err);
 }
 
+
+// ---------------------------------------------------------------------------
+// Q8_0 with 2..8 tokens on the same ring: the tokens are the mma's eight columns.
+//
+// Plans with one unit pair per warp only (W == K / 512, K = 2048 .. 6144): warp w meets the same
+// 512 activations of every token in every tile, so its B operand - two int8 limbs of the 15-bit
+// block floating point, per (token, 32-block) power-of-two steps - is built once from x and stays
+// in 64 registers.  Per 32-weight block: one ldmatrix.x4 takes the 16 rows x 32 int8 out of the
+// swizzled box (conflict free: the eight rows of a matrix sit in eight different bank groups),
+// one mma per limb gives the integer tile [16 rows][8 tokens], and lane (g, t) folds its four
+// entries with d[row][block] * step[token][block] in f32.  Weights leave HBM once for all tokens.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kBatchRedBufs = 4;
+
+struct BatchPlan {
+    uint32_t W, D;
+    uint32_t off_steps, off_red, off_bar, off_rec, off_data, smem_bytes;
+};
+
+enum : unsigned int { kErrBatchFull = 0x18, kErrBatchFold = 0x19, kErrBatchFree = 0x1a, kErrBatchDrain = 0x1b };
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t saddr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(saddr));
+}
+
+__global__ void __launch_bounds__(kMaxWarps * 32u, 1)
+gemm_ring_q8_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant__ CUtensorMap rmap,
+                    const float* __restrict__ bias, const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim,
+                    uint32_t out_dim, uint32_t batch, const BatchPlan pl, unsigned int* __restrict__ err) {
+    constexpr uint32_t kUnitData = 2u * kBoxBytes;             // a unit's two boxes (blocks 0..3 | 4..7)
+    constexpr uint32_t kRecRow = 2u * Q80::kRecBytes;          // a pair's records of one row
+    constexpr uint32_t kStageData = 2u * kUnitData, kStageRec = 16u * kRecRow;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    float* steps = reinterpret_cast<float*>(smem + pl.off_steps);   // [W][16 blocks][8 tokens]
+    float* red = reinterpret_cast<float*>(smem + pl.off_red);       // [kBatchRedBufs][W][16 rows][8 tokens]
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + pl.off_bar);
+    uint64_t* red_full = full + kMaxWarps * kMaxDepth;
+    uint64_t* red_free = red_full + kBatchRedBufs;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(red_free + kBatchRedBufs);
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t W = pl.W, D = pl.D;
+    const uint32_t n_tiles = (out_dim + 15u) >> 4;
+    const uint32_t tile_lo = (uint32_t)((uint64_t)blockIdx.x * n_tiles / gridDim.x);
+    const uint32_t tile_hi = (uint32_t)((uint64_t)(blockIdx.x + 1u) * n_tiles / gridDim.x);
+    const uint32_t my_tiles = tile_hi - tile_lo;
+
+    uint64_t* my_full = full + warp * kMaxDepth;
+    uint8_t* my_data = smem + pl.off_data + (size_t)warp * D * kStageData;
+    uint8_t* my_rec = smem + pl.off_rec + (size_t)warp * D * kStageRec;
+
+    auto issue = [&](uint32_t stage, uint32_t tl) {
+        uint64_t* bar = my_full + stage;
+        tc5::mbar_arrive_expect_tx_elect(bar, kStageData + kStageRec);
+        const int32_t row = (int32_t)((tile_lo + tl) * 16u);
+#pragma unroll
+        for (uint32_t b = 0; b < 4u; ++b)
+            tc5::tma_load_2d_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
+                                   (int32_t)(warp * 2u * Q80::kDataBytes + b * 128u), row);
+        tc5::tma_load_2d_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(warp * kRecRow), row);
+    };
+
+    if (lane == 0u) {
+        for (uint32_t s = 0; s < D; ++s) tc5::mbar_init(my_full + s, 1u);
+        tc5::mbar_fence_init();
+    }
+    __syncwarp();
+    uint32_t issued = 0;
+    if (my_tiles > 0u) { issue(0u, 0u); issued = 1u; }
+    if (tid == 0u) {
+        for (uint32_t b = 0; b < kBatchRedBufs; ++b) {
+            tc5::mbar_init(&red_full[b], W);
+            tc5::mbar_init(&red_free[b], 1u);
+        }
+        *abort_flag = 0;
+        tc5::mbar_fence_init();
+    }
+    __syncthreads();
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();   // x and y belong to the previous kernel until here
+
+    // ---- B operand: token g, this warp's 16 blocks.  Lane (g, t) holds elements 4t..4t+3 and
+    // 16+4t..16+4t+3 of each block, which is exactly its share of the mma's B fragment.
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    uint32_t bh[16][2], bl[16][2];
+    {
+        const float* xt = x + (size_t)(g < batch ? g : 0u) * in_dim + warp * 512u + 4u * t;
+        float* my_steps = steps + warp * 128u;
+#pragma unroll
+        for (uint32_t b = 0; b < 16u; ++b) {
+            float4 v0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), v1 = v0;
+            if (g < batch) {
+                v0 = *reinterpret_cast<const float4*>(xt + b * 32u);
+                v1 = *reinterpret_cast<const float4*>(xt + b * 32u + 16u);
+            }
+            float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                               fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            // amax < 2^ex -> step 2^(ex-14): |q| <= 2^14, q = 256 * hi + lo with lo in [-128, 127]
+            float step = 1.0f, inv = 0.0f;
+            if (amax > 0.0f && amax < 3.0e38f) {
+                const int ex = max((int)(__float_as_uint(amax) >> 23) - 126, -110);
+                step = __uint_as_float((uint32_t)(ex + 113) << 23);
+                inv = __uint_as_float((uint32_t)(141 - ex) << 23);
+            }
+            const int q0 = __float2int_rn(v0.x * inv), q1 = __float2int_rn(v0.y * inv), q2 = __float2int_rn(v0.z * inv),
+                      q3 = __float2int_rn(v0.w * inv), q4 = __float2int_rn(v1.x * inv), q5 = __float2int_rn(v1.y * inv),
+                      q6 = __float2int_rn(v1.z * inv), q7 = __float2int_rn(v1.w * inv);
+            bl[b][0] = __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+            bl[b][1] = __byte_perm(__byte_perm(q4, q5, 0x0040), __byte_perm(q6, q7, 0x0040), 0x5410);
+            bh[b][0] = __byte_perm(__byte_perm(q0 + 128, q1 + 128, 0x0051), __byte_perm(q2 + 128, q3 + 128, 0x0051), 0x5410);
+            bh[b][1] = __byte_perm(__byte_perm(q4 + 128, q5 + 128, 0x0051), __byte_perm(q6 + 128, q7 + 128, 0x0051), 0x5410);
+            if (t == 0u) my_steps[b * 8u + g] = step;
+        }
+        __syncwarp();
+    }
+    while (issued < D && issued < my_tiles) { issue(issued % D, issued); ++issued; }
+    const tc5::WaitCtx ctx{abort_flag, err};
+
+    // ldmatrix row addresses: lane l supplies row (l & 7) + 8 * ((l >> 3) & 1) of k-half (l >> 4);
+    // block bb of a unit = chunks 2 * (bb & 3) + k-half of box bb >> 2
+    const uint32_t m_row = (lane & 7u) + ((lane >> 3) & 1u) * 8u, m_half = lane >> 4;
+    uint32_t a_off[4];
+#pragma unroll
+    for (uint32_t c = 0; c < 4u; ++c) a_off[c] = swz(m_row, 2u * c + m_half);
+    const float* my_steps = steps + warp * 128u + 2u * t;
+    const uint32_t rec_g = g * kRecRow, rec8 = 8u * kRecRow;
+
+    constexpr uint32_t kNone = 0xffffffffu;
+    uint32_t pend = kNone;
+    bool alive = true;
+    auto fold_tile = [&](uint32_t tl_f) {
+        const uint32_t rbf = tl_f % kBatchRedBufs;
+        const float* rbuf = red + (size_t)rbf * (W * 128u);
+        // lane -> row lane & 15, tokens 4 * (lane >> 4) .. + 3
+        const uint32_t r = lane & 15u, c0 = (lane >> 4) * 4u;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t w = 0; w < W; ++w) {
+            const float4 p = *reinterpret_cast<const float4*>(rbuf + w * 128u + r * 8u + c0);
+            v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+        }
+        __syncwarp();
+        if (lane == 0u) tc5::mbar_arrive(&red_free[rbf]);
+        const uint32_t row = (tile_lo + tl_f) * 16u + r;
+        if (row < out_dim) {
+            const float bv = bias ? bias[row] : 0.0f;
+#pragma unroll
+            for (uint32_t c = 0; c < 4u; ++c)
+                if (c0 + c < batch) y[(size_t)(c0 + c) * out_dim + row] = v[c] + bv;
+        }
+    };
+    auto poll_fold = [&](bool block) {
+        if (pend == kNone || !alive) return;
+        const uint32_t rbf = pend % kBatchRedBufs, ph = (pend / kBatchRedBufs) & 1u;
+        bool done;
+        if (block) {
+            alive = __all_sync(0xffffffffu, tc5::mbar_wait(&red_full[rbf], ph, ctx, kErrBatchFold, rbf));
+            done = alive;
+        } else {
+            done = __all_sync(0xffffffffu, tc5::mbar_try_wait(&red_full[rbf], ph));
+        }
+        if (done) {
+            fold_tile(pend);
+            pend = kNone;
+        }
+    };
+
+    uint32_t stage = 0, phase = 0, rb = 0, rb_phase = 0, owner = 0;
+    for (uint32_t tl = 0; tl < my_tiles; ++tl) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // (g, 2t) (g, 2t+1) (g+8, 2t) (g+8, 2t+1)
+        if (alive) alive = __all_sync(0xffffffffu, tc5::mbar_wait(my_full + stage, phase, ctx, kErrBatchFull, stage));
+        if (alive) {
+            const uint32_t sd = tc5::smem_u32(my_data + stage * kStageData);
+            const uint8_t* sr = my_rec + stage * kStageRec + rec_g;
+#pragma unroll
+            for (uint32_t i = 0; i < 2u; ++i) {
+                const uint4 dg = *reinterpret_cast<const uint4*>(sr + i * Q80::kRecBytes);
+                const uint4 dg8 = *reinterpret_cast<const uint4*>(sr + rec8 + i * Q80::kRecBytes);
+#pragma unroll
+                for (uint32_t bb = 0; bb < 8u; ++bb) {
+                    const uint32_t b = i * 8u + bb;
+                    uint32_t a0, a1, a2, a3;
+                    ldmatrix_x4(sd + i * kUnitData + (bb >> 2) * kBoxBytes + a_off[bb & 3u], a0, a1, a2, a3);
+                    int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+                    mma_s8_nv(ch, a0, a1, a2, a3, bh[b][0], bh[b][1]);
+                    mma_s8_nv(cl, a0, a1, a2, a3, bl[b][0], bl[b][1]);
+                    const float2 s = *reinterpret_cast<const float2*>(my_steps + b * 8u);
+                    const uint32_t wg = word4(dg, bb >> 1), wg8 = word4(dg8, bb >> 1);
+                    const __half2 hg = *reinterpret_cast<const __half2*>(&wg), hg8 = *reinterpret_cast<const __half2*>(&wg8);
+                    const float d0 = (bb & 1u) ? __high2float(hg) : __low2float(hg);
+                    const float d8 = (bb & 1u) ? __high2float(hg8) : __low2float(hg8);
+                    acc[0] += (float)(ch[0] * 256 + cl[0]) * (d0 * s.x);
+                    acc[1] += (float)(ch[1] * 256 + cl[1]) * (d0 * s.y);
+                    acc[2] += (float)(ch[2] * 256 + cl[2]) * (d8 * s.x);
+                    acc[3] += (float)(ch[3] * 256 + cl[3]) * (d8 * s.y);
+                }
+            }
+            __syncwarp();
+            if (issued < my_tiles) { issue(issued % D, issued); ++issued; }
+        }
+        if (++stage == D) { stage = 0; phase ^= 1u; }
+
+        float* rbuf = red + (size_t)rb * (W * 128u);
+        if (alive && tl >= kBatchRedBufs)
+            alive = __all_sync(0xffffffffu, tc5::mbar_wait(&red_free[rb], rb_phase ^ 1u, ctx, kErrBatchFree, rb));
+        if (alive) {
+            *reinterpret_cast<float2*>(rbuf + warp * 128u + g * 8u + 2u * t) = make_float2(acc[0], acc[1]);
+            *reinterpret_cast<float2*>(rbuf + warp * 128u + (g + 8u) * 8u + 2u * t) = make_float2(acc[2], acc[3]);
+            __syncwarp();
+            if (lane == 0u) tc5::mbar_arrive(&red_full[rb]);
+        }
+        if (owner == warp) {
+            poll_fold(true);
+            pend = tl;
+        }
+        poll_fold(false);
+        if (++owner == W) owner = 0;
+        if (++rb == kBatchRedBufs) { rb = 0; rb_phase ^= 1u; }
+    }
+    poll_fold(true);
+    if (!alive) {
+        const unsigned long long t0 = tc5::globaltimer_ns();
+        for (uint32_t s = 0; s < D && s < issued; ++s) {
+            const uint32_t n = issued - 1u - ((issued - 1u - s) % D);
+            while (!tc5::mbar_try_wait(my_full + s, (n / D) & 1u)) {
+                if (tc5::globaltimer_ns() - t0 > tc5::kWaitBudgetNs) {
+                    if (lane == 0u) tc5::report(err, kErrBatchDrain, s);
+                    break;
+                }
+            }
+        }
+    }
+}
+
+bool make_batch_plan(uint32_t in_dim, BatchPlan& p) {
+    if (in_dim == 0u || (in_dim & 511u) != 0u) return false;
+    const uint32_t W = in_dim >> 9;
+    if (W < 4u || W > kMaxWarps) return false;
+    constexpr uint32_t kStage = 4u * kBoxBytes + 32u * Q80::kRecBytes;
+    p.W = W;
+    p.off_steps = 0u;
+    p.off_red = W * 512u;
+    p.off_bar = p.off_red + kBatchRedBufs * W * 512u;
+    p.off_rec = (p.off_bar + (kMaxWarps * kMaxDepth + 2u * kBatchRedBufs) * 8u + 16u + 127u) & ~127u;
+    if (p.off_rec + 1024u + 2u * W * kStage > kSmemMax) return false;
+    p.D = (kSmemMax - p.off_rec - 1024u) / (W * kStage);
+    if (p.D > kMaxDepth) p.D = kMaxDepth;
+    p.off_data = (p.off_rec + W * p.D * 32u * Q80::kRecBytes + 1023u) & ~1023u;
+    p.smem_bytes = p.off_data + W * p.D * 4u * kBoxBytes;
+    return p.smem_bytes <= kSmemMax && p.D >= 2u;
+}
+
 }  // namespace
 
 // gemv_i8.cu: the register-staged kernel
@@ -575,6 +830,39 @@ int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, con
                      uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
     const int rc = launch_ring<RQ80>(data, scale, bias, x, y, in_dim, out_dim, st);
     return rc != -1 ? rc : pdk_q8_0_gemv_i8_regs(data, scale, bias, x, y, in_dim, out_dim, st);
+}
+
+// Q8_0 small batch: x f32 [batch][in_dim], y f32 [batch][out_dim]; tokens in groups of up to eight,
+// one weight pass per group.  -1 when the shape is outside the plan (K / 512 warps, 4 .. 12).
+int pdk_q8_0_gemm_i8(const void* data, const void* scale, const float* bias, const float* x, float* y, uint32_t in_dim,
+                     uint32_t out_dim, uint32_t batch, cudaStream_t st) {
+    if (force_regs() || !pdk_aligned(scale, 16)) return -1;
+    BatchPlan pl;
+    if (!make_batch_plan(in_dim, pl)) return -1;
+    const MapEntry* maps = nullptr;
+    if (plane_maps<RQ80>(data, scale, in_dim, out_dim, &maps) != 0) return -1;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        e = cudaFuncSetAttribute(gemm_ring_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax);
+        if (e != cudaSuccess) return (int)e;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    unsigned int* err = pdk_error_word();
+    if (err == nullptr) return (int)cudaErrorUnknown;
+    const uint32_t n_tiles = (out_dim + 15u) / 16u;
+    uint32_t grid = (uint32_t)pdk_sm_count();
+    if (grid > n_tiles) grid = n_tiles;
+    for (uint32_t t0 = 0; t0 < batch; t0 += 8u) {
+        const uint32_t nb = batch - t0 < 8u ? batch - t0 : 8u;
+        const int rc = pdk_launch_pdl(gemm_ring_q8_kernel, dim3(grid), dim3(pl.W * 32u), (size_t)pl.smem_bytes, st, maps->dmap,
+                                      maps->rmap, bias, x + (size_t)t0 * in_dim, y + (size_t)t0 * out_dim, in_dim, out_dim,
+                                      nb, pl, err);
+        if (rc != 0) return rc;
+    }
+    return 0;
 }
 
 // Q4_K GEMV on int8 activations (xq int8 [in_dim], one f32 scale per 32): same kernels, the

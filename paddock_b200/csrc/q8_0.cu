@@ -11,6 +11,8 @@
 
 #include "pdk_common.cuh"
 
+int pdk_q8_0_gemm_i8(const void* data, const void* scale, const float* bias, const float* x, float* y, uint32_t in_dim,
+                     uint32_t out_dim, uint32_t batch, cudaStream_t st);
 int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, const float* x, float* y,
                      uint32_t in_dim, uint32_t out_dim, cudaStream_t st);
 
@@ -164,9 +166,12 @@ PDK_EXPORT int pd_q8_0_gemm_repacked(const void* data, const void* scale, const 
     float* yf = (float*)y;
     auto st = (cudaStream_t)stream;
     if (!force_plain()) {
-        // There is no batch kernel on the tensor path for Q8_0 yet: one decode GEMV per token (18 us each at
-        // K=5120 N=17408) beats the plain f32 kernel below (169 us per four tokens)
-        int rc = 0;
+        // two or more tokens: the tokens-as-columns kernel on the TMA ring (one weight pass per eight
+        // tokens); shapes outside its plan take one decode GEMV per token, which still beats the plain
+        // f32 kernel below (169 us per four tokens against 18 us per token at K=5120 N=17408)
+        int rc = batch >= 2u ? pdk_q8_0_gemm_i8(data, scale, (const float*)bias, xf, yf, in_dim, out_dim, batch, st) : -1;
+        if (rc != -1) return rc;
+        rc = 0;
         for (uint32_t t = 0; t < batch && rc == 0; ++t)
             rc = pdk_q8_0_gemv_i8(data, scale, (const float*)bias, xf + (size_t)t * in_dim, yf + (size_t)t * out_dim, in_dim,
                                   out_dim, st);

@@ -69,6 +69,33 @@ def test_q8_0_gemm_small_batch(pack, batch):
     assert cond_err(d_y.cpu().numpy().reshape(batch, n), ref, ab) < 1e-5
 
 
+@pytest.mark.parametrize("k,n", [(5120, 1000), (2048, 33), (6144, 160)])
+@pytest.mark.parametrize("batch", [2, 4, 8, 9, 16])
+def test_q8_0_gemm_tokens_as_columns(pack, k, n, batch):
+    """K / 512 between 4 and 12: the ring kernel with the tokens as the mma's columns, one weight
+    pass per eight tokens; rows that do not fill the last 16-row tile, a bias, tokens that do not
+    fill the last group of eight."""
+    w = oracle.fill_normal(n * k, 35 + k, 0.02)
+    x = bf16_activations(batch * k, 36 + batch)
+    x[:64] = 0.0                                   # all-zero activation blocks: step 1, limbs 0
+    x[k + 32:k + 64] *= 1e-20
+    bias = oracle.fill_normal(n, 37, 0.5)
+    raw, d_data, d_scale = q8_planes(pack, w, n, k)
+    d_y = torch.full((batch * n,), float("nan"), dtype=torch.float32, device="cuda")
+    pack.call("q8_0_gemm_repacked", d_data, d_scale, dev_f32(bias), dev_f32(x), d_y, k, n, batch)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    ref, ab = oracle.matmul_f64(oracle.dequant_q8_0(raw), x, k, n, batch, with_abs=True)
+    y = d_y.cpu().numpy().reshape(batch, n) - bias[None, :]
+    assert np.isfinite(y).all()
+    assert cond_err(y, ref, ab) < 1e-5 < TOL
+    # bit-identical from call to call (fixed fold order)
+    d_y2 = torch.zeros_like(d_y)
+    pack.call("q8_0_gemm_repacked", d_data, d_scale, dev_f32(bias), dev_f32(x), d_y2, k, n, batch)
+    torch.cuda.synchronize()
+    assert torch.equal(d_y, d_y2)
+
+
 def test_q8_0_gemv_refuses_bad_shapes(pack):
     buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     assert pack.status("q8_0_gemv_repacked", buf, buf, None, buf, buf, 48, 4) == 1
