@@ -221,7 +221,17 @@ def other_configs(ex, quick):
     import torch
     import kbench
     it = 10 if quick else 30
+    # the tensor core's own issue rate per operand kind (operands resident in shared memory): the
+    # measured denominator beside the 2x / 4x bf16 proxies of the FP8 and NVFP4 records
+    probe = {}
+    try:
+        pr = kbench.run_case(ex, kbench.Case("tc5_probe", iters=128))
+        probe = {k: round(v["tflops"], 1) for k, v in pr.items() if isinstance(v, dict)}
+    except Exception as err:
+        probe = {"error": str(err)[:200]}
     cases = [("q8_0_gemv_n17408", kbench.Case("q8_gemv", graph=True, iters=it)),
+             ("q8_0_m4_n17408", kbench.Case("q8_gemv", m=4, graph=True, iters=it)),
+             ("q8_0_m16_n17408", kbench.Case("q8_gemv", m=16, graph=True, iters=it)),
              ("q4k_m4_n25600", kbench.Case("q4k_gemv", m=4, graph=True, iters=it)),
              ("q4k_m16_n25600", kbench.Case("q4k_gemv", m=16, graph=True, iters=it))]
     cases += [(f"fp8_m4096_n{n}", kbench.Case("f8row_gemm", m=4096, n=n, iters=max(5, it // 3))) for n in (5120, 17408, 27648)]
@@ -237,9 +247,14 @@ def other_configs(ex, quick):
                    "device_error": r["device_error"]}
             if case.op == "f8row_gemm":
                 rec.update(achieved=r["tflops"], unit="TFLOP/s", frac=r["frac_of_2x_bf16"], denominator="2 x measured bf16 burst")
+                if probe.get("e4m3_m128n256k32"):
+                    rec.update(frac_of_probe=r["tflops"] / probe["e4m3_m128n256k32"], probe_denominator="tcgen05.mma e4m3 issue rate")
             elif case.op == "nvf4_gemm" and case.m >= 512:
                 rec.update(achieved=r["tflops"], unit="TFLOP/s", frac=r["frac_of_4x_bf16"], denominator="4 x measured bf16 burst",
                            gbs=r["gbs"], frac_of_hbm=r["frac_of_hbm"])
+                if probe.get("nvf4_m128n128k64_with_scale_copies"):
+                    rec.update(frac_of_probe=r["tflops"] / probe["nvf4_m128n128k64_with_scale_copies"],
+                               probe_denominator="tcgen05.mma NVFP4 issue rate with its scale-cell copies")
             else:
                 rec.update(achieved=r["gbs"], unit="GB/s", frac=r["frac_of_hbm"], denominator="measured HBM copy")
             if "distinct_experts" in r:
@@ -249,6 +264,7 @@ def other_configs(ex, quick):
             out[name] = {"error": str(err)[:200]}
         gc.collect()
         torch.cuda.empty_cache()
+    out["tensor_core_probe_tflops"] = probe
     return out
 
 
