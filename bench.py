@@ -206,8 +206,12 @@ def run_reference(args, rank):
 
 
 def workload_config(n_gpus, exchange="peer"):
-    how = ("each rank's GEMV stores its band into every rank's y over NVLink (peer memory)" if exchange == "peer"
-           else "NCCL all-gather of y")
+    how = {"peer": "each rank's GEMV stores its band into every rank's y over NVLink (peer memory) and raises a per-step "
+                   "flag there; y double buffered, every launch checks on the device that the buffer's previous step "
+                   "has arrived from every rank, the last steps are checked by a wait kernel inside the timed region",
+           "peer-serial": "each rank's GEMV stores its band into every rank's y over NVLink (peer memory), then a wait "
+                          "kernel for every rank's flag, then the next step",
+           "nccl": "NCCL all-gather of y"}[exchange]
     return {"workload": "Q4_K decode GEMV M=1 K=5120 N=25600, f32 activations holding bf16 values",
             "sharding": "none" if n_gpus == 1 else f"N rows / {n_gpus} ranks, {how}",
             "l2": "cold: steps rotate over weight-plane clones totalling > 2x the 126 MB L2"}
@@ -299,10 +303,12 @@ def run_ours(args, rank, world, local_rank):
 
     # N > 1: the row bands are exchanged by the GEMV kernel's own stores into every rank's y over
     # NVLink (peer memory); --exchange nccl keeps the kernel local and all-gathers y with NCCL.
-    peer_out = None
+    peer_out = peer_b = None
     first_row, _ = shard.row_band(N_DIM, world, rank, align=16)
-    if world > 1 and args.exchange == "peer":
+    if world > 1 and args.exchange in ("peer", "peer-serial"):
         peer_out = shard.PeerOutput(N_DIM)
+        if args.exchange == "peer":
+            peer_b = shard.PeerOutput(N_DIM)     # y is double buffered: steps alternate between the two
         y_all = peer_out.local
         # the two exchanges must agree bit for bit
         ex.kquant_gemv(planes[0], x, y)
@@ -316,28 +322,40 @@ def run_ours(args, rank, world, local_rank):
             raise RuntimeError("peer-store exchange differs from the all-gather")
 
     # One pre-bound launcher per plane clone (arguments converted once; the call is the C ABI entry).
-    # N > 1, peer exchange: a step is the sharded GEMV, whose last CTA raises this rank's flag on every
-    # rank once its band is stored there, followed by the device-side wait for every rank's flag -
-    # what a consumer of y needs before it may read - so no step relies on a host barrier.  Both
-    # calls count their steps on the device, so their arguments never change.  (Folding the wait into
-    # the next GEMV's prologue instead - one launch per step - measured slower: 25.8 against 19.0 us
-    # at two GPUs; every CTA then idles through the peers' signalling latency.)
+    # N > 1, peer exchange (default): a step is ONE launch, the sharded GEMV whose last CTA raises this
+    # rank's flag on every rank once its band is stored there and then checks, on the device and with
+    # a bounded wait, that every rank's band of the same y buffer's previous step has arrived here -
+    # the condition for re-using the buffer.  y is double buffered and steps alternate, so
+    # consecutive steps overlap the way single-GPU launches do while every step's arrival is still
+    # observed on the device; the last step of each buffer is observed by a wait kernel at the end of
+    # the timed region.  No step relies on a host barrier, and the calls count their steps on the
+    # device, so their arguments never change and a captured sequence replays.
+    # --exchange peer-serial is the single-buffered loop: GEMV, then a wait kernel for every rank's
+    # flag, then the next GEMV (a consumer that must read y before the next step starts).
     st = torch.cuda.current_stream().cuda_stream
+    bufs = [b for b in (peer_out, peer_b) if b is not None]
 
     def bind_all(stream, xin, yout):
+        """-> (launch(i) for step i, tail() that observes the arrival of the last steps)."""
         if peer_out is not None:
-            gem = [ex.pack.bind("pdk_q4k_gemv_shard_sync", p.data, p.scales, xin, peer_out.ptrs_address(),
-                                peer_out.flag_ptrs_address(), peer_out.ctr, world, rank, first_row, 0, p.dims[0],
-                                p.dims[1], stream=stream) for p in planes]
-            wait = ex.pack.bind("pdk_peer_flags_wait", peer_out.flags, world, 0, 2000000, stream=stream)
-            return [(lambda g=g: (g(), wait())) for g in gem]
-        return [ex.pack.bind("kquant_gemv", p.data, p.scales, xin, yout, p.dims[0], p.dims[1], p.ty, stream=stream)
-                for p in planes]
+            name = "pdk_q4k_gemv_shard_lagged" if peer_b is not None else "pdk_q4k_gemv_shard_sync"
+            gem = [[ex.pack.bind(name, p.data, p.scales, xin, b.ptrs_address(), b.flag_ptrs_address(), b.ctr, world, rank,
+                                 first_row, 0, p.dims[0], p.dims[1], stream=stream) for b in bufs] for p in planes]
+            if peer_b is None:
+                wait = ex.pack.bind("pdk_peer_flags_wait", peer_out.flags, world, 0, 2000000, stream=stream)
+                return (lambda i: (gem[i % n_clones][0](), wait())), (lambda: None)
+            # target of the closing waits: this rank's own latest step on that buffer
+            waits = [ex.pack.bind("pdk_peer_flags_wait", b.flags, world, 0x80000000 | rank, 2000000, stream=stream)
+                     for b in bufs]
+            return (lambda i: gem[i % n_clones][i & 1]()), (lambda: [w() for w in waits])
+        ls = [ex.pack.bind("kquant_gemv", p.data, p.scales, xin, yout, p.dims[0], p.dims[1], p.ty, stream=stream)
+              for p in planes]
+        return (lambda i: ls[i % n_clones]()), (lambda: None)
 
-    bound = bind_all(st, x, y)
+    bound, bound_tail = bind_all(st, x, y)
 
     def step(i):
-        bound[i % n_clones]()
+        bound(i)
         if world > 1 and peer_out is None:
             dist.all_gather_into_tensor(y_all, y)
 
@@ -364,11 +382,12 @@ def run_ours(args, rank, world, local_rank):
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             g_st = side.cuda_stream
-            g_bound = bind_all(g_st, x, y)
+            g_bound, g_tail = bind_all(g_st, x, y)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 for i in range(args.steps):
-                    g_bound[i % n_clones]()
+                    g_bound(i)
+                g_tail()
             torch.cuda.synchronize()
             graph.replay()                      # one untimed replay
             torch.cuda.synchronize()
@@ -382,6 +401,7 @@ def run_ours(args, rank, world, local_rank):
     else:
         for i in range(args.steps):
             step(i)
+        bound_tail()
     e1.record()
     barrier()
     total_ms = e0.elapsed_time(e1)
@@ -469,12 +489,17 @@ def run_ours(args, rank, world, local_rank):
         rt = Cudart()
         ev = rt.event()
         x_src, x_bytes = x_host.data_ptr(), x_host.numel() * 4
-        y_dst, y_src, y_bytes = y_host.data_ptr(), y_all.data_ptr(), y_all.numel() * 4
+        y_dst, y_bytes = y_host.data_ptr(), y_all.numel() * 4
+        y_srcs = [b.local.data_ptr() for b in bufs] or [y_all.data_ptr()]
+        e2e_waits = ([ex.pack.bind("pdk_peer_flags_wait", b.flags, world, 0x80000000 | rank, 2000000, stream=st)
+                      for b in bufs] if peer_b is not None else None)
 
         def e2e_step(i):
             rt.copy(x.data_ptr(), x_src, x_bytes, 1, st)
             step(i)
-            rt.copy(y_dst, y_src, y_bytes, 2, st)
+            if e2e_waits is not None:
+                e2e_waits[i & 1]()               # the host reads this step's y: every band must be here
+            rt.copy(y_dst, y_srcs[(i & 1) % len(y_srcs)], y_bytes, 2, st)
             rt.record(ev, st)
             rt.sync_event(ev)
 
@@ -525,14 +550,14 @@ def run_ours(args, rank, world, local_rank):
             gbs, cores, sample, _ = cpu_baseline(3, 1)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
             if args.configs:
-                del planes, bound
+                del planes, bound, bound_tail
                 torch.cuda.empty_cache()
                 line["configs"] = other_configs(ex, quick=args.steps < 50)
     if world > 1 and args.configs:
         # the other sharded shapes (every rank runs them; rank 0 reports): FP8 prefill GEMM with its
         # output channels sharded, and the expert-parallel MXFP4 MoE block
         import kbench
-        del planes, bound
+        del planes, bound, bound_tail
         torch.cuda.empty_cache()
         sharded = {}
         quick = args.steps < 50
@@ -566,7 +591,7 @@ def main():
                     help="time K direct launches instead of one replay of a CUDA graph holding them")
     ap.add_argument("--no-configs", dest="configs", action="store_false",
                     help="N = 1: skip the records of the other benchmark shapes")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer-serial", "nccl"],
                     help="N > 1: how the row bands of y reach every rank")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

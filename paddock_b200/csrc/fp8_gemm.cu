@@ -16,7 +16,13 @@
 // Tokens are the MMA's M dimension because y is token-major.  Tiles are walked
 // token-tile fastest so the CTAs of a wave share a few W tiles through L2.
 // Scales touch only the epilogue: the accumulation is the exact product sum.
+#include <cstdlib>
+
 #include "tc5.cuh"
+
+// fp8_gemm2.cu: the same GEMM on pairs of SMs
+int pdk_f8row_gemm_pair_f32(const void*, const void*, const void*, const void*, void*, uint32_t, uint32_t, uint32_t, cudaStream_t);
+int pdk_f8row_gemm_pair_bf16(const void*, const void*, const void*, const void*, void*, uint32_t, uint32_t, uint32_t, cudaStream_t);
 
 namespace {
 
@@ -224,6 +230,15 @@ f8row_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     }
 }
 
+// PDK_F8_PAIR=0 keeps every call on the one-SM kernel (A/B switch, read once).
+bool pair_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("PDK_F8_PAIR");
+        return !(e && e[0] == '0');
+    }();
+    return v;
+}
+
 template <typename TO>
 int launch(const void* data, const void* w_scale, const void* xq, const void* x_scale, void* y, uint32_t in_dim,
            uint32_t out_dim, uint32_t batch, cudaStream_t st) {
@@ -232,6 +247,13 @@ int launch(const void* data, const void* w_scale, const void* xq, const void* x_
     if (!pdk_aligned(data, 16) || !pdk_aligned(xq, 16) || !pdk_aligned(w_scale, 4) || !pdk_aligned(x_scale, 4) ||
         !pdk_aligned(y, sizeof(TO)))
         return cudaErrorInvalidValue;
+    // prefill widths: 256-token tiles on pairs of SMs (fp8_gemm2.cu), when there are enough of them to
+    // give every pair work
+    if (pair_enabled() && batch > BM &&
+        (uint64_t)((batch + 2u * BM - 1u) / (2u * BM)) * ((out_dim + BN - 1u) / BN) >= (uint64_t)pdk_sm_count() / 2u) {
+        if constexpr (sizeof(TO) == 4) return pdk_f8row_gemm_pair_f32(data, w_scale, xq, x_scale, y, in_dim, out_dim, batch, st);
+        else return pdk_f8row_gemm_pair_bf16(data, w_scale, xq, x_scale, y, in_dim, out_dim, batch, st);
+    }
     CUtensorMap tx, tw;
     if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, in_dim, batch, in_dim, BK, BM)) return rc;
     if (int rc = pdk_make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, data, in_dim, out_dim, in_dim, BK, BN))

@@ -325,11 +325,21 @@ struct PeerOut {
 };
 
 // Called by one thread of each CTA after a CTA-wide barrier that follows the CTA's last store.
-__device__ __forceinline__ void peer_signal(const PeerOut& po) {
+// signal == 1: the last CTA to get here stores the step number into this rank's word of every
+// rank's flag array.  signal == 2: it then also checks that every rank's band of the step before
+// has arrived here (flags >= step - 1) - the condition under which the caller may hand this y to
+// the step after next - waiting at most a second for it; a rank that is late is recorded as
+// 0x1c << 8 | rank in the error word.
+__device__ __forceinline__ void peer_signal(const PeerOut& po, unsigned int* err = nullptr) {
     if (po.n == 0u || po.signal == 0u) return;
-    __threadfence_system();                            // this CTA's stores, seen through the barrier, before the count
+    // Release at GPU scope: this CTA's stores (seen through the barrier) before the count.  Only the
+    // last CTA pays for a system-scope fence - it has observed every other CTA's count, so its
+    // fence covers their stores too (causality order is cumulative) - instead of every CTA waiting
+    // for its own peer stores to be acknowledged over NVLink before it may even count itself out.
+    __threadfence();
     const uint32_t prev = atomicAdd(po.ctr, 1u);
     if (prev == gridDim.x - 1u) {
+        __threadfence();                               // acquire: the other CTAs' stores
         po.ctr[0] = 0u;                                // the next launch on this stream counts from zero
         uint32_t step = po.step;
         if (step == 0u) {
@@ -337,9 +347,29 @@ __device__ __forceinline__ void peer_signal(const PeerOut& po) {
             po.ctr[1] = step;
         }
         __threadfence_system();                        // every CTA's stores before the flags
+        const volatile uint32_t* mine = nullptr;
 #pragma unroll
         for (uint32_t p = 0; p < 8u; ++p)
-            if (p < po.n) *reinterpret_cast<volatile uint32_t*>(po.flag[p] + po.rank) = step;
+            if (p < po.n) {
+                *reinterpret_cast<volatile uint32_t*>(po.flag[p] + po.rank) = step;
+                if (p == po.rank) mine = po.flag[p];
+            }
+        if (po.signal == 2u && step > 1u && mine != nullptr) {
+            unsigned long long t0, t1;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+            for (uint32_t q = 0; q < po.n; ++q) {
+                uint32_t spins = 0;
+                while ((int32_t)(mine[q] - (step - 1u)) < 0) {
+                    if ((++spins & 31u) != 0u) continue;
+                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+                    if (t1 - t0 > 1000000000ull) {
+                        if (err != nullptr) atomicOr(err, (0x1cu << 8) | q);
+                        break;
+                    }
+                }
+            }
+            __threadfence_system();
+        }
     }
 }
 

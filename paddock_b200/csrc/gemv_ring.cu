@@ -404,7 +404,7 @@ gemv_ring_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant
     poll_fold(true);
     if (peers.n != 0u && peers.signal != 0u) {   // uniform over the grid
         __syncthreads();
-        if (tid == 0u) peer_signal(peers);
+        if (tid == 0u) peer_signal(peers, err);
     }
     if (!alive) {
         // a wait ran out somewhere in the CTA: the copies this warp still has in flight must land
@@ -875,7 +875,7 @@ int pdk_q4k_gemv_i8_q8act(const void* data, const void* scales, const int8_t* xq
 
 namespace {
 int shard_launch(const void* data, const void* scales, const void* x, const void* const* y_ptrs, const void* const* flag_ptrs,
-                 void* ctr, uint32_t n_ranks, uint32_t rank, uint32_t row0, uint32_t step, bool signal, uint32_t in_dim,
+                 void* ctr, uint32_t n_ranks, uint32_t rank, uint32_t row0, uint32_t step, uint32_t signal, uint32_t in_dim,
                  uint32_t out_dim, cudaStream_t st) {
     if (out_dim == 0) return 0;
     if (n_ranks == 0 || n_ranks > 8u || y_ptrs == nullptr) return cudaErrorInvalidValue;
@@ -887,7 +887,7 @@ int shard_launch(const void* data, const void* scales, const void* x, const void
     }
     po.n = n_ranks;
     po.row0 = row0;
-    if (signal) {
+    if (signal != 0u) {
         if (flag_ptrs == nullptr || ctr == nullptr || rank >= n_ranks || !pdk_aligned(ctr, 4))
             return cudaErrorInvalidValue;
         for (uint32_t p = 0; p < n_ranks; ++p) {
@@ -897,7 +897,7 @@ int shard_launch(const void* data, const void* scales, const void* x, const void
         po.ctr = (uint32_t*)ctr;
         po.rank = rank;
         po.step = step;
-        po.signal = 1u;
+        po.signal = signal;
     }
     int rc = launch_ring<RQ4K>(data, scales, nullptr, (const float*)x, nullptr, in_dim, out_dim, st, nullptr, nullptr, &po);
     if (rc == -1) rc = pdk_q4k_gemv_peers_regs(data, scales, (const float*)x, &po, in_dim, out_dim, st);
@@ -906,15 +906,15 @@ int shard_launch(const void* data, const void* scales, const void* x, const void
 
 // One warp: lane p waits until flags[p] has reached the step (wrap-around safe), for at most
 // budget_ns; a lane that gives up records kErrFlagWait << 8 | p in the device error word.  The
-// step is `step`, or, when that is 0, one more than the count of waits kept in flags[8], which
-// the kernel then advances.
+// step is `step`; or, when that is 0, one more than the count of waits kept in flags[8], which
+// the kernel then advances; or, when it is 0x80000000 | r, the value of flags[r].
 enum : unsigned int { kErrFlagWait = 0x16 };
 __global__ void peer_flags_wait_kernel(uint32_t* flags, uint32_t n_ranks, uint32_t step, unsigned long long budget_ns,
                                        unsigned int* err) {
     pdk_pdl_launch_dependents();
     pdk_pdl_wait();   // ordered after the kernel before it in the stream (this rank's own band)
     const uint32_t p = threadIdx.x;
-    const uint32_t target = step != 0u ? step : flags[8] + 1u;
+    const uint32_t target = (step & 0x80000000u) ? flags[step & 7u] : step != 0u ? step : flags[8] + 1u;
     __syncwarp();
     if (step == 0u && p == 0u) flags[8] = target;
     if (p >= n_ranks) return;
@@ -940,7 +940,7 @@ __global__ void peer_flags_wait_kernel(uint32_t* flags, uint32_t n_ranks, uint32
 // a barrier across ranks).  n_ranks <= 8.  Returns 801 for shapes outside the GEMV kernels' plans.
 PDK_EXPORT int pdk_q4k_gemv_shard(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
                                   uint32_t n_ranks, uint32_t row0, uint32_t in_dim, uint32_t out_dim, void* stream) {
-    return shard_launch(data, scales, x, y_ptrs, nullptr, nullptr, n_ranks, 0u, row0, 0u, false, in_dim, out_dim,
+    return shard_launch(data, scales, x, y_ptrs, nullptr, nullptr, n_ranks, 0u, row0, 0u, 0u, in_dim, out_dim,
                         (cudaStream_t)stream);
 }
 
@@ -958,13 +958,29 @@ PDK_EXPORT int pdk_q4k_gemv_shard(const void* data, const void* scales, const vo
 PDK_EXPORT int pdk_q4k_gemv_shard_sync(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
                                        const void* const* flag_ptrs, void* ctr, uint32_t n_ranks, uint32_t rank,
                                        uint32_t row0, uint32_t step, uint32_t in_dim, uint32_t out_dim, void* stream) {
-    return shard_launch(data, scales, x, y_ptrs, flag_ptrs, ctr, n_ranks, rank, row0, step, true, in_dim, out_dim,
+    return shard_launch(data, scales, x, y_ptrs, flag_ptrs, ctr, n_ranks, rank, row0, step, 1u, in_dim, out_dim,
+                        (cudaStream_t)stream);
+}
+
+// The same for a loop that keeps two (or more) y buffers in rotation, each with its own flag array
+// and counter words: besides signalling its own step, the kernel's last CTA checks - waiting at
+// most a second, 0x1c << 8 | rank in the error word for a rank that is late - that every rank's
+// band of this buffer's PREVIOUS step has arrived here.  That is the condition for handing the
+// buffer to a later step, so such a loop needs no wait kernel between its steps: one launch per
+// step, consecutive steps overlap like single-GPU launches do, and the arrival of every step is
+// still observed on the device (the last step of each buffer by pdk_peer_flags_wait).
+PDK_EXPORT int pdk_q4k_gemv_shard_lagged(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
+                                         const void* const* flag_ptrs, void* ctr, uint32_t n_ranks, uint32_t rank,
+                                         uint32_t row0, uint32_t step, uint32_t in_dim, uint32_t out_dim, void* stream) {
+    return shard_launch(data, scales, x, y_ptrs, flag_ptrs, ctr, n_ranks, rank, row0, step, 2u, in_dim, out_dim,
                         (cudaStream_t)stream);
 }
 
 // Waits on the device (one small kernel in `stream`) until every one of the n_ranks <= 8 flag
 // words of `flags` (this rank's own 16-word flag array) has reached the step: `step`, or, when
-// that is 0, one more than the array's count of such waits (word 8), which the kernel advances.
+// that is 0, one more than the array's count of such waits (word 8), which the kernel advances;
+// or, when it is 0x80000000 | r, the step rank r (the caller's own rank) signalled last: every
+// rank has then caught up with this rank.
 // The wait is bounded: after budget_us microseconds (1 .. 10,000,000) the kernel records
 // 0x16 << 8 | rank-that-is-late in the device error word (pdk_device_error) and returns; the
 // context stays usable.  What follows in the stream sees every rank's band of that step.

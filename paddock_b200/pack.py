@@ -119,6 +119,7 @@ _EXTRA_SIGS = {
     "pdk_mxfp4_moe_down_combine_static": "ppppppppppuuuuuu",
     "pdk_q4k_gemv_shard": "ppppuuuu",
     "pdk_q4k_gemv_shard_sync": "ppppppuuuuuu",
+    "pdk_q4k_gemv_shard_lagged": "ppppppuuuuuu",
     "pdk_peer_flags_wait": "puuu",
     "pdk_selftest_bounded_wait": "up",
     "pdk_tc5_issue_probe": "uup",
