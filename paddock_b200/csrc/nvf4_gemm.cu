@@ -22,11 +22,28 @@
 //   warps 2..5  epilogue: TMEM -> registers -> y (f32 or bf16), * scale2 + bias
 // Accumulators are double buffered (2 x 128 TMEM columns); scale cells take
 // 32 columns per slab.
+#include <cstdlib>
+
 #include "nvf4_tc5.cuh"
+
+// nvf4_gemm2.cu: prefill widths on pairs of SMs
+int pdk_nvf4_gemm_pair_f32(const void*, const void*, const void*, const void*, const void*, void*, float, uint32_t, uint32_t,
+                           uint32_t, cudaStream_t);
+int pdk_nvf4_gemm_pair_bf16(const void*, const void*, const void*, const void*, const void*, void*, float, uint32_t, uint32_t,
+                            uint32_t, cudaStream_t);
 
 namespace {
 
 using namespace nvf4tc5;
+
+// PDK_NVF4_PAIR=0 keeps every call on the one-SM kernel (A/B switch, read once).
+bool pair_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("PDK_NVF4_PAIR");
+        return !(e && e[0] == '0');
+    }();
+    return v;
+}
 
 template <typename TO>
 __device__ __forceinline__ void store_one(TO* p, float v);
@@ -339,6 +356,12 @@ int launch(const void* data, const void* scale_tiled, const void* bias, const vo
     const size_t need = (size_t)((batch + 127u) / 128u) * (in_dim >> 8) * kSfBytes;
     if (uint8_t* xt = xsf_slice(st, need)) {
         if (int rc = pd_nvf4_tc5_tile_scales(xs, xt, in_dim, batch, st)) return rc;
+        // enough 256-row x 128-token tiles to give every pair of SMs work: the pair kernel
+        if (pair_enabled() &&
+            (uint64_t)((out_dim + 2u * BM - 1u) / (2u * BM)) * ((batch + 127u) / 128u) >= (uint64_t)pdk_sm_count() / 2u) {
+            if constexpr (sizeof(TO) == 4) return pdk_nvf4_gemm_pair_f32(data, scale_tiled, bias, xq, xt, y, scale2, in_dim, out_dim, batch, st);
+            else return pdk_nvf4_gemm_pair_bf16(data, scale_tiled, bias, xq, xt, y, scale2, in_dim, out_dim, batch, st);
+        }
         return launch_bn<128, TO, true>(data, scale_tiled, bias, xq, xt, y, scale2, in_dim, out_dim, batch, st);
     }
     return launch_bn<128, TO, false>(data, scale_tiled, bias, xq, xs, y, scale2, in_dim, out_dim, batch, st);

@@ -262,6 +262,72 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- pairs of CTAs (tcgen05 cta_group::2) -----------------------------------------
+// Two CTAs of a cluster drive one MMA: the leader (cluster rank 0) issues, each CTA's tensor core
+// reads A and its half of B from its own shared memory and the other half of B from its partner's.
+namespace pair {
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;   // a shared::cluster address with the pair's rank bit cleared: the leader's copy
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// one full warp of each CTA of the pair, the same warp index in both
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// 2-D tiled load into this CTA's shared memory whose bytes are counted on the leader's barrier
+__device__ __forceinline__ void tma_load_2d_pair_elect(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int32_t x, int32_t y) {
+    asm volatile(TC5_ELECT
+                 "@e cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4}], [%2];\n\t}" ::"r"(smem_u32(smem_dst)),
+                 "l"(m), "r"(smem_u32(bar) & kPeerMask), "r"(x), "r"(y)
+                 : "memory");
+}
+// four MMAs over the four 32-byte K steps of a stage, both CTAs' tensor cores
+__device__ __forceinline__ void mma_f8f6f4_x4_pair_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                         uint32_t acc_first) {
+    asm volatile(
+        "{\n\t.reg .pred e, p, q;\n\t.reg .b64 a, b;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], a, b, %3, q;\n\t"
+        "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], a, b, %3, q;\n\t"
+        "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], a, b, %3, q;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc_first)
+        : "memory");
+}
+// arrive on the barrier at this offset in BOTH CTAs once the MMAs issued so far are complete
+__device__ __forceinline__ void mma_commit_pair_elect(uint64_t* bar) {
+    asm volatile(TC5_ELECT
+                 ".reg .b16 mask;\n\tmov.b16 mask, 3;\n\t"
+                 "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], mask;\n\t}" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+// arrive on the leader's copy of a barrier (for the leader: its own)
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPeerMask) : "memory");
+}
+
+}  // namespace pair
+
 }  // namespace tc5
 
 // Host: 2-D byte/element tensor map with 128-byte-swizzled boxes.

@@ -50,7 +50,10 @@ def fp8_case(m, n, k, seed):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 256, 512), (256, 512, 5120), (1, 8, 64), (300, 260, 1040),
-                                   (129, 257 * 4, 2048), (1024, 2048, 5120)])
+                                   (129, 257 * 4, 2048), (1024, 2048, 5120),
+                                   # enough 256 x 256 tiles for every pair of SMs: the cta_group::2 kernel,
+                                   # whole tiles and ragged ones (tokens, channels and K)
+                                   (1024, 4864, 256), (1000, 4900, 400), (257, 19000, 128)])
 @pytest.mark.parametrize("out", ["f32", "bf16"])
 def test_f8row_gemm(pack, m, n, k, out):
     if out == "bf16" and (m, n, k) == (1024, 2048, 5120):

@@ -79,7 +79,10 @@ def test_tile_scales_layout(pack):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 256), (8, 128, 512), (64, 384, 5120), (33, 256, 1280), (128, 128, 256), (130, 200, 768),
-                                   (512, 1024, 5120)])
+                                   (512, 1024, 5120),
+                                   # enough 256-row x 128-token tiles for every pair of SMs: the cta_group::2
+                                   # kernel, whole tiles and ragged ones (odd count of 128-row tiles, odd slabs)
+                                   (1024, 2560, 512), (1000, 2440, 768), (200, 9600, 256)])
 @pytest.mark.parametrize("out", ["f32", "bf16"])
 def test_nvf4_gemm_w4a4(pack, m, n, k, out):
     q, s, scale2 = nvf4_weights(n, k, 620 + n + m)
