@@ -239,7 +239,7 @@ def other_configs(ex, quick):
              ("q4k_m4_n25600", kbench.Case("q4k_gemv", m=4, graph=True, iters=it)),
              ("q4k_m16_n25600", kbench.Case("q4k_gemv", m=16, graph=True, iters=it))]
     cases += [(f"fp8_m4096_n{n}", kbench.Case("f8row_gemm", m=4096, n=n, iters=max(5, it // 3))) for n in (5120, 17408, 27648)]
-    cases += [(f"nvf4_m{m}_n17408", kbench.Case("nvf4_gemm", m=m, iters=it if m <= 512 else max(5, it // 3)))
+    cases += [(f"nvf4_m{m}_n17408", kbench.Case("nvf4_gemm", m=m, graph=(m <= 64), iters=it if m <= 512 else max(5, it // 3)))
               for m in (1, 8, 64, 512, 8192)]
     cases += [(f"moe_mxfp4_t{t}", kbench.Case("moe_mxfp4", m=t, graph=(t == 1), iters=it if t <= 64 else max(5, it // 3)))
               for t in (1, 64, 1024)]
@@ -476,6 +476,54 @@ def run_ours(args, rank, world, local_rank):
             rt.sync_event(ev_out[j])
         e2e_ms = (time.perf_counter() - w0) * 1e3   # three streams: host clock around the fully drained loop
         torch.cuda.synchronize()
+        host_paced_ms = e2e_ms
+        # The same pipeline captured once and replayed, the way a serving loop replays its captured
+        # step: per step an H2D copy node (pinned host activations), the kernel node and a D2H copy node
+        # (the result into pinned host memory) on three captured streams with the same buffer
+        # dependencies; the host launches the graph and waits for the last result.  Every step still
+        # moves its input and its output over PCIe; what is gone is the host's per-call cost (12 runtime
+        # calls a step from Python, about 30 us, more than the kernel takes).
+        try:
+            cap = torch.cuda.CUDAGraph()
+            evi, evk, evo = ([rt.event() for _ in range(D)] for _ in range(3))
+            fork, j_in, j_out = rt.event(), rt.event(), rt.event()
+            with torch.cuda.graph(cap, stream=s_k):
+                rt.record(fork, q_k)
+                rt.wait(q_in, fork)
+                rt.wait(q_out, fork)
+                for i in range(args.steps):
+                    b = i % D
+                    if i >= D:
+                        rt.wait(q_in, evk[b])        # the kernel of step i-D has consumed this input buffer
+                    rt.copy(xd[b], x_src, x_bytes, 1, q_in)
+                    rt.record(evi[b], q_in)
+                    rt.wait(q_k, evi[b])
+                    if i >= D:
+                        rt.wait(q_k, evo[b])         # step i-D's result has left this output buffer
+                    launch[i % n_clones][b]()
+                    rt.record(evk[b], q_k)
+                    rt.wait(q_out, evk[b])
+                    rt.copy(yhp[b], yd[b], y_bytes, 2, q_out)
+                    rt.record(evo[b], q_out)
+                rt.record(j_in, q_in)
+                rt.record(j_out, q_out)
+                rt.wait(q_k, j_in)
+                rt.wait(q_k, j_out)
+            for t in yh:
+                t.zero_()
+            cap.replay()
+            torch.cuda.synchronize()
+            w0 = time.perf_counter()
+            cap.replay()
+            torch.cuda.synchronize()                 # the graph runs on the current stream: wait for the device
+            graph_ms = (time.perf_counter() - w0) * 1e3
+            if graph_ms < e2e_ms:
+                e2e_ms = graph_ms
+                e2e_mode = ("the K steps captured into one CUDA graph and replayed: per step an H2D copy node, the kernel "
+                            "node and a D2H copy node on three captured streams, 3 steps in flight; the host launches "
+                            "the graph and waits for the last result")
+        except Exception as err:
+            print(f"bench: end-to-end graph capture failed ({err}); keeping the host-paced loop", file=sys.stderr)
         # the pipelined loop must produce the same y as a plain call
         ex.kquant_gemv(planes[(args.steps - 1) % n_clones], x, y)
         torch.cuda.synchronize()
@@ -536,7 +584,8 @@ def run_ours(args, rank, world, local_rank):
             "data": "synthetic", "config": workload_config(world, args.exchange),
             "e2e": {"value": bytes_step / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": K_DIM * 4, "d2h_bytes_per_step": N_DIM * 4,
-                    "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode},
+                    "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode,
+                    **({"host_paced_ms_per_step": host_paced_ms / args.steps} if world == 1 else {})},
             "gpu_launches": args.steps,
             "launch": "one replay of a CUDA graph holding the K launches" if graph is not None else "K direct launches",
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

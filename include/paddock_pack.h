@@ -314,7 +314,8 @@ void pdk_stream_release(void* stream);
  * packs/cuda/src/gemm/dense_nvf4_tc5.cuh:306-309).  Issue-rate probe of the tensor core: one CTA per
  * SM issues n_mma (8 .. 2^20, a multiple of 4) tcgen05.mma on operands that stay in shared memory - kind 0 bf16
  * M128 N256 K16, 1 e4m3 M128 N256 K32, 2 NVFP4 block-scaled M128 N128 K64, 3 as 2 with the two
- * scale-cell copies a GEMM issues per MMA.  cycles: device u64[SM count] or NULL, SM clocks from
+ * scale-cell copies a GEMM issues per MMA; 4 and 5: kinds 1 and 3 on pairs of SMs (cta_group::2,
+ * M256 per pair, one issuing CTA per pair, flops = pairs * n_mma * 2 * 256 * N * K).  cycles: device u64[SM count] or NULL, SM clocks from
  * first issue to completion per CTA.  Flops of a launch = SMs * n_mma * 2 * 128 * N * K. */
 int pdk_tc5_issue_probe(uint32_t kind, uint32_t n_mma, void* cycles, void* stream);
 

@@ -179,7 +179,8 @@ def bench_tc5_probe(ex, a):
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     cyc = torch.zeros(sms, dtype=torch.int64, device="cuda")
     kinds = [("bf16_m128n256k16", 256, 16), ("e4m3_m128n256k32", 256, 32), ("nvf4_m128n128k64", 128, 64),
-             ("nvf4_m128n128k64_with_scale_copies", 128, 64)]
+             ("nvf4_m128n128k64_with_scale_copies", 128, 64), ("e4m3_pair_m256n256k32", 256, 32),
+             ("nvf4_pair_m256n128k64_with_scale_copies", 128, 64)]
     out = {}
     st = torch.cuda.current_stream().cuda_stream
     for kind, (name, n, k) in enumerate(kinds):
@@ -192,7 +193,7 @@ def bench_tc5_probe(ex, a):
         e1.record()
         torch.cuda.synchronize()
         sec = e0.elapsed_time(e1) * 1e-3
-        flops = sms * n_mma * 2 * 128 * n * k
+        flops = sms * n_mma * 2 * 128 * n * k          # a pair's MMA is M256 on two SMs: the same flops per SM
         per = cyc.float().median().item() / n_mma
         out[name] = {"tflops": flops / sec / 1e12, "ms": sec * 1e3, "sm_cycles_per_mma": per,
                      "tflops_at_cycle_rate_1965mhz": sms * 2 * 128 * n * k / per * 1.965e9 / 1e12}
@@ -271,11 +272,11 @@ def bench_nvf4(ex, a):
     if a.out == "bf16":
         y = torch.zeros(m * n, dtype=torch.bfloat16, device="cuda")
         call = lambda i: ex.pack.call("pdk_nvf4_gemm_bf16", ws[i % nc][0], ws[i % nc][1], None, xq, xs, y, 1.0, k, n, m,
-                                      stream=st)
+                                      stream=torch.cuda.current_stream().cuda_stream)
     else:
         y = torch.zeros(m * n, dtype=torch.float32, device="cuda")   # the table slot writes f32
         call = lambda i: ex.pack.call("nvf4_gemm_tc5w", ws[i % nc][0], ws[i % nc][1], None, xq, xs, y, 1.0, k, n, m, None,
-                                      0, stream=st)
+                                      0, stream=torch.cuda.current_stream().cuda_stream)
     sec = time_launches(call, a.iters)
     # spot check: clone 0's first rows against an f32 product of the dequantized operands
     call(0)
@@ -656,7 +657,7 @@ class Case:
 def run_case(ex, a):
     """Time one case; returns the JSON-able record the command line prints."""
     global GRAPH_REPLAY
-    GRAPH_REPLAY = a.graph and a.op in ("q4k_gemv", "q8_gemv", "nvf4_gemv", "norm_nvf4")
+    GRAPH_REPLAY = a.graph and a.op in ("q4k_gemv", "q8_gemv", "nvf4_gemv", "norm_nvf4", "nvf4_gemm")
     sec, info = OPS[a.op](ex, a)
     err = ex.pack.device_error() if not a.pack else 0
     hbm, bf16, kind = peaks()
@@ -681,7 +682,7 @@ def main():
     ap.add_argument("--out", default="bf16", choices=["bf16", "f32"])
     ap.add_argument("--moe-path", default="tc5", choices=["tc5", "mma"],
                     help="expert GEMMs: block-scaled tcgen05 (default) or the mma.sync kernels")
-    ap.add_argument("--graph", action="store_true", help="replay the timed launches from a CUDA graph (moe_mxfp4, moe_ep, q4k_gemv, q8_gemv, nvf4_gemv)")
+    ap.add_argument("--graph", action="store_true", help="replay the timed launches from a CUDA graph (moe_mxfp4, moe_ep, q4k_gemv, q8_gemv, nvf4_gemv, nvf4_gemm)")
     ap.add_argument("--dtype", default="q4_k", choices=["q4_k", "q5_k", "q6_k", "q4_0"], help="q4k_gemv: the plane's format")
     ap.add_argument("--pack", default=None, help="path of a kernel-pack library to time instead of this package's")
     args = ap.parse_args()
