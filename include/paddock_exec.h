@@ -130,6 +130,14 @@ int pdx_quantw_gemm(PdxExecutor* ex, const PdxPlane* w, const void* bias, const 
  * in_dim % 128 == 0 and the pack has it, else slot f8row_gemm) */
 int pdx_quantize_e4m3_row(PdxExecutor* ex, const void* x, void* q, void* rscale, uint32_t n_dim, uint32_t batch);
 int pdx_f8row_gemm(PdxExecutor* ex, const PdxPlane* w, const void* xq, const void* xrs, void* y, uint32_t batch);
+/* the fused producers in front of f8row_gemm (gpu/fp8.rs:469-590): *fused = 1 when the pack ran the
+ * fused kernel, 0 when the slot is absent or declined (the engine's Ok(false)): run the unfused chain */
+int pdx_swiglu_quant_e4m3_row(PdxExecutor* ex, const void* gate, const void* up, void* q, void* rs, uint32_t n_ff,
+                              uint32_t batch, int* fused);
+int pdx_rmsnorm_quant_e4m3_row(PdxExecutor* ex, const void* x, const void* w, void* xn, void* q, void* rs, uint32_t n,
+                               float eps, uint32_t batch, int* fused);
+int pdx_add_rmsnorm_scaled_quant_e4m3_row(PdxExecutor* ex, void* x, const void* proj, const void* w, void* xn, void* q,
+                                          void* rs, uint32_t n, float eps, float pscale, uint32_t batch, int* fused);
 /* quantize_nvf4 (gpu/fp4.rs:181-205), nvf4_gemm_f4 (fp4.rs:1902-1975: Row layout only; the tcgen05
  * slot when the plane carries tiled scales) and the W4A16 decode GEMV (slot nvf4_gemv) */
 int pdx_quantize_nvf4(PdxExecutor* ex, const void* x, void* q, void* scale, uint32_t n);

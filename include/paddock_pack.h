@@ -93,7 +93,10 @@ enum PdkSlot {
     PDK_SLOT_mxfp4_moe_down_mmq = 89,
     PDK_SLOT_mxfp4_moe_gate_up_dp4a_b = 92,
     PDK_SLOT_mxfp4_moe_down_dp4a_b = 93,
-    PDK_SLOT_mxfp4_gu_interleave = 155
+    PDK_SLOT_mxfp4_gu_interleave = 155,
+    PDK_SLOT_swiglu_quant_e4m3_row = 511,
+    PDK_SLOT_rmsnorm_quant_e4m3_row = 512,
+    PDK_SLOT_add_rmsnorm_scaled_quant_e4m3_row = 513
 };
 
 /* ---- the drop-in boundary ------------------------------------------------ */
@@ -181,6 +184,20 @@ int pd_f8row_gemm(const void* data, const void* w_rowscale, const void* xq, cons
 /* slot 855, packs/cuda/src/gemm/dense_nvf4_tc5.cuh:1480-1515: same contract as slot 184. */
 int pd_f8row_gemm_tc5x(const void* data, const void* w_rowscale, const void* xq, const void* x_rowscale, void* y,
                        uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* stream);
+/* slots 511, 512, 513 (packs/cuda/src/exports.cuh:380-500, gemm/dense_f8_decode.cuh:4357-4575; callers
+ * gpu/fp8.rs:469-590): the fused producers in front of the e4m3 GEMM.  All end in slot 183's row
+ * quantizer (q e4m3 [batch][n] + one power-of-two f32 scale per row); n % 32 == 0, 16-byte
+ * aligned rows.
+ *   swiglu_quant:  h = silu(gate) * up in f32
+ *   rmsnorm_quant: xn f32 [batch][n] = x * (1 / sqrtf(mean(x^2) + eps)) * w, quantized
+ *   add_rmsnorm_scaled_quant: x += pscale * proj first (written back), then as rmsnorm_quant
+ * Status 100 = declined (rows beyond 65536 elements): the engine then runs the unfused chain. */
+int pd_swiglu_quant_e4m3_row(const void* gate, const void* up, void* q, void* rscale, uint32_t n, uint32_t batch,
+                             void* stream);
+int pd_rmsnorm_quant_e4m3_row(const void* x, const void* w, void* xn, void* q, void* rscale, uint32_t n, float eps,
+                              uint32_t batch, void* stream);
+int pd_add_rmsnorm_scaled_quant_e4m3_row(void* x, const void* proj, const void* w, void* xn, void* q, void* rscale,
+                                         uint32_t n, float eps, float pscale, uint32_t batch, void* stream);
 /* No slot: slot 184 with bf16 output (the reference writes f32). */
 int pdk_f8row_gemm_bf16(const void* data, const void* w_rowscale, const void* xq, const void* x_rowscale, void* y,
                         uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* stream);

@@ -204,6 +204,32 @@ def add_rmsnorm(x, proj, w, eps):
     return v, out
 
 
+def rmsnorm_scaled_add(x, proj, w, eps, pscale=1.0):
+    """The arithmetic in front of the e4m3 row quantizer (packs/cuda/src/gemm/dense_f8_decode.cuh:4357-4530):
+    v = fmaf(pscale, proj, x) in f32 (proj None: v = x); f32 squares, mean in f64 here (the reference sums
+    in double-float or f32, which agrees to an ulp of the sum); inv = 1 / sqrtf(mean + eps); xn = (v * inv) * w.
+    Returns (v, xn)."""
+    x = np.asarray(x, np.float32)
+    if proj is None:
+        v = x
+    else:   # one rounding: the product of two f32 is exact in f64
+        v = (x.astype(np.float64) + np.float64(np.float32(pscale)) * np.asarray(proj, np.float32).astype(np.float64)).astype(np.float32)
+    n = v.shape[-1]
+    total = (v * v).astype(np.float32).astype(np.float64).sum(axis=-1)
+    mean = (total / float(n)).astype(np.float32) + np.float32(eps)
+    inv = (np.float32(1.0) / np.sqrt(mean.astype(np.float32))).astype(np.float32)
+    xn = ((v * inv[..., None]).astype(np.float32) * np.asarray(w, np.float32)).astype(np.float32)
+    return v, xn
+
+
+def swiglu_silu(gate, up):
+    """h = (g / (1 + expf(-g))) * u in f32 (packs/cuda/src/exports.cuh:404-412); numpy's f32 exp may differ
+    from the device's by an ulp."""
+    g = np.asarray(gate, np.float32)
+    one = np.float32(1.0)
+    return ((g / (one + np.exp(-g).astype(np.float32))).astype(np.float32) * np.asarray(up, np.float32)).astype(np.float32)
+
+
 def quantize_mxfp4(w):
     w = _f32(w)
     out = np.empty(w.size // 32 * 17, np.uint8)

@@ -34,6 +34,8 @@ PDK_EXPORT unsigned int pdk_device_error(void) {
     return v;
 }
 
+int pdk_quantize_e4m3_row_1p(const float* x, uint8_t* q, float* rscale, uint32_t n, uint32_t batch, cudaStream_t st);
+
 namespace {
 
 __device__ __forceinline__ uint8_t to_e4m3(float v) {
@@ -81,6 +83,9 @@ PDK_EXPORT int pd_quantize_e4m3_row(const void* x, void* q, void* rscale, uint32
                                     void* stream) {
     if (n_dim == 0 || batch == 0) return 0;
     if (!pdk_aligned(x, 4) || !pdk_aligned(rscale, 4)) return cudaErrorInvalidValue;
+    // rows of whole, aligned float4: one pass with the row in registers (f8_producers.cu)
+    const int rc = pdk_quantize_e4m3_row_1p((const float*)x, (uint8_t*)q, (float*)rscale, n_dim, batch, (cudaStream_t)stream);
+    if (rc != -1) return rc;
     quantize_row_kernel<float><<<batch, 256, 0, (cudaStream_t)stream>>>((const float*)x, (uint8_t*)q, (float*)rscale,
                                                                         n_dim);
     return pdk_launch_status();

@@ -201,6 +201,26 @@ class GpuExecutor:
         self._check(_lib().pdx_quantize_e4m3_row(self._h, _ptr(x), _ptr(q), _ptr(rscale), C.c_uint32(n_dim),
                                                  C.c_uint32(batch)))
 
+    def swiglu_quant_e4m3_row(self, gate, up, q, rs, n_ff, batch):
+        """-> True when the pack ran the fused kernel (gpu/fp8.rs:469-497)."""
+        fused = C.c_int()
+        self._check(_lib().pdx_swiglu_quant_e4m3_row(self._h, _ptr(gate), _ptr(up), _ptr(q), _ptr(rs), C.c_uint32(n_ff),
+                                                     C.c_uint32(batch), C.byref(fused)))
+        return bool(fused.value)
+
+    def rmsnorm_quant_e4m3_row(self, x, w, xn, q, rs, n, eps, batch):
+        fused = C.c_int()
+        self._check(_lib().pdx_rmsnorm_quant_e4m3_row(self._h, _ptr(x), _ptr(w), _ptr(xn), _ptr(q), _ptr(rs), C.c_uint32(n),
+                                                      C.c_float(eps), C.c_uint32(batch), C.byref(fused)))
+        return bool(fused.value)
+
+    def add_rmsnorm_scaled_quant_e4m3_row(self, x, proj, w, xn, q, rs, n, eps, pscale, batch):
+        fused = C.c_int()
+        self._check(_lib().pdx_add_rmsnorm_scaled_quant_e4m3_row(self._h, _ptr(x), _ptr(proj), _ptr(w), _ptr(xn), _ptr(q),
+                                                                 _ptr(rs), C.c_uint32(n), C.c_float(eps), C.c_float(pscale),
+                                                                 C.c_uint32(batch), C.byref(fused)))
+        return bool(fused.value)
+
     def f8row_gemm(self, w, xq, xrs, y, batch):
         self._check(_lib().pdx_f8row_gemm(self._h, w._h, _ptr(xq), _ptr(xrs), _ptr(y), C.c_uint32(batch)))
 

@@ -225,13 +225,14 @@ const char* const kSlotNames[] = {
     "mxfp4_dequant_f32", "q8_0_dequant_f32", "add_inplace_f32", "mxfp4_repack", "q8_0_repack", "q8_0_gemv_repacked",
     "q8_0_gemm_repacked", "kquant_dequant", "kquant_repack", "kquant_gemv", "quantize_e4m3_row", "f8row_gemm",
     "bf16_to_f8row", "f8row_gemm_tc5x", "quantize_nvf4", "nvf4_dequant", "nvf4_gemv", "nvf4_gemm_tc5w",
-    "nvf4_tc5_tile_scales"};
+    "nvf4_tc5_tile_scales", "swiglu_quant_e4m3_row", "rmsnorm_quant_e4m3_row", "add_rmsnorm_scaled_quant_e4m3_row"};
 const int kSlotIndex[] = {
     PDK_SLOT_mxfp4_dequant_f32, PDK_SLOT_q8_0_dequant_f32, PDK_SLOT_add_inplace_f32, PDK_SLOT_mxfp4_repack,
     PDK_SLOT_q8_0_repack, PDK_SLOT_q8_0_gemv_repacked, PDK_SLOT_q8_0_gemm_repacked, PDK_SLOT_kquant_dequant,
     PDK_SLOT_kquant_repack, PDK_SLOT_kquant_gemv, PDK_SLOT_quantize_e4m3_row, PDK_SLOT_f8row_gemm,
     PDK_SLOT_bf16_to_f8row, PDK_SLOT_f8row_gemm_tc5x, PDK_SLOT_quantize_nvf4, PDK_SLOT_nvf4_dequant,
-    PDK_SLOT_nvf4_gemv, PDK_SLOT_nvf4_gemm_tc5w, PDK_SLOT_nvf4_tc5_tile_scales};
+    PDK_SLOT_nvf4_gemv, PDK_SLOT_nvf4_gemm_tc5w, PDK_SLOT_nvf4_tc5_tile_scales, PDK_SLOT_swiglu_quant_e4m3_row,
+    PDK_SLOT_rmsnorm_quant_e4m3_row, PDK_SLOT_add_rmsnorm_scaled_quant_e4m3_row};
 
 void set_msg(char* err, size_t n, const char* fmt, ...) {
     if (!err || n == 0) return;
@@ -711,6 +712,44 @@ PDX_EXPORT int pdx_quantize_e4m3_row(PdxExecutor* ex, const void* x, void* q, vo
     auto f = ex->op<decltype(&pd_quantize_e4m3_row)>(PDK_SLOT_quantize_e4m3_row);
     if (!f) return ex->fail(PDX_MISSING_OP, "quantize_e4m3_row");
     return ex->launched(f(x, q, rscale, n_dim, batch, ex->stream), "quantize_e4m3_row");
+}
+
+// The fused producers in front of f8row_gemm (gpu/fp8.rs:469-590).  *fused receives 1 when the pack
+// ran the fused kernel and 0 when the slot is absent or declined (status 100): the caller then runs
+// the unfused chain, as the engine does on Ok(false).
+PDX_EXPORT int pdx_swiglu_quant_e4m3_row(PdxExecutor* ex, const void* gate, const void* up, void* q, void* rs, uint32_t n_ff,
+                                         uint32_t batch, int* fused) {
+    if (fused) *fused = 0;
+    auto f = ex->op<decltype(&pd_swiglu_quant_e4m3_row)>(PDK_SLOT_swiglu_quant_e4m3_row);
+    if (!f) return PDX_OK;
+    if (int rc = ex->launched(f(gate, up, q, rs, n_ff, batch, ex->stream), "swiglu_quant_e4m3_row")) return rc;
+    if (fused) *fused = 1;
+    return PDX_OK;
+}
+
+PDX_EXPORT int pdx_rmsnorm_quant_e4m3_row(PdxExecutor* ex, const void* x, const void* w, void* xn, void* q, void* rs,
+                                          uint32_t n, float eps, uint32_t batch, int* fused) {
+    if (fused) *fused = 0;
+    auto f = ex->op<decltype(&pd_rmsnorm_quant_e4m3_row)>(PDK_SLOT_rmsnorm_quant_e4m3_row);
+    if (!f) return PDX_OK;
+    const int rc = f(x, w, xn, q, rs, n, eps, batch, ex->stream);
+    if (rc == 100) return PDX_OK;
+    if (int e = ex->launched(rc, "rmsnorm_quant_e4m3_row")) return e;
+    if (fused) *fused = 1;
+    return PDX_OK;
+}
+
+PDX_EXPORT int pdx_add_rmsnorm_scaled_quant_e4m3_row(PdxExecutor* ex, void* x, const void* proj, const void* w, void* xn,
+                                                     void* q, void* rs, uint32_t n, float eps, float pscale, uint32_t batch,
+                                                     int* fused) {
+    if (fused) *fused = 0;
+    auto f = ex->op<decltype(&pd_add_rmsnorm_scaled_quant_e4m3_row)>(PDK_SLOT_add_rmsnorm_scaled_quant_e4m3_row);
+    if (!f) return PDX_OK;
+    const int rc = f(x, proj, w, xn, q, rs, n, eps, pscale, batch, ex->stream);
+    if (rc == 100) return PDX_OK;
+    if (int e = ex->launched(rc, "add_rmsnorm_scaled_quant_e4m3_row")) return e;
+    if (fused) *fused = 1;
+    return PDX_OK;
 }
 
 PDX_EXPORT int pdx_f8row_gemm(PdxExecutor* ex, const PdxPlane* w, const void* xq, const void* xrs, void* y, uint32_t batch) {

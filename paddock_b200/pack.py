@@ -99,6 +99,8 @@ _SIGS = {
     "q8_0_gemv_repacked": "pppppuu", "q8_0_gemm_repacked": "pppppuuu",
     "quantize_e4m3_row": "pppuu", "bf16_to_f8row": "pppuu",
     "f8row_gemm": "pppppuuu", "f8row_gemm_tc5x": "pppppuuu",
+    "swiglu_quant_e4m3_row": "ppppuu", "rmsnorm_quant_e4m3_row": "pppppufu",
+    "add_rmsnorm_scaled_quant_e4m3_row": "ppppppuffu",
     "quantize_nvf4": "pppu", "add_rmsnorm_quant_nvf4_batch": "ppppppufu", "nvf4_dequant": "ppfpuu", "nvf4_gemv": "pppppfuu",
     "nvf4_tc5_tile_scales": "ppuu", "nvf4_gemm_tc5w": "ppppppfuuupU",
     "moe_topk_batch": "ppuuppu", "moe_align": "ppppuuuu", "moe_align_bm": "ppppuuuuu", "moe_slot_combine": "ppuuu",

@@ -171,6 +171,30 @@ def test_f8row_plane_from_bf16_and_from_a_checkpoint_view(ex):
     assert torch.equal(d_y, d_y2)
 
 
+def test_fused_e4m3_producers_feed_the_gemm(ex):
+    """rmsnorm + quantize in one launch, then the FP8 GEMM on what it wrote: the chain the engine
+    runs in front of every FP8 linear layer (gpu/fp8.rs:504-659)."""
+    m, n, k, eps = 12, 128, 512, 1e-6
+    x = oracle.fill_normal(m * k, 9600, 1.5).reshape(m, k)
+    g = (1.0 + 0.1 * oracle.fill_normal(k, 9601, 1.0)).astype(np.float32)
+    w = oracle.bf16_round(oracle.fill_normal(n * k, 9602, 0.02))
+    plane = ex.bf16_to_f8row((w.view(np.uint32) >> 16).astype(np.uint16), k, n)
+    d_x, d_xn = dev_f32(x.reshape(-1)), torch.zeros(m * k, dtype=torch.float32, device="cuda")
+    d_q, d_s = torch.zeros(m * k, dtype=torch.uint8, device="cuda"), torch.zeros(m, dtype=torch.float32, device="cuda")
+    d_y = torch.zeros(m * n, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    assert ex.rmsnorm_quant_e4m3_row(d_x, dev_f32(g), d_xn, d_q, d_s, k, eps, m) is True
+    ex.f8row_gemm(plane, d_q, d_s, d_y, m)
+    ex.synchronize()
+    _, xn = oracle.rmsnorm_scaled_add(x, None, g, eps)
+    assert np.allclose(d_xn.cpu().numpy().reshape(m, k), xn, rtol=4e-7, atol=0)
+    wq, wsc = oracle.quantize_e4m3_row_pow2(w, n, k)
+    xq, xsc = oracle.quantize_e4m3_row_pow2(d_xn.cpu().numpy(), m, k)
+    ref, ab = oracle.matmul_f64(oracle.dequant_fp8_channel(wq, wsc, k, n), oracle.dequant_fp8_channel(xq, xsc, k, m), k, n, m,
+                                with_abs=True)
+    assert cond_err(d_y.cpu().numpy().reshape(m, n), ref, ab) < 1e-5 < TOL
+
+
 def test_nvf4_upload_checks_geometry_tiles_scales_and_runs_both_lanes(ex):
     m, n, k = 24, 200, 768
     w = oracle.fill_normal(n * k, 9500, 0.02)

@@ -38,6 +38,80 @@ def test_bf16_to_f8row_bit_exact(pack):
     assert np.array_equal(d_q.cpu().numpy().reshape(rows, k), q_ref)
 
 
+def codes_agree(got, want, budget=2e-3):
+    """e4m3 codes equal, or one step apart where the input sat within an ulp of a rounding tie."""
+    got, want = np.asarray(got, np.int16), np.asarray(want, np.int16)
+    off = got != want
+    assert np.mean(off) < budget
+    assert (np.abs(got[off] - want[off]) <= 1).all()
+
+
+@pytest.mark.parametrize("rows,n", [(1, 64), (3, 5120), (70, 17408), (2, 40000)])
+def test_quantize_e4m3_row_single_pass_route(pack, rows, n):
+    """Rows of whole, aligned float4 take the register-resident kernel: same bytes as the oracle."""
+    x = oracle.fill_normal(rows * n, 430 + n, 3.0)
+    x[:n] *= 1e-3
+    q_ref, s_ref = oracle.quantize_e4m3_row_pow2(x, rows, n)
+    d_q = torch.zeros(rows * n, dtype=torch.uint8, device="cuda")
+    d_s = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    pack.call("quantize_e4m3_row", dev_f32(x), d_q, d_s, n, rows)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_s.cpu().numpy(), s_ref)
+    assert np.array_equal(d_q.cpu().numpy().reshape(rows, n), q_ref)
+
+
+@pytest.mark.parametrize("rows,n", [(1, 64), (5, 5120), (80, 17408)])
+def test_swiglu_quant_e4m3_row(pack, rows, n):
+    """Slot 511: silu(gate) * up, then the row quantizer."""
+    g = oracle.fill_normal(rows * n, 440 + n, 2.0).reshape(rows, n)
+    u = oracle.fill_normal(rows * n, 441 + n, 1.0).reshape(rows, n)
+    g[0, :32] = 0.0
+    h = oracle.swiglu_silu(g, u)
+    q_ref, s_ref = oracle.quantize_e4m3_row_pow2(h.reshape(-1), rows, n)
+    d_q = torch.zeros(rows * n, dtype=torch.uint8, device="cuda")
+    d_s = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    pack.call("swiglu_quant_e4m3_row", dev_f32(g.reshape(-1)), dev_f32(u.reshape(-1)), d_q, d_s, n, rows)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_s.cpu().numpy(), s_ref)
+    codes_agree(d_q.cpu().numpy().reshape(rows, n), q_ref)
+
+
+@pytest.mark.parametrize("rows,n,residual", [(1, 64, False), (4, 5120, True), (70, 5120, True), (3, 17408, False), (2, 32768, True)])
+def test_rmsnorm_quant_e4m3_row(pack, rows, n, residual):
+    """Slots 512 / 513: the summed row is written back bit-exactly, the normed row agrees with the
+    oracle to an ulp of the norm scale, and the codes are exactly the row quantizer's on the normed
+    row the kernel wrote."""
+    x = oracle.fill_normal(rows * n, 450 + n, 1.5).reshape(rows, n)
+    proj = oracle.fill_normal(rows * n, 451 + n, 0.5).reshape(rows, n) if residual else None
+    w = (1.0 + 0.1 * oracle.fill_normal(n, 452, 1.0)).astype(np.float32)
+    eps, pscale = 1e-6, 0.75
+    v_ref, xn_ref = oracle.rmsnorm_scaled_add(x, proj, w, eps, pscale)
+    d_x = dev_f32(x.reshape(-1))
+    d_xn = torch.zeros(rows * n, dtype=torch.float32, device="cuda")
+    d_q = torch.zeros(rows * n, dtype=torch.uint8, device="cuda")
+    d_s = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    if residual:
+        pack.call("add_rmsnorm_scaled_quant_e4m3_row", d_x, dev_f32(proj.reshape(-1)), dev_f32(w), d_xn, d_q, d_s, n, eps,
+                  pscale, rows)
+    else:
+        pack.call("rmsnorm_quant_e4m3_row", d_x, dev_f32(w), d_xn, d_q, d_s, n, eps, rows)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_x.cpu().numpy().reshape(rows, n).view(np.uint32), v_ref.view(np.uint32))
+    xn = d_xn.cpu().numpy().reshape(rows, n)
+    assert np.allclose(xn, xn_ref, rtol=4e-7, atol=0)
+    q_own, s_own = oracle.quantize_e4m3_row_pow2(xn.reshape(-1), rows, n)
+    assert np.array_equal(d_s.cpu().numpy(), s_own)
+    assert np.array_equal(d_q.cpu().numpy().reshape(rows, n), q_own)
+
+
+def test_e4m3_producers_refuse_bad_shapes(pack):
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    assert pack.status("swiglu_quant_e4m3_row", buf, buf, buf, buf, 100, 2) == 1                 # n % 32
+    assert pack.status("rmsnorm_quant_e4m3_row", buf.data_ptr() + 4, buf, buf, buf, buf, 64, 1e-6, 1) == 1
+    assert pack.status("add_rmsnorm_scaled_quant_e4m3_row", buf, None, buf, buf, buf, buf, 64, 1e-6, 1.0, 1) == 1
+    assert pack.status("rmsnorm_quant_e4m3_row", buf, buf, buf, buf, buf, 64, 1e-6, 0) == 0
+
+
 def fp8_case(m, n, k, seed):
     w = oracle.fill_normal(n * k, seed, 0.02)
     x = oracle.bf16_round(oracle.fill_normal(m * k, seed + 1, 1.0))

@@ -324,6 +324,39 @@ def test_add_rmsnorm_quant_nvf4_against_reference_pack(pack, ref):
     assert np.mean(ours[3] != theirs[3]) < 1e-3
 
 
+def test_e4m3_producers_against_reference_pack(pack, ref):
+    """Slots 511 / 512 / 513 on both packs: SwiGLU + quantizer byte-identical; the norm forms write the
+    same summed rows, normed rows that agree to an ulp of the norm scale, the same row scales and
+    codes that differ, if at all, only where that ulp crosses a rounding tie."""
+    n, batch, eps = 5120, 6, 1e-6
+    g = oracle.fill_normal(batch * n, 5300, 2.0)
+    u = oracle.fill_normal(batch * n, 5301, 1.0)
+
+    def mk_sw():
+        q = torch.zeros(batch * n, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(batch, dtype=torch.float32, device="cuda")
+        return (dev_f32(g), dev_f32(u), q, s, n, batch), [q, s]
+    assert_bytes_equal(run_both(pack, ref, "swiglu_quant_e4m3_row", mk_sw, 2))
+    w = (1.0 + 0.1 * oracle.fill_normal(n, 5302, 1.0)).astype(np.float32)
+
+    def mk_norm(residual):
+        def mk():
+            dx = dev_f32(g)
+            xn = torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+            q = torch.zeros(batch * n, dtype=torch.uint8, device="cuda")
+            s = torch.zeros(batch, dtype=torch.float32, device="cuda")
+            if residual:
+                return (dx, dev_f32(u), dev_f32(w), xn, q, s, n, eps, 0.5, batch), [dx, xn, s, q]
+            return (dx, dev_f32(w), xn, q, s, n, eps, batch), [dx, xn, s, q]
+        return mk
+    for name, residual in (("rmsnorm_quant_e4m3_row", False), ("add_rmsnorm_scaled_quant_e4m3_row", True)):
+        ours, theirs = run_both(pack, ref, name, mk_norm(residual), 4)
+        assert np.array_equal(ours[0], theirs[0])
+        assert np.allclose(ours[1].view(np.float32), theirs[1].view(np.float32), rtol=4e-7, atol=0)
+        assert np.array_equal(ours[2], theirs[2])
+        assert np.mean(ours[3] != theirs[3]) < 1e-3
+
+
 def _moe_slot_chain(p, raw, x, idx, w, tokens, n_expert, k, embd, ff, decode):
     """The engine's MoE chain through pack `p`'s own slots (its own fused gate|up plane);
     decode: the unsorted pair 92 / 93, else align -> 88 -> 89 -> combine."""
