@@ -96,7 +96,10 @@ enum PdkSlot {
     PDK_SLOT_mxfp4_gu_interleave = 155,
     PDK_SLOT_swiglu_quant_e4m3_row = 511,
     PDK_SLOT_rmsnorm_quant_e4m3_row = 512,
-    PDK_SLOT_add_rmsnorm_scaled_quant_e4m3_row = 513
+    PDK_SLOT_add_rmsnorm_scaled_quant_e4m3_row = 513,
+    PDK_SLOT_quantize_nvf4_swiglu = 120,
+    PDK_SLOT_swiglu_fused_nvf4 = 516,
+    PDK_SLOT_add_rmsnorm_nvf4_batch = 861
 };
 
 /* ---- the drop-in boundary ------------------------------------------------ */
@@ -218,6 +221,14 @@ int pd_quantize_nvf4(const void* x, void* q, void* scale, uint32_t n, void* stre
  * scale e4m3 [batch][n/16] = pd_quantize_nvf4 of each row of out.  n % 32 == 0, n <= 51200. */
 int pd_add_rmsnorm_quant_nvf4_batch(void* x, const void* proj, const void* w, void* out, void* q, void* scale,
                                     uint32_t n, float eps, uint32_t batch, void* stream);
+/* slots 120 and 516 (packs/cuda/src/quant/nvf4.cuh:714-775; gpu/fp4.rs:206-260): SwiGLU in front of
+ * the NVFP4 quantizer, h = (g / (1 + expf(-g))) * u in f32.  120: gate and up are planes of n
+ * elements; 516: the two halves of fused rows [n_rows][2 * ff].  n, ff multiples of 32. */
+int pd_quantize_nvf4_swiglu(const void* gate, const void* up, void* q, void* scale, uint32_t n, void* stream);
+int pd_swiglu_fused_nvf4(const void* fused, void* q, void* scale, uint32_t ff, uint32_t n_rows, void* stream);
+/* slot 861 (packs/cuda/src/exports.cuh:505-520): slot 436's contract with proj required */
+int pd_add_rmsnorm_nvf4_batch(void* x, const void* proj, const void* w, void* out, void* q, void* qs, uint32_t n, float eps,
+                              uint32_t batch, void* stream);
 /* slot 393, packs/cuda/src/quant/nvf4.cuh:4365-4403: y f32[out][in] = (e2m1 * e4m3) * scale2. */
 int pd_nvf4_dequant(const void* data, const void* scale, float scale2, void* y, uint32_t in_dim,
                     uint32_t out_dim, void* stream);

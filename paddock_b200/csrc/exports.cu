@@ -95,6 +95,9 @@ static void fill_table_for(PdkKernelTableV1& g_table, int cc_major, int cc_minor
     PDK_SET(f8row_gemm_tc5x);
     PDK_SET(quantize_nvf4);
     PDK_SET(add_rmsnorm_quant_nvf4_batch);
+    PDK_SET(add_rmsnorm_nvf4_batch);
+    PDK_SET(quantize_nvf4_swiglu);
+    PDK_SET(swiglu_fused_nvf4);
     PDK_SET(swiglu_quant_e4m3_row);
     PDK_SET(rmsnorm_quant_e4m3_row);
     PDK_SET(add_rmsnorm_scaled_quant_e4m3_row);

@@ -81,6 +81,30 @@ __global__ void quantize_nvf4_kernel(const float* __restrict__ x, uint8_t* __res
     if ((lane & 1u) == 0u) scale[i >> 4] = (uint8_t)s.byte;
 }
 
+// SwiGLU in front of the quantizer: h = (g / (1 + expf(-g))) * u in f32, then quantize_nvf4_kernel's
+// blocks.  gate / up: two planes of n elements (stride 0), or the two halves of fused rows
+// [rows][2 * ff] (stride = ff: element i of the output is row i / ff, column i % ff).
+__device__ __forceinline__ float silu_times(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+__global__ void quantize_nvf4_swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                            uint8_t* __restrict__ q, uint8_t* __restrict__ scale, uint32_t n, uint32_t ff) {
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();
+    const uint32_t i = (blockIdx.x * 256u + threadIdx.x) * 8u;
+    if (i >= n) return;  // n % 32 == 0: lane pairs leave together
+    size_t src = i;
+    if (ff != 0u) src = (size_t)(i / ff) * 2u * ff + i % ff;   // ff % 32 == 0: the 8 elements stay in one row
+    const float4 g0 = *reinterpret_cast<const float4*>(gate + src), g1 = *reinterpret_cast<const float4*>(gate + src + 4u);
+    const float4 u0 = *reinterpret_cast<const float4*>(up + src), u1 = *reinterpret_cast<const float4*>(up + src + 4u);
+    const float4 a = make_float4(silu_times(g0.x, u0.x), silu_times(g0.y, u0.y), silu_times(g0.z, u0.z), silu_times(g0.w, u0.w));
+    const float4 b = make_float4(silu_times(g1.x, u1.x), silu_times(g1.y, u1.y), silu_times(g1.z, u1.z), silu_times(g1.w, u1.w));
+    const uint32_t lane = threadIdx.x & 31u;
+    float amax = fmaxf(amax4(a), amax4(b));
+    amax = fmaxf(amax, __shfl_xor_sync(0x3u << (lane & 30u), amax, 1));
+    const Nvf4BlockScale s = nvf4_block_scale(amax);
+    *reinterpret_cast<uint32_t*>(q + (i >> 1)) = nvf4_codes4(a, s.recip) | nvf4_codes4(b, s.recip) << 16;
+    if ((lane & 1u) == 0u) scale[i >> 4] = (uint8_t)s.byte;
+}
+
 // Fused producer in front of an NVFP4 GEMM (the contract of packs/cuda/src/quant/nvf4.cuh:545-571):
 // x += proj, out = rmsnorm(x) * w, q / scale = the NVFP4 planes of out.  One CTA per row, and the
 // summed row never leaves the register file: thread t holds the row's float4 number t, t + T,
@@ -274,6 +298,33 @@ PDK_EXPORT int pd_add_rmsnorm_quant_nvf4_batch(void* x, const void* proj, const 
     }
 #undef PDK_NORM_CASE
     return cudaErrorNotSupported;
+}
+
+// slot 861, packs/cuda/src/exports.cuh:505-520: the decode tick's pre-FFN norm feeding the W4A4 GEMM -
+// slot 436's contract with proj required.
+PDK_EXPORT int pd_add_rmsnorm_nvf4_batch(void* x, const void* proj, const void* w, void* out, void* q, void* qs, uint32_t n,
+                                         float eps, uint32_t batch, void* stream) {
+    if (n == 0 || batch == 0) return 0;
+    if (proj == nullptr) return cudaErrorInvalidValue;
+    return pd_add_rmsnorm_quant_nvf4_batch(x, proj, w, out, q, qs, n, eps, batch, stream);
+}
+
+// slot 120, packs/cuda/src/quant/nvf4.cuh:714-735, 1023-1030: h = silu(gate) * up, NVFP4 planes of h
+PDK_EXPORT int pd_quantize_nvf4_swiglu(const void* gate, const void* up, void* q, void* scale, uint32_t n, void* stream) {
+    if (n == 0) return 0;
+    if ((n & 31u) != 0u || !pdk_aligned(gate, 16) || !pdk_aligned(up, 16) || !pdk_aligned(q, 4)) return cudaErrorInvalidValue;
+    return pdk_launch_pdl(quantize_nvf4_swiglu_kernel, dim3((n / 8u + 255u) / 256u), dim3(256), 0, (cudaStream_t)stream,
+                          (const float*)gate, (const float*)up, (uint8_t*)q, (uint8_t*)scale, n, 0u);
+}
+
+// slot 516, packs/cuda/src/quant/nvf4.cuh:737-775: the same over fused rows [n_rows][2 * ff] (gate | up)
+PDK_EXPORT int pd_swiglu_fused_nvf4(const void* fused, void* q, void* scale, uint32_t ff, uint32_t n_rows, void* stream) {
+    if (n_rows == 0 || ff == 0) return 0;
+    if ((ff & 31u) != 0u || (uint64_t)n_rows * ff > 0xffffffffull || !pdk_aligned(fused, 16) || !pdk_aligned(q, 4))
+        return cudaErrorInvalidValue;
+    const uint32_t n = n_rows * ff;
+    return pdk_launch_pdl(quantize_nvf4_swiglu_kernel, dim3((n / 8u + 255u) / 256u), dim3(256), 0, (cudaStream_t)stream,
+                          (const float*)fused, (const float*)fused + ff, (uint8_t*)q, (uint8_t*)scale, n, ff);
 }
 
 // slot 393, packs/cuda/src/quant/nvf4.cuh:4365-4403

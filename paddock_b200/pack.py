@@ -101,7 +101,8 @@ _SIGS = {
     "f8row_gemm": "pppppuuu", "f8row_gemm_tc5x": "pppppuuu",
     "swiglu_quant_e4m3_row": "ppppuu", "rmsnorm_quant_e4m3_row": "pppppufu",
     "add_rmsnorm_scaled_quant_e4m3_row": "ppppppuffu",
-    "quantize_nvf4": "pppu", "add_rmsnorm_quant_nvf4_batch": "ppppppufu", "nvf4_dequant": "ppfpuu", "nvf4_gemv": "pppppfuu",
+    "quantize_nvf4": "pppu", "add_rmsnorm_quant_nvf4_batch": "ppppppufu", "add_rmsnorm_nvf4_batch": "ppppppufu",
+    "quantize_nvf4_swiglu": "ppppu", "swiglu_fused_nvf4": "pppuu", "nvf4_dequant": "ppfpuu", "nvf4_gemv": "pppppfuu",
     "nvf4_tc5_tile_scales": "ppuu", "nvf4_gemm_tc5w": "ppppppfuuupU",
     "moe_topk_batch": "ppuuppu", "moe_align": "ppppuuuu", "moe_align_bm": "ppppuuuuu", "moe_slot_combine": "ppuuu",
     "kquant_dequant": "ppUu", "kquant_repack": "pppUu", "kquant_gemv": "ppppuuu",

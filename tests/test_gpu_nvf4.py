@@ -149,3 +149,49 @@ def test_add_rmsnorm_quant_nvf4_refuses_bad_shapes(pack):
     buf = torch.zeros(4096, dtype=torch.float32, device="cuda")
     assert pack.status("add_rmsnorm_quant_nvf4_batch", buf, None, buf, buf, buf, buf, 48, 1e-6, 1) == 1
     assert pack.status("add_rmsnorm_quant_nvf4_batch", buf, None, buf, buf, buf, buf, 0, 1e-6, 1) == 0
+
+
+@pytest.mark.parametrize("rows,ff", [(1, 32), (3, 2880), (40, 17408)])
+def test_swiglu_in_front_of_the_nvf4_quantizer(pack, rows, ff):
+    """Slots 120 (two planes) and 516 (fused gate | up rows): the same planes, and the quantizer's
+    output on silu(gate) * up (numpy's f32 exp may be an ulp off the device's: codes equal or one
+    step apart on a handful of elements, scale bytes likewise)."""
+    g = oracle.fill_normal(rows * ff, 4300 + ff, 2.0).reshape(rows, ff)
+    u = oracle.fill_normal(rows * ff, 4301 + ff, 1.0).reshape(rows, ff)
+    h = oracle.swiglu_silu(g, u)
+    q_ref, s_ref = oracle.quantize_nvf4(h.reshape(-1))
+    outs = []
+    for fused in (False, True):
+        d_q = torch.zeros(rows * ff // 2, dtype=torch.uint8, device="cuda")
+        d_s = torch.zeros(rows * ff // 16, dtype=torch.uint8, device="cuda")
+        if fused:
+            pack.call("swiglu_fused_nvf4", dev_f32(np.concatenate([g, u], axis=1).reshape(-1)), d_q, d_s, ff, rows)
+        else:
+            pack.call("quantize_nvf4_swiglu", dev_f32(g.reshape(-1)), dev_f32(u.reshape(-1)), d_q, d_s, rows * ff)
+        torch.cuda.synchronize()
+        outs.append((d_q.cpu().numpy(), d_s.cpu().numpy()))
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    assert np.mean(outs[0][1] != s_ref.reshape(-1)) < 2e-3
+    assert np.mean(outs[0][0] != q_ref.reshape(-1)) < 5e-3
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    assert pack.status("quantize_nvf4_swiglu", buf, buf, buf, buf, 48) == 1
+    assert pack.status("swiglu_fused_nvf4", buf, buf, buf, 48, 2) == 1
+
+
+def test_add_rmsnorm_nvf4_batch_is_slot_436_with_a_residual(pack):
+    n, batch, eps = 5120, 3, 1e-6
+    x = oracle.fill_normal(batch * n, 4400, 1.5)
+    proj = oracle.fill_normal(batch * n, 4401, 0.5)
+    w = (1.0 + 0.1 * oracle.fill_normal(n, 4402, 1.0)).astype(np.float32)
+    res = []
+    for name in ("add_rmsnorm_quant_nvf4_batch", "add_rmsnorm_nvf4_batch"):
+        d_x, d_out = dev_f32(x), torch.zeros(batch * n, dtype=torch.float32, device="cuda")
+        d_q = torch.zeros(batch * n // 2, dtype=torch.uint8, device="cuda")
+        d_s = torch.zeros(batch * n // 16, dtype=torch.uint8, device="cuda")
+        pack.call(name, d_x, dev_f32(proj), dev_f32(w), d_out, d_q, d_s, n, eps, batch)
+        torch.cuda.synchronize()
+        res.append([t.cpu().numpy() for t in (d_x, d_out, d_q, d_s)])
+    for a, b in zip(*res):
+        assert np.array_equal(a, b)
+    d = torch.zeros(64, dtype=torch.float32, device="cuda")
+    assert pack.status("add_rmsnorm_nvf4_batch", d, None, d, d, d, d, 32, eps, 1) == 1

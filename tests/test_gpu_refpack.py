@@ -357,6 +357,26 @@ def test_e4m3_producers_against_reference_pack(pack, ref):
         assert np.mean(ours[3] != theirs[3]) < 1e-3
 
 
+def test_nvf4_swiglu_quantizers_against_reference_pack(pack, ref):
+    """Slots 120 and 516 on both packs: byte-identical planes."""
+    rows, ff = 5, 2880
+    g = oracle.fill_normal(rows * ff, 5400, 2.0)
+    u = oracle.fill_normal(rows * ff, 5401, 1.0)
+
+    def mk():
+        q = torch.zeros(rows * ff // 2, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(rows * ff // 16, dtype=torch.uint8, device="cuda")
+        return (dev_f32(g), dev_f32(u), q, s, rows * ff), [q, s]
+    assert_bytes_equal(run_both(pack, ref, "quantize_nvf4_swiglu", mk, 2))
+    fused = np.concatenate([g.reshape(rows, ff), u.reshape(rows, ff)], axis=1).reshape(-1)
+
+    def mkf():
+        q = torch.zeros(rows * ff // 2, dtype=torch.uint8, device="cuda")
+        s = torch.zeros(rows * ff // 16, dtype=torch.uint8, device="cuda")
+        return (dev_f32(fused), q, s, ff, rows), [q, s]
+    assert_bytes_equal(run_both(pack, ref, "swiglu_fused_nvf4", mkf, 2))
+
+
 def _moe_slot_chain(p, raw, x, idx, w, tokens, n_expert, k, embd, ff, decode):
     """The engine's MoE chain through pack `p`'s own slots (its own fused gate|up plane);
     decode: the unsorted pair 92 / 93, else align -> 88 -> 89 -> combine."""
