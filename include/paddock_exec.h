@@ -90,7 +90,7 @@ void pdx_plane_free(PdxExecutor* ex, PdxPlane* p);
  * Q8_0 transcode */
 int pdx_upload_raw(PdxExecutor* ex, const PdkGgufFamily* map, const char* name, PdxPlane** out);
 /* load_quantw (gpu/kquant.rs:180-240): per-tensor dispatch.  Q8_0 -> RepackedQ8; Q4_K / Q5_K /
- * Q6_K -> RepackedKQ; Q4_0 -> RepackedKQ when the row is whole super-blocks, else the Q8_0
+ * Q6_K / IQ4_XS -> RepackedKQ; Q4_0 -> RepackedKQ when the row is whole super-blocks, else the Q8_0
  * transcode; anything else PDX_NO_KERNEL. */
 int pdx_load_quantw(PdxExecutor* ex, const PdkGgufFamily* map, const char* name, PdxPlane** out);
 /* repack_q8_blocks (gpu/upload.rs:305-353) and repack_kquant_raw (gpu/kquant.rs:284-374) on host bytes */

@@ -76,7 +76,7 @@ def clones_for(nbytes):
     return max(2, -(-2 * L2_BYTES // max(nbytes, 1)) + 1)
 
 
-KQ_MORE = {"q5_k": (13, 176, 256), "q6_k": (14, 210, 256), "q4_0": (2, 18, 32)}  # ggml id, block bytes, elements
+KQ_MORE = {"q5_k": (13, 176, 256), "q6_k": (14, 210, 256), "q4_0": (2, 18, 32), "iq4_xs": (23, 136, 256)}  # ggml id, block bytes, elements
 
 
 def raw_kquant_blocks(name, n_elems):
@@ -100,7 +100,7 @@ def bench_q4k(ex, a):
     if a.dtype != "q4_k":
         ty, nbytes, elems = KQ_MORE[a.dtype]
         raw = raw_kquant_blocks(a.dtype, n * k)
-        data_b = {"q5_k": 160, "q6_k": 192, "q4_0": 128}[a.dtype]
+        data_b = {"q5_k": 160, "q6_k": 192, "q4_0": 128, "iq4_xs": 128}[a.dtype]
         from paddock_b200.planes import RepackedKQ
         planes = []
         for _ in range(clones_for(n * k // 256 * (data_b + 24))):
@@ -683,7 +683,7 @@ def main():
     ap.add_argument("--moe-path", default="tc5", choices=["tc5", "mma"],
                     help="expert GEMMs: block-scaled tcgen05 (default) or the mma.sync kernels")
     ap.add_argument("--graph", action="store_true", help="replay the timed launches from a CUDA graph (moe_mxfp4, moe_ep, q4k_gemv, q8_gemv, nvf4_gemv, nvf4_gemm)")
-    ap.add_argument("--dtype", default="q4_k", choices=["q4_k", "q5_k", "q6_k", "q4_0"], help="q4k_gemv: the plane's format")
+    ap.add_argument("--dtype", default="q4_k", choices=["q4_k", "q5_k", "q6_k", "q4_0", "iq4_xs"], help="q4k_gemv: the plane's format")
     ap.add_argument("--pack", default=None, help="path of a kernel-pack library to time instead of this package's")
     args = ap.parse_args()
     a = Case(args.op, args.m, args.n, args.k, args.iters, args.out, args.moe_path, args.graph, args.dtype, args.pack)

@@ -53,7 +53,7 @@ _dq_mxfp4 = _sig("orc_dequant_mxfp4", C.c_int, _u8p, C.c_size_t, _f32p, C.c_size
 _dq_q8 = _sig("orc_dequant_q8_0", C.c_int, _u8p, C.c_size_t, _f32p, C.c_size_t)
 _dq_q4k = _sig("orc_dequant_q4_k", C.c_int, _u8p, C.c_size_t, _f32p, C.c_size_t)
 _dq_kq = {name: _sig(f"orc_dequant_{name}", C.c_int, _u8p, C.c_size_t, _f32p, C.c_size_t)
-          for name in ("q5_k", "q6_k", "q4_0")}
+          for name in ("q5_k", "q6_k", "q4_0", "iq4_xs")}
 _dq_nvfp4 = _sig("orc_dequant_nvfp4", None, _u8p, _u8p, C.c_float, _f32p, C.c_uint32, C.c_uint32)
 _dq_fp8 = _sig("orc_dequant_fp8_channel", None, _u8p, _f32p, _f32p, C.c_uint32, C.c_uint32)
 _q_q8 = _sig("orc_quantize_q8_0", None, _f32p, C.c_size_t, _u8p)
@@ -117,11 +117,11 @@ def dequant_q8_0(data, out=None):
     return out
 
 
-KQUANT_LAYOUT = {"q4_k": (144, 256), "q5_k": (176, 256), "q6_k": (210, 256), "q4_0": (18, 32)}  # (bytes, elements)
+KQUANT_LAYOUT = {"q4_k": (144, 256), "q5_k": (176, 256), "q6_k": (210, 256), "q4_0": (18, 32), "iq4_xs": (136, 256)}  # (bytes, elements)
 
 
 def dequant_kquant(name, data):
-    """q5_k / q6_k / q4_0 (crates/paddock-engine/tests/gpu_kquant_parity.rs:39-128)."""
+    """q5_k / q6_k / q4_0 / iq4_xs (crates/paddock-engine/tests/gpu_kquant_parity.rs:39-128)."""
     data = _u8(data)
     nbytes, elems = KQUANT_LAYOUT[name]
     out = np.empty(data.size // nbytes * elems, np.float32)

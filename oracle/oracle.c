@@ -264,6 +264,33 @@ int orc_dequant_q4_0(const uint8_t* data, size_t n_bytes, float* out, size_t n_o
     return 0;
 }
 
+/* gpu_kquant_parity.rs:19-21, 96-115 (IQ4_XS arm): super-block of 136 bytes { f16 d, u16 scales_h,
+ * u8 scales_l[4], u8 qs[128] }.  Sub-block ib of 32 weights: ls = 4 bits of scales_l | 2 bits of
+ * scales_h << 4, dl = d * (ls - 32); byte j of the sub-block holds weight j (low nibble) and 16 + j
+ * (high), each an index into ggml's 16-entry non-linear code book; value = dl * book[index]. */
+static const int8_t orc_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+int orc_dequant_iq4_xs(const uint8_t* data, size_t n_bytes, float* out, size_t n_out) {
+    if (n_bytes % 136) return -1;
+    size_t n_super = n_bytes / 136;
+    if (n_out != n_super * 256) return -2;
+#pragma omp parallel for schedule(static)
+    for (size_t b = 0; b < n_super; ++b) {
+        const uint8_t* s = data + b * 136;
+        float d = orc_f16_to_f32((uint16_t)(s[0] | (s[1] << 8)));
+        unsigned sh = (unsigned)(s[2] | (s[3] << 8));
+        const uint8_t *sl = s + 4, *qs = s + 8;
+        for (int ib = 0; ib < 8; ++ib) {
+            int ls = (int)(((sl[ib >> 1] >> (4 * (ib & 1))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)) - 32;
+            float dl = d * (float)ls;
+            for (int j = 0; j < 16; ++j) {
+                out[b * 256 + ib * 32 + j] = dl * (float)orc_iq4nl[qs[ib * 16 + j] & 0xF];
+                out[b * 256 + ib * 32 + 16 + j] = dl * (float)orc_iq4nl[qs[ib * 16 + j] >> 4];
+            }
+        }
+    }
+    return 0;
+}
+
 /* crates/paddock-models/src/modelopt.rs:408-424: op order (e2m1*e4m3)*scale2;
  * byte j holds elements 2j (low nibble) and 2j+1 (high nibble). */
 void orc_dequant_nvfp4(const uint8_t* data, const uint8_t* scale, float scale2, float* out,

@@ -586,7 +586,7 @@ int more_gemv_i8(const void* data, const void* scales, const float* x, float* y,
 
 int check_gemv(const void* data, const void* scales, const void* x, const void* y, uint32_t in_dim, uint32_t dtype) {
     if (dtype != PDK_KQ_Q4K && !pdk_kq_more_has(dtype))
-        return dtype == PDK_KQ_IQ4XS ? cudaErrorNotSupported : cudaErrorInvalidValue;
+        return cudaErrorInvalidValue;
     if (in_dim == 0u || (in_dim & 255u) != 0u) return cudaErrorInvalidValue;
     if (!pdk_aligned(data, 16) || !pdk_aligned(scales, 8) || !pdk_aligned(x, 16) || !pdk_aligned(y, 4))
         return cudaErrorInvalidValue;
@@ -598,7 +598,7 @@ int check_gemv(const void* data, const void* scales, const void* x, const void* 
 PDK_EXPORT int pd_kquant_dequant(const void* src, void* dst, uint64_t n_super, uint32_t dtype, void* stream) {
     if (n_super == 0) return 0;
     if (pdk_kq_more_has(dtype)) return pdk_kq_more_dequant(src, dst, n_super, dtype, (cudaStream_t)stream);
-    if (dtype != PDK_KQ_Q4K) return dtype == PDK_KQ_IQ4XS ? cudaErrorNotSupported : cudaErrorInvalidValue;
+    if (dtype != PDK_KQ_Q4K) return cudaErrorInvalidValue;
     if (!pdk_aligned(src, 2) || !pdk_aligned(dst, 4)) return cudaErrorInvalidValue;
     const uint64_t blocks = (n_super + 7u) / 8u;
     if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
@@ -611,7 +611,7 @@ PDK_EXPORT int pd_kquant_repack(const void* src, void* dst_data, void* dst_scale
     if (n_super == 0) return 0;
     if (pdk_kq_more_has(dtype))
         return pdk_kq_more_repack(src, dst_data, dst_scales, n_super, dtype, (cudaStream_t)stream);
-    if (dtype != PDK_KQ_Q4K) return dtype == PDK_KQ_IQ4XS ? cudaErrorNotSupported : cudaErrorInvalidValue;
+    if (dtype != PDK_KQ_Q4K) return cudaErrorInvalidValue;
     if (!pdk_aligned(src, 4) || !pdk_aligned(dst_data, 4)) return cudaErrorInvalidValue;
     const uint64_t blocks = (n_super + 7u) / 8u;
     if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;

@@ -10,6 +10,8 @@
 //   Q6_K  data 192 B/sb = ql[128] then qh[64];  record 24 B {f16 d, pad2, i8 sc[16], pad4}
 //   Q4_0  data 128 B/sb, nibbles permuted into the Q4_K convention (group g byte l = block 2g
 //         weight l low | block 2g+1 weight l high);  record 24 B {f16 d[8], pad8}
+//   IQ4_XS data 128 B/sb = qs verbatim (sub-block ib byte j = weight j low | weight 16 + j high, each a
+//         code-book index);  record 24 B {f16 d, pad2, i8 ls - 32 [8], pad12}
 #include "pdk_common.cuh"
 
 namespace {
@@ -22,6 +24,12 @@ __device__ __forceinline__ void scale_min_k4(const uint8_t* s, uint32_t j, uint3
         *sc = (uint32_t)(s[j + 4u] & 0xFu) | ((uint32_t)(s[j - 4u] >> 6) << 4);
         *m = (uint32_t)(s[j + 4u] >> 4) | ((uint32_t)(s[j] >> 6) << 4);
     }
+}
+// ggml's 16-entry non-linear 4-bit code book (IQ4_NL / IQ4_XS), eight signed bytes per word
+__device__ __forceinline__ int iq4nl(uint32_t index) {
+    const uint64_t lo = 0xF6EADDCFBFAD9881ull;   // -127 -104 -83 -65 -49 -35 -22 -10
+    const uint64_t hi = 0x7159453526190D01ull;   //    1   13  25  38  53  69  89 113
+    return (int)(int8_t)(((index & 8u) ? hi : lo) >> ((index & 7u) * 8u));
 }
 __device__ __forceinline__ float f16_at(const uint8_t* p) {
     return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8))));
@@ -61,6 +69,16 @@ __global__ void kq_dequant_kernel(const uint8_t* __restrict__ src, float* __rest
                 const float ds = __fmul_rn(d, (float)(int8_t)s[192u + nh * 8u + r * 2u + (l >> 4)]);
                 y[nh * 128u + r * 32u + l] = __fmul_rn(ds, (float)q[r]);
             }
+        }
+    } else if (dtype == PDK_KQ_IQ4XS) {
+        const uint8_t* s = src + b * 136u;
+        const float d = f16_at(s);
+        const uint32_t sh = (uint32_t)s[2] | ((uint32_t)s[3] << 8);
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; ++j) {
+            const int ls = (int)(((s[4u + (j >> 1)] >> (4u * (j & 1u))) & 0xFu) | (((sh >> (2u * j)) & 3u) << 4)) - 32;
+            const uint32_t q = s[8u + j * 16u + (l & 15u)];
+            y[j * 32u + l] = __fmul_rn(__fmul_rn(d, (float)ls), (float)iq4nl(l < 16u ? (q & 0xFu) : (q >> 4)));
         }
     } else {  // Q4_0: eight 18-byte blocks
         const uint8_t* s = src + b * 144u;
@@ -103,6 +121,21 @@ __global__ void kq_repack_kernel(const uint8_t* __restrict__ src, uint8_t* __res
         if (l < 16u) rec[4u + l] = s[192u + l];
         if (l == 16u) { rec[0] = s[208]; rec[1] = s[209]; rec[2] = 0; rec[3] = 0; }
         if (l >= 20u && l < 24u) rec[l] = 0;
+    } else if (dtype == PDK_KQ_IQ4XS) {
+        const uint8_t* s = src + b * 136u;
+        uint8_t* d = dst_data + b * 128u;
+        for (uint32_t i = l; i < 128u; i += 32u) d[i] = s[8u + i];
+        if (l < 8u) {
+            const uint32_t sh = (uint32_t)s[2] | ((uint32_t)s[3] << 8);
+            const int ls = (int)(((s[4u + (l >> 1)] >> (4u * (l & 1u))) & 0xFu) | (((sh >> (2u * l)) & 3u) << 4)) - 32;
+            rec[4u + l] = (uint8_t)(int8_t)ls;
+        } else if (l < 10u) {
+            rec[l - 8u] = s[l - 8u];
+        } else if (l < 12u) {
+            rec[l - 8u] = 0;
+        } else if (l < 24u) {
+            rec[l] = 0;
+        }
     } else {  // Q4_0
         const uint8_t* s = src + b * 144u;
         uint8_t* d = dst_data + b * 128u;
@@ -141,6 +174,13 @@ __device__ __forceinline__ void decode8(uint32_t dtype, const uint8_t* d, const 
 #pragma unroll
             for (uint32_t r = 0; r < 4u; ++r)
                 w[nh * 4u + r] = __fmul_rn(__fmul_rn(dd, (float)(int8_t)rec[4u + nh * 8u + r * 2u + (l >> 4)]), (float)q[r]);
+        }
+    } else if (dtype == PDK_KQ_IQ4XS) {
+        const float dd = f16_at(rec);
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; ++j) {
+            const uint32_t q = d[j * 16u + (l & 15u)];
+            w[j] = __fmul_rn(__fmul_rn(dd, (float)(int8_t)rec[4u + j]), (float)iq4nl(l < 16u ? (q & 0xFu) : (q >> 4)));
         }
     } else {  // Q4_0 in the Q4_K nibble convention, eight independent f16 scales
 #pragma unroll
@@ -189,7 +229,9 @@ uint32_t data_bytes(uint32_t dtype) { return dtype == PDK_KQ_Q5K ? 160u : dtype 
 
 }  // namespace
 
-bool pdk_kq_more_has(uint32_t dtype) { return dtype == PDK_KQ_Q5K || dtype == PDK_KQ_Q6K || dtype == PDK_KQ_Q4_0; }
+bool pdk_kq_more_has(uint32_t dtype) {
+    return dtype == PDK_KQ_Q5K || dtype == PDK_KQ_Q6K || dtype == PDK_KQ_Q4_0 || dtype == PDK_KQ_IQ4XS;
+}
 
 int pdk_kq_more_dequant(const void* src, void* dst, uint64_t n_super, uint32_t dtype, cudaStream_t st) {
     if (!pdk_aligned(dst, 4)) return cudaErrorInvalidValue;

@@ -20,7 +20,7 @@
 namespace {
 
 // (raw ggml id, raw bytes, repacked data bytes) per 256 weights and the scale record size, as
-// the pack's k-quant slots lay planes out (gpu/types.rs:285-381; this pack serves four types)
+// the pack's k-quant slots lay planes out (gpu/types.rs:285-381; this pack serves five types)
 struct KqLayout {
     uint32_t raw_id, raw_b, data_b, scale_b;
 };
@@ -30,6 +30,7 @@ bool kq_layout(uint32_t ty, KqLayout* out) {
         case PDK_GGML_Q4_K: *out = {12u, 144u, 128u, 24u}; return true;
         case PDK_GGML_Q5_K: *out = {13u, 176u, 160u, 24u}; return true;
         case PDK_GGML_Q6_K: *out = {14u, 210u, 192u, 24u}; return true;
+        case PDK_GGML_IQ4_XS: *out = {23u, 136u, 128u, 24u}; return true;
         default: return false;
     }
 }

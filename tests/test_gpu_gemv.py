@@ -255,7 +255,7 @@ def test_q4_k_gemv_refuses_bad_shapes(pack):
     buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     assert pack.status("kquant_gemv", buf, buf, buf, buf, 128, 4, 12) == 1     # K not a multiple of 256
     assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 99) == 1     # unknown dtype
-    assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 23) == 801   # IQ4_XS: known, not built
+    assert pack.status("kquant_gemv", buf, buf, buf, buf, 256, 4, 16) == 1     # IQ2_XXS: no kernel class in this pack
     assert pack.status("pdk_kquant_gemm_f32", buf, buf, buf, buf, 256, 4, 65, 12) == 1
 
 
@@ -316,7 +316,9 @@ def raw_kquant(name, n_super, seed):
     rng = np.random.default_rng(seed)
     raw = rng.integers(0, 256, (n_blocks, nbytes), dtype=np.uint8)
     d = (rng.random(n_blocks) * 0.01 + 1e-4).astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
-    if name == "q6_k":
+    if name == "iq4_xs":
+        raw[:, 0:2] = (rng.random(n_blocks) * 0.001 + 1e-5).astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
+    elif name == "q6_k":
         raw[:, 208:210] = d
     else:
         raw[:, 0:2] = d
@@ -325,7 +327,7 @@ def raw_kquant(name, n_super, seed):
     return raw.reshape(-1)
 
 
-KQ = {"q5_k": (13, 160), "q6_k": (14, 192), "q4_0": (2, 128)}
+KQ = {"q5_k": (13, 160), "q6_k": (14, 192), "q4_0": (2, 128), "iq4_xs": (23, 128)}
 
 
 @pytest.mark.parametrize("k,n", [(1024, 70), (5120, 333), (512, 40)])

@@ -275,7 +275,7 @@ def test_q8_activation_quantizers_and_w4a8_gemv(pack, ref):
     assert rel_l2(ours, theirs.astype(np.float64)) < 1e-4 < TOL
 
 
-@pytest.mark.parametrize("name,dtype,datab", [("q5_k", 13, 160), ("q6_k", 14, 192), ("q4_0", 2, 128)])
+@pytest.mark.parametrize("name,dtype,datab", [("q5_k", 13, 160), ("q6_k", 14, 192), ("q4_0", 2, 128), ("iq4_xs", 23, 128)])
 def test_more_kquants_against_reference_pack(pack, ref, name, dtype, datab):
     from test_gpu_gemv import raw_kquant
     k, n = 1024, 64

@@ -297,3 +297,26 @@ def test_add_rmsnorm_hand_values():
     assert not out[0, 2:].any()
     v2, out2 = oracle.add_rmsnorm(x, None, w, 0.0)
     assert v2[0, 0] == 1.0 and abs(float(out2[0, 1]) - 8.0 / (17.0 / 32.0) ** 0.5) < 1e-6
+
+
+def test_iq4_xs_dequant_against_a_scalar_walk():
+    """IQ4_XS (gpu_kquant_parity.rs:19-21, 96-115): 136-byte super-blocks, 6-bit sub-block scales split
+    over scales_l / scales_h, ggml's 16-entry code book; the C restatement against a plain Python walk."""
+    book = [-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113]
+    rng = np.random.default_rng(77)
+    raw = rng.integers(0, 256, (3, 136), dtype=np.uint8)
+    raw[:, 0:2] = np.array([0.0123, -0.5, 1.0 / 1024], np.float16).view(np.uint8).reshape(3, 2)
+    got = oracle.dequant_kquant("iq4_xs", raw.reshape(-1)).reshape(3, 256)
+    for b in range(3):
+        s = raw[b]
+        d = np.frombuffer(s[0:2].tobytes(), np.float16)[0].astype(np.float32)
+        sh = int(s[2]) | int(s[3]) << 8
+        for ib in range(8):
+            ls = (((int(s[4 + ib // 2]) >> (4 * (ib & 1))) & 15) | (((sh >> (2 * ib)) & 3) << 4)) - 32
+            dl = np.float32(d * np.float32(ls))
+            for j in range(16):
+                q = int(s[8 + ib * 16 + j])
+                assert got[b, ib * 32 + j] == np.float32(dl * np.float32(book[q & 15]))
+                assert got[b, ib * 32 + 16 + j] == np.float32(dl * np.float32(book[q >> 4]))
+    with pytest.raises(Exception):
+        oracle.dequant_kquant("iq4_xs", raw.reshape(-1)[:100])
