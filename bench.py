@@ -256,9 +256,13 @@ def other_configs(ex, quick):
             elif case.op == "nvf4_gemm" and case.m >= 512:
                 rec.update(achieved=r["tflops"], unit="TFLOP/s", frac=r["frac_of_4x_bf16"], denominator="4 x measured bf16 burst",
                            gbs=r["gbs"], frac_of_hbm=r["frac_of_hbm"])
-                if probe.get("nvf4_m128n128k64_with_scale_copies"):
-                    rec.update(frac_of_probe=r["tflops"] / probe["nvf4_m128n128k64_with_scale_copies"],
-                               probe_denominator="tcgen05.mma NVFP4 issue rate with its scale-cell copies")
+                # prefill widths run on pairs of SMs: the pair's rate is the denominator (the one-SM rate
+                # with the same copies is a third lower)
+                key = "nvf4_pair_m256n128k64_with_scale_copies"
+                if probe.get(key):
+                    rec.update(frac_of_probe=r["tflops"] / probe[key],
+                               probe_denominator="tcgen05.mma NVFP4 issue rate on pairs of SMs with its scale-cell copies",
+                               frac_of_one_sm_probe=r["tflops"] / probe.get("nvf4_m128n128k64_with_scale_copies", float("nan")))
             else:
                 rec.update(achieved=r["gbs"], unit="GB/s", frac=r["frac_of_hbm"], denominator="measured HBM copy")
             if "distinct_experts" in r:
@@ -615,7 +619,7 @@ def run_ours(args, rank, world, local_rank):
                            ("moe_mxfp4_t1024_expert_parallel", kbench.Case("moe_ep", m=1024, graph=True, iters=5 if quick else 10))):
             try:
                 r = kbench.run_case(ex, case)
-                keep = ("us", "n_gpus", "us_gemm_only", "us_gemm_nccl_allgather", "us_gemm_peer_stores", "m_chunks",
+                keep = ("us", "n_gpus", "us_gemm_only", "us_gemm_nccl_allgather", "us_gemm_peer_stores", "exchange", "m_chunks",
                         "exchange_bytes_per_rank", "parity_ok", "tflops", "gbs", "frac_of_hbm", "frac_of_2x_bf16",
                         "distinct_experts", "device_error")
                 sharded[name] = {k: r[k] for k in keep if k in r}

@@ -224,6 +224,32 @@ def test_q4_k_batch_shapes(pack, k, n, batch):
         assert not y[2].any()
 
 
+@pytest.mark.parametrize("k,n", [(5120, 1000), (6144, 72), (2048, 33)])
+@pytest.mark.parametrize("batch", [2, 3, 8])
+def test_q4_k_tokens_as_columns_on_the_ring(pack, k, n, batch):
+    """2 .. 8 tokens with K / 512 between 4 and 12: the ring kernel with the tokens as mma columns
+    (14-bit block-floating activations per 256 elements, integer accumulation over a super-block).
+    Ragged rows, an all-zero token, a token of tiny values; bit-identical from call to call."""
+    w = oracle.fill_normal(n * k, seed_for(2, 970 + k), 0.02)
+    x = oracle.fill_normal(batch * k, seed_for(2, 971 + batch), 1.0)
+    x[:k] = 0.0
+    x[k:2 * k] *= 1.0e-12
+    raw, d_data, d_sc = q4k_planes(pack, w, n, k)
+    outs = []
+    for _ in range(2):
+        d_y = torch.full((batch * n,), float("nan"), dtype=torch.float32, device="cuda")
+        pack.call("pdk_kquant_gemm_f32", d_data, d_sc, dev_f32(x), d_y, k, n, batch, 12)
+        torch.cuda.synchronize()
+        outs.append(d_y.cpu().numpy())
+    assert pack.device_error() == 0
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    ref, ab = oracle.matmul_f64(oracle.dequant_q4_k(raw), x, k, n, batch, with_abs=True)
+    y = outs[0].reshape(batch, n)
+    assert np.isfinite(y).all() and not y[0].any()
+    for t in range(1, batch):
+        assert cond_err(y[t:t + 1], ref[t:t + 1], np.maximum(ab[t:t + 1], 1e-30)) < 2e-5 < TOL, t
+
+
 def test_q4_k_batch_is_deterministic(pack):
     """The two K halves of a tile add into y in either order: the result must not depend on it."""
     k, n, batch = 5120, 2048, 16
