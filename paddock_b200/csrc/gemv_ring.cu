@@ -793,295 +793,6 @@ bool make_batch_plan(uint32_t in_dim, BatchPlan& p) {
 }
 
 
-// ---------------------------------------------------------------------------
-// Q4_K with 2..8 tokens on the same ring.  As gemm_ring_q8_kernel, with what the format adds:
-//   * activations are block floating point per 256-element unit (one power-of-two step per token
-//     and unit, 14-bit integers in two int8 limbs), so that the eight 32-weight blocks of a
-//     super-block accumulate in integers: U += sc[block] * T, M += m[block] * (sum of the block's
-//     activation integers), one f32 fold y += step * (d * U - dmin * M) per super-block.
-//     Bounds: |T| <= 32 * 15 * 2^13, |U| <= 8 * 63 * |T| < 2^31.
-//   * one ldmatrix.x4 per 32-byte group gives the A fragments of two blocks (low and high
-//     nibbles); the high nibbles stay in place (16 x code, unsigned) and their sums are shifted back.
-// x f32 [batch][in_dim], or int8 xq with one f32 scale per 32 (the W4A8 slots' operands).
-// ---------------------------------------------------------------------------
-enum : unsigned int { kErrBatch4Full = 0x1d, kErrBatch4Fold = 0x1e, kErrBatch4Free = 0x1f, kErrBatch4Drain = 0x20 };
-
-__global__ void __launch_bounds__(kMaxWarps * 32u, 1)
-gemm_ring_q4k_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant__ CUtensorMap rmap,
-                     const float* __restrict__ x, const int8_t* __restrict__ xq, const float* __restrict__ xq_scale,
-                     float* __restrict__ y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, const BatchPlan pl,
-                     unsigned int* __restrict__ err) {
-    constexpr uint32_t kUnitData = kBoxBytes;                  // a unit's box: 16 rows x 128 bytes
-    constexpr uint32_t kRecRow = 2u * Q4K::kRecBytes;          // a pair's records of one row (48 bytes)
-    constexpr uint32_t kStageData = 2u * kUnitData, kStageRec = 16u * kRecRow;
-    extern __shared__ __align__(1024) uint8_t smem[];
-    float* steps = reinterpret_cast<float*>(smem + pl.off_steps);        // [W][2 units][8 tokens]
-    int* isums = reinterpret_cast<int*>(smem + pl.off_steps + kMaxWarps * 64u);   // [W][16 blocks][8 tokens]
-    float* red = reinterpret_cast<float*>(smem + pl.off_red);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + pl.off_bar);
-    uint64_t* red_full = full + kMaxWarps * kMaxDepth;
-    uint64_t* red_free = red_full + kBatchRedBufs;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(red_free + kBatchRedBufs);
-
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t W = pl.W, D = pl.D;
-    const uint32_t n_tiles = (out_dim + 15u) >> 4;
-    const uint32_t tile_lo = (uint32_t)((uint64_t)blockIdx.x * n_tiles / gridDim.x);
-    const uint32_t tile_hi = (uint32_t)((uint64_t)(blockIdx.x + 1u) * n_tiles / gridDim.x);
-    const uint32_t my_tiles = tile_hi - tile_lo;
-
-    uint64_t* my_full = full + warp * kMaxDepth;
-    uint8_t* my_data = smem + pl.off_data + (size_t)warp * D * kStageData;
-    uint8_t* my_rec = smem + pl.off_rec + (size_t)warp * D * kStageRec;
-
-    auto issue = [&](uint32_t stage, uint32_t tl) {
-        uint64_t* bar = my_full + stage;
-        tc5::mbar_arrive_expect_tx_elect(bar, kStageData + kStageRec);
-        const int32_t row = (int32_t)((tile_lo + tl) * 16u);
-#pragma unroll
-        for (uint32_t b = 0; b < 2u; ++b)
-            tc5::tma_load_2d_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
-                                   (int32_t)(warp * 2u * Q4K::kDataBytes + b * 128u), row);
-        tc5::tma_load_2d_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(warp * kRecRow), row);
-    };
-
-    if (lane == 0u) {
-        for (uint32_t s = 0; s < D; ++s) tc5::mbar_init(my_full + s, 1u);
-        tc5::mbar_fence_init();
-    }
-    __syncwarp();
-    uint32_t issued = 0;
-    if (my_tiles > 0u) { issue(0u, 0u); issued = 1u; }
-    if (tid == 0u) {
-        for (uint32_t b = 0; b < kBatchRedBufs; ++b) {
-            tc5::mbar_init(&red_full[b], W);
-            tc5::mbar_init(&red_free[b], 1u);
-        }
-        *abort_flag = 0;
-        tc5::mbar_fence_init();
-    }
-    __syncthreads();
-    pdk_pdl_launch_dependents();
-    pdk_pdl_wait();
-
-    // ---- B operand: token g, this warp's two units.  Lane (g, t) holds elements 4t..4t+3 and
-    // 16+4t..16+4t+3 of every 32-block: its share of the mma's B fragment.
-    const uint32_t g = lane >> 2, t = lane & 3u;
-    uint32_t bh[16][2], bl[16][2];
-    {
-        float* my_steps = steps + warp * 16u;
-        int* my_isum = isums + warp * 128u;
-        const size_t xoff = (size_t)(g < batch ? g : 0u) * in_dim + warp * 512u + 4u * t;
-#pragma unroll
-        for (uint32_t u = 0; u < 2u; ++u) {
-            float v[8][8];
-            float amax = 0.0f;
-#pragma unroll
-            for (uint32_t b = 0; b < 8u; ++b) {
-                const size_t at = xoff + u * 256u + b * 32u;
-                if (g >= batch) {
-#pragma unroll
-                    for (uint32_t i = 0; i < 8u; ++i) v[b][i] = 0.0f;
-                } else if (xq == nullptr) {
-                    const float4 a0 = *reinterpret_cast<const float4*>(x + at), a1 = *reinterpret_cast<const float4*>(x + at + 16u);
-                    v[b][0] = a0.x; v[b][1] = a0.y; v[b][2] = a0.z; v[b][3] = a0.w;
-                    v[b][4] = a1.x; v[b][5] = a1.y; v[b][6] = a1.z; v[b][7] = a1.w;
-                } else {
-                    const int q0 = *reinterpret_cast<const int*>(xq + at), q1 = *reinterpret_cast<const int*>(xq + at + 16u);
-                    const float sc = xq_scale[at >> 5];
-#pragma unroll
-                    for (uint32_t i = 0; i < 4u; ++i) {
-                        v[b][i] = (float)(int8_t)((q0 >> (8u * i)) & 0xff) * sc;
-                        v[b][4u + i] = (float)(int8_t)((q1 >> (8u * i)) & 0xff) * sc;
-                    }
-                }
-#pragma unroll
-                for (uint32_t i = 0; i < 8u; ++i) amax = fmaxf(amax, fabsf(v[b][i]));
-            }
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            // amax < 2^ex -> step 2^(ex-13): |q| <= 2^13, q = 256 * hi + lo with lo in [-128, 127]
-            float step = 1.0f, inv = 0.0f;
-            if (amax > 0.0f && amax < 3.0e38f) {
-                const int ex = max((int)(__float_as_uint(amax) >> 23) - 126, -110);
-                step = __uint_as_float((uint32_t)(ex + 114) << 23);
-                inv = __uint_as_float((uint32_t)(140 - ex) << 23);
-            }
-            if (t == 0u) my_steps[u * 8u + g] = step;
-#pragma unroll
-            for (uint32_t b = 0; b < 8u; ++b) {
-                int q[8], isum = 0;
-#pragma unroll
-                for (uint32_t i = 0; i < 8u; ++i) {
-                    q[i] = __float2int_rn(v[b][i] * inv);
-                    isum += q[i];
-                }
-                const uint32_t bb = u * 8u + b;
-                bl[bb][0] = __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
-                bl[bb][1] = __byte_perm(__byte_perm(q[4], q[5], 0x0040), __byte_perm(q[6], q[7], 0x0040), 0x5410);
-                bh[bb][0] = __byte_perm(__byte_perm(q[0] + 128, q[1] + 128, 0x0051), __byte_perm(q[2] + 128, q[3] + 128, 0x0051), 0x5410);
-                bh[bb][1] = __byte_perm(__byte_perm(q[4] + 128, q[5] + 128, 0x0051), __byte_perm(q[6] + 128, q[7] + 128, 0x0051), 0x5410);
-                isum += __shfl_xor_sync(0xffffffffu, isum, 1);
-                isum += __shfl_xor_sync(0xffffffffu, isum, 2);
-                if (t == 0u) my_isum[bb * 8u + g] = isum;
-            }
-        }
-        __syncwarp();
-    }
-    while (issued < D && issued < my_tiles) { issue(issued % D, issued); ++issued; }
-    const tc5::WaitCtx ctx{abort_flag, err};
-
-    const uint32_t m_row = (lane & 7u) + ((lane >> 3) & 1u) * 8u, m_half = lane >> 4;
-    uint32_t a_off[4];
-#pragma unroll
-    for (uint32_t c = 0; c < 4u; ++c) a_off[c] = swz(m_row, 2u * c + m_half);
-    const float* my_steps = steps + warp * 16u + 2u * t;
-    const int* my_isum = isums + warp * 128u + 2u * t;
-    const uint32_t rec_g = g * kRecRow, rec8 = 8u * kRecRow;
-
-    constexpr uint32_t kNone = 0xffffffffu;
-    uint32_t pend = kNone;
-    bool alive = true;
-    auto fold_tile = [&](uint32_t tl_f) {
-        const uint32_t rbf = tl_f % kBatchRedBufs;
-        const float* rbuf = red + (size_t)rbf * (W * 128u);
-        const uint32_t r = lane & 15u, c0 = (lane >> 4) * 4u;
-        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (uint32_t w = 0; w < W; ++w) {
-            const float4 p = *reinterpret_cast<const float4*>(rbuf + w * 128u + r * 8u + c0);
-            v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
-        }
-        __syncwarp();
-        if (lane == 0u) tc5::mbar_arrive(&red_free[rbf]);
-        const uint32_t row = (tile_lo + tl_f) * 16u + r;
-        if (row < out_dim) {
-#pragma unroll
-            for (uint32_t c = 0; c < 4u; ++c)
-                if (c0 + c < batch) y[(size_t)(c0 + c) * out_dim + row] = v[c];
-        }
-    };
-    auto poll_fold = [&](bool block) {
-        if (pend == kNone || !alive) return;
-        const uint32_t rbf = pend % kBatchRedBufs, ph = (pend / kBatchRedBufs) & 1u;
-        bool done;
-        if (block) {
-            alive = __all_sync(0xffffffffu, tc5::mbar_wait(&red_full[rbf], ph, ctx, kErrBatch4Fold, rbf));
-            done = alive;
-        } else {
-            done = __all_sync(0xffffffffu, tc5::mbar_try_wait(&red_full[rbf], ph));
-        }
-        if (done) {
-            fold_tile(pend);
-            pend = kNone;
-        }
-    };
-
-    uint32_t stage = 0, phase = 0, rb = 0, rb_phase = 0, owner = 0;
-    for (uint32_t tl = 0; tl < my_tiles; ++tl) {
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // (g, 2t) (g, 2t+1) (g+8, 2t) (g+8, 2t+1)
-        if (alive) alive = __all_sync(0xffffffffu, tc5::mbar_wait(my_full + stage, phase, ctx, kErrBatch4Full, stage));
-        if (alive) {
-            const uint32_t sd = tc5::smem_u32(my_data + stage * kStageData);
-            const uint8_t* sr = my_rec + stage * kStageRec + rec_g;
-#pragma unroll
-            for (uint32_t i = 0; i < 2u; ++i) {
-                // records of rows g and g + 8: {f16 d, f16 dmin, u8 sc[8], u8 m[8], pad4}
-                const uint2 r0 = *reinterpret_cast<const uint2*>(sr + i * Q4K::kRecBytes);
-                const uint2 r1 = *reinterpret_cast<const uint2*>(sr + i * Q4K::kRecBytes + 8u);
-                const uint32_t r2 = *reinterpret_cast<const uint32_t*>(sr + i * Q4K::kRecBytes + 16u);
-                const uint2 s0 = *reinterpret_cast<const uint2*>(sr + rec8 + i * Q4K::kRecBytes);
-                const uint2 s1 = *reinterpret_cast<const uint2*>(sr + rec8 + i * Q4K::kRecBytes + 8u);
-                const uint32_t s2 = *reinterpret_cast<const uint32_t*>(sr + rec8 + i * Q4K::kRecBytes + 16u);
-                // sc[0..7] = r0.y, r1.x; m[0..7] = r1.y, r2
-                const uint32_t sc_g[2] = {r0.y, r1.x}, m_g[2] = {r1.y, r2}, sc_h[2] = {s0.y, s1.x}, m_h[2] = {s1.y, s2};
-                int U[4] = {0, 0, 0, 0}, Mn[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (uint32_t gq = 0; gq < 4u; ++gq) {
-                    uint32_t a0, a1, a2, a3;
-                    ldmatrix_x4(sd + i * kUnitData + a_off[gq], a0, a1, a2, a3);
-#pragma unroll
-                    for (uint32_t hb = 0; hb < 2u; ++hb) {
-                        const uint32_t bb = 2u * gq + hb, b = i * 8u + bb;
-                        const uint32_t mask = hb ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
-                        int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
-                        mma_u8s8_nv(ch, a0 & mask, a1 & mask, a2 & mask, a3 & mask, bh[b][0], bh[b][1]);
-                        mma_u8s8_nv(cl, a0 & mask, a1 & mask, a2 & mask, a3 & mask, bl[b][0], bl[b][1]);
-                        const int sg = (int)((sc_g[bb >> 2] >> (8u * (bb & 3u))) & 0xffu), sh = (int)((sc_h[bb >> 2] >> (8u * (bb & 3u))) & 0xffu);
-                        const int mg = (int)((m_g[bb >> 2] >> (8u * (bb & 3u))) & 0xffu), mh = (int)((m_h[bb >> 2] >> (8u * (bb & 3u))) & 0xffu);
-                        const int2 is = *reinterpret_cast<const int2*>(my_isum + b * 8u);
-                        const int sft = hb ? 4 : 0;
-                        U[0] += sg * ((ch[0] * 256 + cl[0]) >> sft);
-                        U[1] += sg * ((ch[1] * 256 + cl[1]) >> sft);
-                        U[2] += sh * ((ch[2] * 256 + cl[2]) >> sft);
-                        U[3] += sh * ((ch[3] * 256 + cl[3]) >> sft);
-                        Mn[0] += mg * is.x;
-                        Mn[1] += mg * is.y;
-                        Mn[2] += mh * is.x;
-                        Mn[3] += mh * is.y;
-                    }
-                }
-                const __half2 dg = *reinterpret_cast<const __half2*>(&r0.x), dh = *reinterpret_cast<const __half2*>(&s0.x);
-                const float2 st = *reinterpret_cast<const float2*>(my_steps + i * 8u);
-                acc[0] += st.x * (__low2float(dg) * (float)U[0] - __high2float(dg) * (float)Mn[0]);
-                acc[1] += st.y * (__low2float(dg) * (float)U[1] - __high2float(dg) * (float)Mn[1]);
-                acc[2] += st.x * (__low2float(dh) * (float)U[2] - __high2float(dh) * (float)Mn[2]);
-                acc[3] += st.y * (__low2float(dh) * (float)U[3] - __high2float(dh) * (float)Mn[3]);
-            }
-            __syncwarp();
-            if (issued < my_tiles) { issue(issued % D, issued); ++issued; }
-        }
-        if (++stage == D) { stage = 0; phase ^= 1u; }
-
-        float* rbuf = red + (size_t)rb * (W * 128u);
-        if (alive && tl >= kBatchRedBufs)
-            alive = __all_sync(0xffffffffu, tc5::mbar_wait(&red_free[rb], rb_phase ^ 1u, ctx, kErrBatch4Free, rb));
-        if (alive) {
-            *reinterpret_cast<float2*>(rbuf + warp * 128u + g * 8u + 2u * t) = make_float2(acc[0], acc[1]);
-            *reinterpret_cast<float2*>(rbuf + warp * 128u + (g + 8u) * 8u + 2u * t) = make_float2(acc[2], acc[3]);
-            __syncwarp();
-            if (lane == 0u) tc5::mbar_arrive(&red_full[rb]);
-        }
-        if (owner == warp) {
-            poll_fold(true);
-            pend = tl;
-        }
-        poll_fold(false);
-        if (++owner == W) owner = 0;
-        if (++rb == kBatchRedBufs) { rb = 0; rb_phase ^= 1u; }
-    }
-    poll_fold(true);
-    if (!alive) {
-        const unsigned long long t0 = tc5::globaltimer_ns();
-        for (uint32_t s = 0; s < D && s < issued; ++s) {
-            const uint32_t n = issued - 1u - ((issued - 1u - s) % D);
-            while (!tc5::mbar_try_wait(my_full + s, (n / D) & 1u)) {
-                if (tc5::globaltimer_ns() - t0 > tc5::kWaitBudgetNs) {
-                    if (lane == 0u) tc5::report(err, kErrBatch4Drain, s);
-                    break;
-                }
-            }
-        }
-    }
-}
-
-bool make_batch_plan_q4k(uint32_t in_dim, BatchPlan& p) {
-    if (in_dim == 0u || (in_dim & 511u) != 0u) return false;
-    const uint32_t W = in_dim >> 9;
-    if (W < 4u || W > kMaxWarps) return false;
-    constexpr uint32_t kStage = 2u * kBoxBytes + 32u * Q4K::kRecBytes;
-    p.W = W;
-    p.off_steps = 0u;                                   // [kMaxWarps][16] floats, then [kMaxWarps][128] ints
-    p.off_red = kMaxWarps * 64u + kMaxWarps * 512u;
-    p.off_bar = p.off_red + kBatchRedBufs * W * 512u;
-    p.off_rec = (p.off_bar + (kMaxWarps * kMaxDepth + 2u * kBatchRedBufs) * 8u + 16u + 127u) & ~127u;
-    if (p.off_rec + 1024u + 2u * W * kStage > kSmemMax) return false;
-    p.D = (kSmemMax - p.off_rec - 1024u) / (W * kStage);
-    if (p.D > kMaxDepth) p.D = kMaxDepth;
-    p.off_data = (p.off_rec + W * p.D * 32u * Q4K::kRecBytes + 1023u) & ~1023u;
-    p.smem_bytes = p.off_data + W * p.D * 2u * kBoxBytes;
-    return p.smem_bytes <= kSmemMax && p.D >= 2u;
-}
-
 }  // namespace
 
 // gemv_i8.cu: the register-staged kernel
@@ -1120,33 +831,6 @@ int pdk_q8_0_gemv_i8(const void* data, const void* scale, const float* bias, con
                      uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
     const int rc = launch_ring<RQ80>(data, scale, bias, x, y, in_dim, out_dim, st);
     return rc != -1 ? rc : pdk_q8_0_gemv_i8_regs(data, scale, bias, x, y, in_dim, out_dim, st);
-}
-
-// Q4_K with 2..8 tokens (f32 activations, or int8 with per-32 scales): one weight pass.  -1 when the
-// shape is outside the plan (K / 512 warps, 4 .. 12) or batch > 8.
-int pdk_q4k_gemm_ring(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale, float* y,
-                      uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
-    if (force_regs() || batch > 8u || !pdk_aligned(scales, 16)) return -1;
-    BatchPlan pl;
-    if (!make_batch_plan_q4k(in_dim, pl)) return -1;
-    const MapEntry* maps = nullptr;
-    if (plane_maps<RQ4K>(data, scales, in_dim, out_dim, &maps) != 0) return -1;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        e = cudaFuncSetAttribute(gemm_ring_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax);
-        if (e != cudaSuccess) return (int)e;
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
-    }
-    unsigned int* err = pdk_error_word();
-    if (err == nullptr) return (int)cudaErrorUnknown;
-    const uint32_t n_tiles = (out_dim + 15u) / 16u;
-    uint32_t grid = (uint32_t)pdk_sm_count();
-    if (grid > n_tiles) grid = n_tiles;
-    return pdk_launch_pdl(gemm_ring_q4k_kernel, dim3(grid), dim3(pl.W * 32u), (size_t)pl.smem_bytes, st, maps->dmap, maps->rmap, x,
-                          xq, xq_scale, y, in_dim, out_dim, batch, pl, err);
 }
 
 // Q8_0 small batch: x f32 [batch][in_dim], y f32 [batch][out_dim]; tokens in groups of up to eight,

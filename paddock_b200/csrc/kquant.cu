@@ -39,8 +39,6 @@ int pdk_q5k_gemv_i8(const void* data, const void* scales, const float* x, float*
 int pdk_q6k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st);  // gemv_q6k.cu
 // q4k_batch_i8.cu: 1..16 tokens, f32 or int8 activations; -1 = shape outside its plan
-int pdk_q4k_gemm_ring(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale, float* y,
-                      uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
 int pdk_q4k_batch_i8(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale,
                      float* y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
 // q4k_tc5.cu: 1..32 tokens on tcgen05 (f16 weights); same operands and return convention
@@ -502,15 +500,6 @@ bool force_bf16_batch() {
     return v;
 }
 
-// PDK_Q4K_RING_BATCH=0 keeps 2..8 tokens on the register-staged batch kernel (A/B switch, read once).
-bool ring_batch_enabled() {
-    static const bool v = [] {
-        const char* e = getenv("PDK_Q4K_RING_BATCH");
-        return !(e && e[0] == '0');
-    }();
-    return v;
-}
-
 // From how many tokens on the tcgen05 kernel takes a call (PDK_Q4K_TC5_MIN, read once; 0 = never).
 uint32_t tc5_min_tokens() {
     static const uint32_t v = [] {
@@ -538,11 +527,6 @@ int small_batch(const void* data, const void* scales, const float* x, const int8
         if (tc5_min_tokens() != 0u && left >= tc5_min_tokens()) {
             take = left < 32u ? left : 32u;
             rc = pdk_q4k_tc5(data, scales, xb, qb, sb, yb, in_dim, out_dim, take, st);
-        }
-        if (rc == -1 && left <= 8u && ring_batch_enabled()) {
-            // up to eight tokens: the TMA ring with the tokens as mma columns (gemv_ring.cu)
-            take = left;
-            rc = pdk_q4k_gemm_ring(data, scales, xb, qb, sb, yb, in_dim, out_dim, take, st);
         }
         if (rc == -1) {
             take = left < 16u ? left : 16u;

@@ -226,10 +226,9 @@ def test_q4_k_batch_shapes(pack, k, n, batch):
 
 @pytest.mark.parametrize("k,n", [(5120, 1000), (6144, 72), (2048, 33)])
 @pytest.mark.parametrize("batch", [2, 3, 8])
-def test_q4_k_tokens_as_columns_on_the_ring(pack, k, n, batch):
-    """2 .. 8 tokens with K / 512 between 4 and 12: the ring kernel with the tokens as mma columns
-    (14-bit block-floating activations per 256 elements, integer accumulation over a super-block).
-    Ragged rows, an all-zero token, a token of tiny values; bit-identical from call to call."""
+def test_q4_k_two_to_eight_tokens(pack, k, n, batch):
+    """2 .. 8 tokens on the integer batch kernel: ragged rows, an all-zero token, a token of tiny
+    values; bit-identical from call to call."""
     w = oracle.fill_normal(n * k, seed_for(2, 970 + k), 0.02)
     x = oracle.fill_normal(batch * k, seed_for(2, 971 + batch), 1.0)
     x[:k] = 0.0
