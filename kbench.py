@@ -291,7 +291,7 @@ def bench_nvf4(ex, a):
 
 
 def bench_moe_other_pack(ex, a):
-    """Config 5 through another pack's int8-activation chain, the way the reference engine drives it
+    """The MXFP4 MoE block (128 experts, top-4) through another pack's int8-activation chain, the way the reference engine drives it
     (crates/paddock-engine/src/gpu_model/gpt_oss.rs:715-735, 2393-2440): gate|up interleaved once
     (slot 155), then per call top-k, align (32-row blocks), quantize_q8 (18), gate_up_mmq (88),
     down_mmq (89), slot_combine."""
@@ -419,7 +419,7 @@ def bench_moe(ex, a):
 
 
 def bench_moe_ep(ex, a):
-    """Config 5 expert-parallel: run under torchrun, one rank per GPU; experts and tokens split over the ranks."""
+    """The MXFP4 MoE block, expert-parallel: run under torchrun, one rank per GPU; experts and tokens split over the ranks."""
     import torch.distributed as dist
     from paddock_b200 import moe_ep, planes as P
     world, rank = dist.get_world_size(), dist.get_rank()

@@ -43,7 +43,7 @@ def test_q8_0_gemv_shapes(pack, k, n):
     assert rel_l2(y, y_cpu.astype(np.float64)) < 1e-4
 
 
-def test_q8_0_gemv_config1_rows(pack):
+def test_q8_0_gemv_k5120_rows(pack):
     """Q8_0 at the benchmark K=5120 with a 2048-row band of the 17408 rows."""
     k, n = 5120, 2048
     w = oracle.fill_normal(n * k, seed_for(1, 0), 0.02)
@@ -183,7 +183,7 @@ def test_gemv_ring_back_to_back_is_deterministic(pack):
 
 
 @pytest.mark.parametrize("batch", [1, 4, 16])
-def test_q4_k_small_batch_config2_band(pack, batch):
+def test_q4_k_small_batch_k5120_band(pack, batch):
     """Q4_K K=5120 at 1 / 4 / 16 tokens on a 1536-row band of N=25600."""
     k, n = 5120, 1536
     w = oracle.fill_normal(n * k, seed_for(2, 0), 0.02)
