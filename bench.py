@@ -241,6 +241,7 @@ def other_configs(ex, quick):
     cases += [(f"fp8_m4096_n{n}", kbench.Case("f8row_gemm", m=4096, n=n, iters=max(5, it // 3))) for n in (5120, 17408, 27648)]
     cases += [(f"nvf4_m{m}_n17408", kbench.Case("nvf4_gemm", m=m, graph=(m <= 64), iters=it if m <= 512 else max(5, it // 3)))
               for m in (1, 8, 64, 512, 8192)]
+    cases += [("nvf4_w4a16_gemv_n17408", kbench.Case("nvf4_gemv", graph=True, iters=it))]
     cases += [(f"moe_mxfp4_t{t}", kbench.Case("moe_mxfp4", m=t, graph=(t == 1), iters=it if t <= 64 else max(5, it // 3)))
               for t in (1, 64, 1024)]
     out = {}

@@ -423,6 +423,13 @@ int pdk_mxfp4_moe_gemm_tc5(const void* w0_data, const void* w0_sf, const void* w
 /* scale -> tiled records u8[n_expert][ceil(rows/128)][ceil(in_dim/256)][2048]; in_dim % 64 == 0 */
 int pdk_nvf4_moe_tile_scales(const void* scale, void* tiled, uint32_t rows, uint32_t in_dim, uint32_t n_expert,
                              void* stream);
+/* No counterpart in the reference.  Decode widths: moe_topk_batch + moe_align_bm + pdk_moe_prep_act_f4
+ * (mode 0) in one launch - rows * k <= 32 pairs, rows <= 8, n_expert <= 512, max_blocks <= 32.  Leaves
+ * the same idx / w / sorted_row / sorted_slot / block_expert and term rows as the three calls. */
+int pdk_moe_route_prep_f4(const void* logits, const void* router_bias, const void* x, void* idx, void* w,
+                          void* sorted_row, void* sorted_slot, void* block_expert, void* xq, void* xs, void* xstep,
+                          uint32_t n_expert, uint32_t k, uint32_t rows, uint32_t dim, uint32_t bm, uint32_t max_blocks,
+                          void* stream);
 /* pdk_moe_prep_act_f4 with the natural element order of NVFP4 planes.  mode 0 gather; mode 1 gated
  * unit (min(g, limit) * sigmoid(alpha * that)) * (clamp(u, +-limit) + up_add); mode 2 relu(x)^2. */
 int pdk_moe_prep_act_f4n(const void* x, const void* up, const void* sorted_row, const void* block_expert, void* xq,

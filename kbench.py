@@ -602,9 +602,16 @@ def bench_nvf4_gemv(ex, a):
            torch.randint(0x20, 0x48, (n * k // 16,), dtype=torch.uint8, device="cuda")) for _ in range(nc)]
     x = synth.bf16_round(synth.normal(k, 5, 1.0, "cuda"))
     y = torch.zeros(n, dtype=torch.float32, device="cuda")
-    sec = time_launches(lambda i: ex.pack.call("nvf4_gemv", ws[i % nc][0], ws[i % nc][1], None, x, y, 1.0, k, n,
-                                               stream=st), a.iters)
-    return sec, {"bound": "hbm", "bytes": nbytes + 4 + k * 4 + n * 4}
+    call = lambda i: ex.pack.call("nvf4_gemv", ws[i % nc][0], ws[i % nc][1], None, x, y, 1.0, k, n,
+                                  stream=torch.cuda.current_stream().cuda_stream)
+    sec = time_launches(call, a.iters)
+    # spot check: clone 0's first rows against an f32 product of the dequantized weights
+    call(0)
+    rows = min(n, 256)
+    wd = torch.empty(rows * k, dtype=torch.float32, device="cuda")
+    ex.pack.call("nvf4_dequant", ws[0][0], ws[0][1], 1.0, wd, k, rows, stream=st)
+    err = rel_err(y[:rows], wd.view(rows, k) @ x)
+    return sec, {"bound": "hbm", "bytes": nbytes + 4 + k * 4 + n * 4, "parity_rel_l2": err, "parity_ok": err < 1e-3}
 
 
 def bench_moe_nvf4(ex, a):

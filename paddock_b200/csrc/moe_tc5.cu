@@ -24,6 +24,7 @@
 //   (token, slot) rows and multiplied by the routing weight)  ->  pd_moe_slot_combine
 #include <cuda_fp8.h>
 
+#include "moe_route.cuh"
 #include "nvf4_tc5.cuh"
 
 namespace {
@@ -135,25 +136,9 @@ struct PrepArgs {
 // One CTA per block position.  Position (block b, token i) writes the four term rows
 // b*4*bm + k*bm + i.  A 16-element scale group of the tensor core's element order is the
 // two 8-runs (h*8 .. h*8+7) and (16 + h*8 .. 16 + h*8+7) of a 32-element block.
-__global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
-    // dependent launch: may start while the previous kernel of the stream drains; its results are awaited here
-    pdk_pdl_launch_dependents();
-    pdk_pdl_wait();
-    const uint32_t pos = blockIdx.x, b = pos / a.bm, i = pos % a.bm;
+__device__ __forceinline__ void prep_position(const PrepArgs& a, uint32_t pos, uint32_t src) {
+    const uint32_t b = pos / a.bm, i = pos % a.bm;
     const uint32_t tid = threadIdx.x;
-    uint32_t src;
-    if (a.mode == 3u) {
-        src = pos == 0u ? 0u : PDK_MOE_PAD;
-        if (tid == 0) {
-            a.tables[pos] = src;
-            if (pos == 0u) {
-                a.tables[a.bm] = 0u;  // block 0 belongs to expert 0
-                reinterpret_cast<float*>(a.tables)[a.bm + 1u] = a.table_scale2;
-            }
-        }
-    } else {
-        src = a.block_expert[b] == PDK_MOE_PAD ? PDK_MOE_PAD : a.sorted_row[pos];
-    }
     const uint32_t groups = a.dim >> 4, kh = a.dim >> 1;
     __shared__ float s_red[8];
     const bool pad = src == PDK_MOE_PAD;
@@ -288,6 +273,88 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
             xs_g[(rr & 31u) * 16u + (rr >> 5) * 4u] = (uint8_t)sb;
         }
     }
+}
+
+__global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
+    // dependent launch: may start while the previous kernel of the stream drains; its results are awaited here
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();
+    const uint32_t pos = blockIdx.x;
+    uint32_t src;
+    if (a.mode == 3u) {
+        src = pos == 0u ? 0u : PDK_MOE_PAD;
+        if (threadIdx.x == 0) {
+            a.tables[pos] = src;
+            if (pos == 0u) {
+                a.tables[a.bm] = 0u;  // block 0 belongs to expert 0
+                reinterpret_cast<float*>(a.tables)[a.bm + 1u] = a.table_scale2;
+            }
+        }
+    } else {
+        src = a.block_expert[pos / a.bm] == PDK_MOE_PAD ? PDK_MOE_PAD : a.sorted_row[pos];
+    }
+    prep_position(a, pos, src);
+}
+
+// Decode widths (rows * k <= 32 pairs): routing, alignment and the first activation preparation in
+// one launch.  Every CTA (one per block position, as above) routes the few tokens itself - a warp
+// per token for the top-k, one warp for the alignment of at most 32 pairs: rank inside an expert
+// from __match_any_sync, first block of an expert from the block counts of the lower experts - and
+// then prepares its own position; CTA 0 also leaves the routing tables in global memory for the
+// GEMMs and the combine.  The layout is moe_align's: blocks in ascending expert order, a block's
+// entries in ascending pair order, unused blocks marked PDK_MOE_PAD.
+struct RouteArgs {
+    const float* logits;     // [rows][n_expert]
+    const float* bias;       // [n_expert] or null
+    uint32_t* idx;           // out [rows][k]
+    float* w;                // out [rows][k]
+    uint32_t* sorted_row;    // out [max_blocks * bm]
+    uint32_t* sorted_slot;   // out [max_blocks * bm]
+    uint32_t* block_expert;  // out [max_blocks]
+    uint32_t rows, k, n_expert, max_blocks;
+};
+constexpr uint32_t kRouteMaxPos = 32u * 32u;
+
+__global__ void __launch_bounds__(256) moe_route_prep_f4_kernel(const PrepArgs a, const RouteArgs r) {
+    __shared__ uint32_t s_idx[32];
+    __shared__ float s_w[32];
+    __shared__ uint32_t s_row[kRouteMaxPos], s_slot[kRouteMaxPos], s_bexp[32];
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t npairs = r.rows * r.k, n_pos = r.max_blocks * a.bm;
+    if (warp < r.rows) moe_route::topk_warp(r.logits + (size_t)warp * r.n_expert, r.bias, r.n_expert, r.k, lane, s_idx + warp * r.k, s_w + warp * r.k);
+    for (uint32_t p = tid; p < n_pos; p += blockDim.x) { s_row[p] = PDK_MOE_PAD; s_slot[p] = 0u; }
+    if (tid < 32u) s_bexp[tid] = PDK_MOE_PAD;
+    __syncthreads();
+    if (warp == 0u) {
+        const bool valid = lane < npairs;
+        const uint32_t e = valid ? s_idx[lane] : 0xfffffff0u + lane;     // idle lanes: distinct keys that match nobody
+        const uint32_t grp = __match_any_sync(0xffffffffu, e);
+        const uint32_t rank = __popc(grp & ((1u << lane) - 1u)), cnt = __popc(grp);
+        const uint32_t nblk = (valid && rank == 0u) ? (cnt + a.bm - 1u) / a.bm : 0u;   // counted once, by the group's first lane
+        uint32_t first = 0u;
+        for (uint32_t q = 0; q < 32u; ++q) {
+            const uint32_t eq = __shfl_sync(0xffffffffu, e, q), nq = __shfl_sync(0xffffffffu, nblk, q);
+            if (eq < e) first += nq;
+        }
+        if (valid) {
+            const uint32_t blk = first + rank / a.bm, at = blk * a.bm + rank % a.bm;
+            if (blk < r.max_blocks) {
+                s_row[at] = lane / r.k;
+                s_slot[at] = lane % r.k;
+                if (rank % a.bm == 0u) s_bexp[blk] = e;
+            }
+        }
+    }
+    __syncthreads();
+    if (blockIdx.x == 0u) {
+        if (tid < npairs) { r.idx[tid] = s_idx[tid]; r.w[tid] = s_w[tid]; }
+        for (uint32_t p = tid; p < n_pos; p += blockDim.x) { r.sorted_row[p] = s_row[p]; r.sorted_slot[p] = s_slot[p]; }
+        if (tid < r.max_blocks) r.block_expert[tid] = s_bexp[tid];
+    }
+    const uint32_t pos = blockIdx.x;
+    prep_position(a, pos, s_bexp[pos / a.bm] == PDK_MOE_PAD ? PDK_MOE_PAD : s_row[pos]);
 }
 
 // ---------------------------------------------------------------- grouped GEMM
@@ -607,6 +674,30 @@ PDK_EXPORT int pdk_moe_prep_act_f4(const void* x, const void* up, const void* so
     if (mode > 1u) return cudaErrorInvalidValue;
     return prep_impl(x, up, sorted_row, block_expert, xq, xs, xstep, dim, bm, max_blocks, mode, 0u, alpha, limit, 1.0f,
                      stream);
+}
+
+// No counterpart in the reference.  moe_topk_batch + moe_align_bm + pdk_moe_prep_act_f4 (mode 0) in one
+// launch for decode widths: rows * k <= 32 pairs, rows <= 8, n_expert <= 512, max_blocks <= 32.  Writes
+// the same idx / w / sorted_row / sorted_slot / block_expert the three calls would, and the term rows.
+PDK_EXPORT int pdk_moe_route_prep_f4(const void* logits, const void* router_bias, const void* x, void* idx, void* w,
+                                     void* sorted_row, void* sorted_slot, void* block_expert, void* xq, void* xs, void* xstep,
+                                     uint32_t n_expert, uint32_t k, uint32_t rows, uint32_t dim, uint32_t bm,
+                                     uint32_t max_blocks, void* stream) {
+    if (rows == 0 || max_blocks == 0) return 0;
+    if (rows > 8u || k == 0 || k > 16u || rows * k > 32u || n_expert == 0 || n_expert > 512u || k > n_expert ||
+        max_blocks > 32u || (bm != 8u && bm != 32u) || max_blocks * bm > kRouteMaxPos || dim == 0 || (dim & 31u) != 0u)
+        return cudaErrorInvalidValue;
+    if (!pdk_aligned(x, 16) || !pdk_aligned(xq, 16) || !pdk_aligned(xs, 16) || !pdk_aligned(logits, 4)) return cudaErrorInvalidValue;
+    PrepArgs a{};
+    a.x = (const float*)x;
+    a.xq = (uint8_t*)xq; a.xs = (uint8_t*)xs; a.xstep = (float*)xstep;
+    a.dim = dim; a.bm = bm; a.mode = 0u; a.natural = 0u; a.alpha = 1.0f; a.limit = 0.0f; a.up_add = 0.0f;
+    RouteArgs r{};
+    r.logits = (const float*)logits; r.bias = (const float*)router_bias;
+    r.idx = (uint32_t*)idx; r.w = (float*)w;
+    r.sorted_row = (uint32_t*)sorted_row; r.sorted_slot = (uint32_t*)sorted_slot; r.block_expert = (uint32_t*)block_expert;
+    r.rows = rows; r.k = k; r.n_expert = n_expert; r.max_blocks = max_blocks;
+    return pdk_launch_pdl(moe_route_prep_f4_kernel, dim3(max_blocks * bm), dim3(256), 0, (cudaStream_t)stream, a, r);
 }
 
 // The same for NVFP4 expert planes: term rows packed in the natural element order (byte j = elements

@@ -128,6 +128,7 @@ _EXTRA_SIGS = {
     "pdk_tc5_issue_probe": "uup",
     "pdk_mxfp4_tc5_tile_scales": "pppuuu",
     "pdk_moe_prep_act_f4": "pppppppuuuuff",
+    "pdk_moe_route_prep_f4": "p" * 11 + "u" * 6,
     "pdk_mxfp4_moe_gemm_tc5": "p" * 17 + "u" * 7,
     "pdk_nvf4_moe_tile_scales": "ppuuu",
     "pdk_moe_prep_act_f4n": "pppppppuuuufff",

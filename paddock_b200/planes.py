@@ -182,18 +182,23 @@ def moe_mxfp4_experts(ex, planes, ws, x, rows, alpha=1.702, limit=7.0):
     return 5
 
 
-def moe_mxfp4_experts_tc5(ex, planes, ws, x, rows, alpha=1.702, limit=7.0):
+def moe_mxfp4_experts_tc5(ex, planes, ws, x, rows, alpha=1.702, limit=7.0, route=None):
     """moe_mxfp4_experts on the block-scaled tensor-core path (planes prepared with prepare_tc5):
     align -> term rows of x -> gate and up GEMM -> SwiGLU + term rows of h -> down GEMM scattered
-    into ws.part.  Five launches."""
+    into ws.part.  Five launches; with route = (router_logits, router_bias) at decode widths the
+    top-k, the alignment and the first preparation are one launch (four in all)."""
     st = _stream()
     c = ex.pack.call
     k, bm, t = ws.n_active, ws.bm, planes.tc5
     max_blocks = min(ws.max_blocks, min(rows * k, rows * k // bm + planes.n_expert))
-    c("moe_align_bm", ws.idx, ws.sorted_row, ws.sorted_slot, ws.block_expert, rows, k, planes.n_expert, bm,
-      max_blocks, stream=st)
-    c("pdk_moe_prep_act_f4", x, None, ws.sorted_row, ws.block_expert, ws.x4q, ws.x4s, ws.x4step, planes.embd, bm, max_blocks, 0,
-      alpha, limit, stream=st)
+    if route is not None:
+        c("pdk_moe_route_prep_f4", route[0], route[1], x, ws.idx, ws.w, ws.sorted_row, ws.sorted_slot, ws.block_expert,
+          ws.x4q, ws.x4s, ws.x4step, planes.n_expert, k, rows, planes.embd, bm, max_blocks, stream=st)
+    else:
+        c("moe_align_bm", ws.idx, ws.sorted_row, ws.sorted_slot, ws.block_expert, rows, k, planes.n_expert, bm,
+          max_blocks, stream=st)
+        c("pdk_moe_prep_act_f4", x, None, ws.sorted_row, ws.block_expert, ws.x4q, ws.x4s, ws.x4step, planes.embd, bm,
+          max_blocks, 0, alpha, limit, stream=st)
     c("pdk_mxfp4_moe_gemm_tc5", planes.gate.data, t["gate"][0], t["gate"][1], planes.gate_bias, ws.g_raw,
       planes.up.data, t["up"][0], t["up"][1], planes.up_bias, ws.u_raw, ws.x4q, ws.x4s, ws.x4step,
       ws.block_expert, ws.sorted_row, None, None, planes.embd, planes.ff, planes.n_expert, bm, max_blocks, k, 0,
@@ -213,6 +218,11 @@ def moe_mxfp4_forward(ex, planes, ws, x, router_logits, out, alpha=1.702, limit=
     st = _stream()
     c = ex.pack.call
     T, k = ws.tokens, ws.n_active
+    if planes.tc5 is not None and T <= 8 and T * k <= 32 and planes.n_expert <= 512 and ws.max_blocks <= 32:
+        # decode widths: routing, alignment and the first activation preparation in one launch
+        moe_mxfp4_experts_tc5(ex, planes, ws, x, T, alpha, limit, route=(router_logits, router_bias))
+        c("moe_slot_combine", ws.part, out, planes.embd, k, T, stream=st)
+        return 5
     c("moe_topk_batch", router_logits, router_bias, planes.n_expert, k, ws.idx, ws.w, T, stream=st)
     if planes.tc5 is not None:
         moe_mxfp4_experts_tc5(ex, planes, ws, x, T, alpha, limit)

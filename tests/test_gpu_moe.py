@@ -132,6 +132,51 @@ def test_moe_block_tensor_core_path_matches_oracle(pack, tokens, n_expert, k, em
     assert np.max(np.abs(y - ref)) < 1e-2 * np.max(np.abs(ref))
 
 
+@pytest.mark.parametrize("tokens,n_expert,k,embd,bm", [
+    (1, 128, 4, 2880, 8),      # one decode token of the benchmark layer
+    (8, 128, 4, 2880, 8),      # the widest the fused front takes (32 pairs)
+    (3, 16, 4, 2880, 8),
+    (5, 8, 2, 512, 8),
+    (2, 512, 8, 256, 16),
+])
+def test_route_and_prepare_in_one_launch_equals_the_three_calls(pack, tokens, n_expert, k, embd, bm):
+    """pdk_moe_route_prep_f4 leaves the tables and the term rows of moe_topk_batch + moe_align_bm +
+    pdk_moe_prep_act_f4, byte for byte (routing weights bit for bit)."""
+    ex = P.GpuExecutor(pack)
+    c = ex.pack.call
+    pairs = tokens * k
+    max_blocks = min(pairs, pairs // bm + n_expert)
+    nb = max_blocks * bm
+    x = dev_f32(oracle.bf16_round(oracle.fill_normal(tokens * embd, 1310 + tokens, 1.0)))
+    logits = dev_f32(oracle.fill_normal(tokens * n_expert, 1311 + tokens, 1.0))
+    rbias = dev_f32(oracle.fill_normal(n_expert, 1312, 0.1))
+
+    def buffers():
+        i32, u8, f32 = torch.int32, torch.uint8, torch.float32
+        return dict(idx=torch.full((pairs,), -1, dtype=i32, device="cuda"), w=torch.zeros(pairs, dtype=f32, device="cuda"),
+                    row=torch.full((nb,), -7, dtype=i32, device="cuda"), slot=torch.full((nb,), -7, dtype=i32, device="cuda"),
+                    blk=torch.full((max_blocks,), -7, dtype=i32, device="cuda"),
+                    q=torch.zeros(nb * 4 * embd // 2, dtype=u8, device="cuda"),
+                    s=torch.zeros(max_blocks * ((embd + 255) // 256) * 2048, dtype=u8, device="cuda"),
+                    step=torch.zeros(nb, dtype=f32, device="cuda"))
+    for bias in (None, rbias):
+        a, b = buffers(), buffers()
+        c("moe_topk_batch", logits, bias, n_expert, k, a["idx"], a["w"], tokens)
+        c("moe_align_bm", a["idx"], a["row"], a["slot"], a["blk"], tokens, k, n_expert, bm, max_blocks)
+        c("pdk_moe_prep_act_f4", x, None, a["row"], a["blk"], a["q"], a["s"], a["step"], embd, bm, max_blocks, 0, 1.702, 7.0)
+        c("pdk_moe_route_prep_f4", logits, bias, x, b["idx"], b["w"], b["row"], b["slot"], b["blk"], b["q"], b["s"],
+          b["step"], n_expert, k, tokens, embd, bm, max_blocks)
+        torch.cuda.synchronize()
+        assert pack.device_error() == 0
+        # positions of unused blocks: the alignment call leaves their row and slot entries unwritten
+        used = (a["blk"] != -1).repeat_interleave(bm)
+        for name in a:
+            ta, tb = a[name], b[name]
+            if name in ("row", "slot"):
+                ta, tb = ta[used], tb[used]
+            assert torch.equal(ta.view(torch.uint8), tb.view(torch.uint8)), name
+
+
 def test_slot_combine_fixed_order(pack):
     rows, k, embd = 7, 4, 64
     part = oracle.fill_normal(rows * k * embd, 820, 1.0)
