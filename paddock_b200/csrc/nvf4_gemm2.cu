@@ -1,19 +1,27 @@
 // nvf4_gemm2.cu - the NVFP4 x NVFP4 prefill GEMM of nvf4_gemm.cu on pairs of SMs.
 //
-// At prefill widths the one-SM kernel is paced by its L2 feed: 36 KB per 256-element K slab
-// (128 weight rows, 128 tokens, two 2 KB scale records) for four MMAs, and L2 delivers about
-// 116 GB/s to one SM.  Two CTAs of a cluster share a tile of 256 weight rows x 128 tokens
-// (tcgen05 cta_group::2): each loads its own 128 weight rows and their scale record, HALF of the
-// token tile's data, and the whole token tile's scale record (every tensor core needs all 128
-// tokens' scales) - 28 KB per slab - and the leader's instructions drive both tensor cores and
-// both CTAs' scale-cell copies.
+// At prefill widths this GEMM is bound by shared-memory bandwidth (128 bytes per cycle and SM),
+// which every byte crosses twice or more: written once by TMA, read by the tensor core once per
+// MMA that uses it, and a token box additionally by the partner SM's tensor core.  Two CTAs of a
+// cluster share a tile of 256 weight rows x BN tokens (tcgen05 cta_group::2): each loads its own
+// 128 weight rows and their scale record, HALF of the token tile's data, and the whole token
+// tile's scale records (every tensor core needs all tokens' scales); the leader's instructions
+// drive both tensor cores and both CTAs' scale-cell copies.  Per CTA and 256-element K slab:
+//   BN = 128   28 KB written + 4 MMAs x (4 KB weights + 2 KB own tokens + 2 KB served to the
+//              partner) read + 4 KB scale cells = 64 KB = 500 cycles for 256 tensor cycles
+//              (measured: 505 per slab; stages of two slabs, two accumulators)
+//   BN = 256   38 KB + 4 x (4 + 4 + 4) KB + 6 KB = 92 KB = 720 cycles for 512 tensor cycles
+//              (stages of one slab; ONE accumulator, two would fill tensor memory and leave the
+//              scale cells no room, so the tensor core idles from its last MMA of a tile until the
+//              epilogue has the accumulator in registers: measured 875 per slab overall)
+// The one-SM kernel of nvf4_gemm.cu (128 x 128, 36 KB written per slab) needs 600.
 //
 //   CTA r of a pair (r = rank in the cluster, 0 leads):
-//   warp 0      producer: four tiled TMA copies per slab (W box, X half box, two scale records
-//               as [8 rows][256 bytes] boxes), all counted on the LEADER's full barrier
-//   warp 1      leader only: per slab one asm block of 8 tcgen05.cp + 4 tcgen05.mma, cta_group::2;
-//               commits arrive on both CTAs' barriers
-//   warps 2..5  epilogue of the CTA's own 128 channels x 128 tokens
+//   warp 0      producer: tiled TMA copies per slab (W box, X half box, the scale records as
+//               [8 rows][256 bytes] boxes), all counted on the LEADER's full barrier
+//   warp 1      leader only: per slab one asm block of the scale-cell copies + 4 tcgen05.mma,
+//               cta_group::2; commits arrive on both CTAs' barriers
+//   warps 2..9  epilogue of the CTA's own 128 channels x BN tokens, two warps per 32 channels
 // The activation scales come pre-tiled (pd_nvf4_tc5_tile_scales over xs).  No multicast loads;
 // every wait is bounded.
 #include "nvf4_tc5.cuh"
@@ -23,18 +31,36 @@ namespace {
 using namespace nvf4tc5;
 using namespace tc5::pair;
 
-constexpr uint32_t BN = 128;                       // tokens per pair tile
-constexpr uint32_t BNH = 64;                       // tokens whose data one CTA loads
-constexpr uint32_t kBHalf = BNH * BKB;             // 8 KB
-constexpr uint32_t kSlab = kABytes + kBHalf + 2u * kSfBytes;   // 28 KB per CTA and slab
-constexpr uint32_t kStagesP = 3;
-// a stage = KS slabs: [W boxes][X half boxes][W scale records][X scale records]
-constexpr uint32_t kOffB = KS * kABytes, kOffSfa = kOffB + KS * kBHalf, kOffSfb = kOffSfa + KS * kSfBytes;
-constexpr uint32_t kStageBytes = kOffSfb + KS * kSfBytes;
-static_assert(kStageBytes == KS * kSlab, "stage layout");
-constexpr uint32_t kSfCol0 = 2u * BN, kSfCols = KS * 32u;
-// e2m1 x e2m1, UE4M3 scales, M = 256 over the pair
-constexpr uint32_t kIdescPair = (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | (((2u * BM) >> 4) << 24);
+template <uint32_t BN_>
+struct PairCfg {
+    static constexpr uint32_t BN = BN_;                  // tokens per pair tile
+    static constexpr uint32_t BNH = BN / 2u;             // tokens whose data one CTA loads
+    static constexpr uint32_t kRec = BN / 128u;          // token scale records per slab
+    static constexpr uint32_t kSlabs = BN == 128u ? 2u : 1u;   // slabs per pipeline stage
+    static constexpr uint32_t kStages = BN == 128u ? 3u : 4u;   // + the output tile: 200 / 216 KB
+    static constexpr uint32_t kAcc = BN == 128u ? 2u : 1u;     // accumulators in tensor memory
+    static constexpr uint32_t kBHalf = BNH * BKB;
+    // a stage: [W boxes][X half boxes][W scale records][X scale records]
+    static constexpr uint32_t kOffB = kSlabs * kABytes, kOffSfa = kOffB + kSlabs * kBHalf;
+    static constexpr uint32_t kOffSfb = kOffSfa + kSlabs * kSfBytes;
+    static constexpr uint32_t kStageBytes = kOffSfb + kSlabs * kRec * kSfBytes;
+    // tensor-memory columns: the accumulators, then per stage and slab 4 steps x (4 + 4 * kRec) scale columns
+    static constexpr uint32_t kSfCol0 = kAcc * BN, kSlabCols = 16u + 16u * kRec, kSfCols = kSlabs * kSlabCols;
+    static_assert(kSfCol0 + kStages * kSfCols <= kTmemCols, "tensor memory");
+    // e2m1 x e2m1, UE4M3 scales, M = 256 over the pair
+    static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | (((2u * BM) >> 4) << 24);
+};
+constexpr uint32_t kMaxStagesP = 5;
+constexpr uint32_t kThreadsP = 320;   // producer, issuer, 8 epilogue warps (two per lane quarter)
+
+struct SharedP {
+    uint64_t full[kMaxStagesP];
+    uint64_t empty[kMaxStagesP];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
 
 // slab_nvf4 (nvf4_tc5.cuh) for a pair of CTAs: the copies and the MMAs act in both
 __device__ __forceinline__ void slab_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -59,6 +85,31 @@ __device__ __forceinline__ void slab_nvf4_pair(uint32_t d_tmem, uint64_t a_desc,
 #undef PDK_NV4_STEP2
 }
 
+// The same for 256 tokens: the token scales are two records (tokens 0..127, 128..255), two cells of four
+// columns side by side per step.
+__device__ __forceinline__ void slab_nvf4_pair256(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t acc_first, uint32_t sfa_t, uint32_t sfb_t, uint32_t sfa_smem,
+                                                  uint32_t sfb_smem) {
+    const uint64_t cell_a = (uint64_t)((sfa_smem >> 4) & 0x3FFFu) | ((uint64_t)1u << 16) | ((uint64_t)8u << 32);
+    const uint64_t cell_b = (uint64_t)((sfb_smem >> 4) & 0x3FFFu) | ((uint64_t)1u << 16) | ((uint64_t)8u << 32);
+    const uint64_t cell_b2 = (uint64_t)(((sfb_smem + kSfBytes) >> 4) & 0x3FFFu) | ((uint64_t)1u << 16) | ((uint64_t)8u << 32);
+#define PDK_NV4_STEP3(J, PRED)                                                                                        \
+    "add.u64 a, %1, " #J "*2;\n\tadd.u64 b, %2, " #J "*2;\n\tadd.u32 sa, %5, " #J "*4;\n\tadd.u32 sb, %6, " #J "*8;\n\t" \
+    "add.u32 sc, sb, 4;\n\tadd.u64 ca, %7, " #J "*32;\n\tadd.u64 cb, %8, " #J "*32;\n\tadd.u64 cc, %9, " #J "*32;\n\t"   \
+    "@e tcgen05.cp.cta_group::2.32x128b.warpx4 [sa], ca;\n\t@e tcgen05.cp.cta_group::2.32x128b.warpx4 [sb], cb;\n\t" \
+    "@e tcgen05.cp.cta_group::2.32x128b.warpx4 [sc], cc;\n\t"                                                        \
+    "@e tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], a, b, %3, [sa], [sb], " PRED ";\n\t"
+    asm volatile(
+        "{\n\t.reg .pred e, p, q;\n\t.reg .b64 a, b, ca, cb, cc;\n\t.reg .b32 sa, sb, sc;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        PDK_NV4_STEP3(0, "p") PDK_NV4_STEP3(1, "q") PDK_NV4_STEP3(2, "q") PDK_NV4_STEP3(3, "q") "}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc_first), "r"(sfa_t), "r"(sfb_t), "l"(cell_a), "l"(cell_b), "l"(cell_b2)
+        : "memory");
+#undef PDK_NV4_STEP3
+}
+
 template <typename TO>
 __device__ __forceinline__ void store_one2(TO* p, float v);
 template <>
@@ -74,36 +125,41 @@ __device__ __forceinline__ void store_smem2<float>(float* p, float v) { *p = v; 
 template <>
 __device__ __forceinline__ void store_smem2<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-template <typename TO>
-__global__ void __launch_bounds__(kThreads, 1)
+// A = the operand whose rows are the accumulator's lanes (256 per pair tile: the weights), B = the one whose
+// rows are its columns (BN per pair tile: the tokens).  (Tokens as lanes, each epilogue thread writing 16-byte
+// pieces of its token's row straight to global memory, measured 14 % slower at 8192 tokens.)
+template <typename TO, uint32_t BN>
+__global__ void __launch_bounds__(kThreadsP, 1)
 nvf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                       const __grid_constant__ CUtensorMap tmap_wsf, const __grid_constant__ CUtensorMap tmap_xsf,
-                      const float* __restrict__ bias, TO* __restrict__ y, float scale2, uint32_t in_dim, uint32_t out_dim,
-                      uint32_t batch, unsigned int* err_word, const __grid_constant__ CUtensorMap tmap_y,
+                      const float* __restrict__ bias, TO* __restrict__ y, float scale2, uint32_t in_dim, uint32_t a_rows,
+                      uint32_t b_rows, unsigned int* err_word, const __grid_constant__ CUtensorMap tmap_y,
                       const uint32_t tma_out) {
+    using C = PairCfg<BN>;
+    constexpr uint32_t kSlabs = C::kSlabs, kStages = C::kStages, kStageBytes = C::kStageBytes, kAcc = C::kAcc;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
-    Shared* sh = reinterpret_cast<Shared*>(tiles + kStagesP * kStageBytes);
-    TO* stage_out = reinterpret_cast<TO*>(tiles + kStagesP * kStageBytes + 128u);   // [32 tokens][128 channels]
-    static_assert(sizeof(Shared) <= 128u, "control block");
+    SharedP* sh = reinterpret_cast<SharedP*>(tiles + kStages * kStageBytes);
+    uint8_t* stage_out = tiles + kStages * kStageBytes + 128u;   // [BN tokens][128 channels] bf16 (tensor-map output only)
+    static_assert(sizeof(SharedP) <= 128u, "control block");
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0u;
     const uint32_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const uint32_t tiles_w = (out_dim + 2u * BM - 1u) / (2u * BM), tiles_t = (batch + BN - 1u) / BN;
-    const uint32_t n_tiles = tiles_w * tiles_t;
+    const uint32_t tiles_a = (a_rows + 2u * BM - 1u) / (2u * BM), tiles_b = (b_rows + BN - 1u) / BN;
+    const uint32_t n_tiles = tiles_a * tiles_b;
     const uint32_t num_kb = in_dim >> 8;
-    const uint32_t num_ks = (num_kb + KS - 1u) / KS;
+    const uint32_t num_ks = (num_kb + kSlabs - 1u) / kSlabs;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < kStagesP; ++s) {
+        for (uint32_t s = 0; s < kStages; ++s) {
             tc5::mbar_init(&sh->full[s], 1);
             tc5::mbar_init(&sh->empty[s], 1);
         }
         for (uint32_t b = 0; b < 2; ++b) {
             tc5::mbar_init(&sh->tmem_full[b], 1);
-            tc5::mbar_init(&sh->tmem_empty[b], 8);   // in the leader: 4 epilogue warps of each CTA
+            tc5::mbar_init(&sh->tmem_empty[b], 16);   // in the leader: 8 epilogue warps of each CTA
         }
         sh->abort_flag = 0;
         tc5::mbar_fence_init();
@@ -130,27 +186,32 @@ nvf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         bool ok = true;
         pdk_pdl_wait();
         for (uint32_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-            // token tile fastest: the pairs of a wave share a few weight tiles
-            const uint32_t tile_w = (tile / tiles_t) * 2u + rank, tile_t = tile % tiles_t;
+            // B tile fastest: the pairs of a wave share a few A tiles
+            const uint32_t tile_a = (tile / tiles_b) * 2u + rank, tile_b = tile % tiles_b;
             for (uint32_t ks = 0; ks < num_ks; ++ks) {
                 ok = tc5::mbar_wait(&sh->empty[stage], phase ^ 1u, ctx, tc5::kErrEmptyWait, stage);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 uint8_t* a = tiles + stage * kStageBytes;
-                const uint32_t kb0 = ks * KS, nsl = min(KS, num_kb - kb0);
-                // the scale boxes always span KS records (rows past the plane read as zero and count)
-                if (leader) tc5::mbar_arrive_expect_tx_elect(&sh->full[stage], 2u * (nsl * (kABytes + kBHalf) + 2u * KS * kSfBytes));
+                const uint32_t kb0 = ks * kSlabs, nsl = min(kSlabs, num_kb - kb0);
+                // the scale boxes always span kSlabs records (rows past the plane read as zero and count)
+                if (leader)
+                    tc5::mbar_arrive_expect_tx_elect(&sh->full[stage],
+                                                     2u * (nsl * (kABytes + C::kBHalf) + (1u + C::kRec) * kSlabs * kSfBytes));
 #pragma unroll
-                for (uint32_t u = 0; u < KS; ++u)
+                for (uint32_t u = 0; u < kSlabs; ++u)
                     if (u < nsl) {
                         tma_load_2d_pair_elect(a + u * kABytes, &tmap_w, &sh->full[stage], (int32_t)((kb0 + u) * BKB),
-                                               (int32_t)(tile_w * BM));
-                        tma_load_2d_pair_elect(a + kOffB + u * kBHalf, &tmap_x, &sh->full[stage], (int32_t)((kb0 + u) * BKB),
-                                               (int32_t)(tile_t * BN + rank * BNH));
+                                               (int32_t)(tile_a * BM));
+                        tma_load_2d_pair_elect(a + C::kOffB + u * C::kBHalf, &tmap_x, &sh->full[stage], (int32_t)((kb0 + u) * BKB),
+                                               (int32_t)(tile_b * BN + rank * C::BNH));
                     }
-                tma_load_2d_pair_elect(a + kOffSfa, &tmap_wsf, &sh->full[stage], 0, (int32_t)((tile_w * num_kb + kb0) * 8u));
-                tma_load_2d_pair_elect(a + kOffSfb, &tmap_xsf, &sh->full[stage], 0, (int32_t)((tile_t * num_kb + kb0) * 8u));
-                if (++stage == kStagesP) { stage = 0; phase ^= 1u; }
+                tma_load_2d_pair_elect(a + C::kOffSfa, &tmap_wsf, &sh->full[stage], 0, (int32_t)((tile_a * num_kb + kb0) * 8u));
+#pragma unroll
+                for (uint32_t j = 0; j < C::kRec; ++j)   // one box of kSlabs records per 128 tokens
+                    tma_load_2d_pair_elect(a + C::kOffSfb + j * kSlabs * kSfBytes, &tmap_xsf, &sh->full[stage], 0,
+                                           (int32_t)(((tile_b * C::kRec + j) * num_kb + kb0) * 8u));
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
         if (!ok && lane == 0) {
@@ -162,7 +223,7 @@ nvf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             uint32_t stage = 0, phase = 0, iter = 0;
             bool ok = true;
             for (uint32_t tile = pair; tile < n_tiles && ok; tile += n_pairs, ++iter) {
-                const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
+                const uint32_t buf = iter % kAcc, aphase = (iter / kAcc) & 1u;
                 ok = tc5::mbar_wait(&sh->tmem_empty[buf], aphase ^ 1u, ctx, tc5::kErrTmemEmptyWait, buf);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -174,63 +235,88 @@ nvf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                     if (!ok) break;
                     tc5::fence_after_sync();
                     const uint32_t a_addr = tc5::smem_u32(tiles + stage * kStageBytes);
-                    const uint32_t nsl = min(KS, num_kb - ks * KS);
+                    const uint32_t nsl = min(kSlabs, num_kb - ks * kSlabs);
 #pragma unroll
-                    for (uint32_t u = 0; u < KS; ++u) {
+                    for (uint32_t u = 0; u < kSlabs; ++u) {
                         if (u >= nsl) break;
-                        const uint32_t sfa_t = tmem_base + kSfCol0 + stage * kSfCols + u * 32u, sfb_t = sfa_t + 16u;
-                        slab_nvf4_pair(d_tmem, tc5::smem_desc_sw128(a_addr + u * kABytes),
-                                       tc5::smem_desc_sw128(a_addr + kOffB + u * kBHalf), kIdescPair, (ks | u) != 0u, sfa_t, sfb_t,
-                                       a_addr + kOffSfa + u * kSfBytes, a_addr + kOffSfb + u * kSfBytes, 4u);
+                        const uint32_t sfa_t = tmem_base + C::kSfCol0 + stage * C::kSfCols + u * C::kSlabCols, sfb_t = sfa_t + 16u;
+                        const uint64_t a_desc = tc5::smem_desc_sw128(a_addr + u * kABytes);
+                        const uint64_t b_desc = tc5::smem_desc_sw128(a_addr + C::kOffB + u * C::kBHalf);
+                        if constexpr (BN == 128u)
+                            slab_nvf4_pair(d_tmem, a_desc, b_desc, C::kIdesc, (ks | u) != 0u, sfa_t, sfb_t,
+                                           a_addr + C::kOffSfa + u * kSfBytes, a_addr + C::kOffSfb + u * kSfBytes, 4u);
+                        else
+                            slab_nvf4_pair256(d_tmem, a_desc, b_desc, C::kIdesc, (ks | u) != 0u, sfa_t, sfb_t,
+                                              a_addr + C::kOffSfa + u * kSfBytes, a_addr + C::kOffSfb + u * kSfBytes);
                     }
                     mma_commit_pair_elect(&sh->empty[stage]);
-                    if (++stage == kStagesP) { stage = 0; phase ^= 1u; }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) mma_commit_pair_elect(&sh->tmem_full[buf]);
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own 128 channels)
-        const uint32_t quarter = warp & 3u;
+        // The accumulator is read 64 token columns at a time and handed back to the MMA issuer as soon
+        // as the last columns sit in registers; with a bf16 tensor map the whole [BN tokens][128 channels]
+        // tile is staged in shared memory and leaves as ONE tiled store (one proxy fence and two
+        // barriers per tile; the store drains while the next tile accumulates).
+        const uint32_t quarter = warp & 3u, half = (warp - 2u) >> 2;   // this warp: every second group of 64 tokens
         uint32_t iter = 0;
         bool ok = true;
+        TO* out_box = reinterpret_cast<TO*>(stage_out);
         pdk_pdl_wait();
         for (uint32_t tile = pair; tile < n_tiles && ok; tile += n_pairs, ++iter) {
-            const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
-            const uint32_t w0 = ((tile / tiles_t) * 2u + rank) * BM, t0 = (tile % tiles_t) * BN;
+            const uint32_t buf = iter % kAcc, aphase = (iter / kAcc) & 1u;
+            const uint32_t a0 = ((tile / tiles_b) * 2u + rank) * BM, b0 = (tile % tiles_b) * BN;
+            const uint32_t n = a0 + quarter * 32u + lane;
+            const uint32_t n_b = min(BN, b_rows - b0), n_grp = (n_b + 63u) / 64u;
+            const float b = (bias != nullptr && n < a_rows) ? bias[n] : 0.0f;
+            if (tma_out) {   // the previous tile's store has read the box
+                if (threadIdx.x == 64u) tc5::tma_store_wait_read();
+                asm volatile("bar.sync 2, 256;" ::: "memory");
+            }
             ok = tc5::mbar_wait(&sh->tmem_full[buf], aphase, ctx, tc5::kErrTmemFullWait, buf);
             if (!ok) break;
             tc5::fence_after_sync();
-            const uint32_t n = w0 + quarter * 32u + lane;
-            const float b = (bias != nullptr && n < out_dim) ? bias[n] : 0.0f;
-            const uint32_t n_tok = min(BN, batch - t0);
+            if (half >= n_grp) {   // a ragged tile with nothing for this warp to read
+                tc5::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(&sh->tmem_empty[buf]);
+            }
 #pragma unroll 1
-            for (uint32_t c = 0; c * 32u < n_tok; ++c) {
-                uint32_t r[32];
-                tc5::tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + buf * BN + c * 32u, r);
+            for (uint32_t g = half; g < n_grp; g += 2u) {
+                uint32_t ra[32], rb[32];
+                const uint32_t col = tmem_base + ((quarter * 32u) << 16) + buf * BN + g * 64u;
+                tc5::tmem_ld_32x32(col, ra);
+                tc5::tmem_ld_32x32(col + 32u, rb);
                 tc5::tmem_ld_wait();
-                if (tma_out) {
-                    if (threadIdx.x == 64u) tc5::tma_store_wait_read();
-                    asm volatile("bar.sync 2, 128;" ::: "memory");
-#pragma unroll
-                    for (uint32_t i = 0; i < 32u; ++i)
-                        store_smem2<TO>(stage_out + i * BM + quarter * 32u + lane, fmaf(__uint_as_float(r[i]), scale2, b));
-                    fence_proxy_async_smem();
-                    asm volatile("bar.sync 2, 128;" ::: "memory");
-                    if (threadIdx.x == 64u && w0 < out_dim) tc5::tma_store_2d(&tmap_y, stage_out, (int32_t)w0, (int32_t)(t0 + c * 32u));
-                    continue;
+                if (g + 2u >= n_grp) {   // every column this warp reads is in registers
+                    tc5::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_leader(&sh->tmem_empty[buf]);
                 }
-                if (n < out_dim) {
+                if (tma_out) {
 #pragma unroll
-                    for (uint32_t i = 0; i < 32u; ++i) {
-                        const uint32_t t = c * 32u + i;
-                        if (t < n_tok) store_one2<TO>(y + (size_t)(t0 + t) * out_dim + n, fmaf(__uint_as_float(r[i]), scale2, b));
+                    for (uint32_t i = 0; i < 64u; ++i)
+                        store_smem2<TO>(out_box + (g * 64u + i) * BM + quarter * 32u + lane,
+                                        fmaf(__uint_as_float(i < 32u ? ra[i & 31u] : rb[i & 31u]), scale2, b));
+                } else if (n < a_rows) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 64u; ++i) {
+                        const uint32_t t = g * 64u + i;
+                        if (t < n_b)
+                            store_one2<TO>(y + (size_t)(b0 + t) * a_rows + n,
+                                           fmaf(__uint_as_float(i < 32u ? ra[i & 31u] : rb[i & 31u]), scale2, b));
                     }
                 }
             }
-            tc5::fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_leader(&sh->tmem_empty[buf]);
+            if (tma_out) {
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 2, 256;" ::: "memory");
+                // rows past the batch (stale rows of a ragged tile) and channels past a_rows are clipped
+                if (threadIdx.x == 64u && a0 < a_rows) tc5::tma_store_2d(&tmap_y, out_box, (int32_t)a0, (int32_t)b0);
+            }
         }
     }
 
@@ -244,34 +330,38 @@ nvf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     }
 }
 
-template <typename TO>
+template <typename TO, uint32_t BN>
 int launch_pair(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs_tiled, void* y,
                 float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
-    CUtensorMap tw, tx, twsf, txsf;
+    using C = PairCfg<BN>;
+    CUtensorMap ta, tb, tasf, tbsf;
     const uint32_t kbytes = in_dim >> 1, num_kb = in_dim >> 8;
-    if (int rc = pdk_make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, data, kbytes, out_dim, kbytes, BKB, BM)) return rc;
-    if (int rc = pdk_make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, kbytes, batch, kbytes, BKB, BNH)) return rc;
-    // scale records (2048 bytes each) as rows of 256 bytes, eight per record; a box spans KS records
-    const uint64_t w_recs = (uint64_t)((out_dim + BM - 1u) / BM) * num_kb, x_recs = (uint64_t)((batch + BN - 1u) / BN) * num_kb;
-    if (int rc = pdk_make_tmap_2d_dense(&twsf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, scale_tiled, 256u, w_recs * 8u, 256u, 256u, 8u * KS))
+    const void *a_data = data, *b_data = xq, *a_sf = scale_tiled, *b_sf = xs_tiled;
+    const uint32_t a_rows = out_dim, b_rows = batch;
+    if (int rc = pdk_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_data, kbytes, a_rows, kbytes, BKB, BM)) return rc;
+    if (int rc = pdk_make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_data, kbytes, b_rows, kbytes, BKB, C::BNH)) return rc;
+    // scale records (2048 bytes each, one per 128 rows and slab) as rows of 256 bytes, eight per record; a box
+    // spans a stage's records
+    const uint64_t a_recs = (uint64_t)((a_rows + 127u) / 128u) * num_kb, b_recs = (uint64_t)((b_rows + 127u) / 128u) * num_kb;
+    if (int rc = pdk_make_tmap_2d_dense(&tasf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_sf, 256u, a_recs * 8u, 256u, 256u, 8u * C::kSlabs))
         return rc;
-    if (int rc = pdk_make_tmap_2d_dense(&txsf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xs_tiled, 256u, x_recs * 8u, 256u, 256u, 8u * KS))
+    if (int rc = pdk_make_tmap_2d_dense(&tbsf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_sf, 256u, b_recs * 8u, 256u, 256u, 8u * C::kSlabs))
         return rc;
-    CUtensorMap ty = tw;
+    CUtensorMap ty = ta;
     uint32_t tma_out = 0u;
     if (sizeof(TO) == 2u && pdk_aligned(y, 16) && (out_dim & 7u) == 0u &&
-        pdk_make_tmap_2d_dense(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, out_dim, batch, (uint64_t)out_dim * 2u, BM, 32u) == 0)
+        pdk_make_tmap_2d_dense(&ty, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, out_dim, batch, (uint64_t)out_dim * 2u, BM, BN) == 0)
         tma_out = 1u;
-    const size_t smem = (size_t)kStagesP * kStageBytes + 128u + 32u * BM * sizeof(TO) + 1024u;
-    auto kern = nvf4_gemm_pair_kernel<TO>;
+    const size_t smem = (size_t)C::kStages * C::kStageBytes + 128u + (tma_out ? BN * BM * sizeof(TO) : 0u) + 1024u;
+    auto kern = nvf4_gemm_pair_kernel<TO, BN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    const uint32_t n_tiles = ((out_dim + 2u * BM - 1u) / (2u * BM)) * ((batch + BN - 1u) / BN);
+    const uint32_t n_tiles = ((a_rows + 2u * BM - 1u) / (2u * BM)) * ((b_rows + BN - 1u) / BN);
     uint32_t pairs = (uint32_t)pdk_sm_count() / 2u;
     if (pairs > n_tiles) pairs = n_tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2u * pairs);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(kThreadsP);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -283,9 +373,22 @@ int launch_pair(const void* data, const void* scale_tiled, const void* bias, con
     attr[1].val.programmaticStreamSerializationAllowed = pdk_pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    e = cudaLaunchKernelEx(&cfg, kern, tw, tx, twsf, txsf, (const float*)bias, (TO*)y, scale2, in_dim, out_dim, batch,
+    e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tasf, tbsf, (const float*)bias, (TO*)y, scale2, in_dim, a_rows, b_rows,
                            pdk_error_word(), ty, tma_out);
     return e == cudaSuccess ? pdk_launch_status() : (int)e;
+}
+
+// 256-token tiles once every pair of SMs gets at least one of them (PDK_NVF4_PAIR_BN=128 / 256 forces
+// one; read per call: a launch of tens to hundreds of microseconds).
+template <typename TO>
+int launch_pair_any(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs_tiled, void* y,
+                    float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
+    const char* env = getenv("PDK_NVF4_PAIR_BN");
+    const int forced = env ? atoi(env) : 0;
+    const uint32_t tiles256 = ((out_dim + 2u * BM - 1u) / (2u * BM)) * ((batch + 255u) / 256u);
+    const bool wide = forced == 256 || (forced != 128 && tiles256 >= (uint32_t)pdk_sm_count() / 2u);
+    if (wide) return launch_pair<TO, 256u>(data, scale_tiled, bias, xq, xs_tiled, y, scale2, in_dim, out_dim, batch, st);
+    return launch_pair<TO, 128u>(data, scale_tiled, bias, xq, xs_tiled, y, scale2, in_dim, out_dim, batch, st);
 }
 
 }  // namespace
@@ -294,9 +397,9 @@ int launch_pair(const void* data, const void* scale_tiled, const void* bias, con
 // layout (one record per 128 tokens and slab).
 int pdk_nvf4_gemm_pair_f32(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs_tiled,
                            void* y, float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
-    return launch_pair<float>(data, scale_tiled, bias, xq, xs_tiled, y, scale2, in_dim, out_dim, batch, st);
+    return launch_pair_any<float>(data, scale_tiled, bias, xq, xs_tiled, y, scale2, in_dim, out_dim, batch, st);
 }
 int pdk_nvf4_gemm_pair_bf16(const void* data, const void* scale_tiled, const void* bias, const void* xq, const void* xs_tiled,
                             void* y, float scale2, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st) {
-    return launch_pair<__nv_bfloat16>(data, scale_tiled, bias, xq, xs_tiled, y, scale2, in_dim, out_dim, batch, st);
+    return launch_pair_any<__nv_bfloat16>(data, scale_tiled, bias, xq, xs_tiled, y, scale2, in_dim, out_dim, batch, st);
 }

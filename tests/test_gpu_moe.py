@@ -137,7 +137,7 @@ def test_moe_block_tensor_core_path_matches_oracle(pack, tokens, n_expert, k, em
     (8, 128, 4, 2880, 8),      # the widest the fused front takes (32 pairs)
     (3, 16, 4, 2880, 8),
     (5, 8, 2, 512, 8),
-    (2, 512, 8, 256, 16),
+    (2, 512, 8, 256, 32),
 ])
 def test_route_and_prepare_in_one_launch_equals_the_three_calls(pack, tokens, n_expert, k, embd, bm):
     """pdk_moe_route_prep_f4 leaves the tables and the term rows of moe_topk_batch + moe_align_bm +

@@ -85,6 +85,20 @@ def test_tile_scales_layout(pack):
                                    (1024, 2560, 512), (1000, 2440, 768), (200, 9600, 256)])
 @pytest.mark.parametrize("out", ["f32", "bf16"])
 def test_nvf4_gemm_w4a4(pack, m, n, k, out):
+    check_nvf4_gemm_w4a4(pack, m, n, k, out)
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 2560, 512), (1000, 2440, 768), (200, 9600, 256), (300, 2560, 1280), (257, 2304, 256)])
+@pytest.mark.parametrize("out", ["f32", "bf16"])
+@pytest.mark.parametrize("tile", [128, 256])
+def test_nvf4_gemm_w4a4_pair_kernel_forms(pack, monkeypatch, m, n, k, out, tile):
+    """Both token-tile widths of the pair kernel on the same shapes (whole and ragged tiles; an odd
+    count of 128-token scale records)."""
+    monkeypatch.setenv("PDK_NVF4_PAIR_BN", str(tile))
+    check_nvf4_gemm_w4a4(pack, m, n, k, out)
+
+
+def check_nvf4_gemm_w4a4(pack, m, n, k, out):
     q, s, scale2 = nvf4_weights(n, k, 620 + n + m)
     x = oracle.bf16_round(oracle.fill_normal(m * k, 621 + m, 1.0))
     d_x = dev_f32(x)
