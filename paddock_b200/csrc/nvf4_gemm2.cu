@@ -14,7 +14,7 @@
 //              (stages of one slab; ONE accumulator, two would fill tensor memory and leave the
 //              scale cells no room, so the tensor core idles from its last MMA of a tile until the
 //              epilogue has the accumulator in registers: measured 875 per slab overall)
-// The one-SM kernel of nvf4_gemm.cu (128 x 128, 36 KB written per slab) needs 600.
+// The one-SM kernel of nvf4_gemm.cu (128 x 128, 36 KB written per slab) needs 560.
 //
 //   CTA r of a pair (r = rank in the cluster, 0 leads):
 //   warp 0      producer: tiled TMA copies per slab (W box, X half box, the scale records as
