@@ -41,6 +41,10 @@ int pdk_q6k_gemv_i8(const void* data, const void* scales, const float* x, float*
 // q4k_batch_i8.cu: 1..16 tokens, f32 or int8 activations; -1 = shape outside its plan
 int pdk_q4k_batch_i8(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale,
                      float* y, uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
+int pdk_q5k_batch_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                     uint32_t batch, cudaStream_t st);
+int pdk_q6k_batch_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                     uint32_t batch, cudaStream_t st);
 // q4k_tc5.cu: 1..32 tokens on tcgen05 (f16 weights); same operands and return convention
 int pdk_q4k_tc5(const void* data, const void* scales, const float* x, const int8_t* xq, const float* xq_scale, float* y,
                 uint32_t in_dim, uint32_t out_dim, uint32_t batch, cudaStream_t st);
@@ -658,8 +662,26 @@ PDK_EXPORT int pdk_kquant_gemm_f32(const void* data, const void* scales, const v
         y = (float*)y + (size_t)b * out_dim;
         batch -= b;
     }
+    if ((dtype == PDK_KQ_Q5K || dtype == PDK_KQ_Q6K) && batch >= 2u && !force_plain() && pdk_aligned(data, 16)) {
+        // Q5_K: Q4_K's integer batch kernel with the fifth bit ORed into the codes; Q6_K: its sibling with one
+        // product per 16-weight block.  16 tokens per weight pass
+        uint32_t b = 0;
+        int rc = 0;
+        while (b < batch && rc == 0) {
+            const uint32_t take = batch - b < 16u ? batch - b : 16u;
+            rc = (dtype == PDK_KQ_Q5K ? pdk_q5k_batch_i8 : pdk_q6k_batch_i8)(
+                data, scales, (const float*)x + (size_t)b * in_dim, (float*)y + (size_t)b * out_dim, in_dim, out_dim, take,
+                (cudaStream_t)stream);
+            if (rc == 0) b += take;
+        }
+        if (rc > 0) return rc;
+        if (b == batch) return 0;
+        x = (const float*)x + (size_t)b * in_dim;   // -1: outside the kernel's plan, the routes below take what is left
+        y = (float*)y + (size_t)b * out_dim;
+        batch -= b;
+    }
     if (dtype != PDK_KQ_Q4K && !force_plain() && pdk_aligned(data, 16)) {
-        // Q5_K / Q6_K (and Q4_0 below four tokens) have no batch kernel on the tensor path yet: one decode GEMV per token
+        // Q4_0 below four tokens (and Q5_K / Q6_K outside the batch kernels' plan) have no batch kernel on the tensor path yet: one decode GEMV per token
         // (17-25 us each at K=5120 N=25600, the later ones partly from L2) beats the plain f32
         // kernel's 165 us per four tokens
         int rc = 0;

@@ -384,6 +384,33 @@ def test_more_kquants_dequant_repack_gemv(pack, name, k, n):
         assert cond_err(d_out.cpu().numpy().reshape(batch, n), ref, ab) < tol < TOL
 
 
+@pytest.mark.parametrize("name", ["q5_k", "q6_k"])
+@pytest.mark.parametrize("batch", [2, 8, 9, 16, 33])
+def test_q5_k_q6_k_tokens_as_columns(pack, name, batch):
+    """The integer batch kernels of Q5_K and Q6_K (eight or sixteen token columns per weight pass),
+    whole and ragged passes, rows that are not a multiple of the 16-row tile."""
+    dtype, datab = KQ[name]
+    k, n = 2048, 203
+    ns = n * k // 256
+    raw = raw_kquant(name, ns, 760 + dtype + batch)
+    want = oracle.dequant_kquant(name, raw)
+    d_data = torch.zeros(ns * datab, dtype=torch.uint8, device="cuda")
+    d_sc = torch.zeros(ns * 24, dtype=torch.uint8, device="cuda")
+    pack.call("kquant_repack", dev(raw), d_data, d_sc, ns, dtype)
+    x = oracle.fill_normal(batch * k, 761 + batch, 1.0)       # f32 activations that are not bf16 values
+    d_out = torch.full((batch * n,), float("nan"), dtype=torch.float32, device="cuda")
+    pack.call("pdk_kquant_gemm_f32", d_data, d_sc, dev_f32(x), d_out, k, n, batch, dtype)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+    ref, ab = oracle.matmul_f64(want, x, k, n, batch, with_abs=True)
+    assert cond_err(d_out.cpu().numpy().reshape(batch, n), ref, ab) < 1e-5 < TOL
+    # each token alone through the decode GEMV: the same value up to the activations' block-floating step
+    d_one = torch.zeros(n, dtype=torch.float32, device="cuda")
+    pack.call("kquant_gemv", d_data, d_sc, dev_f32(x[:k]), d_one, k, n, dtype)
+    torch.cuda.synchronize()
+    assert cond_err(d_one.cpu().numpy().reshape(1, n), ref[:1], ab[:1]) < 1e-5
+
+
 def test_q4k_gemv_shard_stores_band_into_every_output(pack):
     """pdk_q4k_gemv_shard with two destination vectors on one GPU (the multi-GPU case points the
     second at a peer's buffer): both receive the band at row0, bit-identical to kquant_gemv."""
