@@ -403,12 +403,15 @@ def test_q5_k_q6_k_tokens_as_columns(pack, name, batch):
     torch.cuda.synchronize()
     assert pack.device_error() == 0
     ref, ab = oracle.matmul_f64(want, x, k, n, batch, with_abs=True)
-    assert cond_err(d_out.cpu().numpy().reshape(batch, n), ref, ab) < 1e-5 < TOL
+    # f32 activations: the batch kernels' 15-bit block floating point per 256 elements (the Q4_K batch tests' bound)
+    err = cond_err(d_out.cpu().numpy().reshape(batch, n), ref, ab)
+    assert err < 1e-4 < TOL, ("batch kernel", err)
     # each token alone through the decode GEMV: the same value up to the activations' block-floating step
     d_one = torch.zeros(n, dtype=torch.float32, device="cuda")
     pack.call("kquant_gemv", d_data, d_sc, dev_f32(x[:k]), d_one, k, n, dtype)
     torch.cuda.synchronize()
-    assert cond_err(d_one.cpu().numpy().reshape(1, n), ref[:1], ab[:1]) < 1e-5
+    one = cond_err(d_one.cpu().numpy().reshape(1, n), ref[:1], ab[:1])
+    assert one < 1e-4, ("decode GEMV", one)
 
 
 def test_q4k_gemv_shard_stores_band_into_every_output(pack):
