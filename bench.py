@@ -206,9 +206,11 @@ def run_reference(args, rank):
 
 
 def workload_config(n_gpus, exchange="peer"):
-    how = {"peer": "each rank's GEMV stores its band into every rank's y over NVLink (peer memory) and raises a per-step "
-                   "flag there; y double buffered, every launch checks on the device that the buffer's previous step "
-                   "has arrived from every rank, the last steps are checked by a wait kernel inside the timed region",
+    how = {"peer": "each rank's GEMV stores its band into every rank's y over NVLink (peer memory); y double buffered; "
+                   "every launch first raises the PREVIOUS step's flag on every rank (stream order puts that step's "
+                   "stores before it, no fence inside the kernel) and checks on the device, bounded, that every rank's "
+                   "previous step has arrived; the last step is signalled and awaited by two small kernels inside the "
+                   "timed region",
            "peer-serial": "each rank's GEMV stores its band into every rank's y over NVLink (peer memory), then a wait "
                           "kernel for every rank's flag, then the next step",
            "nccl": "NCCL all-gather of y"}[exchange]
@@ -327,16 +329,18 @@ def run_ours(args, rank, world, local_rank):
             raise RuntimeError("peer-store exchange differs from the all-gather")
 
     # One pre-bound launcher per plane clone (arguments converted once; the call is the C ABI entry).
-    # N > 1, peer exchange (default): a step is ONE launch, the sharded GEMV whose last CTA raises this
-    # rank's flag on every rank once its band is stored there and then checks, on the device and with
-    # a bounded wait, that every rank's band of the same y buffer's previous step has arrived here -
-    # the condition for re-using the buffer.  y is double buffered and steps alternate, so
-    # consecutive steps overlap the way single-GPU launches do while every step's arrival is still
-    # observed on the device; the last step of each buffer is observed by a wait kernel at the end of
-    # the timed region.  No step relies on a host barrier, and the calls count their steps on the
-    # device, so their arguments never change and a captured sequence replays.
-    # --exchange peer-serial is the single-buffered loop: GEMV, then a wait kernel for every rank's
-    # flag, then the next GEMV (a consumer that must read y before the next step starts).
+    # N > 1, peer exchange (default): a step is ONE launch, the sharded GEMV.  y is double buffered and
+    # steps alternate; both buffers share one flag array.  A launch signals nothing when it ends (the
+    # system-scope fence for that costs an NVLink round trip behind which the next launch would wait);
+    # instead every launch first stores - once the previous launch and its peer stores are complete -
+    # the previous step's number into every rank's flags, and before it ends checks, on the device and
+    # with a bounded wait, that every rank's previous step has arrived here.  Consecutive steps overlap
+    # the way single-GPU launches do while every step's arrival is still observed on the device; the
+    # last step is signalled by a post kernel and observed by a wait kernel at the end of the timed
+    # region.  No step relies on a host barrier, and the calls count their steps on the device, so their
+    # arguments never change and a captured sequence replays.
+    # --exchange peer-serial is the single-buffered loop: GEMV that signals at its end, then a wait
+    # kernel for every rank's flag, then the next GEMV (a consumer that must read y before the next step).
     st = torch.cuda.current_stream().cuda_stream
     bufs = [b for b in (peer_out, peer_b) if b is not None]
 
@@ -344,15 +348,16 @@ def run_ours(args, rank, world, local_rank):
         """-> (launch(i) for step i, tail() that observes the arrival of the last steps)."""
         if peer_out is not None:
             name = "pdk_q4k_gemv_shard_lagged" if peer_b is not None else "pdk_q4k_gemv_shard_sync"
-            gem = [[ex.pack.bind(name, p.data, p.scales, xin, b.ptrs_address(), b.flag_ptrs_address(), b.ctr, world, rank,
-                                 first_row, 0, p.dims[0], p.dims[1], stream=stream) for b in bufs] for p in planes]
+            # one flag array and one counter pair (the first buffer's) for every buffer of the loop
+            gem = [[ex.pack.bind(name, p.data, p.scales, xin, b.ptrs_address(), peer_out.flag_ptrs_address(), peer_out.ctr,
+                                 world, rank, first_row, 0, p.dims[0], p.dims[1], stream=stream) for b in bufs] for p in planes]
             if peer_b is None:
                 wait = ex.pack.bind("pdk_peer_flags_wait", peer_out.flags, world, 0, 2000000, stream=stream)
                 return (lambda i: (gem[i % n_clones][0](), wait())), (lambda: None)
-            # target of the closing waits: this rank's own latest step on that buffer
-            waits = [ex.pack.bind("pdk_peer_flags_wait", b.flags, world, 0x80000000 | rank, 2000000, stream=stream)
-                     for b in bufs]
-            return (lambda i: gem[i % n_clones][i & 1]()), (lambda: [w() for w in waits])
+            # closing: signal this rank's last step, then wait until every rank has caught up with it
+            post = ex.pack.bind("pdk_peer_flags_post", peer_out.flag_ptrs_address(), peer_out.ctr, world, rank, stream=stream)
+            wait = ex.pack.bind("pdk_peer_flags_wait", peer_out.flags, world, 0x80000000 | rank, 2000000, stream=stream)
+            return (lambda i: gem[i % n_clones][i & 1]()), (lambda: (post(), wait()))
         ls = [ex.pack.bind("kquant_gemv", p.data, p.scales, xin, yout, p.dims[0], p.dims[1], p.ty, stream=stream)
               for p in planes]
         return (lambda i: ls[i % n_clones]()), (lambda: None)
@@ -544,14 +549,13 @@ def run_ours(args, rank, world, local_rank):
         x_src, x_bytes = x_host.data_ptr(), x_host.numel() * 4
         y_dst, y_bytes = y_host.data_ptr(), y_all.numel() * 4
         y_srcs = [b.local.data_ptr() for b in bufs] or [y_all.data_ptr()]
-        e2e_waits = ([ex.pack.bind("pdk_peer_flags_wait", b.flags, world, 0x80000000 | rank, 2000000, stream=st)
-                      for b in bufs] if peer_b is not None else None)
+        e2e_tail = bound_tail if peer_b is not None else None
 
         def e2e_step(i):
             rt.copy(x.data_ptr(), x_src, x_bytes, 1, st)
             step(i)
-            if e2e_waits is not None:
-                e2e_waits[i & 1]()               # the host reads this step's y: every band must be here
+            if e2e_tail is not None:
+                e2e_tail()                       # the host reads this step's y: signal it, every band must be here
             rt.copy(y_dst, y_srcs[(i & 1) % len(y_srcs)], y_bytes, 2, st)
             rt.record(ev, st)
             rt.sync_event(ev)

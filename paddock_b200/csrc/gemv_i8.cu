@@ -112,6 +112,9 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
             if (d < total) issue(st[d]);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    uint32_t peer_step = 0u;
+    const bool peer_deferred = peers.n != 0u && peers.signal == 2u && blockIdx.x == 0u && tid == 0u;
+    if (peer_deferred) peer_step = peer_post_previous(peers);
 
     act_limbs(x, xq, xq_scale, in_dim, xs_hi, xs_lo, zeros, xmeta, tid, kThreads);
     __syncthreads();
@@ -205,10 +208,11 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
             });
         }
     }
-    if (peers.n != 0u && peers.signal != 0u) {   // uniform over the grid
+    if (peers.n != 0u && peers.signal == 1u) {   // uniform over the grid
         __syncthreads();
         if (tid == 0u) peer_signal(peers);
     }
+    if (peer_deferred) peer_check_previous(peers, peer_step, nullptr);
 }
 
 // PDK_NO_PDL=1 launches without programmatic stream serialization (A/B switch, read once).

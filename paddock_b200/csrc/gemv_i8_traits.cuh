@@ -311,12 +311,17 @@ struct Q80 {
 
 // Row-sharded output: when n > 0 the kernel stores row r of its band at ptr[p][row0 + r] for
 // every p < n - the full-length y of each rank, peer memory over NVLink included - instead of
-// y[r].  Plain peer stores.  With signal != 0 the kernel also tells every rank when its band is
-// complete: its CTAs count themselves out on ctr[0] (this rank's memory, zero between launches)
-// after a system-scope fence, and the last one stores the step number into flag[p][rank] of every
-// rank p, where a consumer waits for it (pdk_peer_flags_wait).  The step number is `step`, or,
-// when that is 0, one more than the rank's own count ctr[1], which the kernel then advances - so
-// that a captured launch can be replayed.  With signal == 0 the caller orders the stores itself.
+// y[r].  Plain peer stores.  With signal == 0 the caller orders the stores itself.
+// signal == 1: the kernel also tells every rank when its band is complete: its CTAs count
+// themselves out on ctr[0] (this rank's memory, zero between launches) and the last one stores the
+// step number into flag[p][rank] of every rank p, where a consumer waits for it
+// (pdk_peer_flags_wait).  The step number is `step`, or, when that is 0, one more than the rank's
+// own count ctr[1], which the kernel then advances - so that a captured launch can be replayed.
+// signal == 2 (deferred): nothing is signalled at the end.  Instead thread 0 of CTA 0 stores, at
+// the START of the launch and behind griddepcontrol.wait - when the previous kernel of the stream,
+// peer stores included, is complete - the number of the PREVIOUS launch into the flags (one flag
+// array and one counter shared by all y buffers of the loop), and checks before it leaves that every
+// rank's previous step has arrived here.
 struct PeerOut {
     float* ptr[8];
     uint32_t* flag[8];
@@ -324,51 +329,82 @@ struct PeerOut {
     uint32_t n, row0, rank, step, signal;
 };
 
-// Called by one thread of each CTA after a CTA-wide barrier that follows the CTA's last store.
-// signal == 1: the last CTA to get here stores the step number into this rank's word of every
-// rank's flag array.  signal == 2: it then also checks that every rank's band of the step before
-// has arrived here (flags >= step - 1) - the condition under which the caller may hand this y to
-// the step after next - waiting at most a second for it; a rank that is late is recorded as
-// 0x1c << 8 | rank in the error word.
+// peer_signal: called by one thread of each CTA after a CTA-wide barrier that follows the CTA's last
+// store (signal == 1).
+//
+// Cost: the system-scope fence waits until the peers have acknowledged this GPU's outstanding stores,
+// one NVLink round trip at the end of the kernel, behind which the next kernel of the stream waits:
+// 3.5 - 4 us per step at two GPUs (a second fence behind the flag stores cost another 2.4 us).  The
+// deferred form pays none of it: stream order already puts the previous kernel's stores before the
+// flag, and the step's arrival is observed one launch later.  acq_rel fences, not the sequentially
+// consistent ones __threadfence*() give.
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void peer_signal(const PeerOut& po, unsigned int* err = nullptr) {
-    if (po.n == 0u || po.signal == 0u) return;
+    if (po.n == 0u || po.signal != 1u) return;
     // Release at GPU scope: this CTA's stores (seen through the barrier) before the count.  Only the
     // last CTA pays for a system-scope fence - it has observed every other CTA's count, so its
     // fence covers their stores too (causality order is cumulative) - instead of every CTA waiting
     // for its own peer stores to be acknowledged over NVLink before it may even count itself out.
-    __threadfence();
+    fence_acq_rel_gpu();
     const uint32_t prev = atomicAdd(po.ctr, 1u);
-    if (prev == gridDim.x - 1u) {
-        __threadfence();                               // acquire: the other CTAs' stores
-        po.ctr[0] = 0u;                                // the next launch on this stream counts from zero
-        uint32_t step = po.step;
-        if (step == 0u) {
-            step = po.ctr[1] + 1u;
-            po.ctr[1] = step;
-        }
-        __threadfence_system();                        // every CTA's stores before the flags
-        const volatile uint32_t* mine = nullptr;
+    if (prev != gridDim.x - 1u) return;
+    fence_acq_rel_gpu();                               // acquire: the other CTAs' stores
+    po.ctr[0] = 0u;                                    // the next launch on this stream counts from zero
+    uint32_t step = po.step;
+    if (step == 0u) {
+        step = po.ctr[1] + 1u;
+        po.ctr[1] = step;
+    }
+    fence_acq_rel_sys();                               // every CTA's stores before the flags
+#pragma unroll
+    for (uint32_t p = 0; p < 8u; ++p)
+        if (p < po.n) st_relaxed_sys(po.flag[p] + po.rank, step);
+}
+
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// signal == 2, thread 0 of CTA 0, behind griddepcontrol.wait: counts this launch and tells every rank
+// that the previous launch's band is in place.  Returns this launch's number.
+__device__ __forceinline__ uint32_t peer_post_previous(const PeerOut& po) {
+    uint32_t step = po.step;
+    if (step == 0u) step = po.ctr[1] + 1u;
+    po.ctr[1] = step;
+    if (step > 1u) {
 #pragma unroll
         for (uint32_t p = 0; p < 8u; ++p)
-            if (p < po.n) {
-                *reinterpret_cast<volatile uint32_t*>(po.flag[p] + po.rank) = step;
-                if (p == po.rank) mine = po.flag[p];
+            if (p < po.n) st_relaxed_sys(po.flag[p] + po.rank, step - 1u);
+    }
+    return step;
+}
+// signal == 2, the same thread before it leaves: every rank's previous step (flags >= step - 1) has
+// arrived here, or - after a second - 0x1c << 8 | rank of a late one goes into the error word.
+__device__ __forceinline__ void peer_check_previous(const PeerOut& po, uint32_t step, unsigned int* err) {
+    if (step <= 1u || po.rank >= po.n) return;
+    const uint32_t* mine = po.flag[po.rank];
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (uint32_t q = 0; q < po.n; ++q) {
+        uint32_t spins = 0;
+        while ((int32_t)(ld_acquire_sys(mine + q) - (step - 1u)) < 0) {
+            if ((++spins & 31u) != 0u) continue;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+            if (t1 - t0 > 1000000000ull) {
+                if (err != nullptr) atomicOr(err, (0x1cu << 8) | q);
+                break;
             }
-        if (po.signal == 2u && step > 1u && mine != nullptr) {
-            unsigned long long t0, t1;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
-            for (uint32_t q = 0; q < po.n; ++q) {
-                uint32_t spins = 0;
-                while ((int32_t)(mine[q] - (step - 1u)) < 0) {
-                    if ((++spins & 31u) != 0u) continue;
-                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
-                    if (t1 - t0 > 1000000000ull) {
-                        if (err != nullptr) atomicOr(err, (0x1cu << 8) | q);
-                        break;
-                    }
-                }
-            }
-            __threadfence_system();
         }
     }
 }

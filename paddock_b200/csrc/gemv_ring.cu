@@ -235,6 +235,9 @@ gemv_ring_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant
     // first requests: weights never depend on this kernel) as soon as this one's CTAs have all started.
     pdk_pdl_launch_dependents();
     pdk_pdl_wait();  // x (and y's previous contents) belong to the previous kernel until here
+    uint32_t peer_step = 0u;
+    const bool peer_deferred = peers.n != 0u && peers.signal == 2u && blockIdx.x == 0u && tid == 0u;
+    if (peer_deferred) peer_step = peer_post_previous(peers);
     const bool invariant = pl.invariant != 0u;
     if (invariant) {
         // A warp only ever meets its own pair's 512 activations: it builds their limbs itself.  The
@@ -402,10 +405,11 @@ gemv_ring_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant
         if (++rb == kRedBufs) { rb = 0; rb_phase ^= 1u; }
     }
     poll_fold(true);
-    if (peers.n != 0u && peers.signal != 0u) {   // uniform over the grid
+    if (peers.n != 0u && peers.signal == 1u) {   // uniform over the grid
         __syncthreads();
         if (tid == 0u) peer_signal(peers, err);
     }
+    if (peer_deferred) peer_check_previous(peers, peer_step, err);
     if (!alive) {
         // a wait ran out somewhere in the CTA: the copies this warp still has in flight must land
         // before its shared memory can go to another CTA.  At most D are outstanding, one per stage.
@@ -930,6 +934,14 @@ __global__ void peer_flags_wait_kernel(uint32_t* flags, uint32_t n_ranks, uint32
     }
     __threadfence_system();   // acquire: the bands stored before the flags are visible to what follows
 }
+__global__ void peer_flags_post_kernel(const gemv_i8::PeerOut po) {
+    pdk_pdl_launch_dependents();
+    pdk_pdl_wait();   // the launch this signals, peer stores included, is complete
+    if (threadIdx.x != 0u) return;
+    const uint32_t step = po.ctr[1];
+    if (step == 0u) return;
+    for (uint32_t p = 0; p < po.n; ++p) gemv_i8::st_relaxed_sys(po.flag[p] + po.rank, step);
+}
 }  // namespace
 
 // No counterpart in the reference (its multi-GPU story is one process per GPU, replicas only):
@@ -963,18 +975,36 @@ PDK_EXPORT int pdk_q4k_gemv_shard_sync(const void* data, const void* scales, con
                         (cudaStream_t)stream);
 }
 
-// The same for a loop that keeps two (or more) y buffers in rotation, each with its own flag array
-// and counter words: besides signalling its own step, the kernel's last CTA checks - waiting at
-// most a second, 0x1c << 8 | rank in the error word for a rank that is late - that every rank's
-// band of this buffer's PREVIOUS step has arrived here.  That is the condition for handing the
-// buffer to a later step, so such a loop needs no wait kernel between its steps: one launch per
-// step, consecutive steps overlap like single-GPU launches do, and the arrival of every step is
-// still observed on the device (the last step of each buffer by pdk_peer_flags_wait).
+// The same for a loop that keeps two (or more) y buffers in rotation.  All buffers of the loop share
+// ONE flag array per rank and one pair of counter words.  Nothing is signalled at the end of the
+// kernel (the system-scope fence that takes costs an NVLink round trip per step); instead every launch
+// stores, behind its griddepcontrol.wait - when the stream's previous kernel and its peer stores are
+// complete - the number of the PREVIOUS launch into the flags, and checks before it ends (at most a
+// second; 0x1c << 8 | rank in the error word for a rank that is late) that every rank's previous step has
+// arrived here.  What follows launch s in the stream may therefore read step s - 1 of every rank: one
+// launch per step, consecutive steps overlap like single-GPU launches do, and the arrival of every step
+// is still observed on the device.  After the last launch pdk_peer_flags_post signals it and
+// pdk_peer_flags_wait (step = 0x80000000 | rank) observes it.
 PDK_EXPORT int pdk_q4k_gemv_shard_lagged(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
                                          const void* const* flag_ptrs, void* ctr, uint32_t n_ranks, uint32_t rank,
                                          uint32_t row0, uint32_t step, uint32_t in_dim, uint32_t out_dim, void* stream) {
     return shard_launch(data, scales, x, y_ptrs, flag_ptrs, ctr, n_ranks, rank, row0, step, 2u, in_dim, out_dim,
                         (cudaStream_t)stream);
+}
+
+// Closes a pdk_q4k_gemv_shard_lagged loop: stores the number of the stream's last launch (ctr[1]) into
+// word `rank` of every rank's flag array, behind the stream's previous kernel.
+PDK_EXPORT int pdk_peer_flags_post(const void* const* flag_ptrs, void* ctr, uint32_t n_ranks, uint32_t rank, void* stream) {
+    if (flag_ptrs == nullptr || ctr == nullptr || n_ranks == 0u || n_ranks > 8u || rank >= n_ranks) return cudaErrorInvalidValue;
+    gemv_i8::PeerOut po{};
+    for (uint32_t p = 0; p < n_ranks; ++p) {
+        if (flag_ptrs[p] == nullptr || !pdk_aligned(flag_ptrs[p], 4)) return cudaErrorInvalidValue;
+        po.flag[p] = (uint32_t*)flag_ptrs[p];
+    }
+    po.ctr = (uint32_t*)ctr;
+    po.n = n_ranks;
+    po.rank = rank;
+    return pdk_launch_pdl(peer_flags_post_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, po);
 }
 
 // Waits on the device (one small kernel in `stream`) until every one of the n_ranks <= 8 flag

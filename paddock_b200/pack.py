@@ -124,6 +124,7 @@ _EXTRA_SIGS = {
     "pdk_q4k_gemv_shard_sync": "ppppppuuuuuu",
     "pdk_q4k_gemv_shard_lagged": "ppppppuuuuuu",
     "pdk_peer_flags_wait": "puuu",
+    "pdk_peer_flags_post": "ppuu",
     "pdk_selftest_bounded_wait": "up",
     "pdk_tc5_issue_probe": "uup",
     "pdk_mxfp4_tc5_tile_scales": "pppuuu",

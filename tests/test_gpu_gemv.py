@@ -523,10 +523,11 @@ def test_q4k_gemv_shard_sync_raises_flags_and_wait_is_bounded(pack):
 
 
 def test_q4k_gemv_shard_lagged_checks_the_previous_step_on_the_device(pack):
-    """The form for loops that rotate y buffers: besides signalling its own step the kernel checks
-    that every rank's band of the buffer's previous step has arrived.  One rank alone: every check
-    passes, and a closing wait on "my own latest step" returns at once.  Two ranks of which the
-    second never runs: the second launch gives up on rank 1 after its bounded wait and says so."""
+    """The form for loops that rotate y buffers: a launch signals the PREVIOUS launch of its stream (when
+    it starts) and checks that every rank's previous step has arrived (before it ends); the last launch
+    is signalled by pdk_peer_flags_post.  One rank alone: every check passes, and a closing wait on "my
+    own latest step" returns at once.  Two ranks of which the second never runs: the second launch gives
+    up on rank 1 after its bounded wait and says so."""
     import ctypes
     import time
     k, n = 5120, 160
@@ -542,22 +543,27 @@ def test_q4k_gemv_shard_lagged_checks_the_previous_step_on_the_device(pack):
     for i in range(4):
         pack.call("pdk_q4k_gemv_shard_lagged", d_data, d_sc, d_x, ctypes.addressof(yp), ctypes.addressof(fp), ctr, 1, 0,
                   0, 0, k, n)
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0 and int(flags[0]) == 3 and ctr.tolist() == [0, 4]   # launch 4 signalled step 3
+    pack.call("pdk_peer_flags_post", ctypes.addressof(fp), ctr, 1, 0)
     pack.call("pdk_peer_flags_wait", flags, 1, 0x80000000 | 0, 100000)
     torch.cuda.synchronize()
     assert pack.device_error() == 0 and int(flags[0]) == 4 and ctr.tolist() == [0, 4]
     ref, ab = oracle.matmul_f64(oracle.dequant_q4_k(raw), bf16_activations(k, seed_for(2, 961)), k, n, 1, with_abs=True)
     assert cond_err(ys[0].cpu().numpy(), ref[0], ab[0]) < 1e-5
+    assert pack.status("pdk_peer_flags_post", ctypes.addressof(fp), ctr, 9, 0) == 1      # more than 8 ranks
+    assert pack.status("pdk_peer_flags_post", ctypes.addressof(fp), ctr, 2, 2) == 1      # rank outside the group
     # rank 0 of two; nobody plays rank 1, so word 1 stays 0
     flags.zero_()
     ctr.zero_()
     pack.call("pdk_q4k_gemv_shard_lagged", d_data, d_sc, d_x, ctypes.addressof(yp), ctypes.addressof(fp), ctr, 2, 0, 0, 0, k, n)
     torch.cuda.synchronize()
-    assert pack.device_error() == 0                                         # step 1 has no previous step
+    assert pack.device_error() == 0 and int(flags[0]) == 0                  # step 1 has no previous step
     t0 = time.perf_counter()
     pack.call("pdk_q4k_gemv_shard_lagged", d_data, d_sc, d_x, ctypes.addressof(yp), ctypes.addressof(fp), ctr, 2, 0, 0, 0, k, n)
     torch.cuda.synchronize()
     assert 0.5 < time.perf_counter() - t0 < 5.0                             # the one-second budget ran out
     assert pack.device_error() == (0x1c << 8 | 1)
-    assert int(flags[0]) == 2                                               # its own step was still signalled
+    assert int(flags[0]) == 1                                               # step 1 was still signalled
     y = torch.ones(8, device="cuda") * 2                                    # the context still works
     assert float(y.sum()) == 16.0
