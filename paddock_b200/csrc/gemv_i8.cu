@@ -130,24 +130,45 @@ gemv_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ rec
     auto compute = [&](const Stage& s, auto&& prefetch) {
         int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
         const uint32_t xoff = c_u * 256u;
+        if constexpr (F::kSplitBlock) {
+            // mma i feeds block 2t + i/4 alone: low nibbles = its elements 4(i&3).., high nibbles = 16 + 4(i&3)..
+#pragma unroll
+            for (uint32_t half = 0; half < 2u; ++half) {
+                const bool mine = half == 0u ? role_a : role_b;
+                const uint8_t* hs = mine ? xs_hi + xoff + (2u * t + half) * 32u : zeros;
+                const uint8_t* ls = mine ? xs_lo + xoff + (2u * t + half) * 32u : zeros;
+                const uint4 bh0 = *reinterpret_cast<const uint4*>(hs), bh1 = *reinterpret_cast<const uint4*>(hs + 16u);
+                const uint4 bl0 = *reinterpret_cast<const uint4*>(ls), bl1 = *reinterpret_cast<const uint4*>(ls + 16u);
+                const uint32_t vh0[4] = {bh0.x, bh0.y, bh0.z, bh0.w}, vh1[4] = {bh1.x, bh1.y, bh1.z, bh1.w};
+                const uint32_t vl0[4] = {bl0.x, bl0.y, bl0.z, bl0.w}, vl1[4] = {bl1.x, bl1.y, bl1.z, bl1.w};
+#pragma unroll
+                for (uint32_t k = 0; k < 4u; ++k) {
+                    uint32_t a0, a1, a2, a3;
+                    F::a_regs(s, half * 4u + k, a0, a1, a2, a3);
+                    mma_s8(ch, a0, a1, a2, a3, vh0[k], vh1[k]);
+                    mma_s8(cl, a0, a1, a2, a3, vl0[k], vl1[k]);
+                }
+            }
+        } else {
         const uint8_t* ha = role_a ? xs_hi + xoff + 2u * t * 32u : zeros;
-        const uint8_t* hb = role_b ? xs_hi + xoff + (2u * t + 1u) * 32u : zeros;
-        const uint8_t* la = role_a ? xs_lo + xoff + 2u * t * 32u : zeros;
-        const uint8_t* lb = role_b ? xs_lo + xoff + (2u * t + 1u) * 32u : zeros;
-#pragma unroll
-        for (uint32_t half = 0; half < 2u; ++half) {
-            const uint4 bha = *reinterpret_cast<const uint4*>(ha + half * 16u);
-            const uint4 bhb = *reinterpret_cast<const uint4*>(hb + half * 16u);
-            const uint4 bla = *reinterpret_cast<const uint4*>(la + half * 16u);
-            const uint4 blb = *reinterpret_cast<const uint4*>(lb + half * 16u);
-            const uint32_t vha[4] = {bha.x, bha.y, bha.z, bha.w}, vhb[4] = {bhb.x, bhb.y, bhb.z, bhb.w};
-            const uint32_t vla[4] = {bla.x, bla.y, bla.z, bla.w}, vlb[4] = {blb.x, blb.y, blb.z, blb.w};
-#pragma unroll
-            for (uint32_t k = 0; k < 4u; ++k) {
-                uint32_t a0, a1, a2, a3;
-                F::a_regs(s, half * 4u + k, a0, a1, a2, a3);
-                mma_s8(ch, a0, a1, a2, a3, vha[k], vhb[k]);
-                mma_s8(cl, a0, a1, a2, a3, vla[k], vlb[k]);
+            const uint8_t* hb = role_b ? xs_hi + xoff + (2u * t + 1u) * 32u : zeros;
+            const uint8_t* la = role_a ? xs_lo + xoff + 2u * t * 32u : zeros;
+            const uint8_t* lb = role_b ? xs_lo + xoff + (2u * t + 1u) * 32u : zeros;
+    #pragma unroll
+            for (uint32_t half = 0; half < 2u; ++half) {
+                const uint4 bha = *reinterpret_cast<const uint4*>(ha + half * 16u);
+                const uint4 bhb = *reinterpret_cast<const uint4*>(hb + half * 16u);
+                const uint4 bla = *reinterpret_cast<const uint4*>(la + half * 16u);
+                const uint4 blb = *reinterpret_cast<const uint4*>(lb + half * 16u);
+                const uint32_t vha[4] = {bha.x, bha.y, bha.z, bha.w}, vhb[4] = {bhb.x, bhb.y, bhb.z, bhb.w};
+                const uint32_t vla[4] = {bla.x, bla.y, bla.z, bla.w}, vlb[4] = {blb.x, blb.y, blb.z, blb.w};
+    #pragma unroll
+                for (uint32_t k = 0; k < 4u; ++k) {
+                    uint32_t a0, a1, a2, a3;
+                    F::a_regs(s, half * 4u + k, a0, a1, a2, a3);
+                    mma_s8(ch, a0, a1, a2, a3, vha[k], vhb[k]);
+                    mma_s8(cl, a0, a1, a2, a3, vla[k], vlb[k]);
+                }
             }
         }
         // The next loads are issued only now, after every register of this unit
@@ -279,6 +300,11 @@ int pdk_q5k_gemv_i8_regs(const void* data, const void* scales, const float* x, f
 int pdk_q8_0_gemv_i8_regs(const void* data, const void* scale, const float* bias, const float* x, float* y,
                      uint32_t in_dim, uint32_t out_dim, cudaStream_t st) {
     return launch<Q80>(data, scale, bias, x, y, in_dim, out_dim, st);
+}
+
+int pdk_iq4xs_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                      cudaStream_t st) {
+    return launch<IQ4XS>(data, scales, nullptr, x, y, in_dim, out_dim, st);
 }
 
 // Q4_K GEMV on int8 activations (xq int8 [in_dim], one f32 scale per 32): same kernel, the

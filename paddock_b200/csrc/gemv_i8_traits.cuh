@@ -71,6 +71,7 @@ struct Q4K {
     static constexpr uint32_t kDepth = 3;
     static constexpr uint32_t kDataBytes = 128;  // per row per unit
     static constexpr uint32_t kRecBytes = 24;
+    static constexpr bool kSplitBlock = false;   // a 32-byte lane run holds two blocks side by side (low / high nibbles, or halves)
     struct Stage {
         uint4 q[4];      // row g: bytes 0..15 / 16..31 of ggml group t; row g+8 likewise
         uint32_t dd[2];  // {f16 d, f16 dmin} of the two rows
@@ -145,6 +146,7 @@ struct Q5K {
     static constexpr uint32_t kDepth = 2;
     static constexpr uint32_t kDataBytes = 160;
     static constexpr uint32_t kRecBytes = 24;
+    static constexpr bool kSplitBlock = false;   // a 32-byte lane run holds two blocks side by side (low / high nibbles, or halves)
     struct Stage {
         uint4 q[4];      // as Q4K
         uint2 hb[2];     // high-bit bytes 8t..8t+7 of row g / row g+8 (the other lanes of the row hold the rest)
@@ -212,6 +214,7 @@ struct Q40 {
     static constexpr uint32_t kDepth = 3;
     static constexpr uint32_t kDataBytes = 128;
     static constexpr uint32_t kRecBytes = 24;
+    static constexpr bool kSplitBlock = false;   // a 32-byte lane run holds two blocks side by side (low / high nibbles, or halves)
     struct Stage {
         uint4 q[4];
         uint32_t dd[2];  // {f16 d[2t], f16 d[2t+1]} of the two rows
@@ -268,6 +271,7 @@ struct Q80 {
     static constexpr uint32_t kDepth = 2;
     static constexpr uint32_t kDataBytes = 256;  // 8 blocks of 32 int8
     static constexpr uint32_t kRecBytes = 16;    // 8 f16 scales
+    static constexpr bool kSplitBlock = false;   // a 32-byte lane run holds two blocks side by side (low / high nibbles, or halves)
     struct Stage {
         uint4 q[8];      // row g: blocks 2t, 2t+1 (64 bytes); row g+8 likewise
         uint32_t dd[2];  // {f16 d[2t], f16 d[2t+1]} of the two rows
@@ -306,6 +310,73 @@ struct Q80 {
         const __half2 d1 = *reinterpret_cast<const __half2*>(&s.dd[1]);
         acc_g += __low2float(d0) * f[0] + __high2float(d0) * f[1];
         acc_g8 += __low2float(d1) * f[2] + __high2float(d1) * f[3];
+    }
+};
+
+// IQ4_XS repacked (kquant_more.cu): qs verbatim - per 32-weight block 16 bytes, byte j = code of
+// element j (low nibble) and of element 16 + j (high nibble) - and a 24-byte record {f16 d, pad2,
+// i8 ls - 32 [8], pad12}; w = d * (ls - 32) * book[code] with ggml's 16-entry signed code book.
+// Lane t's 32 bytes of a row are blocks 2t (words 0..3) and 2t+1 (words 4..7), so mma i feeds ONE block:
+// both halves of its k-slots (low nibbles = elements 4(i&3).., high nibbles = elements 16 + 4(i&3)..)
+// belong to block 2t + i/4, and the kernel's B operand follows (kSplitBlock).  The codes become book
+// values with byte permutes: per 16 bits of codes one permute over each half of the book, one that
+// picks per byte by the code's top bit; two more put a word's low-nibble and high-nibble values in
+// separate registers.
+struct IQ4XS {
+    static constexpr uint32_t kDepth = 2;
+    static constexpr uint32_t kDataBytes = 128;
+    static constexpr uint32_t kRecBytes = 24;
+    static constexpr bool kSplitBlock = true;
+    struct Stage {
+        uint4 q[4];      // row g: bytes [32t, 32t+32); row g+8 likewise
+        uint32_t d[2];   // f16 d of the two rows (low half)
+        uint32_t ls[2];  // i8 ls' of blocks 2t, 2t+1 of the two rows (low two bytes)
+    };
+    template <bool kShared>
+    __device__ static __forceinline__ void load(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
+                                                const uint8_t* r1, uint32_t t) {
+        s.q[0] = ld16<kShared>(d0 + t * 32u);
+        s.q[1] = ld16<kShared>(d0 + t * 32u + 16u);
+        s.q[2] = ld16<kShared>(d1 + t * 32u);
+        s.q[3] = ld16<kShared>(d1 + t * 32u + 16u);
+        s.d[0] = ld2<kShared>(r0);
+        s.d[1] = ld2<kShared>(r1);
+        s.ls[0] = ld2<kShared>(r0 + 4u + 2u * t);
+        s.ls[1] = ld2<kShared>(r1 + 4u + 2u * t);
+    }
+    __device__ static __forceinline__ uint32_t word(const uint4& v, uint32_t i) {
+        return i == 0u ? v.x : i == 1u ? v.y : i == 2u ? v.z : v.w;
+    }
+    // four book values for the four codes in the low 16 bits of c (code j in bits 4j..4j+3 -> byte j)
+    __device__ static __forceinline__ uint32_t book4(uint32_t c) {
+        const uint32_t sel = c & 0x7777u;
+        const uint32_t low = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, sel);    // -127 -104 -83 -65 | -49 -35 -22 -10
+        const uint32_t high = __byte_perm(0x26190D01u, 0x71594535u, sel);   //    1   13  25  38 |  53  69  89 113
+        return __byte_perm(low, high, 0x3210u | ((c & 0x8888u) >> 1));
+    }
+    // a word of eight codes -> the values of its four low nibbles and of its four high nibbles
+    __device__ static __forceinline__ void book8(uint32_t w, uint32_t& lo, uint32_t& hi) {
+        const uint32_t r0 = book4(w), r1 = book4(w >> 16);   // codes (n0 n1 n2 n3), (n4 n5 n6 n7): low / high nibble alternate
+        lo = __byte_perm(r0, r1, 0x6420u);
+        hi = __byte_perm(r0, r1, 0x7531u);
+    }
+    __device__ static __forceinline__ void a_regs(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        book8(word(s.q[i >> 2], i & 3u), a0, a2);
+        book8(word(s.q[2u + (i >> 2)], i & 3u), a1, a3);
+    }
+    static constexpr bool kUnsignedA = false;
+    static constexpr int kHiShift = 0;
+    __device__ static __forceinline__ void a_frag(const Stage& s, uint32_t i, uint32_t& a0, uint32_t& a1,
+                                                  uint32_t& a2, uint32_t& a3) {
+        a_regs(s, i, a0, a1, a2, a3);
+    }
+    __device__ static __forceinline__ void fold(const Stage& s, const float (&f)[4], float, float, float& acc_g,
+                                                float& acc_g8) {
+        const float d_g = __half2float(__ushort_as_half((unsigned short)s.d[0]));
+        const float d_g8 = __half2float(__ushort_as_half((unsigned short)s.d[1]));
+        acc_g += d_g * ((float)(int8_t)(s.ls[0] & 0xffu) * f[0] + (float)(int8_t)((s.ls[0] >> 8) & 0xffu) * f[1]);
+        acc_g8 += d_g8 * ((float)(int8_t)(s.ls[1] & 0xffu) * f[2] + (float)(int8_t)((s.ls[1] >> 8) & 0xffu) * f[3]);
     }
 };
 

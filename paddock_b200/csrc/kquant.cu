@@ -36,6 +36,8 @@ int pdk_q4_0_gemv_i8(const void* data, const void* scales, const float* x, float
                      uint32_t out_dim, cudaStream_t st);
 int pdk_q5k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st);
+int pdk_iq4xs_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim, uint32_t out_dim,
+                      cudaStream_t st);  // gemv_i8.cu
 int pdk_q6k_gemv_i8(const void* data, const void* scales, const float* x, float* y, uint32_t in_dim,
                     uint32_t out_dim, cudaStream_t st);  // gemv_q6k.cu
 // q4k_batch_i8.cu: 1..16 tokens, f32 or int8 activations; -1 = shape outside its plan
@@ -585,6 +587,7 @@ int more_gemv_i8(const void* data, const void* scales, const float* x, float* y,
     if (dtype == PDK_KQ_Q4_0) return pdk_q4_0_gemv_i8(data, scales, x, y, in_dim, out_dim, st);
     if (dtype == PDK_KQ_Q5K) return pdk_q5k_gemv_i8(data, scales, x, y, in_dim, out_dim, st);
     if (dtype == PDK_KQ_Q6K) return pdk_q6k_gemv_i8(data, scales, x, y, in_dim, out_dim, st);
+    if (dtype == PDK_KQ_IQ4XS) return pdk_iq4xs_gemv_i8(data, scales, x, y, in_dim, out_dim, st);
     return -1;
 }
 
