@@ -405,7 +405,8 @@ int pdk_mxfp4_tc5_tile_scales(const void* scale, void* tiled, void* meta, uint32
 /* Block positions (pd_moe_align_bm order) -> four NVFP4 term rows each:
  * mode 0: position p = row sorted_row[p] of x f32[rows][dim];  mode 1: position p =
  * swiglu_oai(x[p], up[p]) of raw gate / up outputs f32[positions][dim].
- * Positions of unused blocks (block_expert = PDK_MOE_PAD) and padding positions become zero rows.
+ * Padding positions of used blocks become zero rows; the rows of unused blocks (block_expert = PDK_MOE_PAD),
+ * which the GEMMs skip, are left as they are.
  * xq u8[max_blocks*4*bm][dim/2], xs u8[max_blocks][ceil(dim/256)][2048] (scale records, the layout
  * of the tiled weight scales; zero the buffer once), xstep f32[max_blocks*bm]. */
 int pdk_moe_prep_act_f4(const void* x, const void* up, const void* sorted_row, const void* block_expert, void* xq,

@@ -121,7 +121,7 @@ struct PrepArgs {
     const float* x;              // mode 0: [src rows][dim]; mode 1: gate [positions][dim]
     const float* up;             // mode 1: up [positions][dim]
     const uint32_t* sorted_row;  // [positions]; PDK_MOE_PAD = padding (zeros are written)
-    const uint32_t* block_expert;  // [blocks]; PDK_MOE_PAD = unused block (its sorted_row entries are not defined)
+    const uint32_t* block_expert;  // [blocks]; PDK_MOE_PAD = unused block (its sorted_row entries are not defined; its rows are left as they are)
     uint8_t* xq;                 // [blocks][4*bm][dim/2]
     uint8_t* xs;                 // tiled: [blocks][slab][4 cells][512], the weight scale records' layout
     float* xstep;                // [positions] power of two the row was divided by
@@ -206,6 +206,20 @@ __device__ __forceinline__ void prep_position(const PrepArgs& a, uint32_t pos, u
     // ---- four terms per 16-element group
     const size_t r0 = (size_t)b * 4u * a.bm + i;
     uint8_t* xs_blk = a.xs + (size_t)b * num_kb * 2048u;
+    if (!live) {
+        // padding (half of the positions when most experts hold a ragged block) and all-zero rows: zero
+        // term rows and scale bytes, none of the term arithmetic
+        for (uint32_t g = tid; g < num_kb * 16u; g += blockDim.x) {
+            uint8_t* xs_g = xs_blk + (size_t)(g >> 4) * 2048u + ((g >> 2) & 3u) * 512u + (g & 3u);
+#pragma unroll
+            for (uint32_t term = 0; term < 4u; ++term) {
+                const uint32_t rr = term * a.bm + i;
+                xs_g[(rr & 31u) * 16u + (rr >> 5) * 4u] = 0;
+                if (g < groups) *reinterpret_cast<uint2*>(a.xq + (r0 + (size_t)term * a.bm) * kh + (size_t)g * 8u) = make_uint2(0u, 0u);
+            }
+        }
+        return;
+    }
     for (uint32_t g = tid; g < num_kb * 16u; g += blockDim.x) {
         // scale byte of group g and term row r: record g/16, cell (g/4)%4, byte (r%32)*16 + (r/32)*4 + g%4
         uint8_t* xs_g = xs_blk + (size_t)(g >> 4) * 2048u + ((g >> 2) & 3u) * 512u + (g & 3u);
@@ -291,7 +305,8 @@ __global__ void __launch_bounds__(256) moe_prep_f4_kernel(const PrepArgs a) {
             }
         }
     } else {
-        src = a.block_expert[pos / a.bm] == PDK_MOE_PAD ? PDK_MOE_PAD : a.sorted_row[pos];
+        if (a.block_expert[pos / a.bm] == PDK_MOE_PAD) return;   // an unused block: the GEMMs skip it, nothing reads its rows
+        src = a.sorted_row[pos];
     }
     prep_position(a, pos, src);
 }
@@ -354,7 +369,8 @@ __global__ void __launch_bounds__(256) moe_route_prep_f4_kernel(const PrepArgs a
         if (tid < r.max_blocks) r.block_expert[tid] = s_bexp[tid];
     }
     const uint32_t pos = blockIdx.x;
-    prep_position(a, pos, s_bexp[pos / a.bm] == PDK_MOE_PAD ? PDK_MOE_PAD : s_row[pos]);
+    if (s_bexp[pos / a.bm] == PDK_MOE_PAD) return;   // an unused block
+    prep_position(a, pos, s_row[pos]);
 }
 
 // ---------------------------------------------------------------- grouped GEMM
