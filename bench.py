@@ -256,6 +256,10 @@ def other_configs(ex, quick):
                 rec.update(achieved=r["tflops"], unit="TFLOP/s", frac=r["frac_of_2x_bf16"], denominator="2 x measured bf16 burst")
                 if probe.get("e4m3_m128n256k32"):
                     rec.update(frac_of_probe=r["tflops"] / probe["e4m3_m128n256k32"], probe_denominator="tcgen05.mma e4m3 issue rate")
+                    # shared-memory port (128 B per cycle and SM): per 128-byte K stage of the 256 x 256 pair tile
+                    # 32 KB written by TMA + 4 MMAs x (4 + 4 + 4) KB read = 625 cycles for 512 tensor cycles
+                    rec.update(frac_of_port_bound=r["tflops"] / (probe["e4m3_m128n256k32"] * 512.0 / 625.0),
+                               port_bound="issue rate x 512 / 625: shared-memory bytes per K stage of the 256 x 256 pair tile")
             elif case.op == "nvf4_gemm" and case.m >= 512:
                 rec.update(achieved=r["tflops"], unit="TFLOP/s", frac=r["frac_of_4x_bf16"], denominator="4 x measured bf16 burst",
                            gbs=r["gbs"], frac_of_hbm=r["frac_of_hbm"])
@@ -263,6 +267,10 @@ def other_configs(ex, quick):
                 # with the same copies is a third lower)
                 key = "nvf4_pair_m256n128k64_with_scale_copies"
                 if probe.get(key):
+                    # shared-memory port: per 256-element slab of the 256 x 256 pair tile 38 KB written + 4 MMAs x
+                    # (4 + 4 + 4) KB + 6 KB of scale cells read = 720 cycles for 512 tensor cycles
+                    rec.update(frac_of_port_bound=r["tflops"] / (probe[key] * 512.0 / 720.0),
+                               port_bound="pair issue rate x 512 / 720: shared-memory bytes per K slab of the 256 x 256 pair tile")
                     rec.update(frac_of_probe=r["tflops"] / probe[key],
                                probe_denominator="tcgen05.mma NVFP4 issue rate on pairs of SMs with its scale-cell copies",
                                frac_of_one_sm_probe=r["tflops"] / probe.get("nvf4_m128n128k64_with_scale_copies", float("nan")))
