@@ -279,23 +279,7 @@ nvf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             ok = tc5::mbar_wait(&sh->tmem_full[buf], aphase, ctx, tc5::kErrTmemFullWait, buf);
             if (!ok) break;
             tc5::fence_after_sync();
-            if (half >= n_grp) {   // a ragged tile with nothing for this warp to read
-                tc5::fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_leader(&sh->tmem_empty[buf]);
-            }
-#pragma unroll 1
-            for (uint32_t g = half; g < n_grp; g += 2u) {
-                uint32_t ra[32], rb[32];
-                const uint32_t col = tmem_base + ((quarter * 32u) << 16) + buf * BN + g * 64u;
-                tc5::tmem_ld_32x32(col, ra);
-                tc5::tmem_ld_32x32(col + 32u, rb);
-                tc5::tmem_ld_wait();
-                if (g + 2u >= n_grp) {   // every column this warp reads is in registers
-                    tc5::fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_leader(&sh->tmem_empty[buf]);
-                }
+            auto put_group = [&](uint32_t g, const uint32_t (&ra)[32], const uint32_t (&rb)[32]) {
                 if (tma_out) {
 #pragma unroll
                     for (uint32_t i = 0; i < 64u; ++i)
@@ -309,6 +293,41 @@ nvf4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                             store_one2<TO>(y + (size_t)(b0 + t) * a_rows + n,
                                            fmaf(__uint_as_float(i < 32u ? ra[i & 31u] : rb[i & 31u]), scale2, b));
                     }
+                }
+            };
+            auto hand_back = [&]() {   // every column this warp reads is in registers
+                tc5::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(&sh->tmem_empty[buf]);
+            };
+            const uint32_t col0 = tmem_base + ((quarter * 32u) << 16) + buf * BN;
+            if constexpr (BN == 256u) {
+                // this warp's two groups (half, half + 2) are read before either is stored: the accumulator goes back
+                // to the issuer after two load latencies instead of after the first group's 64 stores
+                uint32_t ra0[32], rb0[32], ra1[32], rb1[32];
+                const bool has0 = half < n_grp, has1 = half + 2u < n_grp;   // warp-uniform
+                if (has0) {
+                    tc5::tmem_ld_32x32(col0 + half * 64u, ra0);
+                    tc5::tmem_ld_32x32(col0 + half * 64u + 32u, rb0);
+                }
+                if (has1) {
+                    tc5::tmem_ld_32x32(col0 + (half + 2u) * 64u, ra1);
+                    tc5::tmem_ld_32x32(col0 + (half + 2u) * 64u + 32u, rb1);
+                }
+                tc5::tmem_ld_wait();
+                hand_back();
+                if (has0) put_group(half, ra0, rb0);
+                if (has1) put_group(half + 2u, ra1, rb1);
+            } else {
+                if (half >= n_grp) hand_back();   // a ragged tile with nothing for this warp to read
+#pragma unroll 1
+                for (uint32_t g = half; g < n_grp; g += 2u) {
+                    uint32_t ra[32], rb[32];
+                    tc5::tmem_ld_32x32(col0 + g * 64u, ra);
+                    tc5::tmem_ld_32x32(col0 + g * 64u + 32u, rb);
+                    tc5::tmem_ld_wait();
+                    if (g + 2u >= n_grp) hand_back();
+                    put_group(g, ra, rb);
                 }
             }
             if (tma_out) {
