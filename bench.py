@@ -206,7 +206,7 @@ def run_reference(args, rank):
 
 
 def workload_config(n_gpus, exchange="peer"):
-    how = {"peer": "each rank's GEMV stores its band into every rank's y over NVLink (peer memory); y double buffered; "
+    how = {"peer": "each rank's GEMV stores its band into every rank's y over NVLink (peer memory); y in three buffers used in turn; "
                    "every launch first raises the PREVIOUS step's flag on every rank (stream order puts that step's "
                    "stores before it, no fence inside the kernel) and checks on the device, bounded, that every rank's "
                    "previous step has arrived; the last step is signalled and awaited by two small kernels inside the "
@@ -318,12 +318,15 @@ def run_ours(args, rank, world, local_rank):
 
     # N > 1: the row bands are exchanged by the GEMV kernel's own stores into every rank's y over
     # NVLink (peer memory); --exchange nccl keeps the kernel local and all-gathers y with NCCL.
-    peer_out = peer_b = None
+    peer_out = peer_b = peer_c = None
     first_row, _ = shard.row_band(N_DIM, world, rank, align=16)
     if world > 1 and args.exchange in ("peer", "peer-serial"):
         peer_out = shard.PeerOutput(N_DIM)
         if args.exchange == "peer":
-            peer_b = shard.PeerOutput(N_DIM)     # y is double buffered: steps alternate between the two
+            # y in three buffers, used in turn: while this rank reads step s - 1 (after its launch s has observed
+            # its arrival), a peer that is one launch ahead already stores step s + 1, and only its step s + 2,
+            # which it cannot start before this rank's launch s + 1 has begun, returns to the buffer of s - 1
+            peer_b, peer_c = shard.PeerOutput(N_DIM), shard.PeerOutput(N_DIM)
         y_all = peer_out.local
         # the two exchanges must agree bit for bit
         ex.kquant_gemv(planes[0], x, y)
@@ -337,8 +340,8 @@ def run_ours(args, rank, world, local_rank):
             raise RuntimeError("peer-store exchange differs from the all-gather")
 
     # One pre-bound launcher per plane clone (arguments converted once; the call is the C ABI entry).
-    # N > 1, peer exchange (default): a step is ONE launch, the sharded GEMV.  y is double buffered and
-    # steps alternate; both buffers share one flag array.  A launch signals nothing when it ends (the
+    # N > 1, peer exchange (default): a step is ONE launch, the sharded GEMV.  y lives in three buffers
+    # used in turn; all buffers share one flag array.  A launch signals nothing when it ends (the
     # system-scope fence for that costs an NVLink round trip behind which the next launch would wait);
     # instead every launch first stores - once the previous launch and its peer stores are complete -
     # the previous step's number into every rank's flags, and before it ends checks, on the device and
@@ -350,7 +353,7 @@ def run_ours(args, rank, world, local_rank):
     # --exchange peer-serial is the single-buffered loop: GEMV that signals at its end, then a wait
     # kernel for every rank's flag, then the next GEMV (a consumer that must read y before the next step).
     st = torch.cuda.current_stream().cuda_stream
-    bufs = [b for b in (peer_out, peer_b) if b is not None]
+    bufs = [b for b in (peer_out, peer_b, peer_c) if b is not None]
 
     def bind_all(stream, xin, yout):
         """-> (launch(i) for step i, tail() that observes the arrival of the last steps)."""
@@ -365,7 +368,7 @@ def run_ours(args, rank, world, local_rank):
             # closing: signal this rank's last step, then wait until every rank has caught up with it
             post = ex.pack.bind("pdk_peer_flags_post", peer_out.flag_ptrs_address(), peer_out.ctr, world, rank, stream=stream)
             wait = ex.pack.bind("pdk_peer_flags_wait", peer_out.flags, world, 0x80000000 | rank, 2000000, stream=stream)
-            return (lambda i: gem[i % n_clones][i & 1]()), (lambda: (post(), wait()))
+            return (lambda i: gem[i % n_clones][i % len(bufs)]()), (lambda: (post(), wait()))
         ls = [ex.pack.bind("kquant_gemv", p.data, p.scales, xin, yout, p.dims[0], p.dims[1], p.ty, stream=stream)
               for p in planes]
         return (lambda i: ls[i % n_clones]()), (lambda: None)
@@ -564,7 +567,7 @@ def run_ours(args, rank, world, local_rank):
             step(i)
             if e2e_tail is not None:
                 e2e_tail()                       # the host reads this step's y: signal it, every band must be here
-            rt.copy(y_dst, y_srcs[(i & 1) % len(y_srcs)], y_bytes, 2, st)
+            rt.copy(y_dst, y_srcs[i % len(y_srcs)], y_bytes, 2, st)
             rt.record(ev, st)
             rt.sync_event(ev)
 

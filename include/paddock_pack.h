@@ -372,13 +372,14 @@ int pdk_q4k_gemv_shard(const void* data, const void* scales, const void* x, cons
 int pdk_q4k_gemv_shard_sync(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
                             const void* const* flag_ptrs, void* ctr, uint32_t n_ranks, uint32_t rank,
                             uint32_t row0, uint32_t step, uint32_t in_dim, uint32_t out_dim, void* stream);
-/* The same for a loop that rotates two or more y buffers, which all share ONE flag array per rank and one
+/* The same for a loop that rotates THREE or more y buffers, which all share ONE flag array per rank and one
  * pair of counter words.  Nothing is signalled at the end of the kernel (the system-scope fence that takes
  * costs an NVLink round trip per step).  Every launch stores, once the stream's previous kernel and its
  * peer stores are complete, the number of the PREVIOUS launch into the flags, and checks before it ends (at
  * most a second; 0x1c << 8 | rank in the device error word for a rank that is late) that every rank's
- * previous step has arrived here: what follows launch s in the stream may read step s - 1 of every rank.
- * The loop needs no wait kernel between steps; pdk_peer_flags_post + pdk_peer_flags_wait close it. */
+ * previous step has arrived here: what sits between launch s and launch s + 1 in the stream may read step
+ * s - 1 of every rank (a peer may already be storing step s + 1, hence three buffers).  The loop needs no
+ * wait kernel between steps; pdk_peer_flags_post + pdk_peer_flags_wait close it. */
 int pdk_q4k_gemv_shard_lagged(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
                               const void* const* flag_ptrs, void* ctr, uint32_t n_ranks, uint32_t rank,
                               uint32_t row0, uint32_t step, uint32_t in_dim, uint32_t out_dim, void* stream);

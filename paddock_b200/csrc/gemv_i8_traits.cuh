@@ -391,8 +391,8 @@ struct IQ4XS {
 // signal == 2 (deferred): nothing is signalled at the end.  Instead thread 0 of CTA 0 stores, at
 // the START of the launch and behind griddepcontrol.wait - when the previous kernel of the stream,
 // peer stores included, is complete - the number of the PREVIOUS launch into the flags (one flag
-// array and one counter shared by all y buffers of the loop), and checks before it leaves that every
-// rank's previous step has arrived here.
+// array and one counter shared by all y buffers of the loop, three or more), and checks before it
+// leaves that every rank's previous step has arrived here.
 struct PeerOut {
     float* ptr[8];
     uint32_t* flag[8];

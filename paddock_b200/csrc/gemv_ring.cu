@@ -975,16 +975,18 @@ PDK_EXPORT int pdk_q4k_gemv_shard_sync(const void* data, const void* scales, con
                         (cudaStream_t)stream);
 }
 
-// The same for a loop that keeps two (or more) y buffers in rotation.  All buffers of the loop share
+// The same for a loop that keeps THREE (or more) y buffers in rotation.  All buffers of the loop share
 // ONE flag array per rank and one pair of counter words.  Nothing is signalled at the end of the
 // kernel (the system-scope fence that takes costs an NVLink round trip per step); instead every launch
 // stores, behind its griddepcontrol.wait - when the stream's previous kernel and its peer stores are
 // complete - the number of the PREVIOUS launch into the flags, and checks before it ends (at most a
 // second; 0x1c << 8 | rank in the error word for a rank that is late) that every rank's previous step has
-// arrived here.  What follows launch s in the stream may therefore read step s - 1 of every rank: one
-// launch per step, consecutive steps overlap like single-GPU launches do, and the arrival of every step
-// is still observed on the device.  After the last launch pdk_peer_flags_post signals it and
-// pdk_peer_flags_wait (step = 0x80000000 | rank) observes it.
+// arrived here.  What sits between launch s and launch s + 1 in the stream may therefore read step s - 1
+// of every rank: a peer can be one launch ahead and already store step s + 1, but its step s + 2 - the
+// first to return to the buffer of s - 1 when there are three - cannot start before this rank's launch
+// s + 1 has begun.  One launch per step, consecutive steps overlap like single-GPU launches do, and the
+// arrival of every step is still observed on the device.  After the last launch pdk_peer_flags_post
+// signals it and pdk_peer_flags_wait (step = 0x80000000 | rank) observes it.
 PDK_EXPORT int pdk_q4k_gemv_shard_lagged(const void* data, const void* scales, const void* x, const void* const* y_ptrs,
                                          const void* const* flag_ptrs, void* ctr, uint32_t n_ranks, uint32_t rank,
                                          uint32_t row0, uint32_t step, uint32_t in_dim, uint32_t out_dim, void* stream) {
