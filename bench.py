@@ -211,8 +211,9 @@ def workload_config(n_gpus, exchange="peer"):
                    "stores before it, no fence inside the kernel) and checks on the device, bounded, that every rank's "
                    "previous step has arrived; the last step is signalled and awaited by two small kernels inside the "
                    "timed region",
-           "peer-serial": "each rank's GEMV stores its band into every rank's y over NVLink (peer memory), then a wait "
-                          "kernel for every rank's flag, then the next step",
+           "peer-serial": "each rank's GEMV stores its band into every rank's y over NVLink (peer memory) and raises its flag "
+                          "at the kernel's end, then a wait kernel for every rank's flag, then the next step (two y buffers "
+                          "in turn)",
            "nccl": "NCCL all-gather of y"}[exchange]
     return {"workload": "Q4_K decode GEMV M=1 K=5120 N=25600, f32 activations holding bf16 values",
             "sharding": "none" if n_gpus == 1 else f"N rows / {n_gpus} ranks, {how}",
@@ -327,6 +328,10 @@ def run_ours(args, rank, world, local_rank):
             # its arrival), a peer that is one launch ahead already stores step s + 1, and only its step s + 2,
             # which it cannot start before this rank's launch s + 1 has begun, returns to the buffer of s - 1
             peer_b, peer_c = shard.PeerOutput(N_DIM), shard.PeerOutput(N_DIM)
+        else:
+            # peer-serial: two buffers in turn, so that a peer that has passed its wait for step s and started
+            # step s + 1 does not store into the y this rank is still reading
+            peer_b = shard.PeerOutput(N_DIM)
         y_all = peer_out.local
         # the two exchanges must agree bit for bit
         ex.kquant_gemv(planes[0], x, y)
@@ -358,13 +363,14 @@ def run_ours(args, rank, world, local_rank):
     def bind_all(stream, xin, yout):
         """-> (launch(i) for step i, tail() that observes the arrival of the last steps)."""
         if peer_out is not None:
-            name = "pdk_q4k_gemv_shard_lagged" if peer_b is not None else "pdk_q4k_gemv_shard_sync"
+            serial = args.exchange == "peer-serial"
+            name = "pdk_q4k_gemv_shard_sync" if serial else "pdk_q4k_gemv_shard_lagged"
             # one flag array and one counter pair (the first buffer's) for every buffer of the loop
             gem = [[ex.pack.bind(name, p.data, p.scales, xin, b.ptrs_address(), peer_out.flag_ptrs_address(), peer_out.ctr,
                                  world, rank, first_row, 0, p.dims[0], p.dims[1], stream=stream) for b in bufs] for p in planes]
-            if peer_b is None:
+            if serial:
                 wait = ex.pack.bind("pdk_peer_flags_wait", peer_out.flags, world, 0, 2000000, stream=stream)
-                return (lambda i: (gem[i % n_clones][0](), wait())), (lambda: None)
+                return (lambda i: (gem[i % n_clones][i % len(bufs)](), wait())), (lambda: None)
             # closing: signal this rank's last step, then wait until every rank has caught up with it
             post = ex.pack.bind("pdk_peer_flags_post", peer_out.flag_ptrs_address(), peer_out.ctr, world, rank, stream=stream)
             wait = ex.pack.bind("pdk_peer_flags_wait", peer_out.flags, world, 0x80000000 | rank, 2000000, stream=stream)
@@ -551,16 +557,16 @@ def run_ours(args, rank, world, local_rank):
         if not torch.equal(yh[(args.steps - 1) % D][:y.numel()], y.cpu()):
             raise RuntimeError("pipelined end-to-end loop returned a different y")
     else:
-        # N > 1: one step in flight (every rank's y is single-buffered: a rank may only run ahead of
-        # its peers' read-back when y is double-buffered and a second, "consumed" signal flows back -
-        # not built); copies and waits through the CUDA runtime directly, as at N = 1.
+        # N > 1: one step in flight - the host reads every step's whole y before it launches the next one; the y
+        # buffers are used in turn as in the timed loop, so a peer that is already a step ahead stores elsewhere;
+        # copies and waits through the CUDA runtime directly, as at N = 1.
         e2e_mode = "1 step in flight: H2D, sharded GEMV + flag wait (or NCCL all-gather), D2H of the full y, host wait"
         rt = Cudart()
         ev = rt.event()
         x_src, x_bytes = x_host.data_ptr(), x_host.numel() * 4
         y_dst, y_bytes = y_host.data_ptr(), y_all.numel() * 4
         y_srcs = [b.local.data_ptr() for b in bufs] or [y_all.data_ptr()]
-        e2e_tail = bound_tail if peer_b is not None else None
+        e2e_tail = bound_tail if (peer_out is not None and args.exchange == "peer") else None
 
         def e2e_step(i):
             rt.copy(x.data_ptr(), x_src, x_bytes, 1, st)
