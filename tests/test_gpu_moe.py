@@ -177,6 +177,20 @@ def test_route_and_prepare_in_one_launch_equals_the_three_calls(pack, tokens, n_
             assert torch.equal(ta.view(torch.uint8), tb.view(torch.uint8)), name
 
 
+def test_route_and_prepare_refuses_what_it_cannot_hold(pack):
+    """More than 8 rows, more than 32 pairs, more than 512 experts, more than 32 blocks, a block size other than
+    8 or 32, a row length that is not whole 32-element blocks: cudaErrorInvalidValue, nothing launched."""
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    args = lambda n_expert, k, rows, dim, bm, max_blocks: (buf, None, buf, buf, buf, buf, buf, buf, buf, buf, buf,
+                                                           n_expert, k, rows, dim, bm, max_blocks)
+    assert pack.status("pdk_moe_route_prep_f4", *args(128, 4, 1, 2880, 8, 4)) == 0
+    for bad in [(128, 4, 9, 2880, 8, 36), (128, 8, 5, 2880, 8, 32), (513, 4, 1, 2880, 8, 4), (128, 4, 8, 2880, 8, 33),
+                (128, 4, 1, 2880, 16, 4), (128, 4, 1, 2880 + 16, 8, 4), (4, 5, 1, 2880, 8, 4), (128, 0, 1, 2880, 8, 4)]:
+        assert pack.status("pdk_moe_route_prep_f4", *args(*bad)) == 1, bad
+    torch.cuda.synchronize()
+    assert pack.device_error() == 0
+
+
 def test_slot_combine_fixed_order(pack):
     rows, k, embd = 7, 4, 64
     part = oracle.fill_normal(rows * k * embd, 820, 1.0)
