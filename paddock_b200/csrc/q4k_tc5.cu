@@ -3,8 +3,8 @@
 // With more than a handful of tokens the per-(block, token) integer fold of q4k_batch_i8.cu
 // outgrows the weight stream.  Here the CUDA cores touch each weight once, whatever the token
 // count: TMA brings the packed bytes and the scale records of 128 rows into a shared-memory
-// ring (four super-block columns in flight per SM), and 8 producer warps turn the nibbles into
-// f16 weights
+// ring (six super-block columns in flight per SM), and producer warps - two sets of 8 that take
+// the columns in turn - turn the nibbles into f16 weights
 //     w = (q - 8) * f16(d * sc) + f16(8 d sc - dmin m)          (two weights per instruction)
 // and store them from registers into tensor memory, where tcgen05.mma kind::f16 takes its A
 // operand (128 weight rows = 128 lanes, 256 K = 128 columns per stage): the dequantized weights
@@ -20,6 +20,11 @@
 // zeroed by the kernel in front, and with exactly two addends per element the sum does not
 // depend on their order.
 //
+// What paces it (cycle counters in every role at 16 tokens): the tensor core.  A kind::f16 MMA with the
+// A operand in tensor memory takes 64 cycles at M128 K16 however few columns (32) it has, 16 of them per
+// column of 128 rows x 256 K: 1030 cycles per column in the issuing warp, 31 k of a CTA's 49 k cycles; the
+// producers spend under 1000 cycles on a column and the TMA ring is waited for 13 % of the time.
+//
 // Precision class: f16-rounded block scales (relative 2^-12, independent per 32-weight block)
 // and one f16 rounding per weight; measured rel-L2 against the f64 product of the dequantized
 // operands is 3e-4, the condition-relative error 3e-5.
@@ -30,15 +35,21 @@
 namespace {
 
 constexpr uint32_t BM = 128;          // weight rows per work item (MMA M)
-constexpr uint32_t kProdWarps = 8;    // dequantizing warps; warps 0..3 also drain the accumulator
-constexpr uint32_t kRawWarp = kProdWarps, kActWarp = kProdWarps + 1, kMmaWarp = kProdWarps + 2;
-constexpr uint32_t kThreads = (kProdWarps + 3) * 32;
+constexpr uint32_t kProdWarps = 8;    // dequantizing warps per unit (super-block column of the tile)
+// Two sets of producer warps take the units in turn (set 0 the even ones, set 1 the odd ones): a
+// producer's chain for a unit - box read, nibble arithmetic, tensor-memory stores, barrier - is
+// latency bound, and a second set gives every scheduler four such chains instead of two.
+// Warps 0..3 (set 0) also drain the accumulator.
+constexpr uint32_t kProdSets = 2;   // one set: 31.6 us at 16 tokens against 29.9
+constexpr uint32_t kAllProd = kProdSets * kProdWarps;
+constexpr uint32_t kRawWarp = kAllProd, kActWarp = kAllProd + 1, kMmaWarp = kAllProd + 2;
+constexpr uint32_t kThreads = (kAllProd + 3) * 32;
 constexpr uint32_t kMaxStages = 3;    // operand stages: one Q4_K super-block column (256 K) of 128 rows
 // Packed weights wait in shared memory, not in registers: a ring of TMA boxes, each two
 // super-block columns of the tile - 2 x [128 rows][128 bytes] (128-byte swizzle, so that the
 // 8 rows of a quarter-warp read fall on distinct banks) and [128 rows][48 bytes] of scale
-// records.  Two boxes = four columns = 76 KB per SM in flight, independent of the producers.
-constexpr uint32_t kRawStages = 2;
+// records.  Three boxes = six columns = 114 KB per SM in flight, independent of the producers.
+constexpr uint32_t kRawStages = 3;
 constexpr uint32_t kRawData = BM * 128u, kRawRec = BM * 48u;
 constexpr uint32_t kRawStageBytes = 2u * kRawData + kRawRec;  // 38912
 constexpr uint32_t kMaxK = 16384;
@@ -47,7 +58,8 @@ constexpr uint32_t kMaxK = 16384;
 // super-block columns travel in the weight ring's boxes (everything the tensor core waits for
 // then arrives long before it is needed; with the tiles fetched per operand stage, the L2 round
 // trip between "stage free" and "stage full" bounded the kernel whatever the producers did).
-// The ring then holds 70 KB per box: it fits for NC = 32 only, NC = 64 fetches per operand stage.
+// The ring then holds 70 KB per box (three boxes: 210 KB): it fits for NC = 32 only, NC = 64 fetches
+// per operand stage.
 template <uint32_t NC>
 struct Cfg {
     static constexpr bool BRAW = NC <= 32u;
@@ -57,7 +69,7 @@ struct Cfg {
     static constexpr uint32_t kStageBytes = BRAW ? 0u : 2u * kBBytes;  // shared-memory stage: the activation tile, if not in the ring
     static constexpr uint32_t kRawBytes = kRawStageBytes + (BRAW ? 4u * kBBytes : 0u);
     static constexpr uint32_t kFullCount = kProdWarps + (BRAW ? 0u : 1u);
-    static constexpr uint32_t kRawEmptyCount = kProdWarps + (BRAW ? 1u : 0u);
+    static constexpr uint32_t kRawEmptyCount = 2u * kProdWarps + (BRAW ? 1u : 0u);   // kProdWarps arrivals per unit of a box
     static constexpr uint32_t kACol0 = 2u * NC;                      // after the two accumulators
     static constexpr uint32_t kACols = 128u;                         // per stage: 256 K as f16 pairs
     static constexpr uint32_t kTmemCols = 512u;                      // 2 NC + kStages * 128 <= 512
@@ -239,15 +251,28 @@ __device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // A operand from tensor memory (row i of the 128 in lane i, two f16 of consecutive k per
-// 32-bit column), B operand from shared memory
-__device__ __forceinline__ void mma_f16_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                                 uint32_t accumulate) {
-    asm volatile(TC5_ELECT
-                 ".reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-                 : "memory");
+// 32-bit column), B operand from shared memory.
+// The sixteen MMAs of one unit (256 K = four 64-element B slabs x four K16 steps) from ONE asm block with
+// one election: a_tmem steps by 8 columns per K16 step and 32 per slab, the B descriptor by 32 bytes per
+// step and b_slab16 (the slab pitch in 16-byte units) per slab.  One wrapper call per MMA - its own
+// elect.sync and predicate set-up - cost the issuing warp about 130 cycles each, 2100 per unit, which was
+// what paced the whole kernel; the tensor core needs 16 per M128 N32 K16 step.
+__device__ __forceinline__ void mma_f16_ts_unit_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                      uint32_t acc_first, uint64_t b_slab16) {
+#define PDK_TS_STEP(J, K, PRED)                                                                      \
+    "add.u32 a, %1, " #J "*32+" #K "*8;\n\tmad.lo.u64 b, %5, " #J ", %2;\n\tadd.u64 b, b, " #K "*2;\n\t" \
+    "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, " PRED ";\n\t"
+#define PDK_TS_SLAB(J, PRED0) PDK_TS_STEP(J, 0, PRED0) PDK_TS_STEP(J, 1, "q") PDK_TS_STEP(J, 2, "q") PDK_TS_STEP(J, 3, "q")
+    asm volatile(
+        "{\n\t.reg .pred e, p, q;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        PDK_TS_SLAB(0, "p") PDK_TS_SLAB(1, "q") PDK_TS_SLAB(2, "q") PDK_TS_SLAB(3, "q") "}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc_first), "l"(b_slab16)
+        : "memory");
+#undef PDK_TS_SLAB
+#undef PDK_TS_STEP
 }
 
 // The two f16x2 multipliers and offsets of a k-slab (blocks 2G, 2G+1): w = s * (q - 8) + o, the
@@ -343,30 +368,32 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
     const tc5::WaitCtx ctx{&sh->abort_flag, err_word};
     pdk_pdl_launch_dependents();
 
-    if (warp < kProdWarps) {
+    if (warp < kAllProd) {
         // ------------------------------------------------------------ dequantizing producers
         // A thread owns one row of the tile - the tensor-memory lane its warp may write: warp w
-        // serves lanes 32 (w % 4).. - and, per unit, half of its 256 K (hf = w / 4): the four
+        // serves lanes 32 (w % 4).. - and, per unit, half of its 256 K (hf): the four
         // 16-byte chunks 4 hf .. 4 hf + 3 of the row's packed bytes, i.e. k-slabs G = 2 hf, 2 hf + 1.
         // The f16 pairs go straight from registers into the A operand's tensor-memory columns:
         // no shared-memory copy of the dequantized weights, nothing for the tensor core to
         // fetch but the small activation tile, and one barrier round per 128 weights of a row.
         // The 8 lanes of a quarter-warp hold 8 consecutive rows: their 16-byte reads of the
         // swizzled weight box fall on 8 different chunk positions.
-        const uint32_t qd = warp & 3u, hf = warp >> 2;
+        const uint32_t set = warp / kProdWarps, pw = warp % kProdWarps;
+        const uint32_t qd = pw & 3u, hf = pw >> 2;
         const uint32_t r_in = qd * 32u + lane, swz = r_in & 7u;
         const uint32_t line_off = (r_in >> 3) * 1024u + swz * 128u;  // the row's 128-byte line in a weight box
         const uint32_t my_items = blockIdx.x < n_items ? (n_items - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
         const uint32_t total = my_items * upi;
-        uint32_t stage = 0, phase = 0, rs = 0, rphase = 0, c_u = 0, c_item = blockIdx.x, iter = 0;
         bool ok = true;
-        for (uint32_t n = 0; n < total && ok; ++n) {
-            const uint32_t j = n & 1u;  // unit j of the box
-            if (j == 0u) {
-                ok = mbar_wait_park(&sh->raw_full[rs], rphase, ctx, tc5::kErrFullWait, 0x20u + rs);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-            }
+        // unit n of this CTA's sequence: box n / 2 (unit n % 2 of it: upi is even, so that is the set), operand
+        // stage n % kStages
+        for (uint32_t n = set; n < total && ok; n += kProdSets) {
+            const uint32_t j = n & 1u, box = n >> 1;
+            const uint32_t rs = box % kRawStages, rphase = (box / kRawStages) & 1u;
+            const uint32_t stage = n % kStages, phase = (n / kStages) & 1u;
+            ok = mbar_wait_park(&sh->raw_full[rs], rphase, ctx, tc5::kErrFullWait, 0x20u + rs);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             const uint8_t* raw = ring + rs * C::kRawBytes;
             uint4 q[4];
 #pragma unroll
@@ -400,14 +427,13 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
             __syncwarp();
             if (lane == 0) {
                 tc5::mbar_arrive(&sh->full[stage]);
-                if (j == 1u) tc5::mbar_arrive(&sh->raw_empty[rs]);  // every lane has consumed its bytes of the box
+                tc5::mbar_arrive(&sh->raw_empty[rs]);  // every lane has consumed its bytes of the box
             }
-            if (++stage == kStages) { stage = 0; phase ^= 1u; }
-            if (j == 1u && ++rs == kRawStages) { rs = 0; rphase ^= 1u; }
-            if (++c_u == upi) {
-                // ---- the item's last unit is written: warps 0..3 drain its accumulator
-                c_u = 0;
-                if (warp < 4u) {
+            if (n % upi + kProdSets >= upi && warp < 4u) {
+                // ---- set 0 has written its last unit of the item: warps 0..3 drain the item's accumulator
+                // (full once set 1's last unit has gone through the tensor core too)
+                {
+                    const uint32_t iter = n / upi, c_item = blockIdx.x + iter * gridDim.x;
                     const uint32_t buf = iter & 1u, aphase = (iter >> 1) & 1u;
                     if (iter == 0u) pdk_pdl_wait();  // tokscale and the zeroed y are the previous kernel's output
                     ok = mbar_wait_park(&sh->tmem_full[buf], aphase, ctx, tc5::kErrTmemFullWait, buf);
@@ -436,8 +462,6 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                     __syncwarp();
                     if (lane == 0) tc5::mbar_arrive(&sh->tmem_empty[buf]);
                 }
-                c_item += gridDim.x;
-                ++iter;
             }
         }
     } else if (warp == kRawWarp) {
@@ -518,13 +542,8 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 const uint32_t a_tmem = tmem_base + C::kACol0 + stage * C::kACols;
                 const uint32_t b_addr = C::BRAW ? tc5::smem_u32(ring + rs * C::kRawBytes + kRawStageBytes) + (u & 1u) * 2u * C::kBBytes
                                                 : tc5::smem_u32(tiles + stage * C::kStageBytes);
-#pragma unroll
-                for (uint32_t j = 0; j < 4u; ++j) {
-                    const uint64_t b_desc = tc5::smem_desc_sw128(b_addr + j * C::kBSlab);
-#pragma unroll
-                    for (uint32_t k = 0; k < 4u; ++k)  // 16 f16 of K per instruction: 8 columns of A, 32 bytes of B
-                        mma_f16_ts_elect(d_tmem, a_tmem + j * 32u + k * 8u, b_desc + 2u * k, C::kIdesc, (u | j | k) != 0u);
-                }
+                // 16 f16 of K per instruction: 8 columns of A, 32 bytes of B
+                mma_f16_ts_unit_elect(d_tmem, a_tmem, tc5::smem_desc_sw128(b_addr), C::kIdesc, u != 0u, (uint64_t)(C::kBSlab >> 4));
                 tc5::mma_commit_elect(&sh->empty[stage]);
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 if (C::BRAW && (u & 1u) == 1u) {  // the box's activation tiles have been read
