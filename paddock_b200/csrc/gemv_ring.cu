@@ -191,15 +191,16 @@ gemv_ring_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant
     // (tile, pair) number i of this warp -> stage i % D; issue = arm the barrier, then the copies.
     // Called by the whole (converged) warp: one elected lane issues, so addresses and the
     // tensor-map pointers stay in uniform registers.
+    const uint64_t stream_once = tc5::l2_policy_evict_first();   // a plane is read once per launch
     auto issue = [&](uint32_t stage, uint32_t tl, uint32_t pr) {
         uint64_t* bar = my_full + stage;
         tc5::mbar_arrive_expect_tx_elect(bar, kStageData + kStageRec);
         const int32_t row = (int32_t)((tile_lo + tl) * 16u);
 #pragma unroll
         for (uint32_t b = 0; b < 2u * F::kDataBoxes; ++b)
-            tc5::tma_load_2d_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
-                                   (int32_t)(pr * 2u * F::kDataBytes + b * 128u), row);
-        tc5::tma_load_2d_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(pr * kRecRow), row);
+            tc5::tma_load_2d_hint_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
+                                        (int32_t)(pr * 2u * F::kDataBytes + b * 128u), row, stream_once);
+        tc5::tma_load_2d_hint_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(pr * kRecRow), row, stream_once);
     };
 
     // ---- prologue: every warp arms its own barriers and requests its first D stages; only then
@@ -594,15 +595,16 @@ gemm_ring_q8_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_const
     uint8_t* my_data = smem + pl.off_data + (size_t)warp * D * kStageData;
     uint8_t* my_rec = smem + pl.off_rec + (size_t)warp * D * kStageRec;
 
+    const uint64_t stream_once = tc5::l2_policy_evict_first();   // the plane is read once per launch
     auto issue = [&](uint32_t stage, uint32_t tl) {
         uint64_t* bar = my_full + stage;
         tc5::mbar_arrive_expect_tx_elect(bar, kStageData + kStageRec);
         const int32_t row = (int32_t)((tile_lo + tl) * 16u);
 #pragma unroll
         for (uint32_t b = 0; b < 4u; ++b)
-            tc5::tma_load_2d_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
-                                   (int32_t)(warp * 2u * Q80::kDataBytes + b * 128u), row);
-        tc5::tma_load_2d_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(warp * kRecRow), row);
+            tc5::tma_load_2d_hint_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
+                                        (int32_t)(warp * 2u * Q80::kDataBytes + b * 128u), row, stream_once);
+        tc5::tma_load_2d_hint_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(warp * kRecRow), row, stream_once);
     };
 
     if (lane == 0u) {

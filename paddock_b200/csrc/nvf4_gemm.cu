@@ -153,15 +153,22 @@ nvf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         };
         // weight half of a stage: the expected bytes of the whole stage, the W boxes and their
         // scale records (consecutive slabs' records are contiguous: one bulk copy)
+        const uint64_t stream_once = tc5::l2_policy_evict_first();
         auto issue_w = [&](uint32_t stg, uint32_t tile_w, uint32_t ks) {
             uint8_t* a = tiles + stg * kStageBytes;
             const uint32_t kb0 = ks * KS, nsl = min(KS, num_kb - kb0);
             tc5::mbar_arrive_expect_tx_elect(&sh->full[stg], nsl * (kABytes + kBBytes + kSfBytes + (XT ? kSfBytes : 0u)));
 #pragma unroll
             for (uint32_t u = 0; u < KS; ++u)
-                if (u < nsl)
-                    tc5::tma_load_2d_elect(a + u * kABytes, &tmap_w, &sh->full[stg], (int32_t)((kb0 + u) * BKB),
-                                           (int32_t)(tile_w * BM));
+                if (u < nsl) {
+                    // decode widths have one token tile: a weight box is read once per launch and need not stay in L2
+                    if constexpr (BN < 128u)
+                        tc5::tma_load_2d_hint_elect(a + u * kABytes, &tmap_w, &sh->full[stg], (int32_t)((kb0 + u) * BKB),
+                                                    (int32_t)(tile_w * BM), stream_once);
+                    else
+                        tc5::tma_load_2d_elect(a + u * kABytes, &tmap_w, &sh->full[stg], (int32_t)((kb0 + u) * BKB),
+                                               (int32_t)(tile_w * BM));
+                }
             tc5::bulk_load_elect(a + kOffSfa, w_sf_tiled + ((size_t)tile_w * num_kb + kb0) * kSfBytes, nsl * kSfBytes,
                                  &sh->full[stg]);
         };

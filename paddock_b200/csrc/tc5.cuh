@@ -124,6 +124,21 @@ __device__ __forceinline__ void tma_load_2d_elect(void* smem_dst, const CUtensor
                  "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y)
                  : "memory");
 }
+// The same with an L2 eviction-priority hint (a createpolicy value): evict_first for planes that are
+// streamed once per launch.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tma_load_2d_hint_elect(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int32_t x,
+                                                       int32_t y, uint64_t policy) {
+    asm volatile(TC5_ELECT
+                 "@e cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], "
+                 "[%1, {%3, %4}], [%2], %5;\n\t}" ::"r"(smem_u32(smem_dst)),
+                 "l"(m), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_load_elect(void* smem_dst, const void* gmem, uint32_t bytes, uint64_t* bar) {
     asm volatile(TC5_ELECT
                  "@e cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}" ::"r"(
