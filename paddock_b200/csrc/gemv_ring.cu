@@ -572,7 +572,8 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t saddr, uint32_t& r0, uint32
 __global__ void __launch_bounds__(kMaxWarps * 32u, 1)
 gemm_ring_q8_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_constant__ CUtensorMap rmap,
                     const float* __restrict__ bias, const float* __restrict__ x, float* __restrict__ y, uint32_t in_dim,
-                    uint32_t out_dim, uint32_t batch, const BatchPlan pl, unsigned int* __restrict__ err) {
+                    uint32_t out_dim, uint32_t batch, const BatchPlan pl, unsigned int* __restrict__ err,
+                    const uint32_t last_pass) {
     constexpr uint32_t kUnitData = 2u * kBoxBytes;             // a unit's two boxes (blocks 0..3 | 4..7)
     constexpr uint32_t kRecRow = 2u * Q80::kRecBytes;          // a pair's records of one row
     constexpr uint32_t kStageData = 2u * kUnitData, kStageRec = 16u * kRecRow;
@@ -595,16 +596,26 @@ gemm_ring_q8_kernel(const __grid_constant__ CUtensorMap dmap, const __grid_const
     uint8_t* my_data = smem + pl.off_data + (size_t)warp * D * kStageData;
     uint8_t* my_rec = smem + pl.off_rec + (size_t)warp * D * kStageRec;
 
-    const uint64_t stream_once = tc5::l2_policy_evict_first();   // the plane is read once per launch
+    // The call's last pass over the plane loads it evict-first (nothing reads it again); an earlier pass
+    // of a call with more than eight tokens leaves what fits in L2 to the pass that follows.
+    const uint64_t stream_once = tc5::l2_policy_evict_first();
     auto issue = [&](uint32_t stage, uint32_t tl) {
         uint64_t* bar = my_full + stage;
         tc5::mbar_arrive_expect_tx_elect(bar, kStageData + kStageRec);
         const int32_t row = (int32_t)((tile_lo + tl) * 16u);
+        if (last_pass) {
 #pragma unroll
-        for (uint32_t b = 0; b < 4u; ++b)
-            tc5::tma_load_2d_hint_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
-                                        (int32_t)(warp * 2u * Q80::kDataBytes + b * 128u), row, stream_once);
-        tc5::tma_load_2d_hint_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(warp * kRecRow), row, stream_once);
+            for (uint32_t b = 0; b < 4u; ++b)
+                tc5::tma_load_2d_hint_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
+                                            (int32_t)(warp * 2u * Q80::kDataBytes + b * 128u), row, stream_once);
+            tc5::tma_load_2d_hint_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(warp * kRecRow), row, stream_once);
+        } else {
+#pragma unroll
+            for (uint32_t b = 0; b < 4u; ++b)
+                tc5::tma_load_2d_elect(my_data + stage * kStageData + b * kBoxBytes, &dmap, bar,
+                                       (int32_t)(warp * 2u * Q80::kDataBytes + b * 128u), row);
+            tc5::tma_load_2d_elect(my_rec + stage * kStageRec, &rmap, bar, (int32_t)(warp * kRecRow), row);
+        }
     };
 
     if (lane == 0u) {
@@ -866,7 +877,7 @@ int pdk_q8_0_gemm_i8(const void* data, const void* scale, const float* bias, con
         const uint32_t nb = batch - t0 < 8u ? batch - t0 : 8u;
         const int rc = pdk_launch_pdl(gemm_ring_q8_kernel, dim3(grid), dim3(pl.W * 32u), (size_t)pl.smem_bytes, st, maps->dmap,
                                       maps->rmap, bias, x + (size_t)t0 * in_dim, y + (size_t)t0 * out_dim, in_dim, out_dim,
-                                      nb, pl, err);
+                                      nb, pl, err, t0 + 8u >= batch ? 1u : 0u);
         if (rc != 0) return rc;
     }
     return 0;
