@@ -109,23 +109,6 @@ __device__ __forceinline__ uint2 pdk_ldg_stream8(const void* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
     return r;
 }
-// The same with an L2 eviction-priority hint: planes that a launch reads exactly once are loaded
-// evict-first, so they do not push the activations and the output out of L2 on their way through.
-__device__ __forceinline__ uint64_t pdk_l2_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ uint2 pdk_ldg_once8(const void* p, uint64_t policy) {
-    uint2 r;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v2.u32 {%0,%1}, [%2], %3;" : "=r"(r.x), "=r"(r.y) : "l"(p), "l"(policy));
-    return r;
-}
-__device__ __forceinline__ uint32_t pdk_ldg_once4(const void* p, uint64_t policy) {
-    uint32_t r;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(r) : "l"(p), "l"(policy));
-    return r;
-}
 __device__ __forceinline__ uint32_t pdk_ldg_stream4(const void* p) {
     uint32_t r;
     asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));

@@ -57,15 +57,15 @@ struct Stage {
 
 template <bool K5>
 __device__ __forceinline__ void load_stage(Stage& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
-                                           const uint8_t* r1, uint32_t t, uint64_t once) {
+                                           const uint8_t* r1, uint32_t t) {
 #pragma unroll
     for (uint32_t G = 0; G < 4u; ++G) {
-        s.q0[G] = pdk_ldg_once8(d0 + G * 32u + t * 8u, once);
-        s.q1[G] = pdk_ldg_once8(d1 + G * 32u + t * 8u, once);
+        s.q0[G] = pdk_ldg_stream8(d0 + G * 32u + t * 8u);
+        s.q1[G] = pdk_ldg_stream8(d1 + G * 32u + t * 8u);
     }
     if constexpr (K5) {
-        s.h0 = pdk_ldg_once8(d0 + 128u + t * 8u, once);
-        s.h1 = pdk_ldg_once8(d1 + 128u + t * 8u, once);
+        s.h0 = pdk_ldg_stream8(d0 + 128u + t * 8u);
+        s.h1 = pdk_ldg_stream8(d1 + 128u + t * 8u);
     }
     const uint32_t* w0 = reinterpret_cast<const uint32_t*>(r0);
     const uint32_t* w1 = reinterpret_cast<const uint32_t*>(r1);
@@ -217,7 +217,6 @@ q4k_batch_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict_
     const uint32_t len = u_hi - u_lo;
     constexpr uint32_t kUnitBytes = K5 ? 160u : 128u;
     const size_t row_data = (size_t)n_unit * kUnitBytes, row_rec = (size_t)n_unit * 24u;
-    const uint64_t once = pdk_l2_evict_first();   // the plane is read once per launch
 
     // slot-major tile numbering, as in the decode GEMV
     const uint32_t tile0 = slot * gridDim.x + blockIdx.x, tile_stride = gridDim.x * kSlots;
@@ -236,7 +235,7 @@ q4k_batch_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict_
     };
     auto issue = [&](Stage& s) {
         load_stage<K5>(s, p0 + (size_t)l_u * kUnitBytes, p1 + (size_t)l_u * kUnitBytes, r0 + (size_t)l_u * 24u,
-                       r1 + (size_t)l_u * 24u, t, once);
+                       r1 + (size_t)l_u * 24u, t);
         if (++l_u == u_hi) {
             l_u = u_lo;
             l_tile += tile_stride;
@@ -409,7 +408,7 @@ struct Stage6 {
 };
 
 __device__ __forceinline__ void load_stage6(Stage6& s, const uint8_t* d0, const uint8_t* d1, const uint8_t* r0,
-                                            const uint8_t* r1, uint32_t t, uint64_t once) {
+                                            const uint8_t* r1, uint32_t t) {
     const uint8_t* dp[2] = {d0, d1};
     const uint8_t* rp[2] = {r0, r1};
 #pragma unroll
@@ -418,9 +417,9 @@ __device__ __forceinline__ void load_stage6(Stage6& s, const uint8_t* d0, const 
         for (uint32_t nh = 0; nh < 2u; ++nh) {
 #pragma unroll
             for (uint32_t h = 0; h < 2u; ++h) {
-                s.ql[w][nh][0][h] = pdk_ldg_once4(dp[w] + nh * 64u + h * 16u + t * 4u, once);
-                s.ql[w][nh][1][h] = pdk_ldg_once4(dp[w] + nh * 64u + 32u + h * 16u + t * 4u, once);
-                s.qh[w][nh][h] = pdk_ldg_once4(dp[w] + 128u + nh * 32u + h * 16u + t * 4u, once);
+                s.ql[w][nh][0][h] = pdk_ldg_stream4(dp[w] + nh * 64u + h * 16u + t * 4u);
+                s.ql[w][nh][1][h] = pdk_ldg_stream4(dp[w] + nh * 64u + 32u + h * 16u + t * 4u);
+                s.qh[w][nh][h] = pdk_ldg_stream4(dp[w] + 128u + nh * 32u + h * 16u + t * 4u);
             }
         }
         s.d[w] = __ldg(reinterpret_cast<const uint16_t*>(rp[w]));
@@ -455,7 +454,6 @@ q6k_batch_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict_
     const uint32_t u_lo = slice * n_unit / kSlices, u_hi = (slice + 1u) * n_unit / kSlices;
     const uint32_t len = u_hi - u_lo;
     const size_t row_data = (size_t)n_unit * 192u, row_rec = (size_t)n_unit * 24u;
-    const uint64_t once = pdk_l2_evict_first();   // the plane is read once per launch
     const uint32_t tile0 = slot * gridDim.x + blockIdx.x, tile_stride = gridDim.x * kSlots;
     const uint32_t my_tiles = tile0 < n_tiles ? (n_tiles - tile0 + tile_stride - 1u) / tile_stride : 0u;
     const uint32_t total = my_tiles * len;
@@ -470,7 +468,7 @@ q6k_batch_i8_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict_
         r1 = recs + rb * row_rec;
     };
     auto issue = [&](Stage6& s) {
-        load_stage6(s, p0 + (size_t)l_u * 192u, p1 + (size_t)l_u * 192u, r0 + (size_t)l_u * 24u, r1 + (size_t)l_u * 24u, t, once);
+        load_stage6(s, p0 + (size_t)l_u * 192u, p1 + (size_t)l_u * 192u, r0 + (size_t)l_u * 24u, r1 + (size_t)l_u * 24u, t);
         if (++l_u == u_hi) {
             l_u = u_lo;
             l_tile += tile_stride;

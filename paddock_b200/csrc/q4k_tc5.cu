@@ -469,7 +469,6 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
         // Weights depend on nothing the previous kernel in the stream writes: no wait for it.
         uint32_t rs = 0, rphase = 0;
         bool ok = true, waited = false;
-        const uint64_t stream_once = tc5::l2_policy_evict_first();
         for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const uint32_t row0 = (item / ksplit) * BM, u0 = (item % ksplit) * upi;
             for (uint32_t u = 0; u < upi; u += 2u) {
@@ -478,12 +477,9 @@ q4k_tc5_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant
                 if (!ok) break;
                 uint8_t* raw = ring + rs * C::kRawBytes;
                 tc5::mbar_arrive_expect_tx_elect(&sh->raw_full[rs], C::kRawBytes);
-                // the plane is read once per launch: evict-first in L2
-                tc5::tma_load_2d_hint_elect(raw, &tmap_w, &sh->raw_full[rs], (int32_t)((u0 + u) * 128u), (int32_t)row0, stream_once);
-                tc5::tma_load_2d_hint_elect(raw + kRawData, &tmap_w, &sh->raw_full[rs], (int32_t)((u0 + u + 1u) * 128u), (int32_t)row0,
-                                            stream_once);
-                tc5::tma_load_2d_hint_elect(raw + 2u * kRawData, &tmap_r, &sh->raw_full[rs], (int32_t)((u0 + u) * 24u), (int32_t)row0,
-                                            stream_once);
+                tc5::tma_load_2d_elect(raw, &tmap_w, &sh->raw_full[rs], (int32_t)((u0 + u) * 128u), (int32_t)row0);
+                tc5::tma_load_2d_elect(raw + kRawData, &tmap_w, &sh->raw_full[rs], (int32_t)((u0 + u + 1u) * 128u), (int32_t)row0);
+                tc5::tma_load_2d_elect(raw + 2u * kRawData, &tmap_r, &sh->raw_full[rs], (int32_t)((u0 + u) * 24u), (int32_t)row0);
                 if (C::BRAW) {
                     if (!waited) {  // the f16 rows are the previous kernel's output; the weights above are not
                         pdk_pdl_wait();
