@@ -87,3 +87,55 @@ def wait_for_peers(ex, out, budget_us=200000, stream=None):
     import torch
     st = torch.cuda.current_stream().cuda_stream if stream is None else stream
     ex.pack.call("pdk_peer_flags_wait", out.flags, out.world, 0, budget_us, stream=st)
+
+
+class LaggedLoop:
+    """A decode loop over the row-sharded Q4_K GEMV with the deferred completion signal
+    (pdk_q4k_gemv_shard_lagged): one launch per step and no fence inside it.  The loop owns its y buffers -
+    three or more, used in turn, because a peer may be one launch ahead and already store step s + 1 while
+    this rank reads step s - 1 - and the one flag array / counter pair they share.
+
+        loop = LaggedLoop(ex, n_rows, first_row)
+        for x in activations:
+            y_prev = loop.launch(w, x)     # step s goes out; y_prev = the whole y of step s - 1 (None at first),
+            ...                            # valid for work queued on the stream before the next launch
+        y_last = loop.close()              # signals and awaits the last step
+
+    `buffers` may be given (objects with ptrs_address(), flag_ptrs_address(), ctr, flags, local, world, rank:
+    PeerOutput, or stand-ins in tests)."""
+
+    def __init__(self, ex, n_rows, first_row, n_buffers=3, buffers=None):
+        if buffers is None:
+            if n_buffers < 3:
+                raise ValueError("the deferred signal needs three or more y buffers")
+            buffers = [PeerOutput(n_rows) for _ in range(n_buffers)]
+        if len(buffers) < 3:
+            raise ValueError("the deferred signal needs three or more y buffers")
+        self.ex, self.bufs, self.first_row = ex, list(buffers), first_row
+        self.chan = self.bufs[0]
+        self.world, self.rank = self.chan.world, self.chan.rank
+        self.steps = 0
+
+    def _stream(self, stream):
+        if stream is not None:
+            return stream
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+
+    def launch(self, w, x, stream=None):
+        b = self.bufs[self.steps % len(self.bufs)]
+        self.ex.pack.call("pdk_q4k_gemv_shard_lagged", w.data, w.scales, x, b.ptrs_address(), self.chan.flag_ptrs_address(),
+                          self.chan.ctr, self.world, self.rank, self.first_row, 0, w.dims[0], w.dims[1],
+                          stream=self._stream(stream))
+        self.steps += 1
+        return self.bufs[(self.steps - 2) % len(self.bufs)].local if self.steps >= 2 else None
+
+    def close(self, budget_us=2000000, stream=None):
+        """Signals this rank's last step and waits (on the device, bounded) until every rank has caught up
+        with it; returns the last step's y, or None if nothing was launched."""
+        if self.steps == 0:
+            return None
+        st = self._stream(stream)
+        self.ex.pack.call("pdk_peer_flags_post", self.chan.flag_ptrs_address(), self.chan.ctr, self.world, self.rank, stream=st)
+        self.ex.pack.call("pdk_peer_flags_wait", self.chan.flags, self.world, 0x80000000 | self.rank, budget_us, stream=st)
+        return self.bufs[(self.steps - 1) % len(self.bufs)].local

@@ -35,20 +35,16 @@ def worker(rank, world, port, out_path):
     raw = synth.quantize_q4_k(synth.normal(rows * K_DIM, 0x51 + rank, 0.02, dev))
     plane = ex.repack_kquant_raw(raw, K_DIM, rows)
     xs = [synth.bf16_round(synth.normal(K_DIM, 0x77 + s, 1.0, "cpu")).to(dev) for s in range(STEPS)]
-    # three buffers: a peer one launch ahead stores step s + 1 while this rank still reads step s - 1
-    bufs = [shard.PeerOutput(N_DIM) for _ in range(3)]
-    chan = bufs[0]                               # one flag array and counter pair for the whole loop
-    st = torch.cuda.current_stream().cuda_stream
+    # shard.LaggedLoop owns three y buffers (a peer one launch ahead stores step s + 1 while this rank still
+    # reads step s - 1) and the flag array / counters they share
+    loop = shard.LaggedLoop(ex, N_DIM, first_row)
+    chan = loop.chan
     seen = []
     for s in range(STEPS):
-        b = bufs[s % 3]
-        ex.pack.call("pdk_q4k_gemv_shard_lagged", plane.data, plane.scales, xs[s], b.ptrs_address(), chan.flag_ptrs_address(),
-                     chan.ctr, world, rank, first_row, 0, K_DIM, rows, stream=st)
-        if s >= 1:                               # what follows launch s may read step s - 1 of every rank
-            seen.append(bufs[(s - 1) % 3].local.clone())
-    ex.pack.call("pdk_peer_flags_post", chan.flag_ptrs_address(), chan.ctr, world, rank, stream=st)
-    ex.pack.call("pdk_peer_flags_wait", chan.flags, world, 0x80000000 | rank, 2000000, stream=st)
-    seen.append(bufs[(STEPS - 1) % 3].local.clone())
+        y_prev = loop.launch(plane, xs[s])
+        if y_prev is not None:                   # what follows launch s may read step s - 1 of every rank
+            seen.append(y_prev.clone())
+    seen.append(loop.close().clone())
     torch.cuda.synchronize()
     err = ex.pack.device_error()
     flags = chan.flags[:world].tolist()
@@ -56,7 +52,7 @@ def worker(rank, world, port, out_path):
     ok = err == 0 and flags == [STEPS] * world
     y = torch.zeros(rows, dtype=torch.float32, device=dev)
     for s in range(STEPS):
-        ex.pack.call("kquant_gemv", plane.data, plane.scales, xs[s], y, K_DIM, rows, 12, stream=st)
+        ex.pack.call("kquant_gemv", plane.data, plane.scales, xs[s], y, K_DIM, rows, 12)
         full = torch.zeros(N_DIM, dtype=torch.float32, device=dev)
         full[first_row:first_row + rows] = y
         dist.all_reduce(full)                    # disjoint bands: the sum is the concatenation, bit for bit

@@ -54,3 +54,55 @@ def test_band_helpers():
     import pytest
     with pytest.raises(ValueError):
         shard.row_band(100, 8, 0)
+
+
+class _FakeBuffer:
+    def __init__(self, tag, world=2, rank=1):
+        self.tag, self.world, self.rank = tag, world, rank
+        self.ctr, self.flags, self.local = f"ctr{tag}", f"flags{tag}", f"y{tag}"
+
+    def ptrs_address(self):
+        return f"ptrs{self.tag}"
+
+    def flag_ptrs_address(self):
+        return f"flagptrs{self.tag}"
+
+
+class _FakeExecutor:
+    class _Pack:
+        def __init__(self):
+            self.calls = []
+
+        def call(self, name, *args, stream=None):
+            self.calls.append((name, args, stream))
+
+    def __init__(self):
+        self.pack = self._Pack()
+
+
+class _FakePlane:
+    data, scales, dims = "data", "scales", (512, 64)
+
+
+def test_lagged_loop_rotates_three_buffers_over_one_flag_channel():
+    """Host side of the deferred-signal loop: y buffers in turn, every launch on the first buffer's flag array and
+    counters, the previous step's y handed back, post + wait at the end; fewer than three buffers refused."""
+    import pytest
+    ex = _FakeExecutor()
+    bufs = [_FakeBuffer(i) for i in range(3)]
+    loop = shard.LaggedLoop(ex, 128, 64, buffers=bufs)
+    seen = [loop.launch(_FakePlane, f"x{s}", stream=7) for s in range(5)]
+    assert seen == [None, "y0", "y1", "y2", "y0"]
+    names = [c[0] for c in ex.pack.calls]
+    assert names == ["pdk_q4k_gemv_shard_lagged"] * 5
+    for s, (_, args, stream) in enumerate(ex.pack.calls):
+        data, scales, x, yptrs, flagptrs, ctr, world, rank, row0, step, in_dim, out_dim = args
+        assert (x, yptrs, flagptrs, ctr) == (f"x{s}", f"ptrs{s % 3}", "flagptrs0", "ctr0")
+        assert (world, rank, row0, step, in_dim, out_dim, stream) == (2, 1, 64, 0, 512, 64, 7)
+    assert loop.close(stream=7) == "y1"                      # step 5 went into buffer 4 % 3
+    assert [c[0] for c in ex.pack.calls[5:]] == ["pdk_peer_flags_post", "pdk_peer_flags_wait"]
+    assert ex.pack.calls[5][1] == ("flagptrs0", "ctr0", 2, 1)
+    assert ex.pack.calls[6][1] == ("flags0", 2, 0x80000000 | 1, 2000000)
+    with pytest.raises(ValueError):
+        shard.LaggedLoop(ex, 128, 64, buffers=bufs[:2])
+    assert shard.LaggedLoop(ex, 128, 64, buffers=bufs).close() is None
